@@ -1,0 +1,213 @@
+/*
+ * quixicore_cuda.h - C ABI of the B200 (sm_100a) backend for the QuixiCore quantized
+ * decode-projection path: decode_linear_epilogue, decode_swiglu, fused lm_head_sample and the
+ * runtime output quantizers.
+ *
+ * Plain C: pointers, sizes and PODs only.  No exception crosses this boundary; every entry point
+ * returns a qx_status whose `operation` / `detail` strings are static (never freed by the caller).
+ * All device pointers must belong to the CUDA device that is current on the calling thread.
+ * Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default
+ * stream) and no entry point synchronises the host, so results are valid after the caller
+ * synchronises that stream.  There is no CPU fallback: without a usable CUDA device the calls
+ * return QX_RUNTIME_ERROR.
+ *
+ * Each declaration cites the reference interface it stands in for (path:line inside the
+ * QuixiCore-Metal project).  The reference has no C binding of its own (bindings/c is empty);
+ * the generic call structs mirror its cross-backend contract header
+ * include/quixicore/contract/kernel_abi.hpp:10-107 field for field.
+ */
+#ifndef QUIXICORE_CUDA_H
+#define QUIXICORE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status (kernel_abi.hpp:10-31) ---------------------------------------------------------- */
+typedef enum qx_status_code {
+  QX_OK = 0,
+  QX_INVALID_ARGUMENT,
+  QX_INVALID_SHAPE,
+  QX_UNSUPPORTED_DTYPE,
+  QX_UNSUPPORTED_FORMAT,
+  QX_UNSUPPORTED_LAYOUT,
+  QX_INSUFFICIENT_WORKSPACE,
+  QX_ADAPTER_NOT_WIRED,
+  QX_NOT_IMPLEMENTED,
+  QX_RUNTIME_ERROR
+} qx_status_code;
+
+typedef struct qx_status {
+  qx_status_code code;
+  const char* operation;
+  const char* detail;
+} qx_status;
+
+/* ---- element types (kernel_abi.hpp:33-51) ---------------------------------------------------- */
+typedef enum qx_dtype {
+  QX_DTYPE_UNKNOWN = 0, QX_DTYPE_BOOL, QX_DTYPE_I8, QX_DTYPE_U8, QX_DTYPE_I16, QX_DTYPE_U16,
+  QX_DTYPE_I32, QX_DTYPE_U32, QX_DTYPE_I64, QX_DTYPE_U64, QX_DTYPE_F16, QX_DTYPE_BF16,
+  QX_DTYPE_F32, QX_DTYPE_F64, QX_DTYPE_E4M3, QX_DTYPE_E5M2, QX_DTYPE_PACKED
+} qx_dtype;
+
+typedef enum qx_memory_space {
+  QX_MEMORY_UNKNOWN = 0, QX_MEMORY_HOST, QX_MEMORY_DEVICE, QX_MEMORY_SHARED
+} qx_memory_space;
+
+enum { QX_TENSOR_NONE = 0, QX_TENSOR_READ_ONLY = 1, QX_TENSOR_CONTIGUOUS = 2, QX_TENSOR_OPTIONAL = 4 };
+
+/* ---- generic call (kernel_abi.hpp:66-107) ---------------------------------------------------- */
+typedef struct qx_tensor_view {
+  void* data;
+  const int64_t* shape;
+  const int64_t* strides; /* in elements; NULL = contiguous row-major */
+  size_t rank;
+  qx_dtype dtype;
+  qx_memory_space memory_space;
+  uint32_t flags;
+} qx_tensor_view;
+
+typedef enum qx_attribute_kind {
+  QX_ATTR_BOOL = 0, QX_ATTR_I64, QX_ATTR_F64, QX_ATTR_STRING, QX_ATTR_BYTES
+} qx_attribute_kind;
+
+typedef struct qx_attribute {
+  const char* name;
+  qx_attribute_kind kind;
+  const void* data; /* string / bytes payload */
+  size_t size;
+  int64_t i64;      /* bool / i64 payload */
+  double f64;
+} qx_attribute;
+
+typedef struct qx_kernel_call {
+  const qx_tensor_view* inputs;
+  size_t input_count;
+  qx_tensor_view* outputs;
+  size_t output_count;
+  const qx_attribute* attributes;
+  size_t attribute_count;
+  void* backend_context; /* unused, must be NULL */
+  void* stream;          /* cudaStream_t */
+  void* workspace;       /* device scratch, see qx_cuda_workspace_bytes */
+  size_t workspace_size;
+} qx_kernel_call;
+
+/*
+ * Generic dispatcher: the slot the reference's
+ * quixicore::metal::contract_api::dispatch(OperationId, const KernelCall&)
+ * (include/quixicore/metal/contract.hpp:12-16) leaves as `not_implemented`.
+ * op_name is the contract's operation name (include/quixicore/contract/operations.hpp:72-75,232):
+ *   "decode_linear_epilogue"   inputs x, weight, bias, residual      outputs y
+ *   "decode_swiglu"            inputs x, gate_w, up_w, gate_b, up_b  outputs y
+ *   "quantized_lm_head_sample" inputs h, Wq, bias                    outputs ids(i32)
+ *   "quantize_per_token_fp8" / "quantize_per_token_int8"  inputs x   outputs codes, scale
+ * Attribute names equal the Python keyword names of the reference API: format, activation,
+ * use_bias, use_residual, mode, topk, temperature, seed, top_p.  Unknown op -> QX_NOT_IMPLEMENTED.
+ */
+qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call);
+
+/* Scratch bytes `call->workspace` must provide for op_name with these shapes (0 for ops without
+ * scratch).  Counterpart of the partial buffers the reference host code allocates itself
+ * (bindings/pytorch_mps/tk_torch/torch_kernels.mm:5071-5073, :5093-5094). */
+size_t qx_cuda_workspace_bytes(const char* op_name, const qx_kernel_call* call);
+
+/* ---- typed entry points ----------------------------------------------------------------------
+ * dtype: QX_DTYPE_F32 / QX_DTYPE_F16 / QX_DTYPE_BF16 = element type of x, bias, residual, y.
+ * format: "q4_0" "q8_0" "q6_K" "mxfp8" "nvfp4" "mxfp4"; weight = uint8 (N, K/block_k, block_bytes)
+ * contiguous, K % block_k == 0.  activation: 0 none, 1 erf-GELU (Abramowitz-Stegun), 2 SiLU.
+ */
+
+/* y[m,n] = T( act( dot(x[m,:], deq(W[n,:])) + bias[n] ) + residual[m,n] ), fp32 math, one rounding.
+ * Replaces decode_linear_epilogue_mps (torch_kernels.mm:6407-6435) and
+ * tk::launch_decode_linear_epilogue (kernels/common/tk_launch.h:444-456). bias / residual are
+ * ignored (may be NULL) when their flag is 0. */
+qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void* weight,
+                                         const void* bias, const void* residual, void* y,
+                                         int64_t M, int64_t K, int64_t N, const char* format,
+                                         qx_dtype dtype, int activation, int use_bias,
+                                         int use_residual);
+
+/* y[m,n] = T( silu(gate.x + gb) * (up.x + ub) ).  Replaces decode_swiglu_mps
+ * (torch_kernels.mm:6437-6466) and tk::launch_decode_swiglu (tk_launch.h:458-470). */
+qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_weight,
+                                const void* up_weight, const void* gate_bias, const void* up_bias,
+                                void* y, int64_t M, int64_t K, int64_t N, const char* format,
+                                qx_dtype dtype, int use_bias);
+
+/* Per-row dynamic quantisation of x (rows, D): scale[row] = amax/448 (fp8, e4m3 codes, halves
+ * round away from zero, saturating at 448) or amax/127 (int8).  Replaces
+ * quantize_per_token_fp8 / _int8 (kernels/quantization/quant_rt/quant_rt.metal:21-87,
+ * tk_launch.h:1449-1468, tk_torch/__init__.py:1738-1745). kind: 0 = fp8, 1 = int8. */
+qx_status qx_cuda_quantize_per_token(void* stream, const void* x, void* codes, float* scale,
+                                     int64_t rows, int64_t D, qx_dtype dtype, int kind);
+
+/* x (rows, D), D % 32 == 0 -> MXFP8 blocks (rows, D/32, 33) = {e8m0 exponent; 32 e4m3 codes},
+ * scale = 2^ceil(log2(amax/448)).  The rule of quantize_per_group_fp8 with G = 32, ue8m0 = 1
+ * (quant_rt.metal:266-306) emitted in the packed mxfp8 block layout
+ * (include/metal/ops/warp/register/tile/dequant.metal:422-429). */
+qx_status qx_cuda_quantize_mxfp8_rows(void* stream, const void* x, void* blocks, int64_t rows,
+                                      int64_t D, qx_dtype dtype);
+
+/* ---- fused LM head ---------------------------------------------------------------------------
+ * mode: 0 argmax, 1 categorical, 2 top-k, 3 top-p.  topk in [1,64] for modes 2/3.  bias is fp32
+ * (V,) or NULL.  seed is the 32-bit RNG key; the noise stream is the reference's stateless hash
+ * keyed by (seed, row, global vocab id) (include/metal/common/rng.metal:18-30).
+ */
+
+/* Scratch bytes for qx_cuda_lm_head_sample_q. */
+size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int mode, int topk);
+
+/* ids[t] = sampled token for row t of h (T,K); logits are never written to memory.  Replaces
+ * lm_head_sample_q_mps (torch_kernels.mm:5019-5101) = partial + reduce launches
+ * (tk_launch.h:2836-2871, :2952-3013). */
+qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, const float* bias,
+                                   int32_t* ids, void* workspace, size_t workspace_bytes, int64_t T,
+                                   int64_t V, int64_t K, const char* format, qx_dtype dtype,
+                                   int mode, int topk, double temperature, uint32_t seed,
+                                   double top_p);
+
+/* Vocabulary-sharded form.  A shard holds rows [vocab_offset, vocab_offset + V_local) of the full
+ * matrix, vocab_offset a multiple of 256 so every 256-row tile of the reference lies in one shard.
+ * Stage 1 writes this shard's candidates for every row t:
+ *   cand_val / cand_id  (T, C) with C = qx_cuda_lm_head_shard_candidates(...); absent slots carry
+ *                       id -1; ids are GLOBAL vocab ids
+ *   cand_lse            (T, L) per-tile log-sum-exp (mode 3 only, L = tiles of the largest shard;
+ *                       absent tiles carry -FLT_MAX)
+ * After an all-gather over shards into (S, T, C) / (S, T, L) buffers, stage 2 picks the tokens.
+ * The merges (max with lowest id, top-k of top-k, sum of exp) are associative, so the result
+ * equals the single-device call on the same logits.  The reference has no multi-device code; the
+ * split follows its own two-stage tile -> reduce structure (lm_head.metal:219-235, :444-529).
+ */
+int64_t qx_cuda_lm_head_shard_candidates(int mode, int topk, int64_t max_tiles);
+size_t qx_cuda_lm_head_shard_workspace_bytes(int64_t T, int64_t V_local, int mode, int topk);
+
+qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const void* wq,
+                                           const float* bias_local, float* cand_val,
+                                           int32_t* cand_id, float* cand_lse, void* workspace,
+                                           size_t workspace_bytes, int64_t T, int64_t V_local,
+                                           int64_t K, int64_t vocab_offset, int64_t max_tiles,
+                                           const char* format, qx_dtype dtype, int mode, int topk,
+                                           double temperature, uint32_t seed);
+
+qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, const int32_t* cand_id,
+                                       const float* cand_lse, int32_t* ids, int64_t shards,
+                                       int64_t T, int64_t max_tiles, int mode, int topk,
+                                       double temperature, uint32_t seed, double top_p);
+
+/* ---- introspection --------------------------------------------------------------------------- */
+/* block_k / block_bytes of a format name; returns 0 and leaves the outputs alone if unknown
+ * (the table of kernels/matmul/decode_linear/decode_linear.cpp:25-34). */
+int qx_cuda_format_info(const char* format, int* block_k, int* block_bytes);
+/* Number of kernel launches this library has enqueued since it was loaded. */
+uint64_t qx_cuda_launch_count(void);
+/* Library version string, e.g. "quixicore-b200 0.1 (sm_100a)". */
+const char* qx_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUIXICORE_CUDA_H */

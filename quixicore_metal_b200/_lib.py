@@ -1,0 +1,87 @@
+"""ctypes loader for libquixicore_cuda.so.  Fails loudly: there is no Python or CPU fallback."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libquixicore_cuda.so")
+
+# qx_dtype values of include/quixicore_cuda.h
+DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 10, 11, 12
+DTYPE_U8, DTYPE_I32 = 3, 6
+
+STATUS_NAMES = ["ok", "invalid_argument", "invalid_shape", "unsupported_dtype", "unsupported_format",
+                "unsupported_layout", "insufficient_workspace", "adapter_not_wired",
+                "not_implemented", "runtime_error"]
+
+
+class Status(C.Structure):
+    _fields_ = [("code", C.c_int), ("operation", C.c_char_p), ("detail", C.c_char_p)]
+
+
+class QxError(RuntimeError):
+    """A non-ok qx_status; `.code` is the status name of the contract ABI."""
+
+    def __init__(self, st: Status):
+        self.code = STATUS_NAMES[st.code] if 0 <= st.code < len(STATUS_NAMES) else str(st.code)
+        op = (st.operation or b"").decode()
+        detail = (st.detail or b"").decode()
+        super().__init__(f"{op}: {detail}")
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m quixicore_metal_b200.build` "
+            "(needs nvcc). This backend has no fallback path.")
+    L = C.CDLL(LIB_PATH)
+    vp, i64, i32, u32, f64, sz = C.c_void_p, C.c_int64, C.c_int, C.c_uint32, C.c_double, C.c_size_t
+    cs = C.c_char_p
+    L.qx_cuda_decode_linear_epilogue.restype = Status
+    L.qx_cuda_decode_linear_epilogue.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, i32]
+    L.qx_cuda_decode_swiglu.restype = Status
+    L.qx_cuda_decode_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32]
+    L.qx_cuda_quantize_per_token.restype = Status
+    L.qx_cuda_quantize_per_token.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32]
+    L.qx_cuda_quantize_mxfp8_rows.restype = Status
+    L.qx_cuda_quantize_mxfp8_rows.argtypes = [vp, vp, vp, i64, i64, i32]
+    L.qx_cuda_lm_head_workspace_bytes.restype = sz
+    L.qx_cuda_lm_head_workspace_bytes.argtypes = [i64, i64, i32, i32]
+    L.qx_cuda_lm_head_sample_q.restype = Status
+    L.qx_cuda_lm_head_sample_q.argtypes = [vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, cs, i32, i32, i32, f64, u32, f64]
+    L.qx_cuda_lm_head_shard_candidates.restype = i64
+    L.qx_cuda_lm_head_shard_candidates.argtypes = [i32, i32, i64]
+    L.qx_cuda_lm_head_shard_workspace_bytes.restype = sz
+    L.qx_cuda_lm_head_shard_workspace_bytes.argtypes = [i64, i64, i32, i32]
+    L.qx_cuda_lm_head_shard_partials_q.restype = Status
+    L.qx_cuda_lm_head_shard_partials_q.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, i64, cs, i32, i32, i32, f64, u32]
+    L.qx_cuda_lm_head_shard_reduce.restype = Status
+    L.qx_cuda_lm_head_shard_reduce.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, f64, u32, f64]
+    L.qx_cuda_format_info.restype = i32
+    L.qx_cuda_format_info.argtypes = [cs, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    L.qx_cuda_launch_count.restype = C.c_uint64
+    L.qx_cuda_launch_count.argtypes = []
+    L.qx_cuda_version.restype = cs
+    L.qx_cuda_version.argtypes = []
+    L.qx_cuda_dispatch.restype = Status
+    L.qx_cuda_dispatch.argtypes = [cs, vp]
+    L.qx_cuda_workspace_bytes.restype = sz
+    L.qx_cuda_workspace_bytes.argtypes = [cs, vp]
+    _lib = L
+    return L
+
+
+def check(st: Status) -> None:
+    if st.code != 0:
+        raise QxError(st)
+
+
+def launch_count() -> int:
+    return int(lib().qx_cuda_launch_count())

@@ -1,0 +1,461 @@
+// C ABI and dispatch: argument validation mirroring the reference host checks, kernel selection
+// by (format, dtype, batch, alignment), workspace carving, stream launch.  No CPU fallback.
+#include <atomic>
+#include <cstring>
+
+#include "qx_common.cuh"
+#include "qx_kernels.h"
+
+namespace qx {
+
+static std::atomic<uint64_t> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+qx_status ok(const char* op) { return qx_status{QX_OK, op, ""}; }
+qx_status fail(qx_status_code code, const char* op, const char* detail) {
+  return qx_status{code, op, detail};
+}
+qx_status check_launch(const char* op) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(QX_RUNTIME_ERROR, op, cudaGetErrorString(e));
+  return ok(op);
+}
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int parse_format(const char* name) {
+  if (!name) return -1;
+  static const char* names[F_COUNT] = {"q4_0", "q8_0", "q6_K", "mxfp8", "nvfp4", "mxfp4"};
+  for (int i = 0; i < F_COUNT; ++i)
+    if (std::strcmp(name, names[i]) == 0) return i;
+  return -1;
+}
+
+static bool float_dtype(qx_dtype d) {
+  return d == QX_DTYPE_F32 || d == QX_DTYPE_F16 || d == QX_DTYPE_BF16;
+}
+static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+static bool device_ready(const char* op, qx_status* st) {
+  int dev = -1;
+  const cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    *st = fail(QX_RUNTIME_ERROR, op, "no usable CUDA device (this backend has no CPU fallback)");
+    return false;
+  }
+  return true;
+}
+
+// Shared checks of the two projection ops (the reference's check_decode_epilogue_weight).
+static qx_status check_projection(const char* op, const void* x, const void* w, void* y, int64_t M,
+                                  int64_t K, int64_t N, const char* format, qx_dtype dtype,
+                                  int* fmt_out) {
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "x must be non-empty (B,K) fp32/fp16/bf16");
+  if (!x || !w || !y) return fail(QX_INVALID_ARGUMENT, op, "x, weight and output pointers must be non-null");
+  if (M <= 0 || K <= 0) return fail(QX_INVALID_SHAPE, op, "x must be non-empty (B,K) fp32/fp16/bf16");
+  const int f = parse_format(format);
+  if (f < 0)
+    return fail(QX_UNSUPPORTED_FORMAT, op, "format must be q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4");
+  if (N <= 0 || K % block_k_of(f) != 0)
+    return fail(QX_INVALID_SHAPE, op, "packed weight must be uint8 (N,K/block_k,block_bytes)");
+  if (M > 0x7fffffff || K > 0x7fffffff || N > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "dimensions must fit in 31 bits");
+  *fmt_out = f;
+  return ok(op);
+}
+
+}  // namespace qx
+
+using namespace qx;
+
+extern "C" {
+
+int qx_cuda_format_info(const char* format, int* block_k, int* block_bytes) {
+  const int f = parse_format(format);
+  if (f < 0) return 0;
+  if (block_k) *block_k = block_k_of(f);
+  if (block_bytes) *block_bytes = block_bytes_of(f);
+  return 1;
+}
+uint64_t qx_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* qx_cuda_version(void) { return "quixicore-b200 0.1 (sm_100a)"; }
+
+qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void* weight,
+                                         const void* bias, const void* residual, void* y,
+                                         int64_t M, int64_t K, int64_t N, const char* format,
+                                         qx_dtype dtype, int activation, int use_bias,
+                                         int use_residual) {
+  static const char* op = "decode_linear_epilogue";
+  if (activation < 0 || activation > 2)
+    return fail(QX_INVALID_ARGUMENT, op, "activation must be 0, 1, or 2");
+  int f = -1;
+  qx_status st = check_projection(op, x, weight, y, M, K, N, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  if (use_bias && !bias) return fail(QX_INVALID_ARGUMENT, op, "bias must be (N,) with x dtype");
+  if (use_residual && !residual)
+    return fail(QX_INVALID_ARGUMENT, op, "residual must be (B,N) with x dtype");
+  if (!device_ready(op, &st)) return st;
+  GemvArgs a{x, weight, nullptr, bias, nullptr, residual, y, M, K, N, f, dtype,
+             activation, use_bias ? 1 : 0, use_residual ? 1 : 0};
+  launch_projection((cudaStream_t)stream, a);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_weight,
+                                const void* up_weight, const void* gate_bias, const void* up_bias,
+                                void* y, int64_t M, int64_t K, int64_t N, const char* format,
+                                qx_dtype dtype, int use_bias) {
+  static const char* op = "decode_swiglu";
+  int f = -1;
+  qx_status st = check_projection(op, x, gate_weight, y, M, K, N, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  if (!up_weight)
+    return fail(QX_INVALID_ARGUMENT, op, "gate and up weights must have identical shapes");
+  if (use_bias && (!gate_bias || !up_bias))
+    return fail(QX_INVALID_ARGUMENT, op, "both biases must be (N,) with x dtype");
+  if (!device_ready(op, &st)) return st;
+  GemvArgs a{x, gate_weight, up_weight, gate_bias, up_bias, nullptr, y, M, K, N, f, dtype,
+             0, use_bias ? 1 : 0, 0};
+  launch_projection((cudaStream_t)stream, a);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_quantize_per_token(void* stream, const void* x, void* codes, float* scale,
+                                     int64_t rows, int64_t D, qx_dtype dtype, int kind) {
+  const char* op = kind == 1 ? "quantize_per_token_int8" : "quantize_per_token_fp8";
+  if (kind != 0 && kind != 1) return fail(QX_INVALID_ARGUMENT, "quantize_per_token", "kind must be 0 (fp8) or 1 (int8)");
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "x must be fp32/fp16/bf16");
+  if (!x || !codes || !scale) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (rows <= 0 || D <= 0 || D > 0x7fffffff || rows > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "x must be a non-empty (rows, D) matrix");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  launch_quantize_per_token((cudaStream_t)stream, x, codes, scale, rows, D, dtype, kind);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_quantize_mxfp8_rows(void* stream, const void* x, void* blocks, int64_t rows,
+                                      int64_t D, qx_dtype dtype) {
+  static const char* op = "quantize_mxfp8_rows";
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "x must be fp32/fp16/bf16");
+  if (!x || !blocks) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (rows <= 0 || D <= 0 || D % 32 != 0)
+    return fail(QX_INVALID_SHAPE, op, "x must be (rows, D) with D a positive multiple of 32");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  launch_quantize_mxfp8_rows((cudaStream_t)stream, x, blocks, rows, D, dtype);
+  return check_launch(op);
+}
+
+// ---- LM head ---------------------------------------------------------------------------------
+static qx_status check_lm_head(const char* op, const void* h, const void* wq, int64_t T, int64_t V,
+                               int64_t K, const char* format, qx_dtype dtype, int mode, int topk,
+                               double temperature, int* fmt_out) {
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "h must be floating point");
+  if (!h || !wq) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (mode < 0 || mode > 3)
+    return fail(QX_INVALID_ARGUMENT, op, "mode 0=argmax, 1=categorical, 2=topk, 3=topp");
+  if (!(temperature > 0.0)) return fail(QX_INVALID_ARGUMENT, op, "temperature must be positive");
+  const int f = parse_format(format);
+  if (f < 0)
+    return fail(QX_UNSUPPORTED_FORMAT, op, "format must be q8_0, q4_0, q6_K, mxfp8, nvfp4, or mxfp4");
+  if (T <= 0 || V <= 0 || K <= 0) return fail(QX_INVALID_SHAPE, op, "T, V, and K must be positive");
+  if (K % block_k_of(f) != 0)
+    return fail(QX_INVALID_SHAPE, op, "packed weight shape does not match V/K/format");
+  if (T > 0x7fffffff || V > 0x7fffffff || K > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "dimensions must fit in 31 bits");
+  if (mode >= 2) {
+    if (topk < 1 || topk > 64) return fail(QX_INVALID_ARGUMENT, op, "k must be in [1, 64]");
+  }
+  *fmt_out = f;
+  return ok(op);
+}
+
+static int64_t tiles_of(int64_t V) { return (V + 255) / 256; }
+
+size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int mode, int topk) {
+  if (T <= 0 || V <= 0) return 0;
+  const size_t tiles = (size_t)tiles_of(V);
+  const size_t kk = mode >= 2 ? (size_t)(topk > 0 ? topk : 1) : 1;
+  size_t n = 2 * align256((size_t)T * tiles * kk * 4);
+  if (mode == 3) n += align256((size_t)T * tiles * 4);
+  return n;
+}
+
+qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, const float* bias,
+                                   int32_t* ids, void* workspace, size_t workspace_bytes, int64_t T,
+                                   int64_t V, int64_t K, const char* format, qx_dtype dtype,
+                                   int mode, int topk, double temperature, uint32_t seed,
+                                   double top_p) {
+  static const char* op = "quantized_lm_head_sample";
+  int f = -1;
+  qx_status st = check_lm_head(op, h, wq, T, V, K, format, dtype, mode, topk, temperature, &f);
+  if (st.code != QX_OK) return st;
+  if (!ids) return fail(QX_INVALID_ARGUMENT, op, "null output pointer");
+  if (mode >= 2 && topk > V) return fail(QX_INVALID_ARGUMENT, op, "k must be <= vocab size V");
+  if (mode == 3 && !(top_p > 0.0 && top_p <= 1.0))
+    return fail(QX_INVALID_ARGUMENT, op, "topp requires top_p in (0, 1]");
+  const size_t need = qx_cuda_lm_head_workspace_bytes(T, V, mode, topk);
+  if (!workspace || workspace_bytes < need)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace smaller than qx_cuda_lm_head_workspace_bytes");
+  if (!device_ready(op, &st)) return st;
+  const int64_t tiles = tiles_of(V);
+  const int kk = mode >= 2 ? topk : 1;
+  const size_t seg = align256((size_t)T * tiles * kk * 4);
+  float* pv = (float*)workspace;
+  int32_t* pi = (int32_t*)((char*)workspace + seg);
+  float* pl = (float*)((char*)workspace + 2 * seg);
+  LmHeadArgs a{h, wq, bias, T, V, K, 0, f, dtype, mode, kk, 1.0f / (float)temperature, seed,
+               (float)top_p};
+  launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, pl, tiles);
+  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, pl, 1, T, tiles * kk, tiles, mode, kk,
+                        a.invtemp, seed, a.top_p, ids, 0, nullptr, nullptr);
+  return check_launch(op);
+}
+
+int64_t qx_cuda_lm_head_shard_candidates(int mode, int topk, int64_t max_tiles) {
+  if (mode <= 1) return 1;
+  if (mode == 2) return topk;
+  return max_tiles * topk;
+}
+
+size_t qx_cuda_lm_head_shard_workspace_bytes(int64_t T, int64_t V_local, int mode, int topk) {
+  if (mode == 3 || T <= 0 || V_local <= 0) return 0;
+  const size_t kk = mode == 2 ? (size_t)(topk > 0 ? topk : 1) : 1;
+  return 2 * align256((size_t)T * (size_t)tiles_of(V_local) * kk * 4);
+}
+
+qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const void* wq,
+                                           const float* bias_local, float* cand_val,
+                                           int32_t* cand_id, float* cand_lse, void* workspace,
+                                           size_t workspace_bytes, int64_t T, int64_t V_local,
+                                           int64_t K, int64_t vocab_offset, int64_t max_tiles,
+                                           const char* format, qx_dtype dtype, int mode, int topk,
+                                           double temperature, uint32_t seed) {
+  static const char* op = "quantized_lm_head_sample.shard_partials";
+  int f = -1;
+  qx_status st = check_lm_head(op, h, wq, T, V_local, K, format, dtype, mode, topk, temperature, &f);
+  if (st.code != QX_OK) return st;
+  if (!cand_val || !cand_id || (mode == 3 && !cand_lse))
+    return fail(QX_INVALID_ARGUMENT, op, "null candidate buffer");
+  if (vocab_offset < 0 || vocab_offset % 256 != 0)
+    return fail(QX_INVALID_ARGUMENT, op, "vocab_offset must be a non-negative multiple of 256");
+  const int64_t tiles = tiles_of(V_local);
+  if (max_tiles < tiles) return fail(QX_INVALID_ARGUMENT, op, "max_tiles smaller than this shard's tile count");
+  if (vocab_offset + V_local > 0x7fffffffLL) return fail(QX_INVALID_SHAPE, op, "global vocab ids must fit in 31 bits");
+  const size_t need = qx_cuda_lm_head_shard_workspace_bytes(T, V_local, mode, topk);
+  if (need && (!workspace || workspace_bytes < need))
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace smaller than qx_cuda_lm_head_shard_workspace_bytes");
+  if (!device_ready(op, &st)) return st;
+  const int kk = mode >= 2 ? topk : 1;
+  LmHeadArgs a{h, wq, bias_local, T, V_local, K, vocab_offset, f, dtype, mode, kk,
+               1.0f / (float)temperature, seed, 1.0f};
+  if (mode == 3) {
+    launch_lm_head_partials((cudaStream_t)stream, a, cand_val, cand_id, cand_lse, max_tiles);
+    return check_launch(op);
+  }
+  const size_t seg = align256((size_t)T * tiles * kk * 4);
+  float* pv = (float*)workspace;
+  int32_t* pi = (int32_t*)((char*)workspace + seg);
+  launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, nullptr, tiles);
+  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, nullptr, 1, T, tiles * kk, 0, mode, kk,
+                        a.invtemp, seed, 1.0f, nullptr, 1, cand_val, cand_id);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, const int32_t* cand_id,
+                                       const float* cand_lse, int32_t* ids, int64_t shards,
+                                       int64_t T, int64_t max_tiles, int mode, int topk,
+                                       double temperature, uint32_t seed, double top_p) {
+  static const char* op = "quantized_lm_head_sample.shard_reduce";
+  if (!cand_val || !cand_id || !ids || (mode == 3 && !cand_lse))
+    return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (mode < 0 || mode > 3) return fail(QX_INVALID_ARGUMENT, op, "mode 0=argmax, 1=categorical, 2=topk, 3=topp");
+  if (shards <= 0 || shards > 1024 || T <= 0 || max_tiles <= 0) return fail(QX_INVALID_SHAPE, op, "shards, T and max_tiles must be positive");
+  if (!(temperature > 0.0)) return fail(QX_INVALID_ARGUMENT, op, "temperature must be positive");
+  if (mode >= 2 && (topk < 1 || topk > 64)) return fail(QX_INVALID_ARGUMENT, op, "k must be in [1, 64]");
+  if (mode == 3 && !(top_p > 0.0 && top_p <= 1.0)) return fail(QX_INVALID_ARGUMENT, op, "topp requires top_p in (0, 1]");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  const int kk = mode >= 2 ? topk : 1;
+  const int64_t C = qx_cuda_lm_head_shard_candidates(mode, kk, max_tiles);
+  // stage-1 scores of modes 0/1 already carry temperature, bias and noise: the merge is a plain max
+  launch_lm_head_reduce((cudaStream_t)stream, cand_val, cand_id, cand_lse, (int)shards, T, C,
+                        mode == 3 ? max_tiles : 0, mode, kk, 1.0f / (float)temperature, seed,
+                        (float)top_p, ids, 0, nullptr, nullptr);
+  return check_launch(op);
+}
+
+// ---- generic dispatcher ----------------------------------------------------------------------
+static const qx_attribute* find_attr(const qx_kernel_call* c, const char* name) {
+  for (size_t i = 0; i < c->attribute_count; ++i)
+    if (c->attributes[i].name && std::strcmp(c->attributes[i].name, name) == 0) return &c->attributes[i];
+  return nullptr;
+}
+static int64_t attr_i64(const qx_kernel_call* c, const char* name, int64_t dflt) {
+  const qx_attribute* a = find_attr(c, name);
+  if (!a) return dflt;
+  if (a->kind == QX_ATTR_F64) return (int64_t)a->f64;
+  return a->i64;
+}
+static double attr_f64(const qx_kernel_call* c, const char* name, double dflt) {
+  const qx_attribute* a = find_attr(c, name);
+  if (!a) return dflt;
+  if (a->kind == QX_ATTR_F64) return a->f64;
+  return (double)a->i64;
+}
+static const char* attr_str(const qx_kernel_call* c, const char* name) {
+  const qx_attribute* a = find_attr(c, name);
+  if (!a || a->kind != QX_ATTR_STRING) return nullptr;
+  return (const char*)a->data;
+}
+static bool contiguous(const qx_tensor_view& t) {
+  if (!t.strides) return true;
+  int64_t expect = 1;
+  for (size_t i = t.rank; i-- > 0;) {
+    if (t.shape[i] != 1 && t.strides[i] != expect) return false;
+    expect *= t.shape[i];
+  }
+  return true;
+}
+static bool present(const qx_kernel_call* c, size_t i) {
+  return i < c->input_count && c->inputs[i].data != nullptr;
+}
+
+static qx_status lm_head_dims(const qx_kernel_call* call, int64_t* T, int64_t* V, int64_t* K,
+                              const char** fmt) {
+  static const char* op = "quantized_lm_head_sample";
+  if (!call || call->input_count < 2) return fail(QX_INVALID_ARGUMENT, op, "expects inputs h, Wq[, bias]");
+  const qx_tensor_view& h = call->inputs[0];
+  const qx_tensor_view& w = call->inputs[1];
+  if (h.rank != 2 || w.rank != 3) return fail(QX_INVALID_SHAPE, op, "h must be (T, K)");
+  *fmt = attr_str(call, "format");
+  int bk = 0, bb = 0;
+  if (!qx_cuda_format_info(*fmt, &bk, &bb))
+    return fail(QX_UNSUPPORTED_FORMAT, op, "format must be q8_0, q4_0, q6_K, mxfp8, nvfp4, or mxfp4");
+  *T = h.shape[0]; *K = h.shape[1]; *V = w.shape[0];
+  if (w.shape[1] * bk != *K || w.shape[2] != bb)
+    return fail(QX_INVALID_SHAPE, op, "packed weight shape does not match V/K/format");
+  return ok(op);
+}
+
+size_t qx_cuda_workspace_bytes(const char* op_name, const qx_kernel_call* call) {
+  if (!op_name || !call) return 0;
+  if (std::strcmp(op_name, "quantized_lm_head_sample") == 0) {
+    int64_t T, V, K; const char* fmt;
+    if (lm_head_dims(call, &T, &V, &K, &fmt).code != QX_OK) return 0;
+    const int mode = (int)attr_i64(call, "mode", 0);
+    int topk = (int)attr_i64(call, "topk", 0);
+    if (mode >= 2 && topk <= 0) topk = 32;
+    return qx_cuda_lm_head_workspace_bytes(T, V, mode, topk);
+  }
+  return 0;
+}
+
+qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
+  if (!op_name) return fail(QX_INVALID_ARGUMENT, "dispatch", "null operation name");
+  if (!call) return fail(QX_INVALID_ARGUMENT, op_name, "null call");
+  for (size_t i = 0; i < call->input_count; ++i) {
+    const qx_tensor_view& t = call->inputs[i];
+    if (!t.data) continue;
+    if (t.memory_space != QX_MEMORY_DEVICE) return fail(QX_UNSUPPORTED_LAYOUT, op_name, "tensors must be in device memory");
+    if (!contiguous(t)) return fail(QX_UNSUPPORTED_LAYOUT, op_name, "tensors must be contiguous");
+  }
+  for (size_t i = 0; i < call->output_count; ++i) {
+    const qx_tensor_view& t = call->outputs[i];
+    if (!t.data || t.memory_space != QX_MEMORY_DEVICE || !contiguous(t))
+      return fail(QX_UNSUPPORTED_LAYOUT, op_name, "outputs must be contiguous device tensors");
+  }
+  const bool lin = std::strcmp(op_name, "decode_linear_epilogue") == 0;
+  const bool glu = std::strcmp(op_name, "decode_swiglu") == 0;
+  if (lin || glu) {
+    const size_t wcount = glu ? 3 : 2;
+    if (call->input_count < wcount || call->output_count < 1)
+      return fail(QX_INVALID_ARGUMENT, op_name, "missing inputs or outputs");
+    const qx_tensor_view& x = call->inputs[0];
+    const qx_tensor_view& w = call->inputs[1];
+    if (x.rank != 2) return fail(QX_INVALID_SHAPE, op_name, "x must be non-empty (B,K) fp32/fp16/bf16");
+    const char* fmt = attr_str(call, "format");
+    int bk = 0, bb = 0;
+    if (!qx_cuda_format_info(fmt, &bk, &bb))
+      return fail(QX_UNSUPPORTED_FORMAT, op_name, "format must be q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4");
+    const int64_t M = x.shape[0], K = x.shape[1];
+    if (w.rank != 3 || w.dtype != QX_DTYPE_U8 || K % bk != 0 || w.shape[1] != K / bk || w.shape[2] != bb)
+      return fail(QX_INVALID_SHAPE, op_name, "packed weight must be uint8 (N,K/block_k,block_bytes)");
+    const int64_t N = w.shape[0];
+    const qx_tensor_view& y = call->outputs[0];
+    if (y.rank != 2 || y.shape[0] != M || y.shape[1] != N || y.dtype != x.dtype)
+      return fail(QX_INVALID_SHAPE, op_name, "output must be (B,N) with x dtype");
+    if (lin) {
+      const bool ub = attr_i64(call, "use_bias", present(call, 2)) != 0;
+      const bool ur = attr_i64(call, "use_residual", present(call, 3)) != 0;
+      if (ub && !(present(call, 2) && call->inputs[2].rank == 1 && call->inputs[2].shape[0] == N && call->inputs[2].dtype == x.dtype))
+        return fail(QX_INVALID_SHAPE, op_name, "bias must be (N,) with x dtype");
+      if (ur && !(present(call, 3) && call->inputs[3].rank == 2 && call->inputs[3].shape[0] == M && call->inputs[3].shape[1] == N && call->inputs[3].dtype == x.dtype))
+        return fail(QX_INVALID_SHAPE, op_name, "residual must be (B,N) with x dtype");
+      return qx_cuda_decode_linear_epilogue(call->stream, x.data, w.data, ub ? call->inputs[2].data : nullptr,
+                                            ur ? call->inputs[3].data : nullptr, y.data, M, K, N, fmt, x.dtype,
+                                            (int)attr_i64(call, "activation", 0), ub, ur);
+    }
+    const qx_tensor_view& u = call->inputs[2];
+    if (u.rank != 3 || u.dtype != QX_DTYPE_U8 || u.shape[0] != N || u.shape[1] != w.shape[1] || u.shape[2] != bb)
+      return fail(QX_INVALID_SHAPE, op_name, "gate and up weights must have identical shapes");
+    const bool ub = attr_i64(call, "use_bias", present(call, 3) && present(call, 4)) != 0;
+    if (ub) {
+      for (size_t i = 3; i <= 4; ++i)
+        if (!(present(call, i) && call->inputs[i].rank == 1 && call->inputs[i].shape[0] == N && call->inputs[i].dtype == x.dtype))
+          return fail(QX_INVALID_SHAPE, op_name, "both biases must be (N,) with x dtype");
+    }
+    return qx_cuda_decode_swiglu(call->stream, x.data, w.data, u.data, ub ? call->inputs[3].data : nullptr,
+                                 ub ? call->inputs[4].data : nullptr, y.data, M, K, N, fmt, x.dtype, ub);
+  }
+  if (std::strcmp(op_name, "quantized_lm_head_sample") == 0) {
+    int64_t T, V, K; const char* fmt;
+    qx_status st = lm_head_dims(call, &T, &V, &K, &fmt);
+    if (st.code != QX_OK) return st;
+    if (call->output_count < 1 || call->outputs[0].dtype != QX_DTYPE_I32 || call->outputs[0].rank != 1 || call->outputs[0].shape[0] != T)
+      return fail(QX_INVALID_SHAPE, op_name, "output must be int32 (T,)");
+    const int mode = (int)attr_i64(call, "mode", 0);
+    int topk = (int)attr_i64(call, "topk", 0);
+    if (mode >= 2 && topk <= 0) topk = 32;
+    const float* bias = nullptr;
+    if (present(call, 2)) {
+      const qx_tensor_view& b = call->inputs[2];
+      int64_t n = 1;
+      for (size_t i = 0; i < b.rank; ++i) n *= b.shape[i];
+      if (n > 1) {   // a 1-element bias is the reference's "no bias" placeholder
+        if (b.dtype != QX_DTYPE_F32 || n != V) return fail(QX_INVALID_SHAPE, op_name, "bias must be fp32 (V,)");
+        bias = (const float*)b.data;
+      }
+    }
+    return qx_cuda_lm_head_sample_q(call->stream, call->inputs[0].data, call->inputs[1].data, bias,
+                                    (int32_t*)call->outputs[0].data, call->workspace, call->workspace_size,
+                                    T, V, K, fmt, call->inputs[0].dtype, mode, topk,
+                                    attr_f64(call, "temperature", 1.0), (uint32_t)attr_i64(call, "seed", 0),
+                                    attr_f64(call, "top_p", 0.9));
+  }
+  const bool q8 = std::strcmp(op_name, "quantize_per_token_fp8") == 0;
+  const bool qi = std::strcmp(op_name, "quantize_per_token_int8") == 0;
+  if (q8 || qi) {
+    if (call->input_count < 1 || call->output_count < 2) return fail(QX_INVALID_ARGUMENT, op_name, "expects x -> (codes, scale)");
+    const qx_tensor_view& x = call->inputs[0];
+    if (x.rank < 1) return fail(QX_INVALID_SHAPE, op_name, "x must have at least one dimension");
+    int64_t rows = 1;
+    for (size_t i = 0; i + 1 < x.rank; ++i) rows *= x.shape[i];
+    return qx_cuda_quantize_per_token(call->stream, x.data, call->outputs[0].data, (float*)call->outputs[1].data,
+                                      rows, x.shape[x.rank - 1], x.dtype, qi ? 1 : 0);
+  }
+  return fail(QX_NOT_IMPLEMENTED, op_name, "operation is not part of the B200 decode-projection backend");
+}
+
+}  // extern "C"

@@ -1,0 +1,434 @@
+// Fused LM head + sampling over packed weights: logits live only in shared memory.
+//
+// Stage 1 (partials): one CTA per 256-row vocabulary tile and per group of up to 8 hidden rows.
+// The CTA projects its tile, keeps the (tokens x 256) logits in shared memory and reduces them to
+// per-tile partials: the running (max, id) for argmax / categorical, the tile's top-k for top-k /
+// top-p, plus the tile's tempered log-sum-exp for top-p.  Tiles start at multiples of 256 of the
+// GLOBAL vocabulary id, which is what the top-p pool semantics are defined on.
+//
+// Stage 2 (reduce): one CTA per hidden row merges the partials of all tiles (and, for a sharded
+// vocabulary, of all shards): max with lowest-id tie break; exact top-k by a radix select on the
+// candidate values; nucleus threshold by 32 bisection steps against the full-vocabulary
+// normalizer; Gumbel-max with the stateless (seed, row, global id) noise stream.
+//
+// Ordering everywhere: value descending, ties to the smaller id.
+#include "qx_formats.cuh"
+#include "qx_kernels.h"
+
+namespace qx {
+
+constexpr int LMH_TILE = 256;
+constexpr int LMH_TB = 8;        // hidden rows per stage-1 CTA
+constexpr int LMH_RED_THREADS = 512;
+
+template <int FMT, typename T>
+__global__ void __launch_bounds__(256)
+lmh_partials_kernel(const T* __restrict__ h, const uint8_t* __restrict__ wq,
+                    const float* __restrict__ bias, float* __restrict__ part_val,
+                    int32_t* __restrict__ part_id, float* __restrict__ part_lse, int T_rows, int V,
+                    int K, long long vocab_offset, long long tiles_stride, int mode, int topk,
+                    float invtemp, uint32_t seed) {
+  constexpr int BK = block_k_of(FMT), BB = block_bytes_of(FMT);
+  __shared__ float logit[LMH_TB][LMH_TILE];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tile = blockIdx.x;
+  const int t0 = blockIdx.y * LMH_TB;
+  const int tcount = min(LMH_TB, T_rows - t0);
+  const int v0 = tile * LMH_TILE;   // tiles at or beyond V hold no rows and emit absent partials
+  const size_t row_bytes = (size_t)(K / BK) * BB;
+  const int spans = (K + 31) / 32;
+
+  // ---- projection: warp w owns local rows [32w, 32w+32) ----
+  for (int r = 0; r < 32; ++r) {
+    const int lr = warp * 32 + r;
+    const int v = v0 + lr;
+    if (v >= V || v0 >= V) {
+      if (lane < LMH_TB) logit[lane][lr] = QX_NEG_INF;
+      continue;
+    }
+    const uint8_t* row = wq + (size_t)v * row_bytes;
+    float acc[LMH_TB];
+#pragma unroll
+    for (int m = 0; m < LMH_TB; ++m) acc[m] = 0.f;
+    for (int s = lane; s < spans; s += 32) {
+      float w[32];
+      int ncol = 32;
+      if (FMT == F_NVFP4 && s * 32 + 16 >= K) {
+        const uint8_t* b = row + (size_t)s * 18;
+        const float sc = e4m3_to_f32(b[0]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          w[i] = sc * e2m1_to_f32(b[1 + i] & 15u);
+          w[i + 8] = sc * e2m1_to_f32(b[1 + i] >> 4);
+          w[i + 16] = 0.f; w[i + 24] = 0.f;
+        }
+        ncol = 16;
+      } else {
+        decode_span32<FMT>(row, s, w);
+      }
+#pragma unroll
+      for (int m = 0; m < LMH_TB; ++m) {
+        if (m < tcount) {
+          const T* hp = h + (size_t)(t0 + m) * K + (size_t)s * 32;
+          float a = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < ncol) a = fmaf(to_f32<T>(hp[i]), w[i], a);
+          acc[m] += a;
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < LMH_TB; ++m) {
+      const float s = warp_sum(acc[m]);
+      if (lane == 0) logit[m][lr] = s;
+    }
+  }
+  __syncthreads();
+
+  // ---- per-token selection: warp w handles token t0 + w ----
+  if (warp >= tcount) return;
+  const int t = t0 + warp;
+  const int nvalid = min(LMH_TILE, V - v0);
+  if (mode <= 1) {
+    float best = QX_NEG_INF;
+    int bid = 0x7fffffff;
+    for (int lr = lane; lr < nvalid; lr += 32) {
+      const int gid = (int)(vocab_offset + v0 + lr);
+      float ls = logit[warp][lr] * invtemp;
+      if (bias) ls += bias[v0 + lr];
+      if (mode == 1) ls += rng_gumbel(seed, (uint32_t)t, (uint32_t)gid);
+      if (better(ls, gid, best, bid)) { best = ls; bid = gid; }
+    }
+    warp_argmax(best, bid);
+    if (lane == 0) {
+      part_val[(size_t)t * tiles_stride + tile] = best;
+      part_id[(size_t)t * tiles_stride + tile] = bid == 0x7fffffff ? -1 : bid;
+    }
+    return;
+  }
+  // modes 2/3: tile top-k of the raw logits (+bias); mode 3 also the tempered log-sum-exp
+  float mv[8];
+  int mi[8];
+  float lmax = QX_NEG_INF, lsum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int lr = lane + 32 * j;
+    if (lr < nvalid) {
+      float ls = logit[warp][lr];
+      if (bias) ls += bias[v0 + lr];
+      mv[j] = ls;
+      mi[j] = (int)(vocab_offset + v0 + lr);
+      const float tl = ls * invtemp;
+      if (tl > lmax) { lsum = lsum * expf(lmax - tl) + 1.0f; lmax = tl; }
+      else { lsum += expf(tl - lmax); }
+    } else {
+      mv[j] = QX_NEG_INF;
+      mi[j] = -1;
+    }
+  }
+  if (mode == 3) {
+    const float gmax = warp_max(lmax);
+    const float gsum = warp_sum(lmax == QX_NEG_INF ? 0.f : lsum * expf(lmax - gmax));
+    if (lane == 0)
+      part_lse[(size_t)t * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
+  }
+  const size_t pbase = ((size_t)t * tiles_stride + tile) * topk;
+  for (int kk = 0; kk < topk; ++kk) {
+    float best = QX_NEG_INF;
+    int bid = 0x7fffffff, slot = -1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (mi[j] >= 0 && better(mv[j], mi[j], best, bid)) { best = mv[j]; bid = mi[j]; slot = j; }
+    }
+    float gbest = best;
+    int gid = bid;
+    warp_argmax(gbest, gid);
+    const bool any = gid != 0x7fffffff;
+    if (slot >= 0 && bid == gid) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (j == slot) mi[j] = -1;
+    }
+    if (lane == 0) {
+      part_val[pbase + kk] = any ? gbest : QX_NEG_INF;
+      part_id[pbase + kk] = any ? gid : -1;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Stage 2
+// ------------------------------------------------------------------------------------------
+struct BlockScratch {
+  float fv[32];
+  int iv[32];
+  unsigned hist[256];
+  unsigned u[8];
+};
+
+__device__ __forceinline__ void block_argmax(float& v, int& id, BlockScratch& s) {
+  warp_argmax(v, id);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) { s.fv[warp] = v; s.iv[warp] = id; }
+  __syncthreads();
+  v = lane < nw ? s.fv[lane] : QX_NEG_INF;
+  id = lane < nw ? s.iv[lane] : 0x7fffffff;
+  warp_argmax(v, id);
+}
+__device__ __forceinline__ float block_sum(float v, BlockScratch& s) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) s.fv[warp] = v;
+  __syncthreads();
+  v = lane < nw ? s.fv[lane] : 0.f;
+  return warp_sum(v);
+}
+__device__ __forceinline__ float block_max(float v, BlockScratch& s) {
+  v = warp_max(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) s.fv[warp] = v;
+  __syncthreads();
+  v = lane < nw ? s.fv[lane] : QX_NEG_INF;
+  return warp_max(v);
+}
+__device__ __forceinline__ int block_min_int(int v, BlockScratch& s) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, off));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) s.iv[warp] = v;
+  __syncthreads();
+  v = lane < nw ? s.iv[lane] : 0x7fffffff;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+__device__ __forceinline__ unsigned block_sum_u(unsigned v, BlockScratch& s) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) s.iv[warp] = (int)v;
+  __syncthreads();
+  v = lane < nw ? (unsigned)s.iv[lane] : 0u;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+// order-preserving key: larger float <=> larger key; -0 and +0 share a key
+__device__ __forceinline__ uint32_t float_key(float v) {
+  uint32_t u = __float_as_uint(v);
+  if (v == 0.0f) u = 0u;
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(LMH_RED_THREADS)
+lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict__ cand_id,
+                  const float* __restrict__ cand_lse, int shards, int T_rows, long long ncand_s,
+                  long long nlse_s, int mode,
+                  int topk, float invtemp, uint32_t seed, float top_p, int32_t* __restrict__ ids,
+                  int emit_set, float* __restrict__ out_val, int32_t* __restrict__ out_id) {
+  __shared__ BlockScratch S;
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x, nth = blockDim.x;
+  // candidates of row t: shard s contributes ncand_s entries at ((s*T + t)*ncand_s + j)
+  const long long ncand = ncand_s * shards;
+  const long long nlse = nlse_s * shards;
+  struct View {
+    const float* v; const int32_t* i; long long per, hop;
+    __device__ __forceinline__ long long at(long long j) const {
+      return per == 0 ? j : (j / per) * hop + (j % per);
+    }
+  };
+  const View vw{cand_val + (size_t)t * ncand_s, cand_id + (size_t)t * ncand_s,
+                shards > 1 ? ncand_s : 0, (long long)T_rows * ncand_s};
+#define cv(j) vw.v[vw.at(j)]
+#define ci(j) vw.i[vw.at(j)]
+
+  if (mode <= 1) {
+    float best = QX_NEG_INF;
+    int bid = 0x7fffffff;
+    for (long long j = tid; j < ncand; j += nth) {
+      const int id = ci(j);
+      if (id >= 0 && better(cv(j), id, best, bid)) { best = cv(j); bid = id; }
+    }
+    block_argmax(best, bid, S);
+    if (tid == 0) {
+      if (emit_set) { out_val[t] = best; out_id[t] = bid == 0x7fffffff ? -1 : bid; }
+      else ids[t] = bid;
+    }
+    return;
+  }
+
+  if (mode == 2) {
+    // ---- exact top-k membership by radix select over the candidate keys ----
+    unsigned nvalid_l = 0;
+    for (long long j = tid; j < ncand; j += nth) nvalid_l += ci(j) >= 0 ? 1u : 0u;
+    const unsigned nvalid = block_sum_u(nvalid_l, S);
+    uint32_t tau = 0u;
+    int id_cut = 0x7fffffff;
+    if (nvalid > (unsigned)topk) {
+      uint32_t prefix = 0u, mask = 0u;
+      unsigned remaining = (unsigned)topk, count_eq = 0;
+      for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
+        __syncthreads();
+        for (long long j = tid; j < ncand; j += nth) {
+          if (ci(j) < 0) continue;
+          const uint32_t key = float_key(cv(j));
+          if ((key & mask) == prefix) atomicAdd(&S.hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+          unsigned c = 0;
+          int b = 255;
+          for (; b > 0; --b) {
+            if (c + S.hist[b] >= remaining) break;
+            c += S.hist[b];
+          }
+          S.u[0] = (unsigned)b; S.u[1] = remaining - c; S.u[2] = S.hist[b];
+        }
+        __syncthreads();
+        prefix |= S.u[0] << shift;
+        mask |= 255u << shift;
+        remaining = S.u[1];
+        count_eq = S.u[2];
+        __syncthreads();
+      }
+      tau = prefix;
+      if (count_eq > remaining) {
+        // several candidates share the threshold value: keep the `remaining` smallest ids
+        int cut = -1;
+        for (unsigned r = 0; r < remaining; ++r) {
+          int mine = 0x7fffffff;
+          for (long long j = tid; j < ncand; j += nth) {
+            const int id = ci(j);
+            if (id > cut && float_key(cv(j)) == tau) mine = min(mine, id);
+          }
+          cut = block_min_int(mine, S);
+        }
+        id_cut = cut;
+      }
+    }
+    if (emit_set) {
+      if (tid == 0) S.u[3] = 0u;
+      __syncthreads();
+      for (long long j = tid; j < ncand; j += nth) {
+        const int id = ci(j);
+        if (id < 0) continue;
+        const uint32_t key = float_key(cv(j));
+        if (key > tau || (key == tau && id <= id_cut)) {
+          const unsigned slot = atomicAdd(&S.u[3], 1u);
+          if (slot < (unsigned)topk) {
+            out_val[(size_t)t * topk + slot] = cv(j);
+            out_id[(size_t)t * topk + slot] = id;
+          }
+        }
+      }
+      __syncthreads();
+      for (unsigned slot = S.u[3] + tid; slot < (unsigned)topk; slot += nth) {
+        out_val[(size_t)t * topk + slot] = QX_NEG_INF;
+        out_id[(size_t)t * topk + slot] = -1;
+      }
+      return;
+    }
+    float best = QX_NEG_INF;
+    int bid = 0x7fffffff;
+    for (long long j = tid; j < ncand; j += nth) {
+      const int id = ci(j);
+      if (id < 0) continue;
+      const uint32_t key = float_key(cv(j));
+      if (key > tau || (key == tau && id <= id_cut)) {
+        const float p = cv(j) * invtemp + rng_gumbel(seed, (uint32_t)t, (uint32_t)id);
+        if (better(p, id, best, bid)) { best = p; bid = id; }
+      }
+    }
+    block_argmax(best, bid, S);
+    if (tid == 0) ids[t] = bid == 0x7fffffff ? -1 : bid;
+    return;
+  }
+
+  // ---- mode 3: nucleus over the pooled candidates against the full-vocabulary normalizer ----
+  float mx = QX_NEG_INF;
+  for (long long j = tid; j < ncand; j += nth)
+    if (ci(j) >= 0) mx = fmaxf(mx, cv(j) * invtemp);
+  mx = block_max(mx, S);
+  float Z = 0.f;
+  for (long long j = tid; j < nlse; j += nth) {
+    const float pl = cand_lse[((j / nlse_s) * T_rows + t) * nlse_s + (j % nlse_s)];
+    if (pl > QX_NEG_INF) Z += expf(pl - mx);
+  }
+  Z = block_sum(Z, S);
+  float lo = mx - 40.0f, hi = mx;
+  for (int it = 0; it < 32; ++it) {
+    const float mid = 0.5f * (lo + hi);
+    float sm = 0.f;
+    for (long long j = tid; j < ncand; j += nth) {
+      const float ls = cv(j) * invtemp;
+      if (ci(j) >= 0 && ls >= mid) sm += expf(ls - mx);
+    }
+    sm = block_sum(sm, S) / Z;
+    if (sm >= top_p) lo = mid; else hi = mid;
+  }
+  float best = QX_NEG_INF;
+  int bid = 0x7fffffff;
+  for (long long j = tid; j < ncand; j += nth) {
+    const int id = ci(j);
+    const float ls = cv(j) * invtemp;
+    if (id < 0 || ls < lo) continue;
+    const float p = ls + rng_gumbel(seed, (uint32_t)t, (uint32_t)id);
+    if (better(p, id, best, bid)) { best = p; bid = id; }
+  }
+  block_argmax(best, bid, S);
+  if (tid == 0) ids[t] = (best == QX_NEG_INF || bid == 0x7fffffff) ? -1 : bid;
+}
+#undef cv
+#undef ci
+
+template <int FMT, typename T>
+static void launch_partials_t(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi,
+                              float* pl, int64_t tiles_stride) {
+  // the grid covers tiles_stride tiles so that padding tiles of a short shard are written too
+  dim3 grid((unsigned)tiles_stride, (unsigned)((a.T + LMH_TB - 1) / LMH_TB));
+  lmh_partials_kernel<FMT, T><<<grid, 256, 0, st>>>(
+      (const T*)a.h, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, (int)a.V, (int)a.K,
+      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed);
+  note_launch();
+}
+
+template <typename T>
+static void launch_partials_f(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi,
+                              float* pl, int64_t ts) {
+  switch (a.format) {
+    case F_Q4_0: launch_partials_t<F_Q4_0, T>(st, a, pv, pi, pl, ts); break;
+    case F_Q8_0: launch_partials_t<F_Q8_0, T>(st, a, pv, pi, pl, ts); break;
+    case F_Q6_K: launch_partials_t<F_Q6_K, T>(st, a, pv, pi, pl, ts); break;
+    case F_MXFP8: launch_partials_t<F_MXFP8, T>(st, a, pv, pi, pl, ts); break;
+    case F_NVFP4: launch_partials_t<F_NVFP4, T>(st, a, pv, pi, pl, ts); break;
+    default: launch_partials_t<F_MXFP4, T>(st, a, pv, pi, pl, ts); break;
+  }
+}
+
+void launch_lm_head_partials(cudaStream_t st, const LmHeadArgs& a, float* part_val,
+                             int32_t* part_id, float* part_lse, int64_t tiles_stride) {
+  if (a.dtype == QX_DTYPE_F32) launch_partials_f<float>(st, a, part_val, part_id, part_lse, tiles_stride);
+  else if (a.dtype == QX_DTYPE_F16) launch_partials_f<__half>(st, a, part_val, part_id, part_lse, tiles_stride);
+  else launch_partials_f<__nv_bfloat16>(st, a, part_val, part_id, part_lse, tiles_stride);
+}
+
+void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t* cand_id,
+                           const float* cand_lse, int shards, int64_t T, int64_t ncand,
+                           int64_t nlse, int mode, int topk, float invtemp, uint32_t seed,
+                           float top_p, int32_t* ids, int emit_set, float* out_val,
+                           int32_t* out_id) {
+  lmh_reduce_kernel<<<(unsigned)T, LMH_RED_THREADS, 0, st>>>(
+      cand_val, cand_id, cand_lse, shards, (int)T, (long long)ncand, (long long)(nlse > 0 ? nlse : 1),
+      mode, topk, invtemp, seed, top_p, ids, emit_set, out_val, out_id);
+  note_launch();
+}
+
+}  // namespace qx

@@ -1,0 +1,168 @@
+"""Multi-GPU forms of the path: one process per GPU, torch.distributed (NCCL over NVLink) only
+for the small exchange steps.
+
+Vocabulary-parallel `lm_head_sample`: the vocabulary is cut at multiples of 256 so that every
+256-row tile of the reference's top-p pool lives on one GPU; each rank runs stage 1 on its rows
+(ids stay global), one all-gather moves the per-rank candidates ((val,id) per row for argmax /
+categorical, k pairs for top-k, the tile pools and tile log-sum-exps for top-p), and every rank
+runs the same stage 2.  Max-with-lowest-id, top-k-of-top-k and sum-of-exp merges are associative,
+so the ids equal the single-GPU call on the same logits.  The reference has no multi-device code;
+the split follows its two-stage tile -> reduce structure
+(kernels/quantization/lm_head/lm_head.metal:219-235, :444-529).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .tk import _LM_HEAD_MODES, _LM_QUANT_BLOCK_K
+from .tk_torch import _DT, _check, _check_lm_head, _ptr, _stream
+
+TILE_V = 256
+
+
+def vocab_shard_bounds(V: int, shards: int):
+    """[(row_begin, row_end)] per shard: whole 256-row tiles, spread as evenly as possible."""
+    tiles = (V + TILE_V - 1) // TILE_V
+    base, extra = divmod(tiles, shards)
+    out, t = [], 0
+    for s in range(shards):
+        n = base + (1 if s < extra else 0)
+        out.append((min(t * TILE_V, V), min((t + n) * TILE_V, V)))
+        t += n
+    return out
+
+
+def max_shard_tiles(V: int, shards: int) -> int:
+    tiles = (V + TILE_V - 1) // TILE_V
+    return max(1, -(-tiles // shards))
+
+
+def _mode_id(mode) -> int:
+    if isinstance(mode, str):
+        if mode not in _LM_HEAD_MODES:
+            raise ValueError(f"lm_head_sample: mode must be one of {list(_LM_HEAD_MODES)}")
+        return _LM_HEAD_MODES[mode]
+    return int(mode)
+
+
+def candidate_layout(mode, k: int, max_tiles: int):
+    """(C, L): candidates and tile log-sum-exps a shard emits per hidden row."""
+    m = _mode_id(mode)
+    kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
+    C = int(_lib.lib().qx_cuda_lm_head_shard_candidates(m, max(kk, 1), max_tiles))
+    return C, (max_tiles if m == 3 else 0)
+
+
+def lm_head_shard_partials(h, wq_local, bias_local, vocab_offset: int, max_tiles: int, fmt: str,
+                           mode, k=0, temperature=1.0, seed=0, out=None):
+    """Stage 1 on this shard's rows.  Returns one fp32 tensor (T, 2C + L) holding, per row,
+    C candidate values, C candidate ids (int32 bits) and L tile log-sum-exps: a single buffer so
+    that one all-gather moves everything."""
+    m = _mode_id(mode)
+    kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
+    if fmt not in _LM_QUANT_BLOCK_K:
+        raise ValueError(f"lm_head_sample: quant format must be one of {list(_LM_QUANT_BLOCK_K)}")
+    V_local = wq_local.shape[0]
+    K = wq_local.shape[1] * _LM_QUANT_BLOCK_K[fmt]
+    _check_lm_head(h, wq_local, bias_local, V_local, K, fmt, m, kk, float(temperature), 1.0)
+    T = h.size(0)
+    C, L = candidate_layout(m, kk, max_tiles)
+    lib = _lib.lib()
+    with torch.cuda.device(h.device):
+        hc, wc = h.contiguous(), wq_local.contiguous()
+        bc = None
+        if bias_local is not None and bias_local.numel() > 1:
+            _check(bias_local.numel() == V_local, "lm_head_sample_q: bias must be (V,)")
+            bc = bias_local.to(torch.float32).contiguous()
+        # planar layout inside the buffer: [T*C vals | T*C ids | T*L lses]
+        if out is None:
+            out = torch.empty(T * (2 * C + L), dtype=torch.float32, device=h.device)
+        val = out[: T * C]
+        idt = out[T * C: 2 * T * C]
+        lse = out[2 * T * C:] if L else None
+        nbytes = lib.qx_cuda_lm_head_shard_workspace_bytes(T, V_local, m, max(kk, 1))
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=h.device)
+        _lib.check(lib.qx_cuda_lm_head_shard_partials_q(
+            _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(val), _ptr(idt), _ptr(lse), _ptr(ws),
+            nbytes, T, V_local, K, int(vocab_offset), int(max_tiles), fmt.encode(), _DT[h.dtype], m,
+            max(kk, 1), float(temperature), int(seed) & 0xFFFFFFFF))
+    return out
+
+
+def lm_head_reduce_gathered(gathered, shards: int, T: int, max_tiles: int, mode, k=0,
+                            temperature=1.0, seed=0, top_p=0.9):
+    """Stage 2 over `shards` stage-1 buffers laid end to end (the all-gather output)."""
+    m = _mode_id(mode)
+    kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
+    C, L = candidate_layout(m, kk, max_tiles)
+    per = T * (2 * C + L)
+    g = gathered.view(shards, per)
+    with torch.cuda.device(gathered.device):
+        # regroup the planar per-shard buffers into (S,T,C) vals, (S,T,C) ids, (S,T,L) lses
+        val = g[:, : T * C].contiguous()
+        idt = g[:, T * C: 2 * T * C].contiguous()
+        lse = g[:, 2 * T * C:].contiguous() if L else None
+        ids = torch.empty(T, dtype=torch.int32, device=gathered.device)
+        _lib.check(_lib.lib().qx_cuda_lm_head_shard_reduce(
+            _stream(), _ptr(val), _ptr(idt), _ptr(lse), _ptr(ids), shards, T, max_tiles, m,
+            max(kk, 1), float(temperature), int(seed) & 0xFFFFFFFF, float(top_p)))
+    return ids
+
+
+def lm_head_merge(parts, mode, k=0, temperature=1.0, seed=0, top_p=0.9, max_tiles=None):
+    """Merge stage-1 buffers that already sit on one device (single-process form of the
+    exchange, used by tests and by callers that own several shards)."""
+    m = _mode_id(mode)
+    kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
+    per = parts[0].numel()
+    if m == 3:
+        if max_tiles is None:                      # per = T*(2*mt*kk + mt): needs T; infer below
+            raise ValueError("lm_head_merge: pass max_tiles for mode topp")
+        T = per // (2 * max_tiles * kk + max_tiles)
+    else:
+        max_tiles = max_tiles or 1
+        C = 1 if m <= 1 else kk
+        T = per // (2 * C)
+    return lm_head_reduce_gathered(torch.cat([p.reshape(-1) for p in parts]), len(parts), T,
+                                   max_tiles, m, kk, temperature, seed, top_p)
+
+
+class VocabParallelLMHead:
+    """One rank's shard of a packed LM head plus the merge over a process group.
+
+    wq_local holds rows [begin, end) of the full (V, K/block_k, block_bytes) matrix, where
+    (begin, end) = vocab_shard_bounds(V, world)[rank].  `sample` returns the same int32 (T,)
+    ids on every rank."""
+
+    def __init__(self, wq_local, V: int, fmt: str, group=None, bias_local=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.V, self.fmt = int(V), fmt
+        self.begin, self.end = vocab_shard_bounds(self.V, self.world)[self.rank]
+        _check(wq_local.shape[0] == self.end - self.begin,
+               "VocabParallelLMHead: wq_local must hold this rank's rows of vocab_shard_bounds")
+        self.wq, self.bias = wq_local, bias_local
+        self.max_tiles = max_shard_tiles(self.V, self.world)
+        self._gather = {}
+
+    def sample(self, h, mode="argmax", k=0, temperature=1.0, seed=0, top_p=0.9):
+        m = _mode_id(mode)
+        kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
+        T = h.size(0)
+        C, L = candidate_layout(m, kk, self.max_tiles)
+        per = T * (2 * C + L)
+        key = (per, h.device)
+        if key not in self._gather:
+            self._gather[key] = torch.empty(self.world * per, dtype=torch.float32, device=h.device)
+        g = self._gather[key]
+        mine = g[self.rank * per:(self.rank + 1) * per]
+        lm_head_shard_partials(h, self.wq, self.bias, self.begin, self.max_tiles, self.fmt, m, kk,
+                               temperature, seed, out=mine)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(g, mine, group=self.group)
+        return lm_head_reduce_gathered(g, self.world, T, self.max_tiles, m, kk, temperature, seed,
+                                       top_p)

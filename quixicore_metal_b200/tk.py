@@ -1,0 +1,89 @@
+"""The reference's public operator API (`tk`) for the decode-projection path, on CUDA tensors.
+
+Mirrors the routers of bindings/python/tk/__init__.py: `decode_linear_epilogue` (:3694-3748),
+`decode_swiglu` (:3751-3793), `lm_head_sample` with `format=` (:2357-2412) and the output-quant
+helper (:3684-3691): same keyword names, defaults and ValueError texts.  Only packed formats are
+served here; the dense-weight routes of the reference call the framework matmul and are not part
+of this backend.
+"""
+from __future__ import annotations
+
+from . import tk_torch as _tt
+
+_ACTIVATIONS = {"none": 0, None: 0, "gelu": 1, "silu": 2}
+_LM_HEAD_MODES = {"argmax": 0, "categorical": 1, "topk": 2, "topp": 3}
+_LM_QUANT_BLOCK_K = {"q8_0": 32, "q4_0": 32, "q6_K": 256, "mxfp8": 32, "nvfp4": 16, "mxfp4": 32}
+
+
+def quantize_per_token_fp8(x):
+    return _tt.quantize_per_token_fp8(x)
+
+
+def quantize_per_token_int8(x):
+    return _tt.quantize_per_token_int8(x)
+
+
+def _decode_quantize_output(output, output_quant):
+    if output_quant is None:
+        return output
+    if output_quant == "fp8":
+        return quantize_per_token_fp8(output)
+    if output_quant == "int8":
+        return quantize_per_token_int8(output)
+    if output_quant == "mxfp8":       # extension: packed MXFP8 rows (e4m3 codes, e8m0 per 32)
+        return _tt.quantize_mxfp8_rows(output)
+    raise ValueError("output_quant must be None, 'fp8', 'int8', or 'mxfp8'")
+
+
+def decode_linear_epilogue(x, weight, bias=None, residual=None, activation="none", format=None,
+                           output_quant=None, use_kernel=None):
+    """residual + activation(x @ dequant(weight).T + bias), fp32 accumulation, one rounding to
+    x.dtype.  activation: none / gelu (erf) / silu.  output_quant composes the per-token fp8 /
+    int8 quantizer (returns (codes, scale)) or, as an extension, 'mxfp8' packed rows."""
+    if activation not in _ACTIVATIONS:
+        raise ValueError("activation must be 'none', 'gelu', or 'silu'")
+    if format is None:
+        raise ValueError("decode_linear_epilogue: this backend serves packed weights only; "
+                         "pass format=q4_0/q8_0/q6_K/mxfp8/nvfp4/mxfp4")
+    if use_kernel is not None and not use_kernel:
+        raise ValueError("decode_linear_epilogue: use_kernel=False requires a dense weight")
+    use_bias, use_residual = bias is not None, residual is not None
+    out = _tt.decode_linear_epilogue(x, weight, bias if use_bias else x,
+                                     residual if use_residual else x, str(format),
+                                     _ACTIVATIONS[activation], use_bias, use_residual)
+    return _decode_quantize_output(out, output_quant)
+
+
+def decode_swiglu(x, gate_weight, up_weight, gate_bias=None, up_bias=None, format=None,
+                  output_quant=None, use_kernel=None):
+    """silu(gate) * up over two packed projections sharing the activation reads."""
+    if (gate_bias is None) != (up_bias is None):
+        raise ValueError("decode_swiglu: gate_bias and up_bias must both be present or omitted")
+    if format is None:
+        raise ValueError("decode_swiglu: this backend serves packed weights only; "
+                         "pass format=q4_0/q8_0/q6_K/mxfp8/nvfp4/mxfp4")
+    if use_kernel is not None and not use_kernel:
+        raise ValueError("decode_swiglu: use_kernel=False requires dense weights")
+    use_bias = gate_bias is not None
+    out = _tt.decode_swiglu(x, gate_weight, up_weight, gate_bias if use_bias else x,
+                            up_bias if use_bias else x, str(format), use_bias)
+    return _decode_quantize_output(out, output_quant)
+
+
+def lm_head_sample(h, W, mode="argmax", k=0, temperature=1.0, seed=0, bias=None, fused=False,
+                   format=None, top_p=0.9):
+    """One token id per row of h over a packed (V, K/block_k, block_bytes) head, without ever
+    writing the (T, V) logits.  mode: argmax / categorical / topk / topp; k defaults to 32 for
+    topk / topp; the noise is keyed by the global vocab id, so the draw equals the unfused
+    sampler on the same logits and seed."""
+    if mode not in _LM_HEAD_MODES:
+        raise ValueError(f"lm_head_sample: mode must be one of {list(_LM_HEAD_MODES)}")
+    if format is None:
+        raise ValueError("lm_head_sample: this backend serves packed weights only; pass format=")
+    if format not in _LM_QUANT_BLOCK_K:
+        raise ValueError(f"lm_head_sample: quant format must be one of {list(_LM_QUANT_BLOCK_K)}")
+    kk = int(k) if int(k) > 0 else (32 if mode in ("topk", "topp") else 0)
+    V = W.shape[0]
+    K = W.shape[1] * _LM_QUANT_BLOCK_K[format]
+    return _tt.lm_head_sample_q(h, W, bias, V, K, format, _LM_HEAD_MODES[mode], kk,
+                                float(temperature), int(seed), float(top_p))

@@ -1,0 +1,177 @@
+"""`tk_torch`-compatible binding for CUDA tensors on B200.
+
+Same function names, positional arguments and error behaviour (RuntimeError with the reference's
+message text) as the reference's PyTorch-MPS module for the decode-projection path
+(bindings/pytorch_mps/tk_torch/__init__.py:932-958, :1738-1745), so the reference's Python router
+`tk` can call it unchanged when handed CUDA tensors.  Every function enqueues on torch's current
+CUDA stream through the C ABI of libquixicore_cuda.so; torch only provides device memory and the
+stream.  There is no eager / CPU fallback: a missing library or a non-CUDA tensor raises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+_BLOCK = {"q4_0": (32, 18), "q8_0": (32, 34), "q6_K": (256, 210), "mxfp8": (32, 33),
+          "nvfp4": (16, 9), "mxfp4": (32, 17)}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_weight(x, weight, fmt: str, name: str) -> int:
+    """The reference's check_decode_epilogue_weight (torch_kernels.mm:6376-6405) for CUDA."""
+    _check(x.is_cuda and weight.is_cuda and x.dtype in _DT and x.dim() == 2 and x.size(0) > 0
+           and x.size(1) > 0, f"{name}: x must be non-empty (B,K) fp32/fp16/bf16")
+    _check(fmt in _BLOCK, f"{name}: format must be q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4 "
+           "(dense weights are routed to the framework matmul, not to this backend)")
+    bk, bb = _BLOCK[fmt]
+    K = x.size(1)
+    _check(weight.dtype == torch.uint8 and weight.dim() == 3 and weight.size(0) > 0 and K % bk == 0
+           and weight.size(1) == K // bk and weight.size(2) == bb,
+           f"{name}: packed weight must be uint8 (N,K/block_k,block_bytes)")
+    return weight.size(0)
+
+
+def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
+                           use_bias=False, use_residual=False):
+    """Packed decode linear with fused bias, activation and residual; returns (B,N) in x.dtype.
+    Absent bias / residual are passed as placeholders and ignored when their flag is false."""
+    fmt, activation = str(format), int(activation)
+    _check(0 <= activation <= 2, "decode_linear_epilogue: activation must be 0, 1, or 2")
+    N = _check_weight(x, weight, fmt, "decode_linear_epilogue")
+    B, K = x.shape
+    _check(not use_bias or (bias.is_cuda and bias.dim() == 1 and bias.size(0) == N
+                            and bias.dtype == x.dtype),
+           "decode_linear_epilogue: bias must be (N,) with x dtype")
+    _check(not use_residual or (residual.is_cuda and residual.dim() == 2 and residual.size(0) == B
+                                and residual.size(1) == N and residual.dtype == x.dtype),
+           "decode_linear_epilogue: residual must be (B,N) with x dtype")
+    with torch.cuda.device(x.device):
+        xc, wc = x.contiguous(), weight.contiguous()
+        bc = bias.contiguous() if use_bias else None
+        rc = residual.contiguous() if use_residual else None
+        out = torch.empty((B, N), dtype=x.dtype, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_decode_linear_epilogue(
+            _stream(), _ptr(xc), _ptr(wc), _ptr(bc), _ptr(rc), _ptr(out), B, K, N, fmt.encode(),
+            _DT[x.dtype], activation, int(bool(use_bias)), int(bool(use_residual))))
+    return out
+
+
+def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_bias=False):
+    """Packed gate/up decode projections with fused SwiGLU: silu(gate.x+gb) * (up.x+ub)."""
+    fmt = str(format)
+    N = _check_weight(x, gate_weight, fmt, "decode_swiglu")
+    up_N = _check_weight(x, up_weight, fmt, "decode_swiglu")
+    _check(up_N == N and up_weight.shape == gate_weight.shape,
+           "decode_swiglu: gate and up weights must have identical shapes")
+    _check(not use_bias or (gate_bias.is_cuda and up_bias.is_cuda and gate_bias.dtype == x.dtype
+                            and up_bias.dtype == x.dtype and gate_bias.dim() == 1
+                            and up_bias.dim() == 1 and gate_bias.size(0) == N
+                            and up_bias.size(0) == N),
+           "decode_swiglu: both biases must be (N,) with x dtype")
+    B, K = x.shape
+    with torch.cuda.device(x.device):
+        xc, gc, uc = x.contiguous(), gate_weight.contiguous(), up_weight.contiguous()
+        gb = gate_bias.contiguous() if use_bias else None
+        ub = up_bias.contiguous() if use_bias else None
+        out = torch.empty((B, N), dtype=x.dtype, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_decode_swiglu(
+            _stream(), _ptr(xc), _ptr(gc), _ptr(uc), _ptr(gb), _ptr(ub), _ptr(out), B, K, N,
+            fmt.encode(), _DT[x.dtype], int(bool(use_bias))))
+    return out
+
+
+def _quantize_per_token(x, kind: int, name: str):
+    _check(x.is_cuda and x.dtype in _DT and x.dim() >= 1 and x.numel() > 0,
+           f"{name}: x must be a non-empty CUDA fp32/fp16/bf16 tensor")
+    D = x.size(-1)
+    rows = x.numel() // D
+    with torch.cuda.device(x.device):
+        xc = x.contiguous()
+        codes = torch.empty(x.shape, dtype=torch.uint8 if kind == 0 else torch.int8, device=x.device)
+        scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_quantize_per_token(
+            _stream(), _ptr(xc), _ptr(codes), _ptr(scale), rows, D, _DT[x.dtype], kind))
+    return codes, scale
+
+
+def quantize_per_token_fp8(x):
+    """Per-row fp8 e4m3 quant. Returns (codes uint8, scale f32), scale = absmax/448."""
+    return _quantize_per_token(x, 0, "quantize_per_token_fp8")
+
+
+def quantize_per_token_int8(x):
+    """Per-row symmetric int8 quant. Returns (codes int8, scale f32), scale = absmax/127."""
+    return _quantize_per_token(x, 1, "quantize_per_token_int8")
+
+
+def quantize_mxfp8_rows(x):
+    """(rows, D) -> packed MXFP8 blocks (rows, D/32, 33): e8m0 exponent + 32 e4m3 codes, the
+    block layout the mxfp8 weight format uses.  Extension over the reference's per-token
+    output_quant: the per-group rule with G = 32 and power-of-two scales."""
+    _check(x.is_cuda and x.dtype in _DT and x.dim() == 2 and x.size(1) % 32 == 0 and x.numel() > 0,
+           "quantize_mxfp8_rows: x must be CUDA (rows, D) fp32/fp16/bf16 with D % 32 == 0")
+    rows, D = x.shape
+    with torch.cuda.device(x.device):
+        xc = x.contiguous()
+        blocks = torch.empty((rows, D // 32, 33), dtype=torch.uint8, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_quantize_mxfp8_rows(
+            _stream(), _ptr(xc), _ptr(blocks), rows, D, _DT[x.dtype]))
+    return blocks
+
+
+def _check_lm_head(h, Wq, bias, V, K, fmt, mode, topk, temperature, top_p):
+    _check(h.is_cuda and Wq.is_cuda and (bias is None or bias.is_cuda) and h.dtype in _DT,
+           "lm_head_sample_q: inputs must be CUDA and h must be floating point")
+    _check(h.dim() == 2 and h.size(1) == K, "lm_head_sample_q: h must be (T, K)")
+    _check(0 <= mode <= 3, "lm_head_sample_q: mode 0=argmax, 1=categorical, 2=topk, 3=topp")
+    _check(temperature > 0.0, "lm_head_sample_q: temperature must be positive")
+    _check(fmt in _BLOCK, "lm_head_sample_q: format must be q8_0, q4_0, q6_K, mxfp8, nvfp4, or mxfp4")
+    bk, bb = _BLOCK[fmt]
+    _check(K % bk == 0 and Wq.dtype == torch.uint8 and Wq.dim() == 3 and Wq.size(0) == V
+           and Wq.size(1) == K // bk and Wq.size(2) == bb,
+           "lm_head_sample_q: packed weight shape does not match V/K/format")
+    _check(h.size(0) > 0 and V > 0 and K > 0, "lm_head_sample_q: T, V, and K must be positive")
+    if mode in (2, 3):
+        _check(1 <= topk <= 64, "lm_head_sample_q: k must be in [1, 64]")
+        _check(mode != 3 or 0.0 < top_p <= 1.0, "lm_head_sample_q: topp requires top_p in (0, 1]")
+
+
+def lm_head_sample_q(h, Wq, bias, V, K, fmt, mode, topk, temperature, seed, top_p=0.0):
+    """Fused LM head + sampling over packed weights; logits are never written to memory.
+    mode 0 argmax, 1 categorical, 2 top-k, 3 top-p (nucleus over the per-256-row top-k pool with
+    the exact full-vocabulary normalizer).  bias: fp32 (V,) or a 1-element placeholder.
+    Returns int32 (T,).  Unlike the Metal original, q6_K takes every mode and every h dtype."""
+    V, K, fmt, mode, topk = int(V), int(K), str(fmt), int(mode), int(topk)
+    temperature, seed, top_p = float(temperature), int(seed), float(top_p)
+    _check_lm_head(h, Wq, bias, V, K, fmt, mode, topk, temperature, top_p)
+    if mode in (2, 3):
+        _check(topk <= V, "lm_head_sample_q: k must be <= vocab size V")
+    T = h.size(0)
+    use_bias = bias is not None and bias.numel() > 1
+    if use_bias:
+        _check(bias.numel() == V, "lm_head_sample_q: bias must be (V,)")
+    with torch.cuda.device(h.device):
+        hc, wc = h.contiguous(), Wq.contiguous()
+        bc = bias.to(torch.float32).contiguous() if use_bias else None
+        out = torch.empty((T,), dtype=torch.int32, device=h.device)
+        L = _lib.lib()
+        nbytes = L.qx_cuda_lm_head_workspace_bytes(T, V, mode, topk)
+        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=h.device)
+        _lib.check(L.qx_cuda_lm_head_sample_q(
+            _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(out), _ptr(ws), nbytes, T, V, K,
+            fmt.encode(), _DT[h.dtype], mode, topk, temperature, seed & 0xFFFFFFFF, top_p))
+    return out

@@ -1,0 +1,212 @@
+"""GPU parity of decode_linear_epilogue / decode_swiglu / output quantizers against the CPU oracle.
+Every call goes through the C ABI (via the tk_torch-compatible binding)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import qx_oracle as O
+from tests._util import FMTS, assert_close_dtype, dev, host, rounded
+
+pytestmark = pytest.mark.gpu
+
+tk = pytest.importorskip("quixicore_metal_b200.tk")
+ACT = {"none": 0, "gelu": 1, "silu": 2}
+
+
+def _inputs(fmt, M, K, N, dtype, seed, xs=1.0, ws=0.02, random_bytes=False):
+    rng = np.random.default_rng(seed)
+    x = rounded(xs * rng.standard_normal((M, K)), dtype)
+    if random_bytes:
+        Wq = O.random_packed(fmt, N, K, seed + 1)
+    else:
+        Wq = O.synth_pack(fmt, (ws * rng.standard_normal((N, K))).astype(np.float32))
+    bias = rounded(0.01 * rng.standard_normal(N), dtype)
+    res = rounded(rng.standard_normal((M, N)), dtype)
+    return x, Wq, bias, res
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("activation", ["none", "gelu", "silu"])
+@pytest.mark.parametrize("fmt", FMTS)
+def test_epilogue_reference_test_shape(fmt, activation, dtype):
+    # shape and scales of tests/correctness/matmul/decode_linear/test_decode_linear.py:155-171
+    rng = np.random.default_rng(131 + len(fmt) + len(activation))
+    B, K, N = 2, 512, 35
+    x = rounded(0.08 * rng.standard_normal((B, K)), dtype)
+    Wq = O.synth_pack(fmt, (0.1 * rng.standard_normal((N, K))).astype(np.float32))
+    bias = rounded(0.02 * rng.standard_normal(N), dtype)
+    res = rounded(0.03 * rng.standard_normal((B, N)), dtype)
+    got = tk.decode_linear_epilogue(dev(x, dtype), dev(Wq), dev(bias, dtype), dev(res, dtype),
+                                    activation=activation, format=fmt)
+    ref = O.decode_linear_epilogue(x, Wq, fmt, bias, res, ACT[activation], dtype)
+    assert got.shape == (B, N) and got.dtype == dev(x, dtype).dtype
+    assert_close_dtype(host(got), ref, dtype, scale=0.1)
+    # the reference's own tolerance
+    np.testing.assert_allclose(host(got), ref, rtol=7e-4 if dtype == "f32" else 4e-2,
+                               atol=7e-4 if dtype == "f32" else 4e-2)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_epilogue_golden_fixture_from_reference(fmt, golden_dir):
+    """Inputs packed by the reference's quantizers, outputs of the reference's torch-CPU path."""
+    C = np.load(os.path.join(golden_dir, "compose.npz"))
+    x, bias, bias2, res = C[f"{fmt}_x"], C[f"{fmt}_bias"], C[f"{fmt}_bias2"], C[f"{fmt}_res"]
+    for act in ("none", "silu"):
+        got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(C[f"{fmt}_gate"]), dev(bias, "bf16"),
+                                        dev(res, "bf16"), activation=act, format=fmt)
+        assert_close_dtype(host(got), C[f"{fmt}_lin_{act}"], "bf16")
+    got = tk.decode_swiglu(dev(x, "bf16"), dev(C[f"{fmt}_gate"]), dev(C[f"{fmt}_up"]),
+                           dev(bias, "bf16"), dev(bias2, "bf16"), format=fmt)
+    assert_close_dtype(host(got), C[f"{fmt}_swiglu"], "bf16")
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_epilogue_every_code_value(fmt):
+    """Random bytes: all 256 code values of every field, including e4m3 exponent-15 codes."""
+    x, Wq, bias, res = _inputs(fmt, 3, 512, 48, "f32", 7, random_bytes=True)
+    got = tk.decode_linear_epilogue(dev(x), dev(Wq), dev(bias), dev(res), format=fmt)
+    ref = O.decode_linear_epilogue(x, Wq, fmt, bias, res, 0, "f32")
+    scale = float(np.abs(O.dequantize(fmt, Wq)).max()) * 30
+    assert_close_dtype(host(got), ref, "f32", scale=scale)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 9, 16, 17])
+@pytest.mark.parametrize("fmt", FMTS)
+def test_epilogue_batch_sweep_bf16(fmt, M):
+    K = 1024 if fmt != "q6_K" else 2048
+    x, Wq, bias, res = _inputs(fmt, M, K, 130, "bf16", 11 + M)
+    got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), dev(res, "bf16"),
+                                    activation="silu", format=fmt)
+    ref = O.decode_linear_epilogue(x, Wq, fmt, bias, res, 2, "bf16")
+    assert_close_dtype(host(got), ref, "bf16")
+
+
+@pytest.mark.parametrize("fmt,K", [("q4_0", 32), ("q4_0", 96), ("q8_0", 160), ("q6_K", 256),
+                                   ("mxfp8", 32), ("nvfp4", 16), ("nvfp4", 48), ("nvfp4", 272),
+                                   ("mxfp4", 224)])
+@pytest.mark.parametrize("N", [1, 7, 33])
+def test_epilogue_ragged_shapes(fmt, K, N):
+    """Smallest legal K, K that is not a multiple of any load width, N = 1."""
+    x, Wq, bias, res = _inputs(fmt, 2, K, N, "bf16", 3 + K + N)
+    got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), None, dev(res, "bf16"), format=fmt)
+    ref = O.decode_linear_epilogue(x, Wq, fmt, None, res, 0, "bf16")
+    assert_close_dtype(host(got), ref, "bf16")
+    got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), None, format=fmt)
+    assert_close_dtype(host(got), O.decode_linear_epilogue(x, Wq, fmt, bias, None, 0, "bf16"), "bf16")
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("fmt", FMTS)
+def test_swiglu_reference_test_shape(fmt, dtype):
+    # tests/correctness/matmul/decode_linear/test_decode_linear.py:174-201
+    rng = np.random.default_rng(151 + len(fmt))
+    B, K, N = 2, 512, 33
+    x = rounded(0.07 * rng.standard_normal((B, K)), dtype)
+    g = O.synth_pack(fmt, (0.09 * rng.standard_normal((N, K))).astype(np.float32))
+    u = O.synth_pack(fmt, (0.08 * rng.standard_normal((N, K))).astype(np.float32))
+    gb = rounded(0.02 * rng.standard_normal(N), dtype)
+    ub = rounded(0.02 * rng.standard_normal(N), dtype)
+    got = tk.decode_swiglu(dev(x, dtype), dev(g), dev(u), dev(gb, dtype), dev(ub, dtype), format=fmt)
+    ref = O.decode_swiglu(x, g, u, fmt, gb, ub, dtype)
+    assert_close_dtype(host(got), ref, dtype, scale=0.01)
+    got = tk.decode_swiglu(dev(x, dtype), dev(g), dev(u), format=fmt)
+    assert_close_dtype(host(got), O.decode_swiglu(x, g, u, fmt, None, None, dtype), dtype, scale=0.01)
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_swiglu_mlp_config_shapes_q6k(M):
+    """Llama-3-8B MLP row shapes (hidden 4096) on a slice of the intermediate dimension, then
+    the down projection with residual: the two-launch composition of the reference."""
+    rng = np.random.default_rng(40 + M)
+    K, I = 4096, 512
+    x = rounded(rng.standard_normal((M, K)), "bf16")
+    g = O.synth_pack("q6_K", (0.02 * rng.standard_normal((I, K))).astype(np.float32))
+    u = O.synth_pack("q6_K", (0.02 * rng.standard_normal((I, K))).astype(np.float32))
+    d = O.synth_pack("q6_K", (0.02 * rng.standard_normal((256, I))).astype(np.float32))
+    res = rounded(rng.standard_normal((M, 256)), "bf16")
+    mid = tk.decode_swiglu(dev(x, "bf16"), dev(g), dev(u), format="q6_K")
+    mid_ref = O.decode_swiglu(x, g, u, "q6_K", None, None, "bf16")
+    assert_close_dtype(host(mid), mid_ref, "bf16")
+    out = tk.decode_linear_epilogue(mid, dev(d), None, dev(res, "bf16"), format="q6_K")
+    ref = O.decode_linear_epilogue(host(mid), d, "q6_K", None, res, 0, "bf16")
+    assert_close_dtype(host(out), ref, "bf16")
+
+
+# ---- output quantizers: codes are bit-exact given the identical pre-quant values --------------
+@pytest.mark.parametrize("kind", ["fp8", "int8"])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_per_token_quantizer_bit_exact(kind, dtype):
+    rng = np.random.default_rng(5)
+    y = rounded(rng.standard_normal((7, 333)) * np.array([[1e-3], [1], [50], [0], [3], [1e4], [2e-6]]), dtype)
+    fn = tk.quantize_per_token_fp8 if kind == "fp8" else tk.quantize_per_token_int8
+    codes, scale = fn(dev(y, dtype))
+    rc, rs = O.quantize_per_token(y, kind)
+    np.testing.assert_array_equal(host(scale).view(np.uint32), rs.view(np.uint32))
+    np.testing.assert_array_equal(host(codes).view(np.uint8), rc.view(np.uint8))
+
+
+def test_e4m3_midpoints_round_away_from_zero():
+    """Exact half-way inputs (common for bf16 values under a power-of-two scale)."""
+    dec = O.e4m3_decode(np.arange(256))
+    pos = np.arange(0, 0x7E)
+    mid = ((dec[pos].astype(np.float64) + dec[pos + 1]) / 2).astype(np.float32)
+    row = np.concatenate([mid, -mid, [448.0, -448.0]]).astype(np.float32)[None, :]   # amax 448 -> scale 1
+    codes, scale = tk.quantize_per_token_fp8(dev(row))
+    assert float(scale[0]) == 1.0
+    want = np.concatenate([pos + 1, (pos + 1) | 0x80, [0x7E, 0xFE]]).astype(np.uint8)
+    np.testing.assert_array_equal(host(codes)[0], want)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_mxfp8_rows_bit_exact(dtype):
+    rng = np.random.default_rng(9)
+    y = rounded(rng.standard_normal((5, 256)) * np.array([[1e-4], [1], [300], [0], [7]]), dtype)
+    y[1, 32:64] = 0
+    y[2, :32] = rounded(np.full(32, 448.0), dtype)
+    from quixicore_metal_b200 import tk_torch
+    blocks = tk_torch.quantize_mxfp8_rows(dev(y, dtype))
+    np.testing.assert_array_equal(host(blocks), O.quantize_mxfp8_rows(y))
+
+
+def test_epilogue_output_quant_composition():
+    """decode_linear_epilogue(..., output_quant=...) = quantizer applied to the rounded output."""
+    x, Wq, bias, res = _inputs("nvfp4", 4, 1024, 256, "bf16", 21)
+    y = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), None, format="nvfp4")
+    for oq in ("fp8", "int8"):
+        codes, scale = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), None,
+                                                 format="nvfp4", output_quant=oq)
+        rc, rs = O.quantize_per_token(host(y), oq)
+        np.testing.assert_array_equal(host(codes).view(np.uint8), rc.view(np.uint8))
+        np.testing.assert_array_equal(host(scale), rs)
+    blocks = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), None,
+                                       format="nvfp4", output_quant="mxfp8")
+    np.testing.assert_array_equal(host(blocks), O.quantize_mxfp8_rows(host(y)))
+    # int8 reconstruction bound of test_decode_linear.py:204-215
+    codes, scale = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), None, None, format="nvfp4",
+                                             activation="silu", output_quant="int8")
+    dense = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), None, None, format="nvfp4", activation="silu")
+    err = np.max(np.abs(host(codes).astype(np.float32) * host(scale)[:, None] - host(dense)))
+    assert err <= float(host(scale).max()) * 0.51 + 1e-6
+
+
+def test_error_behaviour_matches_reference_messages():
+    x = torch.zeros(2, 64, device="cuda")
+    w = torch.zeros(3, 2, 18, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="packed weight must be uint8"):
+        tk.decode_linear_epilogue(x, w[:, :1], format="q4_0")
+    with pytest.raises(RuntimeError, match="format must be"):
+        tk.decode_linear_epilogue(x, w, format="q5_1")
+    with pytest.raises(ValueError, match="activation must be"):
+        tk.decode_linear_epilogue(x, w, format="q4_0", activation="relu")
+    with pytest.raises(RuntimeError, match="bias must be"):
+        tk.decode_linear_epilogue(x, w, bias=torch.zeros(4, device="cuda"), format="q4_0")
+    with pytest.raises(ValueError, match="both be present"):
+        tk.decode_swiglu(x, w, w, gate_bias=torch.zeros(3, device="cuda"), format="q4_0")
+    with pytest.raises(ValueError, match="output_quant"):
+        tk.decode_linear_epilogue(x, w, format="q4_0", output_quant="fp4")
+    # placeholders are ignored when the flag is off (the router passes x itself)
+    from quixicore_metal_b200 import tk_torch
+    y = tk_torch.decode_linear_epilogue(x, w, x, x, "q4_0", 0, False, False)
+    assert y.shape == (2, 3) and float(y.abs().max()) == 0.0
