@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized decode-projection hot path on B200.
+
+Headline (the metric that scales over GPUs): fused `lm_head_sample` tokens/s over a 128256-token
+vocabulary, hidden 4096, q8_0 weights, 64 hidden rows per step, top-p = 0.9 at temperature 0.8
+(pool k' = 32), vocabulary split over the GPUs with one NCCL all-gather of the per-shard
+candidates.  Also reported in the same JSON line: the batch-1..8 packed GEMV bandwidth of the
+other configurations ("gemv"), the roofline of the dominant kernel, the CPU baseline (the
+reference's dequantise -> torch-CPU matmul -> sampler composition, restated) and clocks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Inputs are synthetic (seeded Gaussians quantised on the fly); nothing is read from disk.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+V_FULL, K_HID, T_ROWS = 128256, 4096, 64
+FMT, MODE, TOPK, TEMP, TOP_P, SEED = "q8_0", "topp", 32, 0.8, 0.9, 1234
+L2_BYTES = 126 * 2 ** 20
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic packed weights, generated on the device (bench input synthesis, not the product path)
+# ---------------------------------------------------------------------------------------------
+def synth_q8_0(rows: int, K: int, seed: int, device) -> torch.Tensor:
+    """Seeded N(0, 0.02) weights quantised to q8_0 blocks {f16 d; i8 q[32]} (d = amax/127)."""
+    g = torch.Generator(device=device); g.manual_seed(seed)
+    out = torch.empty((rows, K // 32, 34), dtype=torch.uint8, device=device)
+    step = 8192
+    for r0 in range(0, rows, step):
+        r1 = min(rows, r0 + step)
+        W = torch.randn((r1 - r0, K // 32, 32), generator=g, device=device) * 0.02
+        d = (W.abs().amax(-1) / 127.0).to(torch.float16)
+        ds = d.float().clamp_min(1e-30)
+        q = torch.clamp(torch.round(W / ds[..., None]), -127, 127).to(torch.int8)
+        out[r0:r1, :, 0:2] = d.view(torch.uint8).view(r1 - r0, K // 32, 2)
+        out[r0:r1, :, 2:] = q.view(torch.uint8)
+    return out
+
+
+def synth_random_blocks(fmt: str, rows: int, K: int, seed: int, device) -> torch.Tensor:
+    """Valid packed blocks with uniformly random codes and scale fields drawn so that weights are
+    O(0.02): throughput does not depend on the values."""
+    bk, bb = {"q4_0": (32, 18), "q8_0": (32, 34), "q6_K": (256, 210), "mxfp8": (32, 33),
+              "nvfp4": (16, 9), "mxfp4": (32, 17)}[fmt]
+    g = torch.Generator(device=device); g.manual_seed(seed)
+    nb = K // bk
+    out = torch.randint(0, 256, (rows, nb, bb), dtype=torch.uint8, device=device, generator=g)
+    if fmt in ("q4_0", "q8_0", "q6_K"):
+        mag = {"q4_0": 0.006, "q8_0": 0.0004, "q6_K": 0.00002}[fmt]
+        d = (torch.randn((rows, nb), device=device, generator=g) * mag).to(torch.float16)
+        lo = 0 if fmt != "q6_K" else 208
+        out[:, :, lo:lo + 2] = d.view(torch.uint8).view(rows, nb, 2)
+    elif fmt in ("mxfp8", "mxfp4"):
+        out[:, :, 0] = torch.randint(112, 122, (rows, nb), dtype=torch.uint8, device=device, generator=g)
+    else:
+        out[:, :, 0] = torch.randint(0x10, 0x30, (rows, nb), dtype=torch.uint8, device=device, generator=g)
+    return out
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline: the reference's composition (dequantise -> fp32 torch-CPU matmul -> sampler)
+# ---------------------------------------------------------------------------------------------
+def cpu_composition(steps: int, warmup: int, sample_rows: int = 16384):
+    """Times the composition on a bounded vocabulary slice with the fp32 weights resident (the
+    reference's own baseline style) and scales to the full vocabulary.  Returns tokens/s."""
+    from oracle import qx_oracle as O
+    rng = np.random.default_rng(SEED)
+    W = (0.02 * rng.standard_normal((sample_rows, K_HID))).astype(np.float32)
+    Wdq = torch.from_numpy(O.dequantize(FMT, O.synth_pack(FMT, W)))
+    h = torch.from_numpy(rng.standard_normal((T_ROWS, K_HID)).astype(np.float32)).bfloat16()
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        logits = (h.float() @ Wdq.T).numpy()
+        O.lm_head_sample_from_logits(logits, 3, k=TOPK, temperature=TEMP, seed=SEED, top_p=TOP_P)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    per_step_full = float(np.mean(times)) * (V_FULL / sample_rows)
+    return T_ROWS / per_step_full, per_step_full, torch.get_num_threads(), \
+        f"{sample_rows} of {V_FULL} vocabulary rows, {T_ROWS} hidden rows, fp32 weights resident, scaled by rows"
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    tps, per_step, cores, sample = cpu_composition(steps, warmup)
+    line = {
+        "impl": "reference", "metric": "lm_head_sample tokens/s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's kernels are Metal-only; this arm times its dequantise -> torch-CPU matmul -> "
+                "sampler composition as restated in oracle/ on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {"workload": f"lm_head_sample {FMT} V={V_FULL} K={K_HID} T={T_ROWS} mode={MODE} top_p={TOP_P} "
+                        f"k'={TOPK} temperature={TEMP}",
+            "parallelism": f"vocab-parallel x{n_gpus}" if n_gpus > 1 else "single GPU",
+            "l2": "weight shard copies rotated so that consecutive steps touch > 2x L2 of distinct bytes"}
+
+
+# ---------------------------------------------------------------------------------------------
+def gemv_sweep(device, peak_gbs: float):
+    """Packed GEMV bandwidth of the batch-1..8 projection configurations (algorithmic bytes / time)."""
+    from quixicore_metal_b200 import tk
+    res = []
+    cases = [("decode_linear_epilogue", "q4_0", 1, 4096, 4096),
+             ("decode_swiglu+down", "q6_K", 1, 4096, 14336),
+             ("decode_swiglu+down", "q6_K", 8, 4096, 14336),
+             ("decode_linear_epilogue", "nvfp4", 1, 8192, 28672),
+             ("decode_linear_epilogue", "mxfp4", 1, 8192, 28672),
+             ("decode_linear_epilogue", "nvfp4", 8, 8192, 28672)]
+    for op, fmt, M, K, N in cases:
+        x = torch.randn((M, K), device=device).bfloat16()
+        if op == "decode_swiglu+down":
+            wbytes = 0
+            sets = []
+            copies = 3
+            for c in range(copies):
+                g = synth_random_blocks(fmt, N, K, 10 + c, device)
+                u = synth_random_blocks(fmt, N, K, 20 + c, device)
+                d = synth_random_blocks(fmt, K, N, 30 + c, device)
+                sets.append((g, u, d))
+            wbytes = sum(t.numel() for t in sets[0])
+            res_in = torch.randn((M, K), device=device).bfloat16()
+
+            def step(i):
+                g, u, d = sets[i % copies]
+                mid = tk.decode_swiglu(x, g, u, format=fmt)
+                return tk.decode_linear_epilogue(mid, d, None, res_in, format=fmt)
+            alg = wbytes + M * (2 * K + 2 * 2 * N + 2 * K + 2 * K)
+        else:
+            one = N * (K // {"q4_0": 32, "nvfp4": 16, "mxfp4": 32}[fmt]) * {"q4_0": 18, "nvfp4": 9, "mxfp4": 17}[fmt]
+            copies = max(2, -(-2 * L2_BYTES // one))
+            ws = [synth_random_blocks(fmt, N, K, 40 + c, device) for c in range(min(copies, 32))]
+            copies = len(ws)
+            bias = torch.randn(N, device=device).bfloat16() * 0.01
+
+            def step(i):
+                return tk.decode_linear_epilogue(x, ws[i % copies], bias, None, format=fmt)
+            alg = one + 2 * M * K + 2 * N + 2 * M * N
+        for i in range(5):
+            step(i)
+        torch.cuda.synchronize()
+        iters = 40
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            step(i)
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        gbs = alg / (ms * 1e-3) / 1e9
+        res.append({"op": op, "format": fmt, "M": M, "K": K, "N": N, "ms": round(ms, 5),
+                    "algorithmic_bytes": int(alg), "gbs": round(gbs, 1),
+                    "frac_of_measured_peak": round(gbs / peak_gbs, 4), "frac_of_8TBs": round(gbs / 8000.0, 4)})
+        del x
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the secondary GEMV sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+    from quixicore_metal_b200 import _lib, parallel, tk
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    peak_gbs, peak_kind = measured_peaks()
+
+    # ---- inputs: this rank's vocabulary shard, enough rotating copies to defeat L2 ----
+    begin, end = parallel.vocab_shard_bounds(V_FULL, world)[rank]
+    rows = end - begin
+    shard_bytes = rows * (K_HID // 32) * 34
+    copies = max(1, -(-2 * L2_BYTES // shard_bytes)) if shard_bytes < 2 * L2_BYTES else 1
+    shards = [synth_q8_0(rows, K_HID, SEED + 1000 * c + rank, device) for c in range(copies)]
+    heads = [parallel.VocabParallelLMHead(w, V_FULL, FMT) for w in shards]
+    g = torch.Generator(device="cpu"); g.manual_seed(SEED)
+    h_host = torch.randn((T_ROWS, K_HID), generator=g).bfloat16().pin_memory()
+    h_dev = h_host.to(device)
+    ids_host = torch.empty(T_ROWS, dtype=torch.int32).pin_memory()
+
+    def step(i):
+        return heads[i % copies].sample(h_dev, MODE, k=TOPK, temperature=TEMP, seed=SEED + i, top_p=TOP_P)
+
+    def step_e2e(i):
+        hd = h_host.to(device, non_blocking=True)
+        ids = heads[i % copies].sample(hd, MODE, k=TOPK, temperature=TEMP, seed=SEED + i, top_p=TOP_P)
+        ids_host.copy_(ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return ids_host
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for i in range(args.warmup):
+        step(i); step_e2e(i)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    total_ms = timed(step, args.steps)
+    launches = _lib.launch_count() - launches0
+    e2e_ms = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- dominant kernel alone: stage 1 (one launch) on this rank's shard ----
+    mt = parallel.max_shard_tiles(V_FULL, world)
+    buf = torch.empty(T_ROWS * (2 * mt * TOPK + mt), dtype=torch.float32, device=device)
+    for i in range(3):
+        parallel.lm_head_shard_partials(h_dev, shards[i % copies], None, begin, mt, FMT, MODE, TOPK, TEMP, SEED, out=buf)
+    torch.cuda.synchronize()
+    kiters = max(10, min(args.steps, 50))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(kiters):
+        parallel.lm_head_shard_partials(h_dev, shards[i % copies], None, begin, mt, FMT, MODE, TOPK, TEMP, SEED, out=buf)
+    e1.record(); torch.cuda.synchronize()
+    k_ms = e0.elapsed_time(e1) / kiters
+    alg_bytes = shard_bytes + T_ROWS * K_HID * 2 + buf.numel() * 4
+    achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+
+    ms_per_step = total_ms / args.steps
+    value = T_ROWS / (ms_per_step * 1e-3)
+    e2e_value = T_ROWS / (e2e_ms / args.steps * 1e-3)
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier(); dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": "lm_head_sample tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T_ROWS * K_HID * 2,
+                "d2h_bytes_per_step": T_ROWS * 4},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "lm_head stage 1 (projection + tile partials)",
+                     "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                     "frac_of_8TBs": achieved / 8000.0, "peak_kind": peak_kind, "traffic": None,
+                     "kernel_ms": k_ms, "algorithmic_bytes": int(alg_bytes)},
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_sweep:
+        line["gemv"] = gemv_sweep(device, peak_gbs)
+    if world == 1 and not args.no_cpu:
+        tps, per_step, cores, sample = cpu_composition(2, 1)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

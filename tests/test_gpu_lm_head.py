@@ -209,4 +209,6 @@ def test_lm_head_error_messages():
     with pytest.raises(RuntimeError, match="top_p in"):
         tk.lm_head_sample(h, w, mode="topp", top_p=1.5, format="q8_0")
     with pytest.raises(RuntimeError, match="does not match"):
+        tk.lm_head_sample(h, w[:, :, :33], format="q8_0")
+    with pytest.raises(RuntimeError, match=r"h must be \(T, K\)"):
         tk.lm_head_sample(h, w[:, :1], format="q8_0")
