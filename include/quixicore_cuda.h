@@ -170,6 +170,26 @@ qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, 
                                    int mode, int topk, double temperature, uint32_t seed,
                                    double top_p);
 
+/* No counterpart in the reference (whose host code always allocates its partial buffers): the
+ * same operation as qx_cuda_lm_head_sample_q for callers that cannot allocate device memory at
+ * call time - code running inside a latency-critical serving loop that has handed all of its
+ * memory to a pool, a plugin host that forbids cudaMalloc after start-up, or a region that is
+ * being stream-ordered without an allocator.  The stage-1 partials go to a fixed array of
+ * QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES bytes that is part of the library image (every GPU that
+ * loads the library keeps that much memory until the process exits).  Calls whose partials need
+ * more (see qx_cuda_lm_head_workspace_bytes) fail with QX_INSUFFICIENT_WORKSPACE.  Nothing in
+ * this call allocates or frees.  The first call on each device looks the array's device address
+ * up once; make that first call before starting any stream capture.  All calls on one device
+ * share the array: two calls that overlap on the GPU (different streams) race on it, so keep
+ * them on one stream or order them with events.  Stage 1 overwrites every slot that stage 2
+ * reads, so no clearing is needed between calls. */
+#define QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES (4u << 20)
+qx_status qx_cuda_lm_head_sample_q_noalloc(void* stream, const void* h, const void* wq,
+                                           const float* bias, int32_t* ids, int64_t T, int64_t V,
+                                           int64_t K, const char* format, qx_dtype dtype, int mode,
+                                           int topk, double temperature, uint32_t seed,
+                                           double top_p);
+
 /* Vocabulary-sharded form.  A shard holds rows [vocab_offset, vocab_offset + V_local) of the full
  * matrix, vocab_offset a multiple of 256 so every 256-row tile of the reference lies in one shard.
  * Stage 1 writes this shard's candidates for every row t:

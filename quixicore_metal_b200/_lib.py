@@ -56,6 +56,8 @@ def lib() -> C.CDLL:
     L.qx_cuda_lm_head_workspace_bytes.argtypes = [i64, i64, i32, i32]
     L.qx_cuda_lm_head_sample_q.restype = Status
     L.qx_cuda_lm_head_sample_q.argtypes = [vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, cs, i32, i32, i32, f64, u32, f64]
+    L.qx_cuda_lm_head_sample_q_noalloc.restype = Status
+    L.qx_cuda_lm_head_sample_q_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, f64, u32, f64]
     L.qx_cuda_lm_head_shard_candidates.restype = i64
     L.qx_cuda_lm_head_shard_candidates.argtypes = [i32, i32, i64]
     L.qx_cuda_lm_head_shard_workspace_bytes.restype = sz
