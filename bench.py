@@ -77,6 +77,9 @@ def synth_random_blocks(fmt: str, rows: int, K: int, seed: int, device) -> torch
         out[:, :, lo:lo + 2] = d.view(torch.uint8).view(rows, nb, 2)
     elif fmt in ("mxfp8", "mxfp4"):
         out[:, :, 0] = torch.randint(112, 122, (rows, nb), dtype=torch.uint8, device=device, generator=g)
+        if fmt == "mxfp8":      # quantizers never emit the exponent-15 / mantissa-7 code
+            codes = out[:, :, 1:]
+            codes[(codes & 0x7F) == 0x7F] = 0x7E
     else:
         out[:, :, 0] = torch.randint(0x10, 0x30, (rows, nb), dtype=torch.uint8, device=device, generator=g)
     return out

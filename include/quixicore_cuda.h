@@ -224,6 +224,10 @@ qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, cons
 int qx_cuda_format_info(const char* format, int* block_k, int* block_bytes);
 /* Number of kernel launches this library has enqueued since it was loaded. */
 uint64_t qx_cuda_launch_count(void);
+/* 0 while every bounded device-side wait of this library has completed; non-zero once a kernel
+ * gave up waiting for one of its own asynchronous copies (its results are then invalid).
+ * Synchronises the device.  -1 if the flag cannot be read.  No counterpart in the reference. */
+int qx_cuda_device_error(void);
 /* Library version string, e.g. "quixicore-b200 0.1 (sm_100a)". */
 const char* qx_cuda_version(void);
 

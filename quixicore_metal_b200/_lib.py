@@ -70,6 +70,8 @@ def lib() -> C.CDLL:
     L.qx_cuda_format_info.argtypes = [cs, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.qx_cuda_launch_count.restype = C.c_uint64
     L.qx_cuda_launch_count.argtypes = []
+    L.qx_cuda_device_error.restype = i32
+    L.qx_cuda_device_error.argtypes = []
     L.qx_cuda_version.restype = cs
     L.qx_cuda_version.argtypes = []
     L.qx_cuda_dispatch.restype = Status

@@ -89,6 +89,7 @@ int qx_cuda_format_info(const char* format, int* block_k, int* block_bytes) {
 }
 uint64_t qx_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* qx_cuda_version(void) { return "quixicore-b200 0.1 (sm_100a)"; }
+int qx_cuda_device_error(void) { return read_device_error_flag(); }
 
 qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void* weight,
                                          const void* bias, const void* residual, void* y,

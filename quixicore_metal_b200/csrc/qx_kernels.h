@@ -1,6 +1,7 @@
 // Internal launch interface between the C ABI / dispatch layer and the kernel translation units.
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -20,6 +21,16 @@ struct GemvArgs {
 };
 
 void launch_gemv_generic(cudaStream_t st, const GemvArgs& a);
+// Streaming tensor-core path (bf16 activations, batch <= 16, 16-byte aligned bases).
+bool stream_path_ok(const GemvArgs& a);
+bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a);
+// Value of the device-side error flag that bounded waits raise (synchronises the device).
+int read_device_error_flag();
+// Device address of that flag on the current device (nullptr if it cannot be resolved).
+int* device_error_flag();
+// Row-scaled f16 copy of (M,K) bf16 / f16 activations in the column order `perm` of the decoders.
+void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __half* x16,
+                             float* rowscale, int M, int K, int perm);
 // Picks the kernel family for one projection call (format, dtype, batch, alignment).
 void launch_projection(cudaStream_t st, const GemvArgs& a);
 

@@ -12,14 +12,93 @@
 // normalizer; Gumbel-max with the stateless (seed, row, global id) noise stream.
 //
 // Ordering everywhere: value descending, ties to the smaller id.
+#include <cstdlib>
+
 #include "qx_formats.cuh"
 #include "qx_kernels.h"
+#include "qx_stream.cuh"
 
 namespace qx {
 
 constexpr int LMH_TILE = 256;
 constexpr int LMH_TB = 8;        // hidden rows per stage-1 CTA
 constexpr int LMH_RED_THREADS = 512;
+
+// Reduce one hidden row's 256 tile logits (shared memory) to the tile partials of its mode.
+// Executed by one warp.  nvalid <= 0 marks a padding tile: absent partials are written.
+__device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit, int nvalid, int v0,
+                                                 long long vocab_offset,
+                                                 const float* __restrict__ bias, int t, int tile,
+                                                 long long tiles_stride, int mode, int topk,
+                                                 float invtemp, uint32_t seed,
+                                                 float* __restrict__ part_val,
+                                                 int32_t* __restrict__ part_id,
+                                                 float* __restrict__ part_lse, int lane) {
+  if (mode <= 1) {
+    float best = QX_NEG_INF;
+    int bid = 0x7fffffff;
+    for (int lr = lane; lr < nvalid; lr += 32) {
+      const int gid = (int)(vocab_offset + v0 + lr);
+      float ls = logit[lr] * invtemp;
+      if (bias) ls += bias[v0 + lr];
+      if (mode == 1) ls += rng_gumbel(seed, (uint32_t)t, (uint32_t)gid);
+      if (better(ls, gid, best, bid)) { best = ls; bid = gid; }
+    }
+    warp_argmax(best, bid);
+    if (lane == 0) {
+      part_val[(size_t)t * tiles_stride + tile] = best;
+      part_id[(size_t)t * tiles_stride + tile] = bid == 0x7fffffff ? -1 : bid;
+    }
+    return;
+  }
+  // modes 2/3: tile top-k of the raw logits (+bias); mode 3 also the tempered log-sum-exp
+  float mv[8];
+  int mi[8];
+  float lmax = QX_NEG_INF, lsum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int lr = lane + 32 * j;
+    if (lr < nvalid) {
+      float ls = logit[lr];
+      if (bias) ls += bias[v0 + lr];
+      mv[j] = ls;
+      mi[j] = (int)(vocab_offset + v0 + lr);
+      const float tl = ls * invtemp;
+      if (tl > lmax) { lsum = lsum * expf(lmax - tl) + 1.0f; lmax = tl; }
+      else { lsum += expf(tl - lmax); }
+    } else {
+      mv[j] = QX_NEG_INF;
+      mi[j] = -1;
+    }
+  }
+  if (mode == 3) {
+    const float gmax = warp_max(lmax);
+    const float gsum = warp_sum(lmax == QX_NEG_INF ? 0.f : lsum * expf(lmax - gmax));
+    if (lane == 0)
+      part_lse[(size_t)t * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
+  }
+  const size_t pbase = ((size_t)t * tiles_stride + tile) * topk;
+  for (int kk = 0; kk < topk; ++kk) {
+    float best = QX_NEG_INF;
+    int bid = 0x7fffffff, slot = -1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (mi[j] >= 0 && better(mv[j], mi[j], best, bid)) { best = mv[j]; bid = mi[j]; slot = j; }
+    }
+    float gbest = best;
+    int gid = bid;
+    warp_argmax(gbest, gid);
+    const bool any = gid != 0x7fffffff;
+    if (slot >= 0 && bid == gid) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (j == slot) mi[j] = -1;
+    }
+    if (lane == 0) {
+      part_val[pbase + kk] = any ? gbest : QX_NEG_INF;
+      part_id[pbase + kk] = any ? gid : -1;
+    }
+  }
+}
 
 template <int FMT, typename T>
 __global__ void __launch_bounds__(256)
@@ -88,71 +167,214 @@ lmh_partials_kernel(const T* __restrict__ h, const uint8_t* __restrict__ wq,
 
   // ---- per-token selection: warp w handles token t0 + w ----
   if (warp >= tcount) return;
-  const int t = t0 + warp;
-  const int nvalid = min(LMH_TILE, V - v0);
-  if (mode <= 1) {
-    float best = QX_NEG_INF;
-    int bid = 0x7fffffff;
-    for (int lr = lane; lr < nvalid; lr += 32) {
-      const int gid = (int)(vocab_offset + v0 + lr);
-      float ls = logit[warp][lr] * invtemp;
-      if (bias) ls += bias[v0 + lr];
-      if (mode == 1) ls += rng_gumbel(seed, (uint32_t)t, (uint32_t)gid);
-      if (better(ls, gid, best, bid)) { best = ls; bid = gid; }
-    }
-    warp_argmax(best, bid);
-    if (lane == 0) {
-      part_val[(size_t)t * tiles_stride + tile] = best;
-      part_id[(size_t)t * tiles_stride + tile] = bid == 0x7fffffff ? -1 : bid;
-    }
-    return;
-  }
-  // modes 2/3: tile top-k of the raw logits (+bias); mode 3 also the tempered log-sum-exp
-  float mv[8];
-  int mi[8];
-  float lmax = QX_NEG_INF, lsum = 0.f;
+  lmh_select_token(logit[warp], min(LMH_TILE, V - v0), v0, vocab_offset, bias, t0 + warp, tile,
+                   tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse, lane);
+}
+
+
+// ------------------------------------------------------------------------------------------
+// Stage 1, streaming tensor-core form (bf16 / f16 hidden rows, aligned shapes): the projection
+// runs on the per-warp weight stream of qx_stream.cuh.  A CTA is 8 warps and owns one 256-row
+// vocabulary tile at a time; warp w streams rows [32w, 32w+32) of the tile over the full K
+// (two 16-row m-tiles sharing every activation fragment) for up to 64 hidden rows at once, so the
+// packed weights are read exactly once per pass.  The logits stay in the accumulator registers
+// and visit shared memory 16 hidden rows at a time for the per-tile selection.
+// ------------------------------------------------------------------------------------------
+template <int FMT> struct LmhCfg;      // columns per stage and ring depth that fit 8 warps x 32 rows
+template <> struct LmhCfg<F_Q8_0>  { static constexpr int KC = 256, STAGES = 2; };
+template <> struct LmhCfg<F_Q4_0>  { static constexpr int KC = 256, STAGES = 4; };
+template <> struct LmhCfg<F_NVFP4> { static constexpr int KC = 256, STAGES = 4; };
+template <> struct LmhCfg<F_MXFP4> { static constexpr int KC = 512, STAGES = 2; };
+template <> struct LmhCfg<F_MXFP8> { static constexpr int KC = 128, STAGES = 2; };
+
+constexpr int LMH_LOGIT_PITCH = 257;
+constexpr int LMH_TOK_CHUNK = 16;
+
+template <int FMT, int NT>
+__global__ void __launch_bounds__(256, 1)
+lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rowscale,
+                  const uint8_t* __restrict__ wq, const float* __restrict__ bias,
+                  float* __restrict__ part_val, int32_t* __restrict__ part_id,
+                  float* __restrict__ part_lse, int T_pass, int t_base, int V, int K,
+                  long long vocab_offset, long long tiles_stride, int mode, int topk, float invtemp,
+                  uint32_t seed, int* __restrict__ err_flag) {
+  using F = StreamFmt<FMT>;
+  using C = LmhCfg<FMT>;
+  using WS = WarpStream<FMT, C::KC, 32, C::STAGES>;
+  using GP = GroupProc<FMT>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  uint8_t* ring = smem_raw + (size_t)warp * WS::WARP_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)8 * WS::WARP_BYTES) + warp * C::STAGES;
+  float* logit = reinterpret_cast<float*>(smem_raw + (size_t)8 * WS::WARP_BYTES + (size_t)8 * C::STAGES * 8);
+
+  const size_t row_bytes = (size_t)(K / F::BK) * F::BB;
+  WS ws;
+  ws.init(smem_u32(ring), smem_u32(bars), wq, wq + 16 * row_bytes, V, K, lane, err_flag);
+  ws.N1 = V - 16;                                  // the upper 16 rows come from the same matrix
+
+  const int real_tiles = (V + LMH_TILE - 1) / LMH_TILE;
+  const int my_tiles = (int)blockIdx.x < real_tiles ? (real_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int nch = ws.nch;
+  const int steps = my_tiles * nch;
+
+  const __half* xr[NT];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int lr = lane + 32 * j;
-    if (lr < nvalid) {
-      float ls = logit[warp][lr];
-      if (bias) ls += bias[v0 + lr];
-      mv[j] = ls;
-      mi[j] = (int)(vocab_offset + v0 + lr);
-      const float tl = ls * invtemp;
-      if (tl > lmax) { lsum = lsum * expf(lmax - tl) + 1.0f; lmax = tl; }
-      else { lsum += expf(tl - lmax); }
-    } else {
-      mv[j] = QX_NEG_INF;
-      mi[j] = -1;
+  for (int nt = 0; nt < NT; ++nt) {
+    const int m = nt * 8 + g;
+    xr[nt] = m < T_pass ? x16 + (size_t)(t_base + m) * K : nullptr;
+  }
+  auto step_row0 = [&](int i) { return ((int)blockIdx.x + (i / nch) * (int)gridDim.x) * LMH_TILE + warp * 32; };
+
+#pragma unroll
+  for (int p = 0; p < C::STAGES - 1; ++p)
+    if (p < steps) ws.issue(p, step_row0(p), p % nch);
+
+  float acc[2][NT][4];
+  for (int j = 0; j < my_tiles; ++j) {
+    const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+    const int row0 = tile * LMH_TILE + warp * 32;
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int b = 0; b < NT; ++b)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+
+    for (int c = 0; c < nch; ++c) {
+      const int i = j * nch + c;
+      const int stage = i % C::STAGES;
+      const int nxt = i + C::STAGES - 1;
+      if (nxt < steps) ws.issue(nxt % C::STAGES, step_row0(nxt), nxt % nch);
+      const bool ready = ws.wait(stage, (uint32_t)((i / C::STAGES) & 1));
+      const int col_base = c * C::KC;
+      const int ngroups = ready ? min(C::KC, K - col_base) / F::GROUP : 0;
+      uint32_t s[4];
+      s[0] = ws.slot_addr(stage, g, row0, c);
+      s[1] = ws.slot_addr(stage, g + 8, row0, c);
+      s[2] = ws.slot_addr(stage, 16 + g, row0, c);
+      s[3] = ws.slot_addr(stage, 24 + g, row0, c);
+      constexpr uint32_t GROUP_BYTES = F::GROUP / F::BK * F::BB;
+      constexpr bool PRE = NT <= 2;                 // prefetch activations one group ahead
+      typename GP::template BFrag<NT> bcur, bnext;
+      if (PRE && ngroups > 0) GP::template load_b<NT>(xr, col_base, t, bcur);
+      for (int gi = 0; gi < ngroups; ++gi) {
+        if (PRE && gi + 1 < ngroups) GP::template load_b<NT>(xr, col_base + (gi + 1) * F::GROUP, t, bnext);
+        GP::template run<2, NT, PRE>(s, t, bcur, xr, col_base + gi * F::GROUP, acc);
+        if (PRE) bcur = bnext;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s[r] += GROUP_BYTES;
+      }
+      __syncwarp();
+    }
+
+    // ---- selection, 16 hidden rows (two n-tiles) at a time ----
+    const int v0 = tile * LMH_TILE;
+    const int nvalid = min(LMH_TILE, V - v0);
+#pragma unroll
+    for (int tc = 0; tc < (NT + 1) / 2; ++tc) {
+      __syncthreads();                              // previous chunk's readers are done
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int nt = 2 * tc + h;
+        if (nt < NT) {
+#pragma unroll
+          for (int set = 0; set < 2; ++set)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int ml = h * 8 + 2 * t + (e & 1);
+              const int m = nt * 8 + 2 * t + (e & 1);
+              const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
+              logit[ml * LMH_LOGIT_PITCH + warp * 32 + set * 16 + g + (e >> 1) * 8] = acc[set][nt][e] * rs;
+            }
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {                 // warp w reduces chunk rows w and w + 8
+        const int ml = warp + 8 * q;
+        const int m = tc * LMH_TOK_CHUNK + ml;
+        if (m < T_pass)
+          lmh_select_token(logit + ml * LMH_LOGIT_PITCH, nvalid, v0, vocab_offset, bias, t_base + m,
+                           tile, tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse,
+                           lane);
+      }
     }
   }
-  if (mode == 3) {
-    const float gmax = warp_max(lmax);
-    const float gsum = warp_sum(lmax == QX_NEG_INF ? 0.f : lsum * expf(lmax - gmax));
-    if (lane == 0)
-      part_lse[(size_t)t * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
+
+  // padding tiles of a short shard carry absent partials
+  for (long long tile = real_tiles + blockIdx.x; tile < tiles_stride; tile += gridDim.x) {
+    for (int m = warp; m < T_pass; m += 8)
+      lmh_select_token(logit, 0, 0, vocab_offset, nullptr, t_base + m, (int)tile, tiles_stride, mode,
+                       topk, invtemp, seed, part_val, part_id, part_lse, lane);
   }
-  const size_t pbase = ((size_t)t * tiles_stride + tile) * topk;
-  for (int kk = 0; kk < topk; ++kk) {
-    float best = QX_NEG_INF;
-    int bid = 0x7fffffff, slot = -1;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (mi[j] >= 0 && better(mv[j], mi[j], best, bid)) { best = mv[j]; bid = mi[j]; slot = j; }
-    }
-    float gbest = best;
-    int gid = bid;
-    warp_argmax(gbest, gid);
-    const bool any = gid != 0x7fffffff;
-    if (slot >= 0 && bid == gid) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) if (j == slot) mi[j] = -1;
-    }
-    if (lane == 0) {
-      part_val[pbase + kk] = any ? gbest : QX_NEG_INF;
-      part_id[pbase + kk] = any ? gid : -1;
-    }
+}
+
+template <int FMT>
+static bool lmh_stream_ok(const LmHeadArgs& a) {
+  using F = StreamFmt<FMT>;
+  const size_t row_bytes = (size_t)(a.K / F::BK) * F::BB;
+  return (a.dtype == QX_DTYPE_BF16 || a.dtype == QX_DTYPE_F16) && a.K % LmhCfg<FMT>::KC == 0 &&
+         row_bytes % 16 == 0 && ((uintptr_t)a.wq & 15) == 0 && a.V >= 32;
+}
+
+template <int FMT, int NT>
+static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __half* x16,
+                                 const float* rowscale, float* pv, int32_t* pi, float* pl,
+                                 int64_t tiles_stride, int t_base, int t_pass, int* err) {
+  using C = LmhCfg<FMT>;
+  using WS = WarpStream<FMT, C::KC, 32, C::STAGES>;
+  const size_t smem = (size_t)8 * WS::WARP_BYTES + (size_t)8 * C::STAGES * 8 +
+                      (size_t)LMH_TOK_CHUNK * LMH_LOGIT_PITCH * 4;
+  cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
+  const int blocks = real_tiles < sm_count() ? real_tiles : sm_count();
+  lmh_stream_kernel<FMT, NT><<<blocks, 256, smem, st>>>(
+      x16, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, t_pass, t_base, (int)a.V, (int)a.K,
+      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
+  note_launch();
+}
+
+template <int FMT>
+static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
+                              int64_t tiles_stride) {
+  if (!lmh_stream_ok<FMT>(a)) return false;
+  int* err = device_error_flag();
+  if (!err) return false;
+  const size_t x16_bytes = ((size_t)a.T * a.K * 2 + 255) & ~(size_t)255;
+  void* scratch = nullptr;
+  if (cudaMallocAsync(&scratch, x16_bytes + (size_t)a.T * 4, st) != cudaSuccess) { cudaGetLastError(); return false; }
+  __half* x16 = (__half*)scratch;
+  float* rowscale = (float*)((char*)scratch + x16_bytes);
+  launch_prep_activations(st, a.h, a.dtype, x16, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM);
+  note_launch();
+  for (int t_base = 0; t_base < a.T; t_base += 64) {
+    const int t_pass = (int)((a.T - t_base) < 64 ? (a.T - t_base) : 64);
+    if (t_pass <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
+    else if (t_pass <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
+    else if (t_pass <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
+    else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
+  }
+  cudaFreeAsync(scratch, st);
+  return true;
+}
+
+static bool launch_lmh_stream_any(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi,
+                                  float* pl, int64_t ts) {
+  static const bool force_generic = [] {
+    const char* e = getenv("QX_FORCE_GENERIC");
+    return e && e[0] == '1';
+  }();
+  if (force_generic) return false;
+  switch (a.format) {
+    case F_Q8_0: return launch_lmh_stream<F_Q8_0>(st, a, pv, pi, pl, ts);
+    case F_Q4_0: return launch_lmh_stream<F_Q4_0>(st, a, pv, pi, pl, ts);
+    case F_NVFP4: return launch_lmh_stream<F_NVFP4>(st, a, pv, pi, pl, ts);
+    case F_MXFP4: return launch_lmh_stream<F_MXFP4>(st, a, pv, pi, pl, ts);
+    case F_MXFP8: return launch_lmh_stream<F_MXFP8>(st, a, pv, pi, pl, ts);
+    default: return false;    // q6_K heads take the generic kernel
   }
 }
 
@@ -415,6 +637,7 @@ static void launch_partials_f(cudaStream_t st, const LmHeadArgs& a, float* pv, i
 
 void launch_lm_head_partials(cudaStream_t st, const LmHeadArgs& a, float* part_val,
                              int32_t* part_id, float* part_lse, int64_t tiles_stride) {
+  if (launch_lmh_stream_any(st, a, part_val, part_id, part_lse, tiles_stride)) return;
   if (a.dtype == QX_DTYPE_F32) launch_partials_f<float>(st, a, part_val, part_id, part_lse, tiles_stride);
   else if (a.dtype == QX_DTYPE_F16) launch_partials_f<__half>(st, a, part_val, part_id, part_lse, tiles_stride);
   else launch_partials_f<__nv_bfloat16>(st, a, part_val, part_id, part_lse, tiles_stride);

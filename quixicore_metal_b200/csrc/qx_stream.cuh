@@ -1,0 +1,593 @@
+// Streaming small-batch core: packed weight rows -> shared memory by bulk async copies,
+// in-register dequantisation straight into mma.sync A fragments, fp32 block-scaled accumulation.
+//
+// Why this shape.  For batch <= 16 the projection is bound by the HBM stream of packed weights
+// (0.53 - 1.06 bytes per weight).  At 6.5 TB/s an SM has to retire ~40 four-bit weights per clock,
+// i.e. at most ~3 issue slots per weight: fp32 FMAs plus scalar conversions do not fit, so
+//   * the multiply-accumulate runs on the tensor cores (m16n8k16 f16, the batch is the n = 8
+//     dimension, 16 weight rows are the m dimension) with A built in registers - the dequantised
+//     weights never touch shared memory;
+//   * integer / logic / half2 instructions issue at half the fp32 rate on this part, so codes are
+//     turned into f16 with the cheapest exact sequence per format (magic-number OR for integers,
+//     the hardware e2m1 / e4m3 converters for the float codes);
+//   * every scale unit (16 or 32 columns sharing one scale) is multiplied as exact small numbers
+//     and the fp16 / e8m0 scale is applied to the fp32 partial sum afterwards (nvfp4 folds its e4m3
+//     scale into the f16 weight, which is exact), so the result equals fp32 dequantise-then-dot up
+//     to summation order;
+//   * activations are converted once per call to f16, each row scaled by a power of two so that
+//     its largest magnitude sits near 2^14 (exact for every element within 2^28 of the row maximum,
+//     i.e. far below the resolution of the fp32 accumulator for the rest), stored in the column
+//     order the decoders produce; the epilogue multiplies the row scale back;
+//   * raw rows are fetched with cp.async.bulk into a per-warp ring of stages (mbarrier completion),
+//     which keeps tens of KB in flight per SM with a handful of instructions.
+// The k-order inside a scale unit is free (a dot product is order-blind up to rounding), so each
+// thread takes the bytes that are cheapest to unpack and loads the matching activation columns.
+//
+// Every mbarrier wait is bounded; on expiry the warp raises the device error flag and stops computing.
+#pragma once
+
+#include "qx_common.cuh"
+
+namespace qx {
+
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait: returns false (and records the failure) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_flag) {
+  for (int i = 0; i < (1 << 22); ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicExch(err_flag, 1);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Shared-memory loads by 32-bit shared-window address.  Deliberately not volatile: the compiler
+// may hoist and interleave them; the mbarrier wait / __syncwarp carry the memory clobbers that
+// keep them inside their pipeline stage.
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+// 32 bits starting at an arbitrary shared-memory byte address (reads the two enclosing words)
+__device__ __forceinline__ uint32_t lds32_any(uint32_t addr) {
+  const uint32_t base = addr & ~3u;
+  return __funnelshift_r(lds32(base), lds32(base + 4), (addr & 3u) * 8u);
+}
+// 32 bits at a 2-byte aligned address
+__device__ __forceinline__ uint32_t lds32_a2(uint32_t addr) {
+  return lds16(addr) | (lds16(addr + 2) << 16);
+}
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
+  uint32_t r; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
+}
+__device__ __forceinline__ uint32_t h2mul(uint32_t a, uint32_t b) {
+  uint32_t r; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
+}
+__device__ __forceinline__ uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c)); return r;
+}
+// byte `i` of w holds two e2m1 codes: low nibble -> low half, high nibble -> high half
+template <int I>
+__device__ __forceinline__ uint32_t cvt_e2m1x2(uint32_t w) {
+  uint32_t r;
+  asm("{ .reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b%2; }"
+      : "=r"(r) : "r"(w), "n"(I));
+  return r;
+}
+// half `I` (0/1) of w holds two e4m3 codes -> f16 pair (hardware rule: 0x7F / 0xFF decode to NaN)
+template <int I>
+__device__ __forceinline__ uint32_t cvt_e4m3x2(uint32_t w) {
+  uint32_t r;
+  asm("{ .reg .b16 h0, h1;\n\t"
+      "mov.b32 {h0, h1}, %1;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, h%2; }"
+      : "=r"(r) : "r"(w), "n"(I));
+  return r;
+}
+__device__ __forceinline__ float f16lo_to_f32(uint32_t h) {
+  return __half2float(__ushort_as_half((unsigned short)(h & 0xFFFFu)));
+}
+
+// ---- per-format geometry ----------------------------------------------------------------------
+// UNIT  = columns that share one scale and are multiplied before the scale is applied;
+// GROUP = columns one decode step covers (the byte-alignment pattern of the blocks repeats with
+//         this period, so every shared-memory load inside a step has a static alignment);
+// KC    = columns one pipeline stage holds per row (a multiple of GROUP whose byte size is a
+//         multiple of 16, except q6_K whose 210-byte blocks are only 4-byte periodic);
+// PERM  = column order of the prepared activations (see prep_activations_kernel).
+template <int FMT> struct StreamFmt;
+template <> struct StreamFmt<F_Q4_0>  { static constexpr int UNIT = 32, GROUP = 64,  KC = 512, BK = 32,  BB = 18,  PERM = 1; };
+template <> struct StreamFmt<F_Q8_0>  { static constexpr int UNIT = 32, GROUP = 64,  KC = 256, BK = 32,  BB = 34,  PERM = 0; };
+template <> struct StreamFmt<F_Q6_K>  { static constexpr int UNIT = 16, GROUP = 512, KC = 512, BK = 256, BB = 210, PERM = 4; };
+template <> struct StreamFmt<F_MXFP8> { static constexpr int UNIT = 32, GROUP = 128, KC = 256, BK = 32,  BB = 33,  PERM = 0; };
+template <> struct StreamFmt<F_NVFP4> { static constexpr int UNIT = 16, GROUP = 64,  KC = 512, BK = 16,  BB = 9,   PERM = 3; };
+template <> struct StreamFmt<F_MXFP4> { static constexpr int UNIT = 32, GROUP = 128, KC = 512, BK = 32,  BB = 17,  PERM = 2; };
+
+template <int FMT, int KCV>
+struct StageGeom {
+  using F = StreamFmt<FMT>;
+  static constexpr int KC = KCV;
+  static constexpr int CHUNK_BYTES = KC / F::BK * F::BB;          // payload bytes per row and stage
+  // stages whose byte size is not a multiple of 16 start at varying offsets inside a 16-byte line:
+  // leave room for that slack on both sides; then pad so that the 8 rows a warp touches in one
+  // instruction start 16 bytes apart modulo 128 (no shared-memory bank conflicts)
+  static constexpr int RAW = CHUNK_BYTES + (CHUNK_BYTES % 16 == 0 ? 0 : 32);
+  static constexpr int PITCH = ((RAW - 16 + 127) / 128) * 128 + 16;
+};
+
+// Position of column c (0 <= c < 32) of a 32-column group inside the prepared activation row.
+// PERM 0: natural.  The others put the columns a thread's decode produces next to each other so
+// that one 8/16-byte load yields its B fragments:
+//   1 (q4_0)  thread t: 4t,4t+2,4t+1,4t+3, 16+4t,16+4t+2,16+4t+1,16+4t+3
+//   2 (mxfp4) thread t: 4t,16+4t, 4t+1,16+4t+1, 4t+2,16+4t+2, 4t+3,16+4t+3
+//   3 (nvfp4) per 16:   0,8,1,9,2,10,3,11,4,12,5,13,6,14,7,15
+//   4 (q6_K)  per 4:    0,2,1,3
+__host__ __device__ inline int perm_position(int perm, int c) {
+  switch (perm) {
+    case 1: { const int hi = c >> 4, r = c & 15, t = r >> 2, i = r & 3;
+              return 8 * t + 4 * hi + ((i & 1) << 1 | (i >> 1)); }
+    case 2: { const int hi = c >> 4, r = c & 15, t = r >> 2, i = r & 3;
+              return 8 * t + 2 * i + hi; }
+    case 3: { const int blk = c >> 4, r = c & 15;
+              return 16 * blk + ((r & 7) << 1 | (r >> 3)); }
+    case 4: { const int i = c & 3;
+              return (c & ~3) | ((i & 1) << 1 | (i >> 1)); }
+    default: return c;
+  }
+}
+
+// ---- row decoders for the formats with a post-applied scale (unit = 32 columns) ------------------
+// row<J>(s, t, a, scale): s = shared address of the block of unit J (J = position inside the
+// group, which fixes the byte alignment), t = lane & 3.  a[m][0] feeds k-slots (2t, 2t+1) of MMA m,
+// a[m][1] slots (2t+8, 2t+9); the matching activation order is StreamFmt::PERM.
+template <int FMT> struct RowDec;
+
+template <> struct RowDec<F_Q8_0> {
+  // thread t owns code bytes 8t..8t+7 (columns 8t..8t+7); q + 1152 is built by OR-ing the byte
+  // (sign bit flipped) under the f16 exponent of 1024, then 1152 is subtracted: exact.
+  __device__ __forceinline__ static void word(uint32_t w, uint32_t& p01, uint32_t& p23) {
+    const uint32_t u = w ^ 0x80808080u;
+    p01 = h2sub(__byte_perm(u, 0x64646464u, 0x4140), 0x64806480u);
+    p23 = h2sub(__byte_perm(u, 0x64646464u, 0x4342), 0x64806480u);
+  }
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
+    scale = f16lo_to_f32(lds16(s));
+    uint32_t w0, w1;
+    if constexpr ((J & 1) == 0) {            // block starts 4-aligned: codes at +2 straddle words
+      const uint32_t p = s + 8 * t;
+      const uint32_t x0 = lds32(p), x1 = lds32(p + 4), x2 = lds32(p + 8);
+      w0 = __funnelshift_r(x0, x1, 16); w1 = __funnelshift_r(x1, x2, 16);
+    } else {                                 // block starts at 2 mod 4: codes are word aligned
+      const uint32_t p = s + 2 + 8 * t;
+      w0 = lds32(p); w1 = lds32(p + 4);
+    }
+    word(w0, a[0][0], a[0][1]);
+    word(w1, a[1][0], a[1][1]);
+  }
+};
+
+template <> struct RowDec<F_Q4_0> {
+  // thread t owns code bytes 4t..4t+3: low nibbles = columns 4t.., high nibbles = columns 16+4t..
+  // A nibble OR-ed under the f16 exponent of 1024 is 1024+n (bits 0-3) or 1024+16n (bits 4-7).
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
+    scale = f16lo_to_f32(lds16(s));
+    uint32_t w;
+    if constexpr ((J & 1) == 0) {
+      const uint32_t p = s + 4 * t;
+      w = __funnelshift_r(lds32(p), lds32(p + 4), 16);
+    } else {
+      w = lds32(s + 2 + 4 * t);
+    }
+    const uint32_t w8 = w >> 8;
+    a[0][0] = h2sub((w & 0x000F000Fu) | 0x64006400u, 0x64086408u);                  // bytes 0,2 low
+    a[1][0] = h2fma((w & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);     // bytes 0,2 high
+    a[0][1] = h2sub((w8 & 0x000F000Fu) | 0x64006400u, 0x64086408u);                 // bytes 1,3 low
+    a[1][1] = h2fma((w8 & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);    // bytes 1,3 high
+  }
+};
+
+__device__ __forceinline__ float e8m0_scale(uint32_t e) {
+  return __uint_as_float(e == 0 ? 0x00400000u : (e << 23));
+}
+
+template <> struct RowDec<F_MXFP4> {
+  // thread t owns code bytes 4t..4t+3; byte i converts to the pair (column 4t+i, column 16+4t+i)
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
+    scale = e8m0_scale(lds8(s));
+    constexpr int SH = (J + 1) & 3;          // (17*J + 1) mod 4
+    const uint32_t p = s + 1 + 4 * t - SH;
+    uint32_t w;
+    if constexpr (SH == 0) w = lds32(p);
+    else w = __funnelshift_r(lds32(p), lds32(p + 4), 8 * SH);
+    a[0][0] = cvt_e2m1x2<0>(w); a[0][1] = cvt_e2m1x2<1>(w);
+    a[1][0] = cvt_e2m1x2<2>(w); a[1][1] = cvt_e2m1x2<3>(w);
+  }
+};
+
+// e4m3 pair with this contract's rule for the codes 0x7F / 0xFF (+-480, no NaN): bits moved into
+// the f16 exponent / mantissa decode to value * 2^-8 (subnormals included), times 2^8 is exact.
+__device__ __forceinline__ uint32_t e4m3x2_exact(uint32_t h) {          // bytes at [7:0] and [23:16]
+  const uint32_t bits = ((h & 0x007F007Fu) << 7) | ((h & 0x00800080u) << 8);
+  return h2mul(bits, 0x5C005C00u);
+}
+template <> struct RowDec<F_MXFP8> {
+  __device__ __forceinline__ static void word(uint32_t w, uint32_t& p01, uint32_t& p23) {
+    const uint32_t t7 = w & 0x7F7F7F7Fu;
+    if (((t7 + 0x01010101u) & 0x80808080u) != 0u) {    // some byte is 0x7F: the hardware would say NaN
+      p01 = e4m3x2_exact(__byte_perm(w, 0u, 0x4140));
+      p23 = e4m3x2_exact(__byte_perm(w, 0u, 0x4342));
+    } else {
+      p01 = cvt_e4m3x2<0>(w);
+      p23 = cvt_e4m3x2<1>(w);
+    }
+  }
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
+    scale = e8m0_scale(lds8(s));
+    constexpr int SH = (J + 1) & 3;          // (33*J + 1) mod 4
+    const uint32_t p = s + 1 + 8 * t - SH;
+    uint32_t w0, w1;
+    if constexpr (SH == 0) { w0 = lds32(p); w1 = lds32(p + 4); }
+    else {
+      const uint32_t x0 = lds32(p), x1 = lds32(p + 4), x2 = lds32(p + 8);
+      w0 = __funnelshift_r(x0, x1, 8 * SH); w1 = __funnelshift_r(x1, x2, 8 * SH);
+    }
+    word(w0, a[0][0], a[0][1]);
+    word(w1, a[1][0], a[1][1]);
+  }
+};
+
+// One 32-column unit of the post-scaled formats: decode 2 rows per set, one MMA pair per n-tile,
+// then acc += scale * partial.  b[nt] = the thread's 8 prepared activations of this unit.
+template <int FMT, int J, int NSETS, int NT>
+__device__ __forceinline__ void unit32(const uint32_t (&s)[2 * NSETS], uint32_t boff, int t,
+                                       const uint4 (&b)[NT], float (&acc)[NSETS][NT][4]) {
+  uint32_t a[2 * NSETS][2][2];
+  float sc[2 * NSETS];
+#pragma unroll
+  for (int r = 0; r < 2 * NSETS; ++r) RowDec<FMT>::template row<J>(s[r] + boff, t, a[r], sc[r]);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int set = 0; set < NSETS; ++set) {
+      float p[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_f16(p, a[2 * set][0][0], a[2 * set + 1][0][0], a[2 * set][0][1], a[2 * set + 1][0][1], b[nt].x, b[nt].y);
+      mma_f16(p, a[2 * set][1][0], a[2 * set + 1][1][0], a[2 * set][1][1], a[2 * set + 1][1][1], b[nt].z, b[nt].w);
+      acc[set][nt][0] = fmaf(sc[2 * set], p[0], acc[set][nt][0]);
+      acc[set][nt][1] = fmaf(sc[2 * set], p[1], acc[set][nt][1]);
+      acc[set][nt][2] = fmaf(sc[2 * set + 1], p[2], acc[set][nt][2]);
+      acc[set][nt][3] = fmaf(sc[2 * set + 1], p[3], acc[set][nt][3]);
+    }
+  }
+}
+
+__device__ __forceinline__ uint4 ldg_or_zero(const __half* row, int off) {
+  return row ? __ldg(reinterpret_cast<const uint4*>(row + off)) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// ---- group processors: one GROUP of columns for this thread's rows ---------------------------------
+// s[r]: shared address of column 0 of the group in row slot r (r = 0,1: rows g, g+8 of the gate /
+// only matrix; r = 2,3: the same rows of the up matrix).  The thread's prepared activations of the
+// group are fetched by load_b() one group ahead of run(), which hides the L1 latency.
+template <int FMT> struct GroupProc {
+  using F = StreamFmt<FMT>;
+  static constexpr int UNITS = F::GROUP / 32;
+  template <int NT> struct BFrag { uint4 v[UNITS][NT]; };
+  template <int NT>
+  __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int t,
+                                                BFrag<NT>& b) {
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) b.v[u][nt] = ldg_or_zero(xr[nt], col + 32 * u + 8 * t);
+  }
+  // PRE: the fragments were fetched one group ahead into `b` (small batches); otherwise they are
+  // loaded unit by unit from xr / col (large batches, where a whole group would not fit registers).
+  template <int NSETS, int NT, bool PRE, int J>
+  __device__ __forceinline__ static void one(const uint32_t (&s)[2 * NSETS], int t, const BFrag<NT>& b,
+                                             const __half* const (&xr)[NT], int col,
+                                             float (&acc)[NSETS][NT][4]) {
+    if constexpr (PRE) {
+      unit32<FMT, J, NSETS, NT>(s, (uint32_t)(J * F::BB), t, b.v[J], acc);
+    } else {
+      uint4 bb[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) bb[nt] = ldg_or_zero(xr[nt], col + 32 * J + 8 * t);
+      unit32<FMT, J, NSETS, NT>(s, (uint32_t)(J * F::BB), t, bb, acc);
+    }
+  }
+  template <int NSETS, int NT, bool PRE>
+  __device__ __forceinline__ static void run(const uint32_t (&s)[2 * NSETS], int t,
+                                             const BFrag<NT>& b, const __half* const (&xr)[NT],
+                                             int col, float (&acc)[NSETS][NT][4]) {
+    one<NSETS, NT, PRE, 0>(s, t, b, xr, col, acc);
+    if constexpr (UNITS > 1) one<NSETS, NT, PRE, 1>(s, t, b, xr, col, acc);
+    if constexpr (UNITS > 2) one<NSETS, NT, PRE, 2>(s, t, b, xr, col, acc);
+    if constexpr (UNITS > 3) one<NSETS, NT, PRE, 3>(s, t, b, xr, col, acc);
+  }
+};
+
+// nvfp4: a group is four 16-column blocks; thread t owns block t of the group outright (9 bytes),
+// folds the e4m3 scale into the f16 weights (exact: 4 x 2 significant bits) and feeds its block's
+// byte pair (2m, 2m+1) to MMA m; the MMAs accumulate straight into acc.
+template <> struct GroupProc<F_NVFP4> {
+  using F = StreamFmt<F_NVFP4>;
+  __device__ __forceinline__ static void block(uint32_t s, int t, uint32_t (&a)[4][2]) {
+    const uint32_t p = s + (uint32_t)(9 * t & ~3);
+    const uint32_t sh = 8u * (uint32_t)t;                 // (9t mod 4) bytes
+    const uint32_t w0 = lds32(p), w1 = lds32(p + 4), w2 = lds32(p + 8);
+    const uint32_t x0 = __funnelshift_r(w0, w1, sh), x1 = __funnelshift_r(w1, w2, sh), x2 = w2 >> sh;
+    uint32_t s2 = cvt_e4m3x2<0>(__byte_perm(x0, 0u, 0x0000));
+    if ((x0 & 0x7Fu) == 0x7Fu) s2 = (x0 & 0x80u) ? 0xDF80DF80u : 0x5F805F80u;   // +-480, not NaN
+    a[0][0] = h2mul(cvt_e2m1x2<1>(x0), s2); a[0][1] = h2mul(cvt_e2m1x2<2>(x0), s2);
+    a[1][0] = h2mul(cvt_e2m1x2<3>(x0), s2); a[1][1] = h2mul(cvt_e2m1x2<0>(x1), s2);
+    a[2][0] = h2mul(cvt_e2m1x2<1>(x1), s2); a[2][1] = h2mul(cvt_e2m1x2<2>(x1), s2);
+    a[3][0] = h2mul(cvt_e2m1x2<3>(x1), s2); a[3][1] = h2mul(cvt_e2m1x2<0>(x2), s2);
+  }
+  template <int NT> struct BFrag { uint4 v[2][NT]; };
+  template <int NT>
+  __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int t,
+                                                BFrag<NT>& b) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      b.v[0][nt] = ldg_or_zero(xr[nt], col + 16 * t);
+      b.v[1][nt] = ldg_or_zero(xr[nt], col + 16 * t + 8);
+    }
+  }
+  template <int NSETS, int NT, bool PRE>
+  __device__ __forceinline__ static void run(const uint32_t (&s)[2 * NSETS], int t,
+                                             const BFrag<NT>& b, const __half* const (&xr)[NT],
+                                             int col, float (&acc)[NSETS][NT][4]) {
+    uint32_t a[2 * NSETS][4][2];
+#pragma unroll
+    for (int r = 0; r < 2 * NSETS; ++r) block(s[r], t, a[r]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      uint4 b0, b1;
+      if constexpr (PRE) { b0 = b.v[0][nt]; b1 = b.v[1][nt]; }
+      else { b0 = ldg_or_zero(xr[nt], col + 16 * t); b1 = ldg_or_zero(xr[nt], col + 16 * t + 8); }
+#pragma unroll
+      for (int set = 0; set < NSETS; ++set) {
+        mma_f16(acc[set][nt], a[2 * set][0][0], a[2 * set + 1][0][0], a[2 * set][0][1], a[2 * set + 1][0][1], b0.x, b0.y);
+        mma_f16(acc[set][nt], a[2 * set][1][0], a[2 * set + 1][1][0], a[2 * set][1][1], a[2 * set + 1][1][1], b0.z, b0.w);
+        mma_f16(acc[set][nt], a[2 * set][2][0], a[2 * set + 1][2][0], a[2 * set][2][1], a[2 * set + 1][2][1], b1.x, b1.y);
+        mma_f16(acc[set][nt], a[2 * set][3][0], a[2 * set + 1][3][0], a[2 * set][3][1], a[2 * set + 1][3][1], b1.z, b1.w);
+      }
+    }
+  }
+};
+
+// q6_K: a group is two 256-column super-blocks (420 bytes: the first starts 4-byte aligned, the
+// second at 2 mod 4).  Thread t owns columns 16*sub + 4t .. +3 of every 16-column sub-block: a ql
+// word serves two sub-blocks (low / high nibbles), a qh word four (2 bits each).  6-bit codes are
+// OR-ed under the f16 exponent of 1024 as 1024+c or 1024+16c; sub-scale * d is applied in fp32.
+template <> struct GroupProc<F_Q6_K> {
+  using F = StreamFmt<F_Q6_K>;
+  template <int ODD>
+  __device__ __forceinline__ static uint32_t ldw(uint32_t p) {    // p is 4-aligned iff !ODD
+    if constexpr (ODD) return __funnelshift_r(lds32(p - 2), lds32(p + 2), 16);
+    else return lds32(p);
+  }
+  // codes of one sub-block for one row: Q = ql word, H = qh word; SHL moves this sub-block's two
+  // high bits to bit 4 (low-nibble groups) or bit 8 (high-nibble groups) of each byte lane.  Bytes
+  // 1 and 3 are shifted down before the left shift so that byte 3 loses nothing.
+  template <bool HIGH, int SHL>
+  __device__ __forceinline__ static void pair(uint32_t Q, uint32_t H, uint32_t& a0, uint32_t& a1) {
+    const uint32_t H0 = H << SHL, H1 = (H >> 8) << SHL, Q1 = Q >> 8;
+    if constexpr (!HIGH) {
+      a0 = h2sub((H0 & 0x00300030u) | 0x64006400u | (Q & 0x000F000Fu), 0x64206420u);
+      a1 = h2sub((H1 & 0x00300030u) | 0x64006400u | (Q1 & 0x000F000Fu), 0x64206420u);
+    } else {
+      a0 = h2fma((H0 & 0x03000300u) | 0x64006400u | (Q & 0x00F000F0u), 0x2C002C00u, 0xD600D600u);
+      a1 = h2fma((H1 & 0x03000300u) | 0x64006400u | (Q1 & 0x00F000F0u), 0x2C002C00u, 0xD600D600u);
+    }
+  }
+  template <int NT> struct BFrag { const __half* xr[NT]; int col; };   // fetched inside run()
+  template <int NT>
+  __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int,
+                                                BFrag<NT>& b) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) b.xr[nt] = xr[nt];
+    b.col = col;
+  }
+  template <int ODD, int NSETS, int NT>
+  __device__ __forceinline__ static void superblock(const uint32_t (&s)[2 * NSETS], uint32_t boff,
+                                                    int t, const __half* const (&xr)[NT], int col,
+                                                    float (&acc)[NSETS][NT][4]) {
+    float d[2 * NSETS];
+#pragma unroll
+    for (int r = 0; r < 2 * NSETS; ++r) d[r] = f16lo_to_f32(lds16(s[r] + boff + 208));
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {                 // 128-column chunk
+#pragma unroll
+      for (int l = 0; l < 2; ++l) {               // which 16 of the 32 positions
+        uint32_t H[2 * NSETS], Q0[2 * NSETS], Q1[2 * NSETS], SC[2 * NSETS][2];
+        uint2 bq[4][NT];                          // activations of the four sub-blocks of this step
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+            bq[g][nt] = xr[nt] ? __ldg(reinterpret_cast<const uint2*>(xr[nt] + col + 128 * c + 32 * g + 16 * l + 4 * t))
+                               : make_uint2(0u, 0u);
+#pragma unroll
+        for (int r = 0; r < 2 * NSETS; ++r) {
+          const uint32_t base = s[r] + boff;
+          H[r] = ldw<ODD>(base + 128 + 32 * c + 16 * l + 4 * t);
+          Q0[r] = ldw<ODD>(base + 64 * c + 16 * l + 4 * t);
+          Q1[r] = ldw<ODD>(base + 64 * c + 32 + 16 * l + 4 * t);
+          SC[r][0] = ldw<ODD>(base + 192 + 8 * c);         // sub-scales of groups 0,1 (bytes l, 2+l)
+          SC[r][1] = ldw<ODD>(base + 192 + 8 * c + 4);     // groups 2,3
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {             // sub-block index sub = 8c + 2g + l
+          uint32_t a[2 * NSETS][2];
+          float sc[2 * NSETS];
+#pragma unroll
+          for (int r = 0; r < 2 * NSETS; ++r) {
+            const uint32_t Q = (g & 1) ? Q1[r] : Q0[r];
+            if (g == 0) pair<false, 4>(Q, H[r], a[r][0], a[r][1]);
+            else if (g == 1) pair<false, 2>(Q, H[r], a[r][0], a[r][1]);
+            else if (g == 2) pair<true, 4>(Q, H[r], a[r][0], a[r][1]);
+            else pair<true, 2>(Q, H[r], a[r][0], a[r][1]);
+            const uint32_t scw = SC[r][g >> 1];
+            const int sb = (int)(int8_t)((scw >> (8 * (2 * (g & 1) + l))) & 0xFFu);
+            sc[r] = d[r] * (float)sb;
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint2 b = bq[g][nt];
+#pragma unroll
+            for (int set = 0; set < NSETS; ++set) {
+              float p[4] = {0.f, 0.f, 0.f, 0.f};
+              mma_f16(p, a[2 * set][0], a[2 * set + 1][0], a[2 * set][1], a[2 * set + 1][1], b.x, b.y);
+              acc[set][nt][0] = fmaf(sc[2 * set], p[0], acc[set][nt][0]);
+              acc[set][nt][1] = fmaf(sc[2 * set], p[1], acc[set][nt][1]);
+              acc[set][nt][2] = fmaf(sc[2 * set + 1], p[2], acc[set][nt][2]);
+              acc[set][nt][3] = fmaf(sc[2 * set + 1], p[3], acc[set][nt][3]);
+            }
+          }
+        }
+      }
+    }
+  }
+  template <int NSETS, int NT, bool PRE>
+  __device__ __forceinline__ static void run(const uint32_t (&s)[2 * NSETS], int t,
+                                             const BFrag<NT>&, const __half* const (&xr)[NT],
+                                             int col, float (&acc)[NSETS][NT][4]) {
+    superblock<0, NSETS, NT>(s, 0u, t, xr, col, acc);
+    superblock<1, NSETS, NT>(s, 210u, t, xr, col + 256, acc);
+  }
+};
+
+
+// ---- the per-warp weight stream ------------------------------------------------------------------
+// A warp owns a ring of STAGES stages; a stage holds ROWS row-chunks (16 rows, or 16 gate + 16 up
+// rows).  Work is a flat list of steps = (m-tile, chunk) pairs; step i lives in stage i % STAGES.
+template <int FMT, int KCV, int ROWS, int STAGES>
+struct WarpStream {
+  using G = StageGeom<FMT, KCV>;
+  using F = StreamFmt<FMT>;
+  static constexpr int STAGE_BYTES = ROWS * G::PITCH;
+  static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+
+  uint32_t smem;        // shared address of this warp's ring
+  uint32_t bars;        // shared address of this warp's STAGES mbarriers
+  const uint8_t* w0;    // weight tensors (w1 only when ROWS == 32)
+  const uint8_t* w1;
+  size_t row_bytes;
+  int N, N1, K, nch, lane;   // N1 = row limit of the w1 half (DUAL: N; single matrix: N - 16)
+  int* err_flag;        // device-global flag raised when a bounded wait expires
+  bool dead;
+
+  __device__ __forceinline__ void init(uint32_t smem_, uint32_t bars_, const uint8_t* w0_,
+                                       const uint8_t* w1_, int N_, int K_, int lane_,
+                                       int* err_flag_) {
+    smem = smem_; bars = bars_; w0 = w0_; w1 = w1_; N = N_; N1 = N_; K = K_; lane = lane_;
+    err_flag = err_flag_;
+    row_bytes = (size_t)(K / F::BK) * F::BB;
+    nch = (K + G::KC - 1) / G::KC;
+    dead = false;
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, ROWS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+  }
+
+  // shared address at which byte 0 of (row slot r, chunk c) of a tile starting at row0 lands
+  __device__ __forceinline__ uint32_t slot_addr(int stage, int r, int row0, int c) const {
+    const uint8_t* base = (r < 16 ? w0 : w1);
+    const size_t off = (size_t)(row0 + (r & 15)) * row_bytes + (size_t)c * G::CHUNK_BYTES;
+    return smem + stage * STAGE_BYTES + r * G::PITCH + (uint32_t)((uintptr_t)(base + off) & 15u);
+  }
+
+  // every lane < ROWS fetches one row-chunk of step (row0, c) into `stage`
+  __device__ __forceinline__ void issue(int stage, int row0, int c) {
+    if (lane >= ROWS) return;
+    const uint32_t bar = bars + 8 * stage;
+    const int row = row0 + (lane & 15);
+    if (row >= (lane < 16 ? N : N1)) { mbar_arrive(bar); return; }
+    const uint8_t* base = (lane < 16 ? w0 : w1);
+    const size_t off = (size_t)row * row_bytes + (size_t)c * G::CHUNK_BYTES;
+    size_t len = row_bytes - (size_t)c * G::CHUNK_BYTES;
+    if (len > (size_t)G::CHUNK_BYTES) len = G::CHUNK_BYTES;
+    const uintptr_t a = (uintptr_t)(base + off);
+    const uintptr_t a0 = a & ~(uintptr_t)15;
+    const uint32_t bytes = (uint32_t)(((a + len + 15) & ~(uintptr_t)15) - a0);
+    const uint32_t dst = smem + stage * STAGE_BYTES + lane * G::PITCH;
+    mbar_arrive_expect_tx(bar, bytes);
+    bulk_g2s(dst, reinterpret_cast<const void*>(a0), bytes, bar);
+  }
+
+  __device__ __forceinline__ bool wait(int stage, uint32_t parity) {
+    if (dead) return false;
+    if (!mbar_wait(bars + 8 * stage, parity, err_flag)) dead = true;
+    return !dead;
+  }
+};
+
+}  // namespace qx
