@@ -197,7 +197,9 @@ qx_status qx_cuda_lm_head_sample_q_noalloc(void* stream, const void* h, const vo
  *                       id -1; ids are GLOBAL vocab ids
  *   cand_lse            (T, L) per-tile log-sum-exp (mode 3 only, L = tiles of the largest shard;
  *                       absent tiles carry -FLT_MAX)
- * After an all-gather over shards into (S, T, C) / (S, T, L) buffers, stage 2 picks the tokens.
+ * After an all-gather over shards into (S, T, C) / (S, T, L) buffers (shard_stride = 0), or into
+ * one buffer per shard laid end to end in which the three arrays sit at fixed offsets and the
+ * shards are shard_stride elements apart (the all-gather output as it is), stage 2 picks the tokens.
  * The merges (max with lowest id, top-k of top-k, sum of exp) are associative, so the result
  * equals the single-device call on the same logits.  The reference has no multi-device code; the
  * split follows its own two-stage tile -> reduce structure (lm_head.metal:219-235, :444-529).
@@ -215,8 +217,9 @@ qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const vo
 
 qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, const int32_t* cand_id,
                                        const float* cand_lse, int32_t* ids, int64_t shards,
-                                       int64_t T, int64_t max_tiles, int mode, int topk,
-                                       double temperature, uint32_t seed, double top_p);
+                                       int64_t T, int64_t max_tiles, int64_t shard_stride,
+                                       int mode, int topk, double temperature, uint32_t seed,
+                                       double top_p);
 
 /* ---- introspection --------------------------------------------------------------------------- */
 /* block_k / block_bytes of a format name; returns 0 and leaves the outputs alone if unknown

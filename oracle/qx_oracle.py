@@ -552,3 +552,89 @@ def lm_head_sample(h, packed, fmt, mode, k=0, temperature=1.0, seed=0, top_p=0.9
     """The reference composition: dequantise, project, sample (tk/__init__.py:2357-2412)."""
     return lm_head_sample_from_logits(lm_head_logits(h, packed, fmt), mode, k, temperature, seed,
                                       top_p, bias, 0, return_detail)
+
+
+# ----------------------------------------------------------------------------------------------
+# Vocabulary-sharded form of the fused sampler (no reference counterpart: the reference is single
+# device).  A shard emits, per hidden row, the candidates its 256-row tiles would hand to the
+# reference's reduce kernels; the merge over shards applies the same reduce rules to the union.
+# Because max-with-lowest-id, top-k-of-top-k and sum-of-exp are associative, merge(shards) must
+# equal lm_head_sample_from_logits on the concatenated logits - which is what the tests check.
+# ----------------------------------------------------------------------------------------------
+def lm_head_shard_candidates(logits_local, mode, k=0, temperature=1.0, seed=0, bias_local=None,
+                             vocab_offset=0, max_tiles=None):
+    """(val (T,C), id (T,C), lse (T,L)) for rows [vocab_offset, vocab_offset+V_local).  Absent
+    slots: id -1 / value NEG_INF; absent tiles: lse NEG_INF.  C = 1 (modes 0/1), k (mode 2),
+    max_tiles*k (mode 3)."""
+    f = np.float32
+    L = np.asarray(logits_local, f)
+    T, V = L.shape
+    ids = np.arange(V, dtype=np.int64) + int(vocab_offset)
+    invtemp = f(1.0) / f(temperature)
+    tiles = (V + TILE_V - 1) // TILE_V
+    max_tiles = tiles if max_tiles is None else max_tiles
+    b = None if bias_local is None else np.asarray(bias_local, f)
+    C = 1 if mode <= 1 else (k if mode == 2 else max_tiles * k)
+    val = np.full((T, C), NEG_INF, f)
+    idx = np.full((T, C), -1, np.int32)
+    lse = np.full((T, max_tiles if mode == 3 else 0), NEG_INF, f)
+    for t in range(T):
+        row = L[t]
+        if mode <= 1:
+            s = (row * invtemp).astype(f)
+            if b is not None:
+                s = (s + b).astype(f)
+            if mode == 1:
+                s = (s + rng_gumbel(seed, t, ids)).astype(f)
+            w = _argmax_low_id(s, ids)
+            val[t, 0], idx[t, 0] = s[w - int(vocab_offset)], w
+            continue
+        raw = row if b is None else (row + b).astype(f)
+        if mode == 2:
+            tv, ti = _topk_desc(raw, ids, k)
+            val[t, :tv.size], idx[t, :ti.size] = tv, ti
+            continue
+        for j, v0 in enumerate(range(0, V, TILE_V)):
+            seg = raw[v0:v0 + TILE_V]
+            tv, ti = _topk_desc(seg, ids[v0:v0 + TILE_V], k)
+            val[t, j * k:j * k + tv.size], idx[t, j * k:j * k + ti.size] = tv, ti
+            tl = (seg * invtemp).astype(f)
+            m = tl.max()
+            lse[t, j] = f(m + np.log(np.exp((tl - m).astype(f)).astype(f).sum(dtype=f)))
+    return val, idx, lse
+
+
+def lm_head_merge_candidates(vals, idxs, lses, mode, k=0, temperature=1.0, seed=0, top_p=0.9):
+    """Stage 2 over the shards' candidates (lists of the arrays above, one entry per shard)."""
+    f = np.float32
+    val = np.concatenate(vals, axis=1); idx = np.concatenate(idxs, axis=1).astype(np.int64)
+    lse = np.concatenate(lses, axis=1) if mode == 3 else None
+    T = val.shape[0]
+    invtemp = f(1.0) / f(temperature)
+    out = np.zeros(T, np.int32)
+    for t in range(T):
+        ok = idx[t] >= 0
+        v, i = val[t][ok], idx[t][ok]
+        if mode <= 1:
+            out[t] = _argmax_low_id(v, i)
+        elif mode == 2:
+            tv, ti = _topk_desc(v, i, k)
+            s = ((tv * invtemp).astype(f) + rng_gumbel(seed, t, ti)).astype(f)
+            out[t] = _argmax_low_id(s, ti)
+        else:
+            ls = (v * invtemp).astype(f)
+            mx = ls.max()
+            tl = lse[t][lse[t] > NEG_INF]
+            Z = np.exp((tl - mx).astype(f)).astype(f).sum(dtype=f)
+            lo, hi = f(mx - f(40.0)), f(mx)
+            for _ in range(32):
+                mid = f(f(0.5) * f(lo + hi))
+                sm = np.exp((ls[ls >= mid] - mx).astype(f)).astype(f).sum(dtype=f) / Z
+                if sm >= f(top_p):
+                    lo = mid
+                else:
+                    hi = mid
+            keep = ls >= lo
+            s = (ls[keep] + rng_gumbel(seed, t, i[keep])).astype(f)
+            out[t] = _argmax_low_id(s, i[keep]) if keep.any() else -1
+    return out

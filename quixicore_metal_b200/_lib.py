@@ -65,7 +65,7 @@ def lib() -> C.CDLL:
     L.qx_cuda_lm_head_shard_partials_q.restype = Status
     L.qx_cuda_lm_head_shard_partials_q.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, i64, cs, i32, i32, i32, f64, u32]
     L.qx_cuda_lm_head_shard_reduce.restype = Status
-    L.qx_cuda_lm_head_shard_reduce.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, f64, u32, f64]
+    L.qx_cuda_lm_head_shard_reduce.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, f64, u32, f64]
     L.qx_cuda_format_info.restype = i32
     L.qx_cuda_format_info.argtypes = [cs, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.qx_cuda_launch_count.restype = C.c_uint64

@@ -219,7 +219,7 @@ qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, 
   LmHeadArgs a{h, wq, bias, T, V, K, 0, f, dtype, mode, kk, 1.0f / (float)temperature, seed,
                (float)top_p};
   launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, pl, tiles);
-  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, pl, 1, T, tiles * kk, tiles, mode, kk,
+  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, pl, 1, T, tiles * kk, tiles, 0, mode, kk,
                         a.invtemp, seed, a.top_p, ids, 0, nullptr, nullptr);
   return check_launch(op);
 }
@@ -269,20 +269,22 @@ qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const vo
   float* pv = (float*)workspace;
   int32_t* pi = (int32_t*)((char*)workspace + seg);
   launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, nullptr, tiles);
-  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, nullptr, 1, T, tiles * kk, 0, mode, kk,
+  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, nullptr, 1, T, tiles * kk, 0, 0, mode, kk,
                         a.invtemp, seed, 1.0f, nullptr, 1, cand_val, cand_id);
   return check_launch(op);
 }
 
 qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, const int32_t* cand_id,
                                        const float* cand_lse, int32_t* ids, int64_t shards,
-                                       int64_t T, int64_t max_tiles, int mode, int topk,
-                                       double temperature, uint32_t seed, double top_p) {
+                                       int64_t T, int64_t max_tiles, int64_t shard_stride,
+                                       int mode, int topk, double temperature, uint32_t seed,
+                                       double top_p) {
   static const char* op = "quantized_lm_head_sample.shard_reduce";
   if (!cand_val || !cand_id || !ids || (mode == 3 && !cand_lse))
     return fail(QX_INVALID_ARGUMENT, op, "null pointer");
   if (mode < 0 || mode > 3) return fail(QX_INVALID_ARGUMENT, op, "mode 0=argmax, 1=categorical, 2=topk, 3=topp");
   if (shards <= 0 || shards > 1024 || T <= 0 || max_tiles <= 0) return fail(QX_INVALID_SHAPE, op, "shards, T and max_tiles must be positive");
+  if (shard_stride < 0) return fail(QX_INVALID_ARGUMENT, op, "shard_stride must be >= 0");
   if (!(temperature > 0.0)) return fail(QX_INVALID_ARGUMENT, op, "temperature must be positive");
   if (mode >= 2 && (topk < 1 || topk > 64)) return fail(QX_INVALID_ARGUMENT, op, "k must be in [1, 64]");
   if (mode == 3 && !(top_p > 0.0 && top_p <= 1.0)) return fail(QX_INVALID_ARGUMENT, op, "topp requires top_p in (0, 1]");
@@ -292,7 +294,7 @@ qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, cons
   const int64_t C = qx_cuda_lm_head_shard_candidates(mode, kk, max_tiles);
   // stage-1 scores of modes 0/1 already carry temperature, bias and noise: the merge is a plain max
   launch_lm_head_reduce((cudaStream_t)stream, cand_val, cand_id, cand_lse, (int)shards, T, C,
-                        mode == 3 ? max_tiles : 0, mode, kk, 1.0f / (float)temperature, seed,
+                        mode == 3 ? max_tiles : 0, shard_stride, mode, kk, 1.0f / (float)temperature, seed,
                         (float)top_p, ids, 0, nullptr, nullptr);
   return check_launch(op);
 }

@@ -49,11 +49,12 @@ void launch_lm_head_partials(cudaStream_t st, const LmHeadArgs& a, float* part_v
 // ncand candidates per row and shard at cand_val/cand_id (+ nlse tile lses, mode 3).
 // emit_set = 0: write the sampled id per row to ids.  emit_set = 1: write the selected candidate
 // set ((val,id) x set_size per row, absent = id -1) to out_val/out_id instead (modes 0..2).
-// Candidates are laid out (shards, T, ncand) and lses (shards, T, nlse).
+// Candidates are laid out (shards, T, ncand) and lses (shards, T, nlse); with shard_stride > 0 the
+// three arrays instead advance by shard_stride elements from one shard to the next.
 void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t* cand_id,
                            const float* cand_lse, int shards, int64_t T, int64_t ncand,
-                           int64_t nlse, int mode, int topk, float invtemp, uint32_t seed,
-                           float top_p, int32_t* ids, int emit_set, float* out_val,
+                           int64_t nlse, int64_t shard_stride, int mode, int topk, float invtemp,
+                           uint32_t seed, float top_p, int32_t* ids, int emit_set, float* out_val,
                            int32_t* out_id);
 
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,

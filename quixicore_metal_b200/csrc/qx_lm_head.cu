@@ -451,13 +451,16 @@ __device__ __forceinline__ uint32_t float_key(float v) {
 __global__ void __launch_bounds__(LMH_RED_THREADS)
 lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict__ cand_id,
                   const float* __restrict__ cand_lse, int shards, int T_rows, long long ncand_s,
-                  long long nlse_s, int mode,
+                  long long nlse_s, long long shard_stride, long long lse_stride,
+                  int cache_elems, int mode,
                   int topk, float invtemp, uint32_t seed, float top_p, int32_t* __restrict__ ids,
                   int emit_set, float* __restrict__ out_val, int32_t* __restrict__ out_id) {
   __shared__ BlockScratch S;
   const int t = blockIdx.x;
   const int tid = threadIdx.x, nth = blockDim.x;
-  // candidates of row t: shard s contributes ncand_s entries at ((s*T + t)*ncand_s + j)
+  // candidates of row t: shard s contributes ncand_s entries at (s*shard_stride + t*ncand_s + j)
+  // (tile lses: s*shard_stride + t*nlse_s + j)
+  extern __shared__ float cache[];                // mode 3: tempered logits + their exponentials
   const long long ncand = ncand_s * shards;
   const long long nlse = nlse_s * shards;
   struct View {
@@ -467,7 +470,7 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
     }
   };
   const View vw{cand_val + (size_t)t * ncand_s, cand_id + (size_t)t * ncand_s,
-                shards > 1 ? ncand_s : 0, (long long)T_rows * ncand_s};
+                shards > 1 ? ncand_s : 0, shard_stride};
 #define cv(j) vw.v[vw.at(j)]
 #define ci(j) vw.i[vw.at(j)]
 
@@ -581,17 +584,36 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
   mx = block_max(mx, S);
   float Z = 0.f;
   for (long long j = tid; j < nlse; j += nth) {
-    const float pl = cand_lse[((j / nlse_s) * T_rows + t) * nlse_s + (j % nlse_s)];
+    const float pl = cand_lse[(j / nlse_s) * lse_stride + (long long)t * nlse_s + (j % nlse_s)];
     if (pl > QX_NEG_INF) Z += expf(pl - mx);
   }
   Z = block_sum(Z, S);
+  // the 32 bisection steps re-scan every candidate: keep ls and exp(ls - mx) in shared memory
+  // when they fit (absent candidates are stored as -inf / 0 and never pass a threshold)
+  const bool cached = cache_elems >= ncand;
+  float* c_ls = cache;
+  float* c_ex = cache + cache_elems;
+  if (cached) {
+    for (long long j = tid; j < ncand; j += nth) {
+      const bool ok = ci(j) >= 0;
+      const float ls = cv(j) * invtemp;
+      c_ls[j] = ok ? ls : QX_NEG_INF;
+      c_ex[j] = ok ? expf(ls - mx) : 0.f;
+    }
+    __syncthreads();
+  }
   float lo = mx - 40.0f, hi = mx;
   for (int it = 0; it < 32; ++it) {
     const float mid = 0.5f * (lo + hi);
     float sm = 0.f;
-    for (long long j = tid; j < ncand; j += nth) {
-      const float ls = cv(j) * invtemp;
-      if (ci(j) >= 0 && ls >= mid) sm += expf(ls - mx);
+    if (cached) {
+      for (long long j = tid; j < ncand; j += nth)
+        if (c_ls[j] >= mid) sm += c_ex[j];
+    } else {
+      for (long long j = tid; j < ncand; j += nth) {
+        const float ls = cv(j) * invtemp;
+        if (ci(j) >= 0 && ls >= mid) sm += expf(ls - mx);
+      }
     }
     sm = block_sum(sm, S) / Z;
     if (sm >= top_p) lo = mid; else hi = mid;
@@ -599,9 +621,10 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
   float best = QX_NEG_INF;
   int bid = 0x7fffffff;
   for (long long j = tid; j < ncand; j += nth) {
+    const float ls = cached ? c_ls[j] : cv(j) * invtemp;
+    if (ls < lo) continue;
     const int id = ci(j);
-    const float ls = cv(j) * invtemp;
-    if (id < 0 || ls < lo) continue;
+    if (id < 0) continue;
     const float p = ls + rng_gumbel(seed, (uint32_t)t, (uint32_t)id);
     if (better(p, id, best, bid)) { best = p; bid = id; }
   }
@@ -645,12 +668,22 @@ void launch_lm_head_partials(cudaStream_t st, const LmHeadArgs& a, float* part_v
 
 void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t* cand_id,
                            const float* cand_lse, int shards, int64_t T, int64_t ncand,
-                           int64_t nlse, int mode, int topk, float invtemp, uint32_t seed,
-                           float top_p, int32_t* ids, int emit_set, float* out_val,
+                           int64_t nlse, int64_t shard_stride, int mode, int topk, float invtemp,
+                           uint32_t seed, float top_p, int32_t* ids, int emit_set, float* out_val,
                            int32_t* out_id) {
-  lmh_reduce_kernel<<<(unsigned)T, LMH_RED_THREADS, 0, st>>>(
+  // shard_stride = elements between consecutive shards in all three arrays (0: dense (S,T,C))
+  const long long stride_c = shard_stride > 0 ? shard_stride : (long long)T * ncand;
+  int cache_elems = 0;
+  size_t smem = 0;
+  if (mode == 3 && (size_t)ncand * shards * 8 <= 200 * 1024) {
+    cache_elems = (int)(ncand * shards);
+    smem = (size_t)cache_elems * 8;
+    cudaFuncSetAttribute(lmh_reduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  }
+  const long long stride_l = shard_stride > 0 ? shard_stride : (long long)T * (nlse > 0 ? nlse : 1);
+  lmh_reduce_kernel<<<(unsigned)T, LMH_RED_THREADS, smem, st>>>(
       cand_val, cand_id, cand_lse, shards, (int)T, (long long)ncand, (long long)(nlse > 0 ? nlse : 1),
-      mode, topk, invtemp, seed, top_p, ids, emit_set, out_val, out_id);
+      stride_c, stride_l, cache_elems, mode, topk, invtemp, seed, top_p, ids, emit_set, out_val, out_id);
   note_launch();
 }
 

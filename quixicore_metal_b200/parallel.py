@@ -97,16 +97,16 @@ def lm_head_reduce_gathered(gathered, shards: int, T: int, max_tiles: int, mode,
     kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
     C, L = candidate_layout(m, kk, max_tiles)
     per = T * (2 * C + L)
-    g = gathered.view(shards, per)
+    g = gathered.view(-1)
     with torch.cuda.device(gathered.device):
-        # regroup the planar per-shard buffers into (S,T,C) vals, (S,T,C) ids, (S,T,L) lses
-        val = g[:, : T * C].contiguous()
-        idt = g[:, T * C: 2 * T * C].contiguous()
-        lse = g[:, 2 * T * C:].contiguous() if L else None
+        # the planar per-shard buffers are read in place: values, ids and lses start at fixed
+        # offsets of shard 0 and every further shard lies `per` elements on
+        base = g.data_ptr()
         ids = torch.empty(T, dtype=torch.int32, device=gathered.device)
         _lib.check(_lib.lib().qx_cuda_lm_head_shard_reduce(
-            _stream(), _ptr(val), _ptr(idt), _ptr(lse), _ptr(ids), shards, T, max_tiles, m,
-            max(kk, 1), float(temperature), int(seed) & 0xFFFFFFFF, float(top_p)))
+            _stream(), base, base + 4 * T * C, (base + 8 * T * C) if L else None, _ptr(ids), shards, T,
+            max_tiles, per if shards > 1 else 0, m, max(kk, 1), float(temperature),
+            int(seed) & 0xFFFFFFFF, float(top_p)))
     return ids
 
 
