@@ -131,6 +131,14 @@ qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void
                                          qx_dtype dtype, int activation, int use_bias,
                                          int use_residual);
 
+/* y[m,n] = dot(x[m,:], deq(W[n,:])) as fp32, no epilogue: the per-rank piece of a row-parallel
+ * (K-split) projection, to be summed over ranks before bias / activation / residual are applied
+ * once.  No counterpart in the reference (single device).  Needs bf16 / f16 activations, 16-byte
+ * aligned bases and K a multiple of 512; otherwise QX_UNSUPPORTED_LAYOUT. */
+qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void* weight, float* y,
+                                        int64_t M, int64_t K, int64_t N, const char* format,
+                                        qx_dtype dtype);
+
 /* y[m,n] = T( silu(gate.x + gb) * (up.x + ub) ).  Replaces decode_swiglu_mps
  * (torch_kernels.mm:6437-6466) and tk::launch_decode_swiglu (tk_launch.h:458-470). */
 qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_weight,

@@ -46,6 +46,8 @@ def lib() -> C.CDLL:
     cs = C.c_char_p
     L.qx_cuda_decode_linear_epilogue.restype = Status
     L.qx_cuda_decode_linear_epilogue.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, i32]
+    L.qx_cuda_decode_linear_partial.restype = Status
+    L.qx_cuda_decode_linear_partial.argtypes = [vp, vp, vp, vp, i64, i64, i64, cs, i32]
     L.qx_cuda_decode_swiglu.restype = Status
     L.qx_cuda_decode_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32]
     L.qx_cuda_quantize_per_token.restype = Status

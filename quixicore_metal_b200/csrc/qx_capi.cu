@@ -112,6 +112,23 @@ qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void
   return check_launch(op);
 }
 
+qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void* weight, float* y,
+                                        int64_t M, int64_t K, int64_t N, const char* format,
+                                        qx_dtype dtype) {
+  static const char* op = "decode_linear_epilogue.partial";
+  int f = -1;
+  qx_status st = check_projection(op, x, weight, y, M, K, N, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  if (!device_ready(op, &st)) return st;
+  GemvArgs a{x, weight, nullptr, nullptr, nullptr, nullptr, y, M, K, N, f, dtype, 0, 0, 0};
+  a.out_f32 = 1;
+  if (stream_path_ok(a) && launch_gemv_stream((cudaStream_t)stream, a)) return check_launch(op);
+  if (tc_path_ok(a) && launch_gemm_tc((cudaStream_t)stream, a)) return check_launch(op);
+  return fail(QX_UNSUPPORTED_LAYOUT, op,
+              "fp32 partial projections need bf16/f16 activations, 16-byte aligned bases and K a "
+              "multiple of 512 columns");
+}
+
 qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_weight,
                                 const void* up_weight, const void* gate_bias, const void* up_bias,
                                 void* y, int64_t M, int64_t K, int64_t N, const char* format,

@@ -358,6 +358,7 @@ static bool launch_stream_dt(cudaStream_t st, const GemvArgs& a) {
 }
 
 bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a) {
+  if (a.out_f32) return launch_stream_dt<float>(st, a);      // raw fp32 dot products
   if (a.dtype == QX_DTYPE_F16) return launch_stream_dt<__half>(st, a);
   return launch_stream_dt<__nv_bfloat16>(st, a);
 }

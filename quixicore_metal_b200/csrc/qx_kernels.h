@@ -18,17 +18,24 @@ struct GemvArgs {
   int format;          // qx::Format
   qx_dtype dtype;      // F32 / F16 / BF16
   int activation, use_bias, use_residual;
+  int out_f32 = 0;     // 1: y is fp32 (M,N) raw dot products, no bias / activation / residual
 };
 
 void launch_gemv_generic(cudaStream_t st, const GemvArgs& a);
 // Streaming tensor-core path (bf16 activations, batch <= 16, 16-byte aligned bases).
 bool stream_path_ok(const GemvArgs& a);
 bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a);
+// tcgen05 path (bf16 activations, batch > 16, K % 256 == 0, single weight matrix).
+bool tc_path_ok(const GemvArgs& a);
+bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a);
 // Value of the device-side error flag that bounded waits raise (synchronises the device).
 int read_device_error_flag();
 // Device address of that flag on the current device (nullptr if it cannot be resolved).
 int* device_error_flag();
 // Row-scaled f16 copy of (M,K) bf16 / f16 activations in the column order `perm` of the decoders.
+// silu(gate + gb) * (up + ub) over fp32 (M,N) projections -> T (M,N)
+void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, const void* gb,
+                           const void* ub, void* y, int64_t M, int64_t N, qx_dtype dtype, int use_bias);
 void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __half* x16,
                              float* rowscale, int M, int K, int perm);
 // Picks the kernel family for one projection call (format, dtype, batch, alignment).

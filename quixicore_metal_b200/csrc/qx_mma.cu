@@ -1,0 +1,398 @@
+// decode_linear_epilogue / decode_swiglu for 16 < batch <= 128 per pass: tcgen05 tensor-core path.
+//
+// Shape of the problem: out[n, m] = sum_k W[n, k] * x[m, k] with W packed.  The weight rows are the
+// M-mode of the MMA (128 rows per CTA tile), the batch is the N-mode (16..128), so small batches
+// waste nothing ("swap-AB").  Per 64-column k-stage:
+//   * a producer thread streams raw packed rows into a shared-memory ring with cp.async.bulk;
+//   * 128 dequant threads (one weight row each) decode their 64 columns to fp32, split every weight
+//     into NTERMS bf16 terms whose sum is exactly the fp32 weight (1 term for nvfp4 / mxfp4 / mxfp8,
+//     whose weights are exact in bf16; 2 for q4_0; 3 for q8_0 / q6_K) and store each term as a
+//     K-major 128-byte-swizzled operand tile; they also copy the activation tile (bf16, K-major);
+//   * one thread issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32 in TMEM), one MMA chain per
+//     term, all accumulating into the same TMEM columns: the result is the fp32 dequantise-then-dot
+//     up to summation order, with no rounding of the weights;
+//   * the dequant threads read the accumulator back with tcgen05.ld and apply bias / activation /
+//     residual, storing 32 consecutive output channels per warp instruction.
+// Every wait on an mbarrier is bounded; on expiry the CTA raises the device error flag, stops
+// issuing work, frees its tensor memory and returns.
+#include <cstdlib>
+
+#include "qx_formats.cuh"
+#include "qx_kernels.h"
+#include "qx_stream.cuh"
+
+namespace qx {
+
+constexpr int MMA_BM = 128;          // weight rows per CTA tile
+constexpr int MMA_BK = 64;           // columns per MMA stage (128 bytes of bf16: one swizzle atom)
+constexpr int MMA_KR = 256;          // columns per raw-ring stage
+constexpr int MMA_A_STAGES = 2;
+constexpr int MMA_R_STAGES = 2;
+constexpr int MMA_THREADS = 192;     // warps 0-3 dequant/epilogue, warp 4 raw producer, warp 5 MMA
+
+// ---- tcgen05 wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 16 consecutive fp32 columns of this warp's 32 TMEM lanes
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
+// 1024 bytes apart.  `addr` is the shared-window byte address of the first row (+ 32 bytes per
+// 16-column step inside the swizzle atom).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                           // leading-dimension offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride between 8-row groups
+  d |= (uint64_t)1 << 46;                           // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                           // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(MMA_BM >> 4) << 24);
+}
+// byte offset of 16-byte chunk c of row r inside a swizzled tile
+__device__ __forceinline__ uint32_t sw128_offset(int r, int c) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+
+template <int FMT> struct MmaTerms { static constexpr int N = 1; };
+template <> struct MmaTerms<F_Q4_0> { static constexpr int N = 2; };
+template <> struct MmaTerms<F_Q8_0> { static constexpr int N = 3; };
+template <> struct MmaTerms<F_Q6_K> { static constexpr int N = 3; };
+
+
+template <int FMT> struct MmaGeom {
+  static constexpr int NTERMS = MmaTerms<FMT>::N;
+  static constexpr int CH = MMA_KR / block_k_of(FMT) * block_bytes_of(FMT);   // raw bytes per row and chunk
+  static constexpr int RPITCH = ((CH + 15) & ~15) + 32;
+  static constexpr int A_STAGE = NTERMS * MMA_BM * 128;
+  static constexpr int B_STAGE = 128 * 128;
+  static constexpr int OFF_B = MMA_A_STAGES * A_STAGE;
+  static constexpr int OFF_RAW = OFF_B + MMA_A_STAGES * B_STAGE;
+  static constexpr int OFF_BAR = OFF_RAW + MMA_R_STAGES * MMA_BM * RPITCH;
+  static constexpr int SMEM = OFF_BAR + 128 + 1024;   // + barriers / tmem slot + alignment slack
+};
+
+template <int FMT, typename T>
+__global__ void __launch_bounds__(MMA_THREADS, 1)
+gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
+               const T* __restrict__ bias, const T* __restrict__ residual, T* __restrict__ y, int M,
+               int K, int N, int BN, int activation, int use_bias, int use_residual,
+               int* __restrict__ err_flag) {
+  using G = MmaGeom<FMT>;
+  constexpr int NTERMS = G::NTERMS;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // barriers: [0,2) a_full, [2,4) a_empty, [4,6) raw_full, [6,8) raw_empty, 8 acc_full, 9 acc_empty
+  const uint32_t bars = sbase + G::OFF_BAR;
+  auto BAR = [&](int i) { return bars + 8u * (uint32_t)i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + G::OFF_BAR + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BAR + 100);
+
+  if (tid == 0) {
+    for (int s = 0; s < MMA_A_STAGES; ++s) { mbar_init(BAR(0 + s), 4); mbar_init(BAR(2 + s), 1); }
+    for (int s = 0; s < MMA_R_STAGES; ++s) { mbar_init(BAR(4 + s), MMA_BM); mbar_init(BAR(6 + s), 4); }
+    mbar_init(BAR(8), 1);
+    mbar_init(BAR(9), 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  int tmem_cols = 32;
+  while (tmem_cols < BN) tmem_cols <<= 1;
+  if (warp == 5) tmem_alloc(smem_u32((const void*)tmem_slot), (uint32_t)tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const size_t row_bytes = (size_t)(K / block_k_of(FMT)) * block_bytes_of(FMT);
+  const int ntiles = (N + MMA_BM - 1) / MMA_BM;
+  const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int nchunks = K / MMA_KR;                 // raw chunks per tile
+  constexpr int SPC = MMA_KR / MMA_BK;            // MMA stages per raw chunk
+
+  auto wait_or_abort = [&](uint32_t bar, uint32_t parity) -> bool {
+    if (*abort_flag) return false;
+    for (int i = 0; i < (1 << 19); ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(err_flag, 2);
+    *abort_flag = 1;
+    return false;
+  };
+
+  if (warp == 4) {
+    // ---------------- raw producer: 4 row-chunks per lane and stage ----------------
+    int rc = 0;
+    for (int j = 0; j < my_tiles; ++j) {
+      const int row0 = ((int)blockIdx.x + j * (int)gridDim.x) * MMA_BM;
+      for (int c = 0; c < nchunks; ++c, ++rc) {
+        const int rs = rc % MMA_R_STAGES;
+        if (rc >= MMA_R_STAGES && !wait_or_abort(BAR(6 + rs), (uint32_t)((rc / MMA_R_STAGES - 1) & 1))) break;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int r = lane + 32 * q;
+          const int row = row0 + r;
+          if (row >= N) { mbar_arrive(BAR(4 + rs)); continue; }
+          const uintptr_t a = (uintptr_t)(w + (size_t)row * row_bytes + (size_t)c * G::CH);
+          const uintptr_t a0 = a & ~(uintptr_t)15;
+          const uint32_t bytes = (uint32_t)(((a + G::CH + 15) & ~(uintptr_t)15) - a0);
+          mbar_arrive_expect_tx(BAR(4 + rs), bytes);
+          bulk_g2s(sbase + G::OFF_RAW + (uint32_t)((rs * MMA_BM + r) * G::RPITCH), (const void*)a0, bytes, BAR(4 + rs));
+        }
+      }
+      if (*abort_flag) break;
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BN);
+      int it = 0;
+      for (int j = 0; j < my_tiles; ++j) {
+        if (j > 0 && !wait_or_abort(BAR(9), (uint32_t)((j - 1) & 1))) break;
+        tc_fence_after();
+        const int nst = nchunks * SPC;
+        bool ok = true;
+        for (int st = 0; st < nst; ++st, ++it) {
+          const int sa = it % MMA_A_STAGES;
+          if (!wait_or_abort(BAR(0 + sa), (uint32_t)((it / MMA_A_STAGES) & 1))) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = sbase + (uint32_t)(sa * G::A_STAGE);
+          const uint32_t b_base = sbase + (uint32_t)(G::OFF_B + sa * G::B_STAGE);
+#pragma unroll
+          for (int term = 0; term < NTERMS; ++term) {
+#pragma unroll
+            for (int kk = 0; kk < MMA_BK / 16; ++kk) {
+              const uint64_t ad = umma_desc_sw128(a_base + (uint32_t)(term * MMA_BM * 128 + kk * 32));
+              const uint64_t bd = umma_desc_sw128(b_base + (uint32_t)(kk * 32));
+              tc_mma_f16(tmem_base, ad, bd, idesc, (st | term | kk) != 0 ? 1u : 0u);
+            }
+          }
+          tc_commit(BAR(2 + sa));            // stage reusable once these MMAs have read it
+        }
+        if (!ok) break;
+        tc_commit(BAR(8));                   // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- dequant + epilogue: thread r owns weight row r of the tile ----------------
+    const int r = tid;                       // 0..127
+    int it = 0, rc = 0;
+    for (int j = 0; j < my_tiles; ++j) {
+      const int row0 = ((int)blockIdx.x + j * (int)gridDim.x) * MMA_BM;
+      bool ok = true;
+      for (int c = 0; c < nchunks && ok; ++c, ++rc) {
+        const int rs = rc % MMA_R_STAGES;
+        if (!wait_or_abort(BAR(4 + rs), (uint32_t)((rc / MMA_R_STAGES) & 1))) { ok = false; break; }
+        const uintptr_t a = (uintptr_t)(w + (size_t)(row0 + r) * row_bytes + (size_t)c * G::CH);
+        const uint8_t* raw = smem + G::OFF_RAW + (size_t)(rs * MMA_BM + r) * G::RPITCH + (a & 15);
+#pragma unroll 1
+        for (int q = 0; q < SPC; ++q, ++it) {
+          const int sa = it % MMA_A_STAGES;
+          if (it >= MMA_A_STAGES && !wait_or_abort(BAR(2 + sa), (uint32_t)((it / MMA_A_STAGES - 1) & 1))) { ok = false; break; }
+          uint8_t* a_stage = smem + (size_t)sa * G::A_STAGE;
+          // 64 columns of this row, 32 at a time
+#pragma unroll
+          for (int hsp = 0; hsp < 2; ++hsp) {
+            float wv[32];
+            decode_span32<FMT>(raw, q * 2 + hsp, wv);
+            uint32_t pk[NTERMS][16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float v0 = wv[2 * i], v1 = wv[2 * i + 1];
+#pragma unroll
+              for (int term = 0; term < NTERMS; ++term) {
+                const __nv_bfloat16 b0 = __float2bfloat16_rn(v0), b1 = __float2bfloat16_rn(v1);
+                pk[term][i] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
+                v0 -= __bfloat162float(b0); v1 -= __bfloat162float(b1);
+              }
+            }
+#pragma unroll
+            for (int term = 0; term < NTERMS; ++term)
+#pragma unroll
+              for (int cc = 0; cc < 4; ++cc)
+                *reinterpret_cast<uint4*>(a_stage + term * MMA_BM * 128 + sw128_offset(r, hsp * 4 + cc)) =
+                    make_uint4(pk[term][4 * cc], pk[term][4 * cc + 1], pk[term][4 * cc + 2], pk[term][4 * cc + 3]);
+          }
+          // activation tile: BN rows x 64 columns (rows beyond the batch are zero)
+          uint8_t* b_stage = smem + G::OFF_B + (size_t)sa * G::B_STAGE;
+          const int kcol = (c * SPC + q) * MMA_BK;
+          for (int idx = tid; idx < BN * 8; idx += 128) {
+            const int m = idx >> 3, cc = idx & 7;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (m < M) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + kcol + cc * 8));
+            *reinterpret_cast<uint4*>(b_stage + sw128_offset(m, cc)) = v;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR(0 + sa));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(6 + rs));
+      }
+      if (!ok) break;
+      // ---- epilogue ----
+      if (!wait_or_abort(BAR(8), (uint32_t)(j & 1))) break;
+      tc_fence_after();
+      const int n = row0 + r;
+      const float bv = (use_bias && n < N) ? to_f32<T>(bias[n]) : 0.f;
+      for (int cb = 0; cb < BN / 16; ++cb) {
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 16), v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int m = cb * 16 + i;
+          if (m < M && n < N) {
+            const size_t o = (size_t)m * N + n;
+            float val = apply_act(v[i] + bv, activation);
+            if (use_residual) val += to_f32<T>(residual[o]);
+            y[o] = from_f32<T>(val);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(9));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
+}
+
+
+template <int FMT, typename T>
+static bool launch_tc_t(cudaStream_t st, const GemvArgs& a, int* err) {
+  using G = MmaGeom<FMT>;
+  static_assert(G::SMEM <= 227 * 1024, "tile configuration exceeds shared memory");
+  if (cudaFuncSetAttribute(gemm_tc_kernel<FMT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           G::SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  const int ntiles = (int)((a.N + MMA_BM - 1) / MMA_BM);
+  const int blocks = ntiles < sm_count() ? ntiles : sm_count();
+  for (int64_t m0 = 0; m0 < a.M; m0 += 128) {
+    const int mp = (int)((a.M - m0) < 128 ? (a.M - m0) : 128);
+    const int BN = (mp + 15) & ~15;
+    gemm_tc_kernel<FMT, T><<<blocks, MMA_THREADS, G::SMEM, st>>>(
+        (const __nv_bfloat16*)a.x + m0 * a.K, (const uint8_t*)a.w0, (const T*)a.bias0,
+        a.residual ? (const T*)a.residual + m0 * a.N : nullptr, (T*)a.y + m0 * a.N, mp, (int)a.K,
+        (int)a.N, BN < 32 ? 32 : BN, a.activation, a.use_bias, a.use_residual, err);
+    note_launch();
+  }
+  return true;
+}
+
+// Preconditions of the tcgen05 path.
+bool tc_path_ok(const GemvArgs& a) {
+  if (a.dtype != QX_DTYPE_BF16 || a.M <= 16) return false;
+  if (a.w1 && (((uintptr_t)a.w1 & 15) != 0)) return false;
+  if (a.K % MMA_KR != 0 || ((uintptr_t)a.x & 15) != 0 || ((uintptr_t)a.w0 & 15) != 0) return false;
+  return true;
+}
+
+template <typename T>
+static bool launch_tc_fmt(cudaStream_t st, const GemvArgs& a, int* err) {
+  switch (a.format) {
+    case F_Q4_0: return launch_tc_t<F_Q4_0, T>(st, a, err);
+    case F_Q8_0: return launch_tc_t<F_Q8_0, T>(st, a, err);
+    case F_Q6_K: return launch_tc_t<F_Q6_K, T>(st, a, err);
+    case F_MXFP8: return launch_tc_t<F_MXFP8, T>(st, a, err);
+    case F_NVFP4: return launch_tc_t<F_NVFP4, T>(st, a, err);
+    default: return launch_tc_t<F_MXFP4, T>(st, a, err);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_combine_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                      const T* __restrict__ gb, const T* __restrict__ ub,
+                                      T* __restrict__ y, long long total, int N, int use_bias) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float g = gate[i], u = up[i];
+    if (use_bias) { const int n = (int)(i % N); g += to_f32<T>(gb[n]); u += to_f32<T>(ub[n]); }
+    y[i] = from_f32<T>(silu(g) * u);
+  }
+}
+
+void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, const void* gb,
+                           const void* ub, void* y, int64_t M, int64_t N, qx_dtype dtype, int use_bias) {
+  const long long total = (long long)M * N;
+  const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
+  if (dtype == QX_DTYPE_F16)
+    swiglu_combine_kernel<__half><<<blocks, 256, 0, st>>>(gate, up, (const __half*)gb, (const __half*)ub, (__half*)y, total, (int)N, use_bias);
+  else if (dtype == QX_DTYPE_F32)
+    swiglu_combine_kernel<float><<<blocks, 256, 0, st>>>(gate, up, (const float*)gb, (const float*)ub, (float*)y, total, (int)N, use_bias);
+  else
+    swiglu_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(gate, up, (const __nv_bfloat16*)gb, (const __nv_bfloat16*)ub, (__nv_bfloat16*)y, total, (int)N, use_bias);
+  note_launch();
+}
+
+bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a) {
+  int* err = device_error_flag();
+  if (!err) return false;
+  if (a.w1) {
+    // SwiGLU at batch > 16: two fp32 projections into stream-ordered scratch, then the gate
+    const size_t bytes = (size_t)a.M * a.N * sizeof(float);
+    float* tmp = nullptr;
+    if (cudaMallocAsync((void**)&tmp, 2 * bytes, st) != cudaSuccess) { cudaGetLastError(); return false; }
+    GemvArgs g = a;
+    g.w1 = nullptr; g.bias0 = nullptr; g.bias1 = nullptr; g.residual = nullptr;
+    g.use_bias = 0; g.use_residual = 0; g.activation = 0; g.out_f32 = 1;
+    g.y = tmp;
+    bool ok = launch_tc_fmt<float>(st, g, err);
+    g.w0 = a.w1; g.y = tmp + (size_t)a.M * a.N;
+    ok = ok && launch_tc_fmt<float>(st, g, err);
+    if (ok) launch_swiglu_combine(st, tmp, tmp + (size_t)a.M * a.N, a.bias0, a.bias1, a.y, a.M, a.N, a.dtype, a.use_bias);
+    cudaFreeAsync(tmp, st);
+    return ok;
+  }
+  if (a.out_f32) return launch_tc_fmt<float>(st, a, err);
+  using T = __nv_bfloat16;
+  switch (a.format) {
+    case F_Q4_0: return launch_tc_t<F_Q4_0, T>(st, a, err);
+    case F_Q8_0: return launch_tc_t<F_Q8_0, T>(st, a, err);
+    case F_Q6_K: return launch_tc_t<F_Q6_K, T>(st, a, err);
+    case F_MXFP8: return launch_tc_t<F_MXFP8, T>(st, a, err);
+    case F_NVFP4: return launch_tc_t<F_NVFP4, T>(st, a, err);
+    default: return launch_tc_t<F_MXFP4, T>(st, a, err);
+  }
+}
+
+}  // namespace qx

@@ -70,6 +70,20 @@ def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
     return out
 
 
+def decode_linear_partial(x, weight, format):
+    """fp32 (B,N) raw projection x @ dequant(weight).T with no epilogue: one rank's share of a
+    row-parallel (K-split) linear, summed over ranks by the caller."""
+    fmt = str(format)
+    N = _check_weight(x, weight, fmt, "decode_linear_partial")
+    B, K = x.shape
+    with torch.cuda.device(x.device):
+        xc, wc = x.contiguous(), weight.contiguous()
+        out = torch.empty((B, N), dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_decode_linear_partial(
+            _stream(), _ptr(xc), _ptr(wc), _ptr(out), B, K, N, fmt.encode(), _DT[x.dtype]))
+    return out
+
+
 def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_bias=False):
     """Packed gate/up decode projections with fused SwiGLU: silu(gate.x+gb) * (up.x+ub)."""
     fmt = str(format)

@@ -210,3 +210,59 @@ def test_error_behaviour_matches_reference_messages():
     from quixicore_metal_b200 import tk_torch
     y = tk_torch.decode_linear_epilogue(x, w, x, x, "q4_0", 0, False, False)
     assert y.shape == (2, 3) and float(y.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M", [17, 32, 64, 100, 128, 129, 256])
+@pytest.mark.parametrize("fmt", FMTS)
+def test_epilogue_large_batch(fmt, M):
+    """Batch > 16 (the tcgen05 path for bf16): several 128-row weight tiles incl. a ragged last one,
+    batches that need a second pass (M > 128), every epilogue piece."""
+    K, N = 1024, 300
+    x, Wq, bias, res = _inputs(fmt, M, K, N, "bf16", 90 + M)
+    got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), dev(res, "bf16"),
+                                    activation="gelu", format=fmt)
+    ref = O.decode_linear_epilogue(x, Wq, fmt, bias, res, 1, "bf16")
+    assert_close_dtype(host(got), ref, "bf16")
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "q8_0"])
+def test_epilogue_large_batch_every_code_value(fmt):
+    x, Wq, bias, res = _inputs(fmt, 48, 512, 256, "bf16", 17, random_bytes=True)
+    got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), None, None, format=fmt)
+    ref = O.decode_linear_epilogue(x, Wq, fmt, None, None, 0, "bf16")
+    assert_close_dtype(host(got), ref, "bf16", scale=float(np.abs(ref).max()))
+
+
+@pytest.mark.parametrize("M", [24, 130])
+@pytest.mark.parametrize("fmt", ["nvfp4", "q6_K", "q8_0"])
+def test_swiglu_large_batch(fmt, M):
+    rng = np.random.default_rng(7 + M)
+    K, N = 1024, 200
+    x = rounded(rng.standard_normal((M, K)), "bf16")
+    g = O.synth_pack(fmt, (0.02 * rng.standard_normal((N, K))).astype(np.float32))
+    u = O.synth_pack(fmt, (0.02 * rng.standard_normal((N, K))).astype(np.float32))
+    gb = rounded(0.02 * rng.standard_normal(N), "bf16")
+    ub = rounded(0.02 * rng.standard_normal(N), "bf16")
+    got = tk.decode_swiglu(dev(x, "bf16"), dev(g), dev(u), dev(gb, "bf16"), dev(ub, "bf16"), format=fmt)
+    assert_close_dtype(host(got), O.decode_swiglu(x, g, u, fmt, gb, ub, "bf16"), "bf16")
+
+
+@pytest.mark.parametrize("M", [1, 8, 32])
+@pytest.mark.parametrize("fmt", ["nvfp4", "q4_0"])
+def test_row_parallel_partials_sum_to_full_projection(fmt, M):
+    """K split over 4 'ranks' at block boundaries: fp32 partials summed = the unsplit projection."""
+    from quixicore_metal_b200 import tk_torch
+    rng = np.random.default_rng(3 + M)
+    K, N, R = 4096, 160, 4
+    x = rounded(rng.standard_normal((M, K)), "bf16")
+    Wq = O.synth_pack(fmt, (0.02 * rng.standard_normal((N, K))).astype(np.float32))
+    bk = O.FORMATS[fmt][0]
+    nb = K // bk // R
+    total = None
+    for r in range(R):
+        part = tk_torch.decode_linear_partial(dev(x[:, r * K // R:(r + 1) * K // R], "bf16").contiguous(),
+                                              dev(np.ascontiguousarray(Wq[:, r * nb:(r + 1) * nb])), fmt)
+        assert part.dtype == torch.float32
+        total = part if total is None else total + part
+    ref = O.matmul_f64(x, O.dequantize(fmt, Wq))
+    np.testing.assert_allclose(host(total), ref, rtol=2e-5, atol=2e-5)
