@@ -28,7 +28,8 @@ constexpr int MMA_BK = 64;           // columns per MMA stage (128 bytes of bf16
 constexpr int MMA_KR = 256;          // columns per raw-ring stage
 constexpr int MMA_A_STAGES = 2;
 constexpr int MMA_R_STAGES = 2;
-constexpr int MMA_THREADS = 192;     // warps 0-3 dequant/epilogue, warp 4 raw producer, warp 5 MMA
+constexpr int MMA_DQ_WARPS = 8;       // dequant / epilogue warps: thread = (weight row, 32-column half)
+constexpr int MMA_THREADS = 320;     // warps 0-7 dequant/epilogue, warp 8 raw producer, warp 9 MMA
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -124,17 +125,17 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BAR + 100);
 
   if (tid == 0) {
-    for (int s = 0; s < MMA_A_STAGES; ++s) { mbar_init(BAR(0 + s), 4); mbar_init(BAR(2 + s), 1); }
-    for (int s = 0; s < MMA_R_STAGES; ++s) { mbar_init(BAR(4 + s), MMA_BM); mbar_init(BAR(6 + s), 4); }
+    for (int s = 0; s < MMA_A_STAGES; ++s) { mbar_init(BAR(0 + s), MMA_DQ_WARPS); mbar_init(BAR(2 + s), 1); }
+    for (int s = 0; s < MMA_R_STAGES; ++s) { mbar_init(BAR(4 + s), MMA_BM); mbar_init(BAR(6 + s), MMA_DQ_WARPS); }
     mbar_init(BAR(8), 1);
-    mbar_init(BAR(9), 4);
+    mbar_init(BAR(9), MMA_DQ_WARPS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   int tmem_cols = 32;
   while (tmem_cols < BN) tmem_cols <<= 1;
-  if (warp == 5) tmem_alloc(smem_u32((const void*)tmem_slot), (uint32_t)tmem_cols);
+  if (warp == MMA_DQ_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), (uint32_t)tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -155,7 +156,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
     return false;
   };
 
-  if (warp == 4) {
+  if (warp == MMA_DQ_WARPS) {
     // ---------------- raw producer: 4 row-chunks per lane and stage ----------------
     int rc = 0;
     for (int j = 0; j < my_tiles; ++j) {
@@ -177,7 +178,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
       }
       if (*abort_flag) break;
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_DQ_WARPS + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(BN);
@@ -209,8 +210,9 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
       }
     }
   } else {
-    // ---------------- dequant + epilogue: thread r owns weight row r of the tile ----------------
-    const int r = tid;                       // 0..127
+    // ------- dequant + epilogue: thread (r, hsp) owns 32 of the 64 stage columns of weight row r -------
+    const int r = tid & (MMA_BM - 1);        // 0..127
+    const int hsp = tid >> 7;                // which half of the stage columns
     int it = 0, rc = 0;
     for (int j = 0; j < my_tiles; ++j) {
       const int row0 = ((int)blockIdx.x + j * (int)gridDim.x) * MMA_BM;
@@ -225,9 +227,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
           const int sa = it % MMA_A_STAGES;
           if (it >= MMA_A_STAGES && !wait_or_abort(BAR(2 + sa), (uint32_t)((it / MMA_A_STAGES - 1) & 1))) { ok = false; break; }
           uint8_t* a_stage = smem + (size_t)sa * G::A_STAGE;
-          // 64 columns of this row, 32 at a time
-#pragma unroll
-          for (int hsp = 0; hsp < 2; ++hsp) {
+          {
             float wv[32];
             decode_span32<FMT>(raw, q * 2 + hsp, wv);
             uint32_t pk[NTERMS][16];
@@ -251,7 +251,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
           // activation tile: BN rows x 64 columns (rows beyond the batch are zero)
           uint8_t* b_stage = smem + G::OFF_B + (size_t)sa * G::B_STAGE;
           const int kcol = (c * SPC + q) * MMA_BK;
-          for (int idx = tid; idx < BN * 8; idx += 128) {
+          for (int idx = tid; idx < BN * 8; idx += MMA_DQ_WARPS * 32) {
             const int m = idx >> 3, cc = idx & 7;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (m < M) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + kcol + cc * 8));
@@ -270,9 +270,11 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
       tc_fence_after();
       const int n = row0 + r;
       const float bv = (use_bias && n < N) ? to_f32<T>(bias[n]) : 0.f;
-      for (int cb = 0; cb < BN / 16; ++cb) {
+      // warp w may touch TMEM lanes 32*(w % 4)..+31: warps 0-3 take the even 16-column chunks,
+      // warps 4-7 the odd ones
+      for (int cb = hsp; cb < BN / 16; cb += 2) {
         float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 16), v);
+        tmem_ld16(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(cb * 16), v);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int m = cb * 16 + i;
@@ -292,7 +294,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
+  if (warp == MMA_DQ_WARPS + 1) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
 }
 
 

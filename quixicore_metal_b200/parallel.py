@@ -166,3 +166,77 @@ class VocabParallelLMHead:
             self.dist.all_gather_into_tensor(g, mine, group=self.group)
         return lm_head_reduce_gathered(g, self.world, T, self.max_tiles, m, kk, temperature, seed,
                                        top_p)
+
+
+# ----------------------------------------------------------------------------------------------
+# Tensor-parallel decode projection stack (Llama-style blocks without attention math).
+# ----------------------------------------------------------------------------------------------
+class TPDecodeStack:
+    """Per-rank shard of a stack of decoder-block projections over packed weights.
+
+    Per layer: QKV (column-parallel: output rows split), O (row-parallel: K split, fp32 partials
+    summed by one all-reduce, then the residual is added once), fused gate/up SwiGLU
+    (column-parallel), down (row-parallel + all-reduce + residual).  Attention itself is outside
+    this path and is replaced by the identity on V: every local query head takes the value vector
+    of its KV group, which makes the local input of O exactly this rank's K-shard.
+
+    `layers` is a list of dicts with this rank's packed tensors:
+        qkv  (q_local + 2*kv_local, hidden/bk, bb)     o    (hidden, q_local/bk, bb)
+        gate (inter_local, hidden/bk, bb)  up (same)   down (hidden, inter_local/bk, bb)
+    Partial sums cross the ranks in fp32 (not in the 16-bit I/O type), so the only difference from
+    the single-device result is the order of the K summation."""
+
+    def __init__(self, layers, fmt: str, head_dim: int = 128, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.layers, self.fmt, self.head_dim = layers, fmt, head_dim
+        bk = _LM_QUANT_BLOCK_K[fmt]
+        l0 = layers[0]
+        self.q_local = l0["o"].shape[1] * bk
+        self.kv_local = (l0["qkv"].shape[0] - self.q_local) // 2
+        _check(self.q_local % self.kv_local == 0 and self.kv_local % head_dim == 0,
+               "TPDecodeStack: query width must be a multiple of the KV width, KV width of head_dim")
+
+    def _all_reduce(self, t):
+        if self.world > 1:
+            self.dist.all_reduce(t, group=self.group)
+        return t
+
+    def layer(self, x, L):
+        from . import tk, tk_torch
+        qkv = tk.decode_linear_epilogue(x, L["qkv"], format=self.fmt)
+        # identity on V: the G query heads of KV group g all take that group's value vector
+        hd = self.head_dim
+        n_kv = self.kv_local // hd
+        v = qkv[:, self.q_local + self.kv_local:].reshape(-1, n_kv, 1, hd)
+        attn = v.expand(-1, n_kv, self.q_local // self.kv_local, hd).reshape(-1, self.q_local).contiguous()
+        o = self._all_reduce(tk_torch.decode_linear_partial(attn, L["o"], self.fmt))
+        x = (o + x.float()).to(x.dtype)
+        mid = tk.decode_swiglu(x, L["gate"], L["up"], format=self.fmt)
+        d = self._all_reduce(tk_torch.decode_linear_partial(mid, L["down"], self.fmt))
+        return (d + x.float()).to(x.dtype)
+
+    def forward(self, x):
+        for L in self.layers:
+            x = self.layer(x, L)
+        return x
+
+    @staticmethod
+    def shard_layer(full, rank: int, world: int, fmt: str, q: int, kv: int):
+        """This rank's tensors cut from one layer's full packed tensors (host or device): rows of
+        q / k / v / gate / up, K-blocks of o / down.  KV groups stay whole: kv % world == 0."""
+        bk = _LM_QUANT_BLOCK_K[fmt]
+        ql, kl = q // world, kv // world
+        W = full["qkv"]
+        qkv = torch.cat([W[rank * ql:(rank + 1) * ql], W[q + rank * kl:q + (rank + 1) * kl],
+                         W[q + kv + rank * kl:q + kv + (rank + 1) * kl]]) if torch.is_tensor(W) else None
+        il = full["gate"].shape[0] // world
+        cut = lambda t, n: t[:, rank * n:(rank + 1) * n].contiguous()
+        return {"qkv": qkv.contiguous(), "o": cut(full["o"], ql // bk),
+                "gate": full["gate"][rank * il:(rank + 1) * il].contiguous(),
+                "up": full["up"][rank * il:(rank + 1) * il].contiguous(),
+                "down": cut(full["down"], il // bk)}
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() for L in self.layers for t in L.values())

@@ -1,0 +1,79 @@
+"""Tensor-parallel projection stack: one rank holding everything equals the oracle composition;
+a K/N split into 2 shards emulated on one device (partials summed by hand) equals it too."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import qx_oracle as O
+from tests._util import dev, host, rounded
+
+pytestmark = pytest.mark.gpu
+
+
+def _full_layer(rng, hidden, q, kv, inter, fmt):
+    mk = lambda n, k: O.synth_pack(fmt, (0.03 * rng.standard_normal((n, k))).astype(np.float32))
+    return {"qkv": mk(q + 2 * kv, hidden), "o": mk(hidden, q), "gate": mk(inter, hidden), "up": mk(inter, hidden),
+            "down": mk(hidden, inter)}
+
+
+def _oracle_layer(x, L, fmt, q, kv):
+    qkv = O.decode_linear_epilogue(x, L["qkv"], fmt, None, None, 0, "bf16")
+    hd = 128                                   # query heads of KV group g take the value vector of group g
+    v = qkv[:, q + kv:].reshape(-1, kv // hd, 1, hd)
+    attn = np.broadcast_to(v, (v.shape[0], kv // hd, q // kv, hd)).reshape(-1, q)
+    o = O.matmul_f64(attn, O.dequantize(fmt, L["o"]))
+    x = O.round_bf16((o + x).astype(np.float32))
+    mid = O.decode_swiglu(x, L["gate"], L["up"], fmt, None, None, "bf16")
+    d = O.matmul_f64(mid, O.dequantize(fmt, L["down"]))
+    return O.round_bf16((d + x).astype(np.float32))
+
+
+@pytest.mark.parametrize("M", [1, 32])
+def test_stack_single_rank_matches_oracle(M):
+    from quixicore_metal_b200 import parallel
+    fmt, hidden, q, kv, inter = "nvfp4", 1024, 512, 512, 1024
+    rng = np.random.default_rng(11 + M)
+    layers = [_full_layer(rng, hidden, q, kv, inter, fmt) for _ in range(2)]
+    x = rounded(rng.standard_normal((M, hidden)), "bf16")
+    stack = parallel.TPDecodeStack([{k: dev(v) for k, v in L.items()} for L in layers], fmt)
+    got = host(stack.forward(dev(x, "bf16")))
+    ref = x
+    for L in layers:
+        ref = _oracle_layer(ref, L, fmt, q, kv)
+    err = np.abs(got - ref)
+    assert np.all(err <= np.abs(ref) * 2.0 ** -6 + 2e-2), float(err.max())   # two bf16 roundings per layer
+    assert np.mean(got == ref) > 0.8
+
+
+def test_stack_two_shards_emulated_on_one_device():
+    """The shard cut (rows of q/k/v/gate/up, K-blocks of o/down) with the two all-reduces done by
+    hand on one device equals the unsharded layer."""
+    from quixicore_metal_b200 import parallel, tk, tk_torch
+    fmt, hidden, q, kv, inter, M = "nvfp4", 1024, 1024, 256, 2048, 4
+    rng = np.random.default_rng(5)
+    full = {k: dev(v) for k, v in _full_layer(rng, hidden, q, kv, inter, fmt).items()}
+    x = rounded(rng.standard_normal((M, hidden)), "bf16")
+    xd = dev(x, "bf16")
+    want = parallel.TPDecodeStack([full], fmt).forward(xd)
+    shards = [parallel.TPDecodeStack([parallel.TPDecodeStack.shard_layer(full, r, 2, fmt, q, kv)], fmt) for r in range(2)]
+    hd = 128
+    o_sum, attn_in = None, []
+    for st in shards:
+        L = st.layers[0]
+        qkv = tk.decode_linear_epilogue(xd, L["qkv"], format=fmt)
+        n_kv = st.kv_local // hd
+        v = qkv[:, st.q_local + st.kv_local:].reshape(-1, n_kv, 1, hd)
+        attn = v.expand(-1, n_kv, st.q_local // st.kv_local, hd).reshape(-1, st.q_local).contiguous()
+        part = tk_torch.decode_linear_partial(attn, L["o"], fmt)
+        o_sum = part if o_sum is None else o_sum + part
+    h = (o_sum + xd.float()).to(xd.dtype)
+    d_sum = None
+    for st in shards:
+        L = st.layers[0]
+        mid = tk.decode_swiglu(h, L["gate"], L["up"], format=fmt)
+        part = tk_torch.decode_linear_partial(mid, L["down"], fmt)
+        d_sum = part if d_sum is None else d_sum + part
+    got = (d_sum + h.float()).to(xd.dtype)
+    g, w = host(got), host(want)
+    assert np.all(np.abs(g - w) <= np.abs(w) * 2.0 ** -6 + 2e-2)
+    assert np.mean(g == w) > 0.9
