@@ -233,6 +233,47 @@ def gemv_sweep(device, peak_gbs: float):
     return res
 
 
+def stack_sweep(device, world: int, rank: int, peak_gbs: float, layers: int = 80):
+    """Llama-3-70B-shaped decode projection stack (80 layers, hidden 8192, QKV 10240, O, gate/up
+    2 x 28672, down; NVFP4; attention = identity on V), tensor-parallel over `world` GPUs with an NCCL
+    all-reduce of fp32 partials after O and down.  Reports ms per full-stack step for batch 1 and 32."""
+    import torch.distributed as dist
+    from quixicore_metal_b200 import parallel
+    hidden, q, kv, inter, fmt = 8192, 8192, 1024, 28672, "nvfp4"
+    ql, kl, il = q // world, kv // world, inter // world
+    mk = lambda n, k, sd: synth_random_blocks(fmt, n, k, sd, device)
+    Ls = [{"qkv": mk(ql + 2 * kl, hidden, 7 * i + 1 + 1000 * rank), "o": mk(hidden, ql, 7 * i + 2 + 1000 * rank),
+           "gate": mk(il, hidden, 7 * i + 3 + 1000 * rank), "up": mk(il, hidden, 7 * i + 4 + 1000 * rank),
+           "down": mk(hidden, il, 7 * i + 5 + 1000 * rank)} for i in range(layers)]
+    stack = parallel.TPDecodeStack(Ls, fmt)
+    out = []
+    for M in (1, 32):
+        x = (torch.randn((M, hidden), device=device) * 0.05).bfloat16()
+        for _ in range(2):
+            stack.forward(x)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 3
+        e0.record()
+        for _ in range(iters):
+            stack.forward(x)
+        e1.record(); torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / iters], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms = float(ms.item())
+        wb = stack.weight_bytes()
+        out.append({"M": M, "layers": layers, "ms_per_step": round(ms, 4), "weight_bytes_per_gpu": int(wb),
+                    "gbs_per_gpu": round(wb / (ms * 1e-3) / 1e9, 1),
+                    "frac_of_measured_peak": round(wb / (ms * 1e-3) / 1e9 / peak_gbs, 4),
+                    "allreduces_per_step": 2 * layers if world > 1 else 0})
+    del stack, Ls
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -241,6 +282,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the secondary GEMV sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-stack", action="store_true", help="skip the 70B-shaped projection stack")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -328,6 +370,10 @@ def main():
     alg_bytes = shard_bytes + T_ROWS * K_HID * 2 + buf.numel() * 4
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
 
+    del shards, heads
+    torch.cuda.empty_cache()
+    stack = None if args.no_stack else stack_sweep(device, world, rank, peak_gbs)
+
     ms_per_step = total_ms / args.steps
     value = T_ROWS / (ms_per_step * 1e-3)
     e2e_value = T_ROWS / (e2e_ms / args.steps * 1e-3)
@@ -351,6 +397,8 @@ def main():
                      "kernel_ms": k_ms, "algorithmic_bytes": int(alg_bytes)},
         "clocks": clocks,
     }
+    if stack is not None:
+        line["stack"] = stack
     if world == 1 and not args.no_sweep:
         line["gemv"] = gemv_sweep(device, peak_gbs)
     if world == 1 and not args.no_cpu:

@@ -101,3 +101,214 @@ __device__ __forceinline__ void decode_span32(const uint8_t* __restrict__ row, i
 }
 
 }  // namespace qx
+
+// ------------------------------------------------------------------------------------------------
+// Word-based decoders: the same values as decode_span32, built from 32-bit loads and a few
+// logic / FMA instructions per weight instead of one byte load and one conversion per weight.
+// ------------------------------------------------------------------------------------------------
+namespace qx {
+
+// NW 32-bit words starting at byte address p (any alignment), assembled from the NW + 1 aligned
+// words that enclose them.  Aligned words that start at or beyond `limit` (the end of the tensor,
+// 4-byte aligned) are not read: the span of the last row may end right at the end of an allocation.
+template <int NW>
+__device__ __forceinline__ void load_words_any(const uint8_t* p, const uint8_t* limit, uint32_t (&r)[NW]) {
+  const uint32_t* base = reinterpret_cast<const uint32_t*>((uintptr_t)p & ~(uintptr_t)3);
+  const uint32_t* lim = reinterpret_cast<const uint32_t*>(limit);
+  const uint32_t sh = (uint32_t)((uintptr_t)p & 3) * 8u;
+  uint32_t prev = base < lim ? base[0] : 0u;
+#pragma unroll
+  for (int i = 0; i < NW; ++i) {
+    const uint32_t next = (base + i + 1) < lim ? base[i + 1] : 0u;
+    r[i] = __funnelshift_r(prev, next, sh);
+    prev = next;
+  }
+}
+// float(8388608 + byte k of w): the byte placed under the fp32 pattern of 2^23
+template <int K>
+__device__ __forceinline__ float magic_byte(uint32_t w) {
+  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | K));
+}
+__device__ __forceinline__ float2 f16x2_to_f32(uint32_t h) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+__device__ __forceinline__ uint32_t cvt_e2m1_pair(uint32_t byte_in_low_bits) {
+  uint32_t r;
+  asm("{ .reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0; }"
+      : "=r"(r) : "r"(byte_in_low_bits));
+  return r;
+}
+__device__ __forceinline__ uint32_t cvt_e4m3_pair(uint32_t two_bytes_in_low_bits) {
+  uint32_t r;
+  asm("{ .reg .b16 h0, h1;\n\t"
+      "mov.b32 {h0, h1}, %1;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, h0; }"
+      : "=r"(r) : "r"(two_bytes_in_low_bits));
+  return r;
+}
+
+// 16 e2m1 codes of 8 bytes in the block order "low nibbles first, then high nibbles"
+// (columns i and i + NB/... as the format defines) are handled by the callers; this converts the
+// two codes of one byte: .x = low nibble, .y = high nibble.
+__device__ __forceinline__ float2 e2m1_byte_to_f32(uint32_t w, int byte_index) {
+  return f16x2_to_f32(cvt_e2m1_pair(w >> (8 * byte_index)));
+}
+
+// The raw bytes of one 32-column span held in registers: load() can be issued one step ahead of
+// decode(), which hides the memory latency behind the previous span's arithmetic.
+// f16 pair -> bf16 pair scaled by `mult` (a bf16 pair holding scale * 2^112): moving the f16
+// exponent / mantissa bits down by three places reads, as bf16, as value * 2^-112 (zero and f16
+// subnormals included), and one bf16 multiply restores value * scale.  Exact whenever value * scale
+// has at most 8 significant bits and stays in the bf16 range.
+__device__ __forceinline__ uint32_t f16x2_to_bf16x2_scaled(uint32_t h, uint32_t mult) {
+  const uint32_t t = ((h >> 3) & 0x0FFF0FFFu) | (h & 0x80008000u);
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&t),
+                             *reinterpret_cast<const __nv_bfloat162*>(&mult));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// bf16 pair (s * 2^112, s * 2^112) for an e4m3 scale byte (this contract: 0x7F decodes to 480)
+__device__ __forceinline__ uint32_t e4m3_scale_mult(uint32_t sc) {
+  // e4m3 bits under the bf16 exponent read as s * 2^-120 (subnormal scales included);
+  // two exact multiplies (2^120, then 2^112) avoid an unrepresentable 2^232
+  uint32_t t = ((sc & 0x7Fu) << 4) | ((sc & 0x80u) << 8);
+  t |= t << 16;
+  const uint32_t k120 = 0x7B807B80u, k112 = 0x77807780u;
+  __nv_bfloat162 a = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&t), *reinterpret_cast<const __nv_bfloat162*>(&k120));
+  a = __hmul2(a, *reinterpret_cast<const __nv_bfloat162*>(&k112));
+  return *reinterpret_cast<uint32_t*>(&a);
+}
+
+template <int FMT> struct RawSpan {
+  static constexpr int NW = FMT == F_Q8_0 ? 9 : (FMT == F_MXFP8 ? 9 : 5);
+  uint32_t r[NW];
+  const uint8_t* row; int span;                              // q6_K decodes from memory directly
+
+  // limit = first byte after the packed tensor (must be 4-byte aligned)
+  __device__ __forceinline__ void load(const uint8_t* __restrict__ row_, int span_,
+                                       const uint8_t* __restrict__ limit) {
+    row = row_; span = span_;
+    if constexpr (FMT == F_Q8_0) load_words_any<9>(row_ + (size_t)span_ * 34, limit, r);
+    else if constexpr (FMT == F_MXFP8) load_words_any<9>(row_ + (size_t)span_ * 33, limit, r);
+    else if constexpr (FMT == F_Q4_0) load_words_any<5>(row_ + (size_t)span_ * 18, limit, r);
+    else if constexpr (FMT == F_MXFP4) load_words_any<5>(row_ + (size_t)span_ * 17, limit, r);
+    else if constexpr (FMT == F_NVFP4) load_words_any<5>(row_ + (size_t)span_ * 18, limit, r);
+  }
+
+  // One-term formats: the 32 weights as 16 bf16 pairs in column order, exact, without fp32.
+  // Returns false when the block scale is outside the range this shortcut covers (the caller
+  // then takes decode()).
+  __device__ __forceinline__ bool decode_bf16(uint32_t (&pk)[16]) const {
+    if constexpr (FMT == F_NVFP4) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t sc = h == 0 ? (r[0] & 0xFFu) : ((r[2] >> 8) & 0xFFu);
+        const uint32_t mult = e4m3_scale_mult(sc);
+        uint32_t c0, c1;
+        if (h == 0) { c0 = __funnelshift_r(r[0], r[1], 8); c1 = __funnelshift_r(r[1], r[2], 8); }
+        else { c0 = __funnelshift_r(r[2], r[3], 16); c1 = __funnelshift_r(r[3], r[4], 16); }
+        // byte i holds columns i (low nibble) and i + 8 (high nibble) of the block
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t v = f16x2_to_bf16x2_scaled(cvt_e2m1_pair((i < 4 ? c0 : c1) >> (8 * (i & 3))), mult);
+          lo[i] = v & 0xFFFFu; hi[i] = v >> 16;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          pk[8 * h + i] = lo[2 * i] | (lo[2 * i + 1] << 16);
+          pk[8 * h + 4 + i] = hi[2 * i] | (hi[2 * i + 1] << 16);
+        }
+      }
+      return true;
+    } else if constexpr (FMT == F_MXFP4) {
+      const uint32_t e = r[0] & 0xFFu;
+      if (e < 16u || e > 140u) return false;               // 2^(e-127) * 2^112 must be a normal bf16
+      uint32_t mult = (e + 112u - 127u + 127u) << 7;        // bf16 bits of 2^(e - 127 + 112)
+      mult |= mult << 16;
+      uint32_t c[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[i] = __funnelshift_r(r[i], r[i + 1], 8);
+      uint32_t lo[16], hi[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t v = f16x2_to_bf16x2_scaled(cvt_e2m1_pair(c[i >> 2] >> (8 * (i & 3))), mult);
+        lo[i] = v & 0xFFFFu; hi[i] = v >> 16;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        pk[i] = lo[2 * i] | (lo[2 * i + 1] << 16);
+        pk[8 + i] = hi[2 * i] | (hi[2 * i + 1] << 16);
+      }
+      return true;
+    } else {
+      return false;
+    }
+  }
+
+  __device__ __forceinline__ void decode(float (&w)[32]) const {
+    if constexpr (FMT == F_Q8_0) {
+      const float d = __half2float(__ushort_as_half((unsigned short)(r[0] & 0xFFFFu)));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int b = 2 + i;                                 // bytes 2..33, sign bit flipped: q + 128
+        const uint32_t word = r[b >> 2] ^ 0x80808080u;
+        float m;
+        if ((b & 3) == 0) m = magic_byte<0>(word);
+        else if ((b & 3) == 1) m = magic_byte<1>(word);
+        else if ((b & 3) == 2) m = magic_byte<2>(word);
+        else m = magic_byte<3>(word);
+        w[i] = (m - 8388736.0f) * d;                         // (2^23 + q + 128) - (2^23 + 128) = q, exact
+      }
+    } else if constexpr (FMT == F_Q4_0) {
+      const float d = __half2float(__ushort_as_half((unsigned short)(r[0] & 0xFFFFu)));
+      uint32_t c[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[i] = __funnelshift_r(r[i], r[i + 1], 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = c[i] & 0x0F0F0F0Fu, hi = (c[i] >> 4) & 0x0F0F0F0Fu;
+        w[4 * i + 0] = (magic_byte<0>(lo) - 8388616.0f) * d; w[4 * i + 1] = (magic_byte<1>(lo) - 8388616.0f) * d;
+        w[4 * i + 2] = (magic_byte<2>(lo) - 8388616.0f) * d; w[4 * i + 3] = (magic_byte<3>(lo) - 8388616.0f) * d;
+        w[16 + 4 * i + 0] = (magic_byte<0>(hi) - 8388616.0f) * d; w[16 + 4 * i + 1] = (magic_byte<1>(hi) - 8388616.0f) * d;
+        w[16 + 4 * i + 2] = (magic_byte<2>(hi) - 8388616.0f) * d; w[16 + 4 * i + 3] = (magic_byte<3>(hi) - 8388616.0f) * d;
+      }
+    } else if constexpr (FMT == F_MXFP4) {
+      const float s = e8m0_to_f32(r[0] & 0xFFu);
+      uint32_t c[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[i] = __funnelshift_r(r[i], r[i + 1], 8);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 v = e2m1_byte_to_f32(c[i >> 2], i & 3);
+        w[i] = s * v.x; w[i + 16] = s * v.y;
+      }
+    } else if constexpr (FMT == F_NVFP4) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                          // block h occupies bytes 9h .. 9h+8
+        const uint32_t sc = h == 0 ? (r[0] & 0xFFu) : ((r[2] >> 8) & 0xFFu);
+        const float s = e4m3_to_f32(sc);
+        uint32_t c0, c1;
+        if (h == 0) { c0 = __funnelshift_r(r[0], r[1], 8); c1 = __funnelshift_r(r[1], r[2], 8); }
+        else { c0 = __funnelshift_r(r[2], r[3], 16); c1 = __funnelshift_r(r[3], r[4], 16); }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 v = e2m1_byte_to_f32(i < 4 ? c0 : c1, i & 3);
+          w[16 * h + i] = s * v.x; w[16 * h + i + 8] = s * v.y;
+        }
+      }
+    } else if constexpr (FMT == F_MXFP8) {
+      const float s = e8m0_to_f32(r[0] & 0xFFu);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int b = 1 + i;
+        w[i] = s * e4m3_to_f32((r[b >> 2] >> (8 * (b & 3))) & 0xFFu);
+      }
+    } else {
+      decode_span32<FMT>(row, span, w);                      // q6_K: byte-wise form
+    }
+  }
+};
+
+}  // namespace qx

@@ -3,8 +3,8 @@
 // Shape of the problem: out[n, m] = sum_k W[n, k] * x[m, k] with W packed.  The weight rows are the
 // M-mode of the MMA (128 rows per CTA tile), the batch is the N-mode (16..128), so small batches
 // waste nothing ("swap-AB").  Per 64-column k-stage:
-//   * a producer thread streams raw packed rows into a shared-memory ring with cp.async.bulk;
-//   * 128 dequant threads (one weight row each) decode their 64 columns to fp32, split every weight
+//   * 256 dequant threads (a weight row and 32 columns each) read their packed bytes from global
+//     memory one stage ahead, decode them to fp32, split every weight
 //     into NTERMS bf16 terms whose sum is exactly the fp32 weight (1 term for nvfp4 / mxfp4 / mxfp8,
 //     whose weights are exact in bf16; 2 for q4_0; 3 for q8_0 / q6_K) and store each term as a
 //     K-major 128-byte-swizzled operand tile; they also copy the activation tile (bf16, K-major);
@@ -25,11 +25,10 @@ namespace qx {
 
 constexpr int MMA_BM = 128;          // weight rows per CTA tile
 constexpr int MMA_BK = 64;           // columns per MMA stage (128 bytes of bf16: one swizzle atom)
-constexpr int MMA_KR = 256;          // columns per raw-ring stage
-constexpr int MMA_A_STAGES = 2;
-constexpr int MMA_R_STAGES = 2;
-constexpr int MMA_DQ_WARPS = 8;       // dequant / epilogue warps: thread = (weight row, 32-column half)
-constexpr int MMA_THREADS = 320;     // warps 0-7 dequant/epilogue, warp 8 raw producer, warp 9 MMA
+constexpr int MMA_GROUP_WARPS = 8;    // one dequant group: thread = (weight row, 32-column half) of a stage
+constexpr int MMA_GROUPS = 2;         // groups alternate stages, which doubles the loads in flight
+constexpr int MMA_DQ_WARPS = MMA_GROUP_WARPS * MMA_GROUPS;
+constexpr int MMA_THREADS = (MMA_DQ_WARPS + 1) * 32;   // + the MMA issuer warp
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -95,16 +94,15 @@ template <> struct MmaTerms<F_Q6_K> { static constexpr int N = 3; };
 
 template <int FMT> struct MmaGeom {
   static constexpr int NTERMS = MmaTerms<FMT>::N;
-  static constexpr int CH = MMA_KR / block_k_of(FMT) * block_bytes_of(FMT);   // raw bytes per row and chunk
-  static constexpr int RPITCH = ((CH + 15) & ~15) + 32;
+  static constexpr int A_STAGES = NTERMS == 1 ? 6 : (NTERMS == 2 ? 4 : 3);   // operand ring depth
   static constexpr int A_STAGE = NTERMS * MMA_BM * 128;
   static constexpr int B_STAGE = 128 * 128;
-  static constexpr int OFF_B = MMA_A_STAGES * A_STAGE;
-  static constexpr int OFF_RAW = OFF_B + MMA_A_STAGES * B_STAGE;
-  static constexpr int OFF_BAR = OFF_RAW + MMA_R_STAGES * MMA_BM * RPITCH;
-  static constexpr int SMEM = OFF_BAR + 128 + 1024;   // + barriers / tmem slot + alignment slack
+  static constexpr int OFF_B = A_STAGES * A_STAGE;
+  static constexpr int OFF_BAR = OFF_B + A_STAGES * B_STAGE;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;   // + barriers / tmem slot + alignment slack
 };
 
+// Barrier slots: [0,8) a_full, [8,16) a_empty, 16 acc_full, 17 acc_empty.
 template <int FMT, typename T>
 __global__ void __launch_bounds__(MMA_THREADS, 1)
 gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ w,
@@ -113,29 +111,28 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
                int* __restrict__ err_flag) {
   using G = MmaGeom<FMT>;
   constexpr int NTERMS = G::NTERMS;
+  constexpr int STAGES = G::A_STAGES;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // barriers: [0,2) a_full, [2,4) a_empty, [4,6) raw_full, [6,8) raw_empty, 8 acc_full, 9 acc_empty
   const uint32_t bars = sbase + G::OFF_BAR;
   auto BAR = [&](int i) { return bars + 8u * (uint32_t)i; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + G::OFF_BAR + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BAR + 100);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + G::OFF_BAR + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BAR + 196);
 
   if (tid == 0) {
-    for (int s = 0; s < MMA_A_STAGES; ++s) { mbar_init(BAR(0 + s), MMA_DQ_WARPS); mbar_init(BAR(2 + s), 1); }
-    for (int s = 0; s < MMA_R_STAGES; ++s) { mbar_init(BAR(4 + s), MMA_BM); mbar_init(BAR(6 + s), MMA_DQ_WARPS); }
-    mbar_init(BAR(8), 1);
-    mbar_init(BAR(9), MMA_DQ_WARPS);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(BAR(s), MMA_GROUP_WARPS); mbar_init(BAR(8 + s), 1); }
+    mbar_init(BAR(16), 1);
+    mbar_init(BAR(17), MMA_DQ_WARPS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   int tmem_cols = 32;
   while (tmem_cols < BN) tmem_cols <<= 1;
-  if (warp == MMA_DQ_WARPS + 1) tmem_alloc(smem_u32((const void*)tmem_slot), (uint32_t)tmem_cols);
+  if (warp == MMA_DQ_WARPS) tmem_alloc(smem_u32((const void*)tmem_slot), (uint32_t)tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -144,8 +141,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
   const size_t row_bytes = (size_t)(K / block_k_of(FMT)) * block_bytes_of(FMT);
   const int ntiles = (N + MMA_BM - 1) / MMA_BM;
   const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-  const int nchunks = K / MMA_KR;                 // raw chunks per tile
-  constexpr int SPC = MMA_KR / MMA_BK;            // MMA stages per raw chunk
+  const int nst = K / MMA_BK;                     // MMA stages per tile
 
   auto wait_or_abort = [&](uint32_t bar, uint32_t parity) -> bool {
     if (*abort_flag) return false;
@@ -157,40 +153,17 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
   };
 
   if (warp == MMA_DQ_WARPS) {
-    // ---------------- raw producer: 4 row-chunks per lane and stage ----------------
-    int rc = 0;
-    for (int j = 0; j < my_tiles; ++j) {
-      const int row0 = ((int)blockIdx.x + j * (int)gridDim.x) * MMA_BM;
-      for (int c = 0; c < nchunks; ++c, ++rc) {
-        const int rs = rc % MMA_R_STAGES;
-        if (rc >= MMA_R_STAGES && !wait_or_abort(BAR(6 + rs), (uint32_t)((rc / MMA_R_STAGES - 1) & 1))) break;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int r = lane + 32 * q;
-          const int row = row0 + r;
-          if (row >= N) { mbar_arrive(BAR(4 + rs)); continue; }
-          const uintptr_t a = (uintptr_t)(w + (size_t)row * row_bytes + (size_t)c * G::CH);
-          const uintptr_t a0 = a & ~(uintptr_t)15;
-          const uint32_t bytes = (uint32_t)(((a + G::CH + 15) & ~(uintptr_t)15) - a0);
-          mbar_arrive_expect_tx(BAR(4 + rs), bytes);
-          bulk_g2s(sbase + G::OFF_RAW + (uint32_t)((rs * MMA_BM + r) * G::RPITCH), (const void*)a0, bytes, BAR(4 + rs));
-        }
-      }
-      if (*abort_flag) break;
-    }
-  } else if (warp == MMA_DQ_WARPS + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_bf16(BN);
       int it = 0;
       for (int j = 0; j < my_tiles; ++j) {
-        if (j > 0 && !wait_or_abort(BAR(9), (uint32_t)((j - 1) & 1))) break;
+        if (j > 0 && !wait_or_abort(BAR(17), (uint32_t)((j - 1) & 1))) break;
         tc_fence_after();
-        const int nst = nchunks * SPC;
         bool ok = true;
         for (int st = 0; st < nst; ++st, ++it) {
-          const int sa = it % MMA_A_STAGES;
-          if (!wait_or_abort(BAR(0 + sa), (uint32_t)((it / MMA_A_STAGES) & 1))) { ok = false; break; }
+          const int sa = it % STAGES;
+          if (!wait_or_abort(BAR(sa), (uint32_t)((it / STAGES) & 1))) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = sbase + (uint32_t)(sa * G::A_STAGE);
           const uint32_t b_base = sbase + (uint32_t)(G::OFF_B + sa * G::B_STAGE);
@@ -203,76 +176,90 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
               tc_mma_f16(tmem_base, ad, bd, idesc, (st | term | kk) != 0 ? 1u : 0u);
             }
           }
-          tc_commit(BAR(2 + sa));            // stage reusable once these MMAs have read it
+          tc_commit(BAR(8 + sa));            // stage reusable once these MMAs have read it
         }
         if (!ok) break;
-        tc_commit(BAR(8));                   // accumulator complete
+        tc_commit(BAR(16));                  // accumulator complete
       }
     }
   } else {
     // ------- dequant + epilogue: thread (r, hsp) owns 32 of the 64 stage columns of weight row r -------
-    const int r = tid & (MMA_BM - 1);        // 0..127
-    const int hsp = tid >> 7;                // which half of the stage columns
-    int it = 0, rc = 0;
+    // Weights come straight from global memory (each thread walks its own row: consecutive stages
+    // hit the same or the next 32-byte sector, so L1/L2 turn the strided reads into one pass over
+    // DRAM); the raw bytes of the next stage are fetched before the current one is decoded.
+    const int r = tid & (MMA_BM - 1);
+    const int hsp = (tid >> 7) & 1;
+    const int grp = tid >> 8;                  // this group handles the stages st with st % MMA_GROUPS == grp
+    const int gtid = tid & (MMA_GROUP_WARPS * 32 - 1);
+    int it0 = 0;                               // global stage counter at the start of the tile
     for (int j = 0; j < my_tiles; ++j) {
       const int row0 = ((int)blockIdx.x + j * (int)gridDim.x) * MMA_BM;
+      const int nrow = min(row0 + r, N - 1);                      // rows past the end re-read the last row
+      const uint8_t* wrow = w + (size_t)nrow * row_bytes;
+      const uint8_t* wend = w + (size_t)N * row_bytes;            // K % 256 == 0 makes this 8-byte aligned
+      RawSpan<FMT> cur, nxt;
+      if (grp < nst) cur.load(wrow, grp * 2 + hsp, wend);
       bool ok = true;
-      for (int c = 0; c < nchunks && ok; ++c, ++rc) {
-        const int rs = rc % MMA_R_STAGES;
-        if (!wait_or_abort(BAR(4 + rs), (uint32_t)((rc / MMA_R_STAGES) & 1))) { ok = false; break; }
-        const uintptr_t a = (uintptr_t)(w + (size_t)(row0 + r) * row_bytes + (size_t)c * G::CH);
-        const uint8_t* raw = smem + G::OFF_RAW + (size_t)(rs * MMA_BM + r) * G::RPITCH + (a & 15);
-#pragma unroll 1
-        for (int q = 0; q < SPC; ++q, ++it) {
-          const int sa = it % MMA_A_STAGES;
-          if (it >= MMA_A_STAGES && !wait_or_abort(BAR(2 + sa), (uint32_t)((it / MMA_A_STAGES - 1) & 1))) { ok = false; break; }
-          uint8_t* a_stage = smem + (size_t)sa * G::A_STAGE;
-          {
-            float wv[32];
-            decode_span32<FMT>(raw, q * 2 + hsp, wv);
-            uint32_t pk[NTERMS][16];
+      for (int st = grp; st < nst; st += MMA_GROUPS) {
+        const int it = it0 + st;
+        const int sa = it % STAGES;
+        if (st + MMA_GROUPS < nst) nxt.load(wrow, (st + MMA_GROUPS) * 2 + hsp, wend);
+        // activation tile: BN rows x 64 columns (rows beyond the batch are zero); issued early
+        const int kcol = st * MMA_BK;
+        uint4 bv[4];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float v0 = wv[2 * i], v1 = wv[2 * i + 1];
-#pragma unroll
-              for (int term = 0; term < NTERMS; ++term) {
-                const __nv_bfloat16 b0 = __float2bfloat16_rn(v0), b1 = __float2bfloat16_rn(v1);
-                pk[term][i] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
-                v0 -= __bfloat162float(b0); v1 -= __bfloat162float(b1);
-              }
-            }
-#pragma unroll
-            for (int term = 0; term < NTERMS; ++term)
-#pragma unroll
-              for (int cc = 0; cc < 4; ++cc)
-                *reinterpret_cast<uint4*>(a_stage + term * MMA_BM * 128 + sw128_offset(r, hsp * 4 + cc)) =
-                    make_uint4(pk[term][4 * cc], pk[term][4 * cc + 1], pk[term][4 * cc + 2], pk[term][4 * cc + 3]);
-          }
-          // activation tile: BN rows x 64 columns (rows beyond the batch are zero)
-          uint8_t* b_stage = smem + G::OFF_B + (size_t)sa * G::B_STAGE;
-          const int kcol = (c * SPC + q) * MMA_BK;
-          for (int idx = tid; idx < BN * 8; idx += MMA_DQ_WARPS * 32) {
-            const int m = idx >> 3, cc = idx & 7;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (m < M) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + kcol + cc * 8));
-            *reinterpret_cast<uint4*>(b_stage + sw128_offset(m, cc)) = v;
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(BAR(0 + sa));
+        for (int u = 0; u < 4; ++u) {
+          const int idx = gtid + u * MMA_GROUP_WARPS * 32;
+          const int m = idx >> 3, cc = idx & 7;
+          bv[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (idx < BN * 8 && m < M) bv[u] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + kcol + cc * 8));
         }
+        uint32_t pk[NTERMS][16];
+        bool direct = false;
+        if constexpr (NTERMS == 1) direct = cur.decode_bf16(pk[0]);
+        if (!direct) {
+          float wv[32];
+          cur.decode(wv);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float v0 = wv[2 * i], v1 = wv[2 * i + 1];
+#pragma unroll
+            for (int term = 0; term < NTERMS; ++term) {
+              const __nv_bfloat16 b0 = __float2bfloat16_rn(v0), b1 = __float2bfloat16_rn(v1);
+              pk[term][i] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
+              v0 -= __bfloat162float(b0); v1 -= __bfloat162float(b1);
+            }
+          }
+        }
+        if (it >= STAGES && !wait_or_abort(BAR(8 + sa), (uint32_t)((it / STAGES - 1) & 1))) { ok = false; break; }
+        uint8_t* a_stage = smem + (size_t)sa * G::A_STAGE;
+        uint8_t* b_stage = smem + G::OFF_B + (size_t)sa * G::B_STAGE;
+#pragma unroll
+        for (int term = 0; term < NTERMS; ++term)
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+            *reinterpret_cast<uint4*>(a_stage + term * MMA_BM * 128 + sw128_offset(r, hsp * 4 + cc)) =
+                make_uint4(pk[term][4 * cc], pk[term][4 * cc + 1], pk[term][4 * cc + 2], pk[term][4 * cc + 3]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = gtid + u * MMA_GROUP_WARPS * 32;
+          if (idx < BN * 8) *reinterpret_cast<uint4*>(b_stage + sw128_offset(idx >> 3, idx & 7)) = bv[u];
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(BAR(6 + rs));
+        if (lane == 0) mbar_arrive(BAR(sa));
+        cur = nxt;
       }
+      it0 += nst;
       if (!ok) break;
       // ---- epilogue ----
-      if (!wait_or_abort(BAR(8), (uint32_t)(j & 1))) break;
+      if (!wait_or_abort(BAR(16), (uint32_t)(j & 1))) break;
       tc_fence_after();
       const int n = row0 + r;
-      const float bv = (use_bias && n < N) ? to_f32<T>(bias[n]) : 0.f;
-      // warp w may touch TMEM lanes 32*(w % 4)..+31: warps 0-3 take the even 16-column chunks,
-      // warps 4-7 the odd ones
-      for (int cb = hsp; cb < BN / 16; cb += 2) {
+      const float bvv = (use_bias && n < N) ? to_f32<T>(bias[n]) : 0.f;
+      // warp w may touch TMEM lanes 32*(w % 4)..+31: the four warps that share a lane quarter
+      // take every fourth 16-column chunk each
+      for (int cb = warp >> 2; cb < BN / 16; cb += MMA_DQ_WARPS / 4) {
         float v[16];
         tmem_ld16(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(cb * 16), v);
 #pragma unroll
@@ -280,7 +267,7 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
           const int m = cb * 16 + i;
           if (m < M && n < N) {
             const size_t o = (size_t)m * N + n;
-            float val = apply_act(v[i] + bv, activation);
+            float val = apply_act(v[i] + bvv, activation);
             if (use_residual) val += to_f32<T>(residual[o]);
             y[o] = from_f32<T>(val);
           }
@@ -288,15 +275,14 @@ gemm_tc_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(9));
+      if (lane == 0) mbar_arrive(BAR(17));
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_DQ_WARPS + 1) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
+  if (warp == MMA_DQ_WARPS) tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
 }
-
 
 template <int FMT, typename T>
 static bool launch_tc_t(cudaStream_t st, const GemvArgs& a, int* err) {
@@ -325,7 +311,7 @@ static bool launch_tc_t(cudaStream_t st, const GemvArgs& a, int* err) {
 bool tc_path_ok(const GemvArgs& a) {
   if (a.dtype != QX_DTYPE_BF16 || a.M <= 16) return false;
   if (a.w1 && (((uintptr_t)a.w1 & 15) != 0)) return false;
-  if (a.K % MMA_KR != 0 || ((uintptr_t)a.x & 15) != 0 || ((uintptr_t)a.w0 & 15) != 0) return false;
+  if (a.K % 256 != 0 || ((uintptr_t)a.x & 15) != 0 || ((uintptr_t)a.w0 & 15) != 0) return false;
   return true;
 }
 

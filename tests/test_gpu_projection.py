@@ -266,3 +266,19 @@ def test_row_parallel_partials_sum_to_full_projection(fmt, M):
         total = part if total is None else total + part
     ref = O.matmul_f64(x, O.dequantize(fmt, Wq))
     np.testing.assert_allclose(host(total), ref, rtol=2e-5, atol=2e-5)
+
+
+def test_large_batch_weight_ending_at_an_allocation_boundary():
+    """A packed tensor of exactly 9 x 2 MiB fills its allocator segment to the last byte: no load
+    of the batch > 16 path may touch anything beyond the tensor."""
+    fmt, M, K, N = "nvfp4", 32, 8192, 4096
+    Wq = O.random_packed(fmt, N, K, 3)
+    assert Wq.nbytes % (2 << 20) == 0
+    rng = np.random.default_rng(1)
+    x = rounded(rng.standard_normal((M, K)), "bf16")
+    torch.cuda.empty_cache()
+    wd = dev(Wq)
+    got = host(tk.decode_linear_epilogue(dev(x, "bf16"), wd, None, None, format=fmt))
+    rows = np.r_[0:8, N - 136:N]                      # first rows and the whole last tile
+    ref = O.decode_linear_epilogue(x, Wq[rows], fmt, None, None, 0, "bf16")
+    assert_close_dtype(got[:, rows], ref, "bf16", scale=float(np.abs(ref).max()))
