@@ -23,6 +23,9 @@ import sys
 import threading
 import time
 
+# keep stdout to the one JSON line: NCCL's banner / debug output goes to stderr
+os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+
 import numpy as np
 import torch
 

@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(256, 1)
 lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rowscale,
                   const uint8_t* __restrict__ wq, const float* __restrict__ bias,
                   float* __restrict__ part_val, int32_t* __restrict__ part_id,
-                  float* __restrict__ part_lse, int T_pass, int t_base, int V, int K,
+                  float* __restrict__ part_lse, int T_total, int tokens_per_group, int V, int K,
                   long long vocab_offset, long long tiles_stride, int mode, int topk, float invtemp,
                   uint32_t seed, int* __restrict__ err_flag) {
   using F = StreamFmt<FMT>;
@@ -205,6 +205,10 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  // blockIdx.y picks the group of hidden rows this CTA serves (all groups stream the same weights:
+  // used when there are fewer vocabulary tiles than SMs, e.g. on a small vocabulary shard)
+  const int t_base = (int)blockIdx.y * tokens_per_group;
+  const int T_pass = min(tokens_per_group, T_total - t_base);
 
   uint8_t* ring = smem_raw + (size_t)warp * WS::WARP_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)8 * WS::WARP_BYTES) + warp * C::STAGES;
@@ -323,7 +327,7 @@ static bool lmh_stream_ok(const LmHeadArgs& a) {
 template <int FMT, int NT>
 static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __half* x16,
                                  const float* rowscale, float* pv, int32_t* pi, float* pl,
-                                 int64_t tiles_stride, int t_base, int t_pass, int* err) {
+                                 int64_t tiles_stride, int* err) {
   using C = LmhCfg<FMT>;
   using WS = WarpStream<FMT, C::KC, 32, C::STAGES>;
   const size_t smem = (size_t)8 * WS::WARP_BYTES + (size_t)8 * C::STAGES * 8 +
@@ -331,8 +335,10 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   const int blocks = real_tiles < sm_count() ? real_tiles : sm_count();
-  lmh_stream_kernel<FMT, NT><<<blocks, 256, smem, st>>>(
-      x16, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, t_pass, t_base, (int)a.V, (int)a.K,
+  const int tpg = NT * 8;
+  dim3 grid(blocks, (unsigned)((a.T + tpg - 1) / tpg));
+  lmh_stream_kernel<FMT, NT><<<grid, 256, smem, st>>>(
+      x16, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
       (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
   note_launch();
 }
@@ -350,13 +356,16 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   float* rowscale = (float*)((char*)scratch + x16_bytes);
   launch_prep_activations(st, a.h, a.dtype, x16, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM);
   note_launch();
-  for (int t_base = 0; t_base < a.T; t_base += 64) {
-    const int t_pass = (int)((a.T - t_base) < 64 ? (a.T - t_base) : 64);
-    if (t_pass <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
-    else if (t_pass <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
-    else if (t_pass <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
-    else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, t_base, t_pass, err);
-  }
+  // hidden rows per CTA: 64 when there are enough vocabulary tiles to fill the GPU; fewer rows
+  // per CTA (more CTAs, each re-reading the weights from L2) when the vocabulary shard is small
+  const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
+  int tpg = 64;
+  while (tpg > 8 && (long long)real_tiles * ((a.T + tpg - 1) / tpg) < sm_count() && a.T > tpg / 2) tpg >>= 1;
+  while (tpg > 8 && a.T <= tpg / 2) tpg >>= 1;
+  if (tpg <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+  else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+  else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+  else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
   cudaFreeAsync(scratch, st);
   return true;
 }
