@@ -9,6 +9,7 @@
 // accumulators in a fixed order (deterministic) and warp 0 of the group applies the row scale,
 // bias / activation / residual and stores.  KS > 1 keeps every SM busy when there are few rows.
 #include <cstdlib>
+#include <mutex>
 
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
@@ -97,6 +98,51 @@ void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __h
     prep_activations_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, x16, rowscale, K, perm);
   else
     prep_activations_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, x16, rowscale, K, perm);
+}
+
+// ---- scratch for the prepared activations -----------------------------------------------------------
+// Calls on one stream are ordered, so a buffer tied to (device, stream) can be reused by every call
+// on that stream without synchronisation.  Up to 16 streams get such a buffer (grown on demand,
+// kept until process exit); further streams fall back to stream-ordered allocation per call.
+struct ScratchSlot { int dev; cudaStream_t st; void* ptr; size_t bytes; };
+static ScratchSlot g_scratch[16] = {};
+static std::mutex g_scratch_mu;
+
+void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free) {
+  *must_free = false;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(st, &cap);
+  if (cap == cudaStreamCaptureStatusNone) {
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    ScratchSlot* free_slot = nullptr;
+    for (auto& s : g_scratch) {
+      if (s.ptr && s.dev == dev && s.st == st) {
+        if (s.bytes >= bytes) return s.ptr;
+        // grow (rare): earlier work of this stream may still read the old buffer
+        cudaStreamSynchronize(st);
+        cudaFree(s.ptr);
+        s.ptr = nullptr;
+        free_slot = &s;
+        break;
+      }
+      if (!s.ptr && !free_slot) free_slot = &s;
+    }
+    if (free_slot) {
+      void* p = nullptr;
+      const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+      if (cudaMalloc(&p, want) == cudaSuccess) {
+        *free_slot = ScratchSlot{dev, st, p, want};
+        return p;
+      }
+      cudaGetLastError();
+    }
+  }
+  void* p = nullptr;
+  if (cudaMallocAsync(&p, bytes, st) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  *must_free = true;
+  return p;
 }
 
 constexpr int STREAM_STAGES = 2;      // per-warp ring depth; latency is hidden by the number of warps
@@ -288,21 +334,26 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   int blocks = (ntiles + groups - 1) / groups;
   if (blocks > sms) blocks = sms;
   const size_t smem = stream_smem_bytes<FMT, NT, DUAL>(nwarps, 1 << ks_log2);
-  if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, NT, DUAL, T>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
+  static bool attr_set[64] = {};                    // per instantiation and device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return false;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, NT, DUAL, T>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    attr_set[dev] = true;
   }
   int* err = device_error_flag();
   if (!err) return false;
 
   // stream-ordered scratch for the prepared activations
   const size_t x16_bytes = ((size_t)a.M * a.K * 2 + 255) & ~(size_t)255;
-  void* scratch = nullptr;
-  if (cudaMallocAsync(&scratch, x16_bytes + (size_t)a.M * 4, st) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
-  }
+  bool must_free = false;
+  void* scratch = stream_scratch(st, x16_bytes + (size_t)a.M * 4, &must_free);
+  if (!scratch) return false;
   __half* x16 = (__half*)scratch;
   float* rowscale = (float*)((char*)scratch + x16_bytes);
   launch_prep_activations(st, a.x, a.dtype, x16, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM);
@@ -310,7 +361,7 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
       x16, rowscale, (const uint8_t*)a.w0, (const uint8_t*)a.w1, (const T*)a.bias0,
       (const T*)a.bias1, (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
       a.use_bias, a.use_residual, ks_log2, err);
-  cudaFreeAsync(scratch, st);
+  if (must_free) cudaFreeAsync(scratch, st);
   note_launch(2);
   return true;
 }

@@ -32,6 +32,9 @@ bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a);
 int read_device_error_flag();
 // Device address of that flag on the current device (nullptr if it cannot be resolved).
 int* device_error_flag();
+// Device scratch of at least `bytes` for work enqueued on `st` (see qx_gemv_stream.cu); when
+// *must_free is set the caller releases it with cudaFreeAsync on the same stream.
+void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free);
 // Row-scaled f16 copy of (M,K) bf16 / f16 activations in the column order `perm` of the decoders.
 // silu(gate + gb) * (up + ub) over fp32 (M,N) projections -> T (M,N)
 void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, const void* gb,

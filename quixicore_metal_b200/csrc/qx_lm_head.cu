@@ -332,7 +332,13 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   using WS = WarpStream<FMT, C::KC, 32, C::STAGES>;
   const size_t smem = (size_t)8 * WS::WARP_BYTES + (size_t)8 * C::STAGES * 8 +
                       (size_t)LMH_TOK_CHUNK * LMH_LOGIT_PITCH * 4;
-  cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    attr_set[dev] = true;
+  }
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   const int blocks = real_tiles < sm_count() ? real_tiles : sm_count();
   const int tpg = NT * 8;
@@ -350,8 +356,9 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   int* err = device_error_flag();
   if (!err) return false;
   const size_t x16_bytes = ((size_t)a.T * a.K * 2 + 255) & ~(size_t)255;
-  void* scratch = nullptr;
-  if (cudaMallocAsync(&scratch, x16_bytes + (size_t)a.T * 4, st) != cudaSuccess) { cudaGetLastError(); return false; }
+  bool must_free = false;
+  void* scratch = stream_scratch(st, x16_bytes + (size_t)a.T * 4, &must_free);
+  if (!scratch) return false;
   __half* x16 = (__half*)scratch;
   float* rowscale = (float*)((char*)scratch + x16_bytes);
   launch_prep_activations(st, a.h, a.dtype, x16, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM);
@@ -366,7 +373,7 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
   else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
   else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-  cudaFreeAsync(scratch, st);
+  if (must_free) cudaFreeAsync(scratch, st);
   return true;
 }
 
