@@ -282,3 +282,28 @@ def test_large_batch_weight_ending_at_an_allocation_boundary():
     rows = np.r_[0:8, N - 136:N]                      # first rows and the whole last tile
     ref = O.decode_linear_epilogue(x, Wq[rows], fmt, None, None, 0, "bf16")
     assert_close_dtype(got[:, rows], ref, "bf16", scale=float(np.abs(ref).max()))
+
+
+def test_wide_dynamic_range_activations():
+    """The batch <= 16 path converts activations to row-scaled f16.  Elements more than 2^28 below
+    the row maximum lose bits there; their contribution is below the resolution of an fp32
+    accumulator anyway, so the result must still match the fp64 oracle to fp32-noise level
+    (measured against the magnitude of the largest term)."""
+    fmt, M, K, N = "q8_0", 4, 1024, 64
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    x[0, ::7] *= 1e-12           # far below the row maximum
+    x[1, 5] = 3.0e30             # one huge element
+    x[2, :] *= 1e-30             # a uniformly tiny row
+    x[3, ::3] = 0.0
+    x = rounded(x, "bf16")
+    Wq = O.synth_pack(fmt, (0.02 * rng.standard_normal((N, K))).astype(np.float32))
+    got = host(tk_torch_partial(x, Wq, fmt))
+    ref = (x.astype(np.float64) @ O.dequantize(fmt, Wq).astype(np.float64).T)
+    scale = (np.abs(x).astype(np.float64) @ np.abs(O.dequantize(fmt, Wq)).astype(np.float64).T)
+    assert np.all(np.abs(got - ref) <= 4e-6 * scale + 1e-37)
+
+
+def tk_torch_partial(x, Wq, fmt):
+    from quixicore_metal_b200 import tk_torch
+    return tk_torch.decode_linear_partial(dev(x, "bf16"), dev(Wq), fmt)
