@@ -190,8 +190,10 @@ template <> struct LmhCfg<F_MXFP8> { static constexpr int KC = 128, STAGES = 2; 
 constexpr int LMH_LOGIT_PITCH = 257;
 constexpr int LMH_TOK_CHUNK = 16;
 
-template <int FMT, int NT>
-__global__ void __launch_bounds__(256, 1)
+// WROWS = vocabulary rows per warp: 32 (8 warps, two m-tiles share every activation fragment) or
+// 16 (16 warps: more loads in flight; used for the large hidden-row counts).
+template <int FMT, int NT, int WROWS>
+__global__ void __launch_bounds__(256 / WROWS * 32, 1)
 lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rowscale,
                   const uint8_t* __restrict__ wq, const float* __restrict__ bias,
                   float* __restrict__ part_val, int32_t* __restrict__ part_id,
@@ -200,7 +202,9 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
                   uint32_t seed, int* __restrict__ err_flag) {
   using F = StreamFmt<FMT>;
   using C = LmhCfg<FMT>;
-  using WS = WarpStream<FMT, C::KC, 32, C::STAGES>;
+  constexpr int NW = 256 / WROWS;             // warps per CTA
+  constexpr int NSETS = WROWS / 16;
+  using WS = WarpStream<FMT, C::KC, WROWS, C::STAGES>;
   using GP = GroupProc<FMT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -211,13 +215,13 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
   const int T_pass = min(tokens_per_group, T_total - t_base);
 
   uint8_t* ring = smem_raw + (size_t)warp * WS::WARP_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)8 * WS::WARP_BYTES) + warp * C::STAGES;
-  float* logit = reinterpret_cast<float*>(smem_raw + (size_t)8 * WS::WARP_BYTES + (size_t)8 * C::STAGES * 8);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NW * WS::WARP_BYTES) + warp * C::STAGES;
+  float* logit = reinterpret_cast<float*>(smem_raw + (size_t)NW * WS::WARP_BYTES + (size_t)NW * C::STAGES * 8);
 
   const size_t row_bytes = (size_t)(K / F::BK) * F::BB;
   WS ws;
   ws.init(smem_u32(ring), smem_u32(bars), wq, wq + 16 * row_bytes, V, K, lane, err_flag);
-  ws.N1 = V - 16;                                  // the upper 16 rows come from the same matrix
+  ws.N1 = V - 16;                                  // rows 16..31 of a warp come from the same matrix
 
   const int real_tiles = (V + LMH_TILE - 1) / LMH_TILE;
   const int my_tiles = (int)blockIdx.x < real_tiles ? (real_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -230,18 +234,18 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
     const int m = nt * 8 + g;
     xr[nt] = m < T_pass ? x16 + (size_t)(t_base + m) * K : nullptr;
   }
-  auto step_row0 = [&](int i) { return ((int)blockIdx.x + (i / nch) * (int)gridDim.x) * LMH_TILE + warp * 32; };
+  auto step_row0 = [&](int i) { return ((int)blockIdx.x + (i / nch) * (int)gridDim.x) * LMH_TILE + warp * WROWS; };
 
 #pragma unroll
   for (int p = 0; p < C::STAGES - 1; ++p)
     if (p < steps) ws.issue(p, step_row0(p), p % nch);
 
-  float acc[2][NT][4];
+  float acc[NSETS][NT][4];
   for (int j = 0; j < my_tiles; ++j) {
     const int tile = (int)blockIdx.x + j * (int)gridDim.x;
-    const int row0 = tile * LMH_TILE + warp * 32;
+    const int row0 = tile * LMH_TILE + warp * WROWS;
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
+    for (int a = 0; a < NSETS; ++a)
 #pragma unroll
       for (int b = 0; b < NT; ++b)
 #pragma unroll
@@ -255,21 +259,33 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
       const bool ready = ws.wait(stage, (uint32_t)((i / C::STAGES) & 1));
       const int col_base = c * C::KC;
       const int ngroups = ready ? min(C::KC, K - col_base) / F::GROUP : 0;
-      uint32_t s[4];
+      uint32_t s[2 * NSETS];
       s[0] = ws.slot_addr(stage, g, row0, c);
       s[1] = ws.slot_addr(stage, g + 8, row0, c);
-      s[2] = ws.slot_addr(stage, 16 + g, row0, c);
-      s[3] = ws.slot_addr(stage, 24 + g, row0, c);
+      if constexpr (NSETS == 2) {
+        s[2] = ws.slot_addr(stage, 16 + g, row0, c);
+        s[3] = ws.slot_addr(stage, 24 + g, row0, c);
+      }
       constexpr uint32_t GROUP_BYTES = F::GROUP / F::BK * F::BB;
-      constexpr bool PRE = NT <= 2;                 // prefetch activations one group ahead
-      typename GP::template BFrag<NT> bcur, bnext;
-      if (PRE && ngroups > 0) GP::template load_b<NT>(xr, col_base, t, bcur);
-      for (int gi = 0; gi < ngroups; ++gi) {
-        if (PRE && gi + 1 < ngroups) GP::template load_b<NT>(xr, col_base + (gi + 1) * F::GROUP, t, bnext);
-        GP::template run<2, NT, PRE>(s, t, bcur, xr, col_base + gi * F::GROUP, acc);
-        if (PRE) bcur = bnext;
+      if constexpr (NT > 2 && GP::PIPED) {
+        uint4 bcar[NT];                              // fragments of the next unit, fetched one unit ahead
+        if (ngroups > 0) GP::template load_first<NT>(xr, col_base, t, bcar);
+        for (int gi = 0; gi < ngroups; ++gi) {
+          GP::template piped<NSETS, NT, 0>(s, t, xr, col_base + gi * F::GROUP, gi + 1 < ngroups, bcar, acc);
 #pragma unroll
-        for (int r = 0; r < 4; ++r) s[r] += GROUP_BYTES;
+          for (int r = 0; r < 2 * NSETS; ++r) s[r] += GROUP_BYTES;
+        }
+      } else {
+        constexpr bool PRE = NT <= 2;               // prefetch activations one group ahead
+        typename GP::template BFrag<NT> bcur, bnext;
+        if (PRE && ngroups > 0) GP::template load_b<NT>(xr, col_base, t, bcur);
+        for (int gi = 0; gi < ngroups; ++gi) {
+          if (PRE && gi + 1 < ngroups) GP::template load_b<NT>(xr, col_base + (gi + 1) * F::GROUP, t, bnext);
+          GP::template run<NSETS, NT, PRE>(s, t, bcur, xr, col_base + gi * F::GROUP, acc);
+          if (PRE) bcur = bnext;
+#pragma unroll
+          for (int r = 0; r < 2 * NSETS; ++r) s[r] += GROUP_BYTES;
+        }
       }
       __syncwarp();
     }
@@ -285,20 +301,19 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
         const int nt = 2 * tc + h;
         if (nt < NT) {
 #pragma unroll
-          for (int set = 0; set < 2; ++set)
+          for (int set = 0; set < NSETS; ++set)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int ml = h * 8 + 2 * t + (e & 1);
               const int m = nt * 8 + 2 * t + (e & 1);
               const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
-              logit[ml * LMH_LOGIT_PITCH + warp * 32 + set * 16 + g + (e >> 1) * 8] = acc[set][nt][e] * rs;
+              logit[ml * LMH_LOGIT_PITCH + warp * WROWS + set * 16 + g + (e >> 1) * 8] = acc[set][nt][e] * rs;
             }
         }
       }
       __syncthreads();
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {                 // warp w reduces chunk rows w and w + 8
-        const int ml = warp + 8 * q;
+      for (int ml = warp; ml < LMH_TOK_CHUNK; ml += NW) {   // each warp reduces some of the 16 rows
         const int m = tc * LMH_TOK_CHUNK + ml;
         if (m < T_pass)
           lmh_select_token(logit + ml * LMH_LOGIT_PITCH, nvalid, v0, vocab_offset, bias, t_base + m,
@@ -310,7 +325,7 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
 
   // padding tiles of a short shard carry absent partials
   for (long long tile = real_tiles + blockIdx.x; tile < tiles_stride; tile += gridDim.x) {
-    for (int m = warp; m < T_pass; m += 8)
+    for (int m = warp; m < T_pass; m += NW)
       lmh_select_token(logit, 0, 0, vocab_offset, nullptr, t_base + m, (int)tile, tiles_stride, mode,
                        topk, invtemp, seed, part_val, part_id, part_lse, lane);
   }
@@ -329,21 +344,23 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
                                  const float* rowscale, float* pv, int32_t* pi, float* pl,
                                  int64_t tiles_stride, int* err) {
   using C = LmhCfg<FMT>;
-  using WS = WarpStream<FMT, C::KC, 32, C::STAGES>;
-  const size_t smem = (size_t)8 * WS::WARP_BYTES + (size_t)8 * C::STAGES * 8 +
+  constexpr int WROWS = NT >= 4 ? 16 : 32;
+  constexpr int NW = 256 / WROWS;
+  using WS = WarpStream<FMT, C::KC, WROWS, C::STAGES>;
+  const size_t smem = (size_t)NW * WS::WARP_BYTES + (size_t)NW * C::STAGES * 8 +
                       (size_t)LMH_TOK_CHUNK * LMH_LOGIT_PITCH * 4;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT, WROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr_set[dev] = true;
   }
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   const int blocks = real_tiles < sm_count() ? real_tiles : sm_count();
   const int tpg = NT * 8;
   dim3 grid(blocks, (unsigned)((a.T + tpg - 1) / tpg));
-  lmh_stream_kernel<FMT, NT><<<grid, 256, smem, st>>>(
+  lmh_stream_kernel<FMT, NT, WROWS><<<grid, NW * 32, smem, st>>>(
       x16, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
       (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
   note_launch();

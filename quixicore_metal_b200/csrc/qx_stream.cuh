@@ -334,6 +334,7 @@ __device__ __forceinline__ uint4 ldg_or_zero(const __half* row, int off) {
 template <int FMT> struct GroupProc {
   using F = StreamFmt<FMT>;
   static constexpr int UNITS = F::GROUP / 32;
+  static constexpr bool PIPED = true;       // has the unit-pipelined form for large batches
   template <int NT> struct BFrag { uint4 v[UNITS][NT]; };
   template <int NT>
   __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int t,
@@ -367,6 +368,32 @@ template <int FMT> struct GroupProc {
     if constexpr (UNITS > 2) one<NSETS, NT, PRE, 2>(s, t, b, xr, col, acc);
     if constexpr (UNITS > 3) one<NSETS, NT, PRE, 3>(s, t, b, xr, col, acc);
   }
+  // Large batches: the activation fragments of one unit (NT x 16 bytes) are fetched one unit ahead.
+  // `carry` holds the fragments of this group's first unit on entry and those of the next group's
+  // first unit on exit (when there is a next group).
+  template <int NSETS, int NT, int J>
+  __device__ __forceinline__ static void piped(const uint32_t (&s)[2 * NSETS], int t,
+                                               const __half* const (&xr)[NT], int col, bool has_next,
+                                               uint4 (&cur)[NT], float (&acc)[NSETS][NT][4]) {
+    uint4 nxt[NT];
+    if constexpr (J + 1 < UNITS) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) nxt[nt] = ldg_or_zero(xr[nt], col + 32 * (J + 1) + 8 * t);
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) nxt[nt] = has_next ? ldg_or_zero(xr[nt], col + F::GROUP + 8 * t) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    unit32<FMT, J, NSETS, NT>(s, (uint32_t)(J * F::BB), t, cur, acc);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) cur[nt] = nxt[nt];
+    if constexpr (J + 1 < UNITS) piped<NSETS, NT, J + 1>(s, t, xr, col, has_next, cur, acc);
+  }
+  template <int NT>
+  __device__ __forceinline__ static void load_first(const __half* const (&xr)[NT], int col, int t,
+                                                    uint4 (&cur)[NT]) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) cur[nt] = ldg_or_zero(xr[nt], col + 8 * t);
+  }
 };
 
 // nvfp4: a group is four 16-column blocks; thread t owns block t of the group outright (9 bytes),
@@ -374,6 +401,7 @@ template <int FMT> struct GroupProc {
 // byte pair (2m, 2m+1) to MMA m; the MMAs accumulate straight into acc.
 template <> struct GroupProc<F_NVFP4> {
   using F = StreamFmt<F_NVFP4>;
+  static constexpr bool PIPED = false;
   __device__ __forceinline__ static void block(uint32_t s, int t, uint32_t (&a)[4][2]) {
     const uint32_t p = s + (uint32_t)(9 * t & ~3);
     const uint32_t sh = 8u * (uint32_t)t;                 // (9t mod 4) bytes
@@ -425,6 +453,7 @@ template <> struct GroupProc<F_NVFP4> {
 // OR-ed under the f16 exponent of 1024 as 1024+c or 1024+16c; sub-scale * d is applied in fp32.
 template <> struct GroupProc<F_Q6_K> {
   using F = StreamFmt<F_Q6_K>;
+  static constexpr bool PIPED = false;
   template <int ODD>
   __device__ __forceinline__ static uint32_t ldw(uint32_t p) {    // p is 4-aligned iff !ODD
     if constexpr (ODD) return __funnelshift_r(lds32(p - 2), lds32(p + 2), 16);
