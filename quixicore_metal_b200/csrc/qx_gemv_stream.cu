@@ -42,12 +42,26 @@ int read_device_error_flag() {
 // whole row (a few KB from L2; cheaper than a second launch or a grid-wide reduction), derives the
 // power-of-two scale 2^-S that puts it in [2^14, 2^15), then converts its slice:
 // x16[m][perm(c)] = f16(x[m][c] * 2^-S); rowscale[m] = 2^S.
+// img_rows > 0 selects the operand-tile image the tcgen05 kernels copy in bulk instead of the plain
+// row-major layout: rows are taken in groups of img_rows; a group is stored k-stage by k-stage
+// (64 columns = 128 bytes per row), each stage as img_rows consecutive 128-byte rows whose 16-byte
+// chunks are XOR-swizzled with the row index (the 128-byte swizzle of a K-major operand tile);
+// rows past M are zero.
 template <typename T>
 __global__ void __launch_bounds__(256)
 prep_activations_kernel(const T* __restrict__ x, __half* __restrict__ x16,
-                        float* __restrict__ rowscale, int K, int perm) {
+                        float* __restrict__ rowscale, int M, int K, int perm, int img_rows) {
   __shared__ float red[8];
   const int m = blockIdx.y;
+  if (m >= M) {                                     // zero padding row of the last image group
+    const int per = (((K + gridDim.x - 1) / gridDim.x) + 31) & ~31;
+    const int c0 = blockIdx.x * per, c1 = min(K, c0 + per);
+    const int grp = m / img_rows, ml = m % img_rows;
+    __half* out = x16 + (size_t)grp * img_rows * K;
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x)
+      out[((size_t)(c >> 6) * img_rows + ml) * 64 + ((((c >> 3) & 7) ^ (ml & 7)) << 3) + (c & 7)] = __float2half_rn(0.f);
+    return;
+  }
   const T* xr = x + (size_t)m * K;
   float amax = 0.f;
   if constexpr (sizeof(T) == 2) {
@@ -79,25 +93,36 @@ prep_activations_kernel(const T* __restrict__ x, __half* __restrict__ x16,
     S = max(-110, min(110, S));
   }
   const float down = __uint_as_float((uint32_t)(127 - S) << 23);   // 2^-S
-  __half* out = x16 + (size_t)m * K;
   const int per = (((K + gridDim.x - 1) / gridDim.x) + 31) & ~31;  // slice: whole 32-column groups
   const int c0 = blockIdx.x * per, c1 = min(K, c0 + per);
-  for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
-    const int pos = (c & ~31) + perm_position(perm, c & 31);
-    out[pos] = __float2half_rn(to_f32<T>(xr[c]) * down);
+  if (img_rows > 0) {
+    const int grp = m / img_rows, ml = m % img_rows;
+    __half* out = x16 + (size_t)grp * img_rows * K;
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+      const int pos = (c & ~31) + perm_position(perm, c & 31);
+      out[((size_t)(pos >> 6) * img_rows + ml) * 64 + ((((pos >> 3) & 7) ^ (ml & 7)) << 3) + (pos & 7)] =
+          __float2half_rn(to_f32<T>(xr[c]) * down);
+    }
+  } else {
+    __half* out = x16 + (size_t)m * K;
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+      const int pos = (c & ~31) + perm_position(perm, c & 31);
+      out[pos] = __float2half_rn(to_f32<T>(xr[c]) * down);
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) rowscale[m] = __uint_as_float((uint32_t)(127 + S) << 23);
 }
 
 void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __half* x16,
-                             float* rowscale, int M, int K, int perm) {
+                             float* rowscale, int M, int K, int perm, int img_rows) {
   int slices = (K + 2047) / 2048;
   if (slices > 16) slices = 16;
-  dim3 grid(slices, M);
+  const int rows = img_rows > 0 ? (M + img_rows - 1) / img_rows * img_rows : M;
+  dim3 grid(slices, rows);
   if (dtype == QX_DTYPE_F16)
-    prep_activations_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, x16, rowscale, K, perm);
+    prep_activations_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, x16, rowscale, M, K, perm, img_rows);
   else
-    prep_activations_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, x16, rowscale, K, perm);
+    prep_activations_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, x16, rowscale, M, K, perm, img_rows);
 }
 
 // ---- scratch for the prepared activations -----------------------------------------------------------

@@ -40,7 +40,7 @@ void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free);
 void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, const void* gb,
                            const void* ub, void* y, int64_t M, int64_t N, qx_dtype dtype, int use_bias);
 void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __half* x16,
-                             float* rowscale, int M, int K, int perm);
+                             float* rowscale, int M, int K, int perm, int img_rows = 0);
 // Picks the kernel family for one projection call (format, dtype, batch, alignment).
 void launch_projection(cudaStream_t st, const GemvArgs& a);
 

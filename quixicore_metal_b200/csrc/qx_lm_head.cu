@@ -12,6 +12,7 @@
 // normalizer; Gumbel-max with the stateless (seed, row, global id) noise stream.
 //
 // Ordering everywhere: value descending, ties to the smaller id.
+#include <cstdio>
 #include <cstdlib>
 
 #include "qx_formats.cuh"
@@ -23,6 +24,13 @@ namespace qx {
 constexpr int LMH_TILE = 256;
 constexpr int LMH_TB = 8;        // hidden rows per stage-1 CTA
 constexpr int LMH_RED_THREADS = 512;
+
+// Order-preserving map float -> uint32 (larger float = larger key; +0 and -0 share a key).
+__device__ __forceinline__ uint32_t float_key(float v) {
+  uint32_t u = __float_as_uint(v);
+  if (v == 0.0f) u = 0u;
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
 
 // Reduce one hidden row's 256 tile logits (shared memory) to the tile partials of its mode.
 // Executed by one warp.  nvalid <= 0 marks a padding tile: absent partials are written.
@@ -77,26 +85,60 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
     if (lane == 0)
       part_lse[(size_t)t * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
   }
+  // Tile top-k as an unordered set: find the k-th largest key by a bitwise binary search on the
+  // order-preserving keys (one warp-wide count per step), then emit every element above it and, of
+  // the elements equal to it, the ones with the smallest ids.
   const size_t pbase = ((size_t)t * tiles_stride + tile) * topk;
-  for (int kk = 0; kk < topk; ++kk) {
-    float best = QX_NEG_INF;
-    int bid = 0x7fffffff, slot = -1;
+  const int k_eff = min(topk, max(nvalid, 0));
+  uint32_t key[8];
+  uint32_t kmax = 0u, kmin = 0xFFFFFFFFu;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (mi[j] >= 0 && better(mv[j], mi[j], best, bid)) { best = mv[j]; bid = mi[j]; slot = j; }
-    }
-    float gbest = best;
-    int gid = bid;
-    warp_argmax(gbest, gid);
-    const bool any = gid != 0x7fffffff;
-    if (slot >= 0 && bid == gid) {
+  for (int j = 0; j < 8; ++j) {
+    key[j] = mi[j] >= 0 ? float_key(mv[j]) : 0u;
+    kmax = max(kmax, key[j]);
+    if (mi[j] >= 0) kmin = min(kmin, key[j]);
+  }
+  uint32_t out_pos = 0u;
+  if (k_eff > 0) {
+    const uint32_t hi = __reduce_max_sync(0xffffffffu, kmax);
+    uint32_t lo = __reduce_min_sync(0xffffffffu, kmin);
+    // with a full tile and k <= 32, every lane's largest element is among at least 32 elements
+    // that are >= the smallest such maximum
+    if (k_eff <= 32 && nvalid >= LMH_TILE) lo = max(lo, __reduce_min_sync(0xffffffffu, kmax));
+    const int nb = 32 - __clz(hi ^ lo);                 // bits below the common prefix of lo and hi
+    uint32_t ans = nb >= 32 ? 0u : (lo >> nb) << nb;
+    for (int b = nb - 1; b >= 0; --b) {
+      const uint32_t cand = ans | (1u << b);
+      unsigned c = 0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) if (j == slot) mi[j] = -1;
+      for (int j = 0; j < 8; ++j) c += key[j] >= cand ? 1u : 0u;
+      if (__reduce_add_sync(0xffffffffu, c) >= (unsigned)k_eff) ans = cand;
     }
-    if (lane == 0) {
-      part_val[pbase + kk] = any ? gbest : QX_NEG_INF;
-      part_id[pbase + kk] = any ? gid : -1;
+    unsigned cg = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cg += key[j] > ans ? 1u : 0u;
+    const unsigned need = (unsigned)k_eff - __reduce_add_sync(0xffffffffu, cg);   // ties to take, >= 1
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    unsigned ties_before = 0u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                       // id order = (j, lane) lexicographic
+      const bool valid = mi[j] >= 0;
+      const bool eq = valid && key[j] == ans;
+      const uint32_t bal_eq = __ballot_sync(0xffffffffu, eq);
+      const bool sel = valid && (key[j] > ans || (eq && ties_before + __popc(bal_eq & lt_mask) < need));
+      const uint32_t bal = __ballot_sync(0xffffffffu, sel);
+      if (sel) {
+        const uint32_t pos = out_pos + __popc(bal & lt_mask);
+        part_val[pbase + pos] = mv[j];
+        part_id[pbase + pos] = mi[j];
+      }
+      out_pos += __popc(bal);
+      ties_before += __popc(bal_eq);
     }
+  }
+  for (int kk = (int)out_pos + lane; kk < topk; kk += 32) {
+    part_val[pbase + kk] = QX_NEG_INF;
+    part_id[pbase + kk] = -1;
   }
 }
 
@@ -209,10 +251,10 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  // blockIdx.y picks the group of hidden rows this CTA serves (all groups stream the same weights:
-  // used when there are fewer vocabulary tiles than SMs, e.g. on a small vocabulary shard)
-  const int t_base = (int)blockIdx.y * tokens_per_group;
-  const int T_pass = min(tokens_per_group, T_total - t_base);
+  // Work items are (vocabulary tile, group of hidden rows) pairs, the group index running fastest
+  // so that the CTAs that stream the same tile for different row groups run at the same time and
+  // share the tile through L2.
+  const int groups = (T_total + tokens_per_group - 1) / tokens_per_group;
 
   uint8_t* ring = smem_raw + (size_t)warp * WS::WARP_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NW * WS::WARP_BYTES) + warp * C::STAGES;
@@ -224,17 +266,11 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
   ws.N1 = V - 16;                                  // rows 16..31 of a warp come from the same matrix
 
   const int real_tiles = (V + LMH_TILE - 1) / LMH_TILE;
-  const int my_tiles = (int)blockIdx.x < real_tiles ? (real_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int items = real_tiles * groups;
+  const int my_tiles = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nch = ws.nch;
   const int steps = my_tiles * nch;
-
-  const __half* xr[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int m = nt * 8 + g;
-    xr[nt] = m < T_pass ? x16 + (size_t)(t_base + m) * K : nullptr;
-  }
-  auto step_row0 = [&](int i) { return ((int)blockIdx.x + (i / nch) * (int)gridDim.x) * LMH_TILE + warp * WROWS; };
+  auto step_row0 = [&](int i) { return (((int)blockIdx.x + (i / nch) * (int)gridDim.x) / groups) * LMH_TILE + warp * WROWS; };
 
 #pragma unroll
   for (int p = 0; p < C::STAGES - 1; ++p)
@@ -242,8 +278,17 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
 
   float acc[NSETS][NT][4];
   for (int j = 0; j < my_tiles; ++j) {
-    const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+    const int item = (int)blockIdx.x + j * (int)gridDim.x;
+    const int tile = item / groups;
+    const int t_base = (item % groups) * tokens_per_group;
+    const int T_pass = min(tokens_per_group, T_total - t_base);
     const int row0 = tile * LMH_TILE + warp * WROWS;
+    const __half* xr[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int m = nt * 8 + g;
+      xr[nt] = m < T_pass ? x16 + (size_t)(t_base + m) * K : nullptr;
+    }
 #pragma unroll
     for (int a = 0; a < NSETS; ++a)
 #pragma unroll
@@ -325,11 +370,15 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
 
   // padding tiles of a short shard carry absent partials
   for (long long tile = real_tiles + blockIdx.x; tile < tiles_stride; tile += gridDim.x) {
-    for (int m = warp; m < T_pass; m += NW)
-      lmh_select_token(logit, 0, 0, vocab_offset, nullptr, t_base + m, (int)tile, tiles_stride, mode,
+    for (int m = warp; m < T_total; m += NW)
+      lmh_select_token(logit, 0, 0, vocab_offset, nullptr, m, (int)tile, tiles_stride, mode,
                        topk, invtemp, seed, part_val, part_id, part_lse, lane);
   }
 }
+
+}  // namespace qx
+#include "qx_lm_head_tc.cuh"
+namespace qx {
 
 template <int FMT>
 static bool lmh_stream_ok(const LmHeadArgs& a) {
@@ -357,19 +406,70 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
     attr_set[dev] = true;
   }
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
-  const int blocks = real_tiles < sm_count() ? real_tiles : sm_count();
   const int tpg = NT * 8;
-  dim3 grid(blocks, (unsigned)((a.T + tpg - 1) / tpg));
+  const long long items = (long long)real_tiles * ((a.T + tpg - 1) / tpg);
+  dim3 grid((unsigned)(items < sm_count() ? items : sm_count()));
   lmh_stream_kernel<FMT, NT, WROWS><<<grid, NW * 32, smem, st>>>(
       x16, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
       (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
   note_launch();
 }
 
+// tcgen05 form of stage 1 for more than 16 hidden rows.
+template <int FMT, int BN>
+static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
+                             int64_t tiles_stride, int* err) {
+  using S = LmhTcSmem<FMT, BN>;
+  static_assert(S::TOTAL <= 227 * 1024, "stage-1 tensor-core configuration exceeds shared memory");
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(lmh_tc_kernel<FMT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    attr_set[dev] = true;
+  }
+  const int groups = (int)((a.T + BN - 1) / BN);
+  const size_t img_bytes = ((size_t)groups * BN * a.K * 2 + 255) & ~(size_t)255;
+  bool must_free = false;
+  void* scratch = stream_scratch(st, img_bytes + (size_t)a.T * 4, &must_free);
+  if (!scratch) return false;
+  __half* ximg = (__half*)scratch;
+  float* rowscale = (float*)((char*)scratch + img_bytes);
+  launch_prep_activations(st, a.h, a.dtype, ximg, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM, BN);
+  note_launch();
+  const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
+  const long long items = (long long)real_tiles * groups;
+  const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
+  lmh_tc_kernel<FMT, BN><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
+      ximg, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, (int)a.V, (int)a.K,
+      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
+  note_launch();
+  if (must_free) cudaFreeAsync(scratch, st);
+  return true;
+}
+
+template <int FMT>
+static bool launch_lmh_tc(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
+                          int64_t tiles_stride, int* err) {
+  static const bool enabled = [] {
+    const char* e = getenv("QX_LMH_TC");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled || a.T <= 16 || a.K % LmhTcCfg<FMT>::KC != 0 || a.K % StreamFmt<FMT>::GROUP != 0) return false;
+  if (a.T <= 32) return launch_lmh_tc_bn<FMT, 32>(st, a, pv, pi, pl, tiles_stride, err);
+  return launch_lmh_tc_bn<FMT, 64>(st, a, pv, pi, pl, tiles_stride, err);
+}
+
 template <int FMT>
 static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
                               int64_t tiles_stride) {
   if (!lmh_stream_ok<FMT>(a)) return false;
+  if (int* e = device_error_flag()) {
+    if (launch_lmh_tc<FMT>(st, a, pv, pi, pl, tiles_stride, e)) return true;
+  }
   int* err = device_error_flag();
   if (!err) return false;
   const size_t x16_bytes = ((size_t)a.T * a.K * 2 + 255) & ~(size_t)255;
@@ -384,6 +484,21 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   // per CTA (more CTAs, each re-reading the weights from L2) when the vocabulary shard is small
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   int tpg = 64;
+  static const int tpg_override = [] {                 // A/B override of the hidden rows per CTA
+    const char* e = getenv("QX_LMH_TPG");
+    return e ? atoi(e) : 0;
+  }();
+  {
+    const int v = tpg_override;
+    if (v == 8 || v == 16 || v == 32 || v == 64) {
+      if (v <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+      else if (v <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+      else if (v <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+      else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+      if (must_free) cudaFreeAsync(scratch, st);
+      return true;
+    }
+  }
   while (tpg > 8 && (long long)real_tiles * ((a.T + tpg - 1) / tpg) < sm_count() && a.T > tpg / 2) tpg >>= 1;
   while (tpg > 8 && a.T <= tpg / 2) tpg >>= 1;
   if (tpg <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
@@ -475,11 +590,6 @@ __device__ __forceinline__ unsigned block_sum_u(unsigned v, BlockScratch& s) {
 }
 
 // order-preserving key: larger float <=> larger key; -0 and +0 share a key
-__device__ __forceinline__ uint32_t float_key(float v) {
-  uint32_t u = __float_as_uint(v);
-  if (v == 0.0f) u = 0u;
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
 
 __global__ void __launch_bounds__(LMH_RED_THREADS)
 lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict__ cand_id,

@@ -1,0 +1,405 @@
+// LM head stage 1 for 17..64 hidden rows per pass: tcgen05 tensor-core form.
+//
+// Shape: logits[v, m] = sum_k W[v, k] * x[m, k].  The vocabulary rows are the M-mode of the MMA
+// (128 rows per instruction), the hidden rows its N-mode (BN = 32 or 64), f16 x f16 -> fp32 in
+// tensor memory.  A CTA owns one 256-row vocabulary tile at a time and runs its two 128-row halves
+// one after the other, 128 columns (two 128-byte swizzle atoms) per operand stage.  Warp roles:
+//   * DQW dequant warps.  Each streams its own 128 / DQW rows with bulk async copies into a private
+//     ring (the per-warp weight stream of qx_stream.cuh), decodes the codes with the same exact
+//     f16 sequences as the small-batch path and stores them, UNSCALED, as a K-major 128-byte-
+//     swizzled operand tile (64 columns per stage).  The block scales go to a small ring.
+//   * one loader thread copies the matching activation tile (prepared once per call as row-scaled
+//     f16 in the decoders' column order, already in operand-tile layout) with one bulk copy.
+//   * one MMA thread issues tcgen05.mma.  For the formats whose scale is applied afterwards
+//     (q8_0, q4_0, mxfp4, mxfp8) every 32-column unit accumulates into its own TMEM buffer; the
+//     buffers are handed over in pairs (one swizzle atom = two units) through a ring of three
+//     pairs.  nvfp4 folds its scale into the f16 weight (exact) and accumulates the whole row in
+//     place.
+//   * eight scale warps (two per TMEM lane quarter, each taking half of the hidden rows; a thread
+//     owns one vocabulary row) read each unit buffer back and add scale * partial into fp32
+//     registers: the result is the fp32 dequantise-then-dot up to summation order.  At the end
+//     of a half they park the row's logits in TMEM.
+// When both halves are done the scale warps move the logits to shared memory (the idle operand
+// ring), where all warps run the per-tile selection.
+// Every mbarrier wait is bounded; on expiry the CTA raises the device error flag, stops issuing
+// work, runs its loops to the end without waiting, frees its tensor memory and returns.
+#pragma once
+
+#include "qx_tc.cuh"
+
+namespace qx {
+
+template <int FMT> struct LmhTcCfg;     // raw-ring geometry: columns per row chunk, ring depth
+template <> struct LmhTcCfg<F_Q8_0>  { static constexpr int KC = 256, RST = 2; static constexpr bool POST = true; };
+template <> struct LmhTcCfg<F_Q4_0>  { static constexpr int KC = 256, RST = 3; static constexpr bool POST = true; };
+template <> struct LmhTcCfg<F_NVFP4> { static constexpr int KC = 256, RST = 3; static constexpr bool POST = false; };
+template <> struct LmhTcCfg<F_MXFP4> { static constexpr int KC = 512, RST = 2; static constexpr bool POST = true; };
+template <> struct LmhTcCfg<F_MXFP8> { static constexpr int KC = 128, RST = 2; static constexpr bool POST = true; };
+
+constexpr int LTC_DQW = 8;                       // dequant warps (16 rows each)
+constexpr int LTC_SCW = 8;                       // scale warps
+constexpr int LTC_WARPS = LTC_DQW + 2 + LTC_SCW; // + MMA, loader
+constexpr int LTC_AST = 2;                       // operand-stage ring depth (weights)
+constexpr int LTC_BST = 3;                       // operand-stage ring depth (activations)
+constexpr int LTC_DONE = 6;                      // "stage consumed" barrier ring (multiple of AST and BST)
+constexpr int LTC_NACC = 3;                      // TMEM ring of unit-buffer pairs
+constexpr int LTC_SCR = 16;                      // scale ring depth in units (4 stages)
+constexpr int LTC_KS = 128;                      // columns per operand stage (two swizzle atoms)
+
+template <int FMT, int BN>
+struct LmhTcSmem {
+  using C = LmhTcCfg<FMT>;
+  using WS = WarpStream<FMT, C::KC, 16, C::RST>;
+  static constexpr int A_ATOM = 128 * 128;
+  static constexpr int B_ATOM = BN * 128;
+  static constexpr int A_STAGE = 2 * A_ATOM;
+  static constexpr int B_STAGE = 2 * B_ATOM;
+  static constexpr int OFF_A = 0;                 // also the logit buffer [BN][256] of the selection
+  static constexpr int OFF_B = OFF_A + LTC_AST * A_STAGE;
+  static constexpr int OFF_RAW = OFF_B + LTC_BST * B_STAGE;
+  static constexpr int OFF_SC = OFF_RAW + LTC_DQW * WS::WARP_BYTES;
+  static constexpr int OFF_BAR = OFF_SC + LTC_SCR * 128 * 4;
+  // barriers (8 bytes each): a_full[AST] b_full[BST] done[DONE] acc_full[NACC] acc_empty[NACC]
+  // acc_done, then the raw rings' DQW * RST, then the TMEM slot and the abort flag
+  static constexpr int NBARS = LTC_AST + LTC_BST + LTC_DONE + 2 * LTC_NACC + 1 + LTC_DQW * C::RST;
+  static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 16 + 1024;     // + alignment slack
+  static_assert(BN * LMH_TILE * 4 <= LTC_AST * A_STAGE, "logit buffer must fit the operand ring");
+};
+
+template <int FMT, int BN>
+__global__ void __launch_bounds__(LTC_WARPS * 32, 1)
+lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscale,
+              const uint8_t* __restrict__ wq, const float* __restrict__ bias,
+              float* __restrict__ part_val, int32_t* __restrict__ part_id,
+              float* __restrict__ part_lse, int T_total, int V, int K, long long vocab_offset,
+              long long tiles_stride, int mode, int topk, float invtemp, uint32_t seed,
+              int* __restrict__ err_flag) {
+  using F = StreamFmt<FMT>;
+  using C = LmhTcCfg<FMT>;
+  using S = LmhTcSmem<FMT, BN>;
+  using WS = typename S::WS;
+  constexpr bool POST = C::POST;
+  constexpr int HB = BN / 2;                      // hidden rows per scale warp
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const uint32_t bars = sbase + S::OFF_BAR;
+  auto A_FULL = [&](int i) { return bars + 8u * (uint32_t)i; };
+  auto B_FULL = [&](int i) { return bars + 8u * (uint32_t)(LTC_AST + i); };
+  auto DONE = [&](int i) { return bars + 8u * (uint32_t)(LTC_AST + LTC_BST + i); };
+  auto ACC_FULL = [&](int i) { return bars + 8u * (uint32_t)(LTC_AST + LTC_BST + LTC_DONE + i); };
+  auto ACC_EMPTY = [&](int i) { return bars + 8u * (uint32_t)(LTC_AST + LTC_BST + LTC_DONE + LTC_NACC + i); };
+  const uint32_t ACC_DONE = bars + 8u * (uint32_t)(LTC_AST + LTC_BST + LTC_DONE + 2 * LTC_NACC);
+  const uint32_t raw_bars = ACC_DONE + 8u;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S::OFF_BAR + S::NBARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::OFF_BAR + S::NBARS * 8 + 4);
+  float* sc_ring = reinterpret_cast<float*>(smem + S::OFF_SC);
+  float* logit = reinterpret_cast<float*>(smem + S::OFF_A);
+
+  if (tid == 0) {
+    for (int s = 0; s < LTC_AST; ++s) mbar_init(A_FULL(s), LTC_DQW);
+    for (int s = 0; s < LTC_BST; ++s) mbar_init(B_FULL(s), 1);
+    for (int s = 0; s < LTC_DONE; ++s) mbar_init(DONE(s), 1);
+    for (int s = 0; s < LTC_NACC; ++s) { mbar_init(ACC_FULL(s), 1); mbar_init(ACC_EMPTY(s), LTC_SCW); }
+    mbar_init(ACC_DONE, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == LTC_DQW) tmem_alloc(smem_u32((const void*)tmem_slot), 512u);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: [0, BN) logits of half 0, [BN, 2 BN) of half 1, then NACC pairs of unit buffers
+  constexpr uint32_t ACC_COL0 = 2 * BN;
+
+  // Bounded wait.  The CTA-wide abort flag is looked at only while spinning.
+  auto wait_or_abort = [&](uint32_t bar, uint32_t parity) -> bool {
+    for (int i = 0; i < (1 << 21); ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    atomicExch(err_flag, 3);
+    *abort_flag = 1;
+    return false;
+  };
+
+  const int groups = (T_total + BN - 1) / BN;                 // hidden-row groups (work items)
+  const int real_tiles = (V + LMH_TILE - 1) / LMH_TILE;
+  const int items = real_tiles * groups;
+  const int my_items = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int nks = K / LTC_KS;                                 // operand stages per half
+  auto item_of = [&](int j) { return (int)blockIdx.x + j * (int)gridDim.x; };
+
+  // role state that outlives an item
+  WS ws;
+  int raw_issued = 0, raw_done = 0;
+  const int nch = (K + C::KC - 1) / C::KC;
+  const int raw_steps = my_items * 2 * nch;
+  auto raw_row0 = [&](int i) {          // first row of this warp at raw step i
+    const int it = item_of(i / (2 * nch));
+    return (it / groups) * LMH_TILE + ((i / nch) & 1) * 128 + warp * 16;
+  };
+  if (warp < LTC_DQW) {
+    ws.init(sbase + S::OFF_RAW + (uint32_t)warp * WS::WARP_BYTES, raw_bars + 8u * (uint32_t)(warp * C::RST),
+            wq, wq, V, K, lane, err_flag);
+#pragma unroll
+    for (int p = 0; p < C::RST - 1; ++p)
+      if (p < raw_steps) { ws.issue(p, raw_row0(p), p % nch); ++raw_issued; }
+  }
+
+  for (int j = 0; j < my_items; ++j) {
+    const int item = item_of(j);
+    const int tile = item / groups;
+    const int grp = item % groups;
+    const int t_base = grp * BN;
+    const int T_pass = min(BN, T_total - t_base);
+    const int it_base = j * 2 * nks;                          // global operand-stage counter
+
+    if (warp < LTC_DQW) {
+      // ================= dequant =================
+      const int q = ((lane >> 2) & 1) * 4 + (lane >> 3);      // row pair (q, q + 8) of this warp's 16
+      const int t = lane & 3;
+      for (int h = 0; h < 2; ++h) {
+        const int row0 = tile * LMH_TILE + h * 128 + warp * 16;
+        for (int c = 0; c < nch; ++c) {
+          const int i = (j * 2 + h) * nch + c;
+          const int rstage = i % C::RST;
+          const int nxt = i + C::RST - 1;
+          if (nxt < raw_steps) { ws.issue(nxt % C::RST, raw_row0(nxt), nxt % nch); ++raw_issued; }
+          ws.wait(rstage, (uint32_t)((i / C::RST) & 1));
+          ++raw_done;
+          uint32_t s[2] = {ws.slot_addr(rstage, q, row0, c), ws.slot_addr(rstage, q + 8, row0, c)};
+          constexpr uint32_t ATOM_BYTES = 64 / F::BK * F::BB;   // packed bytes of 64 columns
+          const int nstages = min(C::KC, K - c * C::KC) / LTC_KS;
+          for (int ss = 0; ss < nstages; ++ss) {
+            const int it = it_base + h * nks + c * (C::KC / LTC_KS) + ss;
+            const int sa = it % LTC_AST;
+            if (it >= LTC_AST) wait_or_abort(DONE((it - LTC_AST) % LTC_DONE), (uint32_t)(((it - LTC_AST) / LTC_DONE) & 1));
+            uint8_t* a_stage = smem + S::OFF_A + (size_t)sa * S::A_STAGE;
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {                       // swizzle atom = 64 columns
+              uint8_t* a_atom = a_stage + a * S::A_ATOM;
+              if constexpr (FMT == F_NVFP4) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                  uint32_t w[4][2];
+                  GroupProc<F_NVFP4>::block(s[r] + a * ATOM_BYTES, t, w);
+                  const int R = warp * 16 + q + 8 * r;
+                  *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
+                  *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t + 1)) = make_uint4(w[2][0], w[2][1], w[3][0], w[3][1]);
+                }
+              } else {
+                float* scs = sc_ring + (size_t)((it * 4 + a * 2) % LTC_SCR) * 128;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                  for (int r = 0; r < 2; ++r) {
+                    uint32_t w[2][2];
+                    float scale;
+                    // the unit's position inside the decode group fixes its byte alignment
+                    constexpr bool WIDE = F::GROUP == 128;
+                    const uint32_t sp = s[r] + (uint32_t)((2 * a + u) * F::BB);
+                    if (!WIDE || a == 0) {
+                      if (u == 0) RowDec<FMT>::template row<0>(sp, t, w, scale);
+                      else RowDec<FMT>::template row<1>(sp, t, w, scale);
+                    } else {
+                      if (u == 0) RowDec<FMT>::template row<2>(sp, t, w, scale);
+                      else RowDec<FMT>::template row<3>(sp, t, w, scale);
+                    }
+                    const int R = warp * 16 + q + 8 * r;
+                    *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 4 * u + t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
+                    if (t == 0) scs[u * 128 + R] = scale;
+                  }
+                }
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(A_FULL(sa));
+            s[0] += 2 * ATOM_BYTES; s[1] += 2 * ATOM_BYTES;
+          }
+          __syncwarp();
+        }
+      }
+    } else if (warp == LTC_DQW) {
+      // ================= MMA issuer =================
+      if (lane == 0) {
+        const uint32_t idesc = umma_idesc_f16(BN);
+        for (int h = 0; h < 2; ++h) {
+          for (int st = 0; st < nks; ++st) {
+            const int it = it_base + h * nks + st;
+            const int sa = it % LTC_AST, sb = it % LTC_BST;
+            bool ok = wait_or_abort(B_FULL(sb), (uint32_t)((it / LTC_BST) & 1));
+            ok = wait_or_abort(A_FULL(sa), (uint32_t)((it / LTC_AST) & 1)) && ok;
+            tc_fence_after();
+            const uint32_t a_base = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
+            const uint32_t b_base = sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE);
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {                       // swizzle atom = pair of units
+              if constexpr (POST) {
+                const int pg = it * 2 + p;
+                const int buf = pg % LTC_NACC;
+                if (pg >= LTC_NACC) {
+                  ok = wait_or_abort(ACC_EMPTY(buf), (uint32_t)((pg / LTC_NACC - 1) & 1)) && ok;
+                  tc_fence_after();
+                }
+                if (ok) {
+#pragma unroll
+                  for (int kk = 0; kk < 4; ++kk)
+                    tc_mma_f16(tmem_base + ACC_COL0 + (uint32_t)(buf * 2 * BN + (kk >> 1) * BN),
+                               umma_desc_sw128(a_base + (uint32_t)(p * S::A_ATOM + kk * 32)),
+                               umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc, kk & 1);
+                }
+                tc_commit(ACC_FULL(buf));
+              } else {
+                if (ok) {
+#pragma unroll
+                  for (int kk = 0; kk < 4; ++kk)
+                    tc_mma_f16(tmem_base + (uint32_t)(h * BN),
+                               umma_desc_sw128(a_base + (uint32_t)(p * S::A_ATOM + kk * 32)),
+                               umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc,
+                               (st | p | kk) != 0 ? 1u : 0u);
+                }
+              }
+            }
+            tc_commit(DONE(it % LTC_DONE));
+          }
+        }
+        if constexpr (!POST) tc_commit(ACC_DONE);
+      }
+      __syncwarp();
+    } else if (warp == LTC_DQW + 1) {
+      // ================= activation-tile loader =================
+      if (lane == 0) {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(ximg) + (size_t)grp * BN * K * 2;
+        for (int h = 0; h < 2; ++h) {
+          for (int st = 0; st < nks; ++st) {
+            const int it = it_base + h * nks + st;
+            const int sb = it % LTC_BST;
+            bool ok = true;
+            if (it >= LTC_BST) ok = wait_or_abort(DONE((it - LTC_BST) % LTC_DONE), (uint32_t)(((it - LTC_BST) / LTC_DONE) & 1));
+            if (ok) {
+              mbar_arrive_expect_tx(B_FULL(sb), (uint32_t)S::B_STAGE);
+              bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)st * S::B_STAGE,
+                       (uint32_t)S::B_STAGE, B_FULL(sb));
+            }
+          }
+        }
+      }
+      __syncwarp();
+    } else {
+      // ================= scale warps: thread = vocabulary row, warp = half of the hidden rows =================
+      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+      const int R = (warp & 3) * 32 + lane;
+      const int ch = (warp - (LTC_DQW + 2)) >> 2;               // which half of the hidden rows
+      if constexpr (POST) {
+        for (int h = 0; h < 2; ++h) {
+          float acc[HB];
+#pragma unroll
+          for (int i = 0; i < HB; ++i) acc[i] = 0.f;
+          for (int st = 0; st < nks; ++st) {
+            const int it = it_base + h * nks + st;
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+              const int pg = it * 2 + p;
+              const int buf = pg % LTC_NACC;
+              const bool ok = wait_or_abort(ACC_FULL(buf), (uint32_t)((pg / LTC_NACC) & 1));
+              tc_fence_after();
+              const uint32_t col = tmem_base + lane_sel + ACC_COL0 + (uint32_t)(buf * 2 * BN + ch * HB);
+              const float sc0 = sc_ring[(size_t)((it * 4 + p * 2) % LTC_SCR) * 128 + R];
+              const float sc1 = sc_ring[(size_t)((it * 4 + p * 2 + 1) % LTC_SCR) * 128 + R];
+              if (ok) {
+#pragma unroll
+                for (int cb = 0; cb < HB / 16; ++cb) {
+                  uint32_t v0[16], v1[16];
+                  tmem_ld16_nowait(col + (uint32_t)(cb * 16), v0);
+                  tmem_ld16_nowait(col + (uint32_t)(BN + cb * 16), v1);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) {
+                    acc[cb * 16 + i] = fmaf(sc0, __uint_as_float(v0[i]), acc[cb * 16 + i]);
+                    acc[cb * 16 + i] = fmaf(sc1, __uint_as_float(v1[i]), acc[cb * 16 + i]);
+                  }
+                }
+              }
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(ACC_EMPTY(buf));
+            }
+          }
+          // park the row's logits of this half
+#pragma unroll
+          for (int cb = 0; cb < HB / 16; ++cb) {
+            uint32_t v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(acc[cb * 16 + i]);
+            tmem_st16(tmem_base + lane_sel + (uint32_t)(h * BN + ch * HB + cb * 16), v);
+          }
+          tmem_wait_st();
+        }
+      } else {
+        wait_or_abort(ACC_DONE, (uint32_t)(j & 1));
+        tc_fence_after();
+      }
+    }
+
+    // ---- logits of both halves are in TMEM columns [0, 2 BN); the operand ring is idle ----
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const int v0 = tile * LMH_TILE;
+    const int nvalid = min(LMH_TILE, V - v0);
+    if (warp >= LTC_DQW + 2) {
+      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+      const int R = (warp & 3) * 32 + lane;
+      const int ch = (warp - (LTC_DQW + 2)) >> 2;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int cb = 0; cb < HB / 16; ++cb) {
+          uint32_t v[16];
+          tmem_ld16_nowait(tmem_base + lane_sel + (uint32_t)(h * BN + ch * HB + cb * 16), v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = ch * HB + cb * 16 + i;
+            const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
+            logit[m * LMH_TILE + h * 128 + R] = __uint_as_float(v[i]) * rs;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    for (int m = warp; m < T_pass; m += LTC_WARPS)
+      lmh_select_token(logit + m * LMH_TILE, nvalid, v0, vocab_offset, bias, t_base + m, tile,
+                       tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse, lane);
+    __syncthreads();
+    tc_fence_after();
+  }
+
+  // on an aborted run, raw copies that were issued but never consumed may still be in flight
+  if (warp < LTC_DQW && *abort_flag) {
+    for (int i = raw_done; i < raw_issued; ++i) {
+      ws.dead = false;
+      ws.wait(i % C::RST, (uint32_t)((i / C::RST) & 1));
+    }
+  }
+
+  // padding tiles of a short shard carry absent partials
+  for (long long tile = real_tiles + blockIdx.x; tile < tiles_stride; tile += gridDim.x) {
+    for (int m = warp; m < T_total; m += LTC_WARPS)
+      lmh_select_token(logit, 0, 0, vocab_offset, nullptr, m, (int)tile, tiles_stride, mode,
+                       topk, invtemp, seed, part_val, part_id, part_lse, lane);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == LTC_DQW) tmem_dealloc(tmem_base, 512u);
+}
+
+}  // namespace qx

@@ -20,6 +20,7 @@
 #include "qx_formats.cuh"
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
+#include "qx_tc.cuh"
 
 namespace qx {
 
@@ -29,62 +30,6 @@ constexpr int MMA_GROUP_WARPS = 8;    // one dequant group: thread = (weight row
 constexpr int MMA_GROUPS = 2;         // groups alternate stages, which doubles the loads in flight
 constexpr int MMA_DQ_WARPS = MMA_GROUP_WARPS * MMA_GROUPS;
 constexpr int MMA_THREADS = (MMA_DQ_WARPS + 1) * 32;   // + the MMA issuer warp
-
-// ---- tcgen05 wrappers ----------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// 16 consecutive fp32 columns of this warp's 32 TMEM lanes
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
-// 1024 bytes apart.  `addr` is the shared-window byte address of the first row (+ 32 bytes per
-// 16-column step inside the swizzle atom).
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                           // leading-dimension offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;                 // stride between 8-row groups
-  d |= (uint64_t)1 << 46;                           // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                           // 128-byte swizzle
-  return d;
-}
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc_bf16(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(MMA_BM >> 4) << 24);
-}
-// byte offset of 16-byte chunk c of row r inside a swizzled tile
-__device__ __forceinline__ uint32_t sw128_offset(int r, int c) {
-  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
-}
 
 template <int FMT> struct MmaTerms { static constexpr int N = 1; };
 template <> struct MmaTerms<F_Q4_0> { static constexpr int N = 2; };

@@ -147,6 +147,22 @@ def test_batch_sizes_q8_0_bf16(T):
         assert n >= T - 1
 
 
+@pytest.mark.parametrize("T", [17, 32, 33, 64, 100])
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_0", "mxfp8", "nvfp4", "mxfp4"])
+def test_many_hidden_rows_all_formats(fmt, T):
+    """More than 16 hidden rows per call (the tensor-memory form of stage 1): every packed format,
+    row counts on both sides of the 32- and 64-row pass sizes, a ragged last vocabulary tile."""
+    dtype = "f16" if T == 33 else "bf16"
+    h, Wq = _case(fmt, T, 2048 + 77, 1024, dtype, 300 + T, hs=1.0, ws=0.05)
+    L = O.lm_head_logits(h, Wq, fmt)
+    for mode, kw in (("argmax", {}), ("topk", dict(k=50)), ("topp", dict(k=32, top_p=0.9)), ("categorical", {})):
+        tok = _run(h, Wq, fmt, dtype, mode, temperature=0.8, seed=77, **kw)
+        want, margin = O.lm_head_sample_from_logits(L, MODES[mode], k=kw.get("k", 0), temperature=0.8,
+                                                    seed=77, top_p=kw.get("top_p", 0.9), return_detail=True)
+        n = check_ids(tok, want, margin, EPS, f"{fmt}/T{T}/{mode}")
+        assert n >= T - 1
+
+
 @pytest.mark.parametrize("mode", ["argmax", "categorical", "topk", "topp"])
 @pytest.mark.parametrize("shards", [2, 3, 8])
 def test_vocab_sharded_merge_equals_single_call(mode, shards):
