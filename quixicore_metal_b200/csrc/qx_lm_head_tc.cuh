@@ -120,7 +120,7 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
   auto wait_or_abort = [&](uint32_t bar, uint32_t parity) -> bool {
     for (int i = 0; i < (1 << 21); ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((i & 255) == 255 && *abort_flag) return false;
+      if ((i & 63) == 63 && *abort_flag) return false;
     }
     atomicExch(err_flag, 3);
     *abort_flag = 1;

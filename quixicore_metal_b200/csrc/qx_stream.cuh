@@ -56,6 +56,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// The same with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
+// (or until the phase completes) instead of returning at once.  Measured on the tcgen05 LM head:
+// fewer polling instructions but a later wake-up, 4 % slower overall, so the kernels poll.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok;
+}
 // Bounded wait: returns false (and records the failure) if the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_flag) {
   for (int i = 0; i < (1 << 22); ++i)
