@@ -415,11 +415,43 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   note_launch();
 }
 
+// Tensor map over a packed weight matrix seen as V rows of 32-bit words, box = (box_bytes / 4) x 128
+// rows.  The driver entry point is looked up at run time, so the library does not link libcuda.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                      CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encode_fn() {
+  static TensorMapEncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return (TensorMapEncodeFn) nullptr;
+    }
+    return (TensorMapEncodeFn)p;
+  }();
+  return fn;
+}
+static bool make_weight_map(CUtensorMap* map, const void* w, int64_t V, size_t row_bytes, int box_bytes) {
+  TensorMapEncodeFn enc = tensor_map_encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)V};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(w), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // tcgen05 form of stage 1 for more than 16 hidden rows.
 template <int FMT, int BN>
 static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
                              int64_t tiles_stride, int* err) {
   using S = LmhTcSmem<FMT, BN>;
+  using C = LmhTcCfg<FMT>;
   static_assert(S::TOTAL <= 227 * 1024, "stage-1 tensor-core configuration exceeds shared memory");
   static bool attr_set[64] = {};
   int dev = 0;
@@ -431,6 +463,9 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
     }
     attr_set[dev] = true;
   }
+  const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
+  CUtensorMap wmap;
+  if (!make_weight_map(&wmap, a.wq, a.V, row_bytes, C::BOX)) return false;
   const int groups = (int)((a.T + BN - 1) / BN);
   const size_t img_bytes = ((size_t)groups * BN * a.K * 2 + 255) & ~(size_t)255;
   bool must_free = false;
@@ -444,7 +479,7 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
   const long long items = (long long)real_tiles * groups;
   const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
   lmh_tc_kernel<FMT, BN><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
-      ximg, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, (int)a.V, (int)a.K,
+      wmap, ximg, rowscale, a.bias, pv, pi, pl, (int)a.T, (int)a.V, (int)a.K,
       (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
   note_launch();
   if (must_free) cudaFreeAsync(scratch, st);
@@ -458,7 +493,7 @@ static bool launch_lmh_tc(cudaStream_t st, const LmHeadArgs& a, float* pv, int32
     const char* e = getenv("QX_LMH_TC");
     return !(e && e[0] == '0');
   }();
-  if (!enabled || a.T <= 16 || a.K % LmhTcCfg<FMT>::KC != 0 || a.K % StreamFmt<FMT>::GROUP != 0) return false;
+  if (!enabled || a.T <= 16 || a.K % LTC_KS != 0 || a.V < 128) return false;
   if (a.T <= 32) return launch_lmh_tc_bn<FMT, 32>(st, a, pv, pi, pl, tiles_stride, err);
   return launch_lmh_tc_bn<FMT, 64>(st, a, pv, pi, pl, tiles_stride, err);
 }

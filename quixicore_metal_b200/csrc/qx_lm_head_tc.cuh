@@ -25,16 +25,27 @@
 // work, runs its loops to the end without waiting, frees its tensor memory and returns.
 #pragma once
 
+#include <cuda.h>
+
 #include "qx_tc.cuh"
 
 namespace qx {
 
-template <int FMT> struct LmhTcCfg;     // raw-ring geometry: columns per row chunk, ring depth
-template <> struct LmhTcCfg<F_Q8_0>  { static constexpr int KC = 256, RST = 2; static constexpr bool POST = true; };
-template <> struct LmhTcCfg<F_Q4_0>  { static constexpr int KC = 256, RST = 3; static constexpr bool POST = true; };
-template <> struct LmhTcCfg<F_NVFP4> { static constexpr int KC = 256, RST = 3; static constexpr bool POST = false; };
-template <> struct LmhTcCfg<F_MXFP4> { static constexpr int KC = 512, RST = 2; static constexpr bool POST = true; };
-template <> struct LmhTcCfg<F_MXFP8> { static constexpr int KC = 128, RST = 2; static constexpr bool POST = true; };
+// Raw-stage geometry.  A stage holds 128 columns of 128 rows.  Its bytes start at a multiple of 4
+// inside the row but not of 16, so the box starts at the 16-byte boundary below and is wide
+// enough for the largest misalignment; the box width is an odd multiple of 16 bytes, which puts
+// the 8 rows a warp instruction touches in different bank groups.
+template <int FMT> struct LmhTcCfg {
+  using F = StreamFmt<FMT>;
+  static constexpr int CHUNK_BYTES = 128 / F::BK * F::BB;
+  static constexpr int G16 = (CHUNK_BYTES % 16 == 0) ? 16 : ((CHUNK_BYTES % 8 == 0) ? 8 : 4);
+  static constexpr int NEED = CHUNK_BYTES + 16 - G16;
+  static constexpr int N16 = (NEED + 15) / 16;
+  static constexpr int BOX = (N16 | 1) * 16;                 // odd multiple of 16 bytes
+  static constexpr int RAW_STAGE = 128 * BOX;
+  static constexpr int RST = RAW_STAGE > 16 * 1024 ? 5 : 6;  // raw ring depth
+  static constexpr bool POST = FMT != F_NVFP4;
+};
 
 constexpr int LTC_DQW = 8;                       // dequant warps (16 rows each)
 constexpr int LTC_SCW = 8;                       // scale warps
@@ -49,7 +60,6 @@ constexpr int LTC_KS = 128;                      // columns per operand stage (t
 template <int FMT, int BN>
 struct LmhTcSmem {
   using C = LmhTcCfg<FMT>;
-  using WS = WarpStream<FMT, C::KC, 16, C::RST>;
   static constexpr int A_ATOM = 128 * 128;
   static constexpr int B_ATOM = BN * 128;
   static constexpr int A_STAGE = 2 * A_ATOM;
@@ -57,19 +67,27 @@ struct LmhTcSmem {
   static constexpr int OFF_A = 0;                 // also the logit buffer [BN][256] of the selection
   static constexpr int OFF_B = OFF_A + LTC_AST * A_STAGE;
   static constexpr int OFF_RAW = OFF_B + LTC_BST * B_STAGE;
-  static constexpr int OFF_SC = OFF_RAW + LTC_DQW * WS::WARP_BYTES;
+  static constexpr int OFF_SC = OFF_RAW + C::RST * C::RAW_STAGE;
   static constexpr int OFF_BAR = OFF_SC + LTC_SCR * 128 * 4;
   // barriers (8 bytes each): a_full[AST] b_full[BST] done[DONE] acc_full[NACC] acc_empty[NACC]
-  // acc_done, then the raw rings' DQW * RST, then the TMEM slot and the abort flag
-  static constexpr int NBARS = LTC_AST + LTC_BST + LTC_DONE + 2 * LTC_NACC + 1 + LTC_DQW * C::RST;
+  // acc_done raw_full[RST] raw_empty[RST], then the TMEM slot and the abort flag
+  static constexpr int NBARS = LTC_AST + LTC_BST + LTC_DONE + 2 * LTC_NACC + 1 + 2 * C::RST;
   static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 16 + 1024;     // + alignment slack
   static_assert(BN * LMH_TILE * 4 <= LTC_AST * A_STAGE, "logit buffer must fit the operand ring");
+  static_assert(C::RAW_STAGE % 128 == 0, "raw stages must keep the TMA destination aligned");
 };
+
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
 
 template <int FMT, int BN>
 __global__ void __launch_bounds__(LTC_WARPS * 32, 1)
-lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscale,
-              const uint8_t* __restrict__ wq, const float* __restrict__ bias,
+lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ ximg,
+              const float* __restrict__ rowscale, const float* __restrict__ bias,
               float* __restrict__ part_val, int32_t* __restrict__ part_id,
               float* __restrict__ part_lse, int T_total, int V, int K, long long vocab_offset,
               long long tiles_stride, int mode, int topk, float invtemp, uint32_t seed,
@@ -77,9 +95,9 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
   using F = StreamFmt<FMT>;
   using C = LmhTcCfg<FMT>;
   using S = LmhTcSmem<FMT, BN>;
-  using WS = typename S::WS;
   constexpr bool POST = C::POST;
   constexpr int HB = BN / 2;                      // hidden rows per scale warp
+  constexpr int RST = C::RST;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -92,7 +110,8 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
   auto ACC_FULL = [&](int i) { return bars + 8u * (uint32_t)(LTC_AST + LTC_BST + LTC_DONE + i); };
   auto ACC_EMPTY = [&](int i) { return bars + 8u * (uint32_t)(LTC_AST + LTC_BST + LTC_DONE + LTC_NACC + i); };
   const uint32_t ACC_DONE = bars + 8u * (uint32_t)(LTC_AST + LTC_BST + LTC_DONE + 2 * LTC_NACC);
-  const uint32_t raw_bars = ACC_DONE + 8u;
+  auto RAW_FULL = [&](int i) { return ACC_DONE + 8u * (uint32_t)(1 + i); };
+  auto RAW_EMPTY = [&](int i) { return ACC_DONE + 8u * (uint32_t)(1 + RST + i); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S::OFF_BAR + S::NBARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::OFF_BAR + S::NBARS * 8 + 4);
   float* sc_ring = reinterpret_cast<float*>(smem + S::OFF_SC);
@@ -104,6 +123,7 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
     for (int s = 0; s < LTC_DONE; ++s) mbar_init(DONE(s), 1);
     for (int s = 0; s < LTC_NACC; ++s) { mbar_init(ACC_FULL(s), 1); mbar_init(ACC_EMPTY(s), LTC_SCW); }
     mbar_init(ACC_DONE, 1);
+    for (int s = 0; s < RST; ++s) { mbar_init(RAW_FULL(s), 1); mbar_init(RAW_EMPTY(s), LTC_DQW); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -132,24 +152,9 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
   const int items = real_tiles * groups;
   const int my_items = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nks = K / LTC_KS;                                 // operand stages per half
+  const int total_stages = my_items * 2 * nks;                // global stage counter range of this CTA
   auto item_of = [&](int j) { return (int)blockIdx.x + j * (int)gridDim.x; };
-
-  // role state that outlives an item
-  WS ws;
-  int raw_issued = 0, raw_done = 0;
-  const int nch = (K + C::KC - 1) / C::KC;
-  const int raw_steps = my_items * 2 * nch;
-  auto raw_row0 = [&](int i) {          // first row of this warp at raw step i
-    const int it = item_of(i / (2 * nch));
-    return (it / groups) * LMH_TILE + ((i / nch) & 1) * 128 + warp * 16;
-  };
-  if (warp < LTC_DQW) {
-    ws.init(sbase + S::OFF_RAW + (uint32_t)warp * WS::WARP_BYTES, raw_bars + 8u * (uint32_t)(warp * C::RST),
-            wq, wq, V, K, lane, err_flag);
-#pragma unroll
-    for (int p = 0; p < C::RST - 1; ++p)
-      if (p < raw_steps) { ws.issue(p, raw_row0(p), p % nch); ++raw_issued; }
-  }
+  int raw_next = 0;                                           // loader: next raw stage to request
 
   for (int j = 0; j < my_items; ++j) {
     const int item = item_of(j);
@@ -163,66 +168,57 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
       // ================= dequant =================
       const int q = ((lane >> 2) & 1) * 4 + (lane >> 3);      // row pair (q, q + 8) of this warp's 16
       const int t = lane & 3;
+      constexpr uint32_t ATOM_BYTES = 64 / F::BK * F::BB;     // packed bytes of 64 columns
       for (int h = 0; h < 2; ++h) {
-        const int row0 = tile * LMH_TILE + h * 128 + warp * 16;
-        for (int c = 0; c < nch; ++c) {
-          const int i = (j * 2 + h) * nch + c;
-          const int rstage = i % C::RST;
-          const int nxt = i + C::RST - 1;
-          if (nxt < raw_steps) { ws.issue(nxt % C::RST, raw_row0(nxt), nxt % nch); ++raw_issued; }
-          ws.wait(rstage, (uint32_t)((i / C::RST) & 1));
-          ++raw_done;
-          uint32_t s[2] = {ws.slot_addr(rstage, q, row0, c), ws.slot_addr(rstage, q + 8, row0, c)};
-          constexpr uint32_t ATOM_BYTES = 64 / F::BK * F::BB;   // packed bytes of 64 columns
-          const int nstages = min(C::KC, K - c * C::KC) / LTC_KS;
-          for (int ss = 0; ss < nstages; ++ss) {
-            const int it = it_base + h * nks + c * (C::KC / LTC_KS) + ss;
-            const int sa = it % LTC_AST;
-            if (it >= LTC_AST) wait_or_abort(DONE((it - LTC_AST) % LTC_DONE), (uint32_t)(((it - LTC_AST) / LTC_DONE) & 1));
-            uint8_t* a_stage = smem + S::OFF_A + (size_t)sa * S::A_STAGE;
+        for (int st = 0; st < nks; ++st) {
+          const int it = it_base + h * nks + st;
+          const int sa = it % LTC_AST, sr = it % RST;
+          const uint32_t off = (uint32_t)(st * C::CHUNK_BYTES) & 15u;
+          const uint32_t rbase = sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE) + off;
+          const uint32_t s[2] = {rbase + (uint32_t)((warp * 16 + q) * C::BOX), rbase + (uint32_t)((warp * 16 + q + 8) * C::BOX)};
+          wait_or_abort(RAW_FULL(sr), (uint32_t)((it / RST) & 1));
+          if (it >= LTC_AST) wait_or_abort(DONE((it - LTC_AST) % LTC_DONE), (uint32_t)(((it - LTC_AST) / LTC_DONE) & 1));
+          uint8_t* a_stage = smem + S::OFF_A + (size_t)sa * S::A_STAGE;
 #pragma unroll
-            for (int a = 0; a < 2; ++a) {                       // swizzle atom = 64 columns
-              uint8_t* a_atom = a_stage + a * S::A_ATOM;
-              if constexpr (FMT == F_NVFP4) {
+          for (int a = 0; a < 2; ++a) {                       // swizzle atom = 64 columns
+            uint8_t* a_atom = a_stage + a * S::A_ATOM;
+            if constexpr (FMT == F_NVFP4) {
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                uint32_t w[4][2];
+                GroupProc<F_NVFP4>::block(s[r] + a * ATOM_BYTES, t, w);
+                const int R = warp * 16 + q + 8 * r;
+                *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
+                *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t + 1)) = make_uint4(w[2][0], w[2][1], w[3][0], w[3][1]);
+              }
+            } else {
+              float* scs = sc_ring + (size_t)((it * 4 + a * 2) % LTC_SCR) * 128;
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
-                  uint32_t w[4][2];
-                  GroupProc<F_NVFP4>::block(s[r] + a * ATOM_BYTES, t, w);
-                  const int R = warp * 16 + q + 8 * r;
-                  *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
-                  *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t + 1)) = make_uint4(w[2][0], w[2][1], w[3][0], w[3][1]);
-                }
-              } else {
-                float* scs = sc_ring + (size_t)((it * 4 + a * 2) % LTC_SCR) * 128;
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                  for (int r = 0; r < 2; ++r) {
-                    uint32_t w[2][2];
-                    float scale;
-                    // the unit's position inside the decode group fixes its byte alignment
-                    constexpr bool WIDE = F::GROUP == 128;
-                    const uint32_t sp = s[r] + (uint32_t)((2 * a + u) * F::BB);
-                    if (!WIDE || a == 0) {
-                      if (u == 0) RowDec<FMT>::template row<0>(sp, t, w, scale);
-                      else RowDec<FMT>::template row<1>(sp, t, w, scale);
-                    } else {
-                      if (u == 0) RowDec<FMT>::template row<2>(sp, t, w, scale);
-                      else RowDec<FMT>::template row<3>(sp, t, w, scale);
-                    }
-                    const int R = warp * 16 + q + 8 * r;
-                    *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 4 * u + t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
-                    if (t == 0) scs[u * 128 + R] = scale;
+                  uint32_t w[2][2];
+                  float scale;
+                  // the unit's position inside the decode group fixes its byte alignment
+                  constexpr bool WIDE = F::GROUP == 128;
+                  const uint32_t sp = s[r] + (uint32_t)((2 * a + u) * F::BB);
+                  if (!WIDE || a == 0) {
+                    if (u == 0) RowDec<FMT>::template row<0>(sp, t, w, scale);
+                    else RowDec<FMT>::template row<1>(sp, t, w, scale);
+                  } else {
+                    if (u == 0) RowDec<FMT>::template row<2>(sp, t, w, scale);
+                    else RowDec<FMT>::template row<3>(sp, t, w, scale);
                   }
+                  const int R = warp * 16 + q + 8 * r;
+                  *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 4 * u + t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
+                  if (t == 0) scs[u * 128 + R] = scale;
                 }
               }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(A_FULL(sa));
-            s[0] += 2 * ATOM_BYTES; s[1] += 2 * ATOM_BYTES;
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
+          if (lane == 0) { mbar_arrive(A_FULL(sa)); mbar_arrive(RAW_EMPTY(sr)); }
         }
       }
     } else if (warp == LTC_DQW) {
@@ -273,22 +269,40 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
       }
       __syncwarp();
     } else if (warp == LTC_DQW + 1) {
-      // ================= activation-tile loader =================
+      // ================= loader: raw weight boxes (may run ahead into the next item) + activation tiles =================
       if (lane == 0) {
         const uint8_t* src = reinterpret_cast<const uint8_t*>(ximg) + (size_t)grp * BN * K * 2;
-        for (int h = 0; h < 2; ++h) {
-          for (int st = 0; st < nks; ++st) {
-            const int it = it_base + h * nks + st;
-            const int sb = it % LTC_BST;
-            bool ok = true;
-            if (it >= LTC_BST) ok = wait_or_abort(DONE((it - LTC_BST) % LTC_DONE), (uint32_t)(((it - LTC_BST) / LTC_DONE) & 1));
-            if (ok) {
-              mbar_arrive_expect_tx(B_FULL(sb), (uint32_t)S::B_STAGE);
-              bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)st * S::B_STAGE,
-                       (uint32_t)S::B_STAGE, B_FULL(sb));
-            }
+        int nb = it_base;                                       // next activation stage to request
+        const int nb_end = it_base + 2 * nks;
+        const int raw_need = min(total_stages, nb_end);          // every raw stage of this item must be requested here
+        int idle = 0;
+        while ((nb < nb_end || raw_next < raw_need) && idle < (1 << 22)) {
+          bool progressed = false;
+          if (raw_next < total_stages &&
+              (raw_next < RST || mbar_try_wait(RAW_EMPTY(raw_next % RST), (uint32_t)((raw_next / RST - 1) & 1)))) {
+            const int jj = raw_next / (2 * nks), rem = raw_next % (2 * nks);
+            const int row0 = (item_of(jj) / groups) * LMH_TILE + (rem / nks) * 128;
+            const int st = rem % nks;
+            const int sr = raw_next % RST;
+            mbar_arrive_expect_tx(RAW_FULL(sr), (uint32_t)C::RAW_STAGE);
+            tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), &wmap,
+                       (int)(((uint32_t)(st * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
+            ++raw_next;
+            progressed = true;
           }
+          if (nb < nb_end && (nb < LTC_BST || mbar_try_wait(DONE((nb - LTC_BST) % LTC_DONE), (uint32_t)(((nb - LTC_BST) / LTC_DONE) & 1)))) {
+            const int sb = nb % LTC_BST;
+            const int st = (nb - it_base) % nks;
+            mbar_arrive_expect_tx(B_FULL(sb), (uint32_t)S::B_STAGE);
+            bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)st * S::B_STAGE,
+                     (uint32_t)S::B_STAGE, B_FULL(sb));
+            ++nb;
+            progressed = true;
+          }
+          if (progressed) idle = 0;
+          else if (((++idle) & 63) == 0 && *abort_flag) break;
         }
+        if ((nb < nb_end || raw_next < raw_need) && !*abort_flag) { atomicExch(err_flag, 3); *abort_flag = 1; }
       }
       __syncwarp();
     } else {
@@ -382,12 +396,11 @@ lmh_tc_kernel(const __half* __restrict__ ximg, const float* __restrict__ rowscal
     tc_fence_after();
   }
 
-  // on an aborted run, raw copies that were issued but never consumed may still be in flight
-  if (warp < LTC_DQW && *abort_flag) {
-    for (int i = raw_done; i < raw_issued; ++i) {
-      ws.dead = false;
-      ws.wait(i % C::RST, (uint32_t)((i / C::RST) & 1));
-    }
+  // on an aborted run, raw boxes that were requested but never consumed may still be in flight
+  if (warp == LTC_DQW + 1 && lane == 0 && *abort_flag) {
+    for (int i = max(0, raw_next - RST); i < raw_next; ++i)
+      for (int k = 0; k < (1 << 20); ++k)
+        if (mbar_try_wait(RAW_FULL(i % RST), (uint32_t)((i / RST) & 1))) break;
   }
 
   // padding tiles of a short shard carry absent partials
