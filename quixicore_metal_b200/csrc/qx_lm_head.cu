@@ -23,7 +23,7 @@ namespace qx {
 
 constexpr int LMH_TILE = 256;
 constexpr int LMH_TB = 8;        // hidden rows per stage-1 CTA
-constexpr int LMH_RED_THREADS = 512;
+constexpr int LMH_RED_THREADS = 1024;
 
 // Order-preserving map float -> uint32 (larger float = larger key; +0 and -0 share a key).
 __device__ __forceinline__ uint32_t float_key(float v) {
@@ -590,6 +590,17 @@ __device__ __forceinline__ float block_sum(float v, BlockScratch& s) {
   v = lane < nw ? s.fv[lane] : 0.f;
   return warp_sum(v);
 }
+// sum of f and bitwise OR of u over the block, one pair of barriers
+__device__ __forceinline__ void block_sum_or(float& f, unsigned& u, BlockScratch& s) {
+  f = warp_sum(f);
+  u = __reduce_or_sync(0xffffffffu, u);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) { s.fv[warp] = f; s.iv[warp] = (int)u; }
+  __syncthreads();
+  f = warp_sum(lane < nw ? s.fv[lane] : 0.f);
+  u = __reduce_or_sync(0xffffffffu, lane < nw ? (unsigned)s.iv[lane] : 0u);
+}
 __device__ __forceinline__ float block_max(float v, BlockScratch& s) {
   v = warp_max(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -785,8 +796,19 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
     const float mid = 0.5f * (lo + hi);
     float sm = 0.f;
     if (cached) {
-      for (long long j = tid; j < ncand; j += nth)
-        if (c_ls[j] >= mid) sm += c_ex[j];
+      // Also note whether any candidate lies in each half of [lo, hi): once the half that is kept
+      // holds none, further halvings cannot change the set {ls >= lo}, and the search stops.
+      unsigned fl = 0u;
+      const int n = (int)ncand;
+      for (int j = tid; j < n; j += nth) {
+        const float ls = c_ls[j];
+        if (ls >= mid) { sm += c_ex[j]; fl |= ls < hi ? 2u : 0u; }
+        else fl |= ls >= lo ? 1u : 0u;
+      }
+      block_sum_or(sm, fl, S);
+      if (sm / Z >= top_p) { lo = mid; if (!(fl & 2u)) break; }
+      else { hi = mid; if (!(fl & 1u)) break; }
+      continue;
     } else {
       for (long long j = tid; j < ncand; j += nth) {
         const float ls = cv(j) * invtemp;

@@ -15,11 +15,11 @@
 //     buffers are handed over in pairs (one swizzle atom = two units) through a ring of three
 //     pairs.  nvfp4 folds its scale into the f16 weight (exact) and accumulates the whole row in
 //     place.
-//   * eight scale warps (two per TMEM lane quarter, each taking half of the hidden rows; a thread
-//     owns one vocabulary row) read each unit buffer back and add scale * partial into fp32
-//     registers: the result is the fp32 dequantise-then-dot up to summation order.  At the end
-//     of a half they park the row's logits in TMEM.
-// When both halves are done the scale warps move the logits to shared memory (the idle operand
+//   * the same worker warps, as scale warps (four per TMEM lane quarter, each taking a quarter of
+//     the hidden rows; a thread owns one vocabulary row), read each unit buffer back and add
+//     scale * partial into fp32 registers: the result is the fp32 dequantise-then-dot up to
+//     summation order.  At the end of a half they park the row's logits in TMEM.
+// When both halves are done the worker warps move the logits to shared memory (the idle operand
 // ring), where all warps run the per-tile selection.
 // Every mbarrier wait is bounded; on expiry the CTA raises the device error flag, stops issuing
 // work, runs its loops to the end without waiting, frees its tensor memory and returns.
@@ -47,9 +47,8 @@ template <int FMT> struct LmhTcCfg {
   static constexpr bool POST = FMT != F_NVFP4;
 };
 
-constexpr int LTC_DQW = 8;                       // dequant warps (16 rows each)
-constexpr int LTC_SCW = 8;                       // scale warps
-constexpr int LTC_WARPS = LTC_DQW + 2 + LTC_SCW; // + MMA, loader
+constexpr int LTC_DQW = 16;                      // worker warps (8 rows each; also the scale warps)
+constexpr int LTC_WARPS = LTC_DQW + 2;           // + MMA, loader
 constexpr int LTC_AST = 2;                       // operand-stage ring depth (weights)
 constexpr int LTC_BST = 3;                       // operand-stage ring depth (activations)
 constexpr int LTC_DONE = 6;                      // "stage consumed" barrier ring (multiple of AST and BST)
@@ -96,7 +95,7 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
   using C = LmhTcCfg<FMT>;
   using S = LmhTcSmem<FMT, BN>;
   constexpr bool POST = C::POST;
-  constexpr int HB = BN / 2;                      // hidden rows per scale warp
+  constexpr int CW = BN / 4;                      // hidden rows per worker warp in its scale role
   constexpr int RST = C::RST;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -121,7 +120,7 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
     for (int s = 0; s < LTC_AST; ++s) mbar_init(A_FULL(s), LTC_DQW);
     for (int s = 0; s < LTC_BST; ++s) mbar_init(B_FULL(s), 1);
     for (int s = 0; s < LTC_DONE; ++s) mbar_init(DONE(s), 1);
-    for (int s = 0; s < LTC_NACC; ++s) { mbar_init(ACC_FULL(s), 1); mbar_init(ACC_EMPTY(s), LTC_SCW); }
+    for (int s = 0; s < LTC_NACC; ++s) { mbar_init(ACC_FULL(s), 1); mbar_init(ACC_EMPTY(s), LTC_DQW); }
     mbar_init(ACC_DONE, 1);
     for (int s = 0; s < RST; ++s) { mbar_init(RAW_FULL(s), 1); mbar_init(RAW_EMPTY(s), LTC_DQW); }
     *abort_flag = 0;
@@ -165,84 +164,131 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
     const int it_base = j * 2 * nks;                          // global operand-stage counter
 
     if (warp < LTC_DQW) {
-      // ================= dequant =================
-      const int q = ((lane >> 2) & 1) * 4 + (lane >> 3);      // row pair (q, q + 8) of this warp's 16
+      // ================= workers: decode stage `it`, then scale the accumulators of stage `it - 1` =================
+      const int q = ((lane >> 2) & 1) * 4 + (lane >> 3);      // this thread's row of the warp's 8
       const int t = lane & 3;
+      const int R = warp * 8 + q;                             // row inside the 128-row half (decode role)
       constexpr uint32_t ATOM_BYTES = 64 / F::BK * F::BB;     // packed bytes of 64 columns
+      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+      const int RS = (warp & 3) * 32 + lane;                  // row inside the half (scale role)
+      const int cg = warp >> 2;                               // which quarter of the hidden rows
+      float acc[CW];
+      auto scale_stage = [&](int it) {                          // both unit pairs of stage `it`
+        const int pg = it * 2;
+        const int buf0 = pg % LTC_NACC, buf1 = (pg + 1) % LTC_NACC;
+        bool ok = wait_or_abort(ACC_FULL(buf0), (uint32_t)((pg / LTC_NACC) & 1));
+        ok = wait_or_abort(ACC_FULL(buf1), (uint32_t)(((pg + 1) / LTC_NACC) & 1)) && ok;
+        tc_fence_after();
+        const uint32_t col = tmem_base + lane_sel + ACC_COL0 + (uint32_t)(cg * CW);
+        const float* scs = sc_ring + (size_t)((it * 4) % LTC_SCR) * 128 + RS;
+        const float sc0 = scs[0], sc1 = scs[128], sc2 = scs[256], sc3 = scs[384];
+        if (ok) {
+          uint32_t v0[CW], v1[CW], v2[CW], v3[CW];
+          tmem_ld_nowait<CW>(col + (uint32_t)(buf0 * 2 * BN), v0);
+          tmem_ld_nowait<CW>(col + (uint32_t)(buf0 * 2 * BN + BN), v1);
+          tmem_ld_nowait<CW>(col + (uint32_t)(buf1 * 2 * BN), v2);
+          tmem_ld_nowait<CW>(col + (uint32_t)(buf1 * 2 * BN + BN), v3);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(ACC_EMPTY(buf0)); mbar_arrive(ACC_EMPTY(buf1)); }
+#pragma unroll
+          for (int i = 0; i < CW; ++i) {
+            acc[i] = fmaf(sc0, __uint_as_float(v0[i]), acc[i]);
+            acc[i] = fmaf(sc1, __uint_as_float(v1[i]), acc[i]);
+            acc[i] = fmaf(sc2, __uint_as_float(v2[i]), acc[i]);
+            acc[i] = fmaf(sc3, __uint_as_float(v3[i]), acc[i]);
+          }
+        } else {
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(ACC_EMPTY(buf0)); mbar_arrive(ACC_EMPTY(buf1)); }
+        }
+      };
       for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < CW; ++i) acc[i] = 0.f;
         for (int st = 0; st < nks; ++st) {
           const int it = it_base + h * nks + st;
           const int sa = it % LTC_AST, sr = it % RST;
           const uint32_t off = (uint32_t)(st * C::CHUNK_BYTES) & 15u;
-          const uint32_t rbase = sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE) + off;
-          const uint32_t s[2] = {rbase + (uint32_t)((warp * 16 + q) * C::BOX), rbase + (uint32_t)((warp * 16 + q + 8) * C::BOX)};
+          const uint32_t sp0 = sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE) + off + (uint32_t)(R * C::BOX);
           wait_or_abort(RAW_FULL(sr), (uint32_t)((it / RST) & 1));
           if (it >= LTC_AST) wait_or_abort(DONE((it - LTC_AST) % LTC_DONE), (uint32_t)(((it - LTC_AST) / LTC_DONE) & 1));
           uint8_t* a_stage = smem + S::OFF_A + (size_t)sa * S::A_STAGE;
+          if constexpr (FMT == F_NVFP4) {
 #pragma unroll
-          for (int a = 0; a < 2; ++a) {                       // swizzle atom = 64 columns
-            uint8_t* a_atom = a_stage + a * S::A_ATOM;
-            if constexpr (FMT == F_NVFP4) {
-#pragma unroll
-              for (int r = 0; r < 2; ++r) {
-                uint32_t w[4][2];
-                GroupProc<F_NVFP4>::block(s[r] + a * ATOM_BYTES, t, w);
-                const int R = warp * 16 + q + 8 * r;
-                *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
-                *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t + 1)) = make_uint4(w[2][0], w[2][1], w[3][0], w[3][1]);
-              }
+            for (int a = 0; a < 2; ++a) {                     // swizzle atom = 64 columns
+              uint8_t* a_atom = a_stage + a * S::A_ATOM;
+              uint32_t w[4][2];
+              GroupProc<F_NVFP4>::block(sp0 + a * ATOM_BYTES, t, w);
+              *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
+              *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t + 1)) = make_uint4(w[2][0], w[2][1], w[3][0], w[3][1]);
+            }
+          } else {
+            // all shared-memory loads of the stage first (four units), then the conversions and stores
+            using RD = RowDec<FMT>;
+            constexpr bool WIDE = F::GROUP == 128;            // the unit's position inside the decode
+            uint32_t raw[4][RD::RAWN], scb[4];                // group fixes its byte alignment
+            RD::template load<0>(sp0, t, raw[0], scb[0]);
+            RD::template load<1>(sp0 + F::BB, t, raw[1], scb[1]);
+            if constexpr (WIDE) {
+              RD::template load<2>(sp0 + 2 * F::BB, t, raw[2], scb[2]);
+              RD::template load<3>(sp0 + 3 * F::BB, t, raw[3], scb[3]);
             } else {
-              float* scs = sc_ring + (size_t)((it * 4 + a * 2) % LTC_SCR) * 128;
+              RD::template load<0>(sp0 + 2 * F::BB, t, raw[2], scb[2]);
+              RD::template load<1>(sp0 + 3 * F::BB, t, raw[3], scb[3]);
+            }
+            float* scs = sc_ring + (size_t)((it * 4) % LTC_SCR) * 128;
 #pragma unroll
-              for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                  uint32_t w[2][2];
-                  float scale;
-                  // the unit's position inside the decode group fixes its byte alignment
-                  constexpr bool WIDE = F::GROUP == 128;
-                  const uint32_t sp = s[r] + (uint32_t)((2 * a + u) * F::BB);
-                  if (!WIDE || a == 0) {
-                    if (u == 0) RowDec<FMT>::template row<0>(sp, t, w, scale);
-                    else RowDec<FMT>::template row<1>(sp, t, w, scale);
-                  } else {
-                    if (u == 0) RowDec<FMT>::template row<2>(sp, t, w, scale);
-                    else RowDec<FMT>::template row<3>(sp, t, w, scale);
-                  }
-                  const int R = warp * 16 + q + 8 * r;
-                  *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 4 * u + t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
-                  if (t == 0) scs[u * 128 + R] = scale;
-                }
-              }
+            for (int u4 = 0; u4 < 4; ++u4) {                  // unit u4: atom u4 / 2, chunk group u4 % 2
+              uint32_t w[2][2];
+              RD::convert(raw[u4], w);
+              *reinterpret_cast<uint4*>(a_stage + (u4 >> 1) * S::A_ATOM + sw128_offset(R, 4 * (u4 & 1) + t)) =
+                  make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
+              if (t == 0) scs[u4 * 128 + R] = RD::scale(scb[u4]);
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) { mbar_arrive(A_FULL(sa)); mbar_arrive(RAW_EMPTY(sr)); }
+          if constexpr (POST) { if (st > 0) scale_stage(it - 1); }
+        }
+        if constexpr (POST) {
+          scale_stage(it_base + h * nks + nks - 1);
+          // park the row's logits of this half
+          uint32_t v[CW];
+#pragma unroll
+          for (int i = 0; i < CW; ++i) v[i] = __float_as_uint(acc[i]);
+          tmem_st<CW>(tmem_base + lane_sel + (uint32_t)(h * BN + cg * CW), v);
+          tmem_wait_st();
         }
       }
+      if constexpr (!POST) {
+        wait_or_abort(ACC_DONE, (uint32_t)(j & 1));
+        tc_fence_after();
+      }
     } else if (warp == LTC_DQW) {
-      // ================= MMA issuer =================
-      if (lane == 0) {
-        const uint32_t idesc = umma_idesc_f16(BN);
-        for (int h = 0; h < 2; ++h) {
-          for (int st = 0; st < nks; ++st) {
-            const int it = it_base + h * nks + st;
-            const int sa = it % LTC_AST, sb = it % LTC_BST;
-            bool ok = wait_or_abort(B_FULL(sb), (uint32_t)((it / LTC_BST) & 1));
-            ok = wait_or_abort(A_FULL(sa), (uint32_t)((it / LTC_AST) & 1)) && ok;
-            tc_fence_after();
-            const uint32_t a_base = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
-            const uint32_t b_base = sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE);
+      // ================= MMA issuer (the whole warp polls: the wake-up is faster; lane 0 issues) =================
+      const uint32_t idesc = umma_idesc_f16(BN);
+      for (int h = 0; h < 2; ++h) {
+        for (int st = 0; st < nks; ++st) {
+          const int it = it_base + h * nks + st;
+          const int sa = it % LTC_AST, sb = it % LTC_BST;
+          bool ok = wait_or_abort(B_FULL(sb), (uint32_t)((it / LTC_BST) & 1));
+          ok = wait_or_abort(A_FULL(sa), (uint32_t)((it / LTC_AST) & 1)) && ok;
+          tc_fence_after();
+          const uint32_t a_base = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
+          const uint32_t b_base = sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE);
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {                       // swizzle atom = pair of units
-              if constexpr (POST) {
-                const int pg = it * 2 + p;
-                const int buf = pg % LTC_NACC;
-                if (pg >= LTC_NACC) {
-                  ok = wait_or_abort(ACC_EMPTY(buf), (uint32_t)((pg / LTC_NACC - 1) & 1)) && ok;
-                  tc_fence_after();
-                }
+          for (int p = 0; p < 2; ++p) {                       // swizzle atom = pair of units
+            if constexpr (POST) {
+              const int pg = it * 2 + p;
+              const int buf = pg % LTC_NACC;
+              if (pg >= LTC_NACC) {
+                ok = wait_or_abort(ACC_EMPTY(buf), (uint32_t)((pg / LTC_NACC - 1) & 1)) && ok;
+                tc_fence_after();
+              }
+              if (lane == 0) {
                 if (ok) {
 #pragma unroll
                   for (int kk = 0; kk < 4; ++kk)
@@ -251,22 +297,23 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
                                umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc, kk & 1);
                 }
                 tc_commit(ACC_FULL(buf));
-              } else {
-                if (ok) {
+              }
+            } else {
+              if (lane == 0 && ok) {
 #pragma unroll
-                  for (int kk = 0; kk < 4; ++kk)
-                    tc_mma_f16(tmem_base + (uint32_t)(h * BN),
-                               umma_desc_sw128(a_base + (uint32_t)(p * S::A_ATOM + kk * 32)),
-                               umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc,
-                               (st | p | kk) != 0 ? 1u : 0u);
-                }
+                for (int kk = 0; kk < 4; ++kk)
+                  tc_mma_f16(tmem_base + (uint32_t)(h * BN),
+                             umma_desc_sw128(a_base + (uint32_t)(p * S::A_ATOM + kk * 32)),
+                             umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc,
+                             (st | p | kk) != 0 ? 1u : 0u);
               }
             }
-            tc_commit(DONE(it % LTC_DONE));
           }
+          if (lane == 0) tc_commit(DONE(it % LTC_DONE));
+          __syncwarp();
         }
-        if constexpr (!POST) tc_commit(ACC_DONE);
       }
+      if constexpr (!POST) { if (lane == 0) tc_commit(ACC_DONE); }
       __syncwarp();
     } else if (warp == LTC_DQW + 1) {
       // ================= loader: raw weight boxes (may run ahead into the next item) + activation tiles =================
@@ -305,60 +352,6 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
         if ((nb < nb_end || raw_next < raw_need) && !*abort_flag) { atomicExch(err_flag, 3); *abort_flag = 1; }
       }
       __syncwarp();
-    } else {
-      // ================= scale warps: thread = vocabulary row, warp = half of the hidden rows =================
-      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-      const int R = (warp & 3) * 32 + lane;
-      const int ch = (warp - (LTC_DQW + 2)) >> 2;               // which half of the hidden rows
-      if constexpr (POST) {
-        for (int h = 0; h < 2; ++h) {
-          float acc[HB];
-#pragma unroll
-          for (int i = 0; i < HB; ++i) acc[i] = 0.f;
-          for (int st = 0; st < nks; ++st) {
-            const int it = it_base + h * nks + st;
-#pragma unroll
-            for (int p = 0; p < 2; ++p) {
-              const int pg = it * 2 + p;
-              const int buf = pg % LTC_NACC;
-              const bool ok = wait_or_abort(ACC_FULL(buf), (uint32_t)((pg / LTC_NACC) & 1));
-              tc_fence_after();
-              const uint32_t col = tmem_base + lane_sel + ACC_COL0 + (uint32_t)(buf * 2 * BN + ch * HB);
-              const float sc0 = sc_ring[(size_t)((it * 4 + p * 2) % LTC_SCR) * 128 + R];
-              const float sc1 = sc_ring[(size_t)((it * 4 + p * 2 + 1) % LTC_SCR) * 128 + R];
-              if (ok) {
-#pragma unroll
-                for (int cb = 0; cb < HB / 16; ++cb) {
-                  uint32_t v0[16], v1[16];
-                  tmem_ld16_nowait(col + (uint32_t)(cb * 16), v0);
-                  tmem_ld16_nowait(col + (uint32_t)(BN + cb * 16), v1);
-                  tmem_wait_ld();
-#pragma unroll
-                  for (int i = 0; i < 16; ++i) {
-                    acc[cb * 16 + i] = fmaf(sc0, __uint_as_float(v0[i]), acc[cb * 16 + i]);
-                    acc[cb * 16 + i] = fmaf(sc1, __uint_as_float(v1[i]), acc[cb * 16 + i]);
-                  }
-                }
-              }
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(ACC_EMPTY(buf));
-            }
-          }
-          // park the row's logits of this half
-#pragma unroll
-          for (int cb = 0; cb < HB / 16; ++cb) {
-            uint32_t v[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(acc[cb * 16 + i]);
-            tmem_st16(tmem_base + lane_sel + (uint32_t)(h * BN + ch * HB + cb * 16), v);
-          }
-          tmem_wait_st();
-        }
-      } else {
-        wait_or_abort(ACC_DONE, (uint32_t)(j & 1));
-        tc_fence_after();
-      }
     }
 
     // ---- logits of both halves are in TMEM columns [0, 2 BN); the operand ring is idle ----
@@ -367,23 +360,20 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
     tc_fence_after();
     const int v0 = tile * LMH_TILE;
     const int nvalid = min(LMH_TILE, V - v0);
-    if (warp >= LTC_DQW + 2) {
+    if (warp < LTC_DQW) {
       const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-      const int R = (warp & 3) * 32 + lane;
-      const int ch = (warp - (LTC_DQW + 2)) >> 2;
+      const int RS = (warp & 3) * 32 + lane;
+      const int cg = warp >> 2;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        uint32_t v[CW];
+        tmem_ld_nowait<CW>(tmem_base + lane_sel + (uint32_t)(h * BN + cg * CW), v);
+        tmem_wait_ld();
 #pragma unroll
-        for (int cb = 0; cb < HB / 16; ++cb) {
-          uint32_t v[16];
-          tmem_ld16_nowait(tmem_base + lane_sel + (uint32_t)(h * BN + ch * HB + cb * 16), v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = ch * HB + cb * 16 + i;
-            const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
-            logit[m * LMH_TILE + h * 128 + R] = __uint_as_float(v[i]) * rs;
-          }
+        for (int i = 0; i < CW; ++i) {
+          const int m = cg * CW + i;
+          const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
+          logit[m * LMH_TILE + h * 128 + RS] = __uint_as_float(v[i]) * rs;
         }
       }
     }

@@ -223,36 +223,59 @@ template <> struct RowDec<F_Q8_0> {
     p01 = h2sub(__byte_perm(u, 0x64646464u, 0x4140), 0x64806480u);
     p23 = h2sub(__byte_perm(u, 0x64646464u, 0x4342), 0x64806480u);
   }
+  // load<J> / convert / scale: the two halves of row<J>, for callers that want all the shared-memory
+  // loads of a stage in flight before the first conversion
+  static constexpr int RAWN = 2;
   template <int J>
-  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
-    scale = f16lo_to_f32(lds16(s));
-    uint32_t w0, w1;
+  __device__ __forceinline__ static void load(uint32_t s, int t, uint32_t (&raw)[2], uint32_t& sc) {
+    sc = lds16(s);
     if constexpr ((J & 1) == 0) {            // block starts 4-aligned: codes at +2 straddle words
       const uint32_t p = s + 8 * t;
       const uint32_t x0 = lds32(p), x1 = lds32(p + 4), x2 = lds32(p + 8);
-      w0 = __funnelshift_r(x0, x1, 16); w1 = __funnelshift_r(x1, x2, 16);
+      raw[0] = __funnelshift_r(x0, x1, 16); raw[1] = __funnelshift_r(x1, x2, 16);
     } else {                                 // block starts at 2 mod 4: codes are word aligned
       const uint32_t p = s + 2 + 8 * t;
-      w0 = lds32(p); w1 = lds32(p + 4);
+      raw[0] = lds32(p); raw[1] = lds32(p + 4);
     }
-    word(w0, a[0][0], a[0][1]);
-    word(w1, a[1][0], a[1][1]);
+  }
+  __device__ __forceinline__ static void convert(const uint32_t (&raw)[2], uint32_t (&a)[2][2]) {
+    word(raw[0], a[0][0], a[0][1]);
+    word(raw[1], a[1][0], a[1][1]);
+  }
+  __device__ __forceinline__ static float scale(uint32_t sc) { return f16lo_to_f32(sc); }
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& sc_out) {
+    uint32_t raw[2], sc;
+    load<J>(s, t, raw, sc);
+    convert(raw, a);
+    sc_out = scale(sc);
   }
 };
 
 template <> struct RowDec<F_Q4_0> {
   // thread t owns code bytes 4t..4t+3: low nibbles = columns 4t.., high nibbles = columns 16+4t..
   // A nibble OR-ed under the f16 exponent of 1024 is 1024+n (bits 0-3) or 1024+16n (bits 4-7).
+  static constexpr int RAWN = 1;
   template <int J>
-  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
-    scale = f16lo_to_f32(lds16(s));
-    uint32_t w;
+  __device__ __forceinline__ static void load(uint32_t s, int t, uint32_t (&raw)[1], uint32_t& sc) {
+    sc = lds16(s);
     if constexpr ((J & 1) == 0) {
       const uint32_t p = s + 4 * t;
-      w = __funnelshift_r(lds32(p), lds32(p + 4), 16);
+      raw[0] = __funnelshift_r(lds32(p), lds32(p + 4), 16);
     } else {
-      w = lds32(s + 2 + 4 * t);
+      raw[0] = lds32(s + 2 + 4 * t);
     }
+  }
+  __device__ __forceinline__ static float scale(uint32_t sc) { return f16lo_to_f32(sc); }
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& sc_out) {
+    uint32_t raw[1], sc;
+    load<J>(s, t, raw, sc);
+    convert(raw, a);
+    sc_out = scale(sc);
+  }
+  __device__ __forceinline__ static void convert(const uint32_t (&raw)[1], uint32_t (&a)[2][2]) {
+    const uint32_t w = raw[0];
     const uint32_t w8 = w >> 8;
     a[0][0] = h2sub((w & 0x000F000Fu) | 0x64006400u, 0x64086408u);                  // bytes 0,2 low
     a[1][0] = h2fma((w & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);     // bytes 0,2 high
@@ -267,16 +290,27 @@ __device__ __forceinline__ float e8m0_scale(uint32_t e) {
 
 template <> struct RowDec<F_MXFP4> {
   // thread t owns code bytes 4t..4t+3; byte i converts to the pair (column 4t+i, column 16+4t+i)
+  static constexpr int RAWN = 1;
   template <int J>
-  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
-    scale = e8m0_scale(lds8(s));
+  __device__ __forceinline__ static void load(uint32_t s, int t, uint32_t (&raw)[1], uint32_t& sc) {
+    sc = lds8(s);
     constexpr int SH = (J + 1) & 3;          // (17*J + 1) mod 4
     const uint32_t p = s + 1 + 4 * t - SH;
-    uint32_t w;
-    if constexpr (SH == 0) w = lds32(p);
-    else w = __funnelshift_r(lds32(p), lds32(p + 4), 8 * SH);
+    if constexpr (SH == 0) raw[0] = lds32(p);
+    else raw[0] = __funnelshift_r(lds32(p), lds32(p + 4), 8 * SH);
+  }
+  __device__ __forceinline__ static void convert(const uint32_t (&raw)[1], uint32_t (&a)[2][2]) {
+    const uint32_t w = raw[0];
     a[0][0] = cvt_e2m1x2<0>(w); a[0][1] = cvt_e2m1x2<1>(w);
     a[1][0] = cvt_e2m1x2<2>(w); a[1][1] = cvt_e2m1x2<3>(w);
+  }
+  __device__ __forceinline__ static float scale(uint32_t sc) { return e8m0_scale(sc); }
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& sc_out) {
+    uint32_t raw[1], sc;
+    load<J>(s, t, raw, sc);
+    convert(raw, a);
+    sc_out = scale(sc);
   }
 };
 
@@ -297,19 +331,29 @@ template <> struct RowDec<F_MXFP8> {
       p23 = cvt_e4m3x2<1>(w);
     }
   }
+  static constexpr int RAWN = 2;
   template <int J>
-  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& scale) {
-    scale = e8m0_scale(lds8(s));
+  __device__ __forceinline__ static void load(uint32_t s, int t, uint32_t (&raw)[2], uint32_t& sc) {
+    sc = lds8(s);
     constexpr int SH = (J + 1) & 3;          // (33*J + 1) mod 4
     const uint32_t p = s + 1 + 8 * t - SH;
-    uint32_t w0, w1;
-    if constexpr (SH == 0) { w0 = lds32(p); w1 = lds32(p + 4); }
+    if constexpr (SH == 0) { raw[0] = lds32(p); raw[1] = lds32(p + 4); }
     else {
       const uint32_t x0 = lds32(p), x1 = lds32(p + 4), x2 = lds32(p + 8);
-      w0 = __funnelshift_r(x0, x1, 8 * SH); w1 = __funnelshift_r(x1, x2, 8 * SH);
+      raw[0] = __funnelshift_r(x0, x1, 8 * SH); raw[1] = __funnelshift_r(x1, x2, 8 * SH);
     }
-    word(w0, a[0][0], a[0][1]);
-    word(w1, a[1][0], a[1][1]);
+  }
+  __device__ __forceinline__ static void convert(const uint32_t (&raw)[2], uint32_t (&a)[2][2]) {
+    word(raw[0], a[0][0], a[0][1]);
+    word(raw[1], a[1][0], a[1][1]);
+  }
+  __device__ __forceinline__ static float scale(uint32_t sc) { return e8m0_scale(sc); }
+  template <int J>
+  __device__ __forceinline__ static void row(uint32_t s, int t, uint32_t (&a)[2][2], float& sc_out) {
+    uint32_t raw[2], sc;
+    load<J>(s, t, raw, sc);
+    convert(raw, a);
+    sc_out = scale(sc);
   }
 };
 
