@@ -23,8 +23,16 @@ import sys
 import threading
 import time
 
-# keep stdout to the one JSON line: NCCL's banner / debug output goes to stderr
-os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
+# Keep stdout to the one JSON line: libraries (NCCL's version banner, debug output) write to file
+# descriptor 1 directly, so descriptor 1 is pointed at stderr for the whole run and the JSON line
+# goes to a saved duplicate of the original stdout.
+sys.stdout.flush()
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit_json_line(obj) -> None:
+    os.write(_REAL_STDOUT, (json.dumps(obj) + "\n").encode())
 
 import numpy as np
 import torch
@@ -168,7 +176,7 @@ def run_reference(args, rank: int):
         "note": "the reference's kernels are Metal-only; this arm times its dequantise -> torch-CPU matmul -> "
                 "sampler composition as restated in oracle/ on the host cores",
     }
-    print(json.dumps(line), flush=True)
+    emit_json_line(line)
 
 
 def workload_config(n_gpus: int):
@@ -439,7 +447,7 @@ def main():
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     else:
         line["cpu_baseline"] = None
-    print(json.dumps(line), flush=True)
+    emit_json_line(line)
     if world > 1:
         dist.barrier(); dist.destroy_process_group()
 

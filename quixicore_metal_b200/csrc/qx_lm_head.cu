@@ -377,8 +377,60 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
 }
 
 }  // namespace qx
-#include "qx_lm_head_tc.cuh"
+#include "qx_tc_pipeline.cuh"
 namespace qx {
+
+// Epilogue of the tensor-core pipeline for LM-head stage 1: the worker warps move the logits of the
+// item's 256 vocabulary rows to shared memory ([hidden row][256]), then every warp reduces hidden
+// rows to their tile partials.
+template <int BN>
+struct LmhEpi {
+  struct Args {
+    const float* bias;
+    float* part_val; int32_t* part_id; float* part_lse;
+    int T_total, V;
+    long long vocab_offset, tiles_stride;
+    int mode, topk;
+    float invtemp;
+    uint32_t seed;
+  };
+  static constexpr bool DUAL = false;
+  __device__ __forceinline__ static void run(const Args& a, const TcItem& it) {
+    constexpr int CW = BN / 4;
+    if (it.warp < LTC_DQW) {
+      const uint32_t lane_sel = (uint32_t)((it.warp & 3) * 32) << 16;
+      const int RS = (it.warp & 3) * 32 + it.lane;
+      const int cg = it.warp >> 2;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[CW];
+        tmem_ld_nowait<CW>(it.tmem_base + lane_sel + (uint32_t)(h * BN + cg * CW), v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < CW; ++i) {
+          const int m = cg * CW + i;
+          const float rs = m < it.m_count ? it.rowscale[it.m_base + m] : 0.f;
+          it.smem_f32[m * LMH_TILE + h * 128 + RS] = __uint_as_float(v[i]) * rs;
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    const int v0 = it.tile * LMH_TILE;
+    const int nvalid = min(LMH_TILE, a.V - v0);
+    for (int m = it.warp; m < it.m_count; m += LTC_WARPS)
+      lmh_select_token(it.smem_f32 + m * LMH_TILE, nvalid, v0, a.vocab_offset, a.bias, it.m_base + m, it.tile,
+                       a.tiles_stride, a.mode, a.topk, a.invtemp, a.seed, a.part_val, a.part_id, a.part_lse,
+                       it.lane);
+  }
+  // padding tiles of a short shard carry absent partials
+  __device__ __forceinline__ static void tail(const Args& a, const float* scratch, int real_tiles, int warp, int lane) {
+    for (long long tile = real_tiles + blockIdx.x; tile < a.tiles_stride; tile += gridDim.x)
+      for (int m = warp; m < a.T_total; m += LTC_WARPS)
+        lmh_select_token(scratch, 0, 0, a.vocab_offset, nullptr, m, (int)tile, a.tiles_stride, a.mode,
+                         a.topk, a.invtemp, a.seed, a.part_val, a.part_id, a.part_lse, lane);
+  }
+};
 
 template <int FMT>
 static bool lmh_stream_ok(const LmHeadArgs& a) {
@@ -415,49 +467,19 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   note_launch();
 }
 
-// Tensor map over a packed weight matrix seen as V rows of 32-bit words, box = (box_bytes / 4) x 128
-// rows.  The driver entry point is looked up at run time, so the library does not link libcuda.
-typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                      CUtensorMapFloatOOBfill);
-static TensorMapEncodeFn tensor_map_encode_fn() {
-  static TensorMapEncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess) {
-      cudaGetLastError();
-      return (TensorMapEncodeFn) nullptr;
-    }
-    return (TensorMapEncodeFn)p;
-  }();
-  return fn;
-}
-static bool make_weight_map(CUtensorMap* map, const void* w, int64_t V, size_t row_bytes, int box_bytes) {
-  TensorMapEncodeFn enc = tensor_map_encode_fn();
-  if (!enc) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)V};
-  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), 128u};
-  const cuuint32_t estr[2] = {1u, 1u};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(w), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // tcgen05 form of stage 1 for more than 16 hidden rows.
 template <int FMT, int BN>
 static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
                              int64_t tiles_stride, int* err) {
-  using S = LmhTcSmem<FMT, BN>;
-  using C = LmhTcCfg<FMT>;
+  using S = TcSmem<FMT, BN>;
+  using C = TcCfg<FMT>;
+  using Epi = LmhEpi<BN>;
   static_assert(S::TOTAL <= 227 * 1024, "stage-1 tensor-core configuration exceeds shared memory");
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(lmh_tc_kernel<FMT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) {
+    if (cudaFuncSetAttribute(tc_pipeline_kernel<FMT, BN, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
@@ -478,9 +500,10 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   const long long items = (long long)real_tiles * groups;
   const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
-  lmh_tc_kernel<FMT, BN><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
-      wmap, ximg, rowscale, a.bias, pv, pi, pl, (int)a.T, (int)a.V, (int)a.K,
-      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
+  const typename Epi::Args ea{a.bias, pv, pi, pl, (int)a.T, (int)a.V, (long long)a.vocab_offset,
+                              (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed};
+  tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
+      wmap, wmap, ximg, rowscale, (int)a.T, (int)a.V, (int)a.K, err, ea);
   note_launch();
   if (must_free) cudaFreeAsync(scratch, st);
   return true;

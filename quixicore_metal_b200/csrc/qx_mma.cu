@@ -21,6 +21,7 @@
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
 #include "qx_tc.cuh"
+#include "qx_tc_pipeline.cuh"
 
 namespace qx {
 
@@ -252,8 +253,156 @@ static bool launch_tc_t(cudaStream_t st, const GemvArgs& a, int* err) {
   return true;
 }
 
-// Preconditions of the tcgen05 path.
+// ---- projections on the shared tensor-core pipeline (qx_tc_pipeline.cuh) ---------------------------
+// Epilogue: thread = one output channel n of the item, CW activation rows; 32 lanes store 32
+// consecutive channels of one row.  Linear: y = act(v * rowscale + bias) (+ residual); an item is
+// 256 channels.  SwiGLU: half 0 = gate rows, half 1 = up rows of the same 128 channels,
+// y = silu(gate) * up.  Raw fp32 dot products when `raw` is set (row-parallel partials).
+template <int BN, typename OT, bool DUAL_>
+struct ProjEpi {
+  struct Args {
+    const OT* bias0; const OT* bias1; const OT* residual;
+    void* y;
+    int N, activation, use_bias, use_residual, raw;
+  };
+  static constexpr bool DUAL = DUAL_;
+  __device__ __forceinline__ static void run(const Args& a, const TcItem& it) {
+    constexpr int CW = BN / 4;
+    if (it.warp >= LTC_DQW) return;
+    const uint32_t lane_sel = (uint32_t)((it.warp & 3) * 32) << 16;
+    const int RS = (it.warp & 3) * 32 + it.lane;
+    const int cg = it.warp >> 2;
+    if constexpr (DUAL) {
+      uint32_t g[CW], u[CW];
+      tmem_ld_nowait<CW>(it.tmem_base + lane_sel + (uint32_t)(cg * CW), g);
+      tmem_ld_nowait<CW>(it.tmem_base + lane_sel + (uint32_t)(BN + cg * CW), u);
+      tmem_wait_ld();
+      const int n = it.tile * 128 + RS;
+      if (n < a.N) {
+        const float gb = a.use_bias ? to_f32<OT>(a.bias0[n]) : 0.f;
+        const float ub = a.use_bias ? to_f32<OT>(a.bias1[n]) : 0.f;
+#pragma unroll
+        for (int i = 0; i < CW; ++i) {
+          const int m = cg * CW + i;
+          if (m < it.m_count) {
+            const float rs = it.rowscale[it.m_base + m];
+            const float gv = __uint_as_float(g[i]) * rs + gb, uv = __uint_as_float(u[i]) * rs + ub;
+            reinterpret_cast<OT*>(a.y)[(size_t)(it.m_base + m) * a.N + n] = from_f32<OT>(silu(gv) * uv);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[CW];
+        tmem_ld_nowait<CW>(it.tmem_base + lane_sel + (uint32_t)(h * BN + cg * CW), v);
+        tmem_wait_ld();
+        const int n = it.tile * 256 + h * 128 + RS;
+        if (n < a.N) {
+          const float bv = (a.use_bias && !a.raw) ? to_f32<OT>(a.bias0[n]) : 0.f;
+#pragma unroll
+          for (int i = 0; i < CW; ++i) {
+            const int m = cg * CW + i;
+            if (m < it.m_count) {
+              const size_t o = (size_t)(it.m_base + m) * a.N + n;
+              const float dot = __uint_as_float(v[i]) * it.rowscale[it.m_base + m];
+              if (a.raw) {
+                reinterpret_cast<float*>(a.y)[o] = dot;
+              } else {
+                float val = apply_act(dot + bv, a.activation);
+                if (a.use_residual) val += to_f32<OT>(a.residual[o]);
+                reinterpret_cast<OT*>(a.y)[o] = from_f32<OT>(val);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ static void tail(const Args&, const float*, int, int, int) {}
+};
+
+template <int FMT, int BN, typename OT, bool DUAL>
+static bool launch_pipeline_bn(cudaStream_t st, const GemvArgs& a, int* err) {
+  using S = TcSmem<FMT, BN>;
+  using C = TcCfg<FMT>;
+  using Epi = ProjEpi<BN, OT, DUAL>;
+  static_assert(S::TOTAL <= 227 * 1024, "tensor-core pipeline configuration exceeds shared memory");
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(tc_pipeline_kernel<FMT, BN, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    attr_set[dev] = true;
+  }
+  const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
+  CUtensorMap map0, map1;
+  if (!make_weight_map(&map0, a.w0, a.N, row_bytes, C::BOX)) return false;
+  if (DUAL) { if (!make_weight_map(&map1, a.w1, a.N, row_bytes, C::BOX)) return false; }
+  else map1 = map0;
+  const int groups = (int)((a.M + BN - 1) / BN);
+  const size_t img_bytes = ((size_t)groups * BN * a.K * 2 + 255) & ~(size_t)255;
+  bool must_free = false;
+  void* scratch = stream_scratch(st, img_bytes + (size_t)a.M * 4, &must_free);
+  if (!scratch) return false;
+  __half* ximg = (__half*)scratch;
+  float* rowscale = (float*)((char*)scratch + img_bytes);
+  launch_prep_activations(st, a.x, a.dtype, ximg, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM, BN);
+  note_launch();
+  const int item_rows = DUAL ? 128 : 256;
+  const long long items = (long long)((a.N + item_rows - 1) / item_rows) * groups;
+  const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
+  const typename Epi::Args ea{(const OT*)a.bias0, (const OT*)a.bias1, (const OT*)a.residual, a.y, (int)a.N,
+                              a.activation, a.use_bias, a.use_residual, a.out_f32};
+  tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
+      map0, map1, ximg, rowscale, (int)a.M, (int)a.N, (int)a.K, err, ea);
+  note_launch();
+  if (must_free) cudaFreeAsync(scratch, st);
+  return true;
+}
+
+template <int FMT, typename OT>
+static bool launch_pipeline_fmt(cudaStream_t st, const GemvArgs& a, int* err) {
+  if (a.w1) {
+    if (a.M <= 32) return launch_pipeline_bn<FMT, 32, OT, true>(st, a, err);
+    return launch_pipeline_bn<FMT, 64, OT, true>(st, a, err);
+  }
+  if (a.M <= 32) return launch_pipeline_bn<FMT, 32, OT, false>(st, a, err);
+  return launch_pipeline_bn<FMT, 64, OT, false>(st, a, err);
+}
+
+// bf16 / f16 activations, batch > 16, 128-column multiples, 16-byte aligned rows, at least one
+// full 128-row box; q6_K stays on the term-split kernel below.
+static bool pipeline_ok(const GemvArgs& a) {
+  if (a.dtype != QX_DTYPE_BF16 && a.dtype != QX_DTYPE_F16) return false;
+  if (a.M <= 16 || a.format == F_Q6_K || a.K % 128 != 0 || a.N < 128) return false;
+  const size_t row_bytes = (size_t)(a.K / block_k_of(a.format)) * block_bytes_of(a.format);
+  if (row_bytes % 16 != 0 || ((uintptr_t)a.w0 & 15) != 0 || (a.w1 && ((uintptr_t)a.w1 & 15) != 0)) return false;
+  static const bool enabled = [] {
+    const char* e = getenv("QX_TC_PIPELINE");
+    return !(e && e[0] == '0');
+  }();
+  return enabled;
+}
+
+template <typename OT>
+static bool launch_pipeline(cudaStream_t st, const GemvArgs& a, int* err) {
+  switch (a.format) {
+    case F_Q4_0: return launch_pipeline_fmt<F_Q4_0, OT>(st, a, err);
+    case F_Q8_0: return launch_pipeline_fmt<F_Q8_0, OT>(st, a, err);
+    case F_MXFP8: return launch_pipeline_fmt<F_MXFP8, OT>(st, a, err);
+    case F_NVFP4: return launch_pipeline_fmt<F_NVFP4, OT>(st, a, err);
+    case F_MXFP4: return launch_pipeline_fmt<F_MXFP4, OT>(st, a, err);
+    default: return false;
+  }
+}
+
+// Preconditions of the tcgen05 paths.
 bool tc_path_ok(const GemvArgs& a) {
+  if (pipeline_ok(a)) return true;
   if (a.dtype != QX_DTYPE_BF16 || a.M <= 16) return false;
   if (a.w1 && (((uintptr_t)a.w1 & 15) != 0)) return false;
   if (a.K % 256 != 0 || ((uintptr_t)a.x & 15) != 0 || ((uintptr_t)a.w0 & 15) != 0) return false;
@@ -300,6 +449,13 @@ void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, 
 bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a) {
   int* err = device_error_flag();
   if (!err) return false;
+  if (pipeline_ok(a)) {
+    const bool ok = a.out_f32 ? launch_pipeline<float>(st, a, err)       // OT only types bias / residual, unused here
+                  : a.dtype == QX_DTYPE_F16 ? launch_pipeline<__half>(st, a, err)
+                                            : launch_pipeline<__nv_bfloat16>(st, a, err);
+    if (ok) return true;
+  }
+  if (a.dtype != QX_DTYPE_BF16 || a.K % 256 != 0) return false;
   if (a.w1) {
     // SwiGLU at batch > 16: two fp32 projections into stream-ordered scratch, then the gate
     const size_t bytes = (size_t)a.M * a.N * sizeof(float);

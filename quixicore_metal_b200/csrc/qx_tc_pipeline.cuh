@@ -1,26 +1,36 @@
-// LM head stage 1 for 17..64 hidden rows per pass: tcgen05 tensor-core form.
+// Packed-weight projection for 17..64 activation rows per pass on the 5th-generation tensor cores:
+// the pipeline shared by LM-head stage 1 (`lm_head_sample`) and by `decode_linear_epilogue` /
+// `decode_swiglu` at batch > 16.  What happens to the finished accumulators is an epilogue policy.
 //
-// Shape: logits[v, m] = sum_k W[v, k] * x[m, k].  The vocabulary rows are the M-mode of the MMA
-// (128 rows per instruction), the hidden rows its N-mode (BN = 32 or 64), f16 x f16 -> fp32 in
-// tensor memory.  A CTA owns one 256-row vocabulary tile at a time and runs its two 128-row halves
-// one after the other, 128 columns (two 128-byte swizzle atoms) per operand stage.  Warp roles:
-//   * DQW dequant warps.  Each streams its own 128 / DQW rows with bulk async copies into a private
-//     ring (the per-warp weight stream of qx_stream.cuh), decodes the codes with the same exact
-//     f16 sequences as the small-batch path and stores them, UNSCALED, as a K-major 128-byte-
-//     swizzled operand tile (64 columns per stage).  The block scales go to a small ring.
-//   * one loader thread copies the matching activation tile (prepared once per call as row-scaled
-//     f16 in the decoders' column order, already in operand-tile layout) with one bulk copy.
-//   * one MMA thread issues tcgen05.mma.  For the formats whose scale is applied afterwards
-//     (q8_0, q4_0, mxfp4, mxfp8) every 32-column unit accumulates into its own TMEM buffer; the
-//     buffers are handed over in pairs (one swizzle atom = two units) through a ring of three
-//     pairs.  nvfp4 folds its scale into the f16 weight (exact) and accumulates the whole row in
-//     place.
-//   * the same worker warps, as scale warps (four per TMEM lane quarter, each taking a quarter of
-//     the hidden rows; a thread owns one vocabulary row), read each unit buffer back and add
-//     scale * partial into fp32 registers: the result is the fp32 dequantise-then-dot up to
-//     summation order.  At the end of a half they park the row's logits in TMEM.
-// When both halves are done the worker warps move the logits to shared memory (the idle operand
-// ring), where all warps run the per-tile selection.
+// Shape: out[n, m] = sum_k W[n, k] * x[m, k].  The weight rows are the M-mode of the MMA (128 rows
+// per instruction), the activation rows its N-mode (BN = 32 or 64), f16 x f16 -> fp32 in tensor
+// memory.  A CTA owns one work item at a time: two blocks of 128 weight rows ("halves": the two
+// halves of a 256-row tile, or the gate and up rows of a SwiGLU tile) for one group of BN
+// activation rows, run one after the other, 128 columns (two 128-byte swizzle atoms) per operand
+// stage.  Warp roles:
+//   * one loader thread.  Per stage it fetches the packed bytes of 128 rows x 128 columns with ONE
+//     2-D TMA box copy (tensor map over the weight matrix as rows of 32-bit words; rows past the
+//     end of the matrix arrive as zeros) into a ring of raw stages, and the matching activation
+//     tile (prepared once per call as row-scaled f16 in the decoders' column order, already in
+//     operand-tile layout) with one bulk copy.  A bulk copy costs its issuing thread 60-120
+//     cycles whatever its size, so one box per stage instead of one copy per row matters.
+//   * 16 worker warps.  Each decodes 8 rows of every stage with the same exact f16 sequences as
+//     the small-batch path and stores them, UNSCALED, as a K-major 128-byte-swizzled operand
+//     tile (the block scales go to a small ring); then it turns to the accumulators of the
+//     PREVIOUS stage (see below), so that a warp always has work while the tensor core runs the
+//     stage it has just produced.
+//   * the MMA warp (all lanes poll the barriers - the wake-up is faster - lane 0 issues
+//     tcgen05.mma).  For the formats whose scale is applied afterwards (q8_0, q4_0, mxfp4, mxfp8)
+//     every 32-column unit accumulates into its own TMEM buffer; the buffers are handed over in
+//     pairs (one swizzle atom = two units) through a ring of three pairs.  nvfp4 folds its scale
+//     into the f16 weight (exact) and accumulates the whole row in place.
+//   * the worker warps again, as scale warps (four per TMEM lane quarter, each taking a quarter
+//     of the activation rows; a thread owns one weight row): they read the unit buffers back and
+//     add scale * partial into fp32 registers: the result is the fp32 dequantise-then-dot up to
+//     summation order.  At the end of a half they park the row's sums in TMEM.
+// When both halves are done the results of both sit in tensor memory and the epilogue policy runs
+// (LM head: through shared memory - the idle operand ring - into the per-tile selection;
+// projections: bias / activation / residual or the SwiGLU gate, straight to global memory).
 // Every mbarrier wait is bounded; on expiry the CTA raises the device error flag, stops issuing
 // work, runs its loops to the end without waiting, frees its tensor memory and returns.
 #pragma once
@@ -35,7 +45,7 @@ namespace qx {
 // inside the row but not of 16, so the box starts at the 16-byte boundary below and is wide
 // enough for the largest misalignment; the box width is an odd multiple of 16 bytes, which puts
 // the 8 rows a warp instruction touches in different bank groups.
-template <int FMT> struct LmhTcCfg {
+template <int FMT> struct TcCfg {
   using F = StreamFmt<FMT>;
   static constexpr int CHUNK_BYTES = 128 / F::BK * F::BB;
   static constexpr int G16 = (CHUNK_BYTES % 16 == 0) ? 16 : ((CHUNK_BYTES % 8 == 0) ? 8 : 4);
@@ -57,8 +67,8 @@ constexpr int LTC_SCR = 16;                      // scale ring depth in units (4
 constexpr int LTC_KS = 128;                      // columns per operand stage (two swizzle atoms)
 
 template <int FMT, int BN>
-struct LmhTcSmem {
-  using C = LmhTcCfg<FMT>;
+struct TcSmem {
+  using C = TcCfg<FMT>;
   static constexpr int A_ATOM = 128 * 128;
   static constexpr int B_ATOM = BN * 128;
   static constexpr int A_STAGE = 2 * A_ATOM;
@@ -72,7 +82,7 @@ struct LmhTcSmem {
   // acc_done raw_full[RST] raw_empty[RST], then the TMEM slot and the abort flag
   static constexpr int NBARS = LTC_AST + LTC_BST + LTC_DONE + 2 * LTC_NACC + 1 + 2 * C::RST;
   static constexpr int TOTAL = OFF_BAR + NBARS * 8 + 16 + 1024;     // + alignment slack
-  static_assert(BN * LMH_TILE * 4 <= LTC_AST * A_STAGE, "logit buffer must fit the operand ring");
+  static_assert(BN * 256 * 4 <= LTC_AST * A_STAGE, "a [BN][256] fp32 buffer must fit the operand ring");
   static_assert(C::RAW_STAGE % 128 == 0, "raw stages must keep the TMA destination aligned");
 };
 
@@ -83,17 +93,29 @@ __device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int x
       : "memory");
 }
 
-template <int FMT, int BN>
+// What an epilogue policy sees of the finished item.  TMEM columns [0, BN) hold the fp32
+// accumulators of half 0, [BN, 2 BN) of half 1 (lane = weight row inside the half, column =
+// activation row of the group), still in units of the row-scaled activations.
+struct TcItem {
+  uint32_t tmem_base;
+  float* smem_f32;          // [BN][256] floats of shared memory, free during the epilogue
+  const float* rowscale;    // per activation row of the whole call
+  int tile, m_base, m_count;
+  int warp, lane;
+};
+
+// Epi: struct Args (by-value kernel argument);
+//      static constexpr bool DUAL       half 1 reads the second weight matrix at the same rows
+//      static void run(args, item)      all warps call it after a CTA barrier; it may use CTA barriers
+//      static void tail(args, ...)      after the last item (LM head: absent partials of padding tiles)
+template <int FMT, int BN, class Epi>
 __global__ void __launch_bounds__(LTC_WARPS * 32, 1)
-lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ ximg,
-              const float* __restrict__ rowscale, const float* __restrict__ bias,
-              float* __restrict__ part_val, int32_t* __restrict__ part_id,
-              float* __restrict__ part_lse, int T_total, int V, int K, long long vocab_offset,
-              long long tiles_stride, int mode, int topk, float invtemp, uint32_t seed,
-              int* __restrict__ err_flag) {
+tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
+                   const __half* __restrict__ ximg, const float* __restrict__ rowscale, int T_total,
+                   int V, int K, int* __restrict__ err_flag, const typename Epi::Args ea) {
   using F = StreamFmt<FMT>;
-  using C = LmhTcCfg<FMT>;
-  using S = LmhTcSmem<FMT, BN>;
+  using C = TcCfg<FMT>;
+  using S = TcSmem<FMT, BN>;
   constexpr bool POST = C::POST;
   constexpr int CW = BN / 4;                      // hidden rows per worker warp in its scale role
   constexpr int RST = C::RST;
@@ -132,7 +154,7 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: [0, BN) logits of half 0, [BN, 2 BN) of half 1, then NACC pairs of unit buffers
+  // TMEM columns: [0, BN) results of half 0, [BN, 2 BN) of half 1, then NACC pairs of unit buffers
   constexpr uint32_t ACC_COL0 = 2 * BN;
 
   // Bounded wait.  The CTA-wide abort flag is looked at only while spinning.
@@ -147,7 +169,8 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
   };
 
   const int groups = (T_total + BN - 1) / BN;                 // hidden-row groups (work items)
-  const int real_tiles = (V + LMH_TILE - 1) / LMH_TILE;
+  constexpr int ITEM_ROWS = Epi::DUAL ? 128 : 256;            // weight rows per work item
+  const int real_tiles = (V + ITEM_ROWS - 1) / ITEM_ROWS;
   const int items = real_tiles * groups;
   const int my_items = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nks = K / LTC_KS;                                 // operand stages per half
@@ -255,7 +278,7 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
         }
         if constexpr (POST) {
           scale_stage(it_base + h * nks + nks - 1);
-          // park the row's logits of this half
+          // park the row's sums of this half
           uint32_t v[CW];
 #pragma unroll
           for (int i = 0; i < CW; ++i) v[i] = __float_as_uint(acc[i]);
@@ -328,11 +351,12 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
           if (raw_next < total_stages &&
               (raw_next < RST || mbar_try_wait(RAW_EMPTY(raw_next % RST), (uint32_t)((raw_next / RST - 1) & 1)))) {
             const int jj = raw_next / (2 * nks), rem = raw_next % (2 * nks);
-            const int row0 = (item_of(jj) / groups) * LMH_TILE + (rem / nks) * 128;
+            const int hh = rem / nks;
+            const int row0 = (item_of(jj) / groups) * ITEM_ROWS + (Epi::DUAL ? 0 : hh * 128);
             const int st = rem % nks;
             const int sr = raw_next % RST;
             mbar_arrive_expect_tx(RAW_FULL(sr), (uint32_t)C::RAW_STAGE);
-            tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), &wmap,
+            tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), (Epi::DUAL && hh) ? &wmap1 : &wmap0,
                        (int)(((uint32_t)(st * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
             ++raw_next;
             progressed = true;
@@ -354,34 +378,15 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
       __syncwarp();
     }
 
-    // ---- logits of both halves are in TMEM columns [0, 2 BN); the operand ring is idle ----
+    // ---- the results of both halves are in TMEM columns [0, 2 BN); the operand ring is idle ----
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const int v0 = tile * LMH_TILE;
-    const int nvalid = min(LMH_TILE, V - v0);
-    if (warp < LTC_DQW) {
-      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-      const int RS = (warp & 3) * 32 + lane;
-      const int cg = warp >> 2;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t v[CW];
-        tmem_ld_nowait<CW>(tmem_base + lane_sel + (uint32_t)(h * BN + cg * CW), v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < CW; ++i) {
-          const int m = cg * CW + i;
-          const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
-          logit[m * LMH_TILE + h * 128 + RS] = __uint_as_float(v[i]) * rs;
-        }
-      }
+    {
+      TcItem item_ctx{tmem_base, logit, rowscale, tile, t_base, T_pass, warp, lane};
+      Epi::run(ea, item_ctx);
     }
     tc_fence_before();
-    __syncthreads();
-    for (int m = warp; m < T_pass; m += LTC_WARPS)
-      lmh_select_token(logit + m * LMH_TILE, nvalid, v0, vocab_offset, bias, t_base + m, tile,
-                       tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse, lane);
     __syncthreads();
     tc_fence_after();
   }
@@ -393,16 +398,42 @@ lmh_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict
         if (mbar_try_wait(RAW_FULL(i % RST), (uint32_t)((i / RST) & 1))) break;
   }
 
-  // padding tiles of a short shard carry absent partials
-  for (long long tile = real_tiles + blockIdx.x; tile < tiles_stride; tile += gridDim.x) {
-    for (int m = warp; m < T_total; m += LTC_WARPS)
-      lmh_select_token(logit, 0, 0, vocab_offset, nullptr, m, (int)tile, tiles_stride, mode,
-                       topk, invtemp, seed, part_val, part_id, part_lse, lane);
-  }
+  Epi::tail(ea, logit, real_tiles, warp, lane);
 
   tc_fence_before();
   __syncthreads();
   if (warp == LTC_DQW) tmem_dealloc(tmem_base, 512u);
+}
+
+// Tensor map over a packed weight matrix seen as V rows of 32-bit words, box = (box_bytes / 4) x 128
+// rows.  The driver entry point is looked up at run time, so the library does not link libcuda.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                      CUtensorMapFloatOOBfill);
+inline TensorMapEncodeFn tensor_map_encode_fn() {
+  static TensorMapEncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return (TensorMapEncodeFn) nullptr;
+    }
+    return (TensorMapEncodeFn)p;
+  }();
+  return fn;
+}
+inline bool make_weight_map(CUtensorMap* map, const void* w, int64_t V, size_t row_bytes, int box_bytes) {
+  TensorMapEncodeFn enc = tensor_map_encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)V};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(w), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace qx

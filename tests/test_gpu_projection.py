@@ -225,6 +225,19 @@ def test_epilogue_large_batch(fmt, M):
     assert_close_dtype(host(got), ref, "bf16")
 
 
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_0", "mxfp8", "nvfp4", "mxfp4"])
+def test_large_batch_f16(fmt):
+    """f16 activations at batch > 16: linear with every epilogue piece, and SwiGLU."""
+    M, K, N = 40, 512, 384
+    x, Wq, bias, res = _inputs(fmt, M, K, N, "f16", 70)
+    got = tk.decode_linear_epilogue(dev(x, "f16"), dev(Wq), dev(bias, "f16"), dev(res, "f16"),
+                                    activation="silu", format=fmt)
+    assert_close_dtype(host(got), O.decode_linear_epilogue(x, Wq, fmt, bias, res, 2, "f16"), "f16")
+    _, Uq, ub, _ = _inputs(fmt, M, K, N, "f16", 71)
+    got = tk.decode_swiglu(dev(x, "f16"), dev(Wq), dev(Uq), dev(bias, "f16"), dev(ub, "f16"), format=fmt)
+    assert_close_dtype(host(got), O.decode_swiglu(x, Wq, Uq, fmt, bias, ub, "f16"), "f16")
+
+
 @pytest.mark.parametrize("fmt", ["nvfp4", "q8_0"])
 def test_epilogue_large_batch_every_code_value(fmt):
     x, Wq, bias, res = _inputs(fmt, 48, 512, 256, "bf16", 17, random_bytes=True)
