@@ -57,8 +57,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // The same with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
-// (or until the phase completes) instead of returning at once.  Measured on the tcgen05 LM head:
-// fewer polling instructions but a later wake-up, 4 % slower overall, so the kernels poll.
+// (or until the phase completes) instead of returning at once.  Measured: on the tcgen05 pipeline
+// fewer polling instructions but a later wake-up, 4 % slower overall; on the streaming GEMV no
+// difference.  The kernels poll.
 __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
   uint32_t ok;
   asm volatile(
@@ -127,6 +128,15 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// d = a * b (+ 0): the zero C operand is a constant, so no accumulator has to be cleared first
+__device__ __forceinline__ void mma_f16_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 __device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
   uint32_t r; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r;
@@ -284,8 +294,10 @@ template <> struct RowDec<F_Q4_0> {
   }
 };
 
+// 2^(e - 127) for an e8m0 code: code 0 is the subnormal 2^-127, whose bit pattern 0x00400000 is
+// smaller than every shifted non-zero code, so one max replaces the compare-and-select.
 __device__ __forceinline__ float e8m0_scale(uint32_t e) {
-  return __uint_as_float(e == 0 ? 0x00400000u : (e << 23));
+  return __uint_as_float(max(e << 23, 0x00400000u));
 }
 
 template <> struct RowDec<F_MXFP4> {
@@ -370,8 +382,8 @@ __device__ __forceinline__ void unit32(const uint32_t (&s)[2 * NSETS], uint32_t 
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
     for (int set = 0; set < NSETS; ++set) {
-      float p[4] = {0.f, 0.f, 0.f, 0.f};
-      mma_f16(p, a[2 * set][0][0], a[2 * set + 1][0][0], a[2 * set][0][1], a[2 * set + 1][0][1], b[nt].x, b[nt].y);
+      float p[4];
+      mma_f16_zero(p, a[2 * set][0][0], a[2 * set + 1][0][0], a[2 * set][0][1], a[2 * set + 1][0][1], b[nt].x, b[nt].y);
       mma_f16(p, a[2 * set][1][0], a[2 * set + 1][1][0], a[2 * set][1][1], a[2 * set + 1][1][1], b[nt].z, b[nt].w);
       acc[set][nt][0] = fmaf(sc[2 * set], p[0], acc[set][nt][0]);
       acc[set][nt][1] = fmaf(sc[2 * set], p[1], acc[set][nt][1]);
@@ -587,8 +599,8 @@ template <> struct GroupProc<F_Q6_K> {
             const uint2 b = bq[g][nt];
 #pragma unroll
             for (int set = 0; set < NSETS; ++set) {
-              float p[4] = {0.f, 0.f, 0.f, 0.f};
-              mma_f16(p, a[2 * set][0], a[2 * set + 1][0], a[2 * set][1], a[2 * set + 1][1], b.x, b.y);
+              float p[4];
+              mma_f16_zero(p, a[2 * set][0], a[2 * set + 1][0], a[2 * set][1], a[2 * set + 1][1], b.x, b.y);
               acc[set][nt][0] = fmaf(sc[2 * set], p[0], acc[set][nt][0]);
               acc[set][nt][1] = fmaf(sc[2 * set], p[1], acc[set][nt][1]);
               acc[set][nt][2] = fmaf(sc[2 * set + 1], p[2], acc[set][nt][2]);
