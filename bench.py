@@ -299,9 +299,44 @@ def stack_sweep(device, world: int, rank: int, peak_gbs: float, layers: int = 80
         ms = torch.tensor([e0.elapsed_time(e1) / iters], device=device)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        ms = float(ms.item())
+        ms_eager = float(ms.item())
+        # the same step as one CUDA-graph replay (NCCL all-reduces captured with the kernels): what a
+        # serving loop would run; every rank must have captured before any rank replays
+        ms = ms_eager
+        graph = None
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                stack.forward(x)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                stack.forward(x)
+            ok = torch.tensor([1.0], device=device)
+        except Exception:
+            graph = None
+            ok = torch.tensor([0.0], device=device)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) > 0.5:
+            for _ in range(2):
+                graph.replay()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(iters):
+                graph.replay()
+            e1.record(); torch.cuda.synchronize()
+            mg = torch.tensor([e0.elapsed_time(e1) / iters], device=device)
+            if world > 1:
+                dist.all_reduce(mg, op=dist.ReduceOp.MAX)
+            ms = float(mg.item())
+        del graph
         wb = stack.weight_bytes()
-        out.append({"M": M, "layers": layers, "ms_per_step": round(ms, 4), "weight_bytes_per_gpu": int(wb),
+        out.append({"M": M, "layers": layers, "ms_per_step": round(ms, 4), "ms_eager": round(ms_eager, 4),
+                    "timing": "cuda-graph replay" if ms != ms_eager else "eager", "weight_bytes_per_gpu": int(wb),
                     "gbs_per_gpu": round(wb / (ms * 1e-3) / 1e9, 1),
                     "frac_of_measured_peak": round(wb / (ms * 1e-3) / 1e9 / peak_gbs, 4),
                     "allreduces_per_step": 2 * layers if world > 1 else 0})
