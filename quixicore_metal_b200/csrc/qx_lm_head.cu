@@ -62,7 +62,6 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
   // modes 2/3: tile top-k of the raw logits (+bias); mode 3 also the tempered log-sum-exp
   float mv[8];
   int mi[8];
-  float lmax = QX_NEG_INF, lsum = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int lr = lane + 32 * j;
@@ -71,17 +70,21 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
       if (bias) ls += bias[v0 + lr];
       mv[j] = ls;
       mi[j] = (int)(vocab_offset + v0 + lr);
-      const float tl = ls * invtemp;
-      if (tl > lmax) { lsum = lsum * expf(lmax - tl) + 1.0f; lmax = tl; }
-      else { lsum += expf(tl - lmax); }
     } else {
       mv[j] = QX_NEG_INF;
       mi[j] = -1;
     }
   }
   if (mode == 3) {
+    // tempered log-sum-exp of the tile: maximum first, then one exponential per element
+    float lmax = QX_NEG_INF;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lmax = fmaxf(lmax, mi[j] >= 0 ? mv[j] * invtemp : QX_NEG_INF);
     const float gmax = warp_max(lmax);
-    const float gsum = warp_sum(lmax == QX_NEG_INF ? 0.f : lsum * expf(lmax - gmax));
+    float lsum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lsum += mi[j] >= 0 ? expf(mv[j] * invtemp - gmax) : 0.f;
+    const float gsum = warp_sum(lsum);
     if (lane == 0)
       part_lse[(size_t)t * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
   }
