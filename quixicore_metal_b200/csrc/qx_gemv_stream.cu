@@ -13,6 +13,7 @@
 
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
+#include "qx_tmap.h"
 
 namespace qx {
 
@@ -182,8 +183,8 @@ struct StreamCfg {
 
 template <int FMT, int NT, bool DUAL, typename T>
 __global__ void __launch_bounds__(STREAM_MAX_WARPS * 32, 1)
-gemv_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rowscale,
-                   const uint8_t* __restrict__ w0, const uint8_t* __restrict__ w1,
+gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
+                   const __half* __restrict__ x16, const float* __restrict__ rowscale,
                    const T* __restrict__ bias0, const T* __restrict__ bias1,
                    const T* __restrict__ residual, T* __restrict__ y, int M, int K, int N,
                    int activation, int use_bias, int use_residual, int ks_log2,
@@ -208,7 +209,7 @@ gemv_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ row
   red += (size_t)group * 2 * KS * 32 * NACC;
 
   WS ws;
-  ws.init(smem_u32(ring), smem_u32(bars), w0, w1, N, K, lane, err_flag);
+  ws.init(smem_u32(ring), smem_u32(bars), &wmap0, &wmap1, 0, K, lane, err_flag);
 
   const int ntiles = (N + 15) >> 4;
   const int group_global = blockIdx.x * groups + group;
@@ -257,11 +258,11 @@ gemv_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ row
       const int col_base = c * Cfg::KC;
       const int ngroups = ready ? min(Cfg::KC, K - col_base) / F::GROUP : 0;
       uint32_t s[2 * NSETS];
-      s[0] = ws.slot_addr(stage, g, row0, c);
-      s[1] = ws.slot_addr(stage, g + 8, row0, c);
+      s[0] = ws.slot_addr(stage, g, c);
+      s[1] = ws.slot_addr(stage, g + 8, c);
       if constexpr (DUAL) {
-        s[2] = ws.slot_addr(stage, 16 + g, row0, c);
-        s[3] = ws.slot_addr(stage, 24 + g, row0, c);
+        s[2] = ws.slot_addr(stage, 16 + g, c);
+        s[3] = ws.slot_addr(stage, 24 + g, c);
       }
       constexpr uint32_t GROUP_BYTES = F::GROUP / F::BK * F::BB;
       using GP = GroupProc<FMT>;
@@ -382,8 +383,18 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   __half* x16 = (__half*)scratch;
   float* rowscale = (float*)((char*)scratch + x16_bytes);
   launch_prep_activations(st, a.x, a.dtype, x16, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM);
+  using WSG = typename StreamCfg<FMT, DUAL>::WS::G;
+  const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
+  CUtensorMap map0, map1;
+  bool maps_ok = make_weight_map(&map0, a.w0, a.N, row_bytes, WSG::PITCH, 16);
+  if (maps_ok && DUAL) maps_ok = make_weight_map(&map1, a.w1, a.N, row_bytes, WSG::PITCH, 16);
+  if (!DUAL) map1 = map0;
+  if (!maps_ok) {
+    if (must_free) cudaFreeAsync(scratch, st);
+    return false;
+  }
   gemv_stream_kernel<FMT, NT, DUAL, T><<<blocks, nwarps * 32, smem, st>>>(
-      x16, rowscale, (const uint8_t*)a.w0, (const uint8_t*)a.w1, (const T*)a.bias0,
+      map0, map1, x16, rowscale, (const T*)a.bias0,
       (const T*)a.bias1, (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
       a.use_bias, a.use_residual, ks_log2, err);
   if (must_free) cudaFreeAsync(scratch, st);

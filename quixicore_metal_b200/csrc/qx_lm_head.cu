@@ -239,8 +239,8 @@ constexpr int LMH_TOK_CHUNK = 16;
 // 16 (16 warps: more loads in flight; used for the large hidden-row counts).
 template <int FMT, int NT, int WROWS>
 __global__ void __launch_bounds__(256 / WROWS * 32, 1)
-lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rowscale,
-                  const uint8_t* __restrict__ wq, const float* __restrict__ bias,
+lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ x16,
+                  const float* __restrict__ rowscale, const float* __restrict__ bias,
                   float* __restrict__ part_val, int32_t* __restrict__ part_id,
                   float* __restrict__ part_lse, int T_total, int tokens_per_group, int V, int K,
                   long long vocab_offset, long long tiles_stride, int mode, int topk, float invtemp,
@@ -263,10 +263,8 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NW * WS::WARP_BYTES) + warp * C::STAGES;
   float* logit = reinterpret_cast<float*>(smem_raw + (size_t)NW * WS::WARP_BYTES + (size_t)NW * C::STAGES * 8);
 
-  const size_t row_bytes = (size_t)(K / F::BK) * F::BB;
   WS ws;
-  ws.init(smem_u32(ring), smem_u32(bars), wq, wq + 16 * row_bytes, V, K, lane, err_flag);
-  ws.N1 = V - 16;                                  // rows 16..31 of a warp come from the same matrix
+  ws.init(smem_u32(ring), smem_u32(bars), &wmap, &wmap, 16, K, lane, err_flag);   // rows 16..31: same matrix
 
   const int real_tiles = (V + LMH_TILE - 1) / LMH_TILE;
   const int items = real_tiles * groups;
@@ -308,11 +306,11 @@ lmh_stream_kernel(const __half* __restrict__ x16, const float* __restrict__ rows
       const int col_base = c * C::KC;
       const int ngroups = ready ? min(C::KC, K - col_base) / F::GROUP : 0;
       uint32_t s[2 * NSETS];
-      s[0] = ws.slot_addr(stage, g, row0, c);
-      s[1] = ws.slot_addr(stage, g + 8, row0, c);
+      s[0] = ws.slot_addr(stage, g, c);
+      s[1] = ws.slot_addr(stage, g + 8, c);
       if constexpr (NSETS == 2) {
-        s[2] = ws.slot_addr(stage, 16 + g, row0, c);
-        s[3] = ws.slot_addr(stage, 24 + g, row0, c);
+        s[2] = ws.slot_addr(stage, 16 + g, c);
+        s[3] = ws.slot_addr(stage, 24 + g, c);
       }
       constexpr uint32_t GROUP_BYTES = F::GROUP / F::BK * F::BB;
       if constexpr (NT > 2 && GP::PIPED) {
@@ -446,7 +444,7 @@ static bool lmh_stream_ok(const LmHeadArgs& a) {
 template <int FMT, int NT>
 static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __half* x16,
                                  const float* rowscale, float* pv, int32_t* pi, float* pl,
-                                 int64_t tiles_stride, int* err) {
+                                 int64_t tiles_stride, int* err, const CUtensorMap& wmap) {
   using C = LmhCfg<FMT>;
   constexpr int WROWS = NT >= 4 ? 16 : 32;
   constexpr int NW = 256 / WROWS;
@@ -465,7 +463,7 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   const long long items = (long long)real_tiles * ((a.T + tpg - 1) / tpg);
   dim3 grid((unsigned)(items < sm_count() ? items : sm_count()));
   lmh_stream_kernel<FMT, NT, WROWS><<<grid, NW * 32, smem, st>>>(
-      x16, rowscale, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
+      wmap, x16, rowscale, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
       (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
   note_launch();
 }
@@ -533,6 +531,11 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   }
   int* err = device_error_flag();
   if (!err) return false;
+  CUtensorMap wmap;
+  {
+    const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
+    if (!make_weight_map(&wmap, a.wq, a.V, row_bytes, StageGeom<FMT, LmhCfg<FMT>::KC>::PITCH, 16)) return false;
+  }
   const size_t x16_bytes = ((size_t)a.T * a.K * 2 + 255) & ~(size_t)255;
   bool must_free = false;
   void* scratch = stream_scratch(st, x16_bytes + (size_t)a.T * 4, &must_free);
@@ -552,20 +555,20 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   {
     const int v = tpg_override;
     if (v == 8 || v == 16 || v == 32 || v == 64) {
-      if (v <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-      else if (v <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-      else if (v <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-      else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+      if (v <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+      else if (v <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+      else if (v <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+      else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
       if (must_free) cudaFreeAsync(scratch, st);
       return true;
     }
   }
   while (tpg > 8 && (long long)real_tiles * ((a.T + tpg - 1) / tpg) < sm_count() && a.T > tpg / 2) tpg >>= 1;
   while (tpg > 8 && a.T <= tpg / 2) tpg >>= 1;
-  if (tpg <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-  else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-  else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
-  else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err);
+  if (tpg <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
   if (must_free) cudaFreeAsync(scratch, st);
   return true;
 }

@@ -26,6 +26,8 @@
 // Every mbarrier wait is bounded; on expiry the warp raises the device error flag and stops computing.
 #pragma once
 
+#include <cuda.h>
+
 #include "qx_common.cuh"
 
 namespace qx {
@@ -83,6 +85,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
           "r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// One 2-D TMA box (tensor map coordinates x = 32-bit word inside the row, y = row) -> shared memory.
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -191,11 +200,14 @@ struct StageGeom {
   using F = StreamFmt<FMT>;
   static constexpr int KC = KCV;
   static constexpr int CHUNK_BYTES = KC / F::BK * F::BB;          // payload bytes per row and stage
-  // stages whose byte size is not a multiple of 16 start at varying offsets inside a 16-byte line:
-  // leave room for that slack on both sides; then pad so that the 8 rows a warp touches in one
-  // instruction start 16 bytes apart modulo 128 (no shared-memory bank conflicts)
-  static constexpr int RAW = CHUNK_BYTES + (CHUNK_BYTES % 16 == 0 ? 0 : 32);
-  static constexpr int PITCH = ((RAW - 16 + 127) / 128) * 128 + 16;
+  // A stage is fetched as one TMA box of 16 rows.  The payload starts at a multiple of 4 inside
+  // the row but not always of 16, so the box starts at the 16-byte boundary below and is wide
+  // enough for the largest misalignment; its width (= the row pitch in shared memory) is an odd
+  // multiple of 16 bytes, so the 8 rows a warp touches in one instruction start in different
+  // 16-byte bank groups (no shared-memory bank conflicts).
+  static constexpr int ALIGN = (CHUNK_BYTES % 16 == 0) ? 16 : ((CHUNK_BYTES % 8 == 0) ? 8 : 4);
+  static constexpr int PITCH = (((CHUNK_BYTES + 16 - ALIGN + 15) / 16) | 1) * 16;
+  static_assert(PITCH / 4 <= 256, "a TMA box is at most 256 elements wide");
 };
 
 // Position of column c (0 <= c < 32) of a 32-column group inside the prepared activation row.
@@ -622,64 +634,58 @@ template <> struct GroupProc<F_Q6_K> {
 
 
 // ---- the per-warp weight stream ------------------------------------------------------------------
-// A warp owns a ring of STAGES stages; a stage holds ROWS row-chunks (16 rows, or 16 gate + 16 up
-// rows).  Work is a flat list of steps = (m-tile, chunk) pairs; step i lives in stage i % STAGES.
+// A warp owns a ring of STAGES stages; a stage holds ROWS row-chunks (16 rows, or 16 + 16 rows: gate
+// and up rows of a SwiGLU tile, or two consecutive 16-row blocks of one matrix).  Work is a flat
+// list of steps = (m-tile, chunk) pairs; step i lives in stage i % STAGES.  One lane fetches a
+// 16-row block with ONE 2-D TMA box copy (a per-row bulk copy costs the issuing warp an elect loop
+// of ~13 instructions per row); rows past the end of the matrix arrive as zeros.
 template <int FMT, int KCV, int ROWS, int STAGES>
 struct WarpStream {
   using G = StageGeom<FMT, KCV>;
   using F = StreamFmt<FMT>;
   static constexpr int STAGE_BYTES = ROWS * G::PITCH;
   static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+  static_assert((16 * G::PITCH) % 128 == 0, "the second box of a stage must start 128-byte aligned");
 
-  uint32_t smem;        // shared address of this warp's ring
-  uint32_t bars;        // shared address of this warp's STAGES mbarriers
-  const uint8_t* w0;    // weight tensors (w1 only when ROWS == 32)
-  const uint8_t* w1;
-  size_t row_bytes;
-  int N, N1, K, nch, lane;   // N1 = row limit of the w1 half (DUAL: N; single matrix: N - 16)
-  int* err_flag;        // device-global flag raised when a bounded wait expires
+  uint32_t smem;             // shared address of this warp's ring (128-byte aligned)
+  uint32_t bars;             // shared address of this warp's STAGES mbarriers
+  const CUtensorMap* m0;     // tensor maps of the weight matrices (m1 only when ROWS == 32)
+  const CUtensorMap* m1;
+  int row1_off;              // rows 16..31 of a stage: m1 at row0 + row1_off
+  int K, nch, lane;
+  int* err_flag;             // device-global flag raised when a bounded wait expires
   bool dead;
 
-  __device__ __forceinline__ void init(uint32_t smem_, uint32_t bars_, const uint8_t* w0_,
-                                       const uint8_t* w1_, int N_, int K_, int lane_,
+  __device__ __forceinline__ void init(uint32_t smem_, uint32_t bars_, const CUtensorMap* m0_,
+                                       const CUtensorMap* m1_, int row1_off_, int K_, int lane_,
                                        int* err_flag_) {
-    smem = smem_; bars = bars_; w0 = w0_; w1 = w1_; N = N_; N1 = N_; K = K_; lane = lane_;
+    smem = smem_; bars = bars_; m0 = m0_; m1 = m1_; row1_off = row1_off_; K = K_; lane = lane_;
     err_flag = err_flag_;
-    row_bytes = (size_t)(K / F::BK) * F::BB;
     nch = (K + G::KC - 1) / G::KC;
     dead = false;
     if (lane == 0) {
 #pragma unroll
-      for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, ROWS);
+      for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
   }
 
-  // shared address at which byte 0 of (row slot r, chunk c) of a tile starting at row0 lands
-  __device__ __forceinline__ uint32_t slot_addr(int stage, int r, int row0, int c) const {
-    const uint8_t* base = (r < 16 ? w0 : w1);
-    const size_t off = (size_t)(row0 + (r & 15)) * row_bytes + (size_t)c * G::CHUNK_BYTES;
-    return smem + stage * STAGE_BYTES + r * G::PITCH + (uint32_t)((uintptr_t)(base + off) & 15u);
+  // shared address at which byte 0 of (row slot r, chunk c) lands
+  __device__ __forceinline__ uint32_t slot_addr(int stage, int r, int c) const {
+    return smem + stage * STAGE_BYTES + r * G::PITCH + ((uint32_t)(c * G::CHUNK_BYTES) & 15u);
   }
 
-  // every lane < ROWS fetches one row-chunk of step (row0, c) into `stage`
+  // lane 0 fetches the row-chunks of step (row0, c) into `stage`
   __device__ __forceinline__ void issue(int stage, int row0, int c) {
-    if (lane >= ROWS) return;
+    if (lane != 0) return;
     const uint32_t bar = bars + 8 * stage;
-    const int row = row0 + (lane & 15);
-    if (row >= (lane < 16 ? N : N1)) { mbar_arrive(bar); return; }
-    const uint8_t* base = (lane < 16 ? w0 : w1);
-    const size_t off = (size_t)row * row_bytes + (size_t)c * G::CHUNK_BYTES;
-    size_t len = row_bytes - (size_t)c * G::CHUNK_BYTES;
-    if (len > (size_t)G::CHUNK_BYTES) len = G::CHUNK_BYTES;
-    const uintptr_t a = (uintptr_t)(base + off);
-    const uintptr_t a0 = a & ~(uintptr_t)15;
-    const uint32_t bytes = (uint32_t)(((a + len + 15) & ~(uintptr_t)15) - a0);
-    const uint32_t dst = smem + stage * STAGE_BYTES + lane * G::PITCH;
-    mbar_arrive_expect_tx(bar, bytes);
-    bulk_g2s(dst, reinterpret_cast<const void*>(a0), bytes, bar);
+    const uint32_t dst = smem + stage * STAGE_BYTES;
+    const int x = (int)(((uint32_t)(c * G::CHUNK_BYTES) & ~15u) >> 2);
+    mbar_arrive_expect_tx(bar, (uint32_t)STAGE_BYTES);
+    tma_box_2d(dst, m0, x, row0, bar);
+    if constexpr (ROWS == 32) tma_box_2d(dst + 16 * G::PITCH, m1, x, row0 + row1_off, bar);
   }
 
   __device__ __forceinline__ bool wait(int stage, uint32_t parity) {

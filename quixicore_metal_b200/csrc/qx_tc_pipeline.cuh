@@ -35,9 +35,8 @@
 // work, runs its loops to the end without waiting, frees its tensor memory and returns.
 #pragma once
 
-#include <cuda.h>
-
 #include "qx_tc.cuh"
+#include "qx_tmap.h"
 
 namespace qx {
 
@@ -85,13 +84,6 @@ struct TcSmem {
   static_assert(BN * 256 * 4 <= LTC_AST * A_STAGE, "a [BN][256] fp32 buffer must fit the operand ring");
   static_assert(C::RAW_STAGE % 128 == 0, "raw stages must keep the TMA destination aligned");
 };
-
-__device__ __forceinline__ void tma_box_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
 
 // What an epilogue policy sees of the finished item.  TMEM columns [0, BN) hold the fp32
 // accumulators of half 0, [BN, 2 BN) of half 1 (lane = weight row inside the half, column =
@@ -403,37 +395,6 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   tc_fence_before();
   __syncthreads();
   if (warp == LTC_DQW) tmem_dealloc(tmem_base, 512u);
-}
-
-// Tensor map over a packed weight matrix seen as V rows of 32-bit words, box = (box_bytes / 4) x 128
-// rows.  The driver entry point is looked up at run time, so the library does not link libcuda.
-typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                      CUtensorMapFloatOOBfill);
-inline TensorMapEncodeFn tensor_map_encode_fn() {
-  static TensorMapEncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess) {
-      cudaGetLastError();
-      return (TensorMapEncodeFn) nullptr;
-    }
-    return (TensorMapEncodeFn)p;
-  }();
-  return fn;
-}
-inline bool make_weight_map(CUtensorMap* map, const void* w, int64_t V, size_t row_bytes, int box_bytes) {
-  TensorMapEncodeFn enc = tensor_map_encode_fn();
-  if (!enc) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)V};
-  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), 128u};
-  const cuuint32_t estr[2] = {1u, 1u};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(w), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace qx
