@@ -85,6 +85,26 @@ struct TcSmem {
   static_assert(C::RAW_STAGE % 128 == 0, "raw stages must keep the TMA destination aligned");
 };
 
+// Position in a ring of n barrier slots: slot index and phase parity, advanced without divisions.
+struct RingPos {
+  int slot;
+  uint32_t par;
+  __device__ __forceinline__ void advance(int n) {
+    if (++slot == n) { slot = 0; par ^= 1u; }
+  }
+};
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // What an epilogue policy sees of the finished item.  TMEM columns [0, BN) hold the fp32
 // accumulators of half 0, [BN, 2 BN) of half 1 (lane = weight row inside the half, column =
 // activation row of the group), still in units of the row-scaled activations.
@@ -151,6 +171,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
 
   // Bounded wait.  The CTA-wide abort flag is looked at only while spinning.
   auto wait_or_abort = [&](uint32_t bar, uint32_t parity) -> bool {
+    if (mbar_try_wait(bar, parity)) return true;              // the common case: already complete
     for (int i = 0; i < (1 << 21); ++i) {
       if (mbar_try_wait(bar, parity)) return true;
       if ((i & 63) == 63 && *abort_flag) return false;
@@ -168,7 +189,13 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   const int nks = K / LTC_KS;                                 // operand stages per half
   const int total_stages = my_items * 2 * nks;                // global stage counter range of this CTA
   auto item_of = [&](int j) { return (int)blockIdx.x + j * (int)gridDim.x; };
-  int raw_next = 0;                                           // loader: next raw stage to request
+  // Ring positions of each role, carried across items (a stage's global index only ever grows by one).
+  int raw_next = 0, raw_j = 0, raw_h = 0, raw_st = 0;         // loader: next raw stage and where it lies
+  RingPos ld_raw{0, 0}, ld_b{0, 0}, ld_bdone{0, 0};           // loader: raw slot, activation slot, DONE(stage - BST)
+  RingPos wk_raw{0, 0}, wk_done{0, 0}, wk_acc{0, 0};          // workers: raw slot, DONE(stage - AST), accumulator pair
+  RingPos mm_b{0, 0}, mm_acc{0, 0}, mm_done{0, 0};            // MMA warp: activation slot, accumulator pair, DONE slot
+  int g_it = 0;                                               // stages this role has gone through so far
+  int g_pairs = 0;                                            // MMA warp: accumulator pairs issued so far
 
   for (int j = 0; j < my_items; ++j) {
     const int item = item_of(j);
@@ -188,15 +215,18 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       const int RS = (warp & 3) * 32 + lane;                  // row inside the half (scale role)
       const int cg = warp >> 2;                               // which quarter of the hidden rows
       float acc[CW];
-      auto scale_stage = [&](int it) {                          // both unit pairs of stage `it`
-        const int pg = it * 2;
-        const int buf0 = pg % LTC_NACC, buf1 = (pg + 1) % LTC_NACC;
-        bool ok = wait_or_abort(ACC_FULL(buf0), (uint32_t)((pg / LTC_NACC) & 1));
-        ok = wait_or_abort(ACC_FULL(buf1), (uint32_t)(((pg + 1) / LTC_NACC) & 1)) && ok;
+      const uint32_t sc_rd = sbase + (uint32_t)(S::OFF_SC + RS * 4);     // scale ring, this thread's row (scale role)
+      auto scale_stage = [&](int it) {                          // both unit pairs of stage `it`, in ring order
+        const int buf0 = wk_acc.slot;
+        bool ok = wait_or_abort(ACC_FULL(buf0), wk_acc.par);
+        wk_acc.advance(LTC_NACC);
+        const int buf1 = wk_acc.slot;
+        ok = wait_or_abort(ACC_FULL(buf1), wk_acc.par) && ok;
+        wk_acc.advance(LTC_NACC);
         tc_fence_after();
         const uint32_t col = tmem_base + lane_sel + ACC_COL0 + (uint32_t)(cg * CW);
-        const float* scs = sc_ring + (size_t)((it * 4) % LTC_SCR) * 128 + RS;
-        const float sc0 = scs[0], sc1 = scs[128], sc2 = scs[256], sc3 = scs[384];
+        const uint32_t scs = sc_rd + (uint32_t)(((it * 4) & (LTC_SCR - 1)) * 512);
+        const float sc0 = lds_f32(scs), sc1 = lds_f32(scs + 512), sc2 = lds_f32(scs + 1024), sc3 = lds_f32(scs + 1536);
         if (ok) {
           uint32_t v0[CW], v1[CW], v2[CW], v3[CW];
           tmem_ld_nowait<CW>(col + (uint32_t)(buf0 * 2 * BN), v0);
@@ -223,21 +253,22 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
 #pragma unroll
         for (int i = 0; i < CW; ++i) acc[i] = 0.f;
         for (int st = 0; st < nks; ++st) {
-          const int it = it_base + h * nks + st;
-          const int sa = it % LTC_AST, sr = it % RST;
+          const int it = g_it;
+          const int sa = it & (LTC_AST - 1), sr = wk_raw.slot;
           const uint32_t off = (uint32_t)(st * C::CHUNK_BYTES) & 15u;
           const uint32_t sp0 = sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE) + off + (uint32_t)(R * C::BOX);
-          wait_or_abort(RAW_FULL(sr), (uint32_t)((it / RST) & 1));
-          if (it >= LTC_AST) wait_or_abort(DONE((it - LTC_AST) % LTC_DONE), (uint32_t)(((it - LTC_AST) / LTC_DONE) & 1));
-          uint8_t* a_stage = smem + S::OFF_A + (size_t)sa * S::A_STAGE;
+          wait_or_abort(RAW_FULL(sr), wk_raw.par);
+          wk_raw.advance(RST);
+          if (it >= LTC_AST) { wait_or_abort(DONE(wk_done.slot), wk_done.par); wk_done.advance(LTC_DONE); }
+          const uint32_t a_stage = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
           if constexpr (FMT == F_NVFP4) {
 #pragma unroll
             for (int a = 0; a < 2; ++a) {                     // swizzle atom = 64 columns
-              uint8_t* a_atom = a_stage + a * S::A_ATOM;
+              const uint32_t a_atom = a_stage + (uint32_t)(a * S::A_ATOM);
               uint32_t w[4][2];
               GroupProc<F_NVFP4>::block(sp0 + a * ATOM_BYTES, t, w);
-              *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t)) = make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
-              *reinterpret_cast<uint4*>(a_atom + sw128_offset(R, 2 * t + 1)) = make_uint4(w[2][0], w[2][1], w[3][0], w[3][1]);
+              sts128(a_atom + sw128_offset(R, 2 * t), w[0][0], w[0][1], w[1][0], w[1][1]);
+              sts128(a_atom + sw128_offset(R, 2 * t + 1), w[2][0], w[2][1], w[3][0], w[3][1]);
             }
           } else {
             // all shared-memory loads of the stage first (four units), then the conversions and stores
@@ -253,23 +284,24 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
               RD::template load<0>(sp0 + 2 * F::BB, t, raw[2], scb[2]);
               RD::template load<1>(sp0 + 3 * F::BB, t, raw[3], scb[3]);
             }
-            float* scs = sc_ring + (size_t)((it * 4) % LTC_SCR) * 128;
+            const uint32_t scs = sbase + (uint32_t)(S::OFF_SC + ((it * 4) & (LTC_SCR - 1)) * 512 + R * 4);
 #pragma unroll
             for (int u4 = 0; u4 < 4; ++u4) {                  // unit u4: atom u4 / 2, chunk group u4 % 2
               uint32_t w[2][2];
               RD::convert(raw[u4], w);
-              *reinterpret_cast<uint4*>(a_stage + (u4 >> 1) * S::A_ATOM + sw128_offset(R, 4 * (u4 & 1) + t)) =
-                  make_uint4(w[0][0], w[0][1], w[1][0], w[1][1]);
-              if (t == 0) scs[u4 * 128 + R] = RD::scale(scb[u4]);
+              sts128(a_stage + (uint32_t)((u4 >> 1) * S::A_ATOM) + sw128_offset(R, 4 * (u4 & 1) + t),
+                     w[0][0], w[0][1], w[1][0], w[1][1]);
+              if (t == 0) sts_f32(scs + (uint32_t)(u4 * 512), RD::scale(scb[u4]));
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) { mbar_arrive(A_FULL(sa)); mbar_arrive(RAW_EMPTY(sr)); }
+          ++g_it;
           if constexpr (POST) { if (st > 0) scale_stage(it - 1); }
         }
         if constexpr (POST) {
-          scale_stage(it_base + h * nks + nks - 1);
+          scale_stage(g_it - 1);
           // park the row's sums of this half
           uint32_t v[CW];
 #pragma unroll
@@ -287,22 +319,24 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       const uint32_t idesc = umma_idesc_f16(BN);
       for (int h = 0; h < 2; ++h) {
         for (int st = 0; st < nks; ++st) {
-          const int it = it_base + h * nks + st;
-          const int sa = it % LTC_AST, sb = it % LTC_BST;
-          bool ok = wait_or_abort(B_FULL(sb), (uint32_t)((it / LTC_BST) & 1));
-          ok = wait_or_abort(A_FULL(sa), (uint32_t)((it / LTC_AST) & 1)) && ok;
+          const int it = g_it++;
+          const int sa = it & (LTC_AST - 1), sb = mm_b.slot;
+          bool ok = wait_or_abort(B_FULL(sb), mm_b.par);
+          mm_b.advance(LTC_BST);
+          ok = wait_or_abort(A_FULL(sa), (uint32_t)((it >> 1) & 1)) && ok;
           tc_fence_after();
           const uint32_t a_base = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
           const uint32_t b_base = sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE);
 #pragma unroll
           for (int p = 0; p < 2; ++p) {                       // swizzle atom = pair of units
             if constexpr (POST) {
-              const int pg = it * 2 + p;
-              const int buf = pg % LTC_NACC;
-              if (pg >= LTC_NACC) {
-                ok = wait_or_abort(ACC_EMPTY(buf), (uint32_t)((pg / LTC_NACC - 1) & 1)) && ok;
+              const int buf = mm_acc.slot;
+              if (g_pairs >= LTC_NACC) {
+                ok = wait_or_abort(ACC_EMPTY(buf), mm_acc.par ^ 1u) && ok;
                 tc_fence_after();
               }
+              mm_acc.advance(LTC_NACC);
+              ++g_pairs;
               if (lane == 0) {
                 if (ok) {
 #pragma unroll
@@ -324,7 +358,8 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
               }
             }
           }
-          if (lane == 0) tc_commit(DONE(it % LTC_DONE));
+          if (lane == 0) tc_commit(DONE(mm_done.slot));
+          mm_done.advance(LTC_DONE);
           __syncwarp();
         }
       }
@@ -334,31 +369,33 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       // ================= loader: raw weight boxes (may run ahead into the next item) + activation tiles =================
       if (lane == 0) {
         const uint8_t* src = reinterpret_cast<const uint8_t*>(ximg) + (size_t)grp * BN * K * 2;
-        int nb = it_base;                                       // next activation stage to request
+        int nb = it_base, b_st = 0;                             // next activation stage to request (b_st: inside the half)
         const int nb_end = it_base + 2 * nks;
         const int raw_need = min(total_stages, nb_end);          // every raw stage of this item must be requested here
         int idle = 0;
         while ((nb < nb_end || raw_next < raw_need) && idle < (1 << 22)) {
           bool progressed = false;
           if (raw_next < total_stages &&
-              (raw_next < RST || mbar_try_wait(RAW_EMPTY(raw_next % RST), (uint32_t)((raw_next / RST - 1) & 1)))) {
-            const int jj = raw_next / (2 * nks), rem = raw_next % (2 * nks);
-            const int hh = rem / nks;
-            const int row0 = (item_of(jj) / groups) * ITEM_ROWS + (Epi::DUAL ? 0 : hh * 128);
-            const int st = rem % nks;
-            const int sr = raw_next % RST;
+              (raw_next < RST || mbar_try_wait(RAW_EMPTY(ld_raw.slot), ld_raw.par ^ 1u))) {
+            // raw stage raw_next = (item raw_j, half raw_h, stage raw_st)
+            const int row0 = (item_of(raw_j) / groups) * ITEM_ROWS + (Epi::DUAL ? 0 : raw_h * 128);
+            const int sr = ld_raw.slot;
             mbar_arrive_expect_tx(RAW_FULL(sr), (uint32_t)C::RAW_STAGE);
-            tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), (Epi::DUAL && hh) ? &wmap1 : &wmap0,
-                       (int)(((uint32_t)(st * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
+            tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), (Epi::DUAL && raw_h) ? &wmap1 : &wmap0,
+                       (int)(((uint32_t)(raw_st * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
+            ld_raw.advance(RST);
             ++raw_next;
+            if (++raw_st == nks) { raw_st = 0; if (++raw_h == 2) { raw_h = 0; ++raw_j; } }
             progressed = true;
           }
-          if (nb < nb_end && (nb < LTC_BST || mbar_try_wait(DONE((nb - LTC_BST) % LTC_DONE), (uint32_t)(((nb - LTC_BST) / LTC_DONE) & 1)))) {
-            const int sb = nb % LTC_BST;
-            const int st = (nb - it_base) % nks;
+          if (nb < nb_end && (nb < LTC_BST || mbar_try_wait(DONE(ld_bdone.slot), ld_bdone.par))) {
+            if (nb >= LTC_BST) ld_bdone.advance(LTC_DONE);
+            const int sb = ld_b.slot;
             mbar_arrive_expect_tx(B_FULL(sb), (uint32_t)S::B_STAGE);
-            bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)st * S::B_STAGE,
+            bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)b_st * S::B_STAGE,
                      (uint32_t)S::B_STAGE, B_FULL(sb));
+            ld_b.advance(LTC_BST);
+            if (++b_st == nks) b_st = 0;
             ++nb;
             progressed = true;
           }
@@ -387,7 +424,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   if (warp == LTC_DQW + 1 && lane == 0 && *abort_flag) {
     for (int i = max(0, raw_next - RST); i < raw_next; ++i)
       for (int k = 0; k < (1 << 20); ++k)
-        if (mbar_try_wait(RAW_FULL(i % RST), (uint32_t)((i / RST) & 1))) break;
+        if (mbar_try_wait(RAW_FULL(i % RST), (uint32_t)((i / RST) & 1))) break;   // cold path: divisions are fine
   }
 
   Epi::tail(ea, logit, real_tiles, warp, lane);
