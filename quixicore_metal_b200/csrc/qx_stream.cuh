@@ -541,19 +541,18 @@ template <> struct GroupProc<F_Q6_K> {
     if constexpr (ODD) return __funnelshift_r(lds32(p - 2), lds32(p + 2), 16);
     else return lds32(p);
   }
-  // codes of one sub-block for one row: Q = ql word, H = qh word; SHL moves this sub-block's two
-  // high bits to bit 4 (low-nibble groups) or bit 8 (high-nibble groups) of each byte lane.  Bytes
-  // 1 and 3 are shifted down before the left shift so that byte 3 loses nothing.
-  template <bool HIGH, int SHL>
+  // codes of one sub-block for one row: Q = ql word, H = qh word.  Sub-block G of the four that
+  // share the words takes the low (G < 2) or high nibbles of Q and bits 2G, 2G+1 of every H byte.
+  // The four 6-bit codes are assembled byte-wise (two logic ops), then each pair of bytes is
+  // spread under the f16 exponent of 1024 by one byte permute and centred by one subtraction:
+  // a0 <- bytes 0 and 2, a1 <- bytes 1 and 3 (the activation order is StreamFmt::PERM = 4).
+  template <int G>
   __device__ __forceinline__ static void pair(uint32_t Q, uint32_t H, uint32_t& a0, uint32_t& a1) {
-    const uint32_t H0 = H << SHL, H1 = (H >> 8) << SHL, Q1 = Q >> 8;
-    if constexpr (!HIGH) {
-      a0 = h2sub((H0 & 0x00300030u) | 0x64006400u | (Q & 0x000F000Fu), 0x64206420u);
-      a1 = h2sub((H1 & 0x00300030u) | 0x64006400u | (Q1 & 0x000F000Fu), 0x64206420u);
-    } else {
-      a0 = h2fma((H0 & 0x03000300u) | 0x64006400u | (Q & 0x00F000F0u), 0x2C002C00u, 0xD600D600u);
-      a1 = h2fma((H1 & 0x03000300u) | 0x64006400u | (Q1 & 0x00F000F0u), 0x2C002C00u, 0xD600D600u);
-    }
+    const uint32_t q4 = G < 2 ? Q : (Q >> 4);
+    const uint32_t h2 = G == 0 ? (H << 4) : (G == 1 ? (H << 2) : (G == 2 ? H : (H >> 2)));
+    const uint32_t c = (q4 & 0x0F0F0F0Fu) | (h2 & 0x30303030u);
+    a0 = h2sub(__byte_perm(c, 0x64646464u, 0x4240), 0x64206420u);
+    a1 = h2sub(__byte_perm(c, 0x64646464u, 0x4341), 0x64206420u);
   }
   template <int NT> struct BFrag { const __half* xr[NT]; int col; };   // fetched inside run()
   template <int NT>
@@ -598,10 +597,10 @@ template <> struct GroupProc<F_Q6_K> {
 #pragma unroll
           for (int r = 0; r < 2 * NSETS; ++r) {
             const uint32_t Q = (g & 1) ? Q1[r] : Q0[r];
-            if (g == 0) pair<false, 4>(Q, H[r], a[r][0], a[r][1]);
-            else if (g == 1) pair<false, 2>(Q, H[r], a[r][0], a[r][1]);
-            else if (g == 2) pair<true, 4>(Q, H[r], a[r][0], a[r][1]);
-            else pair<true, 2>(Q, H[r], a[r][0], a[r][1]);
+            if (g == 0) pair<0>(Q, H[r], a[r][0], a[r][1]);
+            else if (g == 1) pair<1>(Q, H[r], a[r][0], a[r][1]);
+            else if (g == 2) pair<2>(Q, H[r], a[r][0], a[r][1]);
+            else pair<3>(Q, H[r], a[r][0], a[r][1]);
             const uint32_t scw = SC[r][g >> 1];
             const int sb = (int)(int8_t)((scw >> (8 * (2 * (g & 1) + l))) & 0xFFu);
             sc[r] = d[r] * (float)sb;
