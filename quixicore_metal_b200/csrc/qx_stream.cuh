@@ -276,7 +276,7 @@ template <> struct RowDec<F_Q8_0> {
 
 template <> struct RowDec<F_Q4_0> {
   // thread t owns code bytes 4t..4t+3: low nibbles = columns 4t.., high nibbles = columns 16+4t..
-  // A nibble OR-ed under the f16 exponent of 1024 is 1024+n (bits 0-3) or 1024+16n (bits 4-7).
+  // A nibble placed under the f16 exponent of 1024 (0x6400 | n) is 1024 + n; subtracting 1032 centres it.
   static constexpr int RAWN = 1;
   template <int J>
   __device__ __forceinline__ static void load(uint32_t s, int t, uint32_t (&raw)[1], uint32_t& sc) {
@@ -297,12 +297,12 @@ template <> struct RowDec<F_Q4_0> {
     sc_out = scale(sc);
   }
   __device__ __forceinline__ static void convert(const uint32_t (&raw)[1], uint32_t (&a)[2][2]) {
-    const uint32_t w = raw[0];
-    const uint32_t w8 = w >> 8;
-    a[0][0] = h2sub((w & 0x000F000Fu) | 0x64006400u, 0x64086408u);                  // bytes 0,2 low
-    a[1][0] = h2fma((w & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);     // bytes 0,2 high
-    a[0][1] = h2sub((w8 & 0x000F000Fu) | 0x64006400u, 0x64086408u);                 // bytes 1,3 low
-    a[1][1] = h2fma((w8 & 0x00F000F0u) | 0x64006400u, 0x2C002C00u, 0xD480D480u);    // bytes 1,3 high
+    // nibbles byte-wise, then each pair of bytes under the f16 exponent of 1024 by one byte permute
+    const uint32_t lo = raw[0] & 0x0F0F0F0Fu, hi = (raw[0] >> 4) & 0x0F0F0F0Fu;
+    a[0][0] = h2sub(__byte_perm(lo, 0x64646464u, 0x4240), 0x64086408u);     // bytes 0,2 low nibbles
+    a[0][1] = h2sub(__byte_perm(lo, 0x64646464u, 0x4341), 0x64086408u);     // bytes 1,3 low nibbles
+    a[1][0] = h2sub(__byte_perm(hi, 0x64646464u, 0x4240), 0x64086408u);     // bytes 0,2 high nibbles
+    a[1][1] = h2sub(__byte_perm(hi, 0x64646464u, 0x4341), 0x64086408u);     // bytes 1,3 high nibbles
   }
 };
 
