@@ -1,8 +1,13 @@
-// decode_linear_epilogue / decode_swiglu for 16 < batch <= 128 per pass: tcgen05 tensor-core path.
+// decode_linear_epilogue / decode_swiglu for batch > 16: the tcgen05 tensor-core paths.
 //
-// Shape of the problem: out[n, m] = sum_k W[n, k] * x[m, k] with W packed.  The weight rows are the
-// M-mode of the MMA (128 rows per CTA tile), the batch is the N-mode (16..128), so small batches
-// waste nothing ("swap-AB").  Per 64-column k-stage:
+// 1. Every format but q6_K runs on the shared pipeline of qx_tc_pipeline.cuh (2-D TMA boxes of packed
+//    weights -> in-kernel dequant to f16 operand tiles -> tcgen05.mma, block scales applied from
+//    tensor memory); this file holds its projection epilogues (bias / activation / residual, the
+//    SwiGLU gate, raw fp32 partials) and the launch code.
+// 2. q6_K (and anything the pipeline's preconditions exclude) keeps the first kernel of this path,
+//    gemm_tc_kernel, below.  Shape of the problem: out[n, m] = sum_k W[n, k] * x[m, k] with W
+//    packed.  The weight rows are the M-mode of the MMA (128 rows per CTA tile), the batch is the
+//    N-mode (16..128), so small batches waste nothing ("swap-AB").  Per 64-column k-stage:
 //   * 256 dequant threads (a weight row and 32 columns each) read their packed bytes from global
 //     memory one stage ahead, decode them to fp32, split every weight
 //     into NTERMS bf16 terms whose sum is exactly the fp32 weight (1 term for nvfp4 / mxfp4 / mxfp8,
