@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(256)
 prep_activations_kernel(const T* __restrict__ x, __half* __restrict__ x16,
                         float* __restrict__ rowscale, int M, int K, int perm, int img_rows) {
   __shared__ float red[8];
+  asm volatile("griddepcontrol.launch_dependents;");   // a dependent grid may be scheduled from now on
   const int m = blockIdx.y;
   if (m >= M) {                                     // zero padding row of the last image group
     const int per = (((K + gridDim.x - 1) / gridDim.x) + 31) & ~31;
@@ -235,6 +236,9 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     for (int p = 0; p < STREAM_STAGES - 1; ++p)
       if (p < steps) ws.issue(p, step_tile(p) * 16, step_chunk(p));
   }
+  // Programmatic dependent launch: this grid may start while the activation-preparation kernel is
+  // still running (the weight boxes above do not depend on it); everything below reads its output.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float acc[NSETS][NT][4];
 #pragma unroll
@@ -393,10 +397,26 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
     if (must_free) cudaFreeAsync(scratch, st);
     return false;
   }
-  gemv_stream_kernel<FMT, NT, DUAL, T><<<blocks, nwarps * 32, smem, st>>>(
-      map0, map1, x16, rowscale, (const T*)a.bias0,
-      (const T*)a.bias1, (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
-      a.use_bias, a.use_residual, ks_log2, err);
+  // launched as a programmatic dependent of the preparation kernel (see griddepcontrol.wait)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3((unsigned)(nwarps * 32));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, T>, map0, map1, (const __half*)x16,
+                         (const float*)rowscale, (const T*)a.bias0, (const T*)a.bias1,
+                         (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
+                         a.use_bias, a.use_residual, ks_log2, err) != cudaSuccess) {
+    cudaGetLastError();
+    gemv_stream_kernel<FMT, NT, DUAL, T><<<blocks, nwarps * 32, smem, st>>>(
+        map0, map1, x16, rowscale, (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual,
+        (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, ks_log2, err);
+  }
   if (must_free) cudaFreeAsync(scratch, st);
   note_launch(2);
   return true;
