@@ -183,6 +183,24 @@ def test_vocab_sharded_merge_equals_single_call(mode, shards):
     np.testing.assert_array_equal(host(merged), single)
 
 
+@pytest.mark.parametrize("mode", ["argmax", "topk", "topp"])
+def test_vocab_sharded_merge_many_hidden_rows(mode):
+    """The shard entry points with more than 16 hidden rows (tensor-memory stage 1 per shard, padding
+    tiles of the short last shard, global ids through vocab_offset) equal the unsharded call."""
+    from quixicore_metal_b200 import parallel
+    fmt, T, V, K, shards = "q8_0", 40, 3000 + 13, 512, 3
+    h, Wq = _case(fmt, T, V, K, "bf16", 91)
+    kw = dict(k=16, temperature=0.8, seed=42, top_p=0.9)
+    single = _run(h, Wq, fmt, "bf16", mode, **kw)
+    hd, wd = dev(h, "bf16"), dev(Wq)
+    bounds = parallel.vocab_shard_bounds(V, shards)
+    parts = [parallel.lm_head_shard_partials(hd, wd[a:b].contiguous(), None, a, parallel.max_shard_tiles(V, shards),
+                                             fmt, mode, **{k_: v for k_, v in kw.items() if k_ != "top_p"})
+             for a, b in bounds]
+    merged = parallel.lm_head_merge(parts, mode, max_tiles=parallel.max_shard_tiles(V, shards), **kw)
+    np.testing.assert_array_equal(host(merged), single)
+
+
 def test_generic_dispatch_entry_point():
     """qx_cuda_dispatch with the contract's call structs (kernel_abi.hpp mirror)."""
     from quixicore_metal_b200 import _lib, capi
