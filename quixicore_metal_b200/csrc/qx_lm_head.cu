@@ -13,6 +13,7 @@
 //
 // Ordering everywhere: value descending, ties to the smaller id.
 #include <cstdio>
+#include <atomic>
 #include <cstdlib>
 
 #include "qx_formats.cuh"
@@ -394,6 +395,11 @@ struct LmhEpi {
     int mode, topk;
     float invtemp;
     uint32_t seed;
+    // items shared by several CTAs (each took a slice of K): where the other CTAs leave their partial
+    // logits ([shared item][part - 1][BN * 256] floats), the flags that say so, and the value that
+    // means "written during this launch"
+    float* xchg; unsigned* flags; unsigned epoch;
+    int* err_flag;
   };
   static constexpr bool DUAL = false;
   __device__ __forceinline__ static void run(const Args& a, const TcItem& it) {
@@ -417,6 +423,45 @@ struct LmhEpi {
     }
     tc_fence_before();
     __syncthreads();
+    if (it.kparts > 1) {
+      // the logits above are this CTA's slice of K; part 0 collects the others and selects
+      constexpr int N4 = BN * LMH_TILE / 4;
+      const int tid = it.warp * 32 + it.lane;
+      float4* mine = reinterpret_cast<float4*>(it.smem_f32);
+      float* slots = a.xchg + (size_t)it.split_index * (it.kparts - 1) * (BN * LMH_TILE);
+      unsigned* fl = a.flags + it.split_index * (it.kparts - 1);
+      if (it.kpart != 0) {
+        float4* dst = reinterpret_cast<float4*>(slots + (size_t)(it.kpart - 1) * (BN * LMH_TILE));
+        for (int i = tid; i < N4; i += LTC_WARPS * 32) dst[i] = mine[i];
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(fl + it.kpart - 1), "r"(a.epoch) : "memory");
+        return;
+      }
+      if (tid == 0) {
+        for (int p = 1; p < it.kparts; ++p) {
+          bool seen = false;
+          for (int k = 0; k < (1 << 22) && !seen; ++k) {      // bounded: about a second
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(fl + p - 1) : "memory");
+            seen = v == a.epoch;
+            if (!seen) __nanosleep(200);
+          }
+          if (!seen) atomicExch(a.err_flag, 4);
+        }
+      }
+      __syncthreads();
+      for (int p = 1; p < it.kparts; ++p) {
+        const float4* src = reinterpret_cast<const float4*>(slots + (size_t)(p - 1) * (BN * LMH_TILE));
+        for (int i = tid; i < N4; i += LTC_WARPS * 32) {
+          const float4 o = __ldcg(src + i);
+          float4 v = mine[i];
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+          mine[i] = v;
+        }
+      }
+      __syncthreads();
+    }
     const int v0 = it.tile * LMH_TILE;
     const int nvalid = min(LMH_TILE, a.V - v0);
     for (int m = it.warp; m < it.m_count; m += LTC_WARPS)
@@ -490,21 +535,63 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
   CUtensorMap wmap;
   if (!make_weight_map(&wmap, a.wq, a.V, row_bytes, C::BOX)) return false;
   const int groups = (int)((a.T + BN - 1) / BN);
+  const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
+  const long long items = (long long)real_tiles * groups;
+  // The last, partial round of items (all items, when there are fewer than SMs - a small vocabulary
+  // shard): when it would leave at least half of the SMs idle, each of its items is shared by 2 or
+  // 4 CTAs that take a slice of K each (QX_LMH_KSPLIT=0 turns it off).
+  static const bool split_enabled = [] {
+    const char* e = getenv("QX_LMH_KSPLIT");
+    return !(e && e[0] == '0');
+  }();
+  const int nks = (int)(a.K / LTC_KS);
+  const long long sms = sm_count();
+  const long long leftover = items % sms;
+  int ksplit = 1;
+  if (split_enabled && leftover > 0) {
+    if (leftover * 4 <= sms && nks % 4 == 0) ksplit = 4;
+    else if (leftover * 2 <= sms && nks % 2 == 0) ksplit = 2;
+  }
+  const unsigned grid = (unsigned)(items >= sms ? sms : items * ksplit);
   const size_t img_bytes = ((size_t)groups * BN * a.K * 2 + 255) & ~(size_t)255;
+  const size_t rs_bytes = ((size_t)a.T * 4 + 255) & ~(size_t)255;
+  const size_t xchg_bytes = ksplit > 1 ? (size_t)leftover * (ksplit - 1) * BN * LMH_TILE * 4 : 0;
+  const size_t flag_bytes = ksplit > 1 ? (((size_t)leftover * (ksplit - 1) * 4 + 255) & ~(size_t)255) : 0;
   bool must_free = false;
-  void* scratch = stream_scratch(st, img_bytes + (size_t)a.T * 4, &must_free);
+  void* scratch = stream_scratch(st, img_bytes + rs_bytes + xchg_bytes + flag_bytes, &must_free);
   if (!scratch) return false;
   __half* ximg = (__half*)scratch;
   float* rowscale = (float*)((char*)scratch + img_bytes);
+  float* xchg = (float*)((char*)scratch + img_bytes + rs_bytes);
+  unsigned* flags = (unsigned*)((char*)scratch + img_bytes + rs_bytes + xchg_bytes);
+  static std::atomic<unsigned> epoch_counter{1};
+  const unsigned epoch = epoch_counter.fetch_add(1) | 0x40000000u;     // never 0
   launch_prep_activations(st, a.h, a.dtype, ximg, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM, BN);
   note_launch();
-  const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
-  const long long items = (long long)real_tiles * groups;
-  const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
   const typename Epi::Args ea{a.bias, pv, pi, pl, (int)a.T, (int)a.V, (long long)a.vocab_offset,
-                              (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed};
-  tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
-      wmap, wmap, ximg, rowscale, (int)a.T, (int)a.V, (int)a.K, err, ea);
+                              (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed,
+                              xchg, flags, epoch, err};
+  bool launched = false;
+  if (ksplit > 1) {
+    // CTAs of this launch wait for one another: ask for a cooperative launch, which only starts
+    // when the whole grid is resident
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(LTC_WARPS * 32);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    launched = cudaLaunchKernelEx(&cfg, tc_pipeline_kernel<FMT, BN, Epi>, wmap, wmap, (const __half*)ximg,
+                                  (const float*)rowscale, (int)a.T, (int)a.V, (int)a.K, ksplit, err, ea) == cudaSuccess;
+    if (!launched) { cudaGetLastError(); ksplit = 1; }
+  }
+  if (!launched)
+    tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
+        wmap, wmap, ximg, rowscale, (int)a.T, (int)a.V, (int)a.K, 1, err, ea);
   note_launch();
   if (must_free) cudaFreeAsync(scratch, st);
   return true;

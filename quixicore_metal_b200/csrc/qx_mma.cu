@@ -363,7 +363,7 @@ static bool launch_pipeline_bn(cudaStream_t st, const GemvArgs& a, int* err) {
   const typename Epi::Args ea{(const OT*)a.bias0, (const OT*)a.bias1, (const OT*)a.residual, a.y, (int)a.N,
                               a.activation, a.use_bias, a.use_residual, a.out_f32};
   tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
-      map0, map1, ximg, rowscale, (int)a.M, (int)a.N, (int)a.K, err, ea);
+      map0, map1, ximg, rowscale, (int)a.M, (int)a.N, (int)a.K, 1, err, ea);
   note_launch();
   if (must_free) cudaFreeAsync(scratch, st);
   return true;

@@ -114,6 +114,8 @@ struct TcItem {
   const float* rowscale;    // per activation row of the whole call
   int tile, m_base, m_count;
   int warp, lane;
+  int kpart, kparts;        // this CTA computed columns [kpart, kpart + 1) * K / kparts of the item
+  int split_index;          // which of the shared items this is (0 .. number of shared items - 1)
 };
 
 // Epi: struct Args (by-value kernel argument);
@@ -124,7 +126,7 @@ template <int FMT, int BN, class Epi>
 __global__ void __launch_bounds__(LTC_WARPS * 32, 1)
 tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
                    const __half* __restrict__ ximg, const float* __restrict__ rowscale, int T_total,
-                   int V, int K, int* __restrict__ err_flag, const typename Epi::Args ea) {
+                   int V, int K, int ksplit, int* __restrict__ err_flag, const typename Epi::Args ea) {
   using F = StreamFmt<FMT>;
   using C = TcCfg<FMT>;
   using S = TcSmem<FMT, BN>;
@@ -185,10 +187,19 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   constexpr int ITEM_ROWS = Epi::DUAL ? 128 : 256;            // weight rows per work item
   const int real_tiles = (V + ITEM_ROWS - 1) / ITEM_ROWS;
   const int items = real_tiles * groups;
-  const int my_items = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nks = K / LTC_KS;                                 // operand stages per half
-  const int total_stages = my_items * 2 * nks;                // global stage counter range of this CTA
-  auto item_of = [&](int j) { return (int)blockIdx.x + j * (int)gridDim.x; };
+  // Items are dealt round-robin.  The items of the last, partial round can be shared: with
+  // ksplit > 1 (the host guarantees leftover * ksplit <= grid and ksplit | nks) each of them is
+  // given to ksplit CTAs that take K / ksplit columns each, and the epilogue adds the parts.
+  const int full_rounds = items / (int)gridDim.x;
+  const int leftover = items - full_rounds * (int)gridDim.x;
+  const bool has_tail = (int)blockIdx.x < leftover * ksplit;
+  const int my_items = full_rounds + (has_tail ? 1 : 0);
+  const int tail_nks = nks / ksplit, tail_st0 = ((int)blockIdx.x % ksplit) * tail_nks;
+  const int total_stages = 2 * (full_rounds * nks + (has_tail ? tail_nks : 0));   // stage counter range of this CTA
+  auto item_of = [&](int j) {
+    return j < full_rounds ? (int)blockIdx.x + j * (int)gridDim.x : full_rounds * (int)gridDim.x + (int)blockIdx.x / ksplit;
+  };
   // Ring positions of each role, carried across items (a stage's global index only ever grows by one).
   int raw_next = 0, raw_j = 0, raw_h = 0, raw_st = 0;         // loader: next raw stage and where it lies
   RingPos ld_raw{0, 0}, ld_b{0, 0}, ld_bdone{0, 0};           // loader: raw slot, activation slot, DONE(stage - BST)
@@ -203,7 +214,10 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     const int grp = item % groups;
     const int t_base = grp * BN;
     const int T_pass = min(BN, T_total - t_base);
-    const int it_base = j * 2 * nks;                          // global operand-stage counter
+    const int it_base = j * 2 * nks;                          // global operand-stage counter (a shared item is the last)
+    const bool shared_item = j >= full_rounds && ksplit > 1;
+    const int nks_i = shared_item ? tail_nks : nks;           // stages per half of this item, first column stage
+    const int st0 = shared_item ? tail_st0 : 0;
 
     if (warp < LTC_DQW) {
       // ================= workers: decode stage `it`, then scale the accumulators of stage `it - 1` =================
@@ -252,10 +266,10 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
         for (int i = 0; i < CW; ++i) acc[i] = 0.f;
-        for (int st = 0; st < nks; ++st) {
+        for (int st = 0; st < nks_i; ++st) {
           const int it = g_it;
           const int sa = it & (LTC_AST - 1), sr = wk_raw.slot;
-          const uint32_t off = (uint32_t)(st * C::CHUNK_BYTES) & 15u;
+          const uint32_t off = (uint32_t)((st0 + st) * C::CHUNK_BYTES) & 15u;
           const uint32_t sp0 = sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE) + off + (uint32_t)(R * C::BOX);
           wait_or_abort(RAW_FULL(sr), wk_raw.par);
           wk_raw.advance(RST);
@@ -318,7 +332,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       // ================= MMA issuer (the whole warp polls: the wake-up is faster; lane 0 issues) =================
       const uint32_t idesc = umma_idesc_f16(BN);
       for (int h = 0; h < 2; ++h) {
-        for (int st = 0; st < nks; ++st) {
+        for (int st = 0; st < nks_i; ++st) {
           const int it = g_it++;
           const int sa = it & (LTC_AST - 1), sb = mm_b.slot;
           bool ok = wait_or_abort(B_FULL(sb), mm_b.par);
@@ -370,7 +384,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       if (lane == 0) {
         const uint8_t* src = reinterpret_cast<const uint8_t*>(ximg) + (size_t)grp * BN * K * 2;
         int nb = it_base, b_st = 0;                             // next activation stage to request (b_st: inside the half)
-        const int nb_end = it_base + 2 * nks;
+        const int nb_end = it_base + 2 * nks_i;
         const int raw_need = min(total_stages, nb_end);          // every raw stage of this item must be requested here
         int idle = 0;
         while ((nb < nb_end || raw_next < raw_need) && idle < (1 << 22)) {
@@ -378,24 +392,26 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
           if (raw_next < total_stages &&
               (raw_next < RST || mbar_try_wait(RAW_EMPTY(ld_raw.slot), ld_raw.par ^ 1u))) {
             // raw stage raw_next = (item raw_j, half raw_h, stage raw_st)
+            const bool raw_shared = raw_j >= full_rounds && ksplit > 1;
+            const int raw_nks = raw_shared ? tail_nks : nks, raw_st0 = raw_shared ? tail_st0 : 0;
             const int row0 = (item_of(raw_j) / groups) * ITEM_ROWS + (Epi::DUAL ? 0 : raw_h * 128);
             const int sr = ld_raw.slot;
             mbar_arrive_expect_tx(RAW_FULL(sr), (uint32_t)C::RAW_STAGE);
             tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), (Epi::DUAL && raw_h) ? &wmap1 : &wmap0,
-                       (int)(((uint32_t)(raw_st * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
+                       (int)(((uint32_t)((raw_st0 + raw_st) * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
             ld_raw.advance(RST);
             ++raw_next;
-            if (++raw_st == nks) { raw_st = 0; if (++raw_h == 2) { raw_h = 0; ++raw_j; } }
+            if (++raw_st == raw_nks) { raw_st = 0; if (++raw_h == 2) { raw_h = 0; ++raw_j; } }
             progressed = true;
           }
           if (nb < nb_end && (nb < LTC_BST || mbar_try_wait(DONE(ld_bdone.slot), ld_bdone.par))) {
             if (nb >= LTC_BST) ld_bdone.advance(LTC_DONE);
             const int sb = ld_b.slot;
             mbar_arrive_expect_tx(B_FULL(sb), (uint32_t)S::B_STAGE);
-            bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)b_st * S::B_STAGE,
+            bulk_g2s(sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE), src + (size_t)(st0 + b_st) * S::B_STAGE,
                      (uint32_t)S::B_STAGE, B_FULL(sb));
             ld_b.advance(LTC_BST);
-            if (++b_st == nks) b_st = 0;
+            if (++b_st == nks_i) b_st = 0;
             ++nb;
             progressed = true;
           }
@@ -412,7 +428,9 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     __syncthreads();
     tc_fence_after();
     {
-      TcItem item_ctx{tmem_base, logit, rowscale, tile, t_base, T_pass, warp, lane};
+      TcItem item_ctx{tmem_base, logit, rowscale, tile, t_base, T_pass, warp, lane,
+                      shared_item ? (int)blockIdx.x % ksplit : 0, shared_item ? ksplit : 1,
+                      shared_item ? (int)blockIdx.x / ksplit : 0};
       Epi::run(ea, item_ctx);
     }
     tc_fence_before();

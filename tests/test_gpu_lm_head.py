@@ -183,6 +183,21 @@ def test_vocab_sharded_merge_equals_single_call(mode, shards):
     np.testing.assert_array_equal(host(merged), single)
 
 
+@pytest.mark.parametrize("fmt,K", [("q8_0", 256), ("q8_0", 512), ("nvfp4", 512), ("mxfp4", 1024)])
+def test_last_round_items_shared_between_ctas(fmt, K):
+    """More 256-row tiles than SMs with a small remainder (160 tiles): the tiles of the last, partial
+    round are each computed by 2 or 4 CTAs that take a slice of K and exchange partial logits."""
+    T, V = 20, 160 * 256 - 40
+    h, Wq = _case(fmt, T, V, K, "bf16", 500 + K, hs=1.0, ws=0.05)
+    L = O.lm_head_logits(h, Wq, fmt)
+    for mode, kw in (("argmax", {}), ("topp", dict(k=32, top_p=0.9)), ("topk", dict(k=8))):
+        tok = _run(h, Wq, fmt, "bf16", mode, temperature=0.8, seed=5, **kw)
+        want, margin = O.lm_head_sample_from_logits(L, MODES[mode], k=kw.get("k", 0), temperature=0.8,
+                                                    seed=5, top_p=kw.get("top_p", 0.9), return_detail=True)
+        n = check_ids(tok, want, margin, EPS, f"{fmt}/K{K}/{mode}")
+        assert n >= T - 1
+
+
 @pytest.mark.parametrize("mode", ["argmax", "topk", "topp"])
 def test_vocab_sharded_merge_many_hidden_rows(mode):
     """The shard entry points with more than 16 hidden rows (tensor-memory stage 1 per shard, padding
