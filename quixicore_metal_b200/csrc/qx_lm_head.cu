@@ -548,7 +548,11 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
   const long long sms = sm_count();
   const long long leftover = items % sms;
   int ksplit = 1;
-  if (split_enabled && leftover > 0) {
+  // not while the stream is being captured: a cooperative launch that fails there would
+  // invalidate the capture, and there is no second attempt inside one
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(st, &cap);
+  if (split_enabled && leftover > 0 && cap == cudaStreamCaptureStatusNone) {
     if (leftover * 4 <= sms && nks % 4 == 0) ksplit = 4;
     else if (leftover * 2 <= sms && nks % 2 == 0) ksplit = 2;
   }
