@@ -887,9 +887,23 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
   }
 
   // ---- mode 3: nucleus over the pooled candidates against the full-vocabulary normalizer ----
+  // the bisection steps re-scan every candidate: keep ls and exp(ls - mx) in shared memory when they
+  // fit (absent candidates are stored as -inf / 0 and never pass a threshold); then the candidates
+  // are read from global memory once
+  const bool cached = cache_elems >= ncand;
+  float* c_ls = cache;
+  float* c_ex = cache + cache_elems;
   float mx = QX_NEG_INF;
-  for (long long j = tid; j < ncand; j += nth)
-    if (ci(j) >= 0) mx = fmaxf(mx, cv(j) * invtemp);
+  if (cached) {
+    for (long long j = tid; j < ncand; j += nth) {
+      const float ls = ci(j) >= 0 ? cv(j) * invtemp : QX_NEG_INF;
+      c_ls[j] = ls;
+      mx = fmaxf(mx, ls);
+    }
+  } else {
+    for (long long j = tid; j < ncand; j += nth)
+      if (ci(j) >= 0) mx = fmaxf(mx, cv(j) * invtemp);
+  }
   mx = block_max(mx, S);
   float Z = 0.f;
   for (long long j = tid; j < nlse; j += nth) {
@@ -897,17 +911,11 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
     if (pl > QX_NEG_INF) Z += expf(pl - mx);
   }
   Z = block_sum(Z, S);
-  // the 32 bisection steps re-scan every candidate: keep ls and exp(ls - mx) in shared memory
-  // when they fit (absent candidates are stored as -inf / 0 and never pass a threshold)
-  const bool cached = cache_elems >= ncand;
-  float* c_ls = cache;
-  float* c_ex = cache + cache_elems;
   if (cached) {
-    for (long long j = tid; j < ncand; j += nth) {
-      const bool ok = ci(j) >= 0;
-      const float ls = cv(j) * invtemp;
-      c_ls[j] = ok ? ls : QX_NEG_INF;
-      c_ex[j] = ok ? expf(ls - mx) : 0.f;
+    const int n = (int)ncand;
+    for (int j = tid; j < n; j += nth) {
+      const float ls = c_ls[j];
+      c_ex[j] = ls > QX_NEG_INF ? expf(ls - mx) : 0.f;
     }
     __syncthreads();
   }
