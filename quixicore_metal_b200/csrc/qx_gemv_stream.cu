@@ -4,10 +4,15 @@
 // Two launches per call: prep_activations_kernel turns the activations into row-scaled f16 in the
 // decoder's column order (stream-ordered scratch of M*K*2 + M*4 bytes), then gemv_stream_kernel
 // streams the weights.  Work split of the main kernel: an m-tile is 16 weight rows (16 gate + 16 up
-// rows for SwiGLU).  A CTA is GROUPS x KS warps; the KS warps of a group share one m-tile and each
-// streams its own slice of K through its private ring, then the group adds the KS partial
-// accumulators in a fixed order (deterministic) and warp 0 of the group applies the row scale,
-// bias / activation / residual and stores.  KS > 1 keeps every SM busy when there are few rows.
+// rows for SwiGLU); a step is one pipeline stage (KC columns) of one m-tile.  One CTA per SM takes a
+// contiguous share of the m-tiles, balanced to within one tile, and its warps cut the flat list of
+// the share's (tile, chunk) steps into equal contiguous ranges, each streamed through the warp's
+// private ring.  A tile that lies inside one range is finished by that warp.  A tile cut by range
+// boundaries is finished after a CTA barrier by the warp that holds its chunk 0, which adds the
+// other warps' partial accumulators from shared memory in warp order (deterministic).  Every SM
+// therefore streams the same number of bytes whatever N is (the earlier split - whole tiles per
+// warp group, K halved or quartered inside a group - left half of the SMs idle for the last third
+// of the run at N = 28672: 1792 tiles on 1184 groups).
 #include <cstdlib>
 #include <mutex>
 
@@ -180,16 +185,21 @@ struct StreamCfg {
   static constexpr int KC = StreamFmt<FMT>::KC;
   static constexpr int ROWS = DUAL ? 32 : 16;
   using WS = WarpStream<FMT, KC, ROWS, STREAM_STAGES>;
+  // shared memory per warp: ring, mbarriers, one partial-sum slot (NACC x 32 f32)
+  static constexpr int warp_smem(int nt) { return WS::WARP_BYTES + STREAM_STAGES * 8 + 32 * nt * 4 * (DUAL ? 2 : 1) * 4; }
+  // warps per CTA: as many as 220 KB of shared memory hold, at most STREAM_MAX_WARPS
+  static constexpr int max_warps(int nt) {
+    return 220 * 1024 / warp_smem(nt) < STREAM_MAX_WARPS ? 220 * 1024 / warp_smem(nt) : STREAM_MAX_WARPS;
+  }
 };
 
 template <int FMT, int NT, bool DUAL, typename T>
-__global__ void __launch_bounds__(STREAM_MAX_WARPS * 32, 1)
+__global__ void __launch_bounds__(StreamCfg<FMT, DUAL>::max_warps(NT) * 32, 1)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
                    const __half* __restrict__ x16, const float* __restrict__ rowscale,
                    const T* __restrict__ bias0, const T* __restrict__ bias1,
                    const T* __restrict__ residual, T* __restrict__ y, int M, int K, int N,
-                   int activation, int use_bias, int use_residual, int ks_log2,
-                   int* __restrict__ err_flag) {
+                   int activation, int use_bias, int use_residual, int* __restrict__ err_flag) {
   using Cfg = StreamCfg<FMT, DUAL>;
   using WS = typename Cfg::WS;
   using F = StreamFmt<FMT>;
@@ -199,27 +209,24 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int KS = 1 << ks_log2;
-  const int groups = nwarps >> ks_log2;                 // host guarantees KS divides nwarps
-  const int group = warp >> ks_log2, ks = warp & (KS - 1);
 
-  // shared memory: [per-warp rings][mbarriers][per-group reduction buffers (2 x KS x 32 x NACC f32)]
+  // shared memory: [per-warp rings][mbarriers][one partial-sum slot per warp (NACC x 32 f32)]
   uint8_t* ring = smem_raw + (size_t)warp * WS::WARP_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)nwarps * WS::WARP_BYTES) + warp * STREAM_STAGES;
-  float* red = reinterpret_cast<float*>(smem_raw + (size_t)nwarps * WS::WARP_BYTES + (size_t)nwarps * STREAM_STAGES * 8);
-  red += (size_t)group * 2 * KS * 32 * NACC;
+  float* slots = reinterpret_cast<float*>(smem_raw + (size_t)nwarps * WS::WARP_BYTES + (size_t)nwarps * STREAM_STAGES * 8);
 
   WS ws;
   ws.init(smem_u32(ring), smem_u32(bars), &wmap0, &wmap1, 0, K, lane, err_flag);
 
+  // This CTA's m-tiles [T0, T1) and the flat list of their (tile, chunk) steps; this warp's share
+  // of the list is [sb, se).
   const int ntiles = (N + 15) >> 4;
-  const int group_global = blockIdx.x * groups + group;
-  const int groups_total = gridDim.x * groups;
-  const int my_tiles = group_global < ntiles ? (ntiles - group_global + groups_total - 1) / groups_total : 0;
-  const int c_begin = (int)(((long long)ws.nch * ks) >> ks_log2);
-  const int c_end = (int)(((long long)ws.nch * (ks + 1)) >> ks_log2);
-  const int cper = c_end - c_begin;
-  const int steps = my_tiles * cper;
+  const int nch = ws.nch;
+  const int T0 = (int)((long long)ntiles * blockIdx.x / gridDim.x);
+  const int T1 = (int)((long long)ntiles * (blockIdx.x + 1) / gridDim.x);
+  const long long S = (long long)(T1 - T0) * nch;
+  auto range_begin = [&](int w) { return (int)(S * w / nwarps); };
+  const int sb = range_begin(warp), se = range_begin(warp + 1);
 
   const __half* xr[NT];
 #pragma unroll
@@ -228,142 +235,140 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     xr[nt] = m < M ? x16 + (size_t)m * K : nullptr;
   }
 
-  auto step_tile = [&](int i) { return group_global + (i / cper) * groups_total; };
-  auto step_chunk = [&](int i) { return c_begin + (i % cper); };
-
-  if (cper > 0) {
+  // (tile, chunk) of the next step to fetch
+  int f_tile = T0 + sb / nch, f_c = sb % nch, fetched = sb;
+  auto fetch_next = [&](int stage) {
+    ws.issue(stage, f_tile * 16, f_c);
+    if (++f_c == nch) { f_c = 0; ++f_tile; }
+    ++fetched;
+  };
 #pragma unroll
-    for (int p = 0; p < STREAM_STAGES - 1; ++p)
-      if (p < steps) ws.issue(p, step_tile(p) * 16, step_chunk(p));
-  }
+  for (int p = 0; p < STREAM_STAGES - 1; ++p)
+    if (fetched < se) fetch_next(p);
   // Programmatic dependent launch: this grid may start while the activation-preparation kernel is
   // still running (the weight boxes above do not depend on it); everything below reads its output.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float acc[NSETS][NT][4];
-#pragma unroll
-  for (int a = 0; a < NSETS; ++a)
-#pragma unroll
-    for (int b = 0; b < NT; ++b)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
-
-  int tile_parity = 0;
-  for (int j = 0; j < my_tiles; ++j) {
-    const int row0 = (group_global + j * groups_total) * 16;
-    for (int cc = 0; cc < cper; ++cc) {
-      const int i = j * cper + cc;
-      const int stage = i % STREAM_STAGES;
-      const int nxt = i + STREAM_STAGES - 1;
-      if (nxt < steps) ws.issue(nxt % STREAM_STAGES, step_tile(nxt) * 16, step_chunk(nxt));
-      const bool ready = ws.wait(stage, (uint32_t)((i / STREAM_STAGES) & 1));
-
-      const int c = c_begin + cc;
-      const int col_base = c * Cfg::KC;
-      const int ngroups = ready ? min(Cfg::KC, K - col_base) / F::GROUP : 0;
-      uint32_t s[2 * NSETS];
-      s[0] = ws.slot_addr(stage, g, c);
-      s[1] = ws.slot_addr(stage, g + 8, c);
-      if constexpr (DUAL) {
-        s[2] = ws.slot_addr(stage, 16 + g, c);
-        s[3] = ws.slot_addr(stage, 24 + g, c);
-      }
-      constexpr uint32_t GROUP_BYTES = F::GROUP / F::BK * F::BB;
-      using GP = GroupProc<FMT>;
-      constexpr bool PRE = NT <= 2;                 // prefetch activations one group ahead
-      typename GP::template BFrag<NT> bcur, bnext;
-      if (PRE && ngroups > 0) GP::template load_b<NT>(xr, col_base, t, bcur);
-      for (int gi = 0; gi < ngroups; ++gi) {
-        if (PRE && gi + 1 < ngroups) GP::template load_b<NT>(xr, col_base + (gi + 1) * F::GROUP, t, bnext);
-        GP::template run<NSETS, NT, PRE>(s, t, bcur, xr, col_base + gi * F::GROUP, acc);
-        if (PRE) bcur = bnext;
-#pragma unroll
-        for (int r = 0; r < 2 * NSETS; ++r) s[r] += GROUP_BYTES;
-      }
-      __syncwarp();
-    }
-
-    // ---- combine the KS partial sums of this tile (fixed order) ----
-    if (KS > 1) {
-      float* buf = red + (size_t)tile_parity * KS * 32 * NACC;
-      float* flat = &acc[0][0][0];
-      if (ks != 0) {
-#pragma unroll
-        for (int i = 0; i < NACC; ++i) buf[((size_t)ks * NACC + i) * 32 + lane] = flat[i];
-      }
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(KS * 32) : "memory");
-      if (ks == 0) {
-        for (int k2 = 1; k2 < KS; ++k2) {
-#pragma unroll
-          for (int i = 0; i < NACC; ++i) flat[i] += buf[((size_t)k2 * NACC + i) * 32 + lane];
-        }
-      }
-      tile_parity ^= 1;
-    }
-
-    // ---- epilogue: row scale back, bias, activation, residual, one rounding ----
-    if (ks == 0) {
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int n = row0 + g + (e >> 1) * 8;
-          const int m = nt * 8 + 2 * t + (e & 1);
-          if (n < N && m < M) {
-            const float rs = rowscale[m];
-            float v = acc[0][nt][e] * rs;
-            const size_t o = (size_t)m * N + n;
-            if constexpr (DUAL) {
-              float up = acc[NSETS - 1][nt][e] * rs;
-              if (use_bias) { v += to_f32<T>(bias0[n]); up += to_f32<T>(bias1[n]); }
-              y[o] = from_f32<T>(silu(v) * up);
-            } else {
-              if (use_bias) v += to_f32<T>(bias0[n]);
-              v = apply_act(v, activation);
-              if (use_residual) v += to_f32<T>(residual[o]);
-              y[o] = from_f32<T>(v);
-            }
-          }
-        }
-      }
-    }
+  auto clear_acc = [&]() {
 #pragma unroll
     for (int a = 0; a < NSETS; ++a)
 #pragma unroll
       for (int b = 0; b < NT; ++b)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
-  }
-}
+  };
+  clear_acc();
 
-template <int FMT, int NT, bool DUAL>
-static size_t stream_smem_bytes(int nwarps, int ks) {
-  using WS = typename StreamCfg<FMT, DUAL>::WS;
-  const int nacc = NT * 4 * (DUAL ? 2 : 1);
-  return (size_t)nwarps * WS::WARP_BYTES + (size_t)nwarps * STREAM_STAGES * 8 +
-         (ks > 1 ? (size_t)nwarps * 2 * 32 * nacc * 4 : 0);
+  // row scale back, bias, activation, residual, one rounding
+  auto epilogue = [&](int row0) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int n = row0 + g + (e >> 1) * 8;
+        const int m = nt * 8 + 2 * t + (e & 1);
+        if (n < N && m < M) {
+          const float rs = rowscale[m];
+          float v = acc[0][nt][e] * rs;
+          const size_t o = (size_t)m * N + n;
+          if constexpr (DUAL) {
+            float up = acc[NSETS - 1][nt][e] * rs;
+            if (use_bias) { v += to_f32<T>(bias0[n]); up += to_f32<T>(bias1[n]); }
+            y[o] = from_f32<T>(silu(v) * up);
+          } else {
+            if (use_bias) v += to_f32<T>(bias0[n]);
+            v = apply_act(v, activation);
+            if (use_residual) v += to_f32<T>(residual[o]);
+            y[o] = from_f32<T>(v);
+          }
+        }
+      }
+    }
+  };
+
+  int tile = T0 + sb / nch, c = sb % nch;
+  int seg_c0 = c;            // chunk at which the running partial sum of `tile` started
+  int pending_tile = -1;     // tile whose first chunks this warp summed but whose end lies in later warps
+  for (int i = sb; i < se; ++i) {
+    const int k = i - sb;
+    const int stage = k % STREAM_STAGES;
+    if (fetched < se) fetch_next((k + STREAM_STAGES - 1) % STREAM_STAGES);
+    const bool ready = ws.wait(stage, (uint32_t)((k / STREAM_STAGES) & 1));
+
+    const int col_base = c * Cfg::KC;
+    const int ngroups = ready ? min(Cfg::KC, K - col_base) / F::GROUP : 0;
+    uint32_t s[2 * NSETS];
+    s[0] = ws.slot_addr(stage, g, c);
+    s[1] = ws.slot_addr(stage, g + 8, c);
+    if constexpr (DUAL) {
+      s[2] = ws.slot_addr(stage, 16 + g, c);
+      s[3] = ws.slot_addr(stage, 24 + g, c);
+    }
+    constexpr uint32_t GROUP_BYTES = F::GROUP / F::BK * F::BB;
+    using GP = GroupProc<FMT>;
+    constexpr bool PRE = NT <= 2;                 // prefetch activations one group ahead
+    typename GP::template BFrag<NT> bcur, bnext;
+    if (PRE && ngroups > 0) GP::template load_b<NT>(xr, col_base, t, bcur);
+    for (int gi = 0; gi < ngroups; ++gi) {
+      if (PRE && gi + 1 < ngroups) GP::template load_b<NT>(xr, col_base + (gi + 1) * F::GROUP, t, bnext);
+      GP::template run<NSETS, NT, PRE>(s, t, bcur, xr, col_base + gi * F::GROUP, acc);
+      if (PRE) bcur = bnext;
+#pragma unroll
+      for (int r = 0; r < 2 * NSETS; ++r) s[r] += GROUP_BYTES;
+    }
+    __syncwarp();
+
+    ++c;
+    const bool tile_done = c == nch;
+    if (tile_done || i + 1 == se) {
+      if (seg_c0 != 0) {
+        // the tile began in an earlier warp, which adds this partial sum after the CTA barrier
+        float* slot = slots + (size_t)warp * NACC * 32;
+        const float* flat = &acc[0][0][0];
+#pragma unroll
+        for (int q = 0; q < NACC; ++q) slot[q * 32 + lane] = flat[q];
+        clear_acc();
+      } else if (tile_done) {
+        epilogue(tile * 16);
+        clear_acc();
+      } else {
+        pending_tile = tile;
+      }
+      if (tile_done) { c = 0; ++tile; seg_c0 = 0; }
+    }
+  }
+
+  // ---- tiles split over several warps: the warp that holds chunk 0 adds the others' partial sums
+  //      in warp order (deterministic) and finishes the tile ----
+  __syncthreads();
+  if (pending_tile >= 0) {
+    const long long tile_end = (long long)(pending_tile - T0 + 1) * nch;
+    float* flat = &acc[0][0][0];
+    for (int w2 = warp + 1; w2 < nwarps; ++w2) {
+      const int b2 = range_begin(w2), e2 = range_begin(w2 + 1);
+      if (b2 >= tile_end) break;
+      if (b2 < e2) {
+        const float* slot = slots + (size_t)w2 * NACC * 32;
+#pragma unroll
+        for (int q = 0; q < NACC; ++q) flat[q] += slot[q * 32 + lane];
+      }
+    }
+    epilogue(pending_tile * 16);
+  }
 }
 
 template <int FMT, int NT, bool DUAL, typename T>
 static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
-  using Cfg = StreamCfg<FMT, DUAL>;
   const int sms = sm_count();
   const int ntiles = (int)((a.N + 15) / 16);
-  const int nch = (int)((a.K + Cfg::KC - 1) / Cfg::KC);
-  int nwarps = STREAM_MAX_WARPS;
-  if (const char* e = getenv("QX_STREAM_WARPS")) nwarps = max(1, min(STREAM_MAX_WARPS, atoi(e)));
-  while (nwarps > 1 && stream_smem_bytes<FMT, NT, DUAL>(nwarps, 8) > 220 * 1024) --nwarps;
-  if (nwarps > 4) nwarps &= ~3; else if (nwarps == 3) nwarps = 2;
-  // split K inside a CTA (KS a power of two that divides nwarps) until there are enough
-  // (tile, slice) units for every warp of the GPU
-  int ks_log2 = 0;
-  while (nwarps % (2 << ks_log2) == 0 && ((long long)ntiles << ks_log2) < (long long)sms * nwarps &&
-         (nch >> (ks_log2 + 1)) >= 1)
-    ++ks_log2;
-  const int groups = nwarps >> ks_log2;
-  int blocks = (ntiles + groups - 1) / groups;
-  if (blocks > sms) blocks = sms;
-  const size_t smem = stream_smem_bytes<FMT, NT, DUAL>(nwarps, 1 << ks_log2);
+  using Cfg = StreamCfg<FMT, DUAL>;
+  int nwarps = Cfg::max_warps(NT);
+  if (const char* e = getenv("QX_STREAM_WARPS")) nwarps = max(1, min(nwarps, atoi(e)));
+  // one CTA per SM; a CTA takes a contiguous, balanced share of the m-tiles and its warps split the
+  // (tile, chunk) steps of that share evenly
+  const int blocks = ntiles < sms ? ntiles : sms;
+  const size_t smem = (size_t)nwarps * Cfg::warp_smem(NT);
   static bool attr_set[64] = {};                    // per instantiation and device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -411,11 +416,11 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, T>, map0, map1, (const __half*)x16,
                          (const float*)rowscale, (const T*)a.bias0, (const T*)a.bias1,
                          (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
-                         a.use_bias, a.use_residual, ks_log2, err) != cudaSuccess) {
+                         a.use_bias, a.use_residual, err) != cudaSuccess) {
     cudaGetLastError();
     gemv_stream_kernel<FMT, NT, DUAL, T><<<blocks, nwarps * 32, smem, st>>>(
         map0, map1, x16, rowscale, (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual,
-        (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, ks_log2, err);
+        (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, err);
   }
   if (must_free) cudaFreeAsync(scratch, st);
   note_launch(2);
