@@ -178,18 +178,23 @@ void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free) {
 }
 
 constexpr int STREAM_STAGES = 2;      // per-warp ring depth; latency is hidden by the number of warps
-constexpr int STREAM_MAX_WARPS = 16;
 
+// Measured at K = 8192, N = 28672 (one GPU, batch 1 unless noted):
+//  * single matrix, up to 8 rows: 20 warps (102 registers each) beat 16 by 3-10 % (q8_0 56.7 -> 51.5 us);
+//    mxfp4 needs 103 registers and is left at 16 warps;
+//  * SwiGLU pair: a stage holds 32 rows, so only 10 warps fit with full-width stages; half-width
+//    stages let 16 warps in (nvfp4 85.1 -> 76.5 us).  q6_K cannot halve (a stage is one decode group).
 template <int FMT, bool DUAL>
 struct StreamCfg {
-  static constexpr int KC = StreamFmt<FMT>::KC;
+  static constexpr int KC = (DUAL && FMT != F_Q6_K) ? StreamFmt<FMT>::KC / 2 : StreamFmt<FMT>::KC;
   static constexpr int ROWS = DUAL ? 32 : 16;
   using WS = WarpStream<FMT, KC, ROWS, STREAM_STAGES>;
   // shared memory per warp: ring, mbarriers, one partial-sum slot (NACC x 32 f32)
   static constexpr int warp_smem(int nt) { return WS::WARP_BYTES + STREAM_STAGES * 8 + 32 * nt * 4 * (DUAL ? 2 : 1) * 4; }
-  // warps per CTA: as many as 220 KB of shared memory hold, at most STREAM_MAX_WARPS
+  static constexpr int warp_cap(int nt) { return (!DUAL && nt == 1 && FMT != F_MXFP4) ? 20 : 16; }
+  // warps per CTA: as many as 220 KB of shared memory hold, at most warp_cap
   static constexpr int max_warps(int nt) {
-    return 220 * 1024 / warp_smem(nt) < STREAM_MAX_WARPS ? 220 * 1024 / warp_smem(nt) : STREAM_MAX_WARPS;
+    return 220 * 1024 / warp_smem(nt) < warp_cap(nt) ? 220 * 1024 / warp_smem(nt) : warp_cap(nt);
   }
 };
 
@@ -224,8 +229,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   const int nch = ws.nch;
   const int T0 = (int)((long long)ntiles * blockIdx.x / gridDim.x);
   const int T1 = (int)((long long)ntiles * (blockIdx.x + 1) / gridDim.x);
-  const long long S = (long long)(T1 - T0) * nch;
-  auto range_begin = [&](int w) { return (int)(S * w / nwarps); };
+  const unsigned S = (unsigned)((T1 - T0) * nch);          // the host keeps S * (nwarps + 1) below 2^31
+  auto range_begin = [&](int w) { return (int)(S * (unsigned)w / (unsigned)nwarps); };
   const int sb = range_begin(warp), se = range_begin(warp + 1);
 
   const __half* xr[NT];
@@ -343,16 +348,16 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   //      in warp order (deterministic) and finishes the tile ----
   __syncthreads();
   if (pending_tile >= 0) {
-    const long long tile_end = (long long)(pending_tile - T0 + 1) * nch;
+    const int tile_end = (pending_tile - T0 + 1) * nch;
     float* flat = &acc[0][0][0];
-    for (int w2 = warp + 1; w2 < nwarps; ++w2) {
-      const int b2 = range_begin(w2), e2 = range_begin(w2 + 1);
-      if (b2 >= tile_end) break;
-      if (b2 < e2) {
-        const float* slot = slots + (size_t)w2 * NACC * 32;
+    int b2 = se;                                   // first step of the tile held by another warp
+    while (b2 < tile_end) {
+      // step i belongs to warp floor(((i + 1) * nwarps - 1) / S); warps with empty ranges are skipped
+      const int w2 = (int)(((unsigned)(b2 + 1) * (unsigned)nwarps - 1u) / S);
+      const float* slot = slots + (size_t)w2 * NACC * 32;
 #pragma unroll
-        for (int q = 0; q < NACC; ++q) flat[q] += slot[q * 32 + lane];
-      }
+      for (int q = 0; q < NACC; ++q) flat[q] += slot[q * 32 + lane];
+      b2 = range_begin(w2 + 1);
     }
     epilogue(pending_tile * 16);
   }
@@ -368,6 +373,8 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   // one CTA per SM; a CTA takes a contiguous, balanced share of the m-tiles and its warps split the
   // (tile, chunk) steps of that share evenly
   const int blocks = ntiles < sms ? ntiles : sms;
+  const long long nch = (a.K + Cfg::KC - 1) / Cfg::KC;
+  if ((long long)((ntiles + blocks - 1) / blocks) * nch * (nwarps + 1) >= (1LL << 31)) return false;
   const size_t smem = (size_t)nwarps * Cfg::warp_smem(NT);
   static bool attr_set[64] = {};                    // per instantiation and device
   int dev = 0;

@@ -203,7 +203,9 @@ class TPDecodeStack:
             self.dist.all_reduce(t, group=self.group)
         return t
 
-    def layer(self, x, L):
+    def layer(self, x, L, trace=None):
+        """One block.  `trace`, if given, is a dict that receives the residual stream after the
+        O projection ("h"), for tests that compare each half of the block on its own inputs."""
         from . import tk, tk_torch
         qkv = tk.decode_linear_epilogue(x, L["qkv"], format=self.fmt)
         # identity on V: the G query heads of KV group g all take that group's value vector
@@ -213,6 +215,8 @@ class TPDecodeStack:
         attn = v.expand(-1, n_kv, self.q_local // self.kv_local, hd).reshape(-1, self.q_local).contiguous()
         o = self._all_reduce(tk_torch.decode_linear_partial(attn, L["o"], self.fmt))
         x = (o + x.float()).to(x.dtype)
+        if trace is not None:
+            trace["h"] = x
         mid = tk.decode_swiglu(x, L["gate"], L["up"], format=self.fmt)
         d = self._all_reduce(tk_torch.decode_linear_partial(mid, L["down"], self.fmt))
         return (d + x.float()).to(x.dtype)

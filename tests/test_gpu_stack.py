@@ -16,33 +16,59 @@ def _full_layer(rng, hidden, q, kv, inter, fmt):
             "down": mk(hidden, inter)}
 
 
-def _oracle_layer(x, L, fmt, q, kv):
+def _oracle_attn_half(x, L, fmt, q, kv):
     qkv = O.decode_linear_epilogue(x, L["qkv"], fmt, None, None, 0, "bf16")
     hd = 128                                   # query heads of KV group g take the value vector of group g
     v = qkv[:, q + kv:].reshape(-1, kv // hd, 1, hd)
     attn = np.broadcast_to(v, (v.shape[0], kv // hd, q // kv, hd)).reshape(-1, q)
     o = O.matmul_f64(attn, O.dequantize(fmt, L["o"]))
-    x = O.round_bf16((o + x).astype(np.float32))
-    mid = O.decode_swiglu(x, L["gate"], L["up"], fmt, None, None, "bf16")
+    return O.round_bf16((o + x).astype(np.float32))
+
+
+def _oracle_mlp_half(h, L, fmt):
+    mid = O.decode_swiglu(h, L["gate"], L["up"], fmt, None, None, "bf16")
     d = O.matmul_f64(mid, O.dequantize(fmt, L["down"]))
-    return O.round_bf16((d + x).astype(np.float32))
+    return O.round_bf16((d + h).astype(np.float32))
+
+
+def _oracle_layer(x, L, fmt, q, kv):
+    return _oracle_mlp_half(_oracle_attn_half(x, L, fmt, q, kv), L, fmt)
+
+
+def _check_half(got, ref, what):
+    err = np.abs(got - ref)
+    assert np.all(err <= np.abs(ref) * 2.0 ** -7 * 1.01 + 2e-2), (what, float(err.max()))
+    assert np.mean(got == ref) > 0.9, (what, float(np.mean(got == ref)))
 
 
 @pytest.mark.parametrize("M", [1, 32])
 def test_stack_single_rank_matches_oracle(M):
+    """Every half block (QKV -> O -> residual; SwiGLU -> down -> residual) is compared with the
+    oracle on the device's own input of that half.  The whole chain is checked with a tolerance
+    only: a value that sits on a bf16 rounding boundary may round either way (fp32 vs fp64
+    accumulation order), and one such flip in the residual stream moves a tenth of the next
+    SwiGLU outputs by one ulp, so the fraction of bit-identical values after several blocks
+    measures the summation order, not correctness."""
     from quixicore_metal_b200 import parallel
     fmt, hidden, q, kv, inter = "nvfp4", 1024, 512, 512, 1024
     rng = np.random.default_rng(11 + M)
     layers = [_full_layer(rng, hidden, q, kv, inter, fmt) for _ in range(2)]
     x = rounded(rng.standard_normal((M, hidden)), "bf16")
     stack = parallel.TPDecodeStack([{k: dev(v) for k, v in L.items()} for L in layers], fmt)
-    got = host(stack.forward(dev(x, "bf16")))
+    xd = dev(x, "bf16")
     ref = x
-    for L in layers:
+    for i, (Ld, L) in enumerate(zip(stack.layers, layers)):
+        trace = {}
+        x_in = host(xd)
+        xd = stack.layer(xd, Ld, trace)
+        h = host(trace["h"])
+        _check_half(h, _oracle_attn_half(x_in, L, fmt, q, kv), f"layer {i} attention half")
+        _check_half(host(xd), _oracle_mlp_half(h, L, fmt), f"layer {i} MLP half")
         ref = _oracle_layer(ref, L, fmt, q, kv)
+    got = host(stack.forward(dev(x, "bf16")))
+    assert np.array_equal(got, host(xd))                     # forward() is the same chain
     err = np.abs(got - ref)
     assert np.all(err <= np.abs(ref) * 2.0 ** -6 + 2e-2), float(err.max())   # two bf16 roundings per layer
-    assert np.mean(got == ref) > 0.8
 
 
 def test_stack_two_shards_emulated_on_one_device():
