@@ -123,6 +123,7 @@ qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void*
   GemvArgs a{x, weight, nullptr, nullptr, nullptr, nullptr, y, M, K, N, f, dtype, 0, 0, 0};
   a.out_f32 = 1;
   if (stream_path_ok(a) && launch_gemv_stream((cudaStream_t)stream, a)) return check_launch(op);
+  if (stream_passes_ok(a) && launch_gemv_stream_passes((cudaStream_t)stream, a)) return check_launch(op);
   if (tc_path_ok(a) && launch_gemm_tc((cudaStream_t)stream, a)) return check_launch(op);
   return fail(QX_UNSUPPORTED_LAYOUT, op,
               "fp32 partial projections need bf16/f16 activations, 16-byte aligned bases and K a "

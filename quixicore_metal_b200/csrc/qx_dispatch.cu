@@ -18,6 +18,7 @@ void launch_projection(cudaStream_t st, const GemvArgs& a) {
     return !(e && e[0] == '0');
   }();
   if (!force_generic && stream_path_ok(a) && launch_gemv_stream(st, a)) return;
+  if (!force_generic && stream_passes_ok(a) && launch_gemv_stream_passes(st, a)) return;
   if (!force_generic && tc_enabled && tc_path_ok(a) && launch_gemm_tc(st, a)) return;
   launch_gemv_generic(st, a);
 }

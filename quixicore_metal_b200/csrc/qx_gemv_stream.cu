@@ -179,33 +179,36 @@ void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free) {
 
 constexpr int STREAM_STAGES = 2;      // per-warp ring depth; latency is hidden by the number of warps
 
-// Measured at K = 8192, N = 28672 (one GPU, batch 1 unless noted):
-//  * single matrix, up to 8 rows: 20 warps (102 registers each) beat 16 by 3-10 % (q8_0 56.7 -> 51.5 us);
-//    mxfp4 needs 103 registers and is left at 16 warps;
-//  * SwiGLU pair: a stage holds 32 rows, so only 10 warps fit with full-width stages; half-width
-//    stages let 16 warps in (nvfp4 85.1 -> 76.5 us).  q6_K cannot halve (a stage is one decode group).
-template <int FMT, bool DUAL>
+// HALF = stages of half the format's column count.  Measured at K = 8192, N = 28672 on one GPU:
+//  * single matrix, 1 - 2 rows: full-width stages; 20 warps (102 registers each) beat 16 by 3 - 10 %
+//    (q8_0 56.7 -> 51.5 us); mxfp4 needs 103 registers and is left at 16 warps;
+//  * more rows, or a SwiGLU pair: half-width stages.  The prepared activations (2*K bytes per row)
+//    are re-read from L1 by every warp; the smaller rings leave the L1 side of the SM's memory large
+//    enough to hold them (nvfp4, 8 rows: 60.6 -> 51.9 us), and a SwiGLU stage of 32 rows fits 16
+//    warps instead of 10 (85.1 -> 76.5 us).  q6_K cannot halve (a stage is one decode group).
+template <int FMT, bool DUAL, bool HALF>
 struct StreamCfg {
-  static constexpr int KC = (DUAL && FMT != F_Q6_K) ? StreamFmt<FMT>::KC / 2 : StreamFmt<FMT>::KC;
+  static_assert(!(HALF && FMT == F_Q6_K), "q6_K stages cannot be halved");
+  static constexpr int KC = HALF ? StreamFmt<FMT>::KC / 2 : StreamFmt<FMT>::KC;
   static constexpr int ROWS = DUAL ? 32 : 16;
   using WS = WarpStream<FMT, KC, ROWS, STREAM_STAGES>;
   // shared memory per warp: ring, mbarriers, one partial-sum slot (NACC x 32 f32)
   static constexpr int warp_smem(int nt) { return WS::WARP_BYTES + STREAM_STAGES * 8 + 32 * nt * 4 * (DUAL ? 2 : 1) * 4; }
-  static constexpr int warp_cap(int nt) { return (!DUAL && nt == 1 && FMT != F_MXFP4) ? 20 : 16; }
+  static constexpr int warp_cap(int nt) { return (!DUAL && !HALF && nt == 1 && FMT != F_MXFP4) ? 20 : 16; }
   // warps per CTA: as many as 220 KB of shared memory hold, at most warp_cap
   static constexpr int max_warps(int nt) {
     return 220 * 1024 / warp_smem(nt) < warp_cap(nt) ? 220 * 1024 / warp_smem(nt) : warp_cap(nt);
   }
 };
 
-template <int FMT, int NT, bool DUAL, typename T>
-__global__ void __launch_bounds__(StreamCfg<FMT, DUAL>::max_warps(NT) * 32, 1)
+template <int FMT, int NT, bool DUAL, bool HALF, typename T>
+__global__ void __launch_bounds__(StreamCfg<FMT, DUAL, HALF>::max_warps(NT) * 32, 1)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
                    const __half* __restrict__ x16, const float* __restrict__ rowscale,
                    const T* __restrict__ bias0, const T* __restrict__ bias1,
                    const T* __restrict__ residual, T* __restrict__ y, int M, int K, int N,
                    int activation, int use_bias, int use_residual, int* __restrict__ err_flag) {
-  using Cfg = StreamCfg<FMT, DUAL>;
+  using Cfg = StreamCfg<FMT, DUAL, HALF>;
   using WS = typename Cfg::WS;
   using F = StreamFmt<FMT>;
   constexpr int NSETS = DUAL ? 2 : 1;
@@ -363,11 +366,11 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   }
 }
 
-template <int FMT, int NT, bool DUAL, typename T>
+template <int FMT, int NT, bool DUAL, bool HALF, typename T>
 static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   const int sms = sm_count();
   const int ntiles = (int)((a.N + 15) / 16);
-  using Cfg = StreamCfg<FMT, DUAL>;
+  using Cfg = StreamCfg<FMT, DUAL, HALF>;
   int nwarps = Cfg::max_warps(NT);
   if (const char* e = getenv("QX_STREAM_WARPS")) nwarps = max(1, min(nwarps, atoi(e)));
   // one CTA per SM; a CTA takes a contiguous, balanced share of the m-tiles and its warps split the
@@ -381,7 +384,7 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return false;
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, NT, DUAL, T>,
+    if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, NT, DUAL, HALF, T>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return false;
@@ -399,7 +402,7 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   __half* x16 = (__half*)scratch;
   float* rowscale = (float*)((char*)scratch + x16_bytes);
   launch_prep_activations(st, a.x, a.dtype, x16, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM);
-  using WSG = typename StreamCfg<FMT, DUAL>::WS::G;
+  using WSG = typename Cfg::WS::G;
   const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
   CUtensorMap map0, map1;
   bool maps_ok = make_weight_map(&map0, a.w0, a.N, row_bytes, WSG::PITCH, 16);
@@ -420,12 +423,12 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, T>, map0, map1, (const __half*)x16,
+  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, HALF, T>, map0, map1, (const __half*)x16,
                          (const float*)rowscale, (const T*)a.bias0, (const T*)a.bias1,
                          (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
                          a.use_bias, a.use_residual, err) != cudaSuccess) {
     cudaGetLastError();
-    gemv_stream_kernel<FMT, NT, DUAL, T><<<blocks, nwarps * 32, smem, st>>>(
+    gemv_stream_kernel<FMT, NT, DUAL, HALF, T><<<blocks, nwarps * 32, smem, st>>>(
         map0, map1, x16, rowscale, (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual,
         (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, err);
   }
@@ -437,8 +440,11 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
 template <int FMT, typename T>
 static bool launch_stream_f(cudaStream_t st, const GemvArgs& a) {
   const bool dual = a.w1 != nullptr;
-  if (a.M <= 8) return dual ? launch_stream_t<FMT, 1, true, T>(st, a) : launch_stream_t<FMT, 1, false, T>(st, a);
-  return dual ? launch_stream_t<FMT, 2, true, T>(st, a) : launch_stream_t<FMT, 2, false, T>(st, a);
+  constexpr bool H = FMT != F_Q6_K;                 // half-width stages where the format allows
+  if (a.M <= 2 && !dual) return launch_stream_t<FMT, 1, false, false, T>(st, a);
+  if (a.M <= 8) return dual ? launch_stream_t<FMT, 1, true, H, T>(st, a) : launch_stream_t<FMT, 1, false, H, T>(st, a);
+  // 9 - 16 rows, single matrix: full-width stages measured 3 - 10 % faster than half-width ones
+  return dual ? launch_stream_t<FMT, 2, true, H, T>(st, a) : launch_stream_t<FMT, 2, false, false, T>(st, a);
 }
 
 template <int FMT>
@@ -480,6 +486,42 @@ bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a) {
   if (a.out_f32) return launch_stream_dt<float>(st, a);      // raw fp32 dot products
   if (a.dtype == QX_DTYPE_F16) return launch_stream_dt<__half>(st, a);
   return launch_stream_dt<__nv_bfloat16>(st, a);
+}
+
+// Batches of 17 - 64 rows as passes of 16 rows through the streaming kernel.  The tcgen05 pipeline
+// gives every CTA one item of 256 weight rows; a projection with few such items (O / down / QKV of
+// a 70B-class block, any tensor-parallel shard) leaves most SMs idle there (N = 8192: 32 of 148),
+// while the streaming kernel spreads any N over all SMs.  Re-reading the weights once per pass is
+// cheaper than that as long as the passes are few.  QX_STREAM_PASSES=0 never, =2 whenever possible.
+bool stream_passes_ok(const GemvArgs& a) {
+  const char* e = getenv("QX_STREAM_PASSES");      // read per call: tests switch it
+  const int mode = e ? atoi(e) : 1;
+  // q6_K has no tcgen05 pipeline form (its batch > 16 kernel reads weights per thread and is
+  // 5 - 10 x slower than two streaming passes at 32 rows), so it takes passes up to 256 rows.
+  if (mode == 0 || a.M <= 16 || a.M > (a.format == F_Q6_K ? 256 : 64)) return false;
+  GemvArgs b = a;
+  b.M = 16;
+  if (!stream_path_ok(b)) return false;
+  if (mode == 2 || a.format == F_Q6_K) return true;
+  // Measured (nvfp4, K = 8192, 32 rows): N = 8192 (32 items) 101 -> 59 us, N = 10240 101 -> 64 us,
+  // K = 28672 -> N = 8192 326 -> 158 us, but N = 28672 (112 items) 103 -> 137 us; at 64 rows and
+  // 32 items the two paths are level.
+  const long long items = (a.N + 255) / 256;          // work items of the tcgen05 pipeline
+  const int passes = (int)((a.M + 15) / 16);
+  return (passes <= 2 && items <= 96) || items <= 48;
+}
+
+bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a) {
+  const size_t out_size = a.out_f32 ? 4 : 2;
+  for (int64_t m0 = 0; m0 < a.M; m0 += 16) {
+    GemvArgs b = a;
+    b.M = a.M - m0 < 16 ? a.M - m0 : 16;
+    b.x = (const char*)a.x + (size_t)m0 * a.K * 2;
+    b.y = (char*)a.y + (size_t)m0 * a.N * out_size;
+    if (a.residual) b.residual = (const char*)a.residual + (size_t)m0 * a.N * 2;
+    if (!launch_gemv_stream(st, b)) return false;
+  }
+  return true;
 }
 
 }  // namespace qx

@@ -25,6 +25,9 @@ void launch_gemv_generic(cudaStream_t st, const GemvArgs& a);
 // Streaming tensor-core path (bf16 activations, batch <= 16, 16-byte aligned bases).
 bool stream_path_ok(const GemvArgs& a);
 bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a);
+// The same kernel in passes of 16 rows for batches of 17 - 64 rows, when that beats the tcgen05 path.
+bool stream_passes_ok(const GemvArgs& a);
+bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a);
 // tcgen05 path (bf16 activations, batch > 16, K % 256 == 0, single weight matrix).
 bool tc_path_ok(const GemvArgs& a);
 bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a);

@@ -212,11 +212,22 @@ def test_error_behaviour_matches_reference_messages():
     assert y.shape == (2, 3) and float(y.abs().max()) == 0.0
 
 
+@pytest.fixture(params=["tcgen05", "passes"])
+def large_batch_path(request, monkeypatch):
+    """Batches of 17 - 64 rows have two device paths: the tcgen05 kernels, and the streaming kernel
+    run in passes of 16 rows (chosen by default when the projection has few 256-row items).  The
+    library reads QX_STREAM_PASSES on every call: 0 = never, 2 = whenever the shape allows."""
+    monkeypatch.setenv("QX_STREAM_PASSES", "0" if request.param == "tcgen05" else "2")
+    return request.param
+
+
 @pytest.mark.parametrize("M", [17, 32, 64, 100, 128, 129, 256])
 @pytest.mark.parametrize("fmt", FMTS)
-def test_epilogue_large_batch(fmt, M):
+def test_epilogue_large_batch(fmt, M, large_batch_path):
     """Batch > 16 (the tcgen05 path for bf16): several 128-row weight tiles incl. a ragged last one,
     batches that need a second pass (M > 128), every epilogue piece."""
+    if large_batch_path == "passes" and M > 64 and fmt != "q6_K":
+        pytest.skip("passes serve at most 64 rows (256 for q6_K)")
     K, N = 1024, 300
     x, Wq, bias, res = _inputs(fmt, M, K, N, "bf16", 90 + M)
     got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), dev(res, "bf16"),
@@ -226,7 +237,7 @@ def test_epilogue_large_batch(fmt, M):
 
 
 @pytest.mark.parametrize("fmt", ["q8_0", "q4_0", "mxfp8", "nvfp4", "mxfp4"])
-def test_large_batch_f16(fmt):
+def test_large_batch_f16(fmt, large_batch_path):
     """f16 activations at batch > 16: linear with every epilogue piece, and SwiGLU."""
     M, K, N = 40, 512, 384
     x, Wq, bias, res = _inputs(fmt, M, K, N, "f16", 70)
@@ -239,7 +250,7 @@ def test_large_batch_f16(fmt):
 
 
 @pytest.mark.parametrize("fmt", ["nvfp4", "q8_0"])
-def test_epilogue_large_batch_every_code_value(fmt):
+def test_epilogue_large_batch_every_code_value(fmt, large_batch_path):
     x, Wq, bias, res = _inputs(fmt, 48, 512, 256, "bf16", 17, random_bytes=True)
     got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), None, None, format=fmt)
     ref = O.decode_linear_epilogue(x, Wq, fmt, None, None, 0, "bf16")
@@ -248,7 +259,9 @@ def test_epilogue_large_batch_every_code_value(fmt):
 
 @pytest.mark.parametrize("M", [24, 130])
 @pytest.mark.parametrize("fmt", ["nvfp4", "q6_K", "q8_0"])
-def test_swiglu_large_batch(fmt, M):
+def test_swiglu_large_batch(fmt, M, large_batch_path):
+    if large_batch_path == "passes" and M > 64 and fmt != "q6_K":
+        pytest.skip("passes serve at most 64 rows (256 for q6_K)")
     rng = np.random.default_rng(7 + M)
     K, N = 1024, 200
     x = rounded(rng.standard_normal((M, K)), "bf16")
@@ -262,7 +275,7 @@ def test_swiglu_large_batch(fmt, M):
 
 @pytest.mark.parametrize("M", [1, 8, 32])
 @pytest.mark.parametrize("fmt", ["nvfp4", "q4_0"])
-def test_row_parallel_partials_sum_to_full_projection(fmt, M):
+def test_row_parallel_partials_sum_to_full_projection(fmt, M, large_batch_path):
     """K split over 4 'ranks' at block boundaries: fp32 partials summed = the unsplit projection."""
     from quixicore_metal_b200 import tk_torch
     rng = np.random.default_rng(3 + M)
@@ -281,7 +294,7 @@ def test_row_parallel_partials_sum_to_full_projection(fmt, M):
     np.testing.assert_allclose(host(total), ref, rtol=2e-5, atol=2e-5)
 
 
-def test_large_batch_weight_ending_at_an_allocation_boundary():
+def test_large_batch_weight_ending_at_an_allocation_boundary(large_batch_path):
     """A packed tensor of exactly 9 x 2 MiB fills its allocator segment to the last byte: no load
     of the batch > 16 path may touch anything beyond the tensor."""
     fmt, M, K, N = "nvfp4", 32, 8192, 4096

