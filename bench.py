@@ -187,6 +187,42 @@ def workload_config(n_gpus: int):
 
 
 # ---------------------------------------------------------------------------------------------
+BLOCK_K = {"q4_0": 32, "q8_0": 32, "q6_K": 256, "mxfp8": 32, "nvfp4": 16, "mxfp4": 32}
+BLOCK_BYTES = {"q4_0": 18, "q8_0": 34, "q6_K": 210, "mxfp8": 33, "nvfp4": 9, "mxfp4": 17}
+
+
+def gemv_case(spec: str, device, peak_gbs: float, iters: int = 30):
+    """One projection workload, eager calls only: `fmt,M,K,N[,swiglu]`.  This is the command the
+    kernel captures under profiles/ run (`python bench.py --gemv-case nvfp4,1,8192,28672`)."""
+    from quixicore_metal_b200 import tk
+    parts = spec.split(",")
+    fmt, M, K, N = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
+    dual = len(parts) > 4 and parts[4] in ("1", "swiglu")
+    nw = 2 if dual else 1
+    one = N * (K // BLOCK_K[fmt]) * BLOCK_BYTES[fmt]
+    copies = max(2, -(-2 * L2_BYTES // (one * nw)))
+    ws = [[synth_random_blocks(fmt, N, K, 40 + 2 * c + i, device) for i in range(nw)] for c in range(copies)]
+    x = torch.randn((M, K), device=device).bfloat16()
+
+    def step(i):
+        w = ws[i % copies]
+        if dual:
+            return tk.decode_swiglu(x, w[0], w[1], format=fmt)
+        return tk.decode_linear_epilogue(x, w[0], None, None, format=fmt)
+    for i in range(5):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        step(i)
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    gbs = one * nw / (ms * 1e-3) / 1e9
+    return {"case": spec, "ms_eager": round(ms, 5), "packed_bytes": one * nw, "gbs": round(gbs, 1),
+            "frac_of_measured_peak": round(gbs / peak_gbs, 4), "l2": f"{copies} weight copies rotated (> 2x L2)"}
+
+
 def gemv_sweep(device, peak_gbs: float):
     """Packed GEMV bandwidth of the batch-1..8 projection configurations (algorithmic bytes / time)."""
     from quixicore_metal_b200 import tk
@@ -196,7 +232,8 @@ def gemv_sweep(device, peak_gbs: float):
              ("decode_swiglu+down", "q6_K", 8, 4096, 14336),
              ("decode_linear_epilogue", "nvfp4", 1, 8192, 28672),
              ("decode_linear_epilogue", "mxfp4", 1, 8192, 28672),
-             ("decode_linear_epilogue", "nvfp4", 8, 8192, 28672)]
+             ("decode_linear_epilogue", "nvfp4", 8, 8192, 28672),
+             ("decode_linear_epilogue", "q8_0", 1, 8192, 28672)]
     for op, fmt, M, K, N in cases:
         x = torch.randn((M, K), device=device).bfloat16()
         if op == "decode_swiglu+down":
@@ -217,7 +254,7 @@ def gemv_sweep(device, peak_gbs: float):
                 return tk.decode_linear_epilogue(mid, d, None, res_in, format=fmt)
             alg = wbytes + M * (2 * K + 2 * 2 * N + 2 * K + 2 * K)
         else:
-            one = N * (K // {"q4_0": 32, "nvfp4": 16, "mxfp4": 32}[fmt]) * {"q4_0": 18, "nvfp4": 9, "mxfp4": 17}[fmt]
+            one = N * (K // BLOCK_K[fmt]) * BLOCK_BYTES[fmt]
             copies = max(2, -(-2 * L2_BYTES // one))
             ws = [synth_random_blocks(fmt, N, K, 40 + c, device) for c in range(min(copies, 32))]
             copies = len(ws)
@@ -354,6 +391,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the secondary GEMV sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-stack", action="store_true", help="skip the 70B-shaped projection stack")
+    ap.add_argument("--gemv-case", default=None, metavar="FMT,M,K,N[,swiglu]",
+                    help="time one projection workload (eager calls) and print its line instead of the bench")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -373,6 +412,10 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
     peak_gbs, peak_kind = measured_peaks()
+    if args.gemv_case:
+        assert world == 1, "--gemv-case is a single-GPU run"
+        emit_json_line(gemv_case(args.gemv_case, device, peak_gbs))
+        return
 
     # ---- inputs: this rank's vocabulary shard, enough rotating copies to defeat L2 ----
     begin, end = parallel.vocab_shard_bounds(V_FULL, world)[rank]
@@ -441,6 +484,21 @@ def main():
     alg_bytes = shard_bytes + T_ROWS * K_HID * 2 + buf.numel() * 4
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
 
+    # ---- the other batch sizes and sampling modes of the same configuration (whole call, eager) ----
+    lm_sweep = []
+    if not args.no_sweep:
+        for T in (1, 8, 64):
+            hT = h_dev[:T].contiguous()
+            for mode, kw in (("argmax", {}), ("topk", {"k": 50, "temperature": TEMP}),
+                             ("topp", {"k": TOPK, "temperature": TEMP, "top_p": TOP_P})):
+                fn = lambda i: heads[i % copies].sample(hT, mode, seed=SEED + i, **kw)
+                for i in range(3):
+                    fn(i)
+                ms = timed(fn, 20) / 20
+                lm_sweep.append({"T": T, "mode": mode, "ms": round(ms, 5), "tokens_per_s": round(T / (ms * 1e-3), 1),
+                                 "gbs_per_gpu": round(shard_bytes / (ms * 1e-3) / 1e9, 1),
+                                 "frac_of_measured_peak": round(shard_bytes / (ms * 1e-3) / 1e9 / peak_gbs, 4)})
+
     del shards, heads
     torch.cuda.empty_cache()
     stack = None if args.no_stack else stack_sweep(device, world, rank, peak_gbs)
@@ -473,6 +531,8 @@ def main():
                      "kernel_ms": k_ms, "algorithmic_bytes": int(alg_bytes)},
         "clocks": clocks,
     }
+    if lm_sweep:
+        line["lm_head"] = lm_sweep
     if stack is not None:
         line["stack"] = stack
     if world == 1 and not args.no_sweep:
