@@ -282,7 +282,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
         const int n = row0 + g + (e >> 1) * 8;
         const int m = nt * 8 + 2 * t + (e & 1);
         if (n < N && m < M) {
-          const float rs = rowscale[m];
+          const float rs = rowscale[m] * GroupProc<FMT>::ACC_SCALE;
           float v = acc[0][nt][e] * rs;
           const size_t o = (size_t)m * N + n;
           if constexpr (DUAL) {

@@ -371,7 +371,7 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
             for (int e = 0; e < 4; ++e) {
               const int ml = h * 8 + 2 * t + (e & 1);
               const int m = nt * 8 + 2 * t + (e & 1);
-              const float rs = m < T_pass ? rowscale[t_base + m] : 0.f;
+              const float rs = m < T_pass ? rowscale[t_base + m] * GP::ACC_SCALE : 0.f;
               logit[ml * LMH_LOGIT_PITCH + warp * WROWS + set * 16 + g + (e >> 1) * 8] = acc[set][nt][e] * rs;
             }
         }

@@ -417,6 +417,7 @@ template <int FMT> struct GroupProc {
   using F = StreamFmt<FMT>;
   static constexpr int UNITS = F::GROUP / 32;
   static constexpr bool PIPED = true;       // has the unit-pipelined form for large batches
+  static constexpr float ACC_SCALE = 1.f;   // run() accumulates dot products / ACC_SCALE
   template <int NT> struct BFrag { uint4 v[UNITS][NT]; };
   template <int NT>
   __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int t,
@@ -481,16 +482,30 @@ template <int FMT> struct GroupProc {
 // nvfp4: a group is four 16-column blocks; thread t owns block t of the group outright (9 bytes),
 // folds the e4m3 scale into the f16 weights (exact: 4 x 2 significant bits) and feeds its block's
 // byte pair (2m, 2m+1) to MMA m; the MMAs accumulate straight into acc.
+// block<false>: the scale comes from the hardware converter (codes 0x7F / 0xFF, which it reads as
+// NaN and this contract as +-480, are patched).  block<true>: the scale byte's exponent and mantissa
+// bits are moved under the f16 exponent instead, which is the f16 pattern of scale * 2^-8 for every
+// code (subnormals and 0x7F included) in two logic operations and needs no patch; weight x scale
+// stays exact (a multiple of 2^-18 with at most 6 significant bits, f16 subnormals kept), and the
+// caller multiplies its accumulators by ACC_SCALE = 2^8 once per output.
 template <> struct GroupProc<F_NVFP4> {
   using F = StreamFmt<F_NVFP4>;
   static constexpr bool PIPED = false;
+  static constexpr float ACC_SCALE = 256.f;
+  template <bool PRESCALED = false>
   __device__ __forceinline__ static void block(uint32_t s, int t, uint32_t (&a)[4][2]) {
     const uint32_t p = s + (uint32_t)(9 * t & ~3);
     const uint32_t sh = 8u * (uint32_t)t;                 // (9t mod 4) bytes
     const uint32_t w0 = lds32(p), w1 = lds32(p + 4), w2 = lds32(p + 8);
     const uint32_t x0 = __funnelshift_r(w0, w1, sh), x1 = __funnelshift_r(w1, w2, sh), x2 = w2 >> sh;
-    uint32_t s2 = cvt_e4m3x2<0>(__byte_perm(x0, 0u, 0x0000));
-    if ((x0 & 0x7Fu) == 0x7Fu) s2 = (x0 & 0x80u) ? 0xDF80DF80u : 0x5F805F80u;   // +-480, not NaN
+    uint32_t s2;
+    if constexpr (PRESCALED) {
+      const uint32_t v = __byte_perm(x0, 0u, 0x0404);     // the scale byte at [15:8] and [31:24]
+      s2 = ((v >> 1) & 0x3F803F80u) | (v & 0x80008000u);
+    } else {
+      s2 = cvt_e4m3x2<0>(__byte_perm(x0, 0u, 0x0000));
+      if ((x0 & 0x7Fu) == 0x7Fu) s2 = (x0 & 0x80u) ? 0xDF80DF80u : 0x5F805F80u;   // +-480, not NaN
+    }
     a[0][0] = h2mul(cvt_e2m1x2<1>(x0), s2); a[0][1] = h2mul(cvt_e2m1x2<2>(x0), s2);
     a[1][0] = h2mul(cvt_e2m1x2<3>(x0), s2); a[1][1] = h2mul(cvt_e2m1x2<0>(x1), s2);
     a[2][0] = h2mul(cvt_e2m1x2<1>(x1), s2); a[2][1] = h2mul(cvt_e2m1x2<2>(x1), s2);
@@ -512,7 +527,7 @@ template <> struct GroupProc<F_NVFP4> {
                                              int col, float (&acc)[NSETS][NT][4]) {
     uint32_t a[2 * NSETS][4][2];
 #pragma unroll
-    for (int r = 0; r < 2 * NSETS; ++r) block(s[r], t, a[r]);
+    for (int r = 0; r < 2 * NSETS; ++r) block<true>(s[r], t, a[r]);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       uint4 b0, b1;
@@ -536,6 +551,7 @@ template <> struct GroupProc<F_NVFP4> {
 template <> struct GroupProc<F_Q6_K> {
   using F = StreamFmt<F_Q6_K>;
   static constexpr bool PIPED = false;
+  static constexpr float ACC_SCALE = 1.f;
   template <int ODD>
   __device__ __forceinline__ static uint32_t ldw(uint32_t p) {    // p is 4-aligned iff !ODD
     if constexpr (ODD) return __funnelshift_r(lds32(p - 2), lds32(p + 2), 16);
