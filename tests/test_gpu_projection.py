@@ -83,6 +83,23 @@ def test_epilogue_batch_sweep_bf16(fmt, M):
     assert_close_dtype(host(got), ref, "bf16")
 
 
+@pytest.mark.parametrize("M", [1, 6, 16])
+@pytest.mark.parametrize("K,N", [(768, 16), (768, 2400), (1280, 2373), (2048, 4750)])
+@pytest.mark.parametrize("fmt", ["nvfp4", "q8_0", "mxfp4", "q6_K"])
+def test_streaming_work_split_shapes(fmt, K, N, M):
+    """Shapes that stress the streaming kernel's work split: a single 16-row tile, 150 tiles on 148
+    CTAs (shares of one and two tiles, every tile cut between warps), a ragged last tile, a K whose
+    last stage is partial (the loop that is not unrolled), for one matrix and for a SwiGLU pair."""
+    if fmt == "q6_K" and K != 2048:
+        pytest.skip("q6_K rows are 16-byte aligned only for K % 2048 == 0")
+    x, Wq, bias, res = _inputs(fmt, M, K, N, "bf16", 5 + M + N)
+    got = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), dev(res, "bf16"), format=fmt)
+    assert_close_dtype(host(got), O.decode_linear_epilogue(x, Wq, fmt, bias, res, 0, "bf16"), "bf16")
+    _, Uq, ub, _ = _inputs(fmt, M, K, N, "bf16", 6 + M + N)
+    got = tk.decode_swiglu(dev(x, "bf16"), dev(Wq), dev(Uq), dev(bias, "bf16"), dev(ub, "bf16"), format=fmt)
+    assert_close_dtype(host(got), O.decode_swiglu(x, Wq, Uq, fmt, bias, ub, "bf16"), "bf16")
+
+
 @pytest.mark.parametrize("fmt,K", [("q4_0", 32), ("q4_0", 96), ("q8_0", 160), ("q6_K", 256),
                                    ("mxfp8", 32), ("nvfp4", 16), ("nvfp4", 48), ("nvfp4", 272),
                                    ("mxfp4", 224)])
