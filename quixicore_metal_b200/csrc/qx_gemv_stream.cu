@@ -185,8 +185,8 @@ void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free) {
 constexpr int STREAM_STAGES = 2;      // per-warp ring depth; latency is hidden by the number of warps
 
 // HALF = stages of half the format's column count.  Measured at K = 8192, N = 28672 on one GPU:
-//  * single matrix, 1 - 2 rows: full-width stages; 20 warps (102 registers each) beat 16 by 3 - 10 %
-//    (q8_0 56.7 -> 51.5 us); mxfp4 needs 103 registers and is left at 16 warps;
+//  * single matrix, 1 - 2 rows: full-width stages; 20 warps (102 registers each) beat 16 by 2 - 10 %
+//    (q8_0 56.7 -> 51.5 us; mxfp4, 8 bytes of spill at that limit, 37.1 -> 36.2 us);
 //  * more rows, or a SwiGLU pair: half-width stages.  The prepared activations (2*K bytes per row)
 //    are re-read from L1 by every warp; the smaller rings leave the L1 side of the SM's memory large
 //    enough to hold them (nvfp4, 8 rows: 60.6 -> 51.9 us), and a SwiGLU stage of 32 rows fits 16
@@ -199,7 +199,7 @@ struct StreamCfg {
   using WS = WarpStream<FMT, KC, ROWS, STREAM_STAGES>;
   // shared memory per warp: ring, mbarriers, one partial-sum slot (NACC x 32 f32)
   static constexpr int warp_smem(int nt) { return WS::WARP_BYTES + STREAM_STAGES * 8 + 32 * nt * 4 * (DUAL ? 2 : 1) * 4; }
-  static constexpr int warp_cap(int nt) { return (!DUAL && !HALF && nt == 1 && FMT != F_MXFP4) ? 20 : 16; }
+  static constexpr int warp_cap(int nt) { return (!DUAL && !HALF && nt == 1) ? 20 : 16; }
   // warps per CTA: as many as 220 KB of shared memory hold, at most warp_cap
   static constexpr int max_warps(int nt) {
     return 220 * 1024 / warp_smem(nt) < warp_cap(nt) ? 220 * 1024 / warp_smem(nt) : warp_cap(nt);
