@@ -233,7 +233,14 @@ def gemv_sweep(device, peak_gbs: float):
              ("decode_linear_epilogue", "nvfp4", 1, 8192, 28672),
              ("decode_linear_epilogue", "mxfp4", 1, 8192, 28672),
              ("decode_linear_epilogue", "nvfp4", 8, 8192, 28672),
-             ("decode_linear_epilogue", "q8_0", 1, 8192, 28672)]
+             ("decode_linear_epilogue", "q8_0", 1, 8192, 28672),
+             # the rest of the NVFP4 / MXFP4 batch sweep (16 rows: streaming kernel; 64 and 256: tcgen05 pipeline)
+             ("decode_linear_epilogue", "nvfp4", 16, 8192, 28672),
+             ("decode_linear_epilogue", "nvfp4", 64, 8192, 28672),
+             ("decode_linear_epilogue", "nvfp4", 256, 8192, 28672),
+             ("decode_linear_epilogue", "mxfp4", 16, 8192, 28672),
+             ("decode_linear_epilogue", "mxfp4", 64, 8192, 28672),
+             ("decode_linear_epilogue", "mxfp4", 256, 8192, 28672)]
     for op, fmt, M, K, N in cases:
         x = torch.randn((M, K), device=device).bfloat16()
         if op == "decode_swiglu+down":
