@@ -235,6 +235,11 @@ template <> struct LmhCfg<F_MXFP8> { static constexpr int KC = 128, STAGES = 2; 
 
 // Whole stages run fully unrolled for up to this many 8-row n-tiles (q8_0, V = 128256, argmax:
 // 141 -> 120 us per call at 1 row, 268 -> 211 us at 16 rows).
+// n-tiles from which a CTA is 16 warps of 16 rows instead of 8 warps of 32 rows (q8_0, V = 128256,
+// 16 hidden rows: 212 -> 197 us per argmax call; at 8 rows the 32-row form is 10 % faster).
+#ifndef QX_LMH_WROWS16_MIN_NT
+#define QX_LMH_WROWS16_MIN_NT 2
+#endif
 #ifndef QX_LMH_UNROLL
 #define QX_LMH_UNROLL 2
 #endif
@@ -242,7 +247,7 @@ constexpr int LMH_LOGIT_PITCH = 257;
 constexpr int LMH_TOK_CHUNK = 16;
 
 // WROWS = vocabulary rows per warp: 32 (8 warps, two m-tiles share every activation fragment) or
-// 16 (16 warps: more loads in flight; used for the large hidden-row counts).
+// 16 (16 warps: more loads in flight; used from 9 hidden rows per pass).
 template <int FMT, int NT, int WROWS>
 __global__ void __launch_bounds__(256 / WROWS * 32, 1)
 lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ x16,
@@ -509,7 +514,7 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
                                  const float* rowscale, float* pv, int32_t* pi, float* pl,
                                  int64_t tiles_stride, int* err, const CUtensorMap& wmap) {
   using C = LmhCfg<FMT>;
-  constexpr int WROWS = NT >= 4 ? 16 : 32;
+  constexpr int WROWS = NT >= QX_LMH_WROWS16_MIN_NT ? 16 : 32;
   constexpr int NW = 256 / WROWS;
   using WS = WarpStream<FMT, C::KC, WROWS, C::STAGES>;
   const size_t smem = (size_t)NW * WS::WARP_BYTES + (size_t)NW * C::STAGES * 8 +
