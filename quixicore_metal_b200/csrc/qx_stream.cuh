@@ -1,4 +1,4 @@
-// Streaming small-batch core: packed weight rows -> shared memory by bulk async copies,
+// Streaming small-batch core: packed weight rows -> shared memory by 2-D TMA box copies,
 // in-register dequantisation straight into mma.sync A fragments, fp32 block-scaled accumulation.
 //
 // Why this shape.  For batch <= 16 the projection is bound by the HBM stream of packed weights
@@ -18,8 +18,8 @@
 //     its largest magnitude sits near 2^14 (exact for every element within 2^28 of the row maximum,
 //     i.e. far below the resolution of the fp32 accumulator for the rest), stored in the column
 //     order the decoders produce; the epilogue multiplies the row scale back;
-//   * raw rows are fetched with cp.async.bulk into a per-warp ring of stages (mbarrier completion),
-//     which keeps tens of KB in flight per SM with a handful of instructions.
+//   * raw rows are fetched as 2-D TMA boxes (16 rows per copy) into a per-warp ring of stages
+//     (mbarrier completion), which keeps 70 - 150 KB in flight per SM with a handful of instructions.
 // The k-order inside a scale unit is free (a dot product is order-blind up to rounding), so each
 // thread takes the bytes that are cheapest to unpack and loads the matching activation columns.
 //
