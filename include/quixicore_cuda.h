@@ -13,8 +13,14 @@
  *
  * Each declaration cites the reference interface it stands in for (path:line inside the
  * QuixiCore-Metal project).  The reference has no C binding of its own (bindings/c is empty);
- * the generic call structs mirror its cross-backend contract header
- * include/quixicore/contract/kernel_abi.hpp:10-107 field for field.
+ * the generic call structs have the memory layout of its cross-backend contract header
+ * include/quixicore/contract/kernel_abi.hpp:10-107: the same fields in the same order, and the
+ * enumerations stored in one byte as there (`enum class ... : std::uint8_t`), so that
+ * sizeof / offsetof agree (qx_tensor_view 40 bytes, dtype at 32, memory_space at 33, flags at 36;
+ * qx_attribute 48 bytes; qx_kernel_call 80 bytes; qx_status 24 bytes) and a
+ * quixicore::contract::KernelCall can be handed over by pointer.  The enum TYPES below are what
+ * the typed entry points take as parameters; the structs store the same constants in the
+ * one-byte typedefs qx_status_code_u8 / qx_dtype_u8 / qx_memory_space_u8 / qx_attribute_kind_u8.
  */
 #ifndef QUIXICORE_CUDA_H
 #define QUIXICORE_CUDA_H
@@ -40,8 +46,10 @@ typedef enum qx_status_code {
   QX_RUNTIME_ERROR
 } qx_status_code;
 
+typedef uint8_t qx_status_code_u8; /* a qx_status_code constant in the contract's 1-byte storage */
+
 typedef struct qx_status {
-  qx_status_code code;
+  qx_status_code_u8 code;
   const char* operation;
   const char* detail;
 } qx_status;
@@ -57,6 +65,9 @@ typedef enum qx_memory_space {
   QX_MEMORY_UNKNOWN = 0, QX_MEMORY_HOST, QX_MEMORY_DEVICE, QX_MEMORY_SHARED
 } qx_memory_space;
 
+typedef uint8_t qx_dtype_u8;
+typedef uint8_t qx_memory_space_u8;
+
 enum { QX_TENSOR_NONE = 0, QX_TENSOR_READ_ONLY = 1, QX_TENSOR_CONTIGUOUS = 2, QX_TENSOR_OPTIONAL = 4 };
 
 /* ---- generic call (kernel_abi.hpp:66-107) ---------------------------------------------------- */
@@ -65,8 +76,8 @@ typedef struct qx_tensor_view {
   const int64_t* shape;
   const int64_t* strides; /* in elements; NULL = contiguous row-major */
   size_t rank;
-  qx_dtype dtype;
-  qx_memory_space memory_space;
+  qx_dtype_u8 dtype;
+  qx_memory_space_u8 memory_space;
   uint32_t flags;
 } qx_tensor_view;
 
@@ -74,9 +85,11 @@ typedef enum qx_attribute_kind {
   QX_ATTR_BOOL = 0, QX_ATTR_I64, QX_ATTR_F64, QX_ATTR_STRING, QX_ATTR_BYTES
 } qx_attribute_kind;
 
+typedef uint8_t qx_attribute_kind_u8;
+
 typedef struct qx_attribute {
   const char* name;
-  qx_attribute_kind kind;
+  qx_attribute_kind_u8 kind;
   const void* data; /* string / bytes payload */
   size_t size;
   int64_t i64;      /* bool / i64 payload */
@@ -110,16 +123,47 @@ typedef struct qx_kernel_call {
  */
 qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call);
 
-/* Scratch bytes `call->workspace` must provide for op_name with these shapes (0 for ops without
+/* Scratch bytes `call->workspace` should provide for op_name with these shapes (0 for ops without
  * scratch).  Counterpart of the partial buffers the reference host code allocates itself
- * (bindings/pytorch_mps/tk_torch/torch_kernels.mm:5071-5073, :5093-5094). */
+ * (bindings/pytorch_mps/tk_torch/torch_kernels.mm:5071-5073, :5093-5094).  The LM head requires
+ * that workspace; the projection ops fall back to the library's own scratch (see "Workspace"
+ * below) when call->workspace is NULL. */
 size_t qx_cuda_workspace_bytes(const char* op_name, const qx_kernel_call* call);
 
 /* ---- typed entry points ----------------------------------------------------------------------
  * dtype: QX_DTYPE_F32 / QX_DTYPE_F16 / QX_DTYPE_BF16 = element type of x, bias, residual, y.
  * format: "q4_0" "q8_0" "q6_K" "mxfp8" "nvfp4" "mxfp4"; weight = uint8 (N, K/block_k, block_bytes)
  * contiguous, K % block_k == 0.  activation: 0 none, 1 erf-GELU (Abramowitz-Stegun), 2 SiLU.
+ *
+ * Output quantisation (`output_quant` of tk.decode_linear_epilogue / decode_swiglu,
+ * bindings/python/tk/__init__.py:3684-3691): out_quant selects what is written besides y, on the
+ * values of y as rounded to dtype:
+ *   QX_OUT_QUANT_NONE   nothing
+ *   QX_OUT_QUANT_FP8    out_codes uint8 (M,N) e4m3, out_scale f32 (M,) = amax/448   (quant_rt.metal:21-53)
+ *   QX_OUT_QUANT_INT8   out_codes int8 (M,N),       out_scale f32 (M,) = amax/127   (quant_rt.metal:55-87)
+ *   QX_OUT_QUANT_MXFP8  out_codes uint8 (M, N/32, 33) packed MXFP8 rows, N % 32 == 0; out_scale unused.
+ *                       An extension: the reference router only knows the first two.  For bf16 /
+ *                       f16 calls that take the streaming or tcgen05 kernels the blocks are packed
+ *                       by the projection kernel itself; every other case is a second launch inside
+ *                       the call.
+ *
+ * Workspace.  The bf16 / f16 kernels keep a row-scaled f16 copy of the activations in device
+ * scratch.  Pass `workspace` (256-byte aligned, at least qx_cuda_projection_workspace_bytes) and the
+ * call allocates nothing, frees nothing and never synchronises: it may then be captured in a CUDA
+ * graph and replayed on any stream.  With workspace == NULL the library uses a buffer of its own per
+ * (device, stream): the first call on a stream, and a call that needs more than any before it,
+ * run cudaMalloc (which synchronises the device and is not allowed while another thread captures
+ * in global mode); smaller buffers are kept until exit, nothing is freed or waited for.  Calls on
+ * cudaStreamPerThread, on a stream that is being captured, or on more than 16 distinct streams
+ * use cudaMallocAsync / cudaFreeAsync per call instead.  Too small a non-NULL workspace fails with
+ * QX_INSUFFICIENT_WORKSPACE.
  */
+enum { QX_OUT_QUANT_NONE = 0, QX_OUT_QUANT_FP8 = 1, QX_OUT_QUANT_INT8 = 2, QX_OUT_QUANT_MXFP8 = 3 };
+
+/* Upper bound of the scratch one projection call uses (swiglu != 0: the gate/up pair); 0 when the
+ * shape takes a kernel without scratch (fp32 activations). */
+size_t qx_cuda_projection_workspace_bytes(int64_t M, int64_t K, int64_t N, const char* format,
+                                          qx_dtype dtype, int swiglu);
 
 /* y[m,n] = T( act( dot(x[m,:], deq(W[n,:])) + bias[n] ) + residual[m,n] ), fp32 math, one rounding.
  * Replaces decode_linear_epilogue_mps (torch_kernels.mm:6407-6435) and
@@ -129,7 +173,8 @@ qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void
                                          const void* bias, const void* residual, void* y,
                                          int64_t M, int64_t K, int64_t N, const char* format,
                                          qx_dtype dtype, int activation, int use_bias,
-                                         int use_residual);
+                                         int use_residual, int out_quant, void* out_codes,
+                                         float* out_scale, void* workspace, size_t workspace_bytes);
 
 /* y[m,n] = dot(x[m,:], deq(W[n,:])) as fp32, no epilogue: the per-rank piece of a row-parallel
  * (K-split) projection, to be summed over ranks before bias / activation / residual are applied
@@ -137,14 +182,15 @@ qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void
  * aligned bases and K a multiple of 512; otherwise QX_UNSUPPORTED_LAYOUT. */
 qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void* weight, float* y,
                                         int64_t M, int64_t K, int64_t N, const char* format,
-                                        qx_dtype dtype);
+                                        qx_dtype dtype, void* workspace, size_t workspace_bytes);
 
 /* y[m,n] = T( silu(gate.x + gb) * (up.x + ub) ).  Replaces decode_swiglu_mps
  * (torch_kernels.mm:6437-6466) and tk::launch_decode_swiglu (tk_launch.h:458-470). */
 qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_weight,
                                 const void* up_weight, const void* gate_bias, const void* up_bias,
                                 void* y, int64_t M, int64_t K, int64_t N, const char* format,
-                                qx_dtype dtype, int use_bias);
+                                qx_dtype dtype, int use_bias, int out_quant, void* out_codes,
+                                float* out_scale, void* workspace, size_t workspace_bytes);
 
 /* Per-row dynamic quantisation of x (rows, D): scale[row] = amax/448 (fp8, e4m3 codes, halves
  * round away from zero, saturating at 448) or amax/127 (int8).  Replaces
@@ -166,8 +212,10 @@ qx_status qx_cuda_quantize_mxfp8_rows(void* stream, const void* x, void* blocks,
  * keyed by (seed, row, global vocab id) (include/metal/common/rng.metal:18-30).
  */
 
-/* Scratch bytes for qx_cuda_lm_head_sample_q. */
-size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int mode, int topk);
+/* Scratch bytes for qx_cuda_lm_head_sample_q: the per-tile partials of stage 1, the prepared
+ * hidden rows and the exchange slots of vocabulary tiles that several thread blocks share.  The
+ * workspace must be 256-byte aligned.  With it the call allocates nothing and never synchronises. */
+size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int64_t K, int mode, int topk);
 
 /* ids[t] = sampled token for row t of h (T,K); logits are never written to memory.  Replaces
  * lm_head_sample_q_mps (torch_kernels.mm:5019-5101) = partial + reduce launches
@@ -182,21 +230,42 @@ qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, 
  * same operation as qx_cuda_lm_head_sample_q for callers that cannot allocate device memory at
  * call time - code running inside a latency-critical serving loop that has handed all of its
  * memory to a pool, a plugin host that forbids cudaMalloc after start-up, or a region that is
- * being stream-ordered without an allocator.  The stage-1 partials go to a fixed array of
- * QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES bytes that is part of the library image (every GPU that
- * loads the library keeps that much memory until the process exits).  Calls whose partials need
- * more (see qx_cuda_lm_head_workspace_bytes) fail with QX_INSUFFICIENT_WORKSPACE.  Nothing in
- * this call allocates or frees.  The first call on each device looks the array's device address
- * up once; make that first call before starting any stream capture.  All calls on one device
- * share the array: two calls that overlap on the GPU (different streams) race on it, so keep
- * them on one stream or order them with events.  Stage 1 overwrites every slot that stage 2
- * reads, so no clearing is needed between calls. */
+ * being stream-ordered without an allocator.  All global scratch of the two stages (per-tile
+ * partials, the prepared hidden rows and their row scales, the flags and exchange slots of shared
+ * tiles) is carved out of a fixed array of QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES bytes that is part
+ * of the library image (every GPU that loads the library keeps that much memory until the process
+ * exits).  A call needs  2 * align256(4 * T * tiles * kk)  [+ align256(4 * T * tiles) for top-p]
+ * + 1024 + align256(2 * roundup(T, 64) * K) + align256(4 * T)  bytes of it, tiles = ceil(V / 256),
+ * kk = topk for modes 2 / 3 and 1 otherwise; a call that needs more fails with
+ * QX_INSUFFICIENT_WORKSPACE.  Nothing in this call allocates or frees, for any dtype of h.  The
+ * first call on each device looks the array's device address up once; make that first call before
+ * starting any stream capture.  All calls on one device share the array: two calls that overlap
+ * on the GPU (different streams) race on it, so keep them on one stream or order them with
+ * events.  Stage 1 overwrites every slot that stage 2 reads and the flags are cleared by the call
+ * itself, so nothing has to be cleared between calls. */
 #define QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES (4u << 20)
 qx_status qx_cuda_lm_head_sample_q_noalloc(void* stream, const void* h, const void* wq,
                                            const float* bias, int32_t* ids, int64_t T, int64_t V,
                                            int64_t K, const char* format, qx_dtype dtype, int mode,
                                            int topk, double temperature, uint32_t seed,
                                            double top_p);
+
+/* The same over a dense head W (V,K) in the dtype of h, modes 0..2; logits are never written.
+ * Replaces lm_head_sample_mps (torch_kernels.mm:4966-5016; kernels lm_head.metal:175-235,
+ * :400-470).  bias fp32 (V,) or NULL. */
+size_t qx_cuda_lm_head_dense_workspace_bytes(int64_t T, int64_t V, int mode, int topk);
+qx_status qx_cuda_lm_head_sample_dense(void* stream, const void* h, const void* W, const float* bias,
+                                       int32_t* ids, void* workspace, size_t workspace_bytes,
+                                       int64_t T, int64_t V, int64_t K, qx_dtype dtype, int mode,
+                                       int topk, double temperature, uint32_t seed);
+
+/* Samplers over materialised logits (rows, V): kind 0 argmax (raw logits), 1 categorical, 2 top-k
+ * (k <= 64), 3 top-p; ids int32 (rows,).  The noise row index is the row of the call.  Replaces
+ * argmax_sample / sample_categorical / top_k_sample / top_p_sample
+ * (kernels/sampling/sampling/sampling.metal:19-103, :159-217; tk_torch/__init__.py:1620-1637). */
+qx_status qx_cuda_sample_logits(void* stream, const void* logits, int32_t* ids, int64_t rows, int64_t V,
+                                qx_dtype dtype, int kind, int topk, double top_p, double temperature,
+                                uint32_t seed);
 
 /* Vocabulary-sharded form.  A shard holds rows [vocab_offset, vocab_offset + V_local) of the full
  * matrix, vocab_offset a multiple of 256 so every 256-row tile of the reference lies in one shard.
@@ -213,7 +282,7 @@ qx_status qx_cuda_lm_head_sample_q_noalloc(void* stream, const void* h, const vo
  * split follows its own two-stage tile -> reduce structure (lm_head.metal:219-235, :444-529).
  */
 int64_t qx_cuda_lm_head_shard_candidates(int mode, int topk, int64_t max_tiles);
-size_t qx_cuda_lm_head_shard_workspace_bytes(int64_t T, int64_t V_local, int mode, int topk);
+size_t qx_cuda_lm_head_shard_workspace_bytes(int64_t T, int64_t V_local, int64_t K, int mode, int topk);
 
 qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const void* wq,
                                            const float* bias_local, float* cand_val,
@@ -239,7 +308,17 @@ uint64_t qx_cuda_launch_count(void);
  * gave up waiting for one of its own asynchronous copies (its results are then invalid).
  * Synchronises the device.  -1 if the flag cannot be read.  No counterpart in the reference. */
 int qx_cuda_device_error(void);
-/* Library version string, e.g. "quixicore-b200 0.1 (sm_100a)". */
+/* Chooses between device paths that compute the same result (identical up to fp32 summation
+ * order); meant for tests and A/B timing.  Names: "stream_passes" (0 never / 1 when faster / 2
+ * whenever possible: 17 - 64 rows as 16-row passes of the streaming kernel instead of the tcgen05
+ * pipeline), "force_generic", "tc_pipeline", "lm_head_ksplit", "lm_head_overlap" (0 / 1).  Returns
+ * 1 if the option exists and took the value.  Process-wide, not synchronised with running calls. */
+int qx_cuda_set_option(const char* name, int value);
+/* Number of device allocations the library has made for scratch of its own (calls that passed
+ * no workspace).  Stays unchanged across calls that bring a workspace and across
+ * qx_cuda_lm_head_sample_q_noalloc. */
+uint64_t qx_cuda_scratch_alloc_count(void);
+/* Library version string, e.g. "quixicore-b200 0.2 (sm_100a)". */
 const char* qx_cuda_version(void);
 
 #ifdef __cplusplus

@@ -165,14 +165,17 @@ def dequantize(fmt: str, packed: np.ndarray) -> np.ndarray:
 # Kernel parity is defined on dequantize(packed), so any valid packed tensor is a fair input.
 # ----------------------------------------------------------------------------------------------
 def _nearest_code(x, values):
-    """Index of the nearest table value; ties go to the lower index (np.argmin order)."""
+    """Index of the nearest table value; ties go to the lower index (the order np.argmin over the
+    distances would give).  Both code tables are sign-symmetric - the first half holds the
+    magnitudes in ascending order, the second half their negatives - so the search runs on the
+    magnitude midpoints: O(n log half) instead of an (n, len(values)) distance matrix."""
     x = np.asarray(x, np.float32)
-    out = np.empty(x.shape, np.uint8)
-    flat, o = x.reshape(-1), out.reshape(-1)
-    for i in range(0, flat.size, 1 << 18):
-        seg = flat[i:i + (1 << 18)]
-        o[i:i + (1 << 18)] = np.abs(seg[:, None] - values[None, :]).argmin(-1)
-    return out
+    half = values.size // 2
+    mags = np.asarray(values[:half], np.float64)
+    mid = 0.5 * (mags[1:] + mags[:-1])
+    m = np.searchsorted(mid, np.abs(x.astype(np.float64)), side="left")      # |x| == midpoint -> smaller magnitude
+    neg = (x < 0) & (m > 0)                                                    # nearest-to-zero negatives take +0
+    return (m + half * neg).astype(np.uint8)
 
 
 _E2M1_TABLE = e2m1_decode(np.arange(16))
@@ -446,10 +449,19 @@ def rng_gumbel(seed, a, b) -> np.ndarray:
 # categorical), :444-470 + :579-616 (top-k), :478-529 + :649-702 (top-p); ordering helpers
 # include/metal/ops/group/topk.metal:34-85 (value descending, id ascending).
 # ----------------------------------------------------------------------------------------------
-def lm_head_logits(h: np.ndarray, packed: np.ndarray, fmt: str) -> np.ndarray:
+def lm_head_logits(h: np.ndarray, packed: np.ndarray, fmt: str, chunk_rows: int = 16384) -> np.ndarray:
     """Raw logits (T, V): float64 accumulation of the fp32-exact dequantised weights, rounded to
-    fp32 (the tests' oracle, test_lm_head.py:132-154)."""
-    return matmul_f64(h, dequantize(fmt, packed))
+    fp32 (the tests' oracle, test_lm_head.py:132-154).  The vocabulary is walked in chunks so that
+    a 128K-row head needs a few hundred MB of host memory, not the whole fp64 matrix."""
+    V = packed.shape[0]
+    if V <= chunk_rows:
+        return matmul_f64(h, dequantize(fmt, packed))
+    h64 = np.asarray(h, np.float64)
+    out = np.empty((h64.shape[0], V), np.float32)
+    for v0 in range(0, V, chunk_rows):
+        W = dequantize(fmt, packed[v0:v0 + chunk_rows]).astype(np.float64)
+        out[:, v0:v0 + chunk_rows] = (h64 @ W.T).astype(np.float32)
+    return out
 
 
 def _argmax_low_id(score: np.ndarray, ids: np.ndarray) -> int:

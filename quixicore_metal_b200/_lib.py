@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libquixicore_cuda.so")
 # qx_dtype values of include/quixicore_cuda.h
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 10, 11, 12
 DTYPE_U8, DTYPE_I32 = 3, 6
+OUT_QUANT = {None: 0, "fp8": 1, "int8": 2, "mxfp8": 3}
 
 STATUS_NAMES = ["ok", "invalid_argument", "invalid_shape", "unsupported_dtype", "unsupported_format",
                 "unsupported_layout", "insufficient_workspace", "adapter_not_wired",
@@ -17,7 +18,8 @@ STATUS_NAMES = ["ok", "invalid_argument", "invalid_shape", "unsupported_dtype", 
 
 
 class Status(C.Structure):
-    _fields_ = [("code", C.c_int), ("operation", C.c_char_p), ("detail", C.c_char_p)]
+    # kernel_abi.hpp:22-26: a one-byte status code, then two pointers (24 bytes)
+    _fields_ = [("code", C.c_uint8), ("operation", C.c_char_p), ("detail", C.c_char_p)]
 
 
 class QxError(RuntimeError):
@@ -45,25 +47,34 @@ def lib() -> C.CDLL:
     vp, i64, i32, u32, f64, sz = C.c_void_p, C.c_int64, C.c_int, C.c_uint32, C.c_double, C.c_size_t
     cs = C.c_char_p
     L.qx_cuda_decode_linear_epilogue.restype = Status
-    L.qx_cuda_decode_linear_epilogue.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, i32]
+    L.qx_cuda_decode_linear_epilogue.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, i32,
+                                                 i32, vp, vp, vp, sz]
     L.qx_cuda_decode_linear_partial.restype = Status
-    L.qx_cuda_decode_linear_partial.argtypes = [vp, vp, vp, vp, i64, i64, i64, cs, i32]
+    L.qx_cuda_decode_linear_partial.argtypes = [vp, vp, vp, vp, i64, i64, i64, cs, i32, vp, sz]
     L.qx_cuda_decode_swiglu.restype = Status
-    L.qx_cuda_decode_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32]
+    L.qx_cuda_decode_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, vp, vp, vp, sz]
+    L.qx_cuda_projection_workspace_bytes.restype = sz
+    L.qx_cuda_projection_workspace_bytes.argtypes = [i64, i64, i64, cs, i32, i32]
     L.qx_cuda_quantize_per_token.restype = Status
     L.qx_cuda_quantize_per_token.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32]
     L.qx_cuda_quantize_mxfp8_rows.restype = Status
     L.qx_cuda_quantize_mxfp8_rows.argtypes = [vp, vp, vp, i64, i64, i32]
     L.qx_cuda_lm_head_workspace_bytes.restype = sz
-    L.qx_cuda_lm_head_workspace_bytes.argtypes = [i64, i64, i32, i32]
+    L.qx_cuda_lm_head_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     L.qx_cuda_lm_head_sample_q.restype = Status
     L.qx_cuda_lm_head_sample_q.argtypes = [vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, cs, i32, i32, i32, f64, u32, f64]
     L.qx_cuda_lm_head_sample_q_noalloc.restype = Status
     L.qx_cuda_lm_head_sample_q_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, cs, i32, i32, i32, f64, u32, f64]
+    L.qx_cuda_lm_head_dense_workspace_bytes.restype = sz
+    L.qx_cuda_lm_head_dense_workspace_bytes.argtypes = [i64, i64, i32, i32]
+    L.qx_cuda_lm_head_sample_dense.restype = Status
+    L.qx_cuda_lm_head_sample_dense.argtypes = [vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, i32, i32, i32, f64, u32]
+    L.qx_cuda_sample_logits.restype = Status
+    L.qx_cuda_sample_logits.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, f64, f64, u32]
     L.qx_cuda_lm_head_shard_candidates.restype = i64
     L.qx_cuda_lm_head_shard_candidates.argtypes = [i32, i32, i64]
     L.qx_cuda_lm_head_shard_workspace_bytes.restype = sz
-    L.qx_cuda_lm_head_shard_workspace_bytes.argtypes = [i64, i64, i32, i32]
+    L.qx_cuda_lm_head_shard_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     L.qx_cuda_lm_head_shard_partials_q.restype = Status
     L.qx_cuda_lm_head_shard_partials_q.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, i64, i64, cs, i32, i32, i32, f64, u32]
     L.qx_cuda_lm_head_shard_reduce.restype = Status
@@ -74,6 +85,10 @@ def lib() -> C.CDLL:
     L.qx_cuda_launch_count.argtypes = []
     L.qx_cuda_device_error.restype = i32
     L.qx_cuda_device_error.argtypes = []
+    L.qx_cuda_set_option.restype = i32
+    L.qx_cuda_set_option.argtypes = [cs, i32]
+    L.qx_cuda_scratch_alloc_count.restype = C.c_uint64
+    L.qx_cuda_scratch_alloc_count.argtypes = []
     L.qx_cuda_version.restype = cs
     L.qx_cuda_version.argtypes = []
     L.qx_cuda_dispatch.restype = Status
@@ -87,6 +102,12 @@ def lib() -> C.CDLL:
 def check(st: Status) -> None:
     if st.code != 0:
         raise QxError(st)
+
+
+def set_option(name: str, value: int) -> None:
+    """Chooses between equivalent device paths (see qx_cuda_set_option in the header)."""
+    if not lib().qx_cuda_set_option(name.encode(), int(value)):
+        raise ValueError(f"unknown option or value: {name}={value}")
 
 
 def launch_count() -> int:

@@ -1,6 +1,8 @@
 """ctypes mirror of the generic call structs of include/quixicore_cuda.h (qx_tensor_view,
 qx_attribute, qx_kernel_call) and a builder that fills them from torch CUDA tensors, for callers
-that want the contract-style `qx_cuda_dispatch(op_name, call)` door instead of the typed entries."""
+that want the contract-style `qx_cuda_dispatch(op_name, call)` door instead of the typed entries.
+The layouts equal include/quixicore/contract/kernel_abi.hpp:66-107 of the reference (one-byte
+enumerations): TensorView 40 bytes, Attribute 48, KernelCall 80."""
 from __future__ import annotations
 
 import ctypes as C
@@ -18,12 +20,12 @@ ATTR_BOOL, ATTR_I64, ATTR_F64, ATTR_STRING, ATTR_BYTES = range(5)
 
 class TensorView(C.Structure):
     _fields_ = [("data", C.c_void_p), ("shape", C.POINTER(C.c_int64)),
-                ("strides", C.POINTER(C.c_int64)), ("rank", C.c_size_t), ("dtype", C.c_int),
-                ("memory_space", C.c_int), ("flags", C.c_uint32)]
+                ("strides", C.POINTER(C.c_int64)), ("rank", C.c_size_t), ("dtype", C.c_uint8),
+                ("memory_space", C.c_uint8), ("flags", C.c_uint32)]
 
 
 class Attribute(C.Structure):
-    _fields_ = [("name", C.c_char_p), ("kind", C.c_int), ("data", C.c_void_p),
+    _fields_ = [("name", C.c_char_p), ("kind", C.c_uint8), ("data", C.c_void_p),
                 ("size", C.c_size_t), ("i64", C.c_int64), ("f64", C.c_double)]
 
 

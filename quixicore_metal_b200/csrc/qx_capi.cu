@@ -11,9 +11,9 @@ namespace qx {
 static std::atomic<uint64_t> g_launches{0};
 void note_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
-qx_status ok(const char* op) { return qx_status{QX_OK, op, ""}; }
+qx_status ok(const char* op) { return qx_status{(qx_status_code_u8)QX_OK, op, ""}; }
 qx_status fail(qx_status_code code, const char* op, const char* detail) {
-  return qx_status{code, op, detail};
+  return qx_status{(qx_status_code_u8)code, op, detail};
 }
 qx_status check_launch(const char* op) {
   const cudaError_t e = cudaGetLastError();
@@ -88,14 +88,67 @@ int qx_cuda_format_info(const char* format, int* block_k, int* block_bytes) {
   return 1;
 }
 uint64_t qx_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
-const char* qx_cuda_version(void) { return "quixicore-b200 0.1 (sm_100a)"; }
+const char* qx_cuda_version(void) { return "quixicore-b200 0.2 (sm_100a)"; }
 int qx_cuda_device_error(void) { return read_device_error_flag(); }
+int qx_cuda_set_option(const char* name, int value) { return set_option(name, value) ? 1 : 0; }
+uint64_t qx_cuda_scratch_alloc_count(void) { return scratch_alloc_count(); }
+
+// Scratch for one projection call: the caller's workspace when it brought one, else the library's
+// per-stream buffer.  `held` releases a per-call allocation when it goes out of scope.
+struct ScratchHold {
+  cudaStream_t st; void* ptr = nullptr; bool must_free = false;
+  ~ScratchHold() { if (must_free && ptr) cudaFreeAsync(ptr, st); }
+};
+static qx_status bind_scratch(const char* op, cudaStream_t st, size_t need, void* workspace,
+                              size_t workspace_bytes, ScratchHold* hold, void** out, size_t* out_bytes) {
+  *out = nullptr; *out_bytes = 0;
+  if (need == 0) return ok(op);
+  if (workspace) {
+    if (workspace_bytes < need || ((uintptr_t)workspace & 255) != 0)
+      return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must be 256-byte aligned and at least as large as the op's workspace-bytes query");
+    *out = workspace; *out_bytes = workspace_bytes;
+    return ok(op);
+  }
+  hold->st = st;
+  hold->ptr = default_scratch(st, need, &hold->must_free);
+  if (!hold->ptr) return fail(QX_RUNTIME_ERROR, op, "device scratch allocation failed");
+  *out = hold->ptr; *out_bytes = need;
+  return ok(op);
+}
+
+static qx_status check_out_quant(const char* op, int out_quant, void* out_codes, float* out_scale, int64_t N) {
+  if (out_quant < 0 || out_quant > 3) return fail(QX_INVALID_ARGUMENT, op, "output_quant must be None, 'fp8', 'int8', or 'mxfp8'");
+  if (out_quant != 0 && !out_codes) return fail(QX_INVALID_ARGUMENT, op, "output_quant needs an out_codes buffer");
+  if ((out_quant == 1 || out_quant == 2) && !out_scale) return fail(QX_INVALID_ARGUMENT, op, "per-token output_quant needs an out_scale buffer");
+  if (out_quant == 3 && N % 32 != 0) return fail(QX_INVALID_SHAPE, op, "mxfp8 output rows need N to be a multiple of 32");
+  return ok(op);
+}
+
+// the output quantisation the projection kernel did not fuse
+static void finish_out_quant(cudaStream_t st, const GemvArgs& a, bool fused) {
+  if (a.out_quant == OQ_NONE || fused) return;
+  if (a.out_quant == OQ_MXFP8) launch_quantize_mxfp8_rows(st, a.y, a.q_codes, a.M, a.N, a.dtype);
+  else launch_quantize_per_token(st, a.y, a.q_codes, a.q_scale, a.M, a.N, a.dtype, a.out_quant == OQ_INT8 ? 1 : 0);
+}
+
+size_t qx_cuda_projection_workspace_bytes(int64_t M, int64_t K, int64_t N, const char* format,
+                                          qx_dtype dtype, int swiglu) {
+  const int f = parse_format(format);
+  if (f < 0 || M <= 0 || K <= 0 || N <= 0 || K % block_k_of(f) != 0 || !float_dtype(dtype)) return 0;
+  void* aligned = (void*)(uintptr_t)256;          // alignment stand-in: only the address bits are inspected
+  GemvArgs a{aligned, aligned, swiglu ? aligned : nullptr, nullptr, nullptr, nullptr, aligned, M, K, N, f, dtype, 0, 0, 0};
+  size_t need = projection_scratch_bytes(a);
+  a.out_f32 = 1;                                  // the fp32-partial form of the same shape
+  const size_t p = swiglu ? 0 : projection_scratch_bytes(a);
+  return need > p ? need : p;
+}
 
 qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void* weight,
                                          const void* bias, const void* residual, void* y,
                                          int64_t M, int64_t K, int64_t N, const char* format,
                                          qx_dtype dtype, int activation, int use_bias,
-                                         int use_residual) {
+                                         int use_residual, int out_quant, void* out_codes,
+                                         float* out_scale, void* workspace, size_t workspace_bytes) {
   static const char* op = "decode_linear_epilogue";
   if (activation < 0 || activation > 2)
     return fail(QX_INVALID_ARGUMENT, op, "activation must be 0, 1, or 2");
@@ -105,16 +158,24 @@ qx_status qx_cuda_decode_linear_epilogue(void* stream, const void* x, const void
   if (use_bias && !bias) return fail(QX_INVALID_ARGUMENT, op, "bias must be (N,) with x dtype");
   if (use_residual && !residual)
     return fail(QX_INVALID_ARGUMENT, op, "residual must be (B,N) with x dtype");
+  st = check_out_quant(op, out_quant, out_codes, out_scale, N);
+  if (st.code != QX_OK) return st;
   if (!device_ready(op, &st)) return st;
   GemvArgs a{x, weight, nullptr, bias, nullptr, residual, y, M, K, N, f, dtype,
              activation, use_bias ? 1 : 0, use_residual ? 1 : 0};
-  launch_projection((cudaStream_t)stream, a);
+  a.out_quant = out_quant; a.q_codes = out_codes; a.q_scale = out_scale;
+  ScratchHold hold;
+  st = bind_scratch(op, (cudaStream_t)stream, projection_scratch_bytes(a), workspace, workspace_bytes, &hold,
+                    &a.scratch, &a.scratch_bytes);
+  if (st.code != QX_OK) return st;
+  const bool fused = launch_projection((cudaStream_t)stream, a);
+  finish_out_quant((cudaStream_t)stream, a, fused);
   return check_launch(op);
 }
 
 qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void* weight, float* y,
                                         int64_t M, int64_t K, int64_t N, const char* format,
-                                        qx_dtype dtype) {
+                                        qx_dtype dtype, void* workspace, size_t workspace_bytes) {
   static const char* op = "decode_linear_epilogue.partial";
   int f = -1;
   qx_status st = check_projection(op, x, weight, y, M, K, N, format, dtype, &f);
@@ -122,6 +183,10 @@ qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void*
   if (!device_ready(op, &st)) return st;
   GemvArgs a{x, weight, nullptr, nullptr, nullptr, nullptr, y, M, K, N, f, dtype, 0, 0, 0};
   a.out_f32 = 1;
+  ScratchHold hold;
+  st = bind_scratch(op, (cudaStream_t)stream, projection_scratch_bytes(a), workspace, workspace_bytes, &hold,
+                    &a.scratch, &a.scratch_bytes);
+  if (st.code != QX_OK) return st;
   if (stream_path_ok(a) && launch_gemv_stream((cudaStream_t)stream, a)) return check_launch(op);
   if (stream_passes_ok(a) && launch_gemv_stream_passes((cudaStream_t)stream, a)) return check_launch(op);
   if (tc_path_ok(a) && launch_gemm_tc((cudaStream_t)stream, a)) return check_launch(op);
@@ -133,7 +198,8 @@ qx_status qx_cuda_decode_linear_partial(void* stream, const void* x, const void*
 qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_weight,
                                 const void* up_weight, const void* gate_bias, const void* up_bias,
                                 void* y, int64_t M, int64_t K, int64_t N, const char* format,
-                                qx_dtype dtype, int use_bias) {
+                                qx_dtype dtype, int use_bias, int out_quant, void* out_codes,
+                                float* out_scale, void* workspace, size_t workspace_bytes) {
   static const char* op = "decode_swiglu";
   int f = -1;
   qx_status st = check_projection(op, x, gate_weight, y, M, K, N, format, dtype, &f);
@@ -142,10 +208,18 @@ qx_status qx_cuda_decode_swiglu(void* stream, const void* x, const void* gate_we
     return fail(QX_INVALID_ARGUMENT, op, "gate and up weights must have identical shapes");
   if (use_bias && (!gate_bias || !up_bias))
     return fail(QX_INVALID_ARGUMENT, op, "both biases must be (N,) with x dtype");
+  st = check_out_quant(op, out_quant, out_codes, out_scale, N);
+  if (st.code != QX_OK) return st;
   if (!device_ready(op, &st)) return st;
   GemvArgs a{x, gate_weight, up_weight, gate_bias, up_bias, nullptr, y, M, K, N, f, dtype,
              0, use_bias ? 1 : 0, 0};
-  launch_projection((cudaStream_t)stream, a);
+  a.out_quant = out_quant; a.q_codes = out_codes; a.q_scale = out_scale;
+  ScratchHold hold;
+  st = bind_scratch(op, (cudaStream_t)stream, projection_scratch_bytes(a), workspace, workspace_bytes, &hold,
+                    &a.scratch, &a.scratch_bytes);
+  if (st.code != QX_OK) return st;
+  const bool fused = launch_projection((cudaStream_t)stream, a);
+  finish_out_quant((cudaStream_t)stream, a, fused);
   return check_launch(op);
 }
 
@@ -202,8 +276,7 @@ static qx_status check_lm_head(const char* op, const void* h, const void* wq, in
 
 static int64_t tiles_of(int64_t V) { return (V + 255) / 256; }
 
-size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int mode, int topk) {
-  if (T <= 0 || V <= 0) return 0;
+static size_t partial_bytes(int64_t T, int64_t V, int mode, int topk) {
   const size_t tiles = (size_t)tiles_of(V);
   const size_t kk = mode >= 2 ? (size_t)(topk > 0 ? topk : 1) : 1;
   size_t n = 2 * align256((size_t)T * tiles * kk * 4);
@@ -211,12 +284,21 @@ size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int mode, int topk)
   return n;
 }
 
-qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, const float* bias,
-                                   int32_t* ids, void* workspace, size_t workspace_bytes, int64_t T,
-                                   int64_t V, int64_t K, const char* format, qx_dtype dtype,
-                                   int mode, int topk, double temperature, uint32_t seed,
-                                   double top_p) {
-  static const char* op = "quantized_lm_head_sample";
+size_t qx_cuda_lm_head_workspace_bytes(int64_t T, int64_t V, int64_t K, int mode, int topk) {
+  if (T <= 0 || V <= 0 || K <= 0) return 0;
+  return partial_bytes(T, V, mode, topk) + lm_head_scratch_full_bytes(T, K);
+}
+
+}  // extern "C"
+
+namespace qx {
+// The body of qx_cuda_lm_head_sample_q on a given scratch region: [partials | stage-1 scratch].
+// min_only: the region only has to hold the partials and the minimum stage-1 scratch (K-split
+// items are then shared only as far as the rest reaches).
+qx_status lm_head_sample_on(const char* op, void* stream, const void* h, const void* wq, const float* bias,
+                            int32_t* ids, void* workspace, size_t workspace_bytes, bool min_only, int64_t T,
+                            int64_t V, int64_t K, const char* format, qx_dtype dtype, int mode, int topk,
+                            double temperature, uint32_t seed, double top_p) {
   int f = -1;
   qx_status st = check_lm_head(op, h, wq, T, V, K, format, dtype, mode, topk, temperature, &f);
   if (st.code != QX_OK) return st;
@@ -224,9 +306,10 @@ qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, 
   if (mode >= 2 && topk > V) return fail(QX_INVALID_ARGUMENT, op, "k must be <= vocab size V");
   if (mode == 3 && !(top_p > 0.0 && top_p <= 1.0))
     return fail(QX_INVALID_ARGUMENT, op, "topp requires top_p in (0, 1]");
-  const size_t need = qx_cuda_lm_head_workspace_bytes(T, V, mode, topk);
-  if (!workspace || workspace_bytes < need)
-    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace smaller than qx_cuda_lm_head_workspace_bytes");
+  const size_t pbytes = partial_bytes(T, V, mode, topk);
+  const size_t need = pbytes + (min_only ? lm_head_scratch_min_bytes(T, K) : lm_head_scratch_full_bytes(T, K));
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must be 256-byte aligned and at least qx_cuda_lm_head_workspace_bytes");
   if (!device_ready(op, &st)) return st;
   const int64_t tiles = tiles_of(V);
   const int kk = mode >= 2 ? topk : 1;
@@ -236,9 +319,78 @@ qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, 
   float* pl = (float*)((char*)workspace + 2 * seg);
   LmHeadArgs a{h, wq, bias, T, V, K, 0, f, dtype, mode, kk, 1.0f / (float)temperature, seed,
                (float)top_p};
+  a.scratch = (char*)workspace + pbytes;
+  a.scratch_bytes = workspace_bytes - pbytes;
   launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, pl, tiles);
   launch_lm_head_reduce((cudaStream_t)stream, pv, pi, pl, 1, T, tiles * kk, tiles, 0, mode, kk,
                         a.invtemp, seed, a.top_p, ids, 0, nullptr, nullptr);
+  return check_launch(op);
+}
+}  // namespace qx
+
+extern "C" {
+
+qx_status qx_cuda_lm_head_sample_q(void* stream, const void* h, const void* wq, const float* bias,
+                                   int32_t* ids, void* workspace, size_t workspace_bytes, int64_t T,
+                                   int64_t V, int64_t K, const char* format, qx_dtype dtype,
+                                   int mode, int topk, double temperature, uint32_t seed,
+                                   double top_p) {
+  return lm_head_sample_on("quantized_lm_head_sample", stream, h, wq, bias, ids, workspace, workspace_bytes,
+                           false, T, V, K, format, dtype, mode, topk, temperature, seed, top_p);
+}
+
+size_t qx_cuda_lm_head_dense_workspace_bytes(int64_t T, int64_t V, int mode, int topk) {
+  if (T <= 0 || V <= 0 || mode < 0 || mode > 2) return 0;
+  return partial_bytes(T, V, mode, topk);
+}
+
+qx_status qx_cuda_lm_head_sample_dense(void* stream, const void* h, const void* W, const float* bias,
+                                       int32_t* ids, void* workspace, size_t workspace_bytes,
+                                       int64_t T, int64_t V, int64_t K, qx_dtype dtype, int mode,
+                                       int topk, double temperature, uint32_t seed) {
+  static const char* op = "lm_head_sample";
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "h/W must be the same float dtype (f32/f16/bf16)");
+  if (!h || !W || !ids) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (mode < 0 || mode > 2) return fail(QX_INVALID_ARGUMENT, op, "mode must be 0/1/2");
+  if (!(temperature > 0.0)) return fail(QX_INVALID_ARGUMENT, op, "temperature must be positive");
+  if (T <= 0 || V <= 0 || K <= 0 || T > 0x7fffffff || V > 0x7fffffff || K > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "h (T,K) and W (V,K) must share K");
+  if (mode == 2 && (topk < 1 || topk > 64)) return fail(QX_INVALID_ARGUMENT, op, "topk k must be in [1, 64]");
+  if (mode == 2 && topk > V) return fail(QX_INVALID_ARGUMENT, op, "topk k must be <= vocab size V");
+  const size_t need = partial_bytes(T, V, mode, topk);
+  if (!workspace || workspace_bytes < need)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace smaller than qx_cuda_lm_head_dense_workspace_bytes");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  const int64_t tiles = tiles_of(V);
+  const int kk = mode == 2 ? topk : 1;
+  const size_t seg = align256((size_t)T * tiles * kk * 4);
+  float* pv = (float*)workspace;
+  int32_t* pi = (int32_t*)((char*)workspace + seg);
+  const float invtemp = 1.0f / (float)temperature;
+  launch_lm_head_dense_partials((cudaStream_t)stream, h, W, bias, pv, pi, T, V, K, dtype, mode, kk, invtemp, seed);
+  launch_lm_head_reduce((cudaStream_t)stream, pv, pi, nullptr, 1, T, tiles * kk, 0, 0, mode, kk, invtemp, seed,
+                        1.0f, ids, 0, nullptr, nullptr);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_sample_logits(void* stream, const void* logits, int32_t* ids, int64_t rows, int64_t V,
+                                qx_dtype dtype, int kind, int topk, double top_p, double temperature,
+                                uint32_t seed) {
+  static const char* names[4] = {"argmax_sample", "sample_categorical", "top_k_sample", "top_p_sample"};
+  if (kind < 0 || kind > 3) return fail(QX_INVALID_ARGUMENT, "sample_logits", "kind 0=argmax, 1=categorical, 2=top-k, 3=top-p");
+  const char* op = names[kind];
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "logits must be fp32/fp16/bf16");
+  if (!logits || !ids) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (rows <= 0 || V <= 0 || rows > 0x7fffffff || V > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "logits must be a non-empty (rows, V) matrix");
+  if (kind >= 1 && !(temperature > 0.0)) return fail(QX_INVALID_ARGUMENT, op, "temperature must be positive");
+  if (kind == 2 && (topk < 1 || topk > 64 || topk > V)) return fail(QX_INVALID_ARGUMENT, op, "k must be in [1, min(64, V)]");
+  if (kind == 3 && !(top_p > 0.0 && top_p <= 1.0)) return fail(QX_INVALID_ARGUMENT, op, "p must be in (0, 1]");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  launch_sample_logits((cudaStream_t)stream, logits, ids, rows, V, dtype, kind, topk, (float)top_p,
+                       kind == 0 ? 1.0f : 1.0f / (float)temperature, seed);
   return check_launch(op);
 }
 
@@ -248,10 +400,14 @@ int64_t qx_cuda_lm_head_shard_candidates(int mode, int topk, int64_t max_tiles) 
   return max_tiles * topk;
 }
 
-size_t qx_cuda_lm_head_shard_workspace_bytes(int64_t T, int64_t V_local, int mode, int topk) {
-  if (mode == 3 || T <= 0 || V_local <= 0) return 0;
-  const size_t kk = mode == 2 ? (size_t)(topk > 0 ? topk : 1) : 1;
-  return 2 * align256((size_t)T * (size_t)tiles_of(V_local) * kk * 4);
+size_t qx_cuda_lm_head_shard_workspace_bytes(int64_t T, int64_t V_local, int64_t K, int mode, int topk) {
+  if (T <= 0 || V_local <= 0 || K <= 0) return 0;
+  size_t n = lm_head_scratch_full_bytes(T, K);
+  if (mode != 3) {
+    const size_t kk = mode == 2 ? (size_t)(topk > 0 ? topk : 1) : 1;
+    n += 2 * align256((size_t)T * (size_t)tiles_of(V_local) * kk * 4);
+  }
+  return n;
 }
 
 qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const void* wq,
@@ -272,20 +428,22 @@ qx_status qx_cuda_lm_head_shard_partials_q(void* stream, const void* h, const vo
   const int64_t tiles = tiles_of(V_local);
   if (max_tiles < tiles) return fail(QX_INVALID_ARGUMENT, op, "max_tiles smaller than this shard's tile count");
   if (vocab_offset + V_local > 0x7fffffffLL) return fail(QX_INVALID_SHAPE, op, "global vocab ids must fit in 31 bits");
-  const size_t need = qx_cuda_lm_head_shard_workspace_bytes(T, V_local, mode, topk);
-  if (need && (!workspace || workspace_bytes < need))
-    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace smaller than qx_cuda_lm_head_shard_workspace_bytes");
+  const size_t need = qx_cuda_lm_head_shard_workspace_bytes(T, V_local, K, mode, topk);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must be 256-byte aligned and at least qx_cuda_lm_head_shard_workspace_bytes");
   if (!device_ready(op, &st)) return st;
   const int kk = mode >= 2 ? topk : 1;
   LmHeadArgs a{h, wq, bias_local, T, V_local, K, vocab_offset, f, dtype, mode, kk,
                1.0f / (float)temperature, seed, 1.0f};
   if (mode == 3) {
+    a.scratch = workspace; a.scratch_bytes = workspace_bytes;
     launch_lm_head_partials((cudaStream_t)stream, a, cand_val, cand_id, cand_lse, max_tiles);
     return check_launch(op);
   }
   const size_t seg = align256((size_t)T * tiles * kk * 4);
   float* pv = (float*)workspace;
   int32_t* pi = (int32_t*)((char*)workspace + seg);
+  a.scratch = (char*)workspace + 2 * seg; a.scratch_bytes = workspace_bytes - 2 * seg;
   launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, nullptr, tiles);
   launch_lm_head_reduce((cudaStream_t)stream, pv, pi, nullptr, 1, T, tiles * kk, 0, 0, mode, kk,
                         a.invtemp, seed, 1.0f, nullptr, 1, cand_val, cand_id);
@@ -378,8 +536,14 @@ size_t qx_cuda_workspace_bytes(const char* op_name, const qx_kernel_call* call) 
     const int mode = (int)attr_i64(call, "mode", 0);
     int topk = (int)attr_i64(call, "topk", 0);
     if (mode >= 2 && topk <= 0) topk = 32;
-    return qx_cuda_lm_head_workspace_bytes(T, V, mode, topk);
+    return qx_cuda_lm_head_workspace_bytes(T, V, K, mode, topk);
   }
+  const bool lin = std::strcmp(op_name, "decode_linear_epilogue") == 0;
+  const bool glu = std::strcmp(op_name, "decode_swiglu") == 0;
+  if ((lin || glu) && call->input_count >= 2 && call->inputs[0].rank == 2 && call->inputs[1].rank == 3)
+    return qx_cuda_projection_workspace_bytes(call->inputs[0].shape[0], call->inputs[0].shape[1],
+                                              call->inputs[1].shape[0], attr_str(call, "format"),
+                                              (qx_dtype)call->inputs[0].dtype, glu ? 1 : 0);
   return 0;
 }
 
@@ -417,6 +581,15 @@ qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
     const qx_tensor_view& y = call->outputs[0];
     if (y.rank != 2 || y.shape[0] != M || y.shape[1] != N || y.dtype != x.dtype)
       return fail(QX_INVALID_SHAPE, op_name, "output must be (B,N) with x dtype");
+    // output_quant attribute ("fp8" / "int8" / "mxfp8"): codes in outputs[1], per-row scales in outputs[2]
+    int oq = 0; void* oq_codes = nullptr; float* oq_scale = nullptr;
+    if (const char* q = attr_str(call, "output_quant")) {
+      oq = std::strcmp(q, "fp8") == 0 ? 1 : std::strcmp(q, "int8") == 0 ? 2 : std::strcmp(q, "mxfp8") == 0 ? 3 : -1;
+      if (oq < 0) return fail(QX_INVALID_ARGUMENT, op_name, "output_quant must be None, 'fp8', 'int8', or 'mxfp8'");
+      if (call->output_count < (oq == 3 ? 2u : 3u)) return fail(QX_INVALID_ARGUMENT, op_name, "output_quant needs codes (and scale) outputs");
+      oq_codes = call->outputs[1].data;
+      if (oq != 3) oq_scale = (float*)call->outputs[2].data;
+    }
     if (lin) {
       const bool ub = attr_i64(call, "use_bias", present(call, 2)) != 0;
       const bool ur = attr_i64(call, "use_residual", present(call, 3)) != 0;
@@ -425,8 +598,9 @@ qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
       if (ur && !(present(call, 3) && call->inputs[3].rank == 2 && call->inputs[3].shape[0] == M && call->inputs[3].shape[1] == N && call->inputs[3].dtype == x.dtype))
         return fail(QX_INVALID_SHAPE, op_name, "residual must be (B,N) with x dtype");
       return qx_cuda_decode_linear_epilogue(call->stream, x.data, w.data, ub ? call->inputs[2].data : nullptr,
-                                            ur ? call->inputs[3].data : nullptr, y.data, M, K, N, fmt, x.dtype,
-                                            (int)attr_i64(call, "activation", 0), ub, ur);
+                                            ur ? call->inputs[3].data : nullptr, y.data, M, K, N, fmt, (qx_dtype)x.dtype,
+                                            (int)attr_i64(call, "activation", 0), ub, ur, oq, oq_codes, oq_scale,
+                                            call->workspace, call->workspace_size);
     }
     const qx_tensor_view& u = call->inputs[2];
     if (u.rank != 3 || u.dtype != QX_DTYPE_U8 || u.shape[0] != N || u.shape[1] != w.shape[1] || u.shape[2] != bb)
@@ -438,7 +612,8 @@ qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
           return fail(QX_INVALID_SHAPE, op_name, "both biases must be (N,) with x dtype");
     }
     return qx_cuda_decode_swiglu(call->stream, x.data, w.data, u.data, ub ? call->inputs[3].data : nullptr,
-                                 ub ? call->inputs[4].data : nullptr, y.data, M, K, N, fmt, x.dtype, ub);
+                                 ub ? call->inputs[4].data : nullptr, y.data, M, K, N, fmt, (qx_dtype)x.dtype, ub,
+                                 oq, oq_codes, oq_scale, call->workspace, call->workspace_size);
   }
   if (std::strcmp(op_name, "quantized_lm_head_sample") == 0) {
     int64_t T, V, K; const char* fmt;
@@ -461,7 +636,7 @@ qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
     }
     return qx_cuda_lm_head_sample_q(call->stream, call->inputs[0].data, call->inputs[1].data, bias,
                                     (int32_t*)call->outputs[0].data, call->workspace, call->workspace_size,
-                                    T, V, K, fmt, call->inputs[0].dtype, mode, topk,
+                                    T, V, K, fmt, (qx_dtype)call->inputs[0].dtype, mode, topk,
                                     attr_f64(call, "temperature", 1.0), (uint32_t)attr_i64(call, "seed", 0),
                                     attr_f64(call, "top_p", 0.9));
   }
@@ -474,7 +649,7 @@ qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
     int64_t rows = 1;
     for (size_t i = 0; i + 1 < x.rank; ++i) rows *= x.shape[i];
     return qx_cuda_quantize_per_token(call->stream, x.data, call->outputs[0].data, (float*)call->outputs[1].data,
-                                      rows, x.shape[x.rank - 1], x.dtype, qi ? 1 : 0);
+                                      rows, x.shape[x.rank - 1], (qx_dtype)x.dtype, qi ? 1 : 0);
   }
   return fail(QX_NOT_IMPLEMENTED, op_name, "operation is not part of the B200 decode-projection backend");
 }

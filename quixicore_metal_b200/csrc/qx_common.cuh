@@ -100,4 +100,53 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- output quantizer encoders (fp32 arithmetic on already-rounded I/O-dtype values) ---------
+// e4m3: nearest with halves rounded AWAY from zero, |x| >= 448 and NaN -> 0x7E, |x| < 2^-10 ->
+// signed zero.  int8: round half away, clamp to +-127.
+__device__ __forceinline__ uint32_t e4m3_encode(float x) {
+  const uint32_t sign = (x < 0.0f) ? 0x80u : 0u;
+  const float a = fabsf(x);
+  if (!(a < 448.0f)) return sign | 0x7Eu;                 // overflow and NaN saturate
+  const uint32_t bits = __float_as_uint(a);
+  const int E = (int)((bits >> 23) & 0xFFu) - 127;
+  if (E < -6) {                                           // e4m3 subnormal range: steps of 2^-9
+    const int m = (int)roundf(a * 512.0f);           // half away from zero, exact
+    if (m <= 0) return sign;
+    return sign | (uint32_t)(m >= 8 ? 8 : m);
+  }
+  int mant = (int)(((bits & 0x7FFFFFu) + 0x80000u) >> 20);
+  int exp = E + 7;
+  if (mant >= 8) { mant = 0; exp += 1; }
+  if (exp > 15 || (exp == 15 && mant >= 7)) return sign | 0x7Eu;
+  return sign | ((uint32_t)exp << 3) | (uint32_t)mant;
+}
+
+__device__ __forceinline__ int int8_encode(float x) {
+  float r = roundf(x);                                    // half away from zero
+  r = fminf(fmaxf(r, -127.0f), 127.0f);
+  return (int)r;
+}
+
+// exact ceil(log2(q)) for a positive finite fp32 q
+__device__ __forceinline__ int ceil_log2(float q) {
+  const uint32_t bits = __float_as_uint(q);
+  int e = (int)((bits >> 23) & 0xFFu) - 127;
+  if (bits & 0x7FFFFFu) e += 1;
+  return e;
+}
+
+// One MXFP8 block {e8m0 exponent; 32 e4m3 codes} from the 32 values held one per lane of a full
+// warp: scale 2^ceil(log2(amax / 448)) (amax > 0), an all-zero block stores exponent 127.
+__device__ __forceinline__ void mxfp8_block_store(float v, int lane, uint8_t* __restrict__ block) {
+  const float amax = warp_max(fabsf(v));
+  int code = 127;
+  if (amax > 0.0f) {
+    const int e = ceil_log2(fmaxf(amax, 1e-10f) / 448.0f);
+    code = min(max(e + 127, 1), 254);
+  }
+  const float inv = 1.0f / __uint_as_float((uint32_t)code << 23);
+  block[1 + lane] = (uint8_t)e4m3_encode(v * inv);
+  if (lane == 0) block[0] = (uint8_t)code;
+}
+
 }  // namespace qx

@@ -10,11 +10,7 @@
 // private ring.  A tile that lies inside one range is finished by that warp.  A tile cut by range
 // boundaries is finished after a CTA barrier by the warp that holds its chunk 0, which adds the
 // other warps' partial accumulators from shared memory in warp order (deterministic).  Every SM
-// therefore streams the same number of bytes whatever N is (the earlier split - whole tiles per
-// warp group, K halved or quartered inside a group - left half of the SMs idle for the last third
-// of the run at N = 28672: 1792 tiles on 1184 groups).
-#include <cstdlib>
-#include <mutex>
+// therefore streams the same number of bytes whatever N is.
 
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
@@ -132,65 +128,18 @@ void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __h
     prep_activations_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, x16, rowscale, M, K, perm, img_rows);
 }
 
-// ---- scratch for the prepared activations -----------------------------------------------------------
-// Calls on one stream are ordered, so a buffer tied to (device, stream) can be reused by every call
-// on that stream without synchronisation.  Up to 16 streams get such a buffer (grown on demand,
-// kept until process exit); further streams fall back to stream-ordered allocation per call.
-struct ScratchSlot { int dev; cudaStream_t st; void* ptr; size_t bytes; };
-static ScratchSlot g_scratch[16] = {};
-static std::mutex g_scratch_mu;
-
-void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free) {
-  *must_free = false;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  cudaStreamIsCapturing(st, &cap);
-  if (cap == cudaStreamCaptureStatusNone) {
-    std::lock_guard<std::mutex> lock(g_scratch_mu);
-    ScratchSlot* free_slot = nullptr;
-    for (auto& s : g_scratch) {
-      if (s.ptr && s.dev == dev && s.st == st) {
-        if (s.bytes >= bytes) return s.ptr;
-        // grow (rare): earlier work of this stream may still read the old buffer
-        cudaStreamSynchronize(st);
-        cudaFree(s.ptr);
-        s.ptr = nullptr;
-        free_slot = &s;
-        break;
-      }
-      if (!s.ptr && !free_slot) free_slot = &s;
-    }
-    if (free_slot) {
-      void* p = nullptr;
-      const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
-      if (cudaMalloc(&p, want) == cudaSuccess) {
-        *free_slot = ScratchSlot{dev, st, p, want};
-        return p;
-      }
-      cudaGetLastError();
-    }
-  }
-  void* p = nullptr;
-  if (cudaMallocAsync(&p, bytes, st) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-  *must_free = true;
-  return p;
-}
-
 // Whole stages run fully unrolled in the instantiations with up to this many 8-row n-tiles (0 = never).
-// Measured at K = 8192, N = 28672: nvfp4 44.4 -> 39.2 us (1 row), 69.2 -> 59.5 us (16 rows); q8_0 52.4 -> 48.7 us.
 #ifndef QX_STREAM_UNROLL
 #define QX_STREAM_UNROLL 2
 #endif
 constexpr int STREAM_STAGES = 2;      // per-warp ring depth; latency is hidden by the number of warps
 
-// HALF = stages of half the format's column count.  Measured at K = 8192, N = 28672 on one GPU:
-//  * single matrix, 1 - 2 rows: full-width stages; 20 warps (102 registers each) beat 16 by 2 - 10 %
-//    (q8_0 56.7 -> 51.5 us; mxfp4, 8 bytes of spill at that limit, 37.1 -> 36.2 us);
+// HALF = stages of half the format's column count.
+//  * single matrix, 1 - 2 rows: full-width stages and 20 warps (102 registers each);
 //  * more rows, or a SwiGLU pair: half-width stages.  The prepared activations (2*K bytes per row)
 //    are re-read from L1 by every warp; the smaller rings leave the L1 side of the SM's memory large
-//    enough to hold them (nvfp4, 8 rows: 60.6 -> 51.9 us), and a SwiGLU stage of 32 rows fits 16
-//    warps instead of 10 (85.1 -> 76.5 us).  q6_K cannot halve (a stage is one decode group).
+//    enough to hold them, and a SwiGLU stage of 32 rows fits 16 warps instead of 10.
+//    q6_K cannot halve (a stage is one decode group).
 template <int FMT, bool DUAL, bool HALF>
 struct StreamCfg {
   static_assert(!(HALF && FMT == F_Q6_K), "q6_K stages cannot be halved");
@@ -212,7 +161,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
                    const __half* __restrict__ x16, const float* __restrict__ rowscale,
                    const T* __restrict__ bias0, const T* __restrict__ bias1,
                    const T* __restrict__ residual, T* __restrict__ y, int M, int K, int N,
-                   int activation, int use_bias, int use_residual, int* __restrict__ err_flag) {
+                   int activation, int use_bias, int use_residual, uint8_t* __restrict__ mx_blocks,
+                   int* __restrict__ err_flag) {
   using Cfg = StreamCfg<FMT, DUAL, HALF>;
   using WS = typename Cfg::WS;
   using F = StreamFmt<FMT>;
@@ -233,10 +183,14 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
 
   // This CTA's m-tiles [T0, T1) and the flat list of their (tile, chunk) steps; this warp's share
   // of the list is [sb, se).
+  // With the fused MXFP8 output (mx_blocks) the shares are cut at even tiles, so that every block
+  // of 32 output channels is produced by one CTA, which packs it once its tiles are stored.
   const int ntiles = (N + 15) >> 4;
   const int nch = ws.nch;
-  const int T0 = (int)((long long)ntiles * blockIdx.x / gridDim.x);
-  const int T1 = (int)((long long)ntiles * (blockIdx.x + 1) / gridDim.x);
+  const int tunit = mx_blocks ? 2 : 1;
+  const int nunits = (ntiles + tunit - 1) / tunit;
+  const int T0 = min(ntiles, tunit * (int)((long long)nunits * blockIdx.x / gridDim.x));
+  const int T1 = min(ntiles, tunit * (int)((long long)nunits * (blockIdx.x + 1) / gridDim.x));
   const unsigned S = (unsigned)((T1 - T0) * nch);          // the host keeps S * (nwarps + 1) below 2^31
   auto range_begin = [&](int w) { return (int)(S * (unsigned)w / (unsigned)nwarps); };
   const int sb = range_begin(warp), se = range_begin(warp + 1);
@@ -383,6 +337,20 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     }
     epilogue(pending_tile * 16);
   }
+
+  // ---- fused output requantisation: the rounded outputs of this CTA's channels -> MXFP8 blocks ----
+  if constexpr (sizeof(T) == 2) {
+    if (mx_blocks) {
+      __syncthreads();                               // this CTA's stores to y are visible to the CTA
+      const int nb0 = T0 >> 1, nb = (T1 >> 1) - nb0;
+      const int nblk_row = N >> 5;
+      for (int idx = warp; idx < nb * M; idx += nwarps) {
+        const int blk = nb0 + idx / M, m = idx - (idx / M) * M;
+        const float v = to_f32<T>(y[(size_t)m * N + blk * 32 + lane]);
+        mxfp8_block_store(v, lane, mx_blocks + ((size_t)m * nblk_row + blk) * 33);
+      }
+    }
+  }
 }
 
 template <int FMT, int NT, bool DUAL, bool HALF, typename T>
@@ -390,13 +358,13 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   const int sms = sm_count();
   const int ntiles = (int)((a.N + 15) / 16);
   using Cfg = StreamCfg<FMT, DUAL, HALF>;
-  int nwarps = Cfg::max_warps(NT);
-  if (const char* e = getenv("QX_STREAM_WARPS")) nwarps = max(1, min(nwarps, atoi(e)));
+  const int nwarps = Cfg::max_warps(NT);
   // one CTA per SM; a CTA takes a contiguous, balanced share of the m-tiles and its warps split the
   // (tile, chunk) steps of that share evenly
-  const int blocks = ntiles < sms ? ntiles : sms;
+  const int units = (a.out_quant == OQ_MXFP8 && !a.out_f32 && a.N % 32 == 0) ? (ntiles + 1) / 2 : ntiles;
+  const int blocks = units < sms ? units : sms;
   const long long nch = (a.K + Cfg::KC - 1) / Cfg::KC;
-  if ((long long)((ntiles + blocks - 1) / blocks) * nch * (nwarps + 1) >= (1LL << 31)) return false;
+  if ((long long)((ntiles + blocks - 1) / blocks + 2) * nch * (nwarps + 1) >= (1LL << 31)) return false;
   const size_t smem = (size_t)nwarps * Cfg::warp_smem(NT);
   static bool attr_set[64] = {};                    // per instantiation and device
   int dev = 0;
@@ -413,24 +381,21 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   int* err = device_error_flag();
   if (!err) return false;
 
-  // stream-ordered scratch for the prepared activations
+  // prepared activations and row scales live in the call's scratch
   const size_t x16_bytes = ((size_t)a.M * a.K * 2 + 255) & ~(size_t)255;
-  bool must_free = false;
-  void* scratch = stream_scratch(st, x16_bytes + (size_t)a.M * 4, &must_free);
-  if (!scratch) return false;
-  __half* x16 = (__half*)scratch;
-  float* rowscale = (float*)((char*)scratch + x16_bytes);
+  if (!a.scratch || a.scratch_bytes < x16_bytes + (((size_t)a.M * 4 + 255) & ~(size_t)255)) return false;
+  __half* x16 = (__half*)a.scratch;
+  float* rowscale = (float*)((char*)a.scratch + x16_bytes);
   launch_prep_activations(st, a.x, a.dtype, x16, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM);
   using WSG = typename Cfg::WS::G;
   const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
   CUtensorMap map0, map1;
-  bool maps_ok = make_weight_map(&map0, a.w0, a.N, row_bytes, WSG::PITCH, 16);
-  if (maps_ok && DUAL) maps_ok = make_weight_map(&map1, a.w1, a.N, row_bytes, WSG::PITCH, 16);
+  bool maps_ok = cached_weight_map(&map0, a.w0, a.N, row_bytes, WSG::PITCH, 16);
+  if (maps_ok && DUAL) maps_ok = cached_weight_map(&map1, a.w1, a.N, row_bytes, WSG::PITCH, 16);
   if (!DUAL) map1 = map0;
-  if (!maps_ok) {
-    if (must_free) cudaFreeAsync(scratch, st);
-    return false;
-  }
+  if (!maps_ok) return false;
+  // MXFP8 output rows are packed by the same kernel (needs whole 32-channel blocks)
+  uint8_t* mx = (a.out_quant == OQ_MXFP8 && !a.out_f32 && a.N % 32 == 0) ? (uint8_t*)a.q_codes : nullptr;
   // launched as a programmatic dependent of the preparation kernel (see griddepcontrol.wait)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
@@ -445,13 +410,12 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, HALF, T>, map0, map1, (const __half*)x16,
                          (const float*)rowscale, (const T*)a.bias0, (const T*)a.bias1,
                          (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
-                         a.use_bias, a.use_residual, err) != cudaSuccess) {
+                         a.use_bias, a.use_residual, mx, err) != cudaSuccess) {
     cudaGetLastError();
     gemv_stream_kernel<FMT, NT, DUAL, HALF, T><<<blocks, nwarps * 32, smem, st>>>(
         map0, map1, x16, rowscale, (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual,
-        (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, err);
+        (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, mx, err);
   }
-  if (must_free) cudaFreeAsync(scratch, st);
   note_launch(2);
   return true;
 }
@@ -511,23 +475,27 @@ bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a) {
 // gives every CTA one item of 256 weight rows; a projection with few such items (O / down / QKV of
 // a 70B-class block, any tensor-parallel shard) leaves most SMs idle there (N = 8192: 32 of 148),
 // while the streaming kernel spreads any N over all SMs.  Re-reading the weights once per pass is
-// cheaper than that as long as the passes are few.  QX_STREAM_PASSES=0 never, =2 whenever possible.
+// cheaper than that as long as the passes are few (option "stream_passes": 0 never, 2 whenever possible).
 bool stream_passes_ok(const GemvArgs& a) {
-  const char* e = getenv("QX_STREAM_PASSES");      // read per call: tests switch it
-  const int mode = e ? atoi(e) : 1;
-  // q6_K has no tcgen05 pipeline form (its batch > 16 kernel reads weights per thread and is
-  // 5 - 10 x slower than two streaming passes at 32 rows), so it takes passes up to 256 rows.
+  const int mode = options().stream_passes;
+  // q6_K has no tcgen05 pipeline form, so it takes passes up to 256 rows.
   if (mode == 0 || a.M <= 16 || a.M > (a.format == F_Q6_K ? 256 : 64)) return false;
   GemvArgs b = a;
   b.M = 16;
   if (!stream_path_ok(b)) return false;
   if (mode == 2 || a.format == F_Q6_K) return true;
-  // Measured (nvfp4, K = 8192, 32 rows): N = 8192 (32 items) 101 -> 59 us, N = 10240 101 -> 64 us,
-  // K = 28672 -> N = 8192 326 -> 158 us, but N = 28672 (112 items) 103 -> 137 us; at 64 rows and
-  // 32 items the two paths are level.
+  // passes win while the pipeline would leave most SMs without an item
   const long long items = (a.N + 255) / 256;          // work items of the tcgen05 pipeline
   const int passes = (int)((a.M + 15) / 16);
   return (passes <= 2 && items <= 96) || items <= 48;
+}
+
+size_t stream_scratch_bytes(const GemvArgs& a) {
+  int64_t rows = 0;
+  if (stream_path_ok(a)) rows = a.M;
+  else if (stream_passes_ok(a)) rows = 16;
+  if (rows == 0) return 0;
+  return (((size_t)rows * a.K * 2 + 255) & ~(size_t)255) + (((size_t)rows * 4 + 255) & ~(size_t)255);
 }
 
 bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a) {
@@ -538,6 +506,7 @@ bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a) {
     b.x = (const char*)a.x + (size_t)m0 * a.K * 2;
     b.y = (char*)a.y + (size_t)m0 * a.N * out_size;
     if (a.residual) b.residual = (const char*)a.residual + (size_t)m0 * a.N * 2;
+    if (a.q_codes && a.out_quant == OQ_MXFP8) b.q_codes = (char*)a.q_codes + (size_t)m0 * (a.N / 32) * 33;
     if (!launch_gemv_stream(st, b)) return false;
   }
   return true;

@@ -19,7 +19,34 @@ struct GemvArgs {
   qx_dtype dtype;      // F32 / F16 / BF16
   int activation, use_bias, use_residual;
   int out_f32 = 0;     // 1: y is fp32 (M,N) raw dot products, no bias / activation / residual
+  // Output requantisation fused behind the epilogue: 0 none, 1 per-token fp8, 2 per-token int8,
+  // 3 MXFP8 rows (N % 32 == 0).  q_codes receives the codes / packed blocks, q_scale the per-row
+  // scales (kinds 1 and 2).  y is written in every case (the codes are defined on its rounded values).
+  int out_quant = 0;
+  void* q_codes = nullptr;
+  float* q_scale = nullptr;
+  // Device scratch of at least projection_scratch_bytes(*this) bytes, 256-byte aligned.
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
 };
+
+enum OutQuant : int { OQ_NONE = 0, OQ_FP8 = 1, OQ_INT8 = 2, OQ_MXFP8 = 3 };
+
+// Switches between device paths that compute the same result (identical up to fp32 summation
+// order).  Defaults are the measured-fastest choices; qx_cuda_set_option changes them.
+struct Options {
+  int stream_passes = 1;        // 17 - 64 rows as 16-row passes: 0 never, 1 when faster, 2 whenever possible
+  bool force_generic = false;   // keep every call on the shape-generic kernels
+  bool tc_pipeline = true;      // batch > 16 on the tcgen05 pipeline
+  bool lm_head_ksplit = true;   // share the items of a partial round over K between CTAs
+  bool lm_head_overlap = true;  // selection of one tile overlapped with the projection of the next
+};
+const Options& options();
+bool set_option(const char* name, int value);
+
+// Scratch for a call that brought no workspace (see qx_scratch.cu); *must_free: cudaFreeAsync on st.
+void* default_scratch(cudaStream_t st, size_t bytes, bool* must_free);
+uint64_t scratch_alloc_count();
 
 void launch_gemv_generic(cudaStream_t st, const GemvArgs& a);
 // Streaming tensor-core path (bf16 activations, batch <= 16, 16-byte aligned bases).
@@ -30,22 +57,25 @@ bool stream_passes_ok(const GemvArgs& a);
 bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a);
 // tcgen05 path (bf16 activations, batch > 16, K % 256 == 0, single weight matrix).
 bool tc_path_ok(const GemvArgs& a);
-bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a);
+// *fused_quant (optional): set when the kernel that ran packed the requested MXFP8 output rows itself
+bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a, bool* fused_quant = nullptr);
 // Value of the device-side error flag that bounded waits raise (synchronises the device).
 int read_device_error_flag();
 // Device address of that flag on the current device (nullptr if it cannot be resolved).
 int* device_error_flag();
-// Device scratch of at least `bytes` for work enqueued on `st` (see qx_gemv_stream.cu); when
-// *must_free is set the caller releases it with cudaFreeAsync on the same stream.
-void* stream_scratch(cudaStream_t st, size_t bytes, bool* must_free);
+// Scratch bytes each path family needs for this call (0 when the family cannot take it).
+size_t stream_scratch_bytes(const GemvArgs& a);
+size_t tc_scratch_bytes(const GemvArgs& a);
+size_t projection_scratch_bytes(const GemvArgs& a);
 // Row-scaled f16 copy of (M,K) bf16 / f16 activations in the column order `perm` of the decoders.
 // silu(gate + gb) * (up + ub) over fp32 (M,N) projections -> T (M,N)
 void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, const void* gb,
                            const void* ub, void* y, int64_t M, int64_t N, qx_dtype dtype, int use_bias);
 void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __half* x16,
                              float* rowscale, int M, int K, int perm, int img_rows = 0);
-// Picks the kernel family for one projection call (format, dtype, batch, alignment).
-void launch_projection(cudaStream_t st, const GemvArgs& a);
+// Picks the kernel family for one projection call (format, dtype, batch, alignment); true when the
+// kernel that ran also wrote the requested MXFP8 output rows.
+bool launch_projection(cudaStream_t st, const GemvArgs& a);
 
 // Fused LM head.  Stage 1 writes per-256-row-tile partials, stage 2 merges them.
 struct LmHeadArgs {
@@ -55,7 +85,15 @@ struct LmHeadArgs {
   int format; qx_dtype dtype;
   int mode, topk;
   float invtemp; uint32_t seed; float top_p;
+  // Device scratch of at least lm_head_scratch_bytes(T, K) bytes (prepared activations, row scales,
+  // the release flags and - as far as it reaches - the exchange slots of K-split items).
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
 };
+// Minimum scratch of stage 1 (without exchange slots: items are then not shared) and the size
+// with which every sharing choice fits.
+size_t lm_head_scratch_min_bytes(int64_t T, int64_t K);
+size_t lm_head_scratch_full_bytes(int64_t T, int64_t K);
 // part_val/part_id: (T, tiles_stride, kk) with kk = 1 (modes 0/1) or topk; part_lse: (T, tiles_stride)
 void launch_lm_head_partials(cudaStream_t st, const LmHeadArgs& a, float* part_val,
                              int32_t* part_id, float* part_lse, int64_t tiles_stride);
@@ -69,6 +107,20 @@ void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t
                            int64_t nlse, int64_t shard_stride, int mode, int topk, float invtemp,
                            uint32_t seed, float top_p, int32_t* ids, int emit_set, float* out_val,
                            int32_t* out_id);
+
+// qx_cuda_lm_head_sample_q on a caller-chosen region [partials | stage-1 scratch] (see qx_capi.cu).
+qx_status lm_head_sample_on(const char* op, void* stream, const void* h, const void* wq, const float* bias,
+                            int32_t* ids, void* workspace, size_t workspace_bytes, bool min_only, int64_t T,
+                            int64_t V, int64_t K, const char* format, qx_dtype dtype, int mode, int topk,
+                            double temperature, uint32_t seed, double top_p);
+
+// Stage 1 over a dense (V, K) head in h's dtype (modes 0..2); partials as in the packed form.
+void launch_lm_head_dense_partials(cudaStream_t st, const void* h, const void* W, const float* bias,
+                                   float* part_val, int32_t* part_id, int64_t T, int64_t V, int64_t K,
+                                   qx_dtype dtype, int mode, int topk, float invtemp, uint32_t seed);
+// Samplers over materialised logits (rows, V): kind 0 argmax, 1 categorical, 2 top-k, 3 top-p.
+void launch_sample_logits(cudaStream_t st, const void* logits, int32_t* ids, int64_t rows, int64_t V,
+                          qx_dtype dtype, int kind, int topk, float p, float invtemp, uint32_t seed);
 
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);

@@ -12,26 +12,19 @@
 // normalizer; Gumbel-max with the stateless (seed, row, global id) noise stream.
 //
 // Ordering everywhere: value descending, ties to the smaller id.
-#include <cstdio>
 #include <atomic>
-#include <cstdlib>
 
+#include "qx_block.cuh"
 #include "qx_formats.cuh"
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
+#include "qx_tmap.h"
 
 namespace qx {
 
 constexpr int LMH_TILE = 256;
 constexpr int LMH_TB = 8;        // hidden rows per stage-1 CTA
 constexpr int LMH_RED_THREADS = 1024;
-
-// Order-preserving map float -> uint32 (larger float = larger key; +0 and -0 share a key).
-__device__ __forceinline__ uint32_t float_key(float v) {
-  uint32_t u = __float_as_uint(v);
-  if (v == 0.0f) u = 0u;
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
 
 // Reduce one hidden row's 256 tile logits (shared memory) to the tile partials of its mode.
 // Executed by one warp.  nvalid <= 0 marks a padding tile: absent partials are written.
@@ -218,6 +211,87 @@ lmh_partials_kernel(const T* __restrict__ h, const uint8_t* __restrict__ wq,
 }
 
 
+// Stage 1 over a dense (V, K) head in the dtype of h (the reference's unquantized lm_head_sample,
+// kernels/quantization/lm_head/lm_head.metal:175-217, :400-441): same tiles, same partials, same
+// score formulas as the packed form; a warp walks a vocabulary row with 16-byte loads and keeps
+// fp32 sums for up to 8 hidden rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+lmh_dense_partials_kernel(const T* __restrict__ h, const T* __restrict__ W,
+                          const float* __restrict__ bias, float* __restrict__ part_val,
+                          int32_t* __restrict__ part_id, int T_rows, int V, int K,
+                          long long tiles_stride, int mode, int topk, float invtemp, uint32_t seed) {
+  __shared__ float logit[LMH_TB][LMH_TILE];
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tile = blockIdx.x;
+  const int t0 = blockIdx.y * LMH_TB;
+  const int tcount = min(LMH_TB, T_rows - t0);
+  const int v0 = tile * LMH_TILE;
+  const bool vec_ok = (K % VEC) == 0 && (((uintptr_t)W | (uintptr_t)h) & 15) == 0;
+  for (int r = 0; r < 32; ++r) {
+    const int lr = warp * 32 + r;
+    const int v = v0 + lr;
+    if (v >= V) {
+      if (lane < LMH_TB) logit[lane][lr] = QX_NEG_INF;
+      continue;
+    }
+    const T* row = W + (size_t)v * K;
+    float acc[LMH_TB];
+#pragma unroll
+    for (int m = 0; m < LMH_TB; ++m) acc[m] = 0.f;
+    if (vec_ok) {
+      for (int c = lane * VEC; c < K; c += 32 * VEC) {
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(row + c));
+        const T* we = reinterpret_cast<const T*>(&wv);
+#pragma unroll
+        for (int m = 0; m < LMH_TB; ++m) {
+          if (m < tcount) {
+            const uint4 hv = __ldg(reinterpret_cast<const uint4*>(h + (size_t)(t0 + m) * K + c));
+            const T* he = reinterpret_cast<const T*>(&hv);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[m] = fmaf(to_f32<T>(we[i]), to_f32<T>(he[i]), acc[m]);
+          }
+        }
+      }
+    } else {
+      for (int c = lane; c < K; c += 32) {
+        const float wv = to_f32<T>(row[c]);
+#pragma unroll
+        for (int m = 0; m < LMH_TB; ++m)
+          if (m < tcount) acc[m] = fmaf(wv, to_f32<T>(h[(size_t)(t0 + m) * K + c]), acc[m]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < LMH_TB; ++m) {
+      const float s = warp_sum(acc[m]);
+      if (lane == 0) logit[m][lr] = s;
+    }
+  }
+  __syncthreads();
+  if (warp >= tcount) return;
+  lmh_select_token(logit[warp], min(LMH_TILE, V - v0), v0, 0, bias, t0 + warp, tile, tiles_stride, mode,
+                   topk, invtemp, seed, part_val, part_id, nullptr, lane);
+}
+
+void launch_lm_head_dense_partials(cudaStream_t st, const void* h, const void* W, const float* bias,
+                                   float* part_val, int32_t* part_id, int64_t T, int64_t V, int64_t K,
+                                   qx_dtype dtype, int mode, int topk, float invtemp, uint32_t seed) {
+  const long long tiles = (V + LMH_TILE - 1) / LMH_TILE;
+  dim3 grid((unsigned)tiles, (unsigned)((T + LMH_TB - 1) / LMH_TB));
+  if (dtype == QX_DTYPE_F32)
+    lmh_dense_partials_kernel<float><<<grid, 256, 0, st>>>((const float*)h, (const float*)W, bias, part_val, part_id,
+                                                            (int)T, (int)V, (int)K, tiles, mode, topk, invtemp, seed);
+  else if (dtype == QX_DTYPE_F16)
+    lmh_dense_partials_kernel<__half><<<grid, 256, 0, st>>>((const __half*)h, (const __half*)W, bias, part_val, part_id,
+                                                             (int)T, (int)V, (int)K, tiles, mode, topk, invtemp, seed);
+  else
+    lmh_dense_partials_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)W, bias,
+                                                                    part_val, part_id, (int)T, (int)V, (int)K, tiles,
+                                                                    mode, topk, invtemp, seed);
+  note_launch();
+}
+
 // ------------------------------------------------------------------------------------------
 // Stage 1, streaming tensor-core form (bf16 / f16 hidden rows, aligned shapes): the projection
 // runs on the per-warp weight stream of qx_stream.cuh.  A CTA is 8 warps and owns one 256-row
@@ -233,10 +307,8 @@ template <> struct LmhCfg<F_NVFP4> { static constexpr int KC = 256, STAGES = 4; 
 template <> struct LmhCfg<F_MXFP4> { static constexpr int KC = 512, STAGES = 2; };
 template <> struct LmhCfg<F_MXFP8> { static constexpr int KC = 128, STAGES = 2; };
 
-// Whole stages run fully unrolled for up to this many 8-row n-tiles (q8_0, V = 128256, argmax:
-// 141 -> 120 us per call at 1 row, 268 -> 211 us at 16 rows).
-// n-tiles from which a CTA is 16 warps of 16 rows instead of 8 warps of 32 rows (q8_0, V = 128256,
-// 16 hidden rows: 212 -> 197 us per argmax call; at 8 rows the 32-row form is 10 % faster).
+// QX_LMH_UNROLL: whole stages run fully unrolled for up to this many 8-row n-tiles.
+// QX_LMH_WROWS16_MIN_NT: n-tiles from which a CTA is 16 warps of 16 rows instead of 8 warps of 32.
 #ifndef QX_LMH_WROWS16_MIN_NT
 #define QX_LMH_WROWS16_MIN_NT 2
 #endif
@@ -536,6 +608,36 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   note_launch();
 }
 
+// ---- stage-1 scratch ----------------------------------------------------------------------------
+// [0, 1 KB)  release flags of K-split items (cleared before every launch that shares items)
+// [1 KB, ..) prepared activations (row-major, or the operand-tile image in groups of 32 / 64 rows)
+// then       one fp32 row scale per hidden row
+// then       exchange slots of K-split items, as far as the scratch reaches
+constexpr size_t LMH_FLAG_BYTES = 1024;
+static size_t lmh_round256(size_t n) { return (n + 255) & ~(size_t)255; }
+static size_t lmh_act_bytes(int64_t T, int64_t K) { return lmh_round256((size_t)((T + 63) / 64 * 64) * K * 2); }
+size_t lm_head_scratch_min_bytes(int64_t T, int64_t K) {
+  return LMH_FLAG_BYTES + lmh_act_bytes(T, K) + lmh_round256((size_t)T * 4);
+}
+size_t lm_head_scratch_full_bytes(int64_t T, int64_t K) {
+  // at most 3/4 of the SMs hold a partner slot of 64 x 256 floats
+  return lm_head_scratch_min_bytes(T, K) + (T > 16 ? (size_t)(3 * sm_count() / 4) * 64 * LMH_TILE * 4 : 0);
+}
+struct LmhScratch {
+  unsigned* flags; __half* act; float* rowscale; float* xchg; size_t xchg_bytes;
+};
+static bool lmh_carve(const LmHeadArgs& a, LmhScratch* out) {
+  const size_t need = lm_head_scratch_min_bytes(a.T, a.K);
+  if (!a.scratch || a.scratch_bytes < need) return false;
+  char* p = (char*)a.scratch;
+  out->flags = (unsigned*)p;
+  out->act = (__half*)(p + LMH_FLAG_BYTES);
+  out->rowscale = (float*)(p + LMH_FLAG_BYTES + lmh_act_bytes(a.T, a.K));
+  out->xchg = (float*)(p + need);
+  out->xchg_bytes = a.scratch_bytes - need;
+  return true;
+}
+
 // tcgen05 form of stage 1 for more than 16 hidden rows.
 template <int FMT, int BN>
 static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
@@ -554,19 +656,17 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
     }
     attr_set[dev] = true;
   }
+  LmhScratch sc;
+  if (!lmh_carve(a, &sc)) return false;
   const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
   CUtensorMap wmap;
-  if (!make_weight_map(&wmap, a.wq, a.V, row_bytes, C::BOX)) return false;
+  if (!cached_weight_map(&wmap, a.wq, a.V, row_bytes, C::BOX)) return false;
   const int groups = (int)((a.T + BN - 1) / BN);
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   const long long items = (long long)real_tiles * groups;
   // The last, partial round of items (all items, when there are fewer than SMs - a small vocabulary
   // shard): when it would leave at least half of the SMs idle, each of its items is shared by 2 or
-  // 4 CTAs that take a slice of K each (QX_LMH_KSPLIT=0 turns it off).
-  static const bool split_enabled = [] {
-    const char* e = getenv("QX_LMH_KSPLIT");
-    return !(e && e[0] == '0');
-  }();
+  // 4 CTAs that take a slice of K each, as far as the exchange slots fit the scratch.
   const int nks = (int)(a.K / LTC_KS);
   const long long sms = sm_count();
   const long long leftover = items % sms;
@@ -575,30 +675,27 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
   // invalidate the capture, and there is no second attempt inside one
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   cudaStreamIsCapturing(st, &cap);
-  if (split_enabled && leftover > 0 && cap == cudaStreamCaptureStatusNone) {
-    if (leftover * 4 <= sms && nks % 4 == 0) ksplit = 4;
-    else if (leftover * 2 <= sms && nks % 2 == 0) ksplit = 2;
+  const size_t slot_bytes = (size_t)BN * LMH_TILE * 4;
+  auto fits = [&](int ks) {
+    return (size_t)leftover * (ks - 1) * slot_bytes <= sc.xchg_bytes && (size_t)leftover * (ks - 1) * 4 <= LMH_FLAG_BYTES;
+  };
+  if (options().lm_head_ksplit && leftover > 0 && cap == cudaStreamCaptureStatusNone) {
+    if (leftover * 4 <= sms && nks % 4 == 0 && fits(4)) ksplit = 4;
+    else if (leftover * 2 <= sms && nks % 2 == 0 && fits(2)) ksplit = 2;
   }
   const unsigned grid = (unsigned)(items >= sms ? sms : items * ksplit);
-  const size_t img_bytes = ((size_t)groups * BN * a.K * 2 + 255) & ~(size_t)255;
-  const size_t rs_bytes = ((size_t)a.T * 4 + 255) & ~(size_t)255;
-  const size_t xchg_bytes = ksplit > 1 ? (size_t)leftover * (ksplit - 1) * BN * LMH_TILE * 4 : 0;
-  const size_t flag_bytes = ksplit > 1 ? (((size_t)leftover * (ksplit - 1) * 4 + 255) & ~(size_t)255) : 0;
-  bool must_free = false;
-  void* scratch = stream_scratch(st, img_bytes + rs_bytes + xchg_bytes + flag_bytes, &must_free);
-  if (!scratch) return false;
-  __half* ximg = (__half*)scratch;
-  float* rowscale = (float*)((char*)scratch + img_bytes);
-  float* xchg = (float*)((char*)scratch + img_bytes + rs_bytes);
-  unsigned* flags = (unsigned*)((char*)scratch + img_bytes + rs_bytes + xchg_bytes);
   static std::atomic<unsigned> epoch_counter{1};
   const unsigned epoch = epoch_counter.fetch_add(1) | 0x40000000u;     // never 0
-  launch_prep_activations(st, a.h, a.dtype, ximg, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM, BN);
+  launch_prep_activations(st, a.h, a.dtype, sc.act, sc.rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM, BN);
   note_launch();
   const typename Epi::Args ea{a.bias, pv, pi, pl, (int)a.T, (int)a.V, (long long)a.vocab_offset,
                               (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed,
-                              xchg, flags, epoch, err};
+                              sc.xchg, sc.flags, epoch, err};
   bool launched = false;
+  if (ksplit > 1) {
+    // the flags start every launch at zero, whatever an earlier user of the scratch left there
+    if (cudaMemsetAsync(sc.flags, 0, LMH_FLAG_BYTES, st) != cudaSuccess) { cudaGetLastError(); ksplit = 1; }
+  }
   if (ksplit > 1) {
     // CTAs of this launch wait for one another: ask for a cooperative launch, which only starts
     // when the whole grid is resident
@@ -612,26 +709,23 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    launched = cudaLaunchKernelEx(&cfg, tc_pipeline_kernel<FMT, BN, Epi>, wmap, wmap, (const __half*)ximg,
-                                  (const float*)rowscale, (int)a.T, (int)a.V, (int)a.K, ksplit, err, ea) == cudaSuccess;
+    launched = cudaLaunchKernelEx(&cfg, tc_pipeline_kernel<FMT, BN, Epi>, wmap, wmap, (const __half*)sc.act,
+                                  (const float*)sc.rowscale, (int)a.T, (int)a.V, (int)a.K, ksplit, err, ea) == cudaSuccess;
     if (!launched) { cudaGetLastError(); ksplit = 1; }
   }
-  if (!launched)
-    tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
-        wmap, wmap, ximg, rowscale, (int)a.T, (int)a.V, (int)a.K, 1, err, ea);
+  if (!launched) {
+    const unsigned grid1 = (unsigned)(items >= sms ? sms : items);
+    tc_pipeline_kernel<FMT, BN, Epi><<<grid1, LTC_WARPS * 32, S::TOTAL, st>>>(
+        wmap, wmap, sc.act, sc.rowscale, (int)a.T, (int)a.V, (int)a.K, 1, err, ea);
+  }
   note_launch();
-  if (must_free) cudaFreeAsync(scratch, st);
   return true;
 }
 
 template <int FMT>
 static bool launch_lmh_tc(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
                           int64_t tiles_stride, int* err) {
-  static const bool enabled = [] {
-    const char* e = getenv("QX_LMH_TC");
-    return !(e && e[0] == '0');
-  }();
-  if (!enabled || a.T <= 16 || a.K % LTC_KS != 0 || a.V < 128) return false;
+  if (a.T <= 16 || a.K % LTC_KS != 0 || a.V < 128) return false;
   if (a.T <= 32) return launch_lmh_tc_bn<FMT, 32>(st, a, pv, pi, pl, tiles_stride, err);
   return launch_lmh_tc_bn<FMT, 64>(st, a, pv, pi, pl, tiles_stride, err);
 }
@@ -640,60 +734,36 @@ template <int FMT>
 static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi, float* pl,
                               int64_t tiles_stride) {
   if (!lmh_stream_ok<FMT>(a)) return false;
-  if (int* e = device_error_flag()) {
-    if (launch_lmh_tc<FMT>(st, a, pv, pi, pl, tiles_stride, e)) return true;
-  }
   int* err = device_error_flag();
   if (!err) return false;
+  if (launch_lmh_tc<FMT>(st, a, pv, pi, pl, tiles_stride, err)) return true;
+  LmhScratch sc;
+  if (!lmh_carve(a, &sc)) return false;
   CUtensorMap wmap;
   {
     const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
-    if (!make_weight_map(&wmap, a.wq, a.V, row_bytes, StageGeom<FMT, LmhCfg<FMT>::KC>::PITCH, 16)) return false;
+    if (!cached_weight_map(&wmap, a.wq, a.V, row_bytes, StageGeom<FMT, LmhCfg<FMT>::KC>::PITCH, 16)) return false;
   }
-  const size_t x16_bytes = ((size_t)a.T * a.K * 2 + 255) & ~(size_t)255;
-  bool must_free = false;
-  void* scratch = stream_scratch(st, x16_bytes + (size_t)a.T * 4, &must_free);
-  if (!scratch) return false;
-  __half* x16 = (__half*)scratch;
-  float* rowscale = (float*)((char*)scratch + x16_bytes);
+  __half* x16 = sc.act;
+  float* rowscale = sc.rowscale;
   launch_prep_activations(st, a.h, a.dtype, x16, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM);
   note_launch();
   // hidden rows per CTA: 64 when there are enough vocabulary tiles to fill the GPU; fewer rows
   // per CTA (more CTAs, each re-reading the weights from L2) when the vocabulary shard is small
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   int tpg = 64;
-  static const int tpg_override = [] {                 // A/B override of the hidden rows per CTA
-    const char* e = getenv("QX_LMH_TPG");
-    return e ? atoi(e) : 0;
-  }();
-  {
-    const int v = tpg_override;
-    if (v == 8 || v == 16 || v == 32 || v == 64) {
-      if (v <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-      else if (v <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-      else if (v <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-      else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-      if (must_free) cudaFreeAsync(scratch, st);
-      return true;
-    }
-  }
   while (tpg > 8 && (long long)real_tiles * ((a.T + tpg - 1) / tpg) < sm_count() && a.T > tpg / 2) tpg >>= 1;
   while (tpg > 8 && a.T <= tpg / 2) tpg >>= 1;
   if (tpg <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
   else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
   else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
   else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-  if (must_free) cudaFreeAsync(scratch, st);
   return true;
 }
 
 static bool launch_lmh_stream_any(cudaStream_t st, const LmHeadArgs& a, float* pv, int32_t* pi,
                                   float* pl, int64_t ts) {
-  static const bool force_generic = [] {
-    const char* e = getenv("QX_FORCE_GENERIC");
-    return e && e[0] == '1';
-  }();
-  if (force_generic) return false;
+  if (options().force_generic) return false;
   switch (a.format) {
     case F_Q8_0: return launch_lmh_stream<F_Q8_0>(st, a, pv, pi, pl, ts);
     case F_Q4_0: return launch_lmh_stream<F_Q4_0>(st, a, pv, pi, pl, ts);
@@ -707,78 +777,6 @@ static bool launch_lmh_stream_any(cudaStream_t st, const LmHeadArgs& a, float* p
 // ------------------------------------------------------------------------------------------
 // Stage 2
 // ------------------------------------------------------------------------------------------
-struct BlockScratch {
-  float fv[32];
-  int iv[32];
-  unsigned hist[256];
-  unsigned u[8];
-};
-
-__device__ __forceinline__ void block_argmax(float& v, int& id, BlockScratch& s) {
-  warp_argmax(v, id);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) { s.fv[warp] = v; s.iv[warp] = id; }
-  __syncthreads();
-  v = lane < nw ? s.fv[lane] : QX_NEG_INF;
-  id = lane < nw ? s.iv[lane] : 0x7fffffff;
-  warp_argmax(v, id);
-}
-__device__ __forceinline__ float block_sum(float v, BlockScratch& s) {
-  v = warp_sum(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) s.fv[warp] = v;
-  __syncthreads();
-  v = lane < nw ? s.fv[lane] : 0.f;
-  return warp_sum(v);
-}
-// sum of f and bitwise OR of u over the block, one pair of barriers
-__device__ __forceinline__ void block_sum_or(float& f, unsigned& u, BlockScratch& s) {
-  f = warp_sum(f);
-  u = __reduce_or_sync(0xffffffffu, u);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) { s.fv[warp] = f; s.iv[warp] = (int)u; }
-  __syncthreads();
-  f = warp_sum(lane < nw ? s.fv[lane] : 0.f);
-  u = __reduce_or_sync(0xffffffffu, lane < nw ? (unsigned)s.iv[lane] : 0u);
-}
-__device__ __forceinline__ float block_max(float v, BlockScratch& s) {
-  v = warp_max(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) s.fv[warp] = v;
-  __syncthreads();
-  v = lane < nw ? s.fv[lane] : QX_NEG_INF;
-  return warp_max(v);
-}
-__device__ __forceinline__ int block_min_int(int v, BlockScratch& s) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, off));
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) s.iv[warp] = v;
-  __syncthreads();
-  v = lane < nw ? s.iv[lane] : 0x7fffffff;
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, off));
-  return v;
-}
-__device__ __forceinline__ unsigned block_sum_u(unsigned v, BlockScratch& s) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) s.iv[warp] = (int)v;
-  __syncthreads();
-  v = lane < nw ? (unsigned)s.iv[lane] : 0u;
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  return v;
-}
-
-// order-preserving key: larger float <=> larger key; -0 and +0 share a key
 
 __global__ void __launch_bounds__(LMH_RED_THREADS)
 lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict__ cand_id,
@@ -1029,7 +1027,13 @@ void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t
   if (mode == 3 && (size_t)ncand * shards * 8 <= 200 * 1024) {
     cache_elems = (int)(ncand * shards);
     smem = (size_t)cache_elems * 8;
-    cudaFuncSetAttribute(lmh_reduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      cudaFuncSetAttribute(lmh_reduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      attr_set[dev] = true;
+    }
   }
   const long long stride_l = shard_stride > 0 ? shard_stride : (long long)T * (nlse > 0 ? nlse : 1);
   lmh_reduce_kernel<<<(unsigned)T, LMH_RED_THREADS, smem, st>>>(

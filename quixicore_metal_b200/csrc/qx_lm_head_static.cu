@@ -1,5 +1,6 @@
-// lm_head_sample for callers that must not allocate: the stage-1 partials live in a fixed
-// device array that is part of this library's image instead of a caller-provided workspace.
+// lm_head_sample for callers that must not allocate: every byte of global scratch the two stages
+// use (partials, prepared hidden rows, row scales, flags, exchange slots) lives in a fixed device
+// array that is part of this library's image instead of a caller-provided workspace.
 #include <mutex>
 
 #include "qx_common.cuh"
@@ -44,19 +45,26 @@ extern "C" qx_status qx_cuda_lm_head_sample_q_noalloc(void* stream, const void* 
                                                       double temperature, uint32_t seed,
                                                       double top_p) {
   static const char* op = "quantized_lm_head_sample.noalloc";
-  const size_t need = qx_cuda_lm_head_workspace_bytes(T, V, mode, topk);
-  if (need > kStaticScratchBytes)
-    return fail(QX_INSUFFICIENT_WORKSPACE, op,
-                "T x tiles x k partials exceed the built-in scratch "
-                "(QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES); use qx_cuda_lm_head_sample_q with a "
-                "caller workspace");
+  // Everything the two stages keep in global memory besides inputs and outputs comes out of the
+  // built-in array: the stage-1 partials, then the prepared hidden rows, their row scales and the
+  // release flags; what is left serves as exchange slots for tiles shared between thread blocks
+  // (with none left, tiles are simply not shared).  The K-dependent part makes the limit depend
+  // on T * K as well as on T * tiles * k.
+  if (T > 0 && V > 0 && K > 0) {
+    const size_t need = qx_cuda_lm_head_workspace_bytes(T, V, K, mode, topk) - lm_head_scratch_full_bytes(T, K) +
+                        lm_head_scratch_min_bytes(T, K);
+    if (need > kStaticScratchBytes)
+      return fail(QX_INSUFFICIENT_WORKSPACE, op,
+                  "partials + prepared hidden rows exceed the built-in scratch "
+                  "(QX_CUDA_LM_HEAD_STATIC_SCRATCH_BYTES); use qx_cuda_lm_head_sample_q with a "
+                  "caller workspace");
+  }
   void* scratch = nullptr;
-  // Argument errors are reported before the device is touched; the shared entry validates again.
-  if (T > 0 && V > 0 && h && wq && ids) {
+  // Argument errors are reported before the device is touched; the shared body validates again.
+  if (T > 0 && V > 0 && K > 0 && h && wq && ids) {
     const qx_status st = scratch_for_current_device(op, &scratch);
     if (st.code != QX_OK) return st;
   }
-  return qx_cuda_lm_head_sample_q(stream, h, wq, bias, ids, scratch ? scratch : (void*)ids,
-                                  scratch ? kStaticScratchBytes : 0, T, V, K, format, dtype, mode,
-                                  topk, temperature, seed, top_p);
+  return lm_head_sample_on(op, stream, h, wq, bias, ids, scratch, scratch ? kStaticScratchBytes : 0,
+                           true, T, V, K, format, dtype, mode, topk, temperature, seed, top_p);
 }

@@ -20,8 +20,6 @@
 //     residual, storing 32 consecutive output channels per warp instruction.
 // Every wait on an mbarrier is bounded; on expiry the CTA raises the device error flag, stops
 // issuing work, frees its tensor memory and returns.
-#include <cstdlib>
-
 #include "qx_formats.cuh"
 #include "qx_kernels.h"
 #include "qx_stream.cuh"
@@ -269,6 +267,7 @@ struct ProjEpi {
     const OT* bias0; const OT* bias1; const OT* residual;
     void* y;
     int N, activation, use_bias, use_residual, raw;
+    uint8_t* mx_blocks;     // fused MXFP8 output rows (N % 32 == 0): a warp holds one 32-channel block per row
   };
   static constexpr bool DUAL = DUAL_;
   __device__ __forceinline__ static void run(const Args& a, const TcItem& it) {
@@ -292,7 +291,11 @@ struct ProjEpi {
           if (m < it.m_count) {
             const float rs = it.rowscale[it.m_base + m];
             const float gv = __uint_as_float(g[i]) * rs + gb, uv = __uint_as_float(u[i]) * rs + ub;
-            reinterpret_cast<OT*>(a.y)[(size_t)(it.m_base + m) * a.N + n] = from_f32<OT>(silu(gv) * uv);
+            const OT out = from_f32<OT>(silu(gv) * uv);
+            reinterpret_cast<OT*>(a.y)[(size_t)(it.m_base + m) * a.N + n] = out;
+            if (a.mx_blocks)
+              mxfp8_block_store(to_f32<OT>(out), it.lane,
+                                a.mx_blocks + ((size_t)(it.m_base + m) * (a.N >> 5) + (n >> 5)) * 33);
           }
         }
       }
@@ -316,7 +319,11 @@ struct ProjEpi {
               } else {
                 float val = apply_act(dot + bv, a.activation);
                 if (a.use_residual) val += to_f32<OT>(a.residual[o]);
-                reinterpret_cast<OT*>(a.y)[o] = from_f32<OT>(val);
+                const OT out = from_f32<OT>(val);
+                reinterpret_cast<OT*>(a.y)[o] = out;
+                if (a.mx_blocks)
+                  mxfp8_block_store(to_f32<OT>(out), it.lane,
+                                    a.mx_blocks + ((size_t)(it.m_base + m) * (a.N >> 5) + (n >> 5)) * 33);
               }
             }
           }
@@ -345,27 +352,25 @@ static bool launch_pipeline_bn(cudaStream_t st, const GemvArgs& a, int* err) {
   }
   const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
   CUtensorMap map0, map1;
-  if (!make_weight_map(&map0, a.w0, a.N, row_bytes, C::BOX)) return false;
-  if (DUAL) { if (!make_weight_map(&map1, a.w1, a.N, row_bytes, C::BOX)) return false; }
+  if (!cached_weight_map(&map0, a.w0, a.N, row_bytes, C::BOX)) return false;
+  if (DUAL) { if (!cached_weight_map(&map1, a.w1, a.N, row_bytes, C::BOX)) return false; }
   else map1 = map0;
   const int groups = (int)((a.M + BN - 1) / BN);
   const size_t img_bytes = ((size_t)groups * BN * a.K * 2 + 255) & ~(size_t)255;
-  bool must_free = false;
-  void* scratch = stream_scratch(st, img_bytes + (size_t)a.M * 4, &must_free);
-  if (!scratch) return false;
-  __half* ximg = (__half*)scratch;
-  float* rowscale = (float*)((char*)scratch + img_bytes);
+  if (!a.scratch || a.scratch_bytes < img_bytes + (((size_t)a.M * 4 + 255) & ~(size_t)255)) return false;
+  __half* ximg = (__half*)a.scratch;
+  float* rowscale = (float*)((char*)a.scratch + img_bytes);
   launch_prep_activations(st, a.x, a.dtype, ximg, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM, BN);
   note_launch();
   const int item_rows = DUAL ? 128 : 256;
   const long long items = (long long)((a.N + item_rows - 1) / item_rows) * groups;
   const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
   const typename Epi::Args ea{(const OT*)a.bias0, (const OT*)a.bias1, (const OT*)a.residual, a.y, (int)a.N,
-                              a.activation, a.use_bias, a.use_residual, a.out_f32};
+                              a.activation, a.use_bias, a.use_residual, a.out_f32,
+                              (a.out_quant == OQ_MXFP8 && !a.out_f32 && a.N % 32 == 0) ? (uint8_t*)a.q_codes : nullptr};
   tc_pipeline_kernel<FMT, BN, Epi><<<grid, LTC_WARPS * 32, S::TOTAL, st>>>(
       map0, map1, ximg, rowscale, (int)a.M, (int)a.N, (int)a.K, 1, err, ea);
   note_launch();
-  if (must_free) cudaFreeAsync(scratch, st);
   return true;
 }
 
@@ -386,11 +391,24 @@ static bool pipeline_ok(const GemvArgs& a) {
   if (a.M <= 16 || a.format == F_Q6_K || a.K % 128 != 0 || a.N < 128) return false;
   const size_t row_bytes = (size_t)(a.K / block_k_of(a.format)) * block_bytes_of(a.format);
   if (row_bytes % 16 != 0 || ((uintptr_t)a.w0 & 15) != 0 || (a.w1 && ((uintptr_t)a.w1 & 15) != 0)) return false;
-  static const bool enabled = [] {
-    const char* e = getenv("QX_TC_PIPELINE");
-    return !(e && e[0] == '0');
-  }();
-  return enabled;
+  return options().tc_pipeline;
+}
+
+// Scratch of the tcgen05 paths: the activation image + row scales of the pipeline, or the two fp32
+// projections of a SwiGLU pair on the term-split kernel.
+size_t tc_scratch_bytes(const GemvArgs& a) {
+  if (!tc_path_ok(a)) return 0;
+  size_t need = 0;
+  if (pipeline_ok(a)) {
+    const int BN = a.M <= 32 ? 32 : 64;
+    const size_t groups = (size_t)((a.M + BN - 1) / BN);
+    need = ((groups * BN * a.K * 2 + 255) & ~(size_t)255) + (((size_t)a.M * 4 + 255) & ~(size_t)255);
+  }
+  if (a.w1 && a.dtype == QX_DTYPE_BF16 && a.K % 256 == 0) {
+    const size_t legacy = 2 * (size_t)a.M * a.N * sizeof(float);
+    if (legacy > need) need = legacy;
+  }
+  return need;
 }
 
 template <typename OT>
@@ -451,21 +469,25 @@ void launch_swiglu_combine(cudaStream_t st, const float* gate, const float* up, 
   note_launch();
 }
 
-bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a) {
+bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a, bool* fused_quant) {
   int* err = device_error_flag();
   if (!err) return false;
+  if (fused_quant) *fused_quant = false;
   if (pipeline_ok(a)) {
     const bool ok = a.out_f32 ? launch_pipeline<float>(st, a, err)       // OT only types bias / residual, unused here
                   : a.dtype == QX_DTYPE_F16 ? launch_pipeline<__half>(st, a, err)
                                             : launch_pipeline<__nv_bfloat16>(st, a, err);
-    if (ok) return true;
+    if (ok) {
+      if (fused_quant) *fused_quant = true;
+      return true;
+    }
   }
   if (a.dtype != QX_DTYPE_BF16 || a.K % 256 != 0) return false;
   if (a.w1) {
     // SwiGLU at batch > 16: two fp32 projections into stream-ordered scratch, then the gate
     const size_t bytes = (size_t)a.M * a.N * sizeof(float);
-    float* tmp = nullptr;
-    if (cudaMallocAsync((void**)&tmp, 2 * bytes, st) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (!a.scratch || a.scratch_bytes < 2 * bytes) return false;
+    float* tmp = (float*)a.scratch;
     GemvArgs g = a;
     g.w1 = nullptr; g.bias0 = nullptr; g.bias1 = nullptr; g.residual = nullptr;
     g.use_bias = 0; g.use_residual = 0; g.activation = 0; g.out_f32 = 1;
@@ -474,7 +496,6 @@ bool launch_gemm_tc(cudaStream_t st, const GemvArgs& a) {
     g.w0 = a.w1; g.y = tmp + (size_t)a.M * a.N;
     ok = ok && launch_tc_fmt<float>(st, g, err);
     if (ok) launch_swiglu_combine(st, tmp, tmp + (size_t)a.M * a.N, a.bias0, a.bias1, a.y, a.M, a.N, a.dtype, a.use_bias);
-    cudaFreeAsync(tmp, st);
     return ok;
   }
   if (a.out_f32) return launch_tc_fmt<float>(st, a, err);

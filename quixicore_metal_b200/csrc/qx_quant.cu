@@ -11,30 +11,6 @@
 
 namespace qx {
 
-__device__ __forceinline__ uint32_t e4m3_encode(float x) {
-  const uint32_t sign = (x < 0.0f) ? 0x80u : 0u;
-  const float a = fabsf(x);
-  if (!(a < 448.0f)) return sign | 0x7Eu;                 // overflow and NaN saturate
-  const uint32_t bits = __float_as_uint(a);
-  const int E = (int)((bits >> 23) & 0xFFu) - 127;
-  if (E < -6) {                                           // e4m3 subnormal range: steps of 2^-9
-    const int m = (int)roundf(a * 512.0f);           // half away from zero, exact
-    if (m <= 0) return sign;
-    return sign | (uint32_t)(m >= 8 ? 8 : m);
-  }
-  int mant = (int)(((bits & 0x7FFFFFu) + 0x80000u) >> 20);
-  int exp = E + 7;
-  if (mant >= 8) { mant = 0; exp += 1; }
-  if (exp > 15 || (exp == 15 && mant >= 7)) return sign | 0x7Eu;
-  return sign | ((uint32_t)exp << 3) | (uint32_t)mant;
-}
-
-__device__ __forceinline__ int int8_encode(float x) {
-  float r = roundf(x);                                    // half away from zero
-  r = fminf(fmaxf(r, -127.0f), 127.0f);
-  return (int)r;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256)
 quantize_per_token_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes,
@@ -58,14 +34,6 @@ quantize_per_token_kernel(const T* __restrict__ x, uint8_t* __restrict__ codes,
   if (threadIdx.x == 0) scale[blockIdx.x] = s;
 }
 
-// exact ceil(log2(q)) for a positive finite fp32 q
-__device__ __forceinline__ int ceil_log2(float q) {
-  const uint32_t bits = __float_as_uint(q);
-  int e = (int)((bits >> 23) & 0xFFu) - 127;
-  if (bits & 0x7FFFFFu) e += 1;
-  return e;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256)
 quantize_mxfp8_rows_kernel(const T* __restrict__ x, uint8_t* __restrict__ blocks,
@@ -74,17 +42,7 @@ quantize_mxfp8_rows_kernel(const T* __restrict__ x, uint8_t* __restrict__ blocks
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long g = warp; g < groups; g += nwarps) {
-    const float v = to_f32<T>(x[g * 32 + lane]);
-    const float amax = warp_max(fabsf(v));
-    int code = 127;
-    if (amax > 0.0f) {
-      const int e = ceil_log2(fmaxf(amax, 1e-10f) / 448.0f);
-      code = min(max(e + 127, 1), 254);
-    }
-    const float inv = 1.0f / __uint_as_float((uint32_t)code << 23);
-    uint8_t* b = blocks + g * 33;
-    b[1 + lane] = (uint8_t)e4m3_encode(v * inv);
-    if (lane == 0) b[0] = (uint8_t)code;
+    mxfp8_block_store(to_f32<T>(x[g * 32 + lane]), lane, blocks + g * 33);
   }
 }
 

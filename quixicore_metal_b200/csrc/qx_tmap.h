@@ -40,4 +40,8 @@ inline bool make_weight_map(CUtensorMap* map, const void* w, int64_t V, size_t r
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same through a small cache keyed by (device, base, rows, row bytes, box): see qx_scratch.cu.
+bool cached_weight_map(CUtensorMap* map, const void* w, int64_t rows, size_t row_bytes, int box_bytes,
+                       int box_rows = 128);
+
 }  // namespace qx

@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from .tk import _LM_HEAD_MODES, _LM_QUANT_BLOCK_K
-from .tk_torch import _DT, _check, _check_lm_head, _ptr, _stream
+from .tk_torch import _DT, _check, _check_lm_head, _ptr, _same_device, _stream, _workspace
 
 TILE_V = 256
 
@@ -66,6 +66,8 @@ def lm_head_shard_partials(h, wq_local, bias_local, vocab_offset: int, max_tiles
     V_local = wq_local.shape[0]
     K = wq_local.shape[1] * _LM_QUANT_BLOCK_K[fmt]
     _check_lm_head(h, wq_local, bias_local, V_local, K, fmt, m, kk, float(temperature), 1.0)
+    if out is not None:
+        _same_device("lm_head_shard_partials", h, out)
     T = h.size(0)
     C, L = candidate_layout(m, kk, max_tiles)
     lib = _lib.lib()
@@ -81,8 +83,8 @@ def lm_head_shard_partials(h, wq_local, bias_local, vocab_offset: int, max_tiles
         val = out[: T * C]
         idt = out[T * C: 2 * T * C]
         lse = out[2 * T * C:] if L else None
-        nbytes = lib.qx_cuda_lm_head_shard_workspace_bytes(T, V_local, m, max(kk, 1))
-        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=h.device)
+        nbytes = lib.qx_cuda_lm_head_shard_workspace_bytes(T, V_local, K, m, max(kk, 1))
+        ws = _workspace(h.device, nbytes)
         _lib.check(lib.qx_cuda_lm_head_shard_partials_q(
             _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(val), _ptr(idt), _ptr(lse), _ptr(ws),
             nbytes, T, V_local, K, int(vocab_offset), int(max_tiles), fmt.encode(), _DT[h.dtype], m,
@@ -142,6 +144,12 @@ class VocabParallelLMHead:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.V, self.fmt = int(V), fmt
+        # every rank must own at least one 256-row tile: an empty shard would fail its argument
+        # checks while its peers already wait inside the all-gather
+        tiles = (self.V + TILE_V - 1) // TILE_V
+        if tiles < self.world:
+            raise ValueError(f"VocabParallelLMHead: a vocabulary of {self.V} rows has {tiles} tiles of "
+                             f"{TILE_V} rows, fewer than the {self.world} ranks; use fewer ranks")
         self.begin, self.end = vocab_shard_bounds(self.V, self.world)[self.rank]
         _check(wq_local.shape[0] == self.end - self.begin,
                "VocabParallelLMHead: wq_local must hold this rank's rows of vocab_shard_bounds")

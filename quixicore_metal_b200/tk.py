@@ -2,9 +2,9 @@
 
 Mirrors the routers of bindings/python/tk/__init__.py: `decode_linear_epilogue` (:3694-3748),
 `decode_swiglu` (:3751-3793), `lm_head_sample` with `format=` (:2357-2412) and the output-quant
-helper (:3684-3691): same keyword names, defaults and ValueError texts.  Only packed formats are
-served here; the dense-weight routes of the reference call the framework matmul and are not part
-of this backend.
+helper (:3684-3691): same keyword names, defaults and ValueError texts.  The projections serve
+packed formats only (the reference routes dense weights to the framework matmul); lm_head_sample
+also has the reference's dense routes.
 """
 from __future__ import annotations
 
@@ -23,35 +23,30 @@ def quantize_per_token_int8(x):
     return _tt.quantize_per_token_int8(x)
 
 
-def _decode_quantize_output(output, output_quant):
-    if output_quant is None:
-        return output
-    if output_quant == "fp8":
-        return quantize_per_token_fp8(output)
-    if output_quant == "int8":
-        return quantize_per_token_int8(output)
-    if output_quant == "mxfp8":       # extension: packed MXFP8 rows (e4m3 codes, e8m0 per 32)
-        return _tt.quantize_mxfp8_rows(output)
-    raise ValueError("output_quant must be None, 'fp8', 'int8', or 'mxfp8'")
+_OUTPUT_QUANTS = (None, "fp8", "int8", "mxfp8")   # 'mxfp8' (packed rows, e8m0 per 32) is an extension
 
 
 def decode_linear_epilogue(x, weight, bias=None, residual=None, activation="none", format=None,
                            output_quant=None, use_kernel=None):
     """residual + activation(x @ dequant(weight).T + bias), fp32 accumulation, one rounding to
-    x.dtype.  activation: none / gelu (erf) / silu.  output_quant composes the per-token fp8 /
-    int8 quantizer (returns (codes, scale)) or, as an extension, 'mxfp8' packed rows."""
+    x.dtype.  activation: none / gelu (erf) / silu.  output_quant applies the per-token fp8 /
+    int8 quantizer to the rounded output (returns (codes, scale)) or, as an extension, packs it as
+    'mxfp8' rows - inside the same native call (the reference composes a second operator,
+    bindings/python/tk/__init__.py:3684-3691)."""
     if activation not in _ACTIVATIONS:
         raise ValueError("activation must be 'none', 'gelu', or 'silu'")
+    if output_quant not in _OUTPUT_QUANTS:
+        raise ValueError("output_quant must be None, 'fp8', 'int8', or 'mxfp8'")
     if format is None:
         raise ValueError("decode_linear_epilogue: this backend serves packed weights only; "
                          "pass format=q4_0/q8_0/q6_K/mxfp8/nvfp4/mxfp4")
     if use_kernel is not None and not use_kernel:
         raise ValueError("decode_linear_epilogue: use_kernel=False requires a dense weight")
     use_bias, use_residual = bias is not None, residual is not None
-    out = _tt.decode_linear_epilogue(x, weight, bias if use_bias else x,
-                                     residual if use_residual else x, str(format),
-                                     _ACTIVATIONS[activation], use_bias, use_residual)
-    return _decode_quantize_output(out, output_quant)
+    return _tt.decode_linear_epilogue(x, weight, bias if use_bias else x,
+                                      residual if use_residual else x, str(format),
+                                      _ACTIVATIONS[activation], use_bias, use_residual,
+                                      output_quant=output_quant)
 
 
 def decode_swiglu(x, gate_weight, up_weight, gate_bias=None, up_bias=None, format=None,
@@ -59,27 +54,66 @@ def decode_swiglu(x, gate_weight, up_weight, gate_bias=None, up_bias=None, forma
     """silu(gate) * up over two packed projections sharing the activation reads."""
     if (gate_bias is None) != (up_bias is None):
         raise ValueError("decode_swiglu: gate_bias and up_bias must both be present or omitted")
+    if output_quant not in _OUTPUT_QUANTS:
+        raise ValueError("output_quant must be None, 'fp8', 'int8', or 'mxfp8'")
     if format is None:
         raise ValueError("decode_swiglu: this backend serves packed weights only; "
                          "pass format=q4_0/q8_0/q6_K/mxfp8/nvfp4/mxfp4")
     if use_kernel is not None and not use_kernel:
         raise ValueError("decode_swiglu: use_kernel=False requires dense weights")
     use_bias = gate_bias is not None
-    out = _tt.decode_swiglu(x, gate_weight, up_weight, gate_bias if use_bias else x,
-                            up_bias if use_bias else x, str(format), use_bias)
-    return _decode_quantize_output(out, output_quant)
+    return _tt.decode_swiglu(x, gate_weight, up_weight, gate_bias if use_bias else x,
+                             up_bias if use_bias else x, str(format), use_bias,
+                             output_quant=output_quant)
+
+
+def argmax_sample(logits):
+    return _tt.argmax_sample(logits)
+
+
+def sample_categorical(logits, temperature=1.0, seed=0):
+    return _tt.sample_categorical(logits, temperature, seed)
+
+
+def top_k_sample(logits, k, temperature=1.0, seed=0):
+    return _tt.top_k_sample(logits, k, temperature, seed)
+
+
+def top_p_sample(logits, p, temperature=1.0, seed=0):
+    return _tt.top_p_sample(logits, p, temperature, seed)
+
+
+def _lm_head_sample_dense(h, W, mode, k, temperature, seed, bias, fused, top_p):
+    """The dense routes of the reference router (bindings/python/tk/__init__.py:2413-2451): the
+    fused no-materialisation kernel when asked for (argmax / categorical / topk), otherwise the
+    framework matmul followed by the samplers of this backend."""
+    import torch
+    if fused and mode != "topp":
+        b = bias if bias is not None else torch.zeros(1, dtype=torch.float32, device=h.device)
+        return _tt.lm_head_sample(h, W, b, _LM_HEAD_MODES[mode], int(k), float(temperature), int(seed))
+    logits = torch.matmul(h, W.transpose(-1, -2))
+    if bias is not None:
+        logits = logits + bias.to(logits.dtype)
+    if mode == "argmax":
+        return argmax_sample(logits)
+    if mode == "categorical":
+        return sample_categorical(logits, temperature=temperature, seed=seed)
+    if mode == "topk":
+        return top_k_sample(logits, k, temperature=temperature, seed=seed)
+    return top_p_sample(logits, top_p, temperature=temperature, seed=seed)
 
 
 def lm_head_sample(h, W, mode="argmax", k=0, temperature=1.0, seed=0, bias=None, fused=False,
                    format=None, top_p=0.9):
-    """One token id per row of h over a packed (V, K/block_k, block_bytes) head, without ever
-    writing the (T, V) logits.  mode: argmax / categorical / topk / topp; k defaults to 32 for
+    """One token id per row of h.  With format=: over a packed (V, K/block_k, block_bytes) head,
+    without ever writing the (T, V) logits.  Without: W is dense (V, K) and the reference's dense
+    routes apply (matmul + sampler by default, the fused kernel with fused=True).  mode: argmax / categorical / topk / topp; k defaults to 32 for
     topk / topp; the noise is keyed by the global vocab id, so the draw equals the unfused
     sampler on the same logits and seed."""
     if mode not in _LM_HEAD_MODES:
         raise ValueError(f"lm_head_sample: mode must be one of {list(_LM_HEAD_MODES)}")
     if format is None:
-        raise ValueError("lm_head_sample: this backend serves packed weights only; pass format=")
+        return _lm_head_sample_dense(h, W, mode, k, temperature, seed, bias, fused, top_p)
     if format not in _LM_QUANT_BLOCK_K:
         raise ValueError(f"lm_head_sample: quant format must be one of {list(_LM_QUANT_BLOCK_K)}")
     kk = int(k) if int(k) > 0 else (32 if mode in ("topk", "topp") else 0)

@@ -31,6 +31,32 @@ def _check(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
+def _same_device(name: str, first, *others) -> None:
+    """Every tensor of a call must live on the device of its first operand: the kernels run on that
+    device and build TMA descriptors over the raw pointers, so a tensor from another GPU would be
+    an illegal address (or a silent peer read).  Placeholders passed for absent operands count too."""
+    for t in others:
+        if t is not None and t.device != first.device:
+            raise RuntimeError(f"{name}: all tensors must be on the same device "
+                               f"(got {first.device} and {t.device})")
+
+
+_WS = {}
+
+
+def _workspace(device, nbytes: int):
+    """Scratch tensor for calls on the current stream of `device`, reused by later calls on the same
+    stream (they are ordered, so sharing it is safe) and grown geometrically."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20, 0 if ws is None else 2 * ws.numel())
+        ws = torch.empty((size,), dtype=torch.uint8, device=device)
+        _WS[key] = ws       # a smaller predecessor stays alive while enqueued work may read it:
+        #                     the caching allocator only reuses its block for this same stream
+    return ws
+
+
 def _check_weight(x, weight, fmt: str, name: str) -> int:
     """The reference's check_decode_epilogue_weight (torch_kernels.mm:6376-6405) for CUDA."""
     _check(x.is_cuda and weight.is_cuda and x.dtype in _DT and x.dim() == 2 and x.size(0) > 0
@@ -45,13 +71,37 @@ def _check_weight(x, weight, fmt: str, name: str) -> int:
     return weight.size(0)
 
 
+def _quant_outputs(x, B, N, output_quant):
+    """Buffers for a fused output quantisation: (kind, codes, scale)."""
+    kind = _lib.OUT_QUANT.get(output_quant, -1)
+    _check(kind >= 0, "output_quant must be None, 'fp8', 'int8', or 'mxfp8'")
+    if kind == 0:
+        return 0, None, None
+    if kind == 3:
+        _check(N % 32 == 0, "output_quant='mxfp8' needs N to be a multiple of 32")
+        return 3, torch.empty((B, N // 32, 33), dtype=torch.uint8, device=x.device), None
+    codes = torch.empty((B, N), dtype=torch.uint8 if kind == 1 else torch.int8, device=x.device)
+    return kind, codes, torch.empty((B,), dtype=torch.float32, device=x.device)
+
+
+def _quant_result(out, kind, codes, scale):
+    if kind == 0:
+        return out
+    return codes if kind == 3 else (codes, scale)
+
+
 def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
-                           use_bias=False, use_residual=False):
+                           use_bias=False, use_residual=False, *, output_quant=None):
     """Packed decode linear with fused bias, activation and residual; returns (B,N) in x.dtype.
-    Absent bias / residual are passed as placeholders and ignored when their flag is false."""
+    Absent bias / residual are passed as placeholders and ignored when their flag is false.
+    output_quant (keyword only, not in the reference's positional signature): 'fp8' / 'int8' return
+    (codes, scale) of the per-token quantizer applied to the rounded output, 'mxfp8' the packed
+    MXFP8 rows, all inside the same call."""
     fmt, activation = str(format), int(activation)
     _check(0 <= activation <= 2, "decode_linear_epilogue: activation must be 0, 1, or 2")
     N = _check_weight(x, weight, fmt, "decode_linear_epilogue")
+    _same_device("decode_linear_epilogue", x, weight, bias if use_bias else None,
+                 residual if use_residual else None)
     B, K = x.shape
     _check(not use_bias or (bias.is_cuda and bias.dim() == 1 and bias.size(0) == N
                             and bias.dtype == x.dtype),
@@ -64,10 +114,12 @@ def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
         bc = bias.contiguous() if use_bias else None
         rc = residual.contiguous() if use_residual else None
         out = torch.empty((B, N), dtype=x.dtype, device=x.device)
+        kind, codes, scale = _quant_outputs(x, B, N, output_quant)
         _lib.check(_lib.lib().qx_cuda_decode_linear_epilogue(
             _stream(), _ptr(xc), _ptr(wc), _ptr(bc), _ptr(rc), _ptr(out), B, K, N, fmt.encode(),
-            _DT[x.dtype], activation, int(bool(use_bias)), int(bool(use_residual))))
-    return out
+            _DT[x.dtype], activation, int(bool(use_bias)), int(bool(use_residual)),
+            kind, _ptr(codes), _ptr(scale), None, 0))
+    return _quant_result(out, kind, codes, scale)
 
 
 def decode_linear_partial(x, weight, format):
@@ -75,22 +127,27 @@ def decode_linear_partial(x, weight, format):
     row-parallel (K-split) linear, summed over ranks by the caller."""
     fmt = str(format)
     N = _check_weight(x, weight, fmt, "decode_linear_partial")
+    _same_device("decode_linear_partial", x, weight)
     B, K = x.shape
     with torch.cuda.device(x.device):
         xc, wc = x.contiguous(), weight.contiguous()
         out = torch.empty((B, N), dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().qx_cuda_decode_linear_partial(
-            _stream(), _ptr(xc), _ptr(wc), _ptr(out), B, K, N, fmt.encode(), _DT[x.dtype]))
+            _stream(), _ptr(xc), _ptr(wc), _ptr(out), B, K, N, fmt.encode(), _DT[x.dtype], None, 0))
     return out
 
 
-def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_bias=False):
-    """Packed gate/up decode projections with fused SwiGLU: silu(gate.x+gb) * (up.x+ub)."""
+def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_bias=False, *,
+                  output_quant=None):
+    """Packed gate/up decode projections with fused SwiGLU: silu(gate.x+gb) * (up.x+ub).
+    output_quant: as in decode_linear_epilogue."""
     fmt = str(format)
     N = _check_weight(x, gate_weight, fmt, "decode_swiglu")
     up_N = _check_weight(x, up_weight, fmt, "decode_swiglu")
     _check(up_N == N and up_weight.shape == gate_weight.shape,
            "decode_swiglu: gate and up weights must have identical shapes")
+    _same_device("decode_swiglu", x, gate_weight, up_weight, gate_bias if use_bias else None,
+                 up_bias if use_bias else None)
     _check(not use_bias or (gate_bias.is_cuda and up_bias.is_cuda and gate_bias.dtype == x.dtype
                             and up_bias.dtype == x.dtype and gate_bias.dim() == 1
                             and up_bias.dim() == 1 and gate_bias.size(0) == N
@@ -102,10 +159,11 @@ def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_
         gb = gate_bias.contiguous() if use_bias else None
         ub = up_bias.contiguous() if use_bias else None
         out = torch.empty((B, N), dtype=x.dtype, device=x.device)
+        kind, codes, scale = _quant_outputs(x, B, N, output_quant)
         _lib.check(_lib.lib().qx_cuda_decode_swiglu(
             _stream(), _ptr(xc), _ptr(gc), _ptr(uc), _ptr(gb), _ptr(ub), _ptr(out), B, K, N,
-            fmt.encode(), _DT[x.dtype], int(bool(use_bias))))
-    return out
+            fmt.encode(), _DT[x.dtype], int(bool(use_bias)), kind, _ptr(codes), _ptr(scale), None, 0))
+    return _quant_result(out, kind, codes, scale)
 
 
 def _quantize_per_token(x, kind: int, name: str):
@@ -150,6 +208,7 @@ def quantize_mxfp8_rows(x):
 def _check_lm_head(h, Wq, bias, V, K, fmt, mode, topk, temperature, top_p):
     _check(h.is_cuda and Wq.is_cuda and (bias is None or bias.is_cuda) and h.dtype in _DT,
            "lm_head_sample_q: inputs must be CUDA and h must be floating point")
+    _same_device("lm_head_sample_q", h, Wq, bias if (bias is not None and bias.numel() > 1) else None)
     _check(h.dim() == 2 and h.size(1) == K, "lm_head_sample_q: h must be (T, K)")
     _check(0 <= mode <= 3, "lm_head_sample_q: mode 0=argmax, 1=categorical, 2=topk, 3=topp")
     _check(temperature > 0.0, "lm_head_sample_q: temperature must be positive")
@@ -183,9 +242,74 @@ def lm_head_sample_q(h, Wq, bias, V, K, fmt, mode, topk, temperature, seed, top_
         bc = bias.to(torch.float32).contiguous() if use_bias else None
         out = torch.empty((T,), dtype=torch.int32, device=h.device)
         L = _lib.lib()
-        nbytes = L.qx_cuda_lm_head_workspace_bytes(T, V, mode, topk)
-        ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=h.device)
+        nbytes = L.qx_cuda_lm_head_workspace_bytes(T, V, K, mode, topk)
+        ws = _workspace(h.device, nbytes)
         _lib.check(L.qx_cuda_lm_head_sample_q(
             _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(out), _ptr(ws), nbytes, T, V, K,
             fmt.encode(), _DT[h.dtype], mode, topk, temperature, seed & 0xFFFFFFFF, top_p))
     return out
+
+
+def lm_head_sample(h, W, bias, mode, k, temperature, seed):
+    """Fused LM head + sampling over a dense head W (V,K) in h's dtype: one token id per row of h
+    without materialising the (T,V) logits.  mode 0 argmax, 1 categorical, 2 top-k.  bias (V,) or
+    a 1-element placeholder.  Returns int32 (T,)."""
+    mode, k, temperature, seed = int(mode), int(k), float(temperature), int(seed)
+    _check(h.is_cuda, "lm_head_sample: h must be a CUDA tensor")
+    _check(h.dim() == 2 and W.dim() == 2 and h.size(1) == W.size(1),
+           "lm_head_sample: h (T,K) and W (V,K) must share K")
+    _check(h.dtype in _DT and h.dtype == W.dtype,
+           "lm_head_sample: h/W must be the same float dtype (f32/f16/bf16)")
+    _check(0 <= mode <= 2, "lm_head_sample: mode must be 0/1/2")
+    use_bias = bias is not None and bias.numel() > 1
+    _same_device("lm_head_sample", h, W, bias if use_bias else None)
+    T, K = h.shape
+    V = W.size(0)
+    if mode == 2:
+        _check(1 <= k <= 64, "lm_head_sample: topk k must be in [1, 64]")
+        _check(k <= V, "lm_head_sample: topk k must be <= vocab size V")
+    with torch.cuda.device(h.device):
+        hc, wc = h.contiguous(), W.contiguous()
+        bc = bias.to(torch.float32).contiguous() if use_bias else None
+        out = torch.empty((T,), dtype=torch.int32, device=h.device)
+        L = _lib.lib()
+        nbytes = L.qx_cuda_lm_head_dense_workspace_bytes(T, V, mode, max(k, 1))
+        ws = _workspace(h.device, nbytes)
+        _lib.check(L.qx_cuda_lm_head_sample_dense(
+            _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(out), _ptr(ws), nbytes, T, V, K,
+            _DT[h.dtype], mode, max(k, 1), temperature, seed & 0xFFFFFFFF))
+    return out
+
+
+def _sample_logits(logits, kind: int, name: str, k=0, p=1.0, temperature=1.0, seed=0):
+    _check(logits.is_cuda and logits.dtype in _DT and logits.dim() >= 1 and logits.numel() > 0,
+           f"{name}: logits must be a non-empty CUDA fp32/fp16/bf16 tensor")
+    V = logits.size(-1)
+    rows = logits.numel() // V
+    with torch.cuda.device(logits.device):
+        lc = logits.contiguous()
+        out = torch.empty(logits.shape[:-1], dtype=torch.int32, device=logits.device)
+        _lib.check(_lib.lib().qx_cuda_sample_logits(
+            _stream(), _ptr(lc), _ptr(out), rows, V, _DT[logits.dtype], kind, int(k), float(p),
+            float(temperature), int(seed) & 0xFFFFFFFF))
+    return out
+
+
+def argmax_sample(logits):
+    """Greedy sampling: argmax token index over the last (vocab) axis, ties to the smaller index."""
+    return _sample_logits(logits, 0, "argmax_sample")
+
+
+def sample_categorical(logits, temperature=1.0, seed=0):
+    """Gumbel-max categorical sampling from softmax(logits / temperature)."""
+    return _sample_logits(logits, 1, "sample_categorical", temperature=temperature, seed=seed)
+
+
+def top_k_sample(logits, k, temperature=1.0, seed=0):
+    """Top-k sampling: Gumbel-max from softmax over the k highest logits (k <= 64)."""
+    return _sample_logits(logits, 2, "top_k_sample", k=k, temperature=temperature, seed=seed)
+
+
+def top_p_sample(logits, p, temperature=1.0, seed=0):
+    """Top-p (nucleus) sampling: Gumbel-max from the smallest top-probability set with mass >= p."""
+    return _sample_logits(logits, 3, "top_p_sample", p=p, temperature=temperature, seed=seed)

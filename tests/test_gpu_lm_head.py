@@ -225,7 +225,7 @@ def test_generic_dispatch_entry_point():
     call = capi.KernelCall(inputs=[hd, wd], outputs=[out],
                            attrs=dict(format="q4_0", mode=2, topk=8, temperature=0.7, seed=9))
     nbytes = _lib.lib().qx_cuda_workspace_bytes(b"quantized_lm_head_sample", call.ref())
-    assert nbytes == _lib.lib().qx_cuda_lm_head_workspace_bytes(3, 1000, 2, 8) > 0
+    assert nbytes == _lib.lib().qx_cuda_lm_head_workspace_bytes(3, 1000, 256, 2, 8) > 0
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     call.set_workspace(ws)
     _lib.check(_lib.lib().qx_cuda_dispatch(b"quantized_lm_head_sample", call.ref()))

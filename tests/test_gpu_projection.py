@@ -230,12 +230,14 @@ def test_error_behaviour_matches_reference_messages():
 
 
 @pytest.fixture(params=["tcgen05", "passes"])
-def large_batch_path(request, monkeypatch):
+def large_batch_path(request):
     """Batches of 17 - 64 rows have two device paths: the tcgen05 kernels, and the streaming kernel
     run in passes of 16 rows (chosen by default when the projection has few 256-row items).  The
-    library reads QX_STREAM_PASSES on every call: 0 = never, 2 = whenever the shape allows."""
-    monkeypatch.setenv("QX_STREAM_PASSES", "0" if request.param == "tcgen05" else "2")
-    return request.param
+    library option "stream_passes" picks one: 0 = never, 2 = whenever the shape allows."""
+    from quixicore_metal_b200 import _lib
+    _lib.set_option("stream_passes", 0 if request.param == "tcgen05" else 2)
+    yield request.param
+    _lib.set_option("stream_passes", 1)
 
 
 @pytest.mark.parametrize("M", [17, 32, 64, 100, 128, 129, 256])
