@@ -84,19 +84,22 @@ def _quant_outputs(x, B, N, output_quant):
     return kind, codes, torch.empty((B,), dtype=torch.float32, device=x.device)
 
 
-def _quant_result(out, kind, codes, scale):
+def _quant_result(out, kind, codes, scale, with_output=False):
     if kind == 0:
         return out
-    return codes if kind == 3 else (codes, scale)
+    q = codes if kind == 3 else (codes, scale)
+    return (out, q) if with_output else q
 
 
 def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
-                           use_bias=False, use_residual=False, *, output_quant=None):
+                           use_bias=False, use_residual=False, *, output_quant=None,
+                           with_output=False):
     """Packed decode linear with fused bias, activation and residual; returns (B,N) in x.dtype.
     Absent bias / residual are passed as placeholders and ignored when their flag is false.
     output_quant (keyword only, not in the reference's positional signature): 'fp8' / 'int8' return
     (codes, scale) of the per-token quantizer applied to the rounded output, 'mxfp8' the packed
-    MXFP8 rows, all inside the same call."""
+    MXFP8 rows, all inside the same call; with_output=True returns (output, quantised) instead, the
+    x.dtype output being the one the codes were made from."""
     fmt, activation = str(format), int(activation)
     _check(0 <= activation <= 2, "decode_linear_epilogue: activation must be 0, 1, or 2")
     N = _check_weight(x, weight, fmt, "decode_linear_epilogue")
@@ -119,7 +122,7 @@ def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
             _stream(), _ptr(xc), _ptr(wc), _ptr(bc), _ptr(rc), _ptr(out), B, K, N, fmt.encode(),
             _DT[x.dtype], activation, int(bool(use_bias)), int(bool(use_residual)),
             kind, _ptr(codes), _ptr(scale), None, 0))
-    return _quant_result(out, kind, codes, scale)
+    return _quant_result(out, kind, codes, scale, with_output)
 
 
 def decode_linear_partial(x, weight, format):
@@ -138,7 +141,7 @@ def decode_linear_partial(x, weight, format):
 
 
 def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_bias=False, *,
-                  output_quant=None):
+                  output_quant=None, with_output=False):
     """Packed gate/up decode projections with fused SwiGLU: silu(gate.x+gb) * (up.x+ub).
     output_quant: as in decode_linear_epilogue."""
     fmt = str(format)
@@ -163,7 +166,7 @@ def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_
         _lib.check(_lib.lib().qx_cuda_decode_swiglu(
             _stream(), _ptr(xc), _ptr(gc), _ptr(uc), _ptr(gb), _ptr(ub), _ptr(out), B, K, N,
             fmt.encode(), _DT[x.dtype], int(bool(use_bias)), kind, _ptr(codes), _ptr(scale), None, 0))
-    return _quant_result(out, kind, codes, scale)
+    return _quant_result(out, kind, codes, scale, with_output)
 
 
 def _quantize_per_token(x, kind: int, name: str):

@@ -85,8 +85,11 @@ def test_config3_fp4_sweep_with_mxfp8_output(wide_projection, M):
     rng = np.random.default_rng(300 + M)
     x = rounded(rng.standard_normal((M, K)), "bf16")
     xd = dev(x, "bf16")
-    y = tk.decode_linear_epilogue(xd, wd, format=fmt)
-    blocks = tk.decode_linear_epilogue(xd, wd, format=fmt, output_quant="mxfp8")
+    from quixicore_metal_b200 import tk_torch
+    # the bf16 output and the MXFP8 rows made from it, from ONE call (a second call may split the
+    # work differently and round a few outputs the other way)
+    y, blocks = tk_torch.decode_linear_epilogue(xd, wd, xd, xd, fmt, 0, False, False, output_quant="mxfp8",
+                                                with_output=True)
     assert blocks.shape == (M, N // 32, 33) and blocks.dtype == torch.uint8
     y_np = host(y)
     # bf16 output against the oracle on a sample of the rows (every row when there are few)

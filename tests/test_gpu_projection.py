@@ -194,12 +194,31 @@ def test_epilogue_output_quant_composition():
     for oq in ("fp8", "int8"):
         codes, scale = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), None,
                                                  format="nvfp4", output_quant=oq)
-        rc, rs = O.quantize_per_token(host(y), oq)
+        rc, rs = O.quantize_per_token(host(y), oq)          # same kernel, same split: same rounded output
         np.testing.assert_array_equal(host(codes).view(np.uint8), rc.view(np.uint8))
         np.testing.assert_array_equal(host(scale), rs)
+    from quixicore_metal_b200 import tk_torch
     blocks = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), dev(bias, "bf16"), None,
                                        format="nvfp4", output_quant="mxfp8")
-    np.testing.assert_array_equal(host(blocks), O.quantize_mxfp8_rows(host(y)))
+    assert blocks.shape == (4, 256 // 32, 33)
+    # fused MXFP8 rows against the output of the same call, for the streaming kernel (4 and 16 rows),
+    # 16-row passes / the tcgen05 pipeline (40 rows), SwiGLU, and the second-launch fallback (fp32)
+    for M, dtype in ((4, "bf16"), (16, "bf16"), (40, "bf16"), (40, "f16"), (3, "f32")):
+        xm, Wm, bm, rm = _inputs("nvfp4", M, 1024, 256, dtype, 300 + M)
+        ym, bl = tk_torch.decode_linear_epilogue(dev(xm, dtype), dev(Wm), dev(bm, dtype), dev(rm, dtype), "nvfp4",
+                                                 2, True, True, output_quant="mxfp8", with_output=True)
+        assert_close_dtype(host(ym), O.decode_linear_epilogue(xm, Wm, "nvfp4", bm, rm, 2, dtype), dtype)
+        np.testing.assert_array_equal(host(bl), O.quantize_mxfp8_rows(host(ym)))
+        _, Um, ubm, _ = _inputs("nvfp4", M, 1024, 256, dtype, 400 + M)
+        gm, bl = tk_torch.decode_swiglu(dev(xm, dtype), dev(Wm), dev(Um), dev(bm, dtype), dev(ubm, dtype), "nvfp4",
+                                        True, output_quant="mxfp8", with_output=True)
+        np.testing.assert_array_equal(host(bl), O.quantize_mxfp8_rows(host(gm)))
+        for oq in ("fp8", "int8"):
+            ym, (cq, sq) = tk_torch.decode_linear_epilogue(dev(xm, dtype), dev(Wm), dev(bm, dtype), dev(rm, dtype),
+                                                           "nvfp4", 0, True, False, output_quant=oq, with_output=True)
+            rc, rs = O.quantize_per_token(host(ym), oq)
+            np.testing.assert_array_equal(host(cq).view(np.uint8), rc.view(np.uint8))
+            np.testing.assert_array_equal(host(sq), rs)
     # int8 reconstruction bound of test_decode_linear.py:204-215
     codes, scale = tk.decode_linear_epilogue(dev(x, "bf16"), dev(Wq), None, None, format="nvfp4",
                                              activation="silu", output_quant="int8")
