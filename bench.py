@@ -142,28 +142,36 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 def cpu_composition(steps: int, warmup: int, sample_rows: int = 16384):
     """Times the composition on a bounded vocabulary slice with the fp32 weights resident (the
-    reference's own baseline style) and scales to the full vocabulary.  Returns tokens/s."""
+    reference's own baseline style) and scales to the full vocabulary.  Returns tokens/s.
+    All host cores are used whatever OMP_NUM_THREADS says (torch.distributed.run sets it to 1)."""
     from oracle import qx_oracle as O
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     rng = np.random.default_rng(SEED)
     W = (0.02 * rng.standard_normal((sample_rows, K_HID))).astype(np.float32)
     Wdq = torch.from_numpy(O.dequantize(FMT, O.synth_pack(FMT, W)))
     h = torch.from_numpy(rng.standard_normal((T_ROWS, K_HID)).astype(np.float32)).bfloat16()
-    times = []
+    times, mm_times = [], []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
         logits = (h.float() @ Wdq.T).numpy()
+        t1 = time.perf_counter()
         O.lm_head_sample_from_logits(logits, 3, k=TOPK, temperature=TEMP, seed=SEED, top_p=TOP_P)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
+            mm_times.append(t1 - t0)
     per_step_full = float(np.mean(times)) * (V_FULL / sample_rows)
+    share = float(np.mean(mm_times)) / float(np.mean(times))
     return T_ROWS / per_step_full, per_step_full, torch.get_num_threads(), \
-        f"{sample_rows} of {V_FULL} vocabulary rows, {T_ROWS} hidden rows, fp32 weights resident, scaled by rows"
+        (f"{sample_rows} of {V_FULL} vocabulary rows, {T_ROWS} hidden rows, fp32 weights resident, scaled by rows; "
+         f"matmul {share:.0%} / numpy sampler {1 - share:.0%} of the step")
 
 
 def run_reference(args, rank: int):
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    # every step is a bounded sample (16384 of 128256 vocabulary rows, ~0.1 s), so the requested
+    # step and warm-up counts are run as given
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     tps, per_step, cores, sample = cpu_composition(steps, warmup)
     line = {
         "impl": "reference", "metric": "lm_head_sample tokens/s", "value": tps, "unit": "tokens/s",
@@ -227,21 +235,26 @@ def gemv_sweep(device, peak_gbs: float):
     """Packed GEMV bandwidth of the batch-1..8 projection configurations (algorithmic bytes / time)."""
     from quixicore_metal_b200 import tk
     res = []
-    cases = [("decode_linear_epilogue", "q4_0", 1, 4096, 4096),
-             ("decode_swiglu+down", "q6_K", 1, 4096, 14336),
-             ("decode_swiglu+down", "q6_K", 8, 4096, 14336),
-             ("decode_linear_epilogue", "nvfp4", 1, 8192, 28672),
-             ("decode_linear_epilogue", "mxfp4", 1, 8192, 28672),
-             ("decode_linear_epilogue", "nvfp4", 8, 8192, 28672),
-             ("decode_linear_epilogue", "q8_0", 1, 8192, 28672),
-             # the rest of the NVFP4 / MXFP4 batch sweep (16 rows: streaming kernel; 64 and 256: tcgen05 pipeline)
-             ("decode_linear_epilogue", "nvfp4", 16, 8192, 28672),
-             ("decode_linear_epilogue", "nvfp4", 64, 8192, 28672),
-             ("decode_linear_epilogue", "nvfp4", 256, 8192, 28672),
-             ("decode_linear_epilogue", "mxfp4", 16, 8192, 28672),
-             ("decode_linear_epilogue", "mxfp4", 64, 8192, 28672),
-             ("decode_linear_epilogue", "mxfp4", 256, 8192, 28672)]
-    for op, fmt, M, K, N in cases:
+    # (op, format, rows, K, N, output_quant).  The NVFP4 / MXFP4 sweep is the configuration whose output
+    # is requantised to MXFP8 rows inside the call (16 rows: streaming kernel; 64 and 256: tcgen05 pipeline).
+    cases = [("decode_linear_epilogue", "q4_0", 1, 4096, 4096, None),
+             ("decode_swiglu+down", "q6_K", 1, 4096, 14336, None),
+             ("decode_swiglu+down", "q6_K", 4, 4096, 14336, None),
+             ("decode_swiglu+down", "q6_K", 8, 4096, 14336, None),
+             ("decode_linear_epilogue", "q8_0", 1, 8192, 28672, None),
+             ("decode_linear_epilogue", "mxfp8", 1, 8192, 28672, None),
+             ("decode_linear_epilogue", "q6_K", 1, 8192, 28672, None),
+             ("decode_linear_epilogue", "q4_0", 1, 8192, 28672, None),
+             ("decode_linear_epilogue", "nvfp4", 1, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "nvfp4", 8, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "nvfp4", 16, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "nvfp4", 64, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "nvfp4", 256, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "mxfp4", 1, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "mxfp4", 16, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "mxfp4", 64, 8192, 28672, "mxfp8"),
+             ("decode_linear_epilogue", "mxfp4", 256, 8192, 28672, "mxfp8")]
+    for op, fmt, M, K, N, oq in cases:
         x = torch.randn((M, K), device=device).bfloat16()
         if op == "decode_swiglu+down":
             wbytes = 0
@@ -268,8 +281,8 @@ def gemv_sweep(device, peak_gbs: float):
             bias = torch.randn(N, device=device).bfloat16() * 0.01
 
             def step(i):
-                return tk.decode_linear_epilogue(x, ws[i % copies], bias, None, format=fmt)
-            alg = one + 2 * M * K + 2 * N + 2 * M * N
+                return tk.decode_linear_epilogue(x, ws[i % copies], bias, None, format=fmt, output_quant=oq)
+            alg = one + 2 * M * K + 2 * N + 2 * M * N + (M * (N // 32) * 33 if oq == "mxfp8" else 0)
         for i in range(5):
             step(i)
         torch.cuda.synchronize()
@@ -305,12 +318,40 @@ def gemv_sweep(device, peak_gbs: float):
         except Exception as exc:   # keep the eager number if capture is not possible
             print(f"graph capture skipped for {fmt} M={M}: {exc}", file=sys.stderr)
         gbs = alg / (ms * 1e-3) / 1e9
-        res.append({"op": op, "format": fmt, "M": M, "K": K, "N": N, "ms": round(ms, 5),
+        flops = 2.0 * M * K * N * (3 if op == "decode_swiglu+down" else 1)
+        res.append({"tflops": round(flops / (ms * 1e-3) / 1e12, 1), "op": op, "format": fmt, "M": M, "K": K, "N": N, "output_quant": oq, "ms": round(ms, 5),
                     "ms_eager": round(ms_eager, 5), "timing": "cuda-graph replay of the calls",
                     "algorithmic_bytes": int(alg), "gbs": round(gbs, 1),
                     "frac_of_measured_peak": round(gbs / peak_gbs, 4), "frac_of_8TBs": round(gbs / 8000.0, 4)})
         del x
     return res
+
+
+def sharded_ids_check(device, world: int, rank: int):
+    """Before anything is timed: on a reduced vocabulary whose full packed head every rank builds from
+    the same seed, the vocabulary-parallel call must return the ids of the single-device call on the
+    whole head (argmax, top-k 50, top-p 0.9 at temperature 0.8, 64 hidden rows).  Returns
+    (all ids equal on every rank, number of differing ids summed over ranks)."""
+    import torch.distributed as dist
+    from quixicore_metal_b200 import parallel, tk
+    V = 256 * max(8 * world, 16) + 77                       # whole tiles on every rank + a ragged last tile
+    full = synth_q8_0(V, K_HID, 777, device)                # same generator, same seed: identical on every rank
+    g = torch.Generator(device="cpu"); g.manual_seed(778)
+    h = torch.randn((T_ROWS, K_HID), generator=g).bfloat16().to(device)
+    b, e = parallel.vocab_shard_bounds(V, world)[rank]
+    head = parallel.VocabParallelLMHead(full[b:e].contiguous(), V, FMT)
+    diff = 0
+    for mode, kw in (("argmax", {}), ("topk", {"k": 50, "temperature": TEMP}),
+                     ("topp", {"k": TOPK, "temperature": TEMP, "top_p": TOP_P})):
+        sharded = head.sample(h, mode, seed=SEED, **kw)
+        single = tk.lm_head_sample(h, full, mode=mode, seed=SEED, format=FMT, **kw)
+        diff += int((sharded != single).sum().item())
+    t = torch.tensor([float(diff)], device=device)
+    if world > 1:
+        dist.all_reduce(t)
+    del full, head
+    torch.cuda.empty_cache()
+    return float(t.item()) == 0.0, int(t.item())
 
 
 def stack_sweep(device, world: int, rank: int, peak_gbs: float, layers: int = 80):
@@ -424,6 +465,8 @@ def main():
         emit_json_line(gemv_case(args.gemv_case, device, peak_gbs))
         return
 
+    ids_match, ids_diff = sharded_ids_check(device, world, rank)
+
     # ---- inputs: this rank's vocabulary shard, enough rotating copies to defeat L2 ----
     begin, end = parallel.vocab_shard_bounds(V_FULL, world)[rank]
     rows = end - begin
@@ -527,6 +570,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": T_ROWS * K_HID * 2,
                 "d2h_bytes_per_step": T_ROWS * 4},
         "gpu_launches": int(launches),
+        "ids_match_single_device": bool(ids_match), "ids_differing": ids_diff,
         "roofline": {"bound": "hbm", "kernel": "lm_head stage 1 (projection + tile partials)",
                      "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
                      "frac_of_8TBs": achieved / 8000.0, "peak_kind": peak_kind,
@@ -542,8 +586,17 @@ def main():
         line["lm_head"] = lm_sweep
     if stack is not None:
         line["stack"] = stack
+        line["roofline"]["stack_ms_per_step"] = {f"M{r['M']}": r["ms_per_step"] for r in stack}
     if world == 1 and not args.no_sweep:
         line["gemv"] = gemv_sweep(device, peak_gbs)
+        # the "quant GEMV HBM GB/s" half of the metric, compact: fraction of the measured copy
+        # bandwidth at batch 1 per format (K 8192 -> N 28672), graph-replayed calls
+        line["roofline"]["gemv_batch1_frac_of_measured"] = {
+            r["format"]: r["frac_of_measured_peak"] for r in line["gemv"]
+            if r["M"] == 1 and r["K"] == 8192 and r["op"] == "decode_linear_epilogue"}
+        line["roofline"]["gemv_batch1_frac_of_8TBs"] = {
+            r["format"]: r["frac_of_8TBs"] for r in line["gemv"]
+            if r["M"] == 1 and r["K"] == 8192 and r["op"] == "decode_linear_epilogue"}
     if world == 1 and not args.no_cpu:
         tps, per_step, cores, sample = cpu_composition(2, 1)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}

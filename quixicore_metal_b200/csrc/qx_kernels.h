@@ -39,7 +39,6 @@ struct Options {
   bool force_generic = false;   // keep every call on the shape-generic kernels
   bool tc_pipeline = true;      // batch > 16 on the tcgen05 pipeline
   bool lm_head_ksplit = true;   // share the items of a partial round over K between CTAs
-  bool lm_head_overlap = true;  // selection of one tile overlapped with the projection of the next
 };
 const Options& options();
 bool set_option(const char* name, int value);

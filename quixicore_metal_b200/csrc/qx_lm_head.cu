@@ -109,7 +109,9 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
       unsigned c = 0;
 #pragma unroll
       for (int j = 0; j < 8; ++j) c += key[j] >= cand ? 1u : 0u;
-      if (__reduce_add_sync(0xffffffffu, c) >= (unsigned)k_eff) ans = cand;
+      c = __reduce_add_sync(0xffffffffu, c);
+      if (c >= (unsigned)k_eff) ans = cand;
+      if (c == (unsigned)k_eff) break;      // exactly k elements lie at or above cand: that is the set
     }
     unsigned cg = 0;
 #pragma unroll
@@ -136,6 +138,125 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
   for (int kk = (int)out_pos + lane; kk < topk; kk += 32) {
     part_val[pbase + kk] = QX_NEG_INF;
     part_id[pbase + kk] = -1;
+  }
+}
+
+// The same reduction for up to R hidden rows at once, one warp.  The threshold search is a chain of
+// dependent warp-wide counts (about 25 steps of ~40 cycles each); running R rows through the chain
+// together hides that latency, which is what the per-tile selection of many hidden rows is bound
+// by.  logit[r] = the row's 256 tile logits in shared memory, trow[r] = its row index in the call
+// (< 0: slot unused).  Same results as lmh_select_token row by row.
+template <int R>
+__device__ __forceinline__ void lmh_select_rows(const float* const (&logit)[R], const int (&trow)[R],
+                                                int nvalid, int v0, long long vocab_offset,
+                                                const float* __restrict__ bias, int tile,
+                                                long long tiles_stride, int mode, int topk, float invtemp,
+                                                uint32_t seed, float* __restrict__ part_val,
+                                                int32_t* __restrict__ part_id,
+                                                float* __restrict__ part_lse, int lane) {
+  if (mode <= 1 || nvalid < LMH_TILE) {          // cheap modes and ragged last tiles: row by row
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (trow[r] >= 0)
+        lmh_select_token(logit[r], nvalid, v0, vocab_offset, bias, trow[r], tile, tiles_stride, mode, topk,
+                         invtemp, seed, part_val, part_id, part_lse, lane);
+    return;
+  }
+  // full tile: every lane holds 8 valid elements per row
+  uint32_t key[R][8];
+  uint32_t hi[R], lo[R], ans[R];
+  int nb[R];
+  int maxnb = 0;
+  const int k_eff = min(topk, LMH_TILE);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float mv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float ls = trow[r] >= 0 ? logit[r][lane + 32 * j] : 0.f;
+      if (bias) ls += bias[v0 + lane + 32 * j];
+      mv[j] = ls;
+    }
+    if (mode == 3 && trow[r] >= 0) {
+      float lmax = QX_NEG_INF;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lmax = fmaxf(lmax, mv[j] * invtemp);
+      const float gmax = warp_max(lmax);
+      float lsum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lsum += expf(mv[j] * invtemp - gmax);
+      const float gsum = warp_sum(lsum);
+      if (lane == 0)
+        part_lse[(size_t)trow[r] * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
+    }
+    uint32_t kmax = 0u, kmin = 0xFFFFFFFFu;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      key[r][j] = float_key(mv[j]);
+      kmax = max(kmax, key[r][j]);
+      kmin = min(kmin, key[r][j]);
+    }
+    hi[r] = __reduce_max_sync(0xffffffffu, kmax);
+    lo[r] = __reduce_min_sync(0xffffffffu, kmin);
+    // k <= 32: every lane's largest element is among at least 32 elements >= the smallest such maximum
+    if (k_eff <= 32) lo[r] = max(lo[r], __reduce_min_sync(0xffffffffu, kmax));
+    nb[r] = 32 - __clz(hi[r] ^ lo[r]);
+    ans[r] = nb[r] >= 32 ? 0u : (lo[r] >> nb[r]) << nb[r];
+    maxnb = max(maxnb, nb[r]);
+  }
+  for (int b = maxnb - 1; b >= 0; --b) {
+    unsigned c[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t cand = ans[r] | (1u << b);
+      unsigned cc = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cc += key[r][j] >= cand ? 1u : 0u;
+      c[r] = cc;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) c[r] = __reduce_add_sync(0xffffffffu, c[r]);
+    int pending = 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (b < nb[r] && c[r] >= (unsigned)k_eff) {
+        ans[r] |= 1u << b;
+        if (c[r] == (unsigned)k_eff) nb[r] = 0;   // exactly k elements lie at or above ans: that is the set
+      }
+      pending |= nb[r];
+    }
+    if (pending == 0) break;
+  }
+  const uint32_t lt_mask = (1u << lane) - 1u;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (trow[r] < 0) continue;
+    const size_t pbase = ((size_t)trow[r] * tiles_stride + tile) * topk;
+    unsigned cg = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cg += key[r][j] > ans[r] ? 1u : 0u;
+    const unsigned need = (unsigned)k_eff - __reduce_add_sync(0xffffffffu, cg);   // ties to take, >= 1
+    unsigned ties_before = 0u, out_pos = 0u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                       // id order = (j, lane) lexicographic
+      const bool eq = key[r][j] == ans[r];
+      const uint32_t bal_eq = __ballot_sync(0xffffffffu, eq);
+      const bool sel = key[r][j] > ans[r] || (eq && ties_before + __popc(bal_eq & lt_mask) < need);
+      const uint32_t bal = __ballot_sync(0xffffffffu, sel);
+      if (sel) {
+        const uint32_t pos = out_pos + __popc(bal & lt_mask);
+        float ls = logit[r][lane + 32 * j];
+        if (bias) ls += bias[v0 + lane + 32 * j];
+        part_val[pbase + pos] = ls;
+        part_id[pbase + pos] = (int)(vocab_offset + v0 + lane + 32 * j);
+      }
+      out_pos += __popc(bal);
+      ties_before += __popc(bal_eq);
+    }
+    for (int kk = (int)out_pos + lane; kk < topk; kk += 32) {
+      part_val[pbase + kk] = QX_NEG_INF;
+      part_id[pbase + kk] = -1;
+    }
   }
 }
 
@@ -559,10 +680,18 @@ struct LmhEpi {
     }
     const int v0 = it.tile * LMH_TILE;
     const int nvalid = min(LMH_TILE, a.V - v0);
-    for (int m = it.warp; m < it.m_count; m += LTC_WARPS)
-      lmh_select_token(it.smem_f32 + m * LMH_TILE, nvalid, v0, a.vocab_offset, a.bias, it.m_base + m, it.tile,
-                       a.tiles_stride, a.mode, a.topk, a.invtemp, a.seed, a.part_val, a.part_id, a.part_lse,
-                       it.lane);
+    // every warp takes up to four hidden rows (warp, warp + 18, ...) and reduces them together
+    constexpr int RPW = (BN + LTC_WARPS - 1) / LTC_WARPS;
+    const float* rows[RPW];
+    int trow[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int m = it.warp + r * LTC_WARPS;
+      rows[r] = it.smem_f32 + (m < it.m_count ? m : 0) * LMH_TILE;
+      trow[r] = m < it.m_count ? it.m_base + m : -1;
+    }
+    lmh_select_rows<RPW>(rows, trow, nvalid, v0, a.vocab_offset, a.bias, it.tile, a.tiles_stride, a.mode, a.topk,
+                         a.invtemp, a.seed, a.part_val, a.part_id, a.part_lse, it.lane);
   }
   // padding tiles of a short shard carry absent partials
   __device__ __forceinline__ static void tail(const Args& a, const float* scratch, int real_tiles, int warp, int lane) {

@@ -20,7 +20,6 @@ bool set_option(const char* name, int value) {
   if (std::strcmp(name, "force_generic") == 0) { g_options.force_generic = value != 0; return true; }
   if (std::strcmp(name, "tc_pipeline") == 0) { g_options.tc_pipeline = value != 0; return true; }
   if (std::strcmp(name, "lm_head_ksplit") == 0) { g_options.lm_head_ksplit = value != 0; return true; }
-  if (std::strcmp(name, "lm_head_overlap") == 0) { g_options.lm_head_overlap = value != 0; return true; }
   return false;
 }
 

@@ -202,6 +202,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   };
   // Ring positions of each role, carried across items (a stage's global index only ever grows by one).
   int raw_next = 0, raw_j = 0, raw_h = 0, raw_st = 0;         // loader: next raw stage and where it lies
+  int raw_row0 = -1;                                          // loader: first weight row of (raw_j, raw_h); -1 = not computed
   RingPos ld_raw{0, 0}, ld_b{0, 0}, ld_bdone{0, 0};           // loader: raw slot, activation slot, DONE(stage - BST)
   RingPos wk_raw{0, 0}, wk_done{0, 0}, wk_acc{0, 0};          // workers: raw slot, DONE(stage - AST), accumulator pair
   RingPos mm_b{0, 0}, mm_acc{0, 0}, mm_done{0, 0};            // MMA warp: activation slot, accumulator pair, DONE slot
@@ -228,7 +229,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
       const int RS = (warp & 3) * 32 + lane;                  // row inside the half (scale role)
       const int cg = warp >> 2;                               // which quarter of the hidden rows
-      float acc[CW];
+      float2 acc2[CW / 2];                                    // sums of (hidden row 2i, 2i + 1) for this thread's weight row
       const uint32_t sc_rd = sbase + (uint32_t)(S::OFF_SC + RS * 4);     // scale ring, this thread's row (scale role)
       auto scale_stage = [&](int it) {                          // both unit pairs of stage `it`, in ring order
         const int buf0 = wk_acc.slot;
@@ -251,12 +252,17 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
           tc_fence_before();
           __syncwarp();
           if (lane == 0) { mbar_arrive(ACC_EMPTY(buf0)); mbar_arrive(ACC_EMPTY(buf1)); }
+          // two hidden rows per instruction (packed fp32 fma: each half is an ordinary fmaf)
+          const float2 s0 = make_float2(sc0, sc0), s1 = make_float2(sc1, sc1), s2 = make_float2(sc2, sc2),
+                       s3 = make_float2(sc3, sc3);
 #pragma unroll
-          for (int i = 0; i < CW; ++i) {
-            acc[i] = fmaf(sc0, __uint_as_float(v0[i]), acc[i]);
-            acc[i] = fmaf(sc1, __uint_as_float(v1[i]), acc[i]);
-            acc[i] = fmaf(sc2, __uint_as_float(v2[i]), acc[i]);
-            acc[i] = fmaf(sc3, __uint_as_float(v3[i]), acc[i]);
+          for (int i = 0; i < CW / 2; ++i) {
+            float2 a = acc2[i];
+            a = __ffma2_rn(s0, make_float2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1])), a);
+            a = __ffma2_rn(s1, make_float2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1])), a);
+            a = __ffma2_rn(s2, make_float2(__uint_as_float(v2[2 * i]), __uint_as_float(v2[2 * i + 1])), a);
+            a = __ffma2_rn(s3, make_float2(__uint_as_float(v3[2 * i]), __uint_as_float(v3[2 * i + 1])), a);
+            acc2[i] = a;
           }
         } else {
           __syncwarp();
@@ -265,7 +271,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
       };
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int i = 0; i < CW; ++i) acc[i] = 0.f;
+        for (int i = 0; i < CW / 2; ++i) acc2[i] = make_float2(0.f, 0.f);
         for (int st = 0; st < nks_i; ++st) {
           const int it = g_it;
           const int sa = it & (LTC_AST - 1), sr = wk_raw.slot;
@@ -273,7 +279,12 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
           const uint32_t sp0 = sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE) + off + (uint32_t)(R * C::BOX);
           wait_or_abort(RAW_FULL(sr), wk_raw.par);
           wk_raw.advance(RST);
-          if (it >= LTC_AST) { wait_or_abort(DONE(wk_done.slot), wk_done.par); wk_done.advance(LTC_DONE); }
+          // The operand slot is free once the MMAs of stage it - 2 have completed.  The post-scaled
+          // formats have seen that already: scale_stage(it - 2), which precedes this point, waited for
+          // the accumulators those MMAs produced.  nvfp4 accumulates in place and asks the barrier.
+          if constexpr (!POST) {
+            if (it >= LTC_AST) { wait_or_abort(DONE(wk_done.slot), wk_done.par); wk_done.advance(LTC_DONE); }
+          }
           const uint32_t a_stage = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
           if constexpr (FMT == F_NVFP4) {
 #pragma unroll
@@ -319,7 +330,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
           // park the row's sums of this half
           uint32_t v[CW];
 #pragma unroll
-          for (int i = 0; i < CW; ++i) v[i] = __float_as_uint(acc[i]);
+          for (int i = 0; i < CW / 2; ++i) { v[2 * i] = __float_as_uint(acc2[i].x); v[2 * i + 1] = __float_as_uint(acc2[i].y); }
           tmem_st<CW>(tmem_base + lane_sel + (uint32_t)(h * BN + cg * CW), v);
           tmem_wait_st();
         }
@@ -331,7 +342,8 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     } else if (warp == LTC_DQW) {
       // ================= MMA issuer (the whole warp polls: the wake-up is faster; lane 0 issues) =================
       const uint32_t idesc = umma_idesc_f16(BN);
-      for (int h = 0; h < 2; ++h) {
+      const uint64_t desc0 = umma_desc_sw128(sbase);          // the shared window starts 1024-byte aligned: adding
+      for (int h = 0; h < 2; ++h) {                           // offsets below 256 KB never carries out of the field
         for (int st = 0; st < nks_i; ++st) {
           const int it = g_it++;
           const int sa = it & (LTC_AST - 1), sb = mm_b.slot;
@@ -339,8 +351,9 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
           mm_b.advance(LTC_BST);
           ok = wait_or_abort(A_FULL(sa), (uint32_t)((it >> 1) & 1)) && ok;
           tc_fence_after();
-          const uint32_t a_base = sbase + (uint32_t)(S::OFF_A + sa * S::A_STAGE);
-          const uint32_t b_base = sbase + (uint32_t)(S::OFF_B + sb * S::B_STAGE);
+          // descriptors of this stage: only the address field (low word, 16-byte units) varies
+          const uint64_t a_desc = desc0 + (uint64_t)((uint32_t)(S::OFF_A + sa * S::A_STAGE) >> 4);
+          const uint64_t b_desc = desc0 + (uint64_t)((uint32_t)(S::OFF_B + sb * S::B_STAGE) >> 4);
 #pragma unroll
           for (int p = 0; p < 2; ++p) {                       // swizzle atom = pair of units
             if constexpr (POST) {
@@ -356,8 +369,8 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
 #pragma unroll
                   for (int kk = 0; kk < 4; ++kk)
                     tc_mma_f16(tmem_base + ACC_COL0 + (uint32_t)(buf * 2 * BN + (kk >> 1) * BN),
-                               umma_desc_sw128(a_base + (uint32_t)(p * S::A_ATOM + kk * 32)),
-                               umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc, kk & 1);
+                               a_desc + (uint64_t)((p * S::A_ATOM + kk * 32) >> 4),
+                               b_desc + (uint64_t)((p * S::B_ATOM + kk * 32) >> 4), idesc, kk & 1);
                 }
                 tc_commit(ACC_FULL(buf));
               }
@@ -366,8 +379,8 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                   tc_mma_f16(tmem_base + (uint32_t)(h * BN),
-                             umma_desc_sw128(a_base + (uint32_t)(p * S::A_ATOM + kk * 32)),
-                             umma_desc_sw128(b_base + (uint32_t)(p * S::B_ATOM + kk * 32)), idesc,
+                             a_desc + (uint64_t)((p * S::A_ATOM + kk * 32) >> 4),
+                             b_desc + (uint64_t)((p * S::B_ATOM + kk * 32) >> 4), idesc,
                              (st | p | kk) != 0 ? 1u : 0u);
               }
             }
@@ -394,14 +407,15 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
             // raw stage raw_next = (item raw_j, half raw_h, stage raw_st)
             const bool raw_shared = raw_j >= full_rounds && ksplit > 1;
             const int raw_nks = raw_shared ? tail_nks : nks, raw_st0 = raw_shared ? tail_st0 : 0;
-            const int row0 = (item_of(raw_j) / groups) * ITEM_ROWS + (Epi::DUAL ? 0 : raw_h * 128);
+            if (raw_row0 < 0) raw_row0 = (item_of(raw_j) / groups) * ITEM_ROWS + (Epi::DUAL ? 0 : raw_h * 128);
+            const int row0 = raw_row0;
             const int sr = ld_raw.slot;
             mbar_arrive_expect_tx(RAW_FULL(sr), (uint32_t)C::RAW_STAGE);
             tma_box_2d(sbase + (uint32_t)(S::OFF_RAW + sr * C::RAW_STAGE), (Epi::DUAL && raw_h) ? &wmap1 : &wmap0,
                        (int)(((uint32_t)((raw_st0 + raw_st) * C::CHUNK_BYTES) & ~15u) >> 2), row0, RAW_FULL(sr));
             ld_raw.advance(RST);
             ++raw_next;
-            if (++raw_st == raw_nks) { raw_st = 0; if (++raw_h == 2) { raw_h = 0; ++raw_j; } }
+            if (++raw_st == raw_nks) { raw_st = 0; raw_row0 = -1; if (++raw_h == 2) { raw_h = 0; ++raw_j; } }
             progressed = true;
           }
           if (nb < nb_end && (nb < LTC_BST || mbar_try_wait(DONE(ld_bdone.slot), ld_bdone.par))) {
