@@ -267,6 +267,44 @@ qx_status qx_cuda_sample_logits(void* stream, const void* logits, int32_t* ids, 
                                 qx_dtype dtype, int kind, int topk, double top_p, double temperature,
                                 uint32_t seed);
 
+/* ---- LM-head forms that return log-probabilities ------------------------------------------------
+ * format NULL or "" = dense W (V,K) in the dtype of h; otherwise a packed head.  Raw logits (no
+ * temperature); ordering: logit descending, ties to the smaller token id; bias fp32 (V,) or NULL.
+ */
+
+/* Top-k (k <= 8) of the tokens admitted by a per-row bit mask, with log-probabilities.
+ * allow_mask: uint32 (T, ceil(V/32)), bit (v & 31) of word v >> 5 admits token v.  ids / logprobs
+ * (T, topk): ids sorted best first, logprob = logit - log-sum-exp over the admitted tokens
+ * (normalize_allowed != 0) or over the whole vocabulary; missing entries id -1 / -inf.
+ * Replaces lm_head_masked_mps (torch_kernels.mm:6655-6698; lm_head.metal:1152-1304). */
+size_t qx_cuda_lm_head_masked_workspace_bytes(int64_t T, int64_t V, int64_t K, int topk);
+qx_status qx_cuda_lm_head_masked(void* stream, const void* h, const void* w, const float* bias,
+                                 const uint32_t* allow_mask, int32_t* ids, float* logprobs, void* workspace,
+                                 size_t workspace_bytes, int64_t T, int64_t V, int64_t K, const char* format,
+                                 qx_dtype dtype, int topk, int normalize_allowed);
+
+/* Projects only the tokens listed per row in CSR form (candidate_ids flat int32, offsets int32
+ * (T+1,), `entries` = offsets[T]; ids outside [0, V) are skipped; ids within a row must be unique)
+ * and returns their top-k (k <= 8) with log-probabilities normalised over the listed tokens.
+ * workspace: one float per entry.  Replaces lm_head_candidates_mps (torch_kernels.mm:6700-6731;
+ * lm_head.metal:1339-1425). */
+qx_status qx_cuda_lm_head_candidates(void* stream, const void* h, const void* w, const float* bias,
+                                     const int32_t* candidate_ids, const int32_t* offsets, int64_t entries,
+                                     int32_t* ids, float* logprobs, void* workspace, size_t workspace_bytes,
+                                     int64_t T, int64_t V, int64_t K, const char* format, qx_dtype dtype,
+                                     int topk);
+
+/* One beam-search step over a packed head without logits in memory: h (B*BM, K), cum_log_probs
+ * fp32 (B, BM) -> next_token, parent_beam int32 (B, BM), new_cum fp32 (B, BM): per batch the BM best
+ * of (cum[beam] + log_softmax(logits[beam])[token]), ties to the lower (beam, rank) index.
+ * BM <= 16, V >= 2 BM; q4_0 / q8_0 / mxfp8 / nvfp4 / mxfp4.  Replaces lm_head_beam_advance_mps
+ * (torch_kernels.mm:5105-5172; lm_head.metal:534-573, sampling.metal:432-458). */
+size_t qx_cuda_lm_head_beam_workspace_bytes(int64_t rows, int64_t V, int64_t K, int beam_width);
+qx_status qx_cuda_lm_head_beam_advance(void* stream, const void* h, const void* wq, const float* bias,
+                                       const float* cum_log_probs, int32_t* next_token, int32_t* parent_beam,
+                                       float* new_cum, void* workspace, size_t workspace_bytes, int64_t batches,
+                                       int beam_width, int64_t V, int64_t K, const char* format, qx_dtype dtype);
+
 /* Vocabulary-sharded form.  A shard holds rows [vocab_offset, vocab_offset + V_local) of the full
  * matrix, vocab_offset a multiple of 256 so every 256-row tile of the reference lies in one shard.
  * Stage 1 writes this shard's candidates for every row t:

@@ -650,3 +650,69 @@ def lm_head_merge_candidates(vals, idxs, lses, mode, k=0, temperature=1.0, seed=
             s = (ls[keep] + rng_gumbel(seed, t, i[keep])).astype(f)
             out[t] = _argmax_low_id(s, i[keep]) if keep.any() else -1
     return out
+
+
+# ----------------------------------------------------------------------------------------------
+# LM-head forms that return log-probabilities: masked top-k, CSR candidates, beam advance.
+# Restated from the reference's own test oracles (tests/correctness/quantization/lm_head/
+# test_lm_head.py:370-388 `_packed_allow_mask` / `_topk_logprobs`, :496-510 beam search) and kernels
+# (kernels/quantization/lm_head/lm_head.metal:1152-1425, :534-573; sampling.metal:432-458).
+# ----------------------------------------------------------------------------------------------
+def packed_allow_mask(rows, vocab: int) -> np.ndarray:
+    """(T, ceil(V/32)) uint32: bit (v & 31) of word v >> 5 admits token v (test_lm_head.py:370-375)."""
+    mask = np.zeros((len(rows), (vocab + 31) // 32), dtype=np.uint32)
+    for t, allowed in enumerate(rows):
+        for v in allowed:
+            mask[t, v // 32] |= np.uint32(1 << (v % 32))
+    return mask
+
+
+def topk_logprobs(logits_row: np.ndarray, candidates, topk: int, normalizer_ids=None):
+    """Top-k of the listed tokens by (logit desc, id asc) with logprob = logit - log-sum-exp over the
+    listed tokens (or over normalizer_ids); ids outside [0, V) are skipped; short rows are padded
+    with id -1 / -inf (test_lm_head.py:378-388)."""
+    V = logits_row.shape[0]
+    valid = np.array([v for v in candidates if 0 <= v < V], dtype=np.int64)
+    out_ids = np.full(topk, -1, np.int32)
+    out_lp = np.full(topk, -np.inf, np.float32)
+    if valid.size == 0:
+        return out_ids, out_lp
+    order = np.lexsort((valid, -logits_row[valid].astype(np.float64)))[:topk]
+    sel = valid[order]
+    norm = valid if normalizer_ids is None else np.asarray(normalizer_ids, np.int64)
+    vals = logits_row[norm].astype(np.float64)
+    m = vals.max()
+    lse = m + np.log(np.exp(vals - m).sum())
+    out_ids[:sel.size] = sel
+    out_lp[:sel.size] = (logits_row[sel].astype(np.float64) - lse).astype(np.float32)
+    return out_ids, out_lp
+
+
+def lm_head_masked_from_logits(logits: np.ndarray, allowed_rows, topk: int, normalize: str = "allowed"):
+    """(ids (T,k), logprobs (T,k)) of tk.lm_head_masked on raw logits (bias already added)."""
+    T, V = logits.shape
+    full = np.arange(V) if normalize == "full" else None
+    out = [topk_logprobs(logits[t], allowed_rows[t], topk, full) for t in range(T)]
+    return np.stack([o[0] for o in out]), np.stack([o[1] for o in out])
+
+
+def lm_head_candidates_from_logits(logits: np.ndarray, candidate_ids, offsets, topk: int):
+    """(ids, logprobs) of tk.lm_head_candidates: row t lists candidate_ids[offsets[t]:offsets[t+1]]."""
+    T = logits.shape[0]
+    out = [topk_logprobs(logits[t], list(candidate_ids[offsets[t]:offsets[t + 1]]), topk) for t in range(T)]
+    return np.stack([o[0] for o in out]), np.stack([o[1] for o in out])
+
+
+def lm_head_beam_advance_from_logits(logits: np.ndarray, cum: np.ndarray, beam_width: int):
+    """One exact beam-search step (test_lm_head.py:496-510): log-softmax per beam row, add the beam's
+    cumulative score, take the beam_width best of beam_width * V per batch (stable: ties to the lower
+    flat index).  Returns (token (B,BM), parent (B,BM), score (B,BM))."""
+    B, BM = cum.shape
+    V = logits.shape[1]
+    L = logits.astype(np.float64)
+    m = L.max(axis=1, keepdims=True)
+    log_z = m + np.log(np.exp(L - m).sum(axis=1, keepdims=True))
+    flat = (L - log_z).reshape(B, BM, V) + cum.astype(np.float64)[:, :, None]
+    flat = flat.reshape(B, BM * V)
+    sel = np.argsort(-flat, axis=1, kind="stable")[:, :BM]
+    return (sel % V).astype(np.int32), (sel // V).astype(np.int32), np.take_along_axis(flat, sel, axis=1).astype(np.float32)

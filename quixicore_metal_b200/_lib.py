@@ -71,6 +71,16 @@ def lib() -> C.CDLL:
     L.qx_cuda_lm_head_sample_dense.argtypes = [vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, i32, i32, i32, f64, u32]
     L.qx_cuda_sample_logits.restype = Status
     L.qx_cuda_sample_logits.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, f64, f64, u32]
+    L.qx_cuda_lm_head_masked_workspace_bytes.restype = sz
+    L.qx_cuda_lm_head_masked_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    L.qx_cuda_lm_head_masked.restype = Status
+    L.qx_cuda_lm_head_masked.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, cs, i32, i32, i32]
+    L.qx_cuda_lm_head_candidates.restype = Status
+    L.qx_cuda_lm_head_candidates.argtypes = [vp, vp, vp, vp, vp, vp, i64, vp, vp, vp, sz, i64, i64, i64, cs, i32, i32]
+    L.qx_cuda_lm_head_beam_workspace_bytes.restype = sz
+    L.qx_cuda_lm_head_beam_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    L.qx_cuda_lm_head_beam_advance.restype = Status
+    L.qx_cuda_lm_head_beam_advance.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i32, i64, i64, cs, i32]
     L.qx_cuda_lm_head_shard_candidates.restype = i64
     L.qx_cuda_lm_head_shard_candidates.argtypes = [i32, i32, i64]
     L.qx_cuda_lm_head_shard_workspace_bytes.restype = sz

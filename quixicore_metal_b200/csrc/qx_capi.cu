@@ -394,6 +394,133 @@ qx_status qx_cuda_sample_logits(void* stream, const void* logits, int32_t* ids, 
   return check_launch(op);
 }
 
+// ---- masked / candidate / beam forms of the LM head ------------------------------------------------
+static bool dense_format(const char* format) { return !format || format[0] == '\0'; }
+
+static qx_status check_head_weight(const char* op, const void* h, const void* w, int64_t T, int64_t V, int64_t K,
+                                   const char* format, qx_dtype dtype, int* fmt_out) {
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "h must be non-empty (T,K) fp32/fp16/bf16");
+  if (!h || !w) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (T <= 0 || K <= 0 || V <= 0 || T > 0x7fffffff || V > 0x7fffffff || K > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "h must be non-empty (T,K) fp32/fp16/bf16");
+  *fmt_out = -1;
+  if (dense_format(format)) return ok(op);
+  const int f = parse_format(format);
+  if (f < 0) return fail(QX_UNSUPPORTED_FORMAT, op, "format must be empty/dense, q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4");
+  if (K % block_k_of(f) != 0) return fail(QX_INVALID_SHAPE, op, "invalid packed weight shape");
+  *fmt_out = f;
+  return ok(op);
+}
+
+size_t qx_cuda_lm_head_masked_workspace_bytes(int64_t T, int64_t V, int64_t K, int topk) {
+  if (T <= 0 || V <= 0 || K <= 0 || topk <= 0) return 0;
+  return partial_bytes(T, V, 3, topk) + lm_head_scratch_full_bytes(T, K);
+}
+
+qx_status qx_cuda_lm_head_masked(void* stream, const void* h, const void* w, const float* bias,
+                                 const uint32_t* allow_mask, int32_t* ids, float* logprobs, void* workspace,
+                                 size_t workspace_bytes, int64_t T, int64_t V, int64_t K, const char* format,
+                                 qx_dtype dtype, int topk, int normalize_allowed) {
+  static const char* op = "lm_head_masked";
+  int f = -1;
+  qx_status st = check_head_weight(op, h, w, T, V, K, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  if (topk < 1 || topk > 8 || topk > V) return fail(QX_INVALID_ARGUMENT, op, "topk must be in [1,min(8,V)]");
+  if (!allow_mask) return fail(QX_INVALID_ARGUMENT, op, "allow_mask must be (T,ceil(V/32))");
+  if (!ids || !logprobs) return fail(QX_INVALID_ARGUMENT, op, "null output pointer");
+  const size_t need = qx_cuda_lm_head_masked_workspace_bytes(T, V, K, topk);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must be 256-byte aligned and at least qx_cuda_lm_head_masked_workspace_bytes");
+  if (!device_ready(op, &st)) return st;
+  const int64_t tiles = tiles_of(V);
+  const size_t seg = align256((size_t)T * tiles * topk * 4);
+  float* pv = (float*)workspace;
+  int32_t* pi = (int32_t*)((char*)workspace + seg);
+  float* pl = (float*)((char*)workspace + 2 * seg);
+  const size_t pbytes = partial_bytes(T, V, 3, topk);
+  const LmhMask mask{allow_mask, (V + 31) / 32, normalize_allowed ? 1 : 0};
+  if (f < 0) {
+    launch_lm_head_dense_partials((cudaStream_t)stream, h, w, bias, pv, pi, T, V, K, dtype, 4, topk, 1.0f, 0u, pl, mask);
+  } else {
+    LmHeadArgs a{h, w, bias, T, V, K, 0, f, dtype, 4, topk, 1.0f, 0u, 1.0f};
+    a.mask = mask;
+    a.scratch = (char*)workspace + pbytes;
+    a.scratch_bytes = workspace_bytes - pbytes;
+    launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, pl, tiles);
+  }
+  launch_lm_head_topk_logprob((cudaStream_t)stream, pv, pi, nullptr, tiles * topk, pl, tiles, nullptr, T, V, topk, ids, logprobs);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_lm_head_candidates(void* stream, const void* h, const void* w, const float* bias,
+                                     const int32_t* candidate_ids, const int32_t* offsets, int64_t entries,
+                                     int32_t* ids, float* logprobs, void* workspace, size_t workspace_bytes,
+                                     int64_t T, int64_t V, int64_t K, const char* format, qx_dtype dtype,
+                                     int topk) {
+  static const char* op = "lm_head_candidates";
+  int f = -1;
+  qx_status st = check_head_weight(op, h, w, T, V, K, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  if (topk < 1 || topk > 8 || topk > V) return fail(QX_INVALID_ARGUMENT, op, "topk must be in [1,min(8,V)]");
+  if (!offsets || entries < 0 || (entries > 0 && !candidate_ids) || entries > 0x7fffffff)
+    return fail(QX_INVALID_ARGUMENT, op, "flat candidate_ids and T+1 offsets required");
+  if (!ids || !logprobs) return fail(QX_INVALID_ARGUMENT, op, "null output pointer");
+  const size_t need = align256((size_t)(entries > 0 ? entries : 1) * 4);
+  if (!workspace || workspace_bytes < need)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must hold one float per candidate entry");
+  if (!device_ready(op, &st)) return st;
+  float* logit = (float*)workspace;
+  launch_lm_head_candidate_logits((cudaStream_t)stream, f, dtype, h, w, bias, candidate_ids, offsets, logit, T, V, K, entries);
+  launch_lm_head_topk_logprob((cudaStream_t)stream, logit, candidate_ids, offsets, 0, nullptr, 0, nullptr, T, V, topk, ids, logprobs);
+  return check_launch(op);
+}
+
+size_t qx_cuda_lm_head_beam_workspace_bytes(int64_t rows, int64_t V, int64_t K, int beam_width) {
+  if (rows <= 0 || V <= 0 || K <= 0 || beam_width <= 0) return 0;
+  return partial_bytes(rows, V, 3, 2 * beam_width) + 2 * align256((size_t)rows * 2 * beam_width * 4) +
+         lm_head_scratch_full_bytes(rows, K);
+}
+
+qx_status qx_cuda_lm_head_beam_advance(void* stream, const void* h, const void* wq, const float* bias,
+                                       const float* cum_log_probs, int32_t* next_token, int32_t* parent_beam,
+                                       float* new_cum, void* workspace, size_t workspace_bytes, int64_t batches,
+                                       int beam_width, int64_t V, int64_t K, const char* format, qx_dtype dtype) {
+  static const char* op = "lm_head_beam_advance";
+  if (beam_width < 1 || beam_width > 16) return fail(QX_INVALID_ARGUMENT, op, "beam_width must be in [1,16]");
+  if (batches <= 0) return fail(QX_INVALID_SHAPE, op, "cum_log_probs must be (B,BM), h rows B*BM");
+  const int64_t rows = batches * beam_width;
+  int f = -1;
+  qx_status st = check_head_weight(op, h, wq, rows, V, K, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  if (f < 0 || f == F_Q6_K) return fail(QX_UNSUPPORTED_FORMAT, op, "format must be q4_0, q8_0, mxfp8, nvfp4, or mxfp4");
+  const int two_bm = 2 * beam_width;
+  if (V < two_bm) return fail(QX_INVALID_ARGUMENT, op, "vocab must be >= 2*beam_width");
+  if (!cum_log_probs || !next_token || !parent_beam || !new_cum) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  const size_t need = qx_cuda_lm_head_beam_workspace_bytes(rows, V, K, beam_width);
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0)
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must be 256-byte aligned and at least qx_cuda_lm_head_beam_workspace_bytes");
+  if (!device_ready(op, &st)) return st;
+  const int64_t tiles = tiles_of(V);
+  const size_t seg = align256((size_t)rows * tiles * two_bm * 4);
+  const size_t pbytes = partial_bytes(rows, V, 3, two_bm);
+  const size_t cseg = align256((size_t)rows * two_bm * 4);
+  float* pv = (float*)workspace;
+  int32_t* pi = (int32_t*)((char*)workspace + seg);
+  float* pl = (float*)((char*)workspace + 2 * seg);
+  float* cand_score = (float*)((char*)workspace + pbytes);
+  int32_t* cand_token = (int32_t*)((char*)workspace + pbytes + cseg);
+  // per 256-row tile the 2*BM best raw logits and the tile log-sum-exp (the top-p partials at
+  // temperature 1), merged per beam row into cum + logit - lse, then BM of BM x 2BM per batch
+  LmHeadArgs a{h, wq, bias, rows, V, K, 0, f, dtype, 3, two_bm, 1.0f, 0u, 1.0f};
+  a.scratch = (char*)workspace + pbytes + 2 * cseg;
+  a.scratch_bytes = workspace_bytes - pbytes - 2 * cseg;
+  launch_lm_head_partials((cudaStream_t)stream, a, pv, pi, pl, tiles);
+  launch_lm_head_topk_logprob((cudaStream_t)stream, pv, pi, nullptr, tiles * two_bm, pl, tiles, cum_log_probs, rows, V, two_bm,
+                              cand_token, cand_score);
+  launch_beam_select((cudaStream_t)stream, cand_score, cand_token, next_token, parent_beam, new_cum, batches, beam_width, two_bm);
+  return check_launch(op);
+}
+
 int64_t qx_cuda_lm_head_shard_candidates(int mode, int topk, int64_t max_tiles) {
   if (mode <= 1) return 1;
   if (mode == 2) return topk;

@@ -76,14 +76,19 @@ void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __h
 // kernel that ran also wrote the requested MXFP8 output rows.
 bool launch_projection(cudaStream_t st, const GemvArgs& a);
 
+// Per-row allow mask of lm_head_masked: bit (v & 31) of word bits[t * words + (v >> 5)] admits global
+// vocabulary id v for hidden row t; norm_allowed: the log-sum-exp runs over admitted ids only.
+struct LmhMask { const uint32_t* bits; long long words; int norm_allowed; };
+
 // Fused LM head.  Stage 1 writes per-256-row-tile partials, stage 2 merges them.
 struct LmHeadArgs {
   const void* h; const void* wq; const float* bias;   // bias: fp32 (V_local,) or nullptr
   int64_t T, V, K;                                    // V = rows held by this call
   int64_t vocab_offset;                               // global id of local row 0
   int format; qx_dtype dtype;
-  int mode, topk;
+  int mode, topk;                                     // mode 4: masked top-k (mask below), raw logits
   float invtemp; uint32_t seed; float top_p;
+  LmhMask mask = LmhMask{nullptr, 0, 1};
   // Device scratch of at least lm_head_scratch_bytes(T, K) bytes (prepared activations, row scales,
   // the release flags and - as far as it reaches - the exchange slots of K-split items).
   void* scratch = nullptr;
@@ -116,10 +121,22 @@ qx_status lm_head_sample_on(const char* op, void* stream, const void* h, const v
 // Stage 1 over a dense (V, K) head in h's dtype (modes 0..2); partials as in the packed form.
 void launch_lm_head_dense_partials(cudaStream_t st, const void* h, const void* W, const float* bias,
                                    float* part_val, int32_t* part_id, int64_t T, int64_t V, int64_t K,
-                                   qx_dtype dtype, int mode, int topk, float invtemp, uint32_t seed);
+                                   qx_dtype dtype, int mode, int topk, float invtemp, uint32_t seed,
+                                   float* part_lse = nullptr, const LmhMask mask = LmhMask{nullptr, 0, 1});
 // Samplers over materialised logits (rows, V): kind 0 argmax, 1 categorical, 2 top-k, 3 top-p.
 void launch_sample_logits(cudaStream_t st, const void* logits, int32_t* ids, int64_t rows, int64_t V,
                           qx_dtype dtype, int kind, int topk, float p, float invtemp, uint32_t seed);
+
+// Sorted top-k ids with scores (cum + value - log-sum-exp) per row: see qx_lm_head_topk.cu.
+void launch_lm_head_topk_logprob(cudaStream_t st, const float* val, const int32_t* id, const int32_t* offsets,
+                                 int64_t per_row, const float* lse, int64_t nlse, const float* cum, int64_t rows,
+                                 int64_t V, int topk, int32_t* out_id, float* out_score);
+// logit[e] = dot(h[row of e], W[cand[e]]) (+ bias) for every CSR entry e with 0 <= cand[e] < V; format < 0: dense W.
+void launch_lm_head_candidate_logits(cudaStream_t st, int format, qx_dtype dtype, const void* h, const void* w,
+                                     const float* bias, const int32_t* cand, const int32_t* offsets, float* logit,
+                                     int64_t rows, int64_t V, int64_t K, int64_t entries);
+void launch_beam_select(cudaStream_t st, const float* cand_score, const int32_t* cand_token, int32_t* next_token,
+                        int32_t* parent_beam, float* new_cum, int64_t batches, int BM, int two_bm);
 
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);

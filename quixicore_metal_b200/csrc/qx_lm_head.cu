@@ -28,6 +28,9 @@ constexpr int LMH_RED_THREADS = 1024;
 
 // Reduce one hidden row's 256 tile logits (shared memory) to the tile partials of its mode.
 // Executed by one warp.  nvalid <= 0 marks a padding tile: absent partials are written.
+// Mode 4 (lm_head_masked, kernels/quantization/lm_head/lm_head.metal:1152-1262): the tile's top-k
+// among the tokens whose bit is set in the row's allow mask, and the log-sum-exp of the raw logits
+// over the allowed tokens (norm_allowed) or over every token of the tile.
 __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit, int nvalid, int v0,
                                                  long long vocab_offset,
                                                  const float* __restrict__ bias, int t, int tile,
@@ -35,7 +38,8 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
                                                  float invtemp, uint32_t seed,
                                                  float* __restrict__ part_val,
                                                  int32_t* __restrict__ part_id,
-                                                 float* __restrict__ part_lse, int lane) {
+                                                 float* __restrict__ part_lse, int lane,
+                                                 const LmhMask mask = LmhMask{nullptr, 0, 1}) {
   if (mode <= 1) {
     float best = QX_NEG_INF;
     int bid = 0x7fffffff;
@@ -53,9 +57,11 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
     }
     return;
   }
-  // modes 2/3: tile top-k of the raw logits (+bias); mode 3 also the tempered log-sum-exp
+  // modes 2/3/4: tile top-k of the raw logits (+bias); modes 3/4 also the (tempered) log-sum-exp
   float mv[8];
   int mi[8];
+  unsigned in_lse = 0u;          // bit j: element j counts towards the tile's log-sum-exp
+  unsigned ncand_l = 0u;         // this lane's candidates
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int lr = lane + 32 * j;
@@ -63,21 +69,26 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
       float ls = logit[lr];
       if (bias) ls += bias[v0 + lr];
       mv[j] = ls;
-      mi[j] = (int)(vocab_offset + v0 + lr);
+      const long long gid = vocab_offset + v0 + lr;
+      bool cand = true;
+      if (mode == 4) cand = (mask.bits[(size_t)t * mask.words + (gid >> 5)] >> (gid & 31)) & 1u;
+      mi[j] = cand ? (int)gid : -1;
+      ncand_l += cand ? 1u : 0u;
+      if (cand || (mode == 4 && !mask.norm_allowed)) in_lse |= 1u << j;
     } else {
       mv[j] = QX_NEG_INF;
       mi[j] = -1;
     }
   }
-  if (mode == 3) {
-    // tempered log-sum-exp of the tile: maximum first, then one exponential per element
+  if (mode >= 3) {
+    // (tempered) log-sum-exp of the tile: maximum first, then one exponential per element
     float lmax = QX_NEG_INF;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) lmax = fmaxf(lmax, mi[j] >= 0 ? mv[j] * invtemp : QX_NEG_INF);
+    for (int j = 0; j < 8; ++j) lmax = fmaxf(lmax, ((in_lse >> j) & 1u) ? mv[j] * invtemp : QX_NEG_INF);
     const float gmax = warp_max(lmax);
     float lsum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) lsum += mi[j] >= 0 ? expf(mv[j] * invtemp - gmax) : 0.f;
+    for (int j = 0; j < 8; ++j) lsum += ((in_lse >> j) & 1u) ? expf(mv[j] * invtemp - gmax) : 0.f;
     const float gsum = warp_sum(lsum);
     if (lane == 0)
       part_lse[(size_t)t * tiles_stride + tile] = gsum > 0.f ? gmax + logf(gsum) : QX_NEG_INF;
@@ -86,7 +97,7 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
   // order-preserving keys (one warp-wide count per step), then emit every element above it and, of
   // the elements equal to it, the ones with the smallest ids.
   const size_t pbase = ((size_t)t * tiles_stride + tile) * topk;
-  const int k_eff = min(topk, max(nvalid, 0));
+  const int k_eff = min(topk, mode == 4 ? (int)__reduce_add_sync(0xffffffffu, ncand_l) : max(nvalid, 0));
   uint32_t key[8];
   uint32_t kmax = 0u, kmin = 0xFFFFFFFFu;
 #pragma unroll
@@ -101,7 +112,7 @@ __device__ __forceinline__ void lmh_select_token(const float* __restrict__ logit
     uint32_t lo = __reduce_min_sync(0xffffffffu, kmin);
     // with a full tile and k <= 32, every lane's largest element is among at least 32 elements
     // that are >= the smallest such maximum
-    if (k_eff <= 32 && nvalid >= LMH_TILE) lo = max(lo, __reduce_min_sync(0xffffffffu, kmax));
+    if (k_eff <= 32 && nvalid >= LMH_TILE && mode != 4) lo = max(lo, __reduce_min_sync(0xffffffffu, kmax));
     const int nb = 32 - __clz(hi ^ lo);                 // bits below the common prefix of lo and hi
     uint32_t ans = nb >= 32 ? 0u : (lo >> nb) << nb;
     for (int b = nb - 1; b >= 0; --b) {
@@ -153,13 +164,14 @@ __device__ __forceinline__ void lmh_select_rows(const float* const (&logit)[R], 
                                                 long long tiles_stride, int mode, int topk, float invtemp,
                                                 uint32_t seed, float* __restrict__ part_val,
                                                 int32_t* __restrict__ part_id,
-                                                float* __restrict__ part_lse, int lane) {
-  if (mode <= 1 || nvalid < LMH_TILE) {          // cheap modes and ragged last tiles: row by row
+                                                float* __restrict__ part_lse, int lane,
+                                                const LmhMask mask = LmhMask{nullptr, 0, 1}) {
+  if (mode <= 1 || mode == 4 || nvalid < LMH_TILE) {   // cheap modes, masked rows and ragged last tiles: row by row
 #pragma unroll
     for (int r = 0; r < R; ++r)
       if (trow[r] >= 0)
         lmh_select_token(logit[r], nvalid, v0, vocab_offset, bias, trow[r], tile, tiles_stride, mode, topk,
-                         invtemp, seed, part_val, part_id, part_lse, lane);
+                         invtemp, seed, part_val, part_id, part_lse, lane, mask);
     return;
   }
   // full tile: every lane holds 8 valid elements per row
@@ -266,7 +278,7 @@ lmh_partials_kernel(const T* __restrict__ h, const uint8_t* __restrict__ wq,
                     const float* __restrict__ bias, float* __restrict__ part_val,
                     int32_t* __restrict__ part_id, float* __restrict__ part_lse, int T_rows, int V,
                     int K, long long vocab_offset, long long tiles_stride, int mode, int topk,
-                    float invtemp, uint32_t seed) {
+                    float invtemp, uint32_t seed, const LmhMask mask) {
   constexpr int BK = block_k_of(FMT), BB = block_bytes_of(FMT);
   __shared__ float logit[LMH_TB][LMH_TILE];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -328,7 +340,7 @@ lmh_partials_kernel(const T* __restrict__ h, const uint8_t* __restrict__ wq,
   // ---- per-token selection: warp w handles token t0 + w ----
   if (warp >= tcount) return;
   lmh_select_token(logit[warp], min(LMH_TILE, V - v0), v0, vocab_offset, bias, t0 + warp, tile,
-                   tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse, lane);
+                   tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse, lane, mask);
 }
 
 
@@ -340,8 +352,9 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 lmh_dense_partials_kernel(const T* __restrict__ h, const T* __restrict__ W,
                           const float* __restrict__ bias, float* __restrict__ part_val,
-                          int32_t* __restrict__ part_id, int T_rows, int V, int K,
-                          long long tiles_stride, int mode, int topk, float invtemp, uint32_t seed) {
+                          int32_t* __restrict__ part_id, float* __restrict__ part_lse, int T_rows, int V,
+                          int K, long long tiles_stride, int mode, int topk, float invtemp, uint32_t seed,
+                          const LmhMask mask) {
   __shared__ float logit[LMH_TB][LMH_TILE];
   constexpr int VEC = 16 / (int)sizeof(T);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -392,24 +405,25 @@ lmh_dense_partials_kernel(const T* __restrict__ h, const T* __restrict__ W,
   __syncthreads();
   if (warp >= tcount) return;
   lmh_select_token(logit[warp], min(LMH_TILE, V - v0), v0, 0, bias, t0 + warp, tile, tiles_stride, mode,
-                   topk, invtemp, seed, part_val, part_id, nullptr, lane);
+                   topk, invtemp, seed, part_val, part_id, part_lse, lane, mask);
 }
 
 void launch_lm_head_dense_partials(cudaStream_t st, const void* h, const void* W, const float* bias,
                                    float* part_val, int32_t* part_id, int64_t T, int64_t V, int64_t K,
-                                   qx_dtype dtype, int mode, int topk, float invtemp, uint32_t seed) {
+                                   qx_dtype dtype, int mode, int topk, float invtemp, uint32_t seed,
+                                   float* part_lse, const LmhMask mask) {
   const long long tiles = (V + LMH_TILE - 1) / LMH_TILE;
   dim3 grid((unsigned)tiles, (unsigned)((T + LMH_TB - 1) / LMH_TB));
   if (dtype == QX_DTYPE_F32)
-    lmh_dense_partials_kernel<float><<<grid, 256, 0, st>>>((const float*)h, (const float*)W, bias, part_val, part_id,
-                                                            (int)T, (int)V, (int)K, tiles, mode, topk, invtemp, seed);
+    lmh_dense_partials_kernel<float><<<grid, 256, 0, st>>>((const float*)h, (const float*)W, bias, part_val, part_id, part_lse,
+                                                            (int)T, (int)V, (int)K, tiles, mode, topk, invtemp, seed, mask);
   else if (dtype == QX_DTYPE_F16)
-    lmh_dense_partials_kernel<__half><<<grid, 256, 0, st>>>((const __half*)h, (const __half*)W, bias, part_val, part_id,
-                                                             (int)T, (int)V, (int)K, tiles, mode, topk, invtemp, seed);
+    lmh_dense_partials_kernel<__half><<<grid, 256, 0, st>>>((const __half*)h, (const __half*)W, bias, part_val, part_id, part_lse,
+                                                             (int)T, (int)V, (int)K, tiles, mode, topk, invtemp, seed, mask);
   else
     lmh_dense_partials_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)W, bias,
-                                                                    part_val, part_id, (int)T, (int)V, (int)K, tiles,
-                                                                    mode, topk, invtemp, seed);
+                                                                    part_val, part_id, part_lse, (int)T, (int)V, (int)K, tiles,
+                                                                    mode, topk, invtemp, seed, mask);
   note_launch();
 }
 
@@ -448,7 +462,7 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
                   float* __restrict__ part_val, int32_t* __restrict__ part_id,
                   float* __restrict__ part_lse, int T_total, int tokens_per_group, int V, int K,
                   long long vocab_offset, long long tiles_stride, int mode, int topk, float invtemp,
-                  uint32_t seed, int* __restrict__ err_flag) {
+                  uint32_t seed, const LmhMask mask, int* __restrict__ err_flag) {
   using F = StreamFmt<FMT>;
   using C = LmhCfg<FMT>;
   constexpr int NW = 256 / WROWS;             // warps per CTA
@@ -581,7 +595,7 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
         if (m < T_pass)
           lmh_select_token(logit + ml * LMH_LOGIT_PITCH, nvalid, v0, vocab_offset, bias, t_base + m,
                            tile, tiles_stride, mode, topk, invtemp, seed, part_val, part_id, part_lse,
-                           lane);
+                           lane, mask);
       }
     }
   }
@@ -616,6 +630,7 @@ struct LmhEpi {
     // means "written during this launch"
     float* xchg; unsigned* flags; unsigned epoch;
     int* err_flag;
+    LmhMask mask;
   };
   static constexpr bool DUAL = false;
   __device__ __forceinline__ static void run(const Args& a, const TcItem& it) {
@@ -691,7 +706,7 @@ struct LmhEpi {
       trow[r] = m < it.m_count ? it.m_base + m : -1;
     }
     lmh_select_rows<RPW>(rows, trow, nvalid, v0, a.vocab_offset, a.bias, it.tile, a.tiles_stride, a.mode, a.topk,
-                         a.invtemp, a.seed, a.part_val, a.part_id, a.part_lse, it.lane);
+                         a.invtemp, a.seed, a.part_val, a.part_id, a.part_lse, it.lane, a.mask);
   }
   // padding tiles of a short shard carry absent partials
   __device__ __forceinline__ static void tail(const Args& a, const float* scratch, int real_tiles, int warp, int lane) {
@@ -733,7 +748,7 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   dim3 grid((unsigned)(items < sm_count() ? items : sm_count()));
   lmh_stream_kernel<FMT, NT, WROWS><<<grid, NW * 32, smem, st>>>(
       wmap, x16, rowscale, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
-      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, err);
+      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, a.mask, err);
   note_launch();
 }
 
@@ -819,7 +834,7 @@ static bool launch_lmh_tc_bn(cudaStream_t st, const LmHeadArgs& a, float* pv, in
   note_launch();
   const typename Epi::Args ea{a.bias, pv, pi, pl, (int)a.T, (int)a.V, (long long)a.vocab_offset,
                               (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed,
-                              sc.xchg, sc.flags, epoch, err};
+                              sc.xchg, sc.flags, epoch, err, a.mask};
   bool launched = false;
   if (ksplit > 1) {
     // the flags start every launch at zero, whatever an earlier user of the scratch left there
@@ -1119,7 +1134,7 @@ static void launch_partials_t(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   dim3 grid((unsigned)tiles_stride, (unsigned)((a.T + LMH_TB - 1) / LMH_TB));
   lmh_partials_kernel<FMT, T><<<grid, 256, 0, st>>>(
       (const T*)a.h, (const uint8_t*)a.wq, a.bias, pv, pi, pl, (int)a.T, (int)a.V, (int)a.K,
-      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed);
+      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, a.mask);
   note_launch();
 }
 

@@ -121,3 +121,37 @@ def lm_head_sample(h, W, mode="argmax", k=0, temperature=1.0, seed=0, bias=None,
     K = W.shape[1] * _LM_QUANT_BLOCK_K[format]
     return _tt.lm_head_sample_q(h, W, bias, V, K, format, _LM_HEAD_MODES[mode], kk,
                                 float(temperature), int(seed), float(top_p))
+
+
+def lm_head_masked(h, W, allow_mask, bias=None, format=None, topk=1, normalize="allowed"):
+    """Project directly into a packed per-row allow mask without materialising logits: (ids, logprobs),
+    each (T, topk), of the best admitted tokens.  W dense (V,K) or packed with format=; allow_mask
+    (T, ceil(V/32)) packed 32-bit words; normalize 'allowed' (over the admitted tokens) or 'full'
+    (the pre-mask full-vocabulary normaliser).  Ties choose the lower token id.
+    (bindings/python/tk/__init__.py:2469-2491)"""
+    if normalize not in ("allowed", "full"):
+        raise ValueError("lm_head_masked: normalize must be 'allowed' or 'full'")
+    import torch
+    b = bias if bias is not None else torch.zeros(1, dtype=torch.float32, device=h.device)
+    return _tt.lm_head_masked(h, W, b, allow_mask, "" if format is None else str(format), int(topk),
+                              normalize == "allowed")
+
+
+def lm_head_candidates(h, W, candidate_ids, offsets, bias=None, format=None, topk=1):
+    """Project only CSR-listed token candidates and return their top-k log-probabilities, normalised
+    over the valid listed candidates.  (bindings/python/tk/__init__.py:2494-2511)"""
+    import torch
+    b = bias if bias is not None else torch.zeros(1, dtype=torch.float32, device=h.device)
+    return _tt.lm_head_candidates(h, W, b, candidate_ids, offsets, "" if format is None else str(format), int(topk))
+
+
+def lm_head_beam_advance(h, W, cum_log_probs, beam_width, bias=None, format="q4_0"):
+    """Quantized LM head plus exact beam-search advance: next token, parent beam and updated cumulative
+    log-probability, each (B, beam_width).  Every format and row count takes the fused no-logits
+    kernels here (the reference routes q8_0 / mxfp8 and larger batches through a logits matrix,
+    bindings/python/tk/__init__.py:2530-2578)."""
+    if format not in ("q4_0", "q8_0", "mxfp8", "nvfp4", "mxfp4"):
+        raise ValueError("lm_head_beam_advance: format must be q4_0, q8_0, mxfp8, nvfp4, or mxfp4")
+    import torch
+    b = bias if bias is not None else torch.zeros(1, dtype=torch.float32, device=h.device)
+    return _tt.lm_head_beam_advance(h, W, b, cum_log_probs, int(beam_width), str(format))

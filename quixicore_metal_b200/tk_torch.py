@@ -316,3 +316,116 @@ def top_k_sample(logits, k, temperature=1.0, seed=0):
 def top_p_sample(logits, p, temperature=1.0, seed=0):
     """Top-p (nucleus) sampling: Gumbel-max from the smallest top-probability set with mass >= p."""
     return _sample_logits(logits, 3, "top_p_sample", p=p, temperature=temperature, seed=seed)
+
+
+def _check_head_weight(h, W, format, name: str):
+    """The reference's check_masked_lm_weight (torch_kernels.mm:6625-6653): returns (V, K)."""
+    _check(h.is_cuda and W.is_cuda and h.dtype in _DT and h.dim() == 2 and h.size(0) > 0 and h.size(1) > 0,
+           f"{name}: h must be non-empty (T,K) fp32/fp16/bf16")
+    K = h.size(1)
+    if format == "":
+        _check(W.dtype == h.dtype and W.dim() == 2 and W.size(0) > 0 and W.size(1) == K,
+               f"{name}: dense weight must be (V,K) with h dtype")
+        return W.size(0), K
+    _check(format in _BLOCK, f"{name}: format must be empty/dense, q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4")
+    bk, bb = _BLOCK[format]
+    _check(W.dtype == torch.uint8 and W.dim() == 3 and W.size(0) > 0 and K % bk == 0
+           and W.size(1) == K // bk and W.size(2) == bb, f"{name}: invalid packed weight shape")
+    return W.size(0), K
+
+
+def lm_head_masked(h, W, bias, allow_mask, format="", topk=1, normalize_allowed=True):
+    """Masked dense / packed LM head: (ids int32 (T,topk), logprobs fp32 (T,topk)) of the topk best
+    tokens admitted by allow_mask (T, ceil(V/32)) packed 32-bit words; logprobs are normalised over
+    the admitted tokens, or over the whole vocabulary when normalize_allowed is false."""
+    fmt, topk = str(format), int(topk)
+    V, K = _check_head_weight(h, W, fmt, "lm_head_masked")
+    T = h.size(0)
+    _check(1 <= topk <= 8 and topk <= V, "lm_head_masked: topk must be in [1,min(8,V)]")
+    words = (V + 31) // 32
+    _check(allow_mask.is_cuda and allow_mask.dim() == 2 and allow_mask.size(0) == T and allow_mask.size(1) == words,
+           "lm_head_masked: allow_mask must be (T,ceil(V/32))")
+    use_bias = bias is not None and bias.numel() > 1
+    _check(not use_bias or (bias.dim() == 1 and bias.size(0) == V),
+           "lm_head_masked: bias must be (V,) or scalar placeholder")
+    _same_device("lm_head_masked", h, W, allow_mask, bias if use_bias else None)
+    with torch.cuda.device(h.device):
+        hc, wc = h.contiguous(), W.contiguous()
+        bc = bias.to(torch.float32).contiguous() if use_bias else None
+        mc = allow_mask.to(torch.int32).contiguous()
+        ids = torch.empty((T, topk), dtype=torch.int32, device=h.device)
+        lp = torch.empty((T, topk), dtype=torch.float32, device=h.device)
+        L = _lib.lib()
+        nbytes = L.qx_cuda_lm_head_masked_workspace_bytes(T, V, K, topk)
+        ws = _workspace(h.device, nbytes)
+        _lib.check(L.qx_cuda_lm_head_masked(
+            _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(mc), _ptr(ids), _ptr(lp), _ptr(ws), nbytes, T, V, K,
+            fmt.encode(), _DT[h.dtype], topk, int(bool(normalize_allowed))))
+    return ids, lp
+
+
+def lm_head_candidates(h, W, bias, candidate_ids, offsets, format="", topk=1):
+    """CSR candidate dense / packed LM head: only the listed tokens are projected; returns their topk
+    (ids, logprobs) per row, log-probabilities normalised over the valid listed tokens."""
+    fmt, topk = str(format), int(topk)
+    V, K = _check_head_weight(h, W, fmt, "lm_head_candidates")
+    T = h.size(0)
+    _check(1 <= topk <= 8 and topk <= V, "lm_head_candidates: topk must be in [1,min(8,V)]")
+    _check(candidate_ids.is_cuda and offsets.is_cuda and candidate_ids.dim() == 1 and offsets.dim() == 1
+           and offsets.size(0) == T + 1, "lm_head_candidates: flat candidate_ids and T+1 offsets required")
+    use_bias = bias is not None and bias.numel() > 1
+    _check(not use_bias or (bias.dim() == 1 and bias.size(0) == V),
+           "lm_head_candidates: bias must be (V,) or scalar placeholder")
+    _same_device("lm_head_candidates", h, W, candidate_ids, offsets, bias if use_bias else None)
+    with torch.cuda.device(h.device):
+        hc, wc = h.contiguous(), W.contiguous()
+        bc = bias.to(torch.float32).contiguous() if use_bias else None
+        cc, oc = candidate_ids.to(torch.int32).contiguous(), offsets.to(torch.int32).contiguous()
+        entries = cc.numel()
+        ids = torch.empty((T, topk), dtype=torch.int32, device=h.device)
+        lp = torch.empty((T, topk), dtype=torch.float32, device=h.device)
+        nbytes = max(entries, 1) * 4 + 256
+        ws = _workspace(h.device, nbytes)
+        _lib.check(_lib.lib().qx_cuda_lm_head_candidates(
+            _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(cc), _ptr(oc), entries, _ptr(ids), _ptr(lp), _ptr(ws),
+            nbytes, T, V, K, fmt.encode(), _DT[h.dtype], topk))
+    return ids, lp
+
+
+def lm_head_beam_advance(h, Wq, bias, cum_log_probs, beam_width, fmt="q4_0"):
+    """Quantized LM head + exact beam-search advance without full logits: h (B*BM, K), cum_log_probs
+    (B, BM) -> (next_token, parent_beam, new cumulative log-probability), each (B, BM)."""
+    fmt, BM = str(fmt), int(beam_width)
+    _check(h.is_cuda and Wq.is_cuda and cum_log_probs.is_cuda and h.dtype in _DT,
+           "lm_head_beam_advance: inputs must be CUDA and h floating point")
+    _check(h.dim() == 2 and h.size(0) > 0 and h.size(1) > 0, "lm_head_beam_advance: h must be non-empty (B*BM,K)")
+    _check(fmt in ("q4_0", "q8_0", "mxfp8", "nvfp4", "mxfp4"),
+           "lm_head_beam_advance: format must be q4_0, q8_0, mxfp8, nvfp4, or mxfp4")
+    _check(1 <= BM <= 16, "lm_head_beam_advance: beam_width must be in [1,16]")
+    rows, K = h.shape
+    bk, bb = _BLOCK[fmt]
+    _check(K % bk == 0 and Wq.dtype == torch.uint8 and Wq.dim() == 3 and Wq.size(0) > 0
+           and Wq.size(1) == K // bk and Wq.size(2) == bb,
+           "lm_head_beam_advance: packed W has invalid shape for its format")
+    _check(cum_log_probs.dim() == 2 and cum_log_probs.size(1) == BM and rows == cum_log_probs.size(0) * BM,
+           "lm_head_beam_advance: cum_log_probs must be (B,BM), h rows B*BM")
+    B, V = cum_log_probs.size(0), Wq.size(0)
+    _check(V >= 2 * BM, "lm_head_beam_advance: vocab must be >= 2*beam_width")
+    use_bias = bias is not None and bias.numel() > 1
+    _check(not use_bias or (bias.dim() == 1 and bias.size(0) == V),
+           "lm_head_beam_advance: bias must be (V,) or a scalar placeholder")
+    _same_device("lm_head_beam_advance", h, Wq, cum_log_probs, bias if use_bias else None)
+    with torch.cuda.device(h.device):
+        hc, wc = h.contiguous(), Wq.contiguous()
+        bc = bias.to(torch.float32).contiguous() if use_bias else None
+        cc = cum_log_probs.to(torch.float32).contiguous()
+        tok = torch.empty((B, BM), dtype=torch.int32, device=h.device)
+        par = torch.empty((B, BM), dtype=torch.int32, device=h.device)
+        new = torch.empty((B, BM), dtype=torch.float32, device=h.device)
+        L = _lib.lib()
+        nbytes = L.qx_cuda_lm_head_beam_workspace_bytes(rows, V, K, BM)
+        ws = _workspace(h.device, nbytes)
+        _lib.check(L.qx_cuda_lm_head_beam_advance(
+            _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(cc), _ptr(tok), _ptr(par), _ptr(new), _ptr(ws), nbytes,
+            B, BM, V, K, fmt.encode(), _DT[h.dtype]))
+    return tok, par, new

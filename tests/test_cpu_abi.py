@@ -230,6 +230,9 @@ _SIGNATURES = {
     "decode_swiglu": ["x", "gate_weight", "up_weight", "gate_bias", "up_bias", "format=''", "use_bias=False"],
     "lm_head_sample": ["h", "W", "bias", "mode", "k", "temperature", "seed"],
     "lm_head_sample_q": ["h", "Wq", "bias", "V", "K", "fmt", "mode", "topk", "temperature", "seed", "top_p=0.0"],
+    "lm_head_beam_advance": ["h", "Wq", "bias", "cum_log_probs", "beam_width", "fmt='q4_0'"],
+    "lm_head_masked": ["h", "W", "bias", "allow_mask", "format=''", "topk=1", "normalize_allowed=True"],
+    "lm_head_candidates": ["h", "W", "bias", "candidate_ids", "offsets", "format=''", "topk=1"],
     "quantize_per_token_fp8": ["x"],
     "quantize_per_token_int8": ["x"],
     "argmax_sample": ["logits"],

@@ -175,3 +175,36 @@ def test_sampler_modes_small():
     # all-equal logits: ties resolve to the lowest id (topk.metal:34-53 tie rule)
     Z = np.zeros((1, 40), np.float32)
     assert O.lm_head_sample_from_logits(Z, 0)[0] == 0
+
+
+# ---- log-probability forms: the restated reference test oracles behave as the reference tests pin ----
+def test_topk_logprobs_ties_padding_and_normalisers():
+    from oracle import qx_oracle as O
+    # all-equal logits: ids ascending, logprob -log(n) (tests/.../test_lm_head.py:420-427)
+    ids, lp = O.topk_logprobs(np.zeros(40, np.float32), [31, 7, 19, 3], 4)
+    np.testing.assert_array_equal(ids, [3, 7, 19, 31])
+    np.testing.assert_allclose(lp, -np.log(4.0), atol=1e-7)
+    # invalid ids skipped, short rows padded (:464-482)
+    logits = np.arange(10, dtype=np.float32)
+    ids, lp = O.topk_logprobs(logits, [4, -1, 10], 3)
+    np.testing.assert_array_equal(ids, [4, -1, -1])
+    assert lp[0] == 0.0 and np.isneginf(lp[1:]).all()
+    # full-vocabulary normaliser makes the admitted mass less than one
+    ids, lp = O.topk_logprobs(logits, [9, 8], 2, normalizer_ids=np.arange(10))
+    assert np.exp(lp.astype(np.float64)).sum() < 1.0 and ids.tolist() == [9, 8]
+    mask = O.packed_allow_mask([[0, 31, 32, 63], []], 64)
+    assert mask.tolist() == [[0x80000001, 0x80000001], [0, 0]]
+
+
+def test_beam_advance_oracle_first_step():
+    from oracle import qx_oracle as O
+    rng = np.random.default_rng(1)
+    logits = rng.standard_normal((4, 50)).astype(np.float32)           # B = 2, BM = 2
+    cum = np.array([[0.0, -np.inf], [0.0, -np.inf]], np.float32)
+    tok, par, score = O.lm_head_beam_advance_from_logits(logits, cum, 2)
+    assert (par == 0).all()
+    for b in range(2):
+        row = logits[2 * b].astype(np.float64)
+        lsm = row - (row.max() + np.log(np.exp(row - row.max()).sum()))
+        np.testing.assert_array_equal(tok[b], np.argsort(-lsm, kind="stable")[:2])
+        np.testing.assert_allclose(score[b], np.sort(lsm)[::-1][:2], rtol=1e-6)
