@@ -267,6 +267,28 @@ qx_status qx_cuda_sample_logits(void* stream, const void* logits, int32_t* ids, 
                                 qx_dtype dtype, int kind, int topk, double top_p, double temperature,
                                 uint32_t seed);
 
+/* ---- the operators either side of the path ----------------------------------------------------- */
+
+/* out (N, M) = dequantise(wq) (N, K) @ x (K, M), x / out in `dtype` (float16 in the reference; M == 1
+ * is qgemv, where float32 is accepted as well).  The activation matrix is column-major per token as
+ * in the reference; the call transposes it into the row layout of the projection kernels and the
+ * result back, inside the workspace.  Exact fp32 dequantisation and accumulation, one rounding.
+ * Replaces qgemv_mps / qgemm_mps (torch_kernels.mm:5616-5640, :5682-5712; qgemv.metal:13-45,
+ * qgemm.metal:11-50), without their N % 32 / M % 32 restrictions. */
+size_t qx_cuda_qgemm_workspace_bytes(int64_t N, int64_t K, int64_t M, const char* format, qx_dtype dtype);
+qx_status qx_cuda_qgemm(void* stream, const void* wq, const void* x, void* out, int64_t N, int64_t K,
+                        int64_t M, const char* format, qx_dtype dtype, void* workspace,
+                        size_t workspace_bytes);
+
+/* Packed embedding lookup: out (tokens, columns) = T(dequantise(table[ids[t]]) * scale (+ add[t])),
+ * fp32 arithmetic, one rounding; ids outside [0, rows) give all-zero rows and ignore `add`.
+ * table uint8 (rows, columns/block_k, block_bytes), ids int32 (tokens,), add / out in out_dtype.
+ * Replaces dequant_gather_mps / quantized_embedding_mps (torch_kernels.mm:6468-6546;
+ * dequant_gather.metal:10-105) for the six formats of this backend. */
+qx_status qx_cuda_quantized_embedding(void* stream, const void* table, const int32_t* ids, const void* add,
+                                      void* out, int64_t rows, int64_t columns, int64_t tokens,
+                                      const char* format, double scale, int use_add, qx_dtype out_dtype);
+
 /* ---- LM-head forms that return log-probabilities ------------------------------------------------
  * format NULL or "" = dense W (V,K) in the dtype of h; otherwise a packed head.  Raw logits (no
  * temperature); ordering: logit descending, ties to the smaller token id; bias fp32 (V,) or NULL.

@@ -394,6 +394,63 @@ qx_status qx_cuda_sample_logits(void* stream, const void* logits, int32_t* ids, 
   return check_launch(op);
 }
 
+// ---- the operators either side of the path: qgemv / qgemm, packed embedding lookup ------------------
+size_t qx_cuda_qgemm_workspace_bytes(int64_t N, int64_t K, int64_t M, const char* format, qx_dtype dtype) {
+  if (N <= 0 || K <= 0 || M <= 0) return 0;
+  const size_t es = dtype == QX_DTYPE_F32 ? 4 : 2;
+  const size_t proj = qx_cuda_projection_workspace_bytes(M, K, N, format, dtype, 0);
+  if (M == 1) return proj;                                  // (K,1) and (N,1) are already the row layout
+  return align256((size_t)M * K * es) + align256((size_t)M * N * es) + proj;
+}
+
+qx_status qx_cuda_qgemm(void* stream, const void* wq, const void* x, void* out, int64_t N, int64_t K,
+                        int64_t M, const char* format, qx_dtype dtype, void* workspace,
+                        size_t workspace_bytes) {
+  const char* op = M == 1 ? "qgemv" : "qgemm";
+  if (dtype != QX_DTYPE_F16 && dtype != QX_DTYPE_F32 && dtype != QX_DTYPE_BF16)
+    return fail(QX_UNSUPPORTED_DTYPE, op, "x must be float16 (float32 / bfloat16 are accepted too)");
+  int f = -1;
+  qx_status st = check_projection(op, x, wq, out, M, K, N, format, dtype, &f);
+  if (st.code != QX_OK) return st;
+  const size_t need = qx_cuda_qgemm_workspace_bytes(N, K, M, format, dtype);
+  if (need && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255) != 0))
+    return fail(QX_INSUFFICIENT_WORKSPACE, op, "workspace must be 256-byte aligned and at least qx_cuda_qgemm_workspace_bytes");
+  if (!device_ready(op, &st)) return st;
+  const size_t es = dtype == QX_DTYPE_F32 ? 4 : 2;
+  const void* xr = x;
+  void* yr = out;
+  char* ws = (char*)workspace;
+  if (M > 1) {
+    launch_transpose((cudaStream_t)stream, x, ws, K, M, es);           // (K, M) -> (M, K)
+    xr = ws;
+    yr = ws + align256((size_t)M * K * es);
+    ws = (char*)yr + align256((size_t)M * N * es);
+  }
+  GemvArgs a{xr, wq, nullptr, nullptr, nullptr, nullptr, yr, M, K, N, f, dtype, 0, 0, 0};
+  a.scratch = ws;
+  a.scratch_bytes = workspace ? workspace_bytes - (size_t)(ws - (char*)workspace) : 0;
+  launch_projection((cudaStream_t)stream, a);
+  if (M > 1) launch_transpose((cudaStream_t)stream, yr, out, M, N, es);  // (M, N) -> (N, M)
+  return check_launch(op);
+}
+
+qx_status qx_cuda_quantized_embedding(void* stream, const void* table, const int32_t* ids, const void* add,
+                                      void* out, int64_t rows, int64_t columns, int64_t tokens,
+                                      const char* format, double scale, int use_add, qx_dtype out_dtype) {
+  static const char* op = "quantized_embedding";
+  if (!float_dtype(out_dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "output_dtype must be 'float16', 'bfloat16', or 'float32'");
+  const int f = parse_format(format);
+  if (f < 0) return fail(QX_UNSUPPORTED_FORMAT, op, "format must be q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4");
+  if (!table || !ids || !out || (use_add && !add)) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (rows <= 0 || columns <= 0 || tokens <= 0 || columns % block_k_of(f) != 0 || rows > 0x7fffffff || columns > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "table must be packed uint8 (rows,blocks,block_bytes)");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  launch_quantized_embedding((cudaStream_t)stream, f, out_dtype, table, ids, add, out, rows, columns, tokens,
+                             (float)scale, use_add ? 1 : 0);
+  return check_launch(op);
+}
+
 // ---- masked / candidate / beam forms of the LM head ------------------------------------------------
 static bool dense_format(const char* format) { return !format || format[0] == '\0'; }
 

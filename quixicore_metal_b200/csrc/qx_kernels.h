@@ -138,6 +138,13 @@ void launch_lm_head_candidate_logits(cudaStream_t st, int format, qx_dtype dtype
 void launch_beam_select(cudaStream_t st, const float* cand_score, const int32_t* cand_token, int32_t* next_token,
                         int32_t* parent_beam, float* new_cum, int64_t batches, int BM, int two_bm);
 
+// Packed embedding lookup: out (tokens, columns) = T(dequant(table[ids]) * scale (+ add)); see qx_gather.cu.
+void launch_quantized_embedding(cudaStream_t st, int format, qx_dtype out_dtype, const void* table, const int32_t* ids,
+                                const void* add, void* out, int64_t rows, int64_t columns, int64_t tokens, float scale,
+                                int use_add);
+// out (C, R) = in (R, C)^T for 2- or 4-byte elements.
+void launch_transpose(cudaStream_t st, const void* in, void* out, int64_t R, int64_t C, size_t elem_bytes);
+
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);
 void launch_quantize_mxfp8_rows(cudaStream_t st, const void* x, void* blocks, int64_t rows,

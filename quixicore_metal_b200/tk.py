@@ -155,3 +155,36 @@ def lm_head_beam_advance(h, W, cum_log_probs, beam_width, bias=None, format="q4_
     import torch
     b = bias if bias is not None else torch.zeros(1, dtype=torch.float32, device=h.device)
     return _tt.lm_head_beam_advance(h, W, b, cum_log_probs, int(beam_width), str(format))
+
+
+def qgemv(wq, x, format="q8_0"):
+    """Quantized GEMV (batch-1 decode): out = dequantize(wq) @ x.  wq packed weight blocks
+    (N, K//block_k, block_bytes) uint8; x (K, 1) float16 (or fp32).  (tk/__init__.py:3887-3893)"""
+    return _tt.qgemv(wq, x, format)
+
+
+def qgemm(wq, x, format="q8_0"):
+    """Quantized GEMM: out = dequantize(wq) @ x; x (K, M) float16 -> (N, M) float16.  Batch 1 goes to
+    the GEMV path.  (tk/__init__.py:3179-3187)"""
+    if x.shape[-1] == 1:
+        return qgemv(wq, x, format)
+    return _tt.qgemm(wq, x, format)
+
+
+def dequant_gather(table, ids, format, scale=1.0):
+    """Gather packed q4_0/q8_0/q6_K rows directly to fp16; invalid ids yield zero rows.
+    (tk/__init__.py:4132-4136)"""
+    return _tt.dequant_gather(table, ids, format, float(scale))
+
+
+def quantized_embedding_lookup(table, ids, format, scale=1.0, add=None, output_dtype="float16"):
+    """Gather packed embedding rows into fp16, bf16 or fp32 output; `add` is an optional output-shaped
+    positional / residual term.  Invalid ids produce all-zero rows and ignore `add`.
+    (tk/__init__.py:4139-4160)"""
+    if output_dtype not in ("float16", "bfloat16", "float32"):
+        raise ValueError("output_dtype must be 'float16', 'bfloat16', or 'float32'")
+    import torch
+    use_add = add is not None
+    dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}[output_dtype]
+    additive = add.to(dtype) if use_add else torch.zeros(1, dtype=dtype, device=table.device)
+    return _tt.quantized_embedding(table, ids, additive, format, float(scale), use_add, output_dtype)

@@ -429,3 +429,73 @@ def lm_head_beam_advance(h, Wq, bias, cum_log_probs, beam_width, fmt="q4_0"):
             _stream(), _ptr(hc), _ptr(wc), _ptr(bc), _ptr(cc), _ptr(tok), _ptr(par), _ptr(new), _ptr(ws), nbytes,
             B, BM, V, K, fmt.encode(), _DT[h.dtype]))
     return tok, par, new
+
+
+def _qgemm(wq, x, format, name):
+    fmt = str(format)
+    _check(wq.is_cuda and x.is_cuda, f"{name}: wq and x must be CUDA tensors")
+    _check(wq.dtype == torch.uint8, f"{name}: wq must be uint8 packed blocks")
+    _check(x.dtype in _DT, f"{name}: x must be float16 (float32 / bfloat16 are accepted too)")
+    _check(fmt in _BLOCK, f"{name}: format must be q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4")
+    _check(wq.dim() == 3 and x.dim() == 2, f"{name}: wq (N,K/bk,bytes), x (K,M)")
+    bk, bb = _BLOCK[fmt]
+    N, K = wq.size(0), wq.size(1) * bk
+    _check(wq.size(2) == bb and x.size(0) == K and N > 0 and K > 0 and x.size(1) > 0,
+           f"{name}: wq (N,K/bk,bytes), x (K,M) with x rows == K")
+    _same_device(name, wq, x)
+    M = x.size(1)
+    with torch.cuda.device(x.device):
+        wc, xc = wq.contiguous(), x.contiguous()
+        out = torch.empty((N, M), dtype=x.dtype, device=x.device)
+        L = _lib.lib()
+        nbytes = L.qx_cuda_qgemm_workspace_bytes(N, K, M, fmt.encode(), _DT[x.dtype])
+        ws = _workspace(x.device, nbytes)
+        _lib.check(L.qx_cuda_qgemm(_stream(), _ptr(wc), _ptr(xc), _ptr(out), N, K, M, fmt.encode(), _DT[x.dtype],
+                                   _ptr(ws), nbytes))
+    return out
+
+
+def qgemm(wq, x, format="q8_0"):
+    """Quantized GEMM: out = dequantize(wq) @ x.  wq packed weight blocks (N, K//block_k, block_bytes)
+    uint8; x (K, M) float16 -> (N, M) float16."""
+    return _qgemm(wq, x, format, "qgemm")
+
+
+def qgemv(wq, x, format="q8_0"):
+    """Quantized GEMV.  x is (K, 1) float16, or fp32 for q4_0 / q6_K (any format here)."""
+    _check(x.dim() == 2 and x.size(1) == 1, "qgemv: wq (N,K/bk,bytes), x (K,1)")
+    return _qgemm(wq, x, format, "qgemv")
+
+
+def quantized_embedding(table, ids, add, format, scale=1.0, use_add=False, output_dtype="float16"):
+    """Packed embedding lookup with optional additive epilogue: rows of the packed table gathered by
+    ids, dequantised in fp32, times scale (+ add), rounded once to output_dtype.  Invalid ids give
+    all-zero rows and ignore add."""
+    fmt = str(format)
+    names = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
+    _check(output_dtype in names, "quantized_embedding: output_dtype must be 'float16', 'bfloat16', or 'float32'")
+    _check(fmt in _BLOCK, "quantized_embedding: format must be q4_0, q8_0, q6_K, mxfp8, nvfp4, or mxfp4")
+    bk, bb = _BLOCK[fmt]
+    _check(table.is_cuda and ids.is_cuda and table.dtype == torch.uint8 and table.dim() == 3 and table.size(0) > 0
+           and table.size(1) > 0 and table.size(2) == bb and ids.numel() > 0,
+           "quantized_embedding: table must be packed uint8 (rows,blocks,block_bytes)")
+    dtype = names[output_dtype]
+    rows, columns = table.size(0), table.size(1) * bk
+    shape = tuple(ids.shape) + (columns,)
+    _check(not use_add or (add.dtype == dtype and tuple(add.shape) == shape),
+           "quantized_embedding: add must match output shape and output_dtype")
+    _same_device("quantized_embedding", table, ids, add if use_add else None)
+    with torch.cuda.device(table.device):
+        tc, ic = table.contiguous(), ids.to(torch.int32).contiguous()
+        ac = add.contiguous() if use_add else None
+        out = torch.empty(shape, dtype=dtype, device=table.device)
+        _lib.check(_lib.lib().qx_cuda_quantized_embedding(
+            _stream(), _ptr(tc), _ptr(ic), _ptr(ac), _ptr(out), rows, columns, ic.numel(), fmt.encode(),
+            float(scale), int(bool(use_add)), _DT[dtype]))
+    return out
+
+
+def dequant_gather(table, ids, format, scale=1.0):
+    """Gather packed q4_0 / q8_0 / q6_K rows directly to fp16; invalid ids yield zero rows."""
+    _check(str(format) in ("q4_0", "q8_0", "q6_K"), "dequant_gather: format must be q4_0, q8_0, or q6_K")
+    return quantized_embedding(table, ids, None, format, scale, False, "float16")

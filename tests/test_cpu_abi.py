@@ -233,6 +233,10 @@ _SIGNATURES = {
     "lm_head_beam_advance": ["h", "Wq", "bias", "cum_log_probs", "beam_width", "fmt='q4_0'"],
     "lm_head_masked": ["h", "W", "bias", "allow_mask", "format=''", "topk=1", "normalize_allowed=True"],
     "lm_head_candidates": ["h", "W", "bias", "candidate_ids", "offsets", "format=''", "topk=1"],
+    "qgemm": ["wq", "x", "format='q8_0'"],
+    "qgemv": ["wq", "x", "format='q8_0'"],
+    "dequant_gather": ["table", "ids", "format", "scale=1.0"],
+    "quantized_embedding": ["table", "ids", "add", "format", "scale=1.0", "use_add=False", "output_dtype='float16'"],
     "quantize_per_token_fp8": ["x"],
     "quantize_per_token_int8": ["x"],
     "argmax_sample": ["logits"],
