@@ -289,6 +289,30 @@ qx_status qx_cuda_quantized_embedding(void* stream, const void* table, const int
                                       void* out, int64_t rows, int64_t columns, int64_t tokens,
                                       const char* format, double scale, int use_add, qx_dtype out_dtype);
 
+/* ---- norm / activation -> quantiser seams ------------------------------------------------------
+ * What feeds quantised activations into a projection.  fp32 arithmetic on the I/O-dtype inputs.
+ * quant: 0 none, 1 fp8 static per tensor, 2 fp8 dynamic per row (scale = amax/448), 3 int8 dynamic
+ * per row (amax/127), 4 fp8 per block of `group` columns, 5 int8 per block; ue8m0 != 0 rounds the
+ * fp8 block scales up to powers of two.  e4m3 codes round halves away from zero and saturate at 448.
+ */
+
+/* res_out = T(x + residual); n = rms_norm(x + residual) * weight on the unrounded fp32 sum;
+ * quant 0: y = T(n); otherwise codes (rows, D) of n and, for quant >= 2, scale (rows,) or
+ * (rows, D / group).  Replaces rms_norm_add / rms_norm_add_fp8 / _fp8_dyn / _int8_dyn /
+ * rms_norm_add_per_block (kernels/norms/add_norm/add_norm.metal:26-65, :181-392), for any D up to
+ * 51200 and f32 / f16 / bf16 (the Metal kernels: bf16, D in a fixed list). */
+qx_status qx_cuda_rms_norm_add(void* stream, const void* x, const void* residual, const void* weight, void* y,
+                               void* codes, void* res_out, float* scale, int64_t rows, int64_t D, qx_dtype dtype,
+                               double eps, int quant, double static_scale, int group, int ue8m0);
+
+/* codes = quantise(act(x, gate)) without the (rows, D) intermediate: act 0 = silu(x) * gate, 1 = the
+ * clamped variant x' = min(x, limit), g' = clamp(gate, +-limit), x' * sigmoid(alpha x') * (1 + g').
+ * quant 2 / 3 / 4 as above (group % 4 == 0).  Replaces silu_mul_quant_fp8 / _int8 / _fp8_group
+ * (kernels/quantization/act_quant/act_quant.metal:26-160). */
+qx_status qx_cuda_silu_mul_quant(void* stream, const void* x, const void* gate, void* codes, float* scale,
+                                 int64_t rows, int64_t D, qx_dtype dtype, int act, double alpha, double limit,
+                                 int quant, int group, int ue8m0);
+
 /* ---- LM-head forms that return log-probabilities ------------------------------------------------
  * format NULL or "" = dense W (V,K) in the dtype of h; otherwise a packed head.  Raw logits (no
  * temperature); ordering: logit descending, ties to the smaller token id; bias fp32 (V,) or NULL.

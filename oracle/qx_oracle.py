@@ -716,3 +716,49 @@ def lm_head_beam_advance_from_logits(logits: np.ndarray, cum: np.ndarray, beam_w
     flat = flat.reshape(B, BM * V)
     sel = np.argsort(-flat, axis=1, kind="stable")[:, :BM]
     return (sel % V).astype(np.int32), (sel // V).astype(np.int32), np.take_along_axis(flat, sel, axis=1).astype(np.float32)
+
+
+# ----------------------------------------------------------------------------------------------
+# Norm / activation -> quantiser seams.  kernels/norms/add_norm/add_norm.metal:26-65, :181-392;
+# kernels/quantization/act_quant/act_quant.metal:26-160; include/metal/common/glu_eval.metal:49-66.
+# ----------------------------------------------------------------------------------------------
+def rms_norm_add(x, residual, weight, eps=1e-5, dtype="bf16"):
+    """(normalised fp32 row values BEFORE any rounding, x + residual rounded to dtype).  The norm runs
+    on the unrounded fp32 sum: n = ((x + r) * rsqrt(mean((x + r)^2) + eps)) * w."""
+    h = (np.asarray(x, np.float32) + np.asarray(residual, np.float32)).astype(np.float32)
+    ms = (h.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
+    inv = (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+    n = ((h * inv).astype(np.float32) * np.asarray(weight, np.float32)).astype(np.float32)
+    return n, round_to(h, dtype)
+
+
+def gated_act(act: str, x, gate, alpha=1.702, limit=7.0):
+    """swiglu: silu(x) * gate; swiglu_oai: x' = min(x, limit), g' = clip(gate, +-limit),
+    x' * sigmoid(alpha x') * (1 + g')  (tests/correctness/quantization/act_quant/test_act_quant.py:19-26)."""
+    x = np.asarray(x, np.float64); g = np.asarray(gate, np.float64)
+    if act == "swiglu_oai":
+        x = np.minimum(x, limit); g = np.clip(g, -limit, limit)
+        return ((x / (1.0 + np.exp(-x * alpha))) * (1.0 + g)).astype(np.float32)
+    return ((x / (1.0 + np.exp(-x))) * g).astype(np.float32)
+
+
+def quantize_groups(v: np.ndarray, group: int, kind: str = "fp8", ue8m0: bool = False):
+    """Per group of `group` columns: s = amax / qmax (fp8, ue8m0: 2^ceil(log2(max(amax, 1e-10) / 448))
+    when amax > 0); inv = 1/s (0 when s == 0); codes = encode(v * inv).  Returns (codes, scale (.., D/G)).
+    group == D gives the per-row quantisers."""
+    f = np.float32
+    v = np.asarray(v, f)
+    D = v.shape[-1]
+    b = v.reshape(v.shape[:-1] + (D // group, group))
+    amax = np.abs(b).max(-1)
+    qmax = f(448.0) if kind == "fp8" else f(127.0)
+    s = (amax / qmax).astype(f)
+    if ue8m0 and kind == "fp8":
+        q = (np.maximum(amax, f(1e-10)) / qmax).astype(f)
+        e = np.ceil(np.log2(q.astype(np.float64)))
+        s = np.where(amax > 0, np.exp2(e), s).astype(f)
+    with np.errstate(divide="ignore"):
+        inv = np.where(s > 0, (f(1.0) / s).astype(f), f(0.0)).astype(f)
+    scaled = (b * inv[..., None]).astype(f)
+    codes = e4m3_encode_device(scaled) if kind == "fp8" else int8_encode(scaled)
+    return codes.reshape(v.shape), s

@@ -71,6 +71,10 @@ def lib() -> C.CDLL:
     L.qx_cuda_lm_head_sample_dense.argtypes = [vp, vp, vp, vp, vp, vp, sz, i64, i64, i64, i32, i32, i32, f64, u32]
     L.qx_cuda_sample_logits.restype = Status
     L.qx_cuda_sample_logits.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, f64, f64, u32]
+    L.qx_cuda_rms_norm_add.restype = Status
+    L.qx_cuda_rms_norm_add.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f64, i32, f64, i32, i32]
+    L.qx_cuda_silu_mul_quant.restype = Status
+    L.qx_cuda_silu_mul_quant.argtypes = [vp, vp, vp, vp, vp, i64, i64, i32, i32, f64, f64, i32, i32, i32]
     L.qx_cuda_qgemm_workspace_bytes.restype = sz
     L.qx_cuda_qgemm_workspace_bytes.argtypes = [i64, i64, i64, cs, i32]
     L.qx_cuda_qgemm.restype = Status

@@ -451,6 +451,47 @@ qx_status qx_cuda_quantized_embedding(void* stream, const void* table, const int
   return check_launch(op);
 }
 
+// ---- norm / activation -> quantiser seams ---------------------------------------------------------
+qx_status qx_cuda_rms_norm_add(void* stream, const void* x, const void* residual, const void* weight, void* y,
+                               void* codes, void* res_out, float* scale, int64_t rows, int64_t D, qx_dtype dtype,
+                               double eps, int quant, double static_scale, int group, int ue8m0) {
+  static const char* op = "rms_norm_add";
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "x must be fp32/fp16/bf16");
+  if (!x || !residual || !weight || !res_out) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (rows <= 0 || D <= 0 || rows > 0x7fffffff || D > 51200) return fail(QX_INVALID_SHAPE, op, "x must be (rows, D) with 0 < D <= 51200");
+  if (quant < 0 || quant > 5) return fail(QX_INVALID_ARGUMENT, op, "quant: 0 none, 1 fp8 static, 2 fp8 per row, 3 int8 per row, 4 fp8 per block, 5 int8 per block");
+  if (quant == 0 && !y) return fail(QX_INVALID_ARGUMENT, op, "null output pointer");
+  if (quant != 0 && !codes) return fail(QX_INVALID_ARGUMENT, op, "null codes pointer");
+  if (quant >= 2 && !scale) return fail(QX_INVALID_ARGUMENT, op, "null scale pointer");
+  if (quant == 1 && !(static_scale > 0.0)) return fail(QX_INVALID_ARGUMENT, op, "static scale must be positive");
+  if (quant >= 4 && (group <= 0 || D % group != 0)) return fail(QX_INVALID_SHAPE, op, "per-block quant requires D % block == 0");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  if (!launch_rms_norm_add((cudaStream_t)stream, dtype, x, residual, weight, y, codes, res_out, scale, rows, D, (float)eps,
+                           quant, quant == 1 ? (float)(1.0 / static_scale) : 0.f, group, ue8m0 ? 1 : 0))
+    return fail(QX_RUNTIME_ERROR, op, "kernel configuration failed");
+  return check_launch(op);
+}
+
+qx_status qx_cuda_silu_mul_quant(void* stream, const void* x, const void* gate, void* codes, float* scale,
+                                 int64_t rows, int64_t D, qx_dtype dtype, int act, double alpha, double limit,
+                                 int quant, int group, int ue8m0) {
+  static const char* op = "silu_mul_quant";
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "x must be fp32/fp16/bf16");
+  if (!x || !gate || !codes || !scale) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (rows <= 0 || D <= 0 || rows > 0x7fffffff || D > 51200) return fail(QX_INVALID_SHAPE, op, "x must be (rows, D) with 0 < D <= 51200");
+  if (act < 0 || act > 1) return fail(QX_INVALID_ARGUMENT, op, "act: 0 swiglu, 1 swiglu_oai");
+  if (quant < 2 || quant > 4) return fail(QX_INVALID_ARGUMENT, op, "quant: 2 fp8 per token, 3 int8 per token, 4 fp8 per group");
+  if (quant == 4 && (group <= 0 || group % 4 != 0 || D % group != 0))
+    return fail(QX_INVALID_SHAPE, op, "group_size must be a multiple of 4 that divides D");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  if (!launch_silu_mul_quant((cudaStream_t)stream, dtype, x, gate, codes, scale, rows, D, act, (float)alpha, (float)limit,
+                             quant, group, ue8m0 ? 1 : 0))
+    return fail(QX_RUNTIME_ERROR, op, "kernel configuration failed");
+  return check_launch(op);
+}
+
 // ---- masked / candidate / beam forms of the LM head ------------------------------------------------
 static bool dense_format(const char* format) { return !format || format[0] == '\0'; }
 

@@ -145,6 +145,14 @@ void launch_quantized_embedding(cudaStream_t st, int format, qx_dtype out_dtype,
 // out (C, R) = in (R, C)^T for 2- or 4-byte elements.
 void launch_transpose(cudaStream_t st, const void* in, void* out, int64_t R, int64_t C, size_t elem_bytes);
 
+// Residual add + RMSNorm with optional quantising tail, gated activation to codes: see qx_seams.cu.
+// qmode: 0 none, 1 fp8 static, 2 fp8 per row, 3 int8 per row, 4 fp8 per group, 5 int8 per group.
+bool launch_rms_norm_add(cudaStream_t st, qx_dtype dtype, const void* x, const void* residual, const void* weight,
+                         void* y, void* codes, void* res_out, float* scale, int64_t rows, int64_t D, float eps,
+                         int qmode, float inv_static, int G, int pow2);
+bool launch_silu_mul_quant(cudaStream_t st, qx_dtype dtype, const void* x, const void* gate, void* codes, float* scale,
+                           int64_t rows, int64_t D, int act, float alpha, float limit, int qmode, int G, int pow2);
+
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);
 void launch_quantize_mxfp8_rows(cudaStream_t st, const void* x, void* blocks, int64_t rows,

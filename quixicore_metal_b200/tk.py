@@ -188,3 +188,35 @@ def quantized_embedding_lookup(table, ids, format, scale=1.0, add=None, output_d
     dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}[output_dtype]
     additive = add.to(dtype) if use_add else torch.zeros(1, dtype=dtype, device=table.device)
     return _tt.quantized_embedding(table, ids, additive, format, float(scale), use_add, output_dtype)
+
+
+# ---- norm / activation -> quantiser seams (bindings/python/tk/__init__.py:606-652, :1489-1522) -------
+def rms_norm_add(x, residual, weight, eps=1e-5):
+    """Fused residual-add + RMSNorm.  Returns (out, x + residual)."""
+    return _tt.rms_norm_add(x, residual, weight, eps)
+
+
+def rms_norm_add_fp8(x, residual, weight, eps=1e-5, scale=None):
+    """Fused add + rms_norm + fp8.  scale=None: dynamic per row (codes, x + residual, scale); else
+    static per tensor (codes, x + residual)."""
+    return _tt.rms_norm_add_fp8(x, residual, weight, eps, scale)
+
+
+def rms_norm_add_per_block(x, residual, weight, eps=1e-5, int8=False, ue8m0=False):
+    """Fused add + rms_norm + per-128-block quant: (codes, x + residual, scale (rows, D/128))."""
+    return _tt.rms_norm_add_per_block(x, residual, weight, eps, int8, ue8m0)
+
+
+def silu_mul_quant_fp8(x, gate, act="swiglu", alpha=1.702, limit=7.0):
+    """Fused gated activation -> dynamic per-token fp8 e4m3: (codes u8, scale (rows,))."""
+    return _tt.silu_mul_quant_fp8(x, gate, act=act, alpha=alpha, limit=limit)
+
+
+def silu_mul_quant_int8(x, gate, act="swiglu", alpha=1.702, limit=7.0):
+    """Fused gated activation -> dynamic per-token symmetric int8: (codes i8, scale (rows,))."""
+    return _tt.silu_mul_quant_int8(x, gate, act=act, alpha=alpha, limit=limit)
+
+
+def silu_mul_quant_fp8_group(x, gate, group_size=128, ue8m0=False, act="swiglu", alpha=1.702, limit=7.0):
+    """Fused gated activation -> per-group fp8: (codes u8, scale (rows, D/G))."""
+    return _tt.silu_mul_quant_fp8_group(x, gate, group_size=group_size, ue8m0=ue8m0, act=act, alpha=alpha, limit=limit)

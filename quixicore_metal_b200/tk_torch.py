@@ -499,3 +499,98 @@ def dequant_gather(table, ids, format, scale=1.0):
     """Gather packed q4_0 / q8_0 / q6_K rows directly to fp16; invalid ids yield zero rows."""
     _check(str(format) in ("q4_0", "q8_0", "q6_K"), "dequant_gather: format must be q4_0, q8_0, or q6_K")
     return quantized_embedding(table, ids, None, format, scale, False, "float16")
+
+
+def _rms_norm_add(x, residual, weight, eps, quant, static_scale=0.0, group=0, ue8m0=False, name="rms_norm_add"):
+    _check(x.is_cuda and x.dtype in _DT and x.dim() >= 1 and x.numel() > 0,
+           f"{name}: x must be a non-empty CUDA fp32/fp16/bf16 tensor")
+    D = x.size(-1)
+    _check(residual.shape == x.shape and residual.dtype == x.dtype and weight.dim() == 1 and weight.size(0) == D
+           and weight.dtype == x.dtype, f"{name}: residual must match x, weight must be (D,) with x dtype")
+    _same_device(name, x, residual, weight)
+    rows = x.numel() // D
+    with torch.cuda.device(x.device):
+        xc, rc, wc = x.contiguous(), residual.contiguous(), weight.contiguous()
+        added = torch.empty_like(xc)
+        y = torch.empty_like(xc) if quant == 0 else None
+        codes = scale = None
+        if quant:
+            codes = torch.empty(x.shape, dtype=torch.int8 if quant in (3, 5) else torch.uint8, device=x.device)
+        if quant in (2, 3):
+            scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+        elif quant in (4, 5):
+            scale = torch.empty(tuple(x.shape[:-1]) + (D // group,), dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_rms_norm_add(
+            _stream(), _ptr(xc), _ptr(rc), _ptr(wc), _ptr(y), _ptr(codes), _ptr(added), _ptr(scale), rows, D,
+            _DT[x.dtype], float(eps), quant, float(static_scale), int(group), int(bool(ue8m0))))
+    return y, codes, added, scale
+
+
+def rms_norm_add(x, residual, weight, eps=1e-5):
+    """Fused residual add + RMSNorm.  Returns (out, x + residual)."""
+    y, _, added, _ = _rms_norm_add(x, residual, weight, eps, 0)
+    return y, added
+
+
+def rms_norm_add_fp8(x, residual, weight, eps=1e-5, scale=None):
+    """Fused add + rms_norm + fp8.  scale=None: dynamic per row (codes, added, scale); else static
+    per tensor (codes, added).  codes are e4m3 uint8."""
+    if scale is None:
+        _, codes, added, s = _rms_norm_add(x, residual, weight, eps, 2, name="rms_norm_add_fp8")
+        return codes, added, s
+    _check(float(scale) > 0.0, "rms_norm_add_fp8: scale must be positive")
+    _, codes, added, _ = _rms_norm_add(x, residual, weight, eps, 1, static_scale=float(scale), name="rms_norm_add_fp8")
+    return codes, added
+
+
+def rms_norm_add_int8_dyn(x, residual, weight, eps=1e-5):
+    """Fused add + rms_norm + dynamic per-row symmetric int8: (codes, added, scale)."""
+    _, codes, added, s = _rms_norm_add(x, residual, weight, eps, 3, name="rms_norm_add_int8_dyn")
+    return codes, added, s
+
+
+def rms_norm_add_per_block(x, residual, weight, eps=1e-5, int8=False, ue8m0=False):
+    """Fused add + rms_norm + per-128-block quant.  Returns (codes, x + residual, scale (rows, D/128))."""
+    _check(x.size(-1) % 128 == 0, "rms_norm_add_per_block: per-block quant requires D % 128 == 0")
+    _, codes, added, s = _rms_norm_add(x, residual, weight, eps, 5 if int8 else 4, group=128, ue8m0=ue8m0,
+                                       name="rms_norm_add_per_block")
+    return codes, added, s
+
+
+_ACTQ_MODES = {"swiglu": 0, "swiglu_oai": 1}
+
+
+def _silu_mul_quant(x, gate, act, alpha, limit, quant, group=0, ue8m0=False, name="silu_mul_quant_fp8"):
+    _check(act in _ACTQ_MODES, f"{name}: act must be 'swiglu' or 'swiglu_oai'")
+    _check(x.is_cuda and x.dtype in _DT and x.dim() >= 1 and x.numel() > 0 and gate.shape == x.shape
+           and gate.dtype == x.dtype, f"{name}: x and gate must be matching non-empty CUDA float tensors")
+    _same_device(name, x, gate)
+    D = x.size(-1)
+    rows = x.numel() // D
+    if quant == 4:
+        _check(group > 0 and group % 4 == 0 and D % group == 0,
+               f"{name}: group_size must be a multiple of 4 that divides D")
+    with torch.cuda.device(x.device):
+        xc, gc = x.contiguous(), gate.contiguous()
+        codes = torch.empty(x.shape, dtype=torch.int8 if quant == 3 else torch.uint8, device=x.device)
+        sshape = tuple(x.shape[:-1]) + ((D // group,) if quant == 4 else ())
+        scale = torch.empty(sshape, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().qx_cuda_silu_mul_quant(
+            _stream(), _ptr(xc), _ptr(gc), _ptr(codes), _ptr(scale), rows, D, _DT[x.dtype], _ACTQ_MODES[act],
+            float(alpha), float(limit), quant, int(group), int(bool(ue8m0))))
+    return codes, scale
+
+
+def silu_mul_quant_fp8(x, gate, act="swiglu", alpha=1.702, limit=7.0):
+    """Fused gated activation -> dynamic per-token fp8.  Returns (codes u8, scale)."""
+    return _silu_mul_quant(x, gate, act, alpha, limit, 2)
+
+
+def silu_mul_quant_int8(x, gate, act="swiglu", alpha=1.702, limit=7.0):
+    """Fused gated activation -> dynamic per-token int8.  Returns (codes i8, scale)."""
+    return _silu_mul_quant(x, gate, act, alpha, limit, 3, name="silu_mul_quant_int8")
+
+
+def silu_mul_quant_fp8_group(x, gate, group_size=128, ue8m0=False, act="swiglu", alpha=1.702, limit=7.0):
+    """Fused gated activation -> per-group fp8 (scale (rows, D/G); ue8m0 = 2^k scales)."""
+    return _silu_mul_quant(x, gate, act, alpha, limit, 4, int(group_size), ue8m0, name="silu_mul_quant_fp8_group")

@@ -237,6 +237,12 @@ _SIGNATURES = {
     "qgemv": ["wq", "x", "format='q8_0'"],
     "dequant_gather": ["table", "ids", "format", "scale=1.0"],
     "quantized_embedding": ["table", "ids", "add", "format", "scale=1.0", "use_add=False", "output_dtype='float16'"],
+    "rms_norm_add": ["x", "residual", "weight", "eps=1e-05"],
+    "rms_norm_add_fp8": ["x", "residual", "weight", "eps=1e-05", "scale=None"],
+    "rms_norm_add_per_block": ["x", "residual", "weight", "eps=1e-05", "int8=False", "ue8m0=False"],
+    "silu_mul_quant_fp8": ["x", "gate", "act='swiglu'", "alpha=1.702", "limit=7.0"],
+    "silu_mul_quant_int8": ["x", "gate", "act='swiglu'", "alpha=1.702", "limit=7.0"],
+    "silu_mul_quant_fp8_group": ["x", "gate", "group_size=128", "ue8m0=False", "act='swiglu'", "alpha=1.702", "limit=7.0"],
     "quantize_per_token_fp8": ["x"],
     "quantize_per_token_int8": ["x"],
     "argmax_sample": ["logits"],
