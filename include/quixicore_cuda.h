@@ -382,6 +382,77 @@ qx_status qx_cuda_lm_head_shard_reduce(void* stream, const float* cand_val, cons
                                        int mode, int topk, double temperature, uint32_t seed,
                                        double top_p);
 
+/* ---- BaseQN: weights as separate code / scale / bias planes -----------------------------------------
+ * codes uint8 (rows, K * bits / 8), lane c of a row in bits [c * bits, (c + 1) * bits) of the row's
+ * little-endian bit string; scales and (asymmetric tensors) biases (rows, K / group) stored as
+ * scale_dtype "bf16" / "f16" (2 bytes) or "e8m0" / "e4m3" (1 byte; e4m3 only with bits == 8).
+ * w = fl(fl(code * scale) + bias); symmetric != 0: w = (code - 2^(bits - 1)) * scale, biases ignored
+ * (may be NULL).  bits in {2,3,4,5,6,8}, group in {32,64,128}, layout "metal", "metal_lane_strided"
+ * or "metal_lane_strided_q<bits>" (one layout, three spellings).  Contract:
+ * kernels/quantization/base_q/README.md:8-27, descriptor checks kernels/common/base_q_descriptor.h:34-68,
+ * storage checks kernels/quantization/base_q/base_q.cpp:57-90.  Activations / outputs f32, f16 or
+ * bf16; 16-bit activations with K % 128 == 0, K >= 512 run on the streaming tensor-core kernel and
+ * need the workspace below, everything else on a shape-generic kernel.  workspace NULL = library
+ * scratch. */
+typedef struct qx_base_q_planes {
+  const void* codes;
+  const void* scales;
+  const void* biases;
+} qx_base_q_planes;
+typedef struct qx_base_q_desc {
+  int32_t bits;
+  int32_t group_size;
+  const char* scale_dtype;
+  int32_t symmetric;
+  const char* layout;
+} qx_base_q_desc;
+
+/* Workspace of the BaseQN calls that multiply: K inner dimension, M activation columns (batch;
+ * total_rows for the expert forms), V = vocabulary rows for base_qlm_head_argmax (its logits live
+ * in the workspace), else 0. */
+size_t qx_cuda_base_q_workspace_bytes(int64_t K, int64_t M, int64_t V, qx_dtype dtype);
+
+/* out (rows, K) = dequantised weights.  Replaces base_qdequant (base_q.cpp:170-187, base_q.metal:71-91). */
+qx_status qx_cuda_base_qdequant(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc, void* out,
+                                int64_t rows, int64_t K, qx_dtype out_dtype);
+/* out (tokens, K) = rows ids[i] of the dequantised table; an id outside [0, rows) gives a zero row.
+ * Replaces base_qembedding (base_q.cpp:279-300, base_q.metal:251-280). */
+qx_status qx_cuda_base_qembedding(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc,
+                                  const int32_t* ids, void* out, int64_t rows, int64_t K, int64_t tokens,
+                                  qx_dtype out_dtype);
+/* out (rows, M) = dequant(W) (rows, K) @ x (K, M), in the dtype of x.  M == 1 is base_qgemv.
+ * Replaces base_qgemv / base_qgemm (base_q.cpp:134-212, base_q.metal:93-115,222-249). */
+qx_status qx_cuda_base_qgemm(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc, const void* x,
+                             void* out, int64_t rows, int64_t K, int64_t M, qx_dtype dtype, void* workspace,
+                             size_t workspace_bytes);
+/* q / k / v (rows_i, 1) = dequant(W_i) @ x (K, 1) for three matrices that share desc and K, one launch.
+ * Replaces base_qgemv_qkv (base_q.cpp:214-251, base_q.metal:117-163). */
+qx_status qx_cuda_base_qgemv_qkv(void* stream, const qx_base_q_planes* q, const qx_base_q_planes* k,
+                                 const qx_base_q_planes* v, const qx_base_q_desc* desc, const void* x, void* q_out,
+                                 void* k_out, void* v_out, int64_t q_rows, int64_t k_rows, int64_t v_rows,
+                                 int64_t K, qx_dtype dtype, void* workspace, size_t workspace_bytes);
+/* out (rows, 1) = silu(W_gate @ x) * (W_up @ x), rounded once.  Replaces base_qgemv_swiglu
+ * (base_q.cpp:253-277, base_q.metal:165-220). */
+qx_status qx_cuda_base_qgemv_swiglu(void* stream, const qx_base_q_planes* gate, const qx_base_q_planes* up,
+                                    const qx_base_q_desc* desc, const void* x, void* out, int64_t rows, int64_t K,
+                                    qx_dtype dtype, void* workspace, size_t workspace_bytes);
+/* ids (batch,) = argmax over the V logits of every column of x (K, batch); logits are rounded to the
+ * dtype of x first, the smaller id wins an exact tie.  Replaces base_qlm_head_argmax
+ * (bindings/python/tk/__init__.py:4033-4059, README.md:43-47). */
+qx_status qx_cuda_base_qlm_head_argmax(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc,
+                                       const void* x, int32_t* ids, int64_t V, int64_t K, int64_t batch,
+                                       qx_dtype dtype, void* workspace, size_t workspace_bytes);
+/* Expert stack: codes (experts, expert_rows, K * bits / 8), scales / biases (experts, expert_rows,
+ * K / group); input (total_rows, K); expert_of_tile (total_rows / 32,) names the expert of every 32
+ * input rows, a negative entry leaves those output rows untouched.  swiglu == 0: out (total_rows,
+ * expert_rows) = input @ dequant(W[e])^T.  swiglu != 0: expert_rows = 2 * I laid out [gate(I), up(I)],
+ * out (total_rows, I) = silu(gate) * up.  Replaces base_qmoe_gemm / base_qmoe_swiglu
+ * (base_q.cpp:302-375, base_q.metal:313-430).  16-bit input, K % 128 == 0, K >= 512. */
+qx_status qx_cuda_base_qmoe(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc, const void* input,
+                            const int32_t* expert_of_tile, void* out, int64_t experts, int64_t expert_rows,
+                            int64_t K, int64_t total_rows, int swiglu, qx_dtype dtype, void* workspace,
+                            size_t workspace_bytes);
+
 /* ---- introspection --------------------------------------------------------------------------- */
 /* block_k / block_bytes of a format name; returns 0 and leaves the outputs alone if unknown
  * (the table of kernels/matmul/decode_linear/decode_linear.cpp:25-34). */

@@ -762,3 +762,123 @@ def quantize_groups(v: np.ndarray, group: int, kind: str = "fp8", ue8m0: bool = 
     scaled = (b * inv[..., None]).astype(f)
     codes = e4m3_encode_device(scaled) if kind == "fp8" else int8_encode(scaled)
     return codes.reshape(v.shape), s
+
+
+# ----------------------------------------------------------------------------------------------
+# BaseQN: codes, scales and biases in separate planes.  kernels/quantization/base_q/README.md:8-27,
+# bindings/python/tk/base_q.py:25-154, kernels/quantization/base_q/base_q.metal:8-41
+# ----------------------------------------------------------------------------------------------
+BASE_Q_BITS = (2, 3, 4, 5, 6, 8)
+BASE_Q_GROUPS = (32, 64, 128)
+
+
+def base_q_pack(codes: np.ndarray, bits: int) -> np.ndarray:
+    """Lane c of a row occupies bits [c*bits, (c+1)*bits) of the row's little-endian bit string
+    (bit i of the string is bit i%8 of byte i//8).  base_q.py:25-47"""
+    v = np.asarray(codes).astype(np.uint32)
+    if bits not in BASE_Q_BITS or (v.shape[-1] * bits) % 8:
+        raise ValueError("BaseQN: bits in {2,3,4,5,6,8} and a byte-aligned row")
+    if v.size and int(v.max()) >= (1 << bits):
+        raise ValueError("BaseQN: code out of range")
+    bit = ((v[..., None] >> np.arange(bits, dtype=np.uint32)) & 1).astype(np.uint8)
+    return np.packbits(bit.reshape(v.shape[:-1] + (-1,)), axis=-1, bitorder="little")
+
+
+def base_q_unpack(packed: np.ndarray, bits: int, columns: int | None = None) -> np.ndarray:
+    """Inverse of base_q_pack.  base_q.py:50-76, base_q.metal:8-18"""
+    p = np.asarray(packed, np.uint8)
+    if columns is None:
+        columns = p.shape[-1] * 8 // bits
+    if columns * bits != p.shape[-1] * 8:
+        raise ValueError("BaseQN: columns * bits must equal packed bytes * 8")
+    bit = np.unpackbits(p, axis=-1, bitorder="little").reshape(p.shape[:-1] + (columns, bits))
+    return (bit.astype(np.uint32) << np.arange(bits, dtype=np.uint32)).sum(-1).astype(np.uint8)
+
+
+def base_q_scale_values(plane: np.ndarray, scale_dtype: str) -> np.ndarray:
+    """Scale / bias plane -> fp32.  uint16 input = raw bf16 / f16 bits.  base_q.py:104-116,
+    base_q.metal:20-26"""
+    a = np.asarray(plane)
+    name = {"bfloat16": "bf16", "float16": "f16"}.get(str(scale_dtype).lower(), str(scale_dtype).lower())
+    if name == "bf16":
+        return (a.astype(np.uint32) << np.uint32(16)).view(np.float32) if a.dtype == np.uint16 else a.astype(np.float32)
+    if name == "f16":
+        return (a.view(np.float16) if a.dtype == np.uint16 else a.astype(np.float16)).astype(np.float32)
+    if name == "e8m0":
+        return e8m0_decode(a)
+    if name == "e4m3":
+        return e4m3_decode(a)
+    raise ValueError("BaseQN: scale_dtype must be bf16, f16, e8m0 or e4m3")
+
+
+def base_q_dequantize(packed, scales, biases, bits, group, scale_dtype="bf16", symmetric=False) -> np.ndarray:
+    """fp32 weights (.., K): asymmetric fl(fl(code * scale) + bias), symmetric
+    (code - 2^(bits-1)) * scale, one scale (and bias) per `group` columns.  base_q.py:119-154,
+    base_q.metal:28-41"""
+    if group not in BASE_Q_GROUPS:
+        raise ValueError("BaseQN: group_size must be 32, 64 or 128")
+    if str(scale_dtype).lower() == "e4m3" and bits != 8:
+        raise ValueError("BaseQN: e4m3 scale storage is valid only for q8")       # base_q_descriptor.h:64-66
+    s = base_q_scale_values(scales, scale_dtype)
+    K = s.shape[-1] * group
+    c = base_q_unpack(packed, bits, K)
+    se = np.repeat(s, group, axis=-1)
+    if symmetric:
+        return ((c.astype(np.int32) - (1 << (bits - 1))).astype(np.float32) * se).astype(np.float32)
+    if biases is None:
+        raise ValueError("BaseQN: biases are required for asymmetric tensors")
+    b = np.repeat(base_q_scale_values(biases, scale_dtype), group, axis=-1)
+    return ((c.astype(np.float32) * se).astype(np.float32) + b).astype(np.float32)
+
+
+def base_q_random_planes(rows, K, bits, group, scale_dtype, symmetric, seed, lead=()):
+    """Seeded planes in storage form: (codes uint8, scales, biases or None).  bf16 / f16 planes are
+    returned as raw uint16 bits, e8m0 / e4m3 as uint8."""
+    rng = np.random.default_rng(seed)
+    shape = tuple(lead) + (rows,)
+    codes = base_q_pack(rng.integers(0, 1 << bits, size=shape + (K,), dtype=np.uint8), bits)
+    G = K // group
+
+    def plane(lo, hi):
+        v = (lo + (hi - lo) * rng.random(shape + (G,))).astype(np.float32)
+        if scale_dtype == "bf16":
+            return (round_bf16(v).view(np.uint32) >> np.uint32(16)).astype(np.uint16)
+        if scale_dtype == "f16":
+            return v.astype(np.float16).view(np.uint16)
+        if scale_dtype == "e8m0":
+            return rng.integers(118, 124, size=v.shape, dtype=np.uint8)          # 2^-9 .. 2^-4
+        sign = (rng.random(v.shape) < (0.5 if lo < 0 else 0.0)).astype(np.uint8) << 7
+        return (rng.integers(0x08, 0x30, size=v.shape, dtype=np.uint8) | sign).astype(np.uint8)
+    scales = plane(0.002, 0.02)
+    biases = None if symmetric else plane(-0.05, 0.05)
+    return codes, scales, biases
+
+
+def base_q_matmul(W: np.ndarray, x: np.ndarray, dtype: str) -> np.ndarray:
+    """dequant(W) (N, K) @ x (K, M), float64 accumulation, rounded to the activation dtype.
+    base_q.metal:93-115,222-249"""
+    return round_to((W.astype(np.float64) @ np.asarray(x, np.float64)).astype(np.float32), dtype)
+
+
+def base_q_swiglu(Wg: np.ndarray, Wu: np.ndarray, x: np.ndarray, dtype: str) -> np.ndarray:
+    """silu(Wg @ x) * (Wu @ x) with one final rounding.  base_q.metal:165-220"""
+    g = Wg.astype(np.float64) @ np.asarray(x, np.float64)
+    u = Wu.astype(np.float64) @ np.asarray(x, np.float64)
+    return round_to(((g / (1.0 + np.exp(-g))) * u).astype(np.float32), dtype)
+
+
+def base_q_embedding(W: np.ndarray, ids: np.ndarray, dtype: str) -> np.ndarray:
+    """Rows of W by id; a negative or out-of-range id gives a zero row.  README.md:24-27"""
+    ids = np.asarray(ids, np.int64)
+    ok = (ids >= 0) & (ids < W.shape[0])
+    out = np.where(ok[..., None], W[np.where(ok, ids, 0)], np.float32(0.0))
+    return round_to(out.astype(np.float32), dtype)
+
+
+def base_q_lm_head_argmax(W: np.ndarray, x: np.ndarray, dtype: str):
+    """Greedy ids over logits rounded to the activation dtype, lowest id on exact ties; also
+    returns per column the gap between the two largest float64 logits.  README.md:43-47"""
+    logits = W.astype(np.float64) @ np.asarray(x, np.float64)                     # (V, batch)
+    r = round_to(logits.astype(np.float32), dtype)
+    top2 = np.sort(logits, axis=0)[-2:]
+    return np.argmax(r, axis=0).astype(np.int32), (top2[1] - top2[0]), r

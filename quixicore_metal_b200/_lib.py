@@ -22,6 +22,17 @@ class Status(C.Structure):
     _fields_ = [("code", C.c_uint8), ("operation", C.c_char_p), ("detail", C.c_char_p)]
 
 
+class BaseQPlanes(C.Structure):
+    # qx_base_q_planes: device pointers of the code / scale / bias planes
+    _fields_ = [("codes", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p)]
+
+
+class BaseQDescriptor(C.Structure):
+    # qx_base_q_desc
+    _fields_ = [("bits", C.c_int32), ("group_size", C.c_int32), ("scale_dtype", C.c_char_p),
+                ("symmetric", C.c_int32), ("layout", C.c_char_p)]
+
+
 class QxError(RuntimeError):
     """A non-ok qx_status; `.code` is the status name of the contract ABI."""
 
@@ -81,6 +92,24 @@ def lib() -> C.CDLL:
     L.qx_cuda_qgemm.argtypes = [vp, vp, vp, vp, i64, i64, i64, cs, i32, vp, sz]
     L.qx_cuda_quantized_embedding.restype = Status
     L.qx_cuda_quantized_embedding.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, cs, f64, i32, i32]
+    pp = C.POINTER(BaseQPlanes)
+    dp = C.POINTER(BaseQDescriptor)
+    L.qx_cuda_base_q_workspace_bytes.restype = sz
+    L.qx_cuda_base_q_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    L.qx_cuda_base_qdequant.restype = Status
+    L.qx_cuda_base_qdequant.argtypes = [vp, pp, dp, vp, i64, i64, i32]
+    L.qx_cuda_base_qembedding.restype = Status
+    L.qx_cuda_base_qembedding.argtypes = [vp, pp, dp, vp, vp, i64, i64, i64, i32]
+    L.qx_cuda_base_qgemm.restype = Status
+    L.qx_cuda_base_qgemm.argtypes = [vp, pp, dp, vp, vp, i64, i64, i64, i32, vp, sz]
+    L.qx_cuda_base_qgemv_qkv.restype = Status
+    L.qx_cuda_base_qgemv_qkv.argtypes = [vp, pp, pp, pp, dp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp, sz]
+    L.qx_cuda_base_qgemv_swiglu.restype = Status
+    L.qx_cuda_base_qgemv_swiglu.argtypes = [vp, pp, pp, dp, vp, vp, i64, i64, i32, vp, sz]
+    L.qx_cuda_base_qlm_head_argmax.restype = Status
+    L.qx_cuda_base_qlm_head_argmax.argtypes = [vp, pp, dp, vp, vp, i64, i64, i64, i32, vp, sz]
+    L.qx_cuda_base_qmoe.restype = Status
+    L.qx_cuda_base_qmoe.argtypes = [vp, pp, dp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz]
     L.qx_cuda_lm_head_masked_workspace_bytes.restype = sz
     L.qx_cuda_lm_head_masked_workspace_bytes.argtypes = [i64, i64, i64, i32]
     L.qx_cuda_lm_head_masked.restype = Status

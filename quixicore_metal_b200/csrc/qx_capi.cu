@@ -4,6 +4,8 @@
 #include <cstring>
 
 #include "qx_common.cuh"
+#include <string>
+
 #include "qx_kernels.h"
 
 namespace qx {
@@ -877,6 +879,200 @@ qx_status qx_cuda_dispatch(const char* op_name, const qx_kernel_call* call) {
                                       rows, x.shape[x.rank - 1], (qx_dtype)x.dtype, qi ? 1 : 0);
   }
   return fail(QX_NOT_IMPLEMENTED, op_name, "operation is not part of the B200 decode-projection backend");
+}
+
+// ---- BaseQN separate-plane consumers -----------------------------------------------------------------
+// The descriptor checks of the reference (kernels/common/base_q_descriptor.h:34-68), same messages.
+static qx_status base_q_desc_of(const char* op, const qx_base_q_desc* d, BaseQDesc* out) {
+  if (!d) return fail(QX_INVALID_ARGUMENT, op, "null descriptor");
+  const int b = d->bits, g = d->group_size;
+  if (b != 2 && b != 3 && b != 4 && b != 5 && b != 6 && b != 8)
+    return fail(QX_INVALID_ARGUMENT, op, "BaseQN: bits must be one of 2, 3, 4, 5, 6, or 8");
+  if (g != 32 && g != 64 && g != 128) return fail(QX_INVALID_ARGUMENT, op, "BaseQN: group_size must be 32, 64, or 128");
+  const std::string sd = d->scale_dtype ? d->scale_dtype : "";
+  int stype = -1;
+  if (sd == "bf16" || sd == "bfloat16") stype = 0;
+  else if (sd == "f16" || sd == "float16") stype = 1;
+  else if (sd == "e8m0") stype = 2;
+  else if (sd == "e4m3") stype = 3;
+  if (stype < 0) return fail(QX_INVALID_ARGUMENT, op, "BaseQN: scale_dtype must be bf16, f16, e8m0, or e4m3");
+  if (stype == 3 && b != 8) return fail(QX_INVALID_ARGUMENT, op, "BaseQN: e4m3 scale storage is valid only for q8");
+  const std::string lay = d->layout ? d->layout : "";
+  if (lay != "metal" && lay != "metal_lane_strided" && lay != "metal_lane_strided_q" + std::to_string(b))
+    return fail(QX_INVALID_ARGUMENT, op, "BaseQN: layout must be metal or metal_lane_strided_q<bits>");
+  *out = BaseQDesc{b, g, stype, d->symmetric ? 1 : 0};
+  return ok(op);
+}
+static qx_status base_q_planes_ok(const char* op, const qx_base_q_planes* w, const BaseQDesc& d, int64_t rows, int64_t K) {
+  if (!w || !w->codes || !w->scales) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (!d.symmetric && !w->biases) return fail(QX_INVALID_ARGUMENT, op, "biases are required for asymmetric BaseQN");
+  if (rows <= 0 || K <= 0 || K % d.group != 0 || rows > 0x7fffffff || K > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "codes/scales rows and group count must be positive and match");
+  return ok(op);
+}
+
+size_t qx_cuda_base_q_workspace_bytes(int64_t K, int64_t M, int64_t V, qx_dtype dtype) {
+  if (K <= 0 || M <= 0) return 0;
+  size_t n = base_q_scratch_bytes(K, M, dtype, true);
+  if (V > 0) n += align256((size_t)M * V * (dtype == QX_DTYPE_F32 ? 4 : 2));
+  return n;
+}
+
+qx_status qx_cuda_base_qdequant(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc, void* out,
+                                int64_t rows, int64_t K, qx_dtype out_dtype) {
+  static const char* op = "base_qdequant";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  if (!float_dtype(out_dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "BaseQN: output_dtype must be float16, bfloat16, or float32");
+  st = base_q_planes_ok(op, w, d, rows, K);
+  if (st.code != QX_OK) return st;
+  if (!out) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (!device_ready(op, &st)) return st;
+  launch_base_q_rows((cudaStream_t)stream, d, w->codes, w->scales, w->biases, nullptr, out, rows, rows, K, out_dtype);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_base_qembedding(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc,
+                                  const int32_t* ids, void* out, int64_t rows, int64_t K, int64_t tokens,
+                                  qx_dtype out_dtype) {
+  static const char* op = "base_qembedding";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  if (!float_dtype(out_dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "BaseQN: output_dtype must be float16, bfloat16, or float32");
+  st = base_q_planes_ok(op, w, d, rows, K);
+  if (st.code != QX_OK) return st;
+  if (tokens <= 0) return fail(QX_INVALID_SHAPE, op, "ids must be non-empty");
+  if (!out || !ids) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (!device_ready(op, &st)) return st;
+  launch_base_q_rows((cudaStream_t)stream, d, w->codes, w->scales, w->biases, ids, out, tokens, rows, K, out_dtype);
+  return check_launch(op);
+}
+
+// shared tail of the multiplying entry points
+static qx_status base_q_run(const char* op, void* stream, const BaseQDesc& d, const BaseQMat* mats, int nmat, int mode,
+                     const void* x, bool x_is_km, int64_t K, int64_t M, qx_dtype dtype, int64_t orow, int64_t ocol,
+                     void* workspace, size_t workspace_bytes, size_t ws_skip, const BaseQExperts* ex) {
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  ScratchHold hold;
+  void* scratch = nullptr; size_t sbytes = 0;
+  const size_t need = ws_skip + base_q_scratch_bytes(K, M, dtype, x_is_km);
+  st = bind_scratch(op, (cudaStream_t)stream, need, workspace, workspace_bytes, &hold, &scratch, &sbytes);
+  if (st.code != QX_OK) return st;
+  if (!launch_base_q_matmul((cudaStream_t)stream, d, mats, nmat, mode, x, x_is_km, K, M, dtype, orow, ocol,
+                            scratch ? (char*)scratch + ws_skip : nullptr, scratch ? sbytes - ws_skip : 0, ex))
+    return fail(QX_INVALID_SHAPE, op, "no device path for this shape (expert stacks: 16-bit input, K % 128 == 0, K >= 512, 16-byte aligned planes)");
+  return check_launch(op);
+}
+
+qx_status qx_cuda_base_qgemm(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc, const void* x,
+                             void* out, int64_t rows, int64_t K, int64_t M, qx_dtype dtype, void* workspace,
+                             size_t workspace_bytes) {
+  const char* op = M == 1 ? "base_qgemv" : "base_qgemm";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  st = base_q_planes_ok(op, w, d, rows, K);
+  if (st.code != QX_OK) return st;
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "BaseQN matmul: x must be float16, bfloat16, or float32");
+  if (M <= 0 || M > 0x7fffffff) return fail(QX_INVALID_SHAPE, op, "BaseQN matmul: M must be positive");
+  if (!x || !out) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  BaseQMat m{w->codes, w->scales, w->biases, rows, out};
+  return base_q_run(op, stream, d, &m, 1, 0, x, true, K, M, dtype, M, 1, workspace, workspace_bytes, 0, nullptr);
+}
+
+qx_status qx_cuda_base_qgemv_qkv(void* stream, const qx_base_q_planes* q, const qx_base_q_planes* k,
+                                 const qx_base_q_planes* v, const qx_base_q_desc* desc, const void* x, void* q_out,
+                                 void* k_out, void* v_out, int64_t q_rows, int64_t k_rows, int64_t v_rows,
+                                 int64_t K, qx_dtype dtype, void* workspace, size_t workspace_bytes) {
+  static const char* op = "base_qgemv_qkv";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  const qx_base_q_planes* w[3] = {q, k, v};
+  const int64_t rows[3] = {q_rows, k_rows, v_rows};
+  void* outs[3] = {q_out, k_out, v_out};
+  BaseQMat m[3];
+  for (int i = 0; i < 3; ++i) {
+    st = base_q_planes_ok(op, w[i], d, rows[i], K);
+    if (st.code != QX_OK) return st;
+    if (!outs[i]) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+    m[i] = BaseQMat{w[i]->codes, w[i]->scales, w[i]->biases, rows[i], outs[i]};
+  }
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "BaseQN matmul: x must be float16, bfloat16, or float32");
+  if (!x) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  return base_q_run(op, stream, d, m, 3, 0, x, true, K, 1, dtype, 1, 1, workspace, workspace_bytes, 0, nullptr);
+}
+
+qx_status qx_cuda_base_qgemv_swiglu(void* stream, const qx_base_q_planes* gate, const qx_base_q_planes* up,
+                                    const qx_base_q_desc* desc, const void* x, void* out, int64_t rows, int64_t K,
+                                    qx_dtype dtype, void* workspace, size_t workspace_bytes) {
+  static const char* op = "base_qgemv_swiglu";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  st = base_q_planes_ok(op, gate, d, rows, K);
+  if (st.code != QX_OK) return st;
+  st = base_q_planes_ok(op, up, d, rows, K);
+  if (st.code != QX_OK) return st;
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "BaseQN matmul: x must be float16, bfloat16, or float32");
+  if (!x || !out) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  BaseQMat m[2] = {{gate->codes, gate->scales, gate->biases, rows, out}, {up->codes, up->scales, up->biases, rows, out}};
+  return base_q_run(op, stream, d, m, 2, 1, x, true, K, 1, dtype, 1, 1, workspace, workspace_bytes, 0, nullptr);
+}
+
+qx_status qx_cuda_base_qlm_head_argmax(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc,
+                                       const void* x, int32_t* ids, int64_t V, int64_t K, int64_t batch,
+                                       qx_dtype dtype, void* workspace, size_t workspace_bytes) {
+  static const char* op = "base_qlm_head_argmax";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  st = base_q_planes_ok(op, w, d, V, K);
+  if (st.code != QX_OK) return st;
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "BaseQN matmul: x must be float16, bfloat16, or float32");
+  if (batch <= 0 || batch > 0x7fffffff) return fail(QX_INVALID_SHAPE, op, "base_qlm_head_argmax: x must be non-empty (K, batch)");
+  if (!x || !ids) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (!device_ready(op, &st)) return st;
+  // logits (batch, V) in the dtype of x at the head of the workspace, then the row-wise argmax
+  const size_t logit_bytes = align256((size_t)batch * V * (dtype == QX_DTYPE_F32 ? 4 : 2));
+  ScratchHold hold;
+  void* scratch = nullptr; size_t sbytes = 0;
+  st = bind_scratch(op, (cudaStream_t)stream, logit_bytes + base_q_scratch_bytes(K, batch, dtype, true), workspace,
+                    workspace_bytes, &hold, &scratch, &sbytes);
+  if (st.code != QX_OK) return st;
+  BaseQMat m{w->codes, w->scales, w->biases, V, scratch};
+  if (!launch_base_q_matmul((cudaStream_t)stream, d, &m, 1, 0, x, true, K, batch, dtype, 1, V,
+                            (char*)scratch + logit_bytes, sbytes - logit_bytes, nullptr))
+    return fail(QX_RUNTIME_ERROR, op, "kernel configuration failed");
+  launch_sample_logits((cudaStream_t)stream, scratch, ids, batch, V, dtype, 0, 0, 1.f, 1.f, 0u);
+  return check_launch(op);
+}
+
+qx_status qx_cuda_base_qmoe(void* stream, const qx_base_q_planes* w, const qx_base_q_desc* desc, const void* input,
+                            const int32_t* expert_of_tile, void* out, int64_t experts, int64_t expert_rows,
+                            int64_t K, int64_t total_rows, int swiglu, qx_dtype dtype, void* workspace,
+                            size_t workspace_bytes) {
+  const char* op = swiglu ? "base_qmoe_swiglu" : "base_qmoe_gemm";
+  BaseQDesc d;
+  qx_status st = base_q_desc_of(op, desc, &d);
+  if (st.code != QX_OK) return st;
+  if (experts <= 0 || experts * expert_rows > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "codes/scales expert, row, and group dimensions must be positive and match");
+  st = base_q_planes_ok(op, w, d, expert_rows, K);
+  if (st.code != QX_OK) return st;
+  if (dtype != QX_DTYPE_F16 && dtype != QX_DTYPE_BF16) return fail(QX_UNSUPPORTED_DTYPE, op, "input must be float16 or bfloat16");
+  if (total_rows <= 0 || total_rows % 32 != 0 || total_rows > 0x7fffffff)
+    return fail(QX_INVALID_SHAPE, op, "input rows must be a positive multiple of 32");
+  if (swiglu && expert_rows % 2 != 0) return fail(QX_INVALID_SHAPE, op, "the gate/up row axis must be even");
+  if (!input || !expert_of_tile || !out) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  const int64_t I = swiglu ? expert_rows / 2 : expert_rows;
+  BaseQExperts ex{expert_of_tile, experts, expert_rows, swiglu ? I : 0};
+  BaseQMat m[2] = {{w->codes, w->scales, w->biases, I, out}, {w->codes, w->scales, w->biases, I, out}};
+  return base_q_run(op, stream, d, m, swiglu ? 2 : 1, swiglu ? 1 : 0, input, false, K, total_rows, dtype, 1, I,
+                    workspace, workspace_bytes, 0, &ex);
 }
 
 }  // extern "C"

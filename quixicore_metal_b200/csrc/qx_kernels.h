@@ -153,6 +153,20 @@ bool launch_rms_norm_add(cudaStream_t st, qx_dtype dtype, const void* x, const v
 bool launch_silu_mul_quant(cudaStream_t st, qx_dtype dtype, const void* x, const void* gate, void* codes, float* scale,
                            int64_t rows, int64_t D, int act, float alpha, float limit, int qmode, int G, int pow2);
 
+// BaseQN separate-plane weights (see qx_base_q.cu).  stype: 0 bf16, 1 f16, 2 e8m0, 3 e4m3.
+struct BaseQDesc { int bits, group, stype, symmetric; };
+struct BaseQMat { const void* codes; const void* scales; const void* biases; int64_t rows; void* out; };
+// Expert stack: activation row m belongs to expert expert_of_tile[m / 32]; an expert holds expert_rows
+// plane rows, the second matrix of a gate / up pair starts up_offset rows into them.
+struct BaseQExperts { const int32_t* expert_of_tile; int64_t experts, expert_rows, up_offset; };
+size_t base_q_scratch_bytes(int64_t K, int64_t M, qx_dtype dtype, bool x_is_km);
+bool launch_base_q_matmul(cudaStream_t st, const BaseQDesc& d, const BaseQMat* mats, int nmat, int mode,
+                          const void* x, bool x_is_km, int64_t K, int64_t M, qx_dtype dtype, int64_t orow,
+                          int64_t ocol, void* scratch, size_t scratch_bytes, const BaseQExperts* ex = nullptr);
+void launch_base_q_rows(cudaStream_t st, const BaseQDesc& d, const void* codes, const void* scales,
+                        const void* biases, const int32_t* ids, void* out, int64_t out_rows, int64_t rows,
+                        int64_t K, qx_dtype out_dtype);
+
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);
 void launch_quantize_mxfp8_rows(cudaStream_t st, const void* x, void* blocks, int64_t rows,

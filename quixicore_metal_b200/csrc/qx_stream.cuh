@@ -58,21 +58,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// The same with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
-// (or until the phase completes) instead of returning at once.  Measured: on the tcgen05 pipeline
-// fewer polling instructions but a later wake-up, 4 % slower overall; on the streaming GEMV no
-// difference.  The kernels poll.
-__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
-      : "memory");
-  return ok;
-}
 // Bounded wait: returns false (and records the failure) if the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_flag) {
   for (int i = 0; i < (1 << 22); ++i)
@@ -217,6 +202,7 @@ struct StageGeom {
 //   2 (mxfp4) thread t: 4t,16+4t, 4t+1,16+4t+1, 4t+2,16+4t+2, 4t+3,16+4t+3
 //   3 (nvfp4) per 16:   0,8,1,9,2,10,3,11,4,12,5,13,6,14,7,15
 //   4 (q6_K)  per 4:    0,2,1,3
+//   5 (BaseQN) per 8:   0,4,1,5,2,6,3,7
 __host__ __device__ inline int perm_position(int perm, int c) {
   switch (perm) {
     case 1: { const int hi = c >> 4, r = c & 15, t = r >> 2, i = r & 3;
@@ -227,6 +213,8 @@ __host__ __device__ inline int perm_position(int perm, int c) {
               return 16 * blk + ((r & 7) << 1 | (r >> 3)); }
     case 4: { const int i = c & 3;
               return (c & ~3) | ((i & 1) << 1 | (i >> 1)); }
+    case 5: { const int i = c & 7;
+              return (c & ~7) | ((i & 3) << 1 | (i >> 2)); }
     default: return c;
   }
 }

@@ -220,3 +220,92 @@ def silu_mul_quant_int8(x, gate, act="swiglu", alpha=1.702, limit=7.0):
 def silu_mul_quant_fp8_group(x, gate, group_size=128, ue8m0=False, act="swiglu", alpha=1.702, limit=7.0):
     """Fused gated activation -> per-group fp8: (codes u8, scale (rows, D/G))."""
     return _tt.silu_mul_quant_fp8_group(x, gate, group_size=group_size, ue8m0=ue8m0, act=act, alpha=alpha, limit=limit)
+
+
+# ---- BaseQN separate-plane consumers (bindings/python/tk/__init__.py:3896-4105) -----------------------
+def _bq_bias(name, biases, scales, symmetric):
+    """A symmetric tensor has no bias plane; the reference passes the scales as a placeholder the
+    kernels never read (tk/__init__.py:3904-3907).  Here the placeholder is simply absent."""
+    if biases is None and not symmetric:
+        raise ValueError(f"{name}: biases are required for asymmetric BaseQN")
+    return None if symmetric else biases
+
+
+def base_qdequant(codes, scales, biases, bits, group_size, scale_dtype="bf16", symmetric=False, layout="metal",
+                  output_dtype="float16"):
+    """Decode canonical BaseQN separate planes to (rows, K).  codes uint8 (rows, K*bits/8); scales and
+    asymmetric biases (rows, K/group_size) in the declared storage dtype; symmetric tensors pass
+    biases=None."""
+    biases = _bq_bias("base_qdequant", biases, scales, symmetric)
+    return _tt.base_qdequant(codes, scales, biases, bits, group_size, scale_dtype, symmetric, layout, output_dtype)
+
+
+def base_qgemv(codes, scales, biases, x, bits, group_size, scale_dtype="bf16", symmetric=False, layout="metal"):
+    """dequant(BaseQN weights) @ x for x shaped (K, 1)."""
+    biases = _bq_bias("base_qgemv", biases, scales, symmetric)
+    return _tt.base_qgemv(codes, scales, biases, x, bits, group_size, scale_dtype, symmetric, layout)
+
+
+def base_qgemm(codes, scales, biases, x, bits, group_size, scale_dtype="bf16", symmetric=False, layout="metal"):
+    """dequant(BaseQN weights) @ x for x shaped (K, M); every M runs on the direct decode kernels."""
+    biases = _bq_bias("base_qgemm", biases, scales, symmetric)
+    return _tt.base_qgemm(codes, scales, biases, x, bits, group_size, scale_dtype, symmetric, layout)
+
+
+def base_qgemv_qkv(q_codes, q_scales, q_biases, k_codes, k_scales, k_biases, v_codes, v_scales, v_biases, x, bits,
+                   group_size, scale_dtype="bf16", symmetric=False, layout="metal"):
+    """Fused BaseQN Q/K/V decode GEMVs over one (K, 1) input; the three matrices share one descriptor
+    but may have different row counts.  Returns (q, k, v)."""
+    if not symmetric and any(b is None for b in (q_biases, k_biases, v_biases)):
+        raise ValueError("base_qgemv_qkv: biases are required for asymmetric BaseQN")
+    if symmetric:
+        q_biases = k_biases = v_biases = None
+    return _tt.base_qgemv_qkv(q_codes, q_scales, q_biases, k_codes, k_scales, k_biases, v_codes, v_scales, v_biases,
+                              x, bits, group_size, scale_dtype, symmetric, layout)
+
+
+def base_qgemv_swiglu(gate_codes, gate_scales, gate_biases, up_codes, up_scales, up_biases, x, bits, group_size,
+                      scale_dtype="bf16", symmetric=False, layout="metal"):
+    """silu(W_gate @ x) * (W_up @ x) directly from BaseQN planes."""
+    if not symmetric and (gate_biases is None or up_biases is None):
+        raise ValueError("base_qgemv_swiglu: biases are required for asymmetric BaseQN")
+    if symmetric:
+        gate_biases = up_biases = None
+    return _tt.base_qgemv_swiglu(gate_codes, gate_scales, gate_biases, up_codes, up_scales, up_biases, x, bits,
+                                 group_size, scale_dtype, symmetric, layout)
+
+
+def base_qembedding(codes, scales, biases, ids, bits, group_size, scale_dtype="bf16", symmetric=False,
+                    layout="metal", output_dtype="float16"):
+    """Gather BaseQN rows and decode directly to ids.shape + (K,); out-of-range ids produce zero rows."""
+    biases = _bq_bias("base_qembedding", biases, scales, symmetric)
+    return _tt.base_qembedding(codes, scales, biases, ids, bits, group_size, scale_dtype, symmetric, layout,
+                               output_dtype)
+
+
+def base_qlm_head_argmax(codes, scales, biases, x, bits, group_size, scale_dtype="bf16", symmetric=False,
+                         layout="metal"):
+    """Greedy token ids (batch,) int32 from a packed BaseQN LM head (V, K) and x (K, batch); lower
+    token ids win exact ties."""
+    biases = _bq_bias("base_qlm_head_argmax", biases, scales, symmetric)
+    if x.ndim != 2 or int(x.shape[1]) <= 0:
+        raise ValueError("base_qlm_head_argmax: x must be non-empty (K, batch)")
+    return _tt.base_qlm_head_argmax(codes, scales, biases, x, bits, group_size, scale_dtype, symmetric, layout)
+
+
+def base_qmoe_gemm(codes, scales, biases, input, expert_of_tile, bits, group_size, scale_dtype="bf16",
+                   symmetric=False, layout="metal"):
+    """Padded MoE rows through a BaseQN expert stack.  codes (experts, output_rows, K*bits/8), input
+    (total_rows, K), expert_of_tile maps each 32-row tile to its expert -> (total_rows, output_rows)."""
+    biases = _bq_bias("base_qmoe_gemm", biases, scales, symmetric)
+    return _tt.base_qmoe_gemm(codes, scales, biases, input, expert_of_tile, bits, group_size, scale_dtype, symmetric,
+                              layout)
+
+
+def base_qmoe_swiglu(codes, scales, biases, input, expert_of_tile, bits, group_size, scale_dtype="bf16",
+                     symmetric=False, layout="metal"):
+    """Fused BaseQN grouped expert gate/up projection and SwiGLU; the packed output-row axis is
+    [gate(intermediate), up(intermediate)]."""
+    biases = _bq_bias("base_qmoe_swiglu", biases, scales, symmetric)
+    return _tt.base_qmoe_swiglu(codes, scales, biases, input, expert_of_tile, bits, group_size, scale_dtype,
+                                symmetric, layout)

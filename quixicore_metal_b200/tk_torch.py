@@ -594,3 +594,205 @@ def silu_mul_quant_int8(x, gate, act="swiglu", alpha=1.702, limit=7.0):
 def silu_mul_quant_fp8_group(x, gate, group_size=128, ue8m0=False, act="swiglu", alpha=1.702, limit=7.0):
     """Fused gated activation -> per-group fp8 (scale (rows, D/G); ue8m0 = 2^k scales)."""
     return _silu_mul_quant(x, gate, act, alpha, limit, 4, int(group_size), ue8m0, name="silu_mul_quant_fp8_group")
+
+
+# ---- BaseQN: separate code / scale / bias planes ------------------------------------------------------
+_BQ_SCALE = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "f16": torch.float16, "float16": torch.float16,
+             "e8m0": torch.uint8, "e4m3": torch.uint8}
+_BQ_OUT = {"float16": torch.float16, "f16": torch.float16, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           "float32": torch.float32, "f32": torch.float32}
+
+
+def _bq_desc(bits, group_size, scale_dtype, symmetric, layout):
+    """The descriptor checks of kernels/common/base_q_descriptor.h:34-68 (the library repeats them)."""
+    bits, group_size = int(bits), int(group_size)
+    _check(bits in (2, 3, 4, 5, 6, 8), "BaseQN: bits must be one of 2, 3, 4, 5, 6, or 8")
+    _check(group_size in (32, 64, 128), "BaseQN: group_size must be 32, 64, or 128")
+    _check(str(scale_dtype) in _BQ_SCALE, "BaseQN: scale_dtype must be bf16, f16, e8m0, or e4m3")
+    _check(str(scale_dtype) != "e4m3" or bits == 8, "BaseQN: e4m3 scale storage is valid only for q8")
+    _check(str(layout) in ("metal", "metal_lane_strided", f"metal_lane_strided_q{bits}"),
+           f"BaseQN: layout must be metal or metal_lane_strided_q{bits}")
+    return _lib.BaseQDescriptor(bits, group_size, str(scale_dtype).encode(), int(bool(symmetric)), str(layout).encode())
+
+
+def _bq_planes(name, codes, scales, biases, desc, rank=2):
+    """The storage checks of kernels/quantization/base_q/base_q.cpp:57-131.  Returns
+    (planes struct, kept-alive tensors, leading dims, K)."""
+    lead = "experts, output_rows" if rank == 3 else "rows"
+    _check(codes.is_cuda and codes.dtype == torch.uint8 and codes.dim() == rank,
+           f"{name}: codes must be uint8 ({lead}, packed_bytes)")
+    sd = _BQ_SCALE[desc.scale_dtype.decode()]
+    _check(scales.is_cuda and scales.dtype == sd and scales.dim() == rank,
+           f"{name}: scales must be a rank-{rank} tensor with the declared scale_dtype")
+    _check(all(int(n) > 0 for n in scales.shape) and tuple(scales.shape[:-1]) == tuple(codes.shape[:-1]),
+           f"{name}: codes/scales rows and group count must be positive and match")
+    K = scales.size(-1) * desc.group_size
+    _check(K * desc.bits % 8 == 0 and codes.size(-1) == K * desc.bits // 8,
+           f"{name}: codes.shape[{rank - 1}] must equal columns * bits / 8")
+    _check(desc.symmetric or biases is not None, f"{name}: biases are required for asymmetric BaseQN")
+    _check(biases is None or (biases.dtype == scales.dtype and tuple(biases.shape) == tuple(scales.shape)),
+           f"{name}: biases must match scales shape and dtype")
+    _same_device(name, codes, scales, biases)
+    keep = (codes.contiguous(), scales.contiguous(), None if biases is None else biases.contiguous())
+    return _lib.BaseQPlanes(_ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2])), keep, tuple(codes.shape[:-1]), K
+
+
+def _bq_ws(L, device, K, M, V, dtype):
+    n = L.qx_cuda_base_q_workspace_bytes(K, M, V, _DT[dtype])
+    return (_workspace(device, n), n) if n else (None, 0)
+
+
+def base_qdequant(codes, scales, biases, bits, group_size, scale_dtype="bf16", symmetric=False, layout="metal",
+                  output_dtype="float16"):
+    """Decode canonical BaseQN separate code / scale / bias planes to (rows, K)."""
+    desc = _bq_desc(bits, group_size, scale_dtype, symmetric, layout)
+    _check(str(output_dtype) in _BQ_OUT, "BaseQN: output_dtype must be float16, bfloat16, or float32")
+    planes, keep, (rows,), K = _bq_planes("base_qdequant", codes, scales, biases, desc)
+    with torch.cuda.device(codes.device):
+        out = torch.empty((rows, K), dtype=_BQ_OUT[str(output_dtype)], device=codes.device)
+        _lib.check(_lib.lib().qx_cuda_base_qdequant(_stream(), planes, desc, _ptr(out), rows, K, _DT[out.dtype]))
+    return out
+
+
+def base_qembedding(codes, scales, biases, ids, bits, group_size, scale_dtype="bf16", symmetric=False,
+                    layout="metal", output_dtype="float16"):
+    """Gather and decode BaseQN weight rows to ids.shape + (K,); ids outside the table give zero rows."""
+    desc = _bq_desc(bits, group_size, scale_dtype, symmetric, layout)
+    _check(str(output_dtype) in _BQ_OUT, "BaseQN: output_dtype must be float16, bfloat16, or float32")
+    planes, keep, (rows,), K = _bq_planes("base_qembedding", codes, scales, biases, desc)
+    _check(ids.is_cuda and ids.numel() > 0 and not ids.dtype.is_floating_point,
+           "base_qembedding: ids must be a non-empty integer tensor")
+    _same_device("base_qembedding", codes, ids)
+    with torch.cuda.device(codes.device):
+        ic = ids.to(torch.int32).contiguous()
+        out = torch.empty(tuple(ids.shape) + (K,), dtype=_BQ_OUT[str(output_dtype)], device=codes.device)
+        _lib.check(_lib.lib().qx_cuda_base_qembedding(_stream(), planes, desc, _ptr(ic), _ptr(out), rows, K,
+                                                      ic.numel(), _DT[out.dtype]))
+    return out
+
+
+def _bq_matmul(name, codes, scales, biases, x, desc, gemv_only):
+    planes, keep, (rows,), K = _bq_planes(name, codes, scales, biases, desc)
+    _check(x.is_cuda and x.dim() == 2 and x.size(0) == K, f"{name}: x must be (K, M) with K matching the packed weights")
+    _check(not gemv_only or x.size(1) == 1, "base_qgemv: x must be (K, 1)")
+    _check(x.dtype in _DT, "BaseQN matmul: x must be float16, bfloat16, or float32")
+    _check(x.size(1) > 0, "BaseQN matmul: M must be positive")
+    _same_device(name, codes, x)
+    M = x.size(1)
+    with torch.cuda.device(x.device):
+        xc = x.contiguous()
+        out = torch.empty((rows, M), dtype=x.dtype, device=x.device)
+        L = _lib.lib()
+        ws, n = _bq_ws(L, x.device, K, M, 0, x.dtype)
+        _lib.check(L.qx_cuda_base_qgemm(_stream(), planes, desc, _ptr(xc), _ptr(out), rows, K, M, _DT[x.dtype],
+                                        _ptr(ws), n))
+    return out
+
+
+def base_qgemv(codes, scales, biases, x, bits, group_size, scale_dtype="bf16", symmetric=False, layout="metal"):
+    """dequant(BaseQN weights) @ x for x (K, 1)."""
+    return _bq_matmul("base_qgemv", codes, scales, biases, x, _bq_desc(bits, group_size, scale_dtype, symmetric, layout), True)
+
+
+def base_qgemm(codes, scales, biases, x, bits, group_size, scale_dtype="bf16", symmetric=False, layout="metal"):
+    """dequant(BaseQN weights) @ x for x (K, M)."""
+    return _bq_matmul("base_qgemm", codes, scales, biases, x, _bq_desc(bits, group_size, scale_dtype, symmetric, layout), False)
+
+
+def base_qgemv_qkv(q_codes, q_scales, q_biases, k_codes, k_scales, k_biases, v_codes, v_scales, v_biases, x, bits,
+                   group_size, scale_dtype="bf16", symmetric=False, layout="metal"):
+    """Q / K / V decode projections of one (K, 1) activation in one launch; row counts may differ."""
+    name = "base_qgemv_qkv"
+    desc = _bq_desc(bits, group_size, scale_dtype, symmetric, layout)
+    q, kq, (qr,), K = _bq_planes(name, q_codes, q_scales, q_biases, desc)
+    k, kk, (kr,), K2 = _bq_planes(name, k_codes, k_scales, k_biases, desc)
+    v, kv, (vr,), K3 = _bq_planes(name, v_codes, v_scales, v_biases, desc)
+    _check(K == K2 == K3, f"{name}: q/k/v must share the inner dimension")
+    _check(x.is_cuda and x.dim() == 2 and x.size(0) == K and x.size(1) == 1 and x.dtype in _DT,
+           f"{name}: x must be (K, 1) float16, bfloat16, or float32")
+    _same_device(name, q_codes, k_codes, v_codes, x)
+    with torch.cuda.device(x.device):
+        xc = x.contiguous()
+        outs = [torch.empty((r, 1), dtype=x.dtype, device=x.device) for r in (qr, kr, vr)]
+        L = _lib.lib()
+        ws, n = _bq_ws(L, x.device, K, 1, 0, x.dtype)
+        _lib.check(L.qx_cuda_base_qgemv_qkv(_stream(), q, k, v, desc, _ptr(xc), _ptr(outs[0]), _ptr(outs[1]),
+                                            _ptr(outs[2]), qr, kr, vr, K, _DT[x.dtype], _ptr(ws), n))
+    return tuple(outs)
+
+
+def base_qgemv_swiglu(gate_codes, gate_scales, gate_biases, up_codes, up_scales, up_biases, x, bits, group_size,
+                      scale_dtype="bf16", symmetric=False, layout="metal"):
+    """silu(W_gate @ x) * (W_up @ x) straight from BaseQN planes, rounded once."""
+    name = "base_qgemv_swiglu"
+    desc = _bq_desc(bits, group_size, scale_dtype, symmetric, layout)
+    g, kg, (rows,), K = _bq_planes(name, gate_codes, gate_scales, gate_biases, desc)
+    u, ku, (rows2,), K2 = _bq_planes(name, up_codes, up_scales, up_biases, desc)
+    _check(rows == rows2 and K == K2, f"{name}: gate and up must have the same shape")
+    _check(x.is_cuda and x.dim() == 2 and x.size(0) == K and x.size(1) == 1 and x.dtype in _DT,
+           f"{name}: x must be (K, 1) float16, bfloat16, or float32")
+    _same_device(name, gate_codes, up_codes, x)
+    with torch.cuda.device(x.device):
+        xc = x.contiguous()
+        out = torch.empty((rows, 1), dtype=x.dtype, device=x.device)
+        L = _lib.lib()
+        ws, n = _bq_ws(L, x.device, K, 1, 0, x.dtype)
+        _lib.check(L.qx_cuda_base_qgemv_swiglu(_stream(), g, u, desc, _ptr(xc), _ptr(out), rows, K, _DT[x.dtype],
+                                               _ptr(ws), n))
+    return out
+
+
+def base_qlm_head_argmax(codes, scales, biases, x, bits, group_size, scale_dtype="bf16", symmetric=False,
+                         layout="metal"):
+    """Greedy token ids (batch,) int32 from a BaseQN LM head (V, K) and activations x (K, batch); logits
+    are rounded to the dtype of x, the lower id wins exact ties."""
+    name = "base_qlm_head_argmax"
+    desc = _bq_desc(bits, group_size, scale_dtype, symmetric, layout)
+    _check(x.dim() == 2 and x.size(1) > 0, "base_qlm_head_argmax: x must be non-empty (K, batch)")
+    planes, keep, (V,), K = _bq_planes(name, codes, scales, biases, desc)
+    _check(x.is_cuda and x.size(0) == K and x.dtype in _DT, f"{name}: x must be (K, batch) with K matching the packed weights")
+    _same_device(name, codes, x)
+    batch = x.size(1)
+    with torch.cuda.device(x.device):
+        xc = x.contiguous()
+        ids = torch.empty((batch,), dtype=torch.int32, device=x.device)
+        L = _lib.lib()
+        ws, n = _bq_ws(L, x.device, K, batch, V, x.dtype)
+        _lib.check(L.qx_cuda_base_qlm_head_argmax(_stream(), planes, desc, _ptr(xc), _ptr(ids), V, K, batch,
+                                                  _DT[x.dtype], _ptr(ws), n))
+    return ids
+
+
+def _bq_moe(name, codes, scales, biases, input, expert_of_tile, desc, swiglu):
+    planes, keep, (experts, expert_rows), K = _bq_planes(name, codes, scales, biases, desc, rank=3)
+    _check(input.is_cuda and input.dim() == 2 and input.size(1) == K and input.dtype in (torch.float16, torch.bfloat16),
+           f"{name}: input must be (total_rows, K) float16 or bfloat16")
+    total = input.size(0)
+    _check(total > 0 and total % 32 == 0, f"{name}: input rows must be a positive multiple of 32")
+    _check(expert_of_tile.is_cuda and expert_of_tile.dtype == torch.int32 and expert_of_tile.numel() == total // 32,
+           f"{name}: expert_of_tile must be int32 (total_rows / 32,)")
+    _check(not swiglu or expert_rows % 2 == 0, f"{name}: the gate/up row axis must be even")
+    _same_device(name, codes, input, expert_of_tile)
+    cols = expert_rows // 2 if swiglu else expert_rows
+    with torch.cuda.device(input.device):
+        xc, ec = input.contiguous(), expert_of_tile.contiguous()
+        out = torch.zeros((total, cols), dtype=input.dtype, device=input.device)
+        L = _lib.lib()
+        ws, n = _bq_ws(L, input.device, K, total, 0, input.dtype)
+        _lib.check(L.qx_cuda_base_qmoe(_stream(), planes, desc, _ptr(xc), _ptr(ec), _ptr(out), experts, expert_rows,
+                                       K, total, int(swiglu), _DT[input.dtype], _ptr(ws), n))
+    return out
+
+
+def base_qmoe_gemm(codes, scales, biases, input, expert_of_tile, bits, group_size, scale_dtype="bf16",
+                   symmetric=False, layout="metal"):
+    """Padded MoE rows through a BaseQN expert stack: (total_rows, K) -> (total_rows, output_rows)."""
+    return _bq_moe("base_qmoe_gemm", codes, scales, biases, input, expert_of_tile,
+                   _bq_desc(bits, group_size, scale_dtype, symmetric, layout), False)
+
+
+def base_qmoe_swiglu(codes, scales, biases, input, expert_of_tile, bits, group_size, scale_dtype="bf16",
+                     symmetric=False, layout="metal"):
+    """Grouped expert gate / up projection with SwiGLU; the row axis is [gate(I), up(I)]."""
+    return _bq_moe("base_qmoe_swiglu", codes, scales, biases, input, expert_of_tile,
+                   _bq_desc(bits, group_size, scale_dtype, symmetric, layout), True)

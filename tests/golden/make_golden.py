@@ -12,6 +12,8 @@ out of the reference's LM-head test file.  Outputs (all small, committed):
     codecs.npz      e4m3 / e2m1 decode tables from the reference's codebooks
     rng.npz         rng_uniform / gumbel samples from the reference's numpy twin
     compose.npz     reference torch-CPU outputs of decode_linear_epilogue / decode_swiglu
+    base_q.npz      BaseQN planes packed and dequantised by the reference's numpy helpers
+                    (`bindings/python/tk/base_q.py`) for every code width, scale storage and group size
 """
 import ast
 import os
@@ -90,6 +92,41 @@ def main(ref_root: str) -> None:
         comp[f"{fmt}_bias2"] = bias2.float().numpy()
         comp[f"{fmt}_res"] = res.float().numpy()
     np.savez_compressed(os.path.join(here, "compose.npz"), **comp)
+
+    # ---- BaseQN separate planes: the reference's numpy pack + dequantise ----
+    import tk.base_q as bq  # noqa: E402
+    base = {}
+    cases = [(bits, "f16", 32, sym) for bits in bq.BASE_Q_BITS for sym in (False, True)]
+    cases += [(4, "bf16", 64, False), (4, "e8m0", 128, False), (8, "e4m3", 32, False), (3, "e8m0", 64, True)]
+    for i, (bits, sd, group, sym) in enumerate(cases):
+        rng = np.random.default_rng(300 + i)
+        rows, K = 5, 256
+        lanes = rng.integers(0, 1 << bits, size=(rows, K), dtype=np.uint8)
+        G = K // group
+        if sd in ("bf16", "f16"):
+            sv = (0.002 + 0.02 * rng.random((rows, G))).astype(np.float32)
+            bv = (-0.05 + 0.1 * rng.random((rows, G))).astype(np.float32)
+            if sd == "f16":
+                scales, biases = sv.astype(np.float16).view(np.uint16), bv.astype(np.float16).view(np.uint16)
+            else:
+                scales = torch.from_numpy(sv).bfloat16().view(torch.int16).numpy().view(np.uint16)
+                biases = torch.from_numpy(bv).bfloat16().view(torch.int16).numpy().view(np.uint16)
+        else:
+            scales = rng.integers(1, 255, size=(rows, G), dtype=np.uint8) if sd == "e8m0" else \
+                rng.integers(0, 256, size=(rows, G), dtype=np.uint8)
+            biases = rng.integers(100, 140, size=(rows, G), dtype=np.uint8) if sd == "e8m0" else \
+                rng.integers(0, 256, size=(rows, G), dtype=np.uint8)
+        packed = bq.pack_base_q_codes(lanes, bits)
+        key = f"b{bits}_{sd}_g{group}_{'sym' if sym else 'asym'}"
+        base[key + "_lanes"] = lanes
+        base[key + "_codes"] = packed
+        base[key + "_scales"] = scales
+        base[key + "_biases"] = biases
+        with np.errstate(over="ignore", invalid="ignore"):
+            base[key + "_dequant"] = bq.dequantize_base_q(packed, scales, None if sym else biases, bits, group, sd, sym)
+    base["e8m0_table"] = bq.decode_e8m0(np.arange(256, dtype=np.uint8))
+    base["e4m3_table"] = bq.decode_e4m3(np.arange(256, dtype=np.uint8))
+    np.savez_compressed(os.path.join(here, "base_q.npz"), **base)
     print("golden fixtures written to", here)
 
 

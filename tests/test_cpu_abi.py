@@ -224,6 +224,7 @@ def test_header_layout_static_asserts(tmp_path):
 _REF_TK_TORCH = "/root/reference/bindings/pytorch_mps/tk_torch/__init__.py"
 # (name, positional parameters with defaults) of bindings/pytorch_mps/tk_torch/__init__.py:932-958,
 # :1620-1637, :1738-1745, kept here so the check also runs where the reference checkout is absent
+_BQ_TAIL = ["bits", "group_size", "scale_dtype='bf16'", "symmetric=False", "layout='metal'"]
 _SIGNATURES = {
     "decode_linear_epilogue": ["x", "weight", "bias", "residual", "format=''", "activation=0",
                                "use_bias=False", "use_residual=False"],
@@ -249,6 +250,17 @@ _SIGNATURES = {
     "sample_categorical": ["logits", "temperature=1.0", "seed=0"],
     "top_k_sample": ["logits", "k", "temperature=1.0", "seed=0"],
     "top_p_sample": ["logits", "p", "temperature=1.0", "seed=0"],
+    "base_qdequant": ["codes", "scales", "biases", *_BQ_TAIL, "output_dtype='float16'"],
+    "base_qembedding": ["codes", "scales", "biases", "ids", *_BQ_TAIL, "output_dtype='float16'"],
+    "base_qgemv": ["codes", "scales", "biases", "x", *_BQ_TAIL],
+    "base_qgemm": ["codes", "scales", "biases", "x", *_BQ_TAIL],
+    "base_qgemv_qkv": ["q_codes", "q_scales", "q_biases", "k_codes", "k_scales", "k_biases", "v_codes", "v_scales",
+                       "v_biases", "x", *_BQ_TAIL],
+    "base_qgemv_swiglu": ["gate_codes", "gate_scales", "gate_biases", "up_codes", "up_scales", "up_biases", "x",
+                          *_BQ_TAIL],
+    "base_qlm_head_argmax": ["codes", "scales", "biases", "x", *_BQ_TAIL],
+    "base_qmoe_gemm": ["codes", "scales", "biases", "input", "expert_of_tile", *_BQ_TAIL],
+    "base_qmoe_swiglu": ["codes", "scales", "biases", "input", "expert_of_tile", *_BQ_TAIL],
 }
 
 

@@ -208,3 +208,59 @@ def test_beam_advance_oracle_first_step():
         lsm = row - (row.max() + np.log(np.exp(row - row.max()).sum()))
         np.testing.assert_array_equal(tok[b], np.argsort(-lsm, kind="stable")[:2])
         np.testing.assert_allclose(score[b], np.sort(lsm)[::-1][:2], rtol=1e-6)
+
+
+# ---- BaseQN separate planes ------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def BQ(golden_dir):
+    return np.load(os.path.join(golden_dir, "base_q.npz"))
+
+
+def test_base_q_known_answer_bytes():
+    # tests/correctness/quantization/base_q/test_base_q_layout.py:22-44
+    for bits, lanes, want in [(2, [0, 1, 2, 3] * 4, [0xE4] * 4), (3, list(range(8)), [0x88, 0xC6, 0xFA]),
+                              (4, list(range(8)), [0x10, 0x32, 0x54, 0x76]),
+                              (5, list(range(8)), [0x20, 0x88, 0x41, 0x8A, 0x39]),
+                              (6, list(range(4)), [0x40, 0x20, 0x0C]), (8, list(range(8)), list(range(8)))]:
+        np.testing.assert_array_equal(O.base_q_pack(np.array([lanes], np.uint8), bits), np.array([want], np.uint8))
+    np.testing.assert_array_equal(O.base_q_pack(np.array([[0xA, 0xB, 0xC, 0xD, 0xE, 0xF, 0x1, 0x2]]), 4),
+                                  [[0xBA, 0xDC, 0xFE, 0x21]])
+    # scale codecs at their edges (:58-64)
+    e8 = O.base_q_scale_values(np.array([0, 1, 127, 128, 254, 255], np.uint8), "e8m0")
+    assert e8[0] == np.float32(2.0 ** -127) and e8[2] == 1.0 and e8[3] == 2.0 and np.isinf(e8[-1])
+    np.testing.assert_array_equal(O.base_q_scale_values(np.array([0x00, 0x01, 0x38, 0x40, 0xB8], np.uint8), "e4m3"),
+                                  np.array([0.0, 2.0 ** -9, 1.0, 2.0, -1.0], np.float32))
+
+
+def test_base_q_pack_and_dequantize_match_reference_bit_for_bit(BQ):
+    keys = sorted(k[:-6] for k in BQ.files if k.endswith("_lanes"))
+    assert len(keys) == 16
+    for key in keys:
+        bits = int(key[1]); _, sd, g, mode = key.split("_")
+        group, sym = int(g[1:]), mode == "sym"
+        np.testing.assert_array_equal(O.base_q_pack(BQ[key + "_lanes"], bits), BQ[key + "_codes"])
+        np.testing.assert_array_equal(O.base_q_unpack(BQ[key + "_codes"], bits), BQ[key + "_lanes"])
+        with np.errstate(over="ignore", invalid="ignore"):
+            got = O.base_q_dequantize(BQ[key + "_codes"], BQ[key + "_scales"], None if sym else BQ[key + "_biases"],
+                                      bits, group, sd, sym)
+        np.testing.assert_array_equal(got.view(np.uint32), BQ[key + "_dequant"].view(np.uint32))
+    np.testing.assert_array_equal(O.e8m0_decode(np.arange(256)).view(np.uint32), BQ["e8m0_table"].view(np.uint32))
+    np.testing.assert_array_equal(O.e4m3_decode(np.arange(256)).view(np.uint32), BQ["e4m3_table"].view(np.uint32))
+
+
+def test_base_q_consumers_on_the_reference_test_planes():
+    # the hand-made planes of tests/correctness/quantization/base_q/test_base_q.py:20-56 (bf16 scales)
+    bits, group = 5, 32
+    lane = ((np.arange(3 * 64, dtype=np.uint16).reshape(3, 64) * 5 + 3) % (1 << bits)).astype(np.uint8)
+    scales = np.array([[0.125, 0.25], [0.5, 0.0625], [0.03125, 1.0]], np.float32)
+    biases = np.array([[0.5, 1.0], [0.25, 0.125], [2.0, 0.0625]], np.float32)
+    W = O.base_q_dequantize(O.base_q_pack(lane, bits), scales, biases, bits, group, "bf16")
+    np.testing.assert_array_equal(W[1, :3], lane[1, :3] * np.float32(0.5) + np.float32(0.25))
+    # embedding: invalid ids give zero rows (:318-329)
+    got = O.base_q_embedding(W, np.array([[2, -1], [99, 0]]), "f32")
+    np.testing.assert_array_equal(got, np.stack([W[2], 0 * W[0], 0 * W[0], W[0]]).reshape(2, 2, -1))
+    # all-equal logits: the lowest id wins (:213-225)
+    ids, _, _ = O.base_q_lm_head_argmax(np.zeros((17, 32), np.float32), np.ones((32, 2), np.float32), "f16")
+    np.testing.assert_array_equal(ids, [0, 0])
+    with pytest.raises(ValueError):
+        O.base_q_dequantize(O.base_q_pack(lane, bits), np.zeros((3, 2), np.uint8), np.zeros((3, 2), np.uint8), bits, 32, "e4m3")
