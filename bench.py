@@ -231,6 +231,91 @@ def gemv_case(spec: str, device, peak_gbs: float, iters: int = 30):
             "frac_of_measured_peak": round(gbs / peak_gbs, 4), "l2": f"{copies} weight copies rotated (> 2x L2)"}
 
 
+def _base_q_planes(rows, K, bits, group, device, seed):
+    """Seeded BaseQN planes on the device: random codes, bf16 scales in [0.002, 0.022), biases in +-0.05."""
+    g = torch.Generator(device=device); g.manual_seed(seed)
+    codes = torch.randint(0, 256, (rows, K * bits // 8), dtype=torch.uint8, device=device, generator=g)
+    scales = (0.002 + 0.02 * torch.rand((rows, K // group), device=device, generator=g)).bfloat16()
+    biases = (-0.05 + 0.1 * torch.rand((rows, K // group), device=device, generator=g)).bfloat16()
+    return codes, scales, biases
+
+
+def base_q_case(spec: str, device, peak_gbs: float, iters: int = 30):
+    """One BaseQN gemv / gemm workload, eager calls: `bits,group,M,K,N[,sym]` (bf16 scales).  The command the
+    base_q_stream_kernel capture under profiles/ runs (`python bench.py --base-q-case 4,32,1,8192,28672`)."""
+    from quixicore_metal_b200 import tk
+    parts = spec.split(",")
+    bits, group, M, K, N = (int(v) for v in parts[:5])
+    sym = len(parts) > 5 and parts[5] in ("1", "sym")
+    one = N * K * bits // 8 + N * (K // group) * 2 * (1 if sym else 2)
+    copies = max(2, -(-2 * L2_BYTES // one))
+    ws = [_base_q_planes(N, K, bits, group, device, 70 + c) for c in range(copies)]
+    x = torch.randn((K, M), device=device).bfloat16()
+
+    def step(i):
+        c, sc, b = ws[i % copies]
+        return tk.base_qgemm(c, sc, None if sym else b, x, bits, group, "bf16", symmetric=sym)
+    for i in range(5):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        step(i)
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    gbs = one / (ms * 1e-3) / 1e9
+    return {"case": spec, "ms_eager": round(ms, 5), "plane_bytes": one, "gbs": round(gbs, 1),
+            "frac_of_measured_peak": round(gbs / peak_gbs, 4), "l2": f"{copies} weight copies rotated (> 2x L2)"}
+
+
+def base_q_sweep(device, peak_gbs: float):
+    """BaseQN decode GEMV (K 8192 -> N 28672, batch 1, bf16 planes), graph-replayed calls."""
+    from quixicore_metal_b200 import tk
+    res = []
+    K, N = 8192, 28672
+    x = torch.randn((K, 1), device=device).bfloat16()
+    for bits, group, sym in ((4, 32, False), (4, 128, True), (8, 32, False), (2, 64, False)):
+        one = N * K * bits // 8 + N * (K // group) * 2 * (1 if sym else 2)
+        copies = max(2, -(-2 * L2_BYTES // one))
+        ws = [_base_q_planes(N, K, bits, group, device, 90 + c) for c in range(copies)]
+
+        def step(i):
+            c, sc, b = ws[i % copies]
+            return tk.base_qgemv(c, sc, None if sym else b, x, bits, group, "bf16", symmetric=sym)
+        ms = _graph_ms(step, copies)
+        gbs = one / (ms * 1e-3) / 1e9
+        res.append({"op": "base_qgemv", "bits": bits, "group": group, "symmetric": sym, "M": 1, "K": K, "N": N,
+                    "ms": round(ms, 5), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4)})
+        del ws
+    return res
+
+
+def _graph_ms(step, copies: int, reps: int = 5):
+    """Per-call time of `step` replayed from a CUDA graph that holds one call per weight copy."""
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for i in range(2):
+            step(i)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(copies):
+                step(i)
+    torch.cuda.synchronize()
+    for _ in range(2):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record(); torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * copies)
+
+
 def gemv_sweep(device, peak_gbs: float):
     """Packed GEMV bandwidth of the batch-1..8 projection configurations (algorithmic bytes / time)."""
     from quixicore_metal_b200 import tk
@@ -441,6 +526,8 @@ def main():
     ap.add_argument("--no-stack", action="store_true", help="skip the 70B-shaped projection stack")
     ap.add_argument("--gemv-case", default=None, metavar="FMT,M,K,N[,swiglu]",
                     help="time one projection workload (eager calls) and print its line instead of the bench")
+    ap.add_argument("--base-q-case", default=None, metavar="BITS,GROUP,M,K,N[,sym]",
+                    help="time one BaseQN gemv / gemm workload (eager calls) and print its line instead of the bench")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -463,6 +550,10 @@ def main():
     if args.gemv_case:
         assert world == 1, "--gemv-case is a single-GPU run"
         emit_json_line(gemv_case(args.gemv_case, device, peak_gbs))
+        return
+    if args.base_q_case:
+        assert world == 1, "--base-q-case is a single-GPU run"
+        emit_json_line(base_q_case(args.base_q_case, device, peak_gbs))
         return
 
     ids_match, ids_diff = sharded_ids_check(device, world, rank)
@@ -589,6 +680,7 @@ def main():
         line["roofline"]["stack_ms_per_step"] = {f"M{r['M']}": r["ms_per_step"] for r in stack}
     if world == 1 and not args.no_sweep:
         line["gemv"] = gemv_sweep(device, peak_gbs)
+        line["base_q"] = base_q_sweep(device, peak_gbs)
         # the "quant GEMV HBM GB/s" half of the metric, compact: fraction of the measured copy
         # bandwidth at batch 1 per format (K 8192 -> N 28672), graph-replayed calls
         line["roofline"]["gemv_batch1_frac_of_measured"] = {

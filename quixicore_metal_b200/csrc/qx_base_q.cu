@@ -272,7 +272,7 @@ struct BQCursor {
 // code * x), S[c,n] the sum of the 32 prepared activations, beta = bias (asymmetric) or
 // -2^(BITS-1) * scale (symmetric).
 template <int BITS, int NC>
-__global__ void __launch_bounds__(BQ_MAX_WARPS * 32, 1)
+__global__ void __launch_bounds__((NC == 8 ? 12 : BQ_MAX_WARPS) * 32, 1)
 base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                      const __grid_constant__ CUtensorMap map2, const BQStreamParams p) {
   using G = BQGeom<BITS>;
@@ -411,26 +411,36 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     consumed = i + 1;
     const uint32_t base = myring + slot * G::BOX_BYTES;
     const uint32_t rowA = base + g * G::PITCH + t * BITS, rowB = rowA + 8 * G::PITCH;
-    const __half* xr = g < ncol ? p.x16 + (size_t)(col0 + g) * K + (size_t)stage * BQ_KC + 8 * t : nullptr;
+    // lanes whose column does not exist read column 0: their D columns are never written out
+    const __half* xr = p.x16 + (size_t)(col0 + (g < ncol ? g : 0)) * K + (size_t)stage * BQ_KC + 8 * t;
     const int nch = min(16, nchunks - stage * 16);
-    uint4 bnext = ldg_or_zero(xr, 0);
+    auto chunk = [&](int c, const uint4& bv) {
+      uint32_t pa[4], pb[4];
+      bq_pairs<BITS>(rowA + c * 4 * BITS, pa);
+      bq_pairs<BITS>(rowB + c * 4 * BITS, pb);
+      float d[4];
+      mma_f16_zero(d, pa[0], pb[0], pa[1], pb[1], bv.x, bv.y);
+      mma_f16(d, pa[2], pb[2], pa[3], pb[3], bv.z, bv.w);
+      const int src = (lane & ~3) | (c >> 2);
+      const float sA = __shfl_sync(0xffffffffu, sfc[0][c & 3], src);
+      const float sB = __shfl_sync(0xffffffffu, sfc[1][c & 3], src);
+      acc[0] = fmaf(sA, d[0], acc[0]); acc[1] = fmaf(sA, d[1], acc[1]);
+      acc[2] = fmaf(sB, d[2], acc[2]); acc[3] = fmaf(sB, d[3], acc[3]);
+    };
+    if (nch == 16) {                               // a whole stage: no branches, the activation loads 4 chunks ahead
+      uint4 bq[4];
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      if (c < nch) {
-        const uint4 bv = bnext;
-        if (c + 1 < nch) bnext = ldg_or_zero(xr, (c + 1) * 32);
-        uint32_t pa[4], pb[4];
-        bq_pairs<BITS>(rowA + c * 4 * BITS, pa);
-        bq_pairs<BITS>(rowB + c * 4 * BITS, pb);
-        float d[4];
-        mma_f16_zero(d, pa[0], pb[0], pa[1], pb[1], bv.x, bv.y);
-        mma_f16(d, pa[2], pb[2], pa[3], pb[3], bv.z, bv.w);
-        const int src = (lane & ~3) | (c >> 2);
-        const float sA = __shfl_sync(0xffffffffu, sfc[0][c & 3], src);
-        const float sB = __shfl_sync(0xffffffffu, sfc[1][c & 3], src);
-        acc[0] = fmaf(sA, d[0], acc[0]); acc[1] = fmaf(sA, d[1], acc[1]);
-        acc[2] = fmaf(sB, d[2], acc[2]); acc[3] = fmaf(sB, d[3], acc[3]);
+      for (int c = 0; c < 4; ++c) bq[c] = __ldg(reinterpret_cast<const uint4*>(xr + c * 32));
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const uint4 bv = bq[c & 3];
+        if (c + 4 < 16) bq[c & 3] = __ldg(reinterpret_cast<const uint4*>(xr + (c + 4) * 32));
+        chunk(c, bv);
       }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        if (c < nch) chunk(c, __ldg(reinterpret_cast<const uint4*>(xr + c * 32)));
     }
     __syncwarp();
     if (issued < n_items) { issue(issued); ++issued; }
@@ -501,7 +511,7 @@ static inline size_t bq_align256(size_t n) { return (n + 255) & ~(size_t)255; }
 static bool bq_stream_fits(int bits, int64_t K, int* warps, int* nst, size_t* smem) {
   const int pitch = BQ_KC * bits / 8 + 16, box = 16 * pitch;
   const size_t fixed = (size_t)(K / 32 + 16) * 32 + BQ_SLOTS * 256 * 4 + BQ_SLOTS * 8 + BQ_MAX_WARPS * 64 + 128;
-  const size_t budget = 226 * 1024;
+  const size_t budget = 168 * 1024;     // the rest of the SM's 256 KB stays L1: every warp re-reads the activations
   for (int w : {16, 12, 8}) {
     if (fixed + (size_t)w * 2 * box > budget) continue;
     int n = (int)((budget - fixed) / ((size_t)w * box));
@@ -542,7 +552,8 @@ static bool bq_launch_stream(cudaStream_t st, const CUtensorMap* maps, const BQS
                              int warps, size_t smem) {
   if (p.M == 1) return bq_launch_stream_nc<BITS, 1>(st, maps, p, gx, gy, warps, smem);
   if (p.M <= 4) return bq_launch_stream_nc<BITS, 4>(st, maps, p, gx, gy, warps, smem);
-  return bq_launch_stream_nc<BITS, 8>(st, maps, p, gx, gy, warps, smem);
+  // 8 columns: wider bias-path accumulators, so at most 12 warps of up to 168 registers
+  return bq_launch_stream_nc<BITS, 8>(st, maps, p, gx, gy, warps > 12 ? 12 : warps, smem);
 }
 
 // One launch over up to three weight matrices (mode 0) or a gate / up pair (mode 1).  x: (K, M) when
