@@ -231,6 +231,35 @@ def gemv_case(spec: str, device, peak_gbs: float, iters: int = 30):
             "frac_of_measured_peak": round(gbs / peak_gbs, 4), "l2": f"{copies} weight copies rotated (> 2x L2)"}
 
 
+def lm_head_case(spec: str, device, peak_gbs: float, iters: int = 10):
+    """One fused LM-head workload on a q8_0 head, eager calls: `V,K,T,mode` (mode argmax / topk / topp with the
+    bench's k, temperature and top_p).  The command the stage-1 kernel captures under profiles/ run
+    (`python bench.py --lm-head-case 37888,4096,64,topp`)."""
+    from quixicore_metal_b200 import tk
+    V, K, T = (int(v) for v in spec.split(",")[:3])
+    mode = spec.split(",")[3]
+    one = V * (K // 32) * 34
+    copies = max(2, -(-2 * L2_BYTES // one))
+    ws = [synth_q8_0(V, K, SEED + c, device) for c in range(copies)]
+    h = torch.randn((T, K), device=device).bfloat16()
+    kw = {"argmax": {}, "topk": {"k": 50, "temperature": TEMP}, "topp": {"k": TOPK, "temperature": TEMP, "top_p": TOP_P}}[mode]
+
+    def step(i):
+        return tk.lm_head_sample(h, ws[i % copies], mode=mode, seed=SEED + i, format="q8_0", **kw)
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        step(i)
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    gbs = one / (ms * 1e-3) / 1e9
+    return {"case": spec, "ms_eager": round(ms, 5), "packed_bytes": one, "gbs": round(gbs, 1),
+            "frac_of_measured_peak": round(gbs / peak_gbs, 4), "l2": f"{copies} weight copies rotated (> 2x L2)"}
+
+
 def _base_q_planes(rows, K, bits, group, device, seed):
     """Seeded BaseQN planes on the device: random codes, bf16 scales in [0.002, 0.022), biases in +-0.05."""
     g = torch.Generator(device=device); g.manual_seed(seed)
@@ -526,6 +555,8 @@ def main():
     ap.add_argument("--no-stack", action="store_true", help="skip the 70B-shaped projection stack")
     ap.add_argument("--gemv-case", default=None, metavar="FMT,M,K,N[,swiglu]",
                     help="time one projection workload (eager calls) and print its line instead of the bench")
+    ap.add_argument("--lm-head-case", default=None, metavar="V,K,T,MODE",
+                    help="time one fused LM-head workload (q8_0, eager calls) and print its line instead of the bench")
     ap.add_argument("--base-q-case", default=None, metavar="BITS,GROUP,M,K,N[,sym]",
                     help="time one BaseQN gemv / gemm workload (eager calls) and print its line instead of the bench")
     args = ap.parse_args()
@@ -550,6 +581,10 @@ def main():
     if args.gemv_case:
         assert world == 1, "--gemv-case is a single-GPU run"
         emit_json_line(gemv_case(args.gemv_case, device, peak_gbs))
+        return
+    if args.lm_head_case:
+        assert world == 1, "--lm-head-case is a single-GPU run"
+        emit_json_line(lm_head_case(args.lm_head_case, device, peak_gbs))
         return
     if args.base_q_case:
         assert world == 1, "--base-q-case is a single-GPU run"
