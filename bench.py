@@ -468,6 +468,28 @@ def sharded_ids_check(device, world: int, rank: int):
     return float(t.item()) == 0.0, int(t.item())
 
 
+def stack_layer_check(device, world: int, rank: int) -> bool:
+    """One decoder-block of a reduced stack (hidden 1024, Q 2048, KV 1024, intermediate 4096, NVFP4, 4 rows),
+    generated from the same seed on every rank: the tensor-parallel layer over `world` GPUs against the
+    unsharded layer on this GPU.  Equal up to the order of the K summation: within 2 bf16 ulps."""
+    import torch.distributed as dist
+    from quixicore_metal_b200 import parallel
+    hidden, q, kv, inter, fmt = 1024, 2048, 1024, 4096, "nvfp4"
+    mk = lambda n, k, sd: synth_random_blocks(fmt, n, k, sd, device)
+    full = {"qkv": mk(q + 2 * kv, hidden, 9001), "o": mk(hidden, q, 9002), "gate": mk(inter, hidden, 9003),
+            "up": mk(inter, hidden, 9004), "down": mk(hidden, inter, 9005)}
+    g = torch.Generator(device="cpu"); g.manual_seed(77)
+    x = (torch.randn((4, hidden), generator=g) * 0.05).bfloat16().to(device)
+    ref = parallel.TPDecodeStack([full], fmt, tensor_parallel=False).layer(x, full).float()
+    mine = parallel.TPDecodeStack.shard_layer(full, rank, world, fmt, q, kv)
+    got = parallel.TPDecodeStack([mine], fmt).layer(x, mine).float()
+    tol = ref.abs() * 2.0 ** -6 + 1e-3 * ref.abs().max()
+    ok = torch.tensor([1.0 if bool(((got - ref).abs() <= tol).all()) else 0.0], device=device)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return float(ok.item()) > 0.5
+
+
 def stack_sweep(device, world: int, rank: int, peak_gbs: float, layers: int = 80):
     """Llama-3-70B-shaped decode projection stack (80 layers, hidden 8192, QKV 10240, O, gate/up
     2 x 28672, down; NVFP4; attention = identity on V), tensor-parallel over `world` GPUs with an NCCL
@@ -677,6 +699,7 @@ def main():
 
     del shards, heads
     torch.cuda.empty_cache()
+    stack_ok = None if args.no_stack else stack_layer_check(device, world, rank)
     stack = None if args.no_stack else stack_sweep(device, world, rank, peak_gbs)
 
     ms_per_step = total_ms / args.steps
@@ -712,6 +735,7 @@ def main():
         line["lm_head"] = lm_sweep
     if stack is not None:
         line["stack"] = stack
+        line["stack_layer_matches_unsharded"] = bool(stack_ok)
         line["roofline"]["stack_ms_per_step"] = {f"M{r['M']}": r["ms_per_step"] for r in stack}
     if world == 1 and not args.no_sweep:
         line["gemv"] = gemv_sweep(device, peak_gbs)

@@ -19,6 +19,15 @@ struct BlockScratch {
   unsigned u[8];
 };
 
+// hist[bin] += 1 for every lane with `pred`; the lanes of a warp that hit the same bin share one
+// atomic (the top byte of float keys takes only a few values, so unaggregated atomics serialise).
+// Every lane of the warp must call it.
+__device__ __forceinline__ void hist_add(unsigned* hist, bool pred, unsigned bin) {
+  const unsigned lane = threadIdx.x & 31u;
+  const unsigned peers = __match_any_sync(0xffffffffu, pred ? bin : (0x100u + lane));
+  if (pred && (unsigned)(__ffs((int)peers) - 1) == lane) atomicAdd(&hist[bin], (unsigned)__popc(peers));
+}
+
 __device__ __forceinline__ void block_argmax(float& v, int& id, BlockScratch& s) {
   warp_argmax(v, id);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;

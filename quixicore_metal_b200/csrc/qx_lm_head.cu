@@ -976,10 +976,11 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
       for (int shift = 24; shift >= 0; shift -= 8) {
         for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
         __syncthreads();
-        for (long long j = tid; j < ncand; j += nth) {
-          if (ci(j) < 0) continue;
-          const uint32_t key = float_key(cv(j));
-          if ((key & mask) == prefix) atomicAdd(&S.hist[(key >> shift) & 255u], 1u);
+        for (long long j0 = 0; j0 < ncand; j0 += nth) {      // warp-uniform trip count
+          const long long j = j0 + tid;
+          const bool ok = j < ncand && ci(j) >= 0;
+          const uint32_t key = ok ? float_key(cv(j)) : 0u;
+          hist_add(S.hist, ok && (key & mask) == prefix, (key >> shift) & 255u);
         }
         __syncthreads();
         if (tid == 0) {

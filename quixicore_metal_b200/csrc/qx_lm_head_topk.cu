@@ -73,10 +73,11 @@ lmh_topk_logprob_kernel(const float* __restrict__ val, const int32_t* __restrict
     for (int shift = 24; shift >= 0; shift -= 8) {
       for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
       __syncthreads();
-      for (long long j = tid; j < n; j += nth) {
-        if (!valid(j)) continue;
-        const uint32_t key = float_key(v[j]);
-        if ((key & mask) == prefix) atomicAdd(&S.hist[(key >> shift) & 255u], 1u);
+      for (long long j0 = 0; j0 < n; j0 += nth) {            // warp-uniform trip count
+        const long long j = j0 + tid;
+        const bool ok = j < n && valid(j);
+        const uint32_t key = ok ? float_key(v[j]) : 0u;
+        hist_add(S.hist, ok && (key & mask) == prefix, (key >> shift) & 255u);
       }
       __syncthreads();
       if (tid == 0) {

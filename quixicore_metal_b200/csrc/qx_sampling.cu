@@ -41,9 +41,11 @@ sample_logits_kernel(const T* __restrict__ logits, int32_t* __restrict__ ids, in
       for (int shift = 24; shift >= 0; shift -= 8) {
         for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
         __syncthreads();
-        for (int i = tid; i < V; i += nth) {
-          const uint32_t key = float_key(to_f32<T>(lr[i]));
-          if ((key & mask) == prefix) atomicAdd(&S.hist[(key >> shift) & 255u], 1u);
+        for (int i0 = 0; i0 < V; i0 += nth) {                // warp-uniform trip count
+          const int i = i0 + tid;
+          const bool ok = i < V;
+          const uint32_t key = ok ? float_key(to_f32<T>(lr[i])) : 0u;
+          hist_add(S.hist, ok && (key & mask) == prefix, (key >> shift) & 255u);
         }
         __syncthreads();
         if (tid == 0) {

@@ -194,10 +194,12 @@ class TPDecodeStack:
     Partial sums cross the ranks in fp32 (not in the 16-bit I/O type), so the only difference from
     the single-device result is the order of the K summation."""
 
-    def __init__(self, layers, fmt: str, head_dim: int = 128, group=None):
+    def __init__(self, layers, fmt: str, head_dim: int = 128, group=None, tensor_parallel: bool = True):
         import torch.distributed as dist
         self.dist, self.group = dist, group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        # tensor_parallel=False: `layers` are whole (unsharded) tensors and no collective runs, even
+        # inside an initialised process group (the single-device result the sharded one is checked against)
+        self.world = dist.get_world_size(group) if (tensor_parallel and dist.is_initialized()) else 1
         self.layers, self.fmt, self.head_dim = layers, fmt, head_dim
         bk = _LM_QUANT_BLOCK_K[fmt]
         l0 = layers[0]
