@@ -32,12 +32,6 @@ __device__ __forceinline__ float bq_scale_at(const uint8_t* __restrict__ plane, 
   if (stype == 2) return e8m0_to_f32(__ldg(plane + index));
   return e4m3_to_f32(__ldg(plane + index));
 }
-__device__ __forceinline__ float bq_scale_bits(uint32_t raw, int stype) {
-  if (stype == 0) return __uint_as_float(raw << 16);
-  if (stype == 1) return __half2float(__ushort_as_half((unsigned short)raw));
-  if (stype == 2) return e8m0_to_f32(raw);
-  return e4m3_to_f32(raw);
-}
 __host__ __device__ inline int bq_scale_bytes(int stype) { return stype < 2 ? 2 : 1; }
 
 // the 8 codes that start at column c8 * 8 (bits bytes, byte aligned) as one 64-bit string
@@ -147,7 +141,7 @@ namespace {
 
 // ---- streaming tensor-core kernel ---------------------------------------------------------------
 constexpr int BQ_KC = 512;            // columns per stage
-constexpr int BQ_SLOTS = 4;           // tiles whose partial sums can be open at once in a CTA
+constexpr int BQ_SLOTS = 16;          // tiles whose partial sums can be open at once in a CTA
 constexpr int BQ_MAX_WARPS = 16;
 
 template <int BITS> struct BQGeom {
@@ -326,14 +320,17 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
   const int b = blockIdx.x, Gx = gridDim.x;
   const int my_tiles = b < p.tiles ? (p.tiles - b + Gx - 1) / Gx : 0;
   const int J = my_tiles * spt;                                       // fits: tiles * stages < 2^31
-  const int n_items = warp < J ? (J - warp + W - 1) / W : 0;
+  // every warp takes a contiguous range of the CTA's (tile, stage) list: its accumulators live across
+  // the stages of a tile, and a tile costs it one update of the shared slot
+  const int per = (J + W - 1) / W;
+  const int first = warp * per;
+  const int n_items = first < J ? min(per, J - first) : 0;
   const uint32_t myring = ring0 + (uint32_t)warp * (uint32_t)(nst * G::BOX_BYTES);
   const int gshift = p.group == 32 ? 0 : (p.group == 64 ? 1 : 2);
   const int sb = bq_scale_bytes(p.stype);
   const int vec_bytes = (128 / p.group) * sb;
   const int groups_per_row = K / p.group;
   const float sym_off = -(float)(1 << (BITS - 1));
-  const int need = mats * min(W, spt1);
   bool dead = false;
 
   // (tile, matrix, stage, segment) of a cursor position
@@ -348,8 +345,7 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     }
     trow0 = (tile - p.seg[sidx].tile0) * 16;
   };
-  BQCursor icur{0, 0};                                                // next item to fetch (lane 0 uses it)
-  icur.advance(warp, spt);
+  BQCursor icur{first / spt, first % spt};                            // next item to fetch (lane 0 uses it)
   auto issue = [&](int i) {
     if (lane == 0) {
       int mat, stage, sidx, trow0;
@@ -361,7 +357,7 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
       mbar_arrive_expect_tx(bar, (uint32_t)G::BOX_BYTES);
       tma_box_2d(myring + slot * G::BOX_BYTES, m, stage * (G::STAGE_BYTES / 4), (int)y, bar);
     }
-    icur.advance(W, spt);
+    icur.advance(1, spt);
   };
 
   int issued = 0;
@@ -374,8 +370,7 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
 #pragma unroll
     for (int n = 0; n < NC; ++n) bacc[rr][n] = 0.f;
   int consumed = 0;
-  BQCursor cur{0, 0};
-  cur.advance(warp, spt);
+  BQCursor cur{first / spt, first % spt};
   for (int i = 0; i < n_items && !dead; ++i) {
     int mat, stage, sidx, trow0;
     locate(cur, mat, stage, sidx, trow0);
@@ -396,11 +391,23 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
           rs = bq_load_vec(sg.scales + off, vec_bytes);
           if (!p.symmetric) rb = bq_load_vec(sg.biases + off, vec_bytes);
         }
+        // storage -> fp32, the storage type tested once per row (not once per element)
+        float scv[4], bev[4];
+        auto convert = [&](auto conv) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            scv[q] = conv(bq_elem(rs, q >> gshift, sb));
+            bev[q] = p.symmetric ? sym_off * scv[q] : conv(bq_elem(rb, q >> gshift, sb));
+          }
+        };
+        if (p.stype == 0) convert([](uint32_t r) { return __uint_as_float(r << 16); });
+        else if (p.stype == 1) convert([](uint32_t r) { return __half2float(__ushort_as_half((unsigned short)r)); });
+        else if (p.stype == 2) convert([](uint32_t r) { return e8m0_to_f32(r); });
+        else convert([](uint32_t r) { return e4m3_to_f32(r); });
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float sc = ok ? bq_scale_bits(bq_elem(rs, q >> gshift, sb), p.stype) : 0.f;
-          sfc[rr][q] = sc;
-          const float beta = !ok ? 0.f : (p.symmetric ? sym_off * sc : bq_scale_bits(bq_elem(rb, q >> gshift, sb), p.stype));
+          sfc[rr][q] = ok ? scv[q] : 0.f;
+          const float beta = ok ? bev[q] : 0.f;
 #pragma unroll
           for (int n = 0; n < NC; ++n) bacc[rr][n] = fmaf(beta, Sq[q * 8 + n], bacc[rr][n]);
         }
@@ -446,7 +453,7 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     if (issued < n_items) { issue(issued); ++issued; }
 
     // last item of this warp for (tile, matrix): add the partial sums to the tile's slot
-    cur.advance(W, spt);
+    cur.advance(1, spt);
     if (i + 1 < n_items && cur.tl == tl && (cur.s >= spt1 ? 1 : 0) == mat) continue;
     const int rs = tl % BQ_SLOTS;
     {
@@ -481,6 +488,11 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     int old = 0;
     if (lane == 0) { __threadfence_block(); old = atomicAdd(cnt + rs, 1); }
     old = __shfl_sync(0xffffffffu, old, 0);
+    int need = 0;                                  // warps whose ranges meet this tile, per matrix
+    for (int m = 0; m < mats; ++m) {
+      const int a = tl * spt + m * spt1;
+      need += (a + spt1 - 1) / per - a / per + 1;
+    }
     if (old != need - 1) continue;
     // every contribution is in: epilogue of the tile by this warp
     __threadfence_block();

@@ -19,15 +19,6 @@ struct BlockScratch {
   unsigned u[8];
 };
 
-// hist[bin] += 1 for every lane with `pred`; the lanes of a warp that hit the same bin share one
-// atomic (the top byte of float keys takes only a few values, so unaggregated atomics serialise).
-// Every lane of the warp must call it.
-__device__ __forceinline__ void hist_add(unsigned* hist, bool pred, unsigned bin) {
-  const unsigned lane = threadIdx.x & 31u;
-  const unsigned peers = __match_any_sync(0xffffffffu, pred ? bin : (0x100u + lane));
-  if (pred && (unsigned)(__ffs((int)peers) - 1) == lane) atomicAdd(&hist[bin], (unsigned)__popc(peers));
-}
-
 __device__ __forceinline__ void block_argmax(float& v, int& id, BlockScratch& s) {
   warp_argmax(v, id);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -90,6 +81,84 @@ __device__ __forceinline__ unsigned block_sum_u(unsigned v, BlockScratch& s) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
   return v;
+}
+
+// The k-th largest of the keys key(j, out), j in [0, n) (key returns false for an absent entry;
+// 1 <= k <= number of present entries).  tau = that key, count_eq = entries equal to tau,
+// remaining = how many of those belong to the k largest.  Histogram passes of up to 8 bits over
+// keys rebased to their minimum, starting at the highest bit in which they differ: the float keys
+// of a candidate pool share their sign and most exponent bits, and unrebased the first passes would
+// put every key into one or two bins and serialise the shared-memory atomics.
+template <typename KeyFn>
+__device__ __forceinline__ void block_radix_select(long long n, KeyFn key, unsigned k, BlockScratch& S,
+                                                   uint32_t& tau, unsigned& remaining, unsigned& count_eq) {
+  const int tid = threadIdx.x, nth = blockDim.x;
+  constexpr int U = 8;                           // keys fetched per thread before any is consumed:
+  //                                                the loads of a batch overlap instead of paying the
+  //                                                memory latency once per key
+  int lo = 0x7fffffff, hi = 0x7fffffff;          // min of key and of ~key, as sign-flipped ints
+  for (long long j0 = tid; j0 < n; j0 += (long long)nth * U) {
+    uint32_t kx[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long j = j0 + (long long)u * nth;
+      kx[u] = 0u;
+      ok[u] = j < n && key(j, kx[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (ok[u]) {
+        lo = min(lo, (int)(kx[u] ^ 0x80000000u));
+        hi = min(hi, (int)(~kx[u] ^ 0x80000000u));
+      }
+  }
+  lo = block_min_int(lo, S);
+  hi = block_min_int(hi, S);
+  const uint32_t kmin = (uint32_t)lo ^ 0x80000000u, kmax = ~((uint32_t)hi ^ 0x80000000u);
+  const uint32_t range = kmax - kmin;
+  int shift = range ? 32 - __clz((int)range) : 0;
+  uint32_t prefix = 0u, mask = 0u;
+  remaining = k; count_eq = 0u;
+  do {
+    const int width = min(8, shift);
+    shift -= width;
+    const uint32_t bmask = (1u << width) - 1u;
+    for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
+    __syncthreads();
+    for (long long j0 = tid; j0 < n; j0 += (long long)nth * U) {
+      uint32_t kx[U];
+      bool ok[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * nth;
+        kx[u] = 0u;
+        ok[u] = j < n && key(j, kx[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t kn = kx[u] - kmin;
+        if (ok[u] && (kn & mask) == prefix) atomicAdd(&S.hist[(kn >> shift) & bmask], 1u);
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned c = 0;
+      int b = (int)bmask;
+      for (; b > 0; --b) {
+        if (c + S.hist[b] >= remaining) break;
+        c += S.hist[b];
+      }
+      S.u[0] = (unsigned)b; S.u[1] = remaining - c; S.u[2] = S.hist[b];
+    }
+    __syncthreads();
+    prefix |= S.u[0] << shift;
+    mask |= bmask << shift;
+    remaining = S.u[1];
+    count_eq = S.u[2];
+    __syncthreads();
+  } while (shift > 0);
+  tau = prefix + kmin;
 }
 
 }  // namespace qx

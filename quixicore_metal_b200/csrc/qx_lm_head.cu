@@ -971,35 +971,12 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
     uint32_t tau = 0u;
     int id_cut = 0x7fffffff;
     if (nvalid > (unsigned)topk) {
-      uint32_t prefix = 0u, mask = 0u;
       unsigned remaining = (unsigned)topk, count_eq = 0;
-      for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
-        __syncthreads();
-        for (long long j0 = 0; j0 < ncand; j0 += nth) {      // warp-uniform trip count
-          const long long j = j0 + tid;
-          const bool ok = j < ncand && ci(j) >= 0;
-          const uint32_t key = ok ? float_key(cv(j)) : 0u;
-          hist_add(S.hist, ok && (key & mask) == prefix, (key >> shift) & 255u);
-        }
-        __syncthreads();
-        if (tid == 0) {
-          unsigned c = 0;
-          int b = 255;
-          for (; b > 0; --b) {
-            if (c + S.hist[b] >= remaining) break;
-            c += S.hist[b];
-          }
-          S.u[0] = (unsigned)b; S.u[1] = remaining - c; S.u[2] = S.hist[b];
-        }
-        __syncthreads();
-        prefix |= S.u[0] << shift;
-        mask |= 255u << shift;
-        remaining = S.u[1];
-        count_eq = S.u[2];
-        __syncthreads();
-      }
-      tau = prefix;
+      block_radix_select(ncand, [&](long long j, uint32_t& kx) {
+        if (ci(j) < 0) return false;
+        kx = float_key(cv(j));
+        return true;
+      }, (unsigned)topk, S, tau, remaining, count_eq);
       if (count_eq > remaining) {
         // several candidates share the threshold value: keep the `remaining` smallest ids
         int cut = -1;
@@ -1038,13 +1015,24 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
     }
     float best = QX_NEG_INF;
     int bid = 0x7fffffff;
-    for (long long j = tid; j < ncand; j += nth) {
-      const int id = ci(j);
-      if (id < 0) continue;
-      const uint32_t key = float_key(cv(j));
-      if (key > tau || (key == tau && id <= id_cut)) {
-        const float p = cv(j) * invtemp + rng_gumbel(seed, (uint32_t)t, (uint32_t)id);
-        if (better(p, id, best, bid)) { best = p; bid = id; }
+    constexpr int U = 8;                           // candidates fetched per thread before any is judged
+    for (long long j0 = tid; j0 < ncand; j0 += (long long)nth * U) {
+      int idu[U];
+      float vu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * nth;
+        idu[u] = j < ncand ? ci(j) : -1;
+        vu[u] = j < ncand ? cv(j) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (idu[u] < 0) continue;
+        const uint32_t key = float_key(vu[u]);
+        if (key > tau || (key == tau && idu[u] <= id_cut)) {
+          const float p = vu[u] * invtemp + rng_gumbel(seed, (uint32_t)t, (uint32_t)idu[u]);
+          if (better(p, idu[u], best, bid)) { best = p; bid = idu[u]; }
+        }
       }
     }
     block_argmax(best, bid, S);
@@ -1061,10 +1049,25 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
   float* c_ex = cache + cache_elems;
   float mx = QX_NEG_INF;
   if (cached) {
-    for (long long j = tid; j < ncand; j += nth) {
-      const float ls = ci(j) >= 0 ? cv(j) * invtemp : QX_NEG_INF;
-      c_ls[j] = ls;
-      mx = fmaxf(mx, ls);
+    constexpr int U = 8;                           // candidates fetched per thread before any is used
+    for (long long j0 = tid; j0 < ncand; j0 += (long long)nth * U) {
+      int idu[U];
+      float vu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * nth;
+        idu[u] = j < ncand ? ci(j) : -1;
+        vu[u] = j < ncand ? cv(j) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * nth;
+        if (j < ncand) {
+          const float ls = idu[u] >= 0 ? vu[u] * invtemp : QX_NEG_INF;
+          c_ls[j] = ls;
+          mx = fmaxf(mx, ls);
+        }
+      }
     }
   } else {
     for (long long j = tid; j < ncand; j += nth)
@@ -1114,13 +1117,24 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
   }
   float best = QX_NEG_INF;
   int bid = 0x7fffffff;
-  for (long long j = tid; j < ncand; j += nth) {
-    const float ls = cached ? c_ls[j] : cv(j) * invtemp;
-    if (ls < lo) continue;
-    const int id = ci(j);
-    if (id < 0) continue;
-    const float p = ls + rng_gumbel(seed, (uint32_t)t, (uint32_t)id);
-    if (better(p, id, best, bid)) { best = p; bid = id; }
+  {
+    constexpr int U = 8;                           // ids of a batch are fetched together (selected or not)
+    for (long long j0 = tid; j0 < ncand; j0 += (long long)nth * U) {
+      int idu[U];
+      float lsu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * nth;
+        idu[u] = j < ncand ? ci(j) : -1;
+        lsu[u] = j < ncand ? (cached ? c_ls[j] : cv(j) * invtemp) : QX_NEG_INF;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (idu[u] < 0 || lsu[u] < lo) continue;
+        const float p = lsu[u] + rng_gumbel(seed, (uint32_t)t, (uint32_t)idu[u]);
+        if (better(p, idu[u], best, bid)) { best = p; bid = idu[u]; }
+      }
+    }
   }
   block_argmax(best, bid, S);
   if (tid == 0) ids[t] = (best == QX_NEG_INF || bid == 0x7fffffff) ? -1 : bid;

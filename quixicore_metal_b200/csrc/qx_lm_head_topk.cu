@@ -68,35 +68,12 @@ lmh_topk_logprob_kernel(const float* __restrict__ val, const int32_t* __restrict
   uint32_t tau = 0u;
   int id_cut = 0x7fffffff;
   if (nvalid > (unsigned)topk) {
-    uint32_t prefix = 0u, mask = 0u;
     unsigned remaining = (unsigned)topk, count_eq = 0;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-      for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
-      __syncthreads();
-      for (long long j0 = 0; j0 < n; j0 += nth) {            // warp-uniform trip count
-        const long long j = j0 + tid;
-        const bool ok = j < n && valid(j);
-        const uint32_t key = ok ? float_key(v[j]) : 0u;
-        hist_add(S.hist, ok && (key & mask) == prefix, (key >> shift) & 255u);
-      }
-      __syncthreads();
-      if (tid == 0) {
-        unsigned c = 0;
-        int b = 255;
-        for (; b > 0; --b) {
-          if (c + S.hist[b] >= remaining) break;
-          c += S.hist[b];
-        }
-        S.u[0] = (unsigned)b; S.u[1] = remaining - c; S.u[2] = S.hist[b];
-      }
-      __syncthreads();
-      prefix |= S.u[0] << shift;
-      mask |= 255u << shift;
-      remaining = S.u[1];
-      count_eq = S.u[2];
-      __syncthreads();
-    }
-    tau = prefix;
+    block_radix_select(n, [&](long long j, uint32_t& kx) {
+      if (!valid(j)) return false;
+      kx = float_key(v[j]);
+      return true;
+    }, (unsigned)topk, S, tau, remaining, count_eq);
     if (count_eq > remaining) {
       int cut = -1;
       for (unsigned q = 0; q < remaining; ++q) {

@@ -36,35 +36,11 @@ sample_logits_kernel(const T* __restrict__ logits, int32_t* __restrict__ ids, in
     uint32_t tau = 0u;
     int id_cut = 0x7fffffff;
     if (V > topk) {
-      uint32_t prefix = 0u, mask = 0u;
       unsigned remaining = (unsigned)topk, count_eq = 0;
-      for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int b = tid; b < 256; b += nth) S.hist[b] = 0u;
-        __syncthreads();
-        for (int i0 = 0; i0 < V; i0 += nth) {                // warp-uniform trip count
-          const int i = i0 + tid;
-          const bool ok = i < V;
-          const uint32_t key = ok ? float_key(to_f32<T>(lr[i])) : 0u;
-          hist_add(S.hist, ok && (key & mask) == prefix, (key >> shift) & 255u);
-        }
-        __syncthreads();
-        if (tid == 0) {
-          unsigned c = 0;
-          int b = 255;
-          for (; b > 0; --b) {
-            if (c + S.hist[b] >= remaining) break;
-            c += S.hist[b];
-          }
-          S.u[0] = (unsigned)b; S.u[1] = remaining - c; S.u[2] = S.hist[b];
-        }
-        __syncthreads();
-        prefix |= S.u[0] << shift;
-        mask |= 255u << shift;
-        remaining = S.u[1];
-        count_eq = S.u[2];
-        __syncthreads();
-      }
-      tau = prefix;
+      block_radix_select(V, [&](long long i, uint32_t& kx) {
+        kx = float_key(to_f32<T>(lr[i]));
+        return true;
+      }, (unsigned)topk, S, tau, remaining, count_eq);
       if (count_eq > remaining) {            // several logits equal the threshold: the smallest indices win
         int cut = -1;
         for (unsigned r = 0; r < remaining; ++r) {
