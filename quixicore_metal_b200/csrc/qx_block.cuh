@@ -142,14 +142,28 @@ __device__ __forceinline__ void block_radix_select(long long n, KeyFn key, unsig
       }
     }
     __syncthreads();
-    if (tid == 0) {
-      unsigned c = 0;
-      int b = (int)bmask;
-      for (; b > 0; --b) {
-        if (c + S.hist[b] >= remaining) break;
-        c += S.hist[b];
+    if (tid < 32) {
+      // the highest bin b with (entries in bins above b) + hist[b] >= remaining, found by the first
+      // warp: 8 bins per lane, a suffix sum over the lanes, then each lane tests its own bins
+      unsigned h[8], sum = 0u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { h[i] = S.hist[tid * 8 + i]; sum += h[i]; }
+      unsigned suffix = sum;                                  // entries in this lane's bins and above
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned v = __shfl_down_sync(0xffffffffu, suffix, off);
+        if (tid + off < 32) suffix += v;
       }
-      S.u[0] = (unsigned)b; S.u[1] = remaining - c; S.u[2] = S.hist[b];
+      unsigned c = suffix - sum, c_at = 0u;
+      int found = -1;
+#pragma unroll
+      for (int i = 7; i >= 0; --i) {
+        if (found < 0 && c + h[i] >= remaining) { found = tid * 8 + i; c_at = c; }
+        c += h[i];
+      }
+      const int b = max(0, (int)__reduce_max_sync(0xffffffffu, found));
+      const unsigned above = __shfl_sync(0xffffffffu, c_at, b >> 3);
+      if (tid == 0) { S.u[0] = (unsigned)b; S.u[1] = remaining - above; S.u[2] = S.hist[b]; }
     }
     __syncthreads();
     prefix |= S.u[0] << shift;

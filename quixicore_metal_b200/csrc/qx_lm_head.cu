@@ -25,6 +25,7 @@ namespace qx {
 constexpr int LMH_TILE = 256;
 constexpr int LMH_TB = 8;        // hidden rows per stage-1 CTA
 constexpr int LMH_RED_THREADS = 1024;
+constexpr int LMH_RED_COMPACT = 4096;   // candidates the stage-2 top-k search keeps in shared memory after its prefilter
 
 // Reduce one hidden row's 256 tile logits (shared memory) to the tile partials of its mode.
 // Executed by one warp.  nvalid <= 0 marks a padding tile: absent partials are written.
@@ -964,79 +965,141 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
   }
 
   if (mode == 2) {
-    // ---- exact top-k membership by radix select over the candidate keys ----
-    unsigned nvalid_l = 0;
-    for (long long j = tid; j < ncand; j += nth) nvalid_l += ci(j) >= 0 ? 1u : 0u;
-    const unsigned nvalid = block_sum_u(nvalid_l, S);
-    uint32_t tau = 0u;
-    int id_cut = 0x7fffffff;
-    if (nvalid > (unsigned)topk) {
-      unsigned remaining = (unsigned)topk, count_eq = 0;
-      block_radix_select(ncand, [&](long long j, uint32_t& kx) {
-        if (ci(j) < 0) return false;
-        kx = float_key(cv(j));
-        return true;
-      }, (unsigned)topk, S, tau, remaining, count_eq);
-      if (count_eq > remaining) {
-        // several candidates share the threshold value: keep the `remaining` smallest ids
-        int cut = -1;
-        for (unsigned r = 0; r < remaining; ++r) {
-          int mine = 0x7fffffff;
-          for (long long j = tid; j < ncand; j += nth) {
-            const int id = ci(j);
-            if (id > cut && float_key(cv(j)) == tau) mine = min(mine, id);
+    // ---- exact top-k membership by radix select over candidate keys ----
+    // `finish` selects among n candidates given by accessors and emits the result.
+    auto finish = [&](long long n, auto val, auto idf) {
+      unsigned nvalid_l = 0;
+      for (long long j = tid; j < n; j += nth) nvalid_l += idf(j) >= 0 ? 1u : 0u;
+      const unsigned nvalid = block_sum_u(nvalid_l, S);
+      uint32_t tau = 0u;
+      int id_cut = 0x7fffffff;
+      if (nvalid > (unsigned)topk) {
+        unsigned remaining = (unsigned)topk, count_eq = 0;
+        block_radix_select(n, [&](long long j, uint32_t& kx) {
+          if (idf(j) < 0) return false;
+          kx = float_key(val(j));
+          return true;
+        }, (unsigned)topk, S, tau, remaining, count_eq);
+        if (count_eq > remaining) {
+          // several candidates share the threshold value: keep the `remaining` smallest ids
+          int cut = -1;
+          for (unsigned r = 0; r < remaining; ++r) {
+            int mine = 0x7fffffff;
+            for (long long j = tid; j < n; j += nth) {
+              const int id = idf(j);
+              if (id > cut && float_key(val(j)) == tau) mine = min(mine, id);
+            }
+            cut = block_min_int(mine, S);
           }
-          cut = block_min_int(mine, S);
-        }
-        id_cut = cut;
-      }
-    }
-    if (emit_set) {
-      if (tid == 0) S.u[3] = 0u;
-      __syncthreads();
-      for (long long j = tid; j < ncand; j += nth) {
-        const int id = ci(j);
-        if (id < 0) continue;
-        const uint32_t key = float_key(cv(j));
-        if (key > tau || (key == tau && id <= id_cut)) {
-          const unsigned slot = atomicAdd(&S.u[3], 1u);
-          if (slot < (unsigned)topk) {
-            out_val[(size_t)t * topk + slot] = cv(j);
-            out_id[(size_t)t * topk + slot] = id;
-          }
+          id_cut = cut;
         }
       }
-      __syncthreads();
-      for (unsigned slot = S.u[3] + tid; slot < (unsigned)topk; slot += nth) {
-        out_val[(size_t)t * topk + slot] = QX_NEG_INF;
-        out_id[(size_t)t * topk + slot] = -1;
+      if (emit_set) {
+        if (tid == 0) S.u[3] = 0u;
+        __syncthreads();
+        for (long long j = tid; j < n; j += nth) {
+          const int id = idf(j);
+          if (id < 0) continue;
+          const uint32_t key = float_key(val(j));
+          if (key > tau || (key == tau && id <= id_cut)) {
+            const unsigned slot = atomicAdd(&S.u[3], 1u);
+            if (slot < (unsigned)topk) {
+              out_val[(size_t)t * topk + slot] = val(j);
+              out_id[(size_t)t * topk + slot] = id;
+            }
+          }
+        }
+        __syncthreads();
+        for (unsigned slot = S.u[3] + tid; slot < (unsigned)topk; slot += nth) {
+          out_val[(size_t)t * topk + slot] = QX_NEG_INF;
+          out_id[(size_t)t * topk + slot] = -1;
+        }
+        return;
       }
+      float best = QX_NEG_INF;
+      int bid = 0x7fffffff;
+      constexpr int U = 8;                           // candidates fetched per thread before any is judged
+      for (long long j0 = tid; j0 < n; j0 += (long long)nth * U) {
+        int idu[U];
+        float vu[U];
+  #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long j = j0 + (long long)u * nth;
+          idu[u] = j < n ? idf(j) : -1;
+          vu[u] = j < n ? val(j) : 0.f;
+        }
+  #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (idu[u] < 0) continue;
+          const uint32_t key = float_key(vu[u]);
+          if (key > tau || (key == tau && idu[u] <= id_cut)) {
+            const float p = vu[u] * invtemp + rng_gumbel(seed, (uint32_t)t, (uint32_t)idu[u]);
+            if (better(p, idu[u], best, bid)) { best = p; bid = idu[u]; }
+          }
+        }
+      }
+      block_argmax(best, bid, S);
+      if (tid == 0) ids[t] = bid == 0x7fffffff ? -1 : bid;
       return;
-    }
-    float best = QX_NEG_INF;
-    int bid = 0x7fffffff;
-    constexpr int U = 8;                           // candidates fetched per thread before any is judged
-    for (long long j0 = tid; j0 < ncand; j0 += (long long)nth * U) {
-      int idu[U];
-      float vu[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long j = j0 + (long long)u * nth;
-        idu[u] = j < ncand ? ci(j) : -1;
-        vu[u] = j < ncand ? cv(j) : 0.f;
+    };
+    // Candidates arrive in groups of topk (one group per vocabulary tile): the topk-th largest of the
+    // group maxima is a lower bound of the topk-th largest candidate, so only the candidates at or
+    // above it - a few hundred of tens of thousands - are copied to shared memory and searched
+    // exactly.  Without the group structure (already merged sets, few groups) or when more than
+    // LMH_RED_COMPACT candidates pass (massive ties), every candidate is searched as it lies.
+    const int ngroups = cache_elems;
+    if (ngroups >= topk && (long long)ngroups * topk == ncand) {
+      uint32_t* g_key = reinterpret_cast<uint32_t*>(cache);
+      float* l_val = cache + ngroups;
+      int* l_id = reinterpret_cast<int*>(l_val + LMH_RED_COMPACT);
+      const int lane = tid & 31, warp = tid >> 5, nwarps = nth >> 5;
+      unsigned present_l = 0;
+      for (int grp = warp; grp < ngroups; grp += nwarps) {
+        uint32_t best = 0u;
+        for (int e = lane; e < topk; e += 32) {
+          const long long j = (long long)grp * topk + e;
+          if (ci(j) >= 0) best = max(best, max(float_key(cv(j)), 1u));
+        }
+        best = __reduce_max_sync(0xffffffffu, best);
+        if (lane == 0) { g_key[grp] = best; present_l += best != 0u ? 1u : 0u; }
       }
+      __syncthreads();
+      const unsigned present = block_sum_u(present_l, S);
+      if (present >= (unsigned)topk) {
+        uint32_t tau0 = 0u;
+        unsigned rem0 = 0, ceq0 = 0;
+        block_radix_select(ngroups, [&](long long gi, uint32_t& kx) {
+          kx = g_key[gi];
+          return kx != 0u;
+        }, (unsigned)topk, S, tau0, rem0, ceq0);
+        if (tid == 0) S.u[4] = 0u;
+        __syncthreads();
+        constexpr int U = 8;
+        for (long long j0 = tid; j0 < ncand; j0 += (long long)nth * U) {
+          int idu[U];
+          float vu[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (idu[u] < 0) continue;
-        const uint32_t key = float_key(vu[u]);
-        if (key > tau || (key == tau && idu[u] <= id_cut)) {
-          const float p = vu[u] * invtemp + rng_gumbel(seed, (uint32_t)t, (uint32_t)idu[u]);
-          if (better(p, idu[u], best, bid)) { best = p; bid = idu[u]; }
+          for (int u = 0; u < U; ++u) {
+            const long long j = j0 + (long long)u * nth;
+            idu[u] = j < ncand ? ci(j) : -1;
+            vu[u] = j < ncand ? cv(j) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (idu[u] < 0 || max(float_key(vu[u]), 1u) < tau0) continue;
+            const unsigned slot = atomicAdd(&S.u[4], 1u);
+            if (slot < (unsigned)LMH_RED_COMPACT) { l_val[slot] = vu[u]; l_id[slot] = idu[u]; }
+          }
+        }
+        __syncthreads();
+        const unsigned m = S.u[4];
+        if (m <= (unsigned)LMH_RED_COMPACT) {
+          finish((long long)m, [&](long long j) { return l_val[j]; }, [&](long long j) { return l_id[j]; });
+          return;
         }
       }
     }
-    block_argmax(best, bid, S);
-    if (tid == 0) ids[t] = bid == 0x7fffffff ? -1 : bid;
+    finish(ncand, [&](long long j) { return cv(j); }, [&](long long j) { return ci(j); });
     return;
   }
 
@@ -1186,6 +1249,15 @@ void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t
   if (mode == 3 && (size_t)ncand * shards * 8 <= 200 * 1024) {
     cache_elems = (int)(ncand * shards);
     smem = (size_t)cache_elems * 8;
+  }
+  if (mode == 2 && topk > 0 && (ncand * shards) % topk == 0) {
+    const long long groups = ncand * shards / topk;             // one group of topk candidates per tile
+    if (groups >= topk && groups <= 8192) {
+      cache_elems = (int)groups;
+      smem = (size_t)groups * 4 + (size_t)LMH_RED_COMPACT * 8;
+    }
+  }
+  if (smem > 48 * 1024) {                                       // once per device
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
