@@ -320,6 +320,70 @@ def base_q_sweep(device, peak_gbs: float):
     return res
 
 
+def neighbour_sweep(device, peak_gbs: float):
+    """The operators either side of the path at decode shapes, eager calls timed with CUDA events:
+    algorithmic bytes (what each must read and write once) / time, against the measured copy rate."""
+    from quixicore_metal_b200 import tk
+    res = []
+
+    def timed(fn, iters=10):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def row(op, shape, ms, nbytes):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res.append({"op": op, "shape": shape, "ms": round(ms, 5), "algorithmic_bytes": int(nbytes),
+                    "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4)})
+
+    # LM-head forms that return log-probabilities (q8_0 head of the headline configuration)
+    V, K = V_FULL, K_HID
+    head_bytes = V * (K // 32) * 34
+    heads = [synth_q8_0(V, K, SEED + 50 + c, device) for c in range(2)]
+    h8 = torch.randn((8, K), device=device).bfloat16()
+    mask = torch.randint(-2 ** 31, 2 ** 31 - 1, (8, (V + 31) // 32), dtype=torch.int32, device=device)
+    row("lm_head_masked", "q8_0 V=128256 K=4096 T=8 topk=8", timed(lambda i: tk.lm_head_masked(
+        h8, heads[i % 2], mask, format="q8_0", topk=8)), head_bytes)
+    h16 = torch.randn((16, K), device=device).bfloat16()
+    cum = torch.zeros((4, 4), dtype=torch.float32, device=device)
+    row("lm_head_beam_advance", "q8_0 V=128256 K=4096 batches=4 beam=4", timed(lambda i: tk.lm_head_beam_advance(
+        h16, heads[i % 2], cum, 4, format="q8_0")), head_bytes)
+    cand = torch.randint(0, V, (8 * 64,), dtype=torch.int32, device=device)
+    offs = torch.arange(0, 8 * 64 + 1, 64, dtype=torch.int32, device=device)
+    row("lm_head_candidates", "q8_0 V=128256 K=4096 T=8 64 candidates per row", timed(lambda i: tk.lm_head_candidates(
+        h8, heads[i % 2], cand, offs, format="q8_0", topk=8)), 8 * 64 * (K // 32) * 34)
+    ids = torch.randint(0, V, (4096,), dtype=torch.int32, device=device)
+    row("quantized_embedding", "q8_0 table 128256 x 4096, 4096 tokens -> f16", timed(lambda i: tk.quantized_embedding_lookup(
+        heads[i % 2], ids, "q8_0")), 4096 * (K // 32) * 34 + 4096 * K * 2)
+    del heads
+    torch.cuda.empty_cache()
+    # qgemv: the reference's column-vector GEMV on the projection kernels
+    N2, K2 = 28672, 8192
+    ws = [synth_random_blocks("q8_0", N2, K2, 60 + c, device) for c in range(2)]
+    xv = torch.randn((K2, 1), device=device).half()
+    row("qgemv", "q8_0 K=8192 N=28672 f16", timed(lambda i: tk.qgemv(ws[i % 2], xv, "q8_0")), N2 * (K2 // 32) * 34)
+    del ws
+    torch.cuda.empty_cache()
+    # norm / activation -> quantiser seams
+    rows, D = 4096, 8192
+    xs = [torch.randn((rows, D), device=device).bfloat16() for _ in range(3)]
+    rs = [torch.randn((rows, D), device=device).bfloat16() for _ in range(3)]
+    w = torch.ones(D, device=device).bfloat16()
+    row("rms_norm_add_fp8 (dynamic per row)", "4096 x 8192 bf16", timed(lambda i: tk.rms_norm_add_fp8(
+        xs[i % 3], rs[i % 3], w)), rows * D * (2 + 2 + 2 + 1))
+    row("rms_norm_add_per_block (fp8, 128)", "4096 x 8192 bf16", timed(lambda i: tk.rms_norm_add_per_block(
+        xs[i % 3], rs[i % 3], w)), rows * D * (2 + 2 + 2 + 1))
+    row("silu_mul_quant_fp8", "4096 x 8192 bf16", timed(lambda i: tk.silu_mul_quant_fp8(
+        xs[i % 3], rs[i % 3])), rows * D * (2 + 2 + 1))
+    return res
+
+
 def _graph_ms(step, copies: int, reps: int = 5):
     """Per-call time of `step` replayed from a CUDA graph that holds one call per weight copy."""
     for i in range(3):
@@ -740,6 +804,7 @@ def main():
     if world == 1 and not args.no_sweep:
         line["gemv"] = gemv_sweep(device, peak_gbs)
         line["base_q"] = base_q_sweep(device, peak_gbs)
+        line["neighbours"] = neighbour_sweep(device, peak_gbs)
         # the "quant GEMV HBM GB/s" half of the metric, compact: fraction of the measured copy
         # bandwidth at batch 1 per format (K 8192 -> N 28672), graph-replayed calls
         line["roofline"]["gemv_batch1_frac_of_measured"] = {
