@@ -50,6 +50,23 @@ quantized_embedding_kernel(const uint8_t* __restrict__ table, const int32_t* __r
       decode_span32<FMT>(base, s, w);
     }
     const T* ad = add + token * columns + (size_t)s * 32;
+    if (ncol == 32 && (((uintptr_t)dst | (use_add ? (uintptr_t)ad : 0)) & 15) == 0) {
+      // whole span, 16-byte aligned: the additive term and the output move as 16-byte vectors
+      constexpr int PER = 16 / (int)sizeof(T);            // elements per vector
+#pragma unroll
+      for (int q = 0; q < 32 / PER; ++q) {
+        T a[PER], o[PER];
+        if (use_add) *reinterpret_cast<uint4*>(a) = __ldg(reinterpret_cast<const uint4*>(ad) + q);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+          float v = __fmul_rn(w[q * PER + e], scale);     // the product is rounded before the addition, as in the reference
+          if (use_add) v = __fadd_rn(v, to_f32<T>(a[e]));
+          o[e] = from_f32<T>(v);
+        }
+        reinterpret_cast<uint4*>(dst)[q] = *reinterpret_cast<const uint4*>(o);
+      }
+      continue;
+    }
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
       if (c < ncol) {

@@ -134,6 +134,37 @@ def test_ties_resolve_to_lowest_id():
     np.testing.assert_array_equal(tok, want)
 
 
+@pytest.mark.parametrize("V,k", [(40000, 50), (3000, 50), (40000, 8), (300, 8)])
+def test_topk_merge_with_massive_ties_and_few_groups(V, k):
+    """All-equal logits over many vocabulary tiles: every candidate of every tile ties at the stage-2
+    threshold (more than the merge stage keeps in shared memory after its group-maxima prefilter, so
+    it searches the candidates where they lie), and a vocabulary with fewer tiles than k (no
+    prefilter).  The top-k set is the k lowest ids, the draw is the oracle's."""
+    K = 64
+    Wq = np.zeros((V, K // 32, 34), np.uint8)
+    h = np.ones((3, K), np.float32)
+    for dtype in ("f32", "bf16"):
+        tok = _run(h, Wq, "q8_0", dtype, "topk", k=k, temperature=1.0, seed=5)
+        want = O.lm_head_sample(h, Wq, "q8_0", 2, k=k, temperature=1.0, seed=5)
+        np.testing.assert_array_equal(tok, want)
+        assert int(tok.max()) < k
+
+
+def test_topk_merge_prefilter_matches_the_oracle_on_clustered_logits():
+    """Logits in a few tight clusters (many near-equal tile maxima): the prefilter's lower bound keeps
+    every member of the true top-k."""
+    rng = np.random.default_rng(21)
+    V, K, T = 20000, 256, 5
+    W = (0.02 * rng.standard_normal((V, K))).astype(np.float32)
+    W[rng.integers(0, V, 400)] *= 3.0                  # a few hundred rows stand out
+    Wq = O.synth_pack("q8_0", W)
+    h = rounded(rng.standard_normal((T, K)), "bf16")
+    for k in (8, 50, 64):
+        tok = _run(h, Wq, "q8_0", "bf16", "topk", k=k, temperature=0.7, seed=9)
+        want, margin = O.lm_head_sample(h, Wq, "q8_0", 2, k=k, temperature=0.7, seed=9, return_detail=True)
+        check_ids(tok, want, margin, EPS, f"topk{k}/clustered")
+
+
 @pytest.mark.parametrize("T", [1, 8, 9, 64])
 def test_batch_sizes_q8_0_bf16(T):
     """Hidden-row counts of the benchmark configuration on a reduced vocabulary."""
