@@ -142,7 +142,11 @@ namespace {
 // ---- streaming tensor-core kernel ---------------------------------------------------------------
 constexpr int BQ_KC = 512;            // columns per stage
 constexpr int BQ_SLOTS = 16;          // tiles whose partial sums can be open at once in a CTA
-constexpr int BQ_MAX_WARPS = 16;
+constexpr int BQ_MAX_WARPS = 16;      // mbarrier slots reserved per CTA
+// Warps launched per code width.  Up to 4 bits: 16 warps of at most 128 registers.  Wider codes move
+// more bytes per stage, gain from deeper rings and from fetching the scales one item ahead, which
+// needs more registers: 12 warps of up to 168.
+__host__ __device__ constexpr int bq_warps(int bits) { return bits <= 4 ? 16 : 12; }
 
 template <int BITS> struct BQGeom {
   static constexpr int STAGE_BYTES = BQ_KC * BITS / 8;       // payload per row
@@ -266,7 +270,7 @@ struct BQCursor {
 // code * x), S[c,n] the sum of the 32 prepared activations, beta = bias (asymmetric) or
 // -2^(BITS-1) * scale (symmetric).
 template <int BITS, int NC>
-__global__ void __launch_bounds__((NC == 8 ? 12 : BQ_MAX_WARPS) * 32, 1)
+__global__ void __launch_bounds__(bq_warps(BITS) * 32, 1)
 base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                      const __grid_constant__ CUtensorMap map2, const BQStreamParams p) {
   using G = BQGeom<BITS>;
@@ -371,26 +375,50 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     for (int n = 0; n < NC; ++n) bacc[rr][n] = 0.f;
   int consumed = 0;
   BQCursor cur{first / spt, first % spt};
+  // raw scale / bias vectors of an item (this lane's 128 columns of rows g and g + 8), fetched one
+  // item ahead so that their latency hides behind the arithmetic of the current item
+  struct RawScales { uint2 s[2], b[2]; bool ok[2]; };
+  auto fetch_scales = [&](const BQCursor& c, RawScales& r) {
+    int mat, stage, sidx, trow0;
+    locate(c, mat, stage, sidx, trow0);
+    const BQSeg& sg = p.seg[sidx];
+    const int colb = stage * BQ_KC + t * 128;
+    const long long prow = rowoff + (mat == 1 ? p.expert_up_off : 0) + trow0 + g;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      r.ok[rr] = colb < K && trow0 + g + 8 * rr < sg.rows;
+      r.s[rr] = make_uint2(0u, 0u); r.b[rr] = make_uint2(0u, 0u);
+      if (r.ok[rr]) {
+        const size_t off = ((size_t)(prow + 8 * rr) * groups_per_row + colb / p.group) * sb;
+        r.s[rr] = bq_load_vec(sg.scales + off, vec_bytes);
+        if (!p.symmetric) r.b[rr] = bq_load_vec(sg.biases + off, vec_bytes);
+      }
+    }
+  };
+  constexpr bool AHEAD = BITS > 4;                 // one-item-ahead fetch where the register budget allows
+  RawScales raw_cur, raw_next;
+  if (AHEAD && n_items > 0) fetch_scales(cur, raw_next);
   for (int i = 0; i < n_items && !dead; ++i) {
     int mat, stage, sidx, trow0;
     locate(cur, mat, stage, sidx, trow0);
     const int tl = cur.tl;
-    const BQSeg& sg = p.seg[sidx];
-    // this lane's share of the stage's scales / biases: the 128 columns from stage * 512 + t * 128
+    if constexpr (AHEAD) {
+      raw_cur = raw_next;
+      if (i + 1 < n_items) {
+        BQCursor nx = cur;
+        nx.advance(1, spt);
+        fetch_scales(nx, raw_next);
+      }
+    } else {
+      fetch_scales(cur, raw_cur);
+    }
     float sfc[2][4];
     {
-      const int colb = stage * BQ_KC + t * 128;
-      const long long prow = rowoff + (mat == 1 ? p.expert_up_off : 0) + trow0 + g;
       const float* Sq = S + (size_t)(stage * 16 + 4 * t) * 8;          // rows past nchunks are zero
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
-        const bool ok = colb < K && trow0 + g + 8 * rr < sg.rows;
-        const size_t off = ((size_t)(prow + 8 * rr) * groups_per_row + colb / p.group) * sb;
-        uint2 rs = make_uint2(0u, 0u), rb = make_uint2(0u, 0u);
-        if (ok) {
-          rs = bq_load_vec(sg.scales + off, vec_bytes);
-          if (!p.symmetric) rb = bq_load_vec(sg.biases + off, vec_bytes);
-        }
+        const bool ok = raw_cur.ok[rr];
+        const uint2 rs = raw_cur.s[rr], rb = raw_cur.b[rr];
         // storage -> fp32, the storage type tested once per row (not once per element)
         float scv[4], bev[4];
         auto convert = [&](auto conv) {
@@ -523,8 +551,9 @@ static inline size_t bq_align256(size_t n) { return (n + 255) & ~(size_t)255; }
 static bool bq_stream_fits(int bits, int64_t K, int* warps, int* nst, size_t* smem) {
   const int pitch = BQ_KC * bits / 8 + 16, box = 16 * pitch;
   const size_t fixed = (size_t)(K / 32 + 16) * 32 + BQ_SLOTS * 256 * 4 + BQ_SLOTS * 8 + BQ_MAX_WARPS * 64 + 128;
-  const size_t budget = 168 * 1024;     // the rest of the SM's 256 KB stays L1: every warp re-reads the activations
-  for (int w : {16, 12, 8}) {
+  // the rest of the SM's 256 KB stays L1: every warp re-reads the activations
+  const size_t budget = (bits <= 4 ? 168 : 200) * 1024;
+  for (int w : {bq_warps(bits), 8}) {
     if (fixed + (size_t)w * 2 * box > budget) continue;
     int n = (int)((budget - fixed) / ((size_t)w * box));
     if (n > 6) n = 6;
@@ -564,8 +593,7 @@ static bool bq_launch_stream(cudaStream_t st, const CUtensorMap* maps, const BQS
                              int warps, size_t smem) {
   if (p.M == 1) return bq_launch_stream_nc<BITS, 1>(st, maps, p, gx, gy, warps, smem);
   if (p.M <= 4) return bq_launch_stream_nc<BITS, 4>(st, maps, p, gx, gy, warps, smem);
-  // 8 columns: wider bias-path accumulators, so at most 12 warps of up to 168 registers
-  return bq_launch_stream_nc<BITS, 8>(st, maps, p, gx, gy, warps > 12 ? 12 : warps, smem);
+  return bq_launch_stream_nc<BITS, 8>(st, maps, p, gx, gy, warps, smem);
 }
 
 // One launch over up to three weight matrices (mode 0) or a gate / up pair (mode 1).  x: (K, M) when
