@@ -761,6 +761,8 @@ def main():
                                  "gbs_per_gpu": round(shard_bytes / (ms * 1e-3) / 1e9, 1),
                                  "frac_of_measured_peak": round(shard_bytes / (ms * 1e-3) / 1e9 / peak_gbs, 4)})
 
+    exchange_kind = heads[0].exchange_used()
+    exchange_bad = sum(hd.exchange_status() for hd in heads)
     del shards, heads
     torch.cuda.empty_cache()
     stack_ok = None if args.no_stack else stack_layer_check(device, world, rank)
@@ -784,6 +786,7 @@ def main():
                 "d2h_bytes_per_step": T_ROWS * 4},
         "gpu_launches": int(launches),
         "ids_match_single_device": bool(ids_match), "ids_differing": ids_diff,
+        "exchange": exchange_kind, "exchange_timeouts": int(exchange_bad),
         "roofline": {"bound": "hbm", "kernel": "lm_head stage 1 (projection + tile partials)",
                      "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
                      "frac_of_8TBs": achieved / 8000.0, "peak_kind": peak_kind,

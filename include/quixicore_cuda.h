@@ -453,6 +453,22 @@ qx_status qx_cuda_base_qmoe(void* stream, const qx_base_q_planes* w, const qx_ba
                             int64_t K, int64_t total_rows, int swiglu, qx_dtype dtype, void* workspace,
                             size_t workspace_bytes);
 
+/* ---- exchange of per-shard candidates by peer stores (no reference counterpart) -----------------------
+ * For hosts whose ranks share a symmetric allocation (the same buffer layout on every GPU, each rank
+ * holding device pointers to every peer's copy): qx_cuda_peer_push copies `bytes` (a multiple of 16)
+ * from src (this rank's slot of its own buffer) to peer_dst[r] for every r != self with plain peer
+ * stores, then writes `step` to ((int*)peer_flags[r])[self] on every peer, data before flag
+ * (system-scope fences).  tickets: one zero-initialised device word owned by the caller.
+ * qx_cuda_peer_wait enqueues a one-warp kernel that waits until flags[r] - step >= 0 for every
+ * r != self; the wait is bounded (timeout_ms): when it runs out the kernel writes 1 to *status (a device
+ * int the caller zeroed) and returns, so a missing peer never hangs the GPU.  world <= 16.
+ * Buffers must alternate between two halves by step parity (a peer may be one step ahead, never two
+ * while every rank enqueues push(n), wait(n), consumer(n) in that order on one stream). */
+qx_status qx_cuda_peer_push(void* stream, const void* src, size_t bytes, void* const* peer_dst,
+                            void* const* peer_flags, int world, int self, int step, void* tickets);
+qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self, int step, int timeout_ms,
+                            int32_t* status);
+
 /* ---- introspection --------------------------------------------------------------------------- */
 /* block_k / block_bytes of a format name; returns 0 and leaves the outputs alone if unknown
  * (the table of kernels/matmul/decode_linear/decode_linear.cpp:25-34). */

@@ -110,6 +110,10 @@ def lib() -> C.CDLL:
     L.qx_cuda_base_qlm_head_argmax.argtypes = [vp, pp, dp, vp, vp, i64, i64, i64, i32, vp, sz]
     L.qx_cuda_base_qmoe.restype = Status
     L.qx_cuda_base_qmoe.argtypes = [vp, pp, dp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz]
+    L.qx_cuda_peer_push.restype = Status
+    L.qx_cuda_peer_push.argtypes = [vp, vp, sz, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, vp]
+    L.qx_cuda_peer_wait.restype = Status
+    L.qx_cuda_peer_wait.argtypes = [vp, vp, i32, i32, i32, i32, vp]
     L.qx_cuda_lm_head_masked_workspace_bytes.restype = sz
     L.qx_cuda_lm_head_masked_workspace_bytes.argtypes = [i64, i64, i64, i32]
     L.qx_cuda_lm_head_masked.restype = Status

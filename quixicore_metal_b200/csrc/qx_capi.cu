@@ -1075,4 +1075,31 @@ qx_status qx_cuda_base_qmoe(void* stream, const qx_base_q_planes* w, const qx_ba
                     workspace, workspace_bytes, 0, &ex);
 }
 
+// ---- peer exchange ---------------------------------------------------------------------------------------
+qx_status qx_cuda_peer_push(void* stream, const void* src, size_t bytes, void* const* peer_dst,
+                            void* const* peer_flags, int world, int self, int step, void* tickets) {
+  static const char* op = "peer_push";
+  if (!src || !peer_dst || !peer_flags || !tickets) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16 and self a rank of it");
+  if (bytes == 0 || bytes % 16 != 0) return fail(QX_INVALID_SHAPE, op, "bytes must be a positive multiple of 16");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  if (!launch_peer_push((cudaStream_t)stream, src, bytes, peer_dst, peer_flags, world, self, step, (unsigned*)tickets))
+    return fail(QX_INVALID_ARGUMENT, op, "source and peer destinations must be 16-byte aligned, flags non-null");
+  return check_launch(op);
+}
+
+qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self, int step, int timeout_ms,
+                            int32_t* status) {
+  static const char* op = "peer_wait";
+  if (!flags || !status) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16 and self a rank of it");
+  if (timeout_ms < 1 || timeout_ms > 10000) return fail(QX_INVALID_ARGUMENT, op, "timeout_ms must be 1..10000");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  // one poll = a volatile load + nanosleep(200): about 0.3 us
+  launch_peer_wait((cudaStream_t)stream, (const int*)flags, world, self, step, timeout_ms * 3000, status);
+  return check_launch(op);
+}
+
 }  // extern "C"

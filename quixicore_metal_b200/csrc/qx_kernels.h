@@ -167,6 +167,12 @@ void launch_base_q_rows(cudaStream_t st, const BaseQDesc& d, const void* codes, 
                         const void* biases, const int32_t* ids, void* out, int64_t out_rows, int64_t rows,
                         int64_t K, qx_dtype out_dtype);
 
+// Peer exchange of a gather-buffer slot by plain peer stores, and the bounded wait for the peers' flags
+// (see qx_peer.cu).
+bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
+                      int world, int self, int step, unsigned* tickets);
+void launch_peer_wait(cudaStream_t st, const int* flags, int world, int self, int step, int max_polls, int* status);
+
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);
 void launch_quantize_mxfp8_rows(cudaStream_t st, const void* x, void* blocks, int64_t rows,

@@ -12,6 +12,8 @@ the split follows its two-stage tile -> reduce structure
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -93,8 +95,9 @@ def lm_head_shard_partials(h, wq_local, bias_local, vocab_offset: int, max_tiles
 
 
 def lm_head_reduce_gathered(gathered, shards: int, T: int, max_tiles: int, mode, k=0,
-                            temperature=1.0, seed=0, top_p=0.9):
-    """Stage 2 over `shards` stage-1 buffers laid end to end (the all-gather output)."""
+                            temperature=1.0, seed=0, top_p=0.9, stride=None):
+    """Stage 2 over `shards` stage-1 buffers laid end to end (the all-gather output), or `stride`
+    elements apart (slots padded to a multiple of 16 bytes for the peer exchange)."""
     m = _mode_id(mode)
     kk = int(k) if int(k) > 0 else (32 if m >= 2 else 0)
     C, L = candidate_layout(m, kk, max_tiles)
@@ -107,7 +110,7 @@ def lm_head_reduce_gathered(gathered, shards: int, T: int, max_tiles: int, mode,
         ids = torch.empty(T, dtype=torch.int32, device=gathered.device)
         _lib.check(_lib.lib().qx_cuda_lm_head_shard_reduce(
             _stream(), base, base + 4 * T * C, (base + 8 * T * C) if L else None, _ptr(ids), shards, T,
-            max_tiles, per if shards > 1 else 0, m, max(kk, 1), float(temperature),
+            max_tiles, (int(stride) if stride else per) if shards > 1 else 0, m, max(kk, 1), float(temperature),
             int(seed) & 0xFFFFFFFF, float(top_p)))
     return ids
 
@@ -137,7 +140,7 @@ class VocabParallelLMHead:
     (begin, end) = vocab_shard_bounds(V, world)[rank].  `sample` returns the same int32 (T,)
     ids on every rank."""
 
-    def __init__(self, wq_local, V: int, fmt: str, group=None, bias_local=None):
+    def __init__(self, wq_local, V: int, fmt: str, group=None, bias_local=None, exchange: str = "auto"):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -156,6 +159,57 @@ class VocabParallelLMHead:
         self.wq, self.bias = wq_local, bias_local
         self.max_tiles = max_shard_tiles(self.V, self.world)
         self._gather = {}
+        # exchange of the per-shard candidates: "peer" = plain stores into every peer's buffer by this
+        # library's own kernels (symmetric allocation), "nccl" = all_gather_into_tensor.  "auto" takes
+        # the peer form when the symmetric allocation can be made and falls back to NCCL otherwise.
+        self.exchange = exchange if self.world > 1 else "none"
+        self._peer = {}
+        self._step = 0
+        self._status = None
+
+    # ---- peer exchange ----------------------------------------------------------------------
+    def _peer_state(self, per: int, device):
+        """Symmetric buffers for slots of `per` floats: two halves of world slots (padded to 16 bytes),
+        a flag word per rank, the push kernel's ticket word and the wait kernel's status word.  None
+        when the symmetric allocation is not available (every rank then takes the NCCL path: the
+        decision is agreed over the group so that no rank waits for a peer that went the other way)."""
+        key = (per, device)
+        if key in self._peer:
+            return self._peer[key]
+        st = None
+        ok = 1
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            stride = (per + 3) // 4 * 4
+            buf = symm.empty(2 * self.world * stride, dtype=torch.float32, device=device)
+            flags = symm.empty(64, dtype=torch.int32, device=device)
+            buf.zero_(); flags.zero_()
+            grp = self.group if self.group is not None else self.dist.group.WORLD
+            hb, hf = symm.rendezvous(buf, grp), symm.rendezvous(flags, grp)
+            st = {"stride": stride, "buf": buf, "flags": flags, "bptr": list(hb.buffer_ptrs), "fptr": list(hf.buffer_ptrs),
+                  "tickets": torch.zeros(1, dtype=torch.int32, device=device), "keep": (hb, hf)}
+        except Exception:                                   # no symmetric memory on this system / build
+            ok = 0
+        agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+        self.dist.all_reduce(agreed, op=self.dist.ReduceOp.MIN, group=self.group)   # also orders the zero-fill before any push
+        if int(agreed.item()) == 0:
+            st = None
+        if self._status is None:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._peer[key] = st
+        return st
+
+    def exchange_used(self) -> str:
+        """'peer' once a call went through the peer-store exchange, else 'nccl' (or 'none' on one GPU)."""
+        if self.world == 1:
+            return "none"
+        return "peer" if any(v is not None for v in self._peer.values()) else "nccl"
+
+    def exchange_status(self) -> int:
+        """0 while every bounded wait for the peers' flags has completed; 1 once one ran out (the ids
+        of that call are invalid).  Synchronises the stream."""
+        return 0 if self._status is None else int(self._status.item())
 
     def sample(self, h, mode="argmax", k=0, temperature=1.0, seed=0, top_p=0.9):
         m = _mode_id(mode)
@@ -163,6 +217,11 @@ class VocabParallelLMHead:
         T = h.size(0)
         C, L = candidate_layout(m, kk, self.max_tiles)
         per = T * (2 * C + L)
+        st = self._peer_state(per, h.device) if self.exchange in ("auto", "peer") else None
+        if st is not None:
+            return self._sample_peer(st, h, m, kk, T, per, temperature, seed, top_p)
+        if self.exchange == "peer":
+            raise RuntimeError("VocabParallelLMHead: exchange='peer' needs torch symmetric memory on every rank")
         key = (per, h.device)
         if key not in self._gather:
             self._gather[key] = torch.empty(self.world * per, dtype=torch.float32, device=h.device)
@@ -174,6 +233,28 @@ class VocabParallelLMHead:
             self.dist.all_gather_into_tensor(g, mine, group=self.group)
         return lm_head_reduce_gathered(g, self.world, T, self.max_tiles, m, kk, temperature, seed,
                                        top_p)
+
+    def _sample_peer(self, st, h, m, kk, T, per, temperature, seed, top_p):
+        """Stage 1 into this rank's slot, push of the slot to every peer, bounded wait for the peers'
+        flags, stage 2 - all on the current stream, no collective call."""
+        import ctypes
+        self._step += 1
+        step, stride, W = self._step, st["stride"], self.world
+        half = (step & 1) * W * stride
+        g = st["buf"][half:half + W * stride]
+        mine = g[self.rank * stride:self.rank * stride + per]
+        lm_head_shard_partials(h, self.wq, self.bias, self.begin, self.max_tiles, self.fmt, m, kk,
+                               temperature, seed, out=mine)
+        off = 4 * (half + self.rank * stride)
+        dst = (ctypes.c_void_p * W)(*[p + off for p in st["bptr"]])
+        flg = (ctypes.c_void_p * W)(*st["fptr"])
+        L = _lib.lib()
+        with torch.cuda.device(h.device):
+            _lib.check(L.qx_cuda_peer_push(_stream(), mine.data_ptr(), 4 * stride, dst, flg, W, self.rank, step,
+                                           st["tickets"].data_ptr()))
+            _lib.check(L.qx_cuda_peer_wait(_stream(), st["flags"].data_ptr(), W, self.rank, step, 5000,
+                                           self._status.data_ptr()))
+        return lm_head_reduce_gathered(g, W, T, self.max_tiles, m, kk, temperature, seed, top_p, stride=stride)
 
 
 # ----------------------------------------------------------------------------------------------
