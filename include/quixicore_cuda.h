@@ -469,6 +469,20 @@ qx_status qx_cuda_peer_push(void* stream, const void* src, size_t bytes, void* c
 qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self, int step, int timeout_ms,
                             int32_t* status);
 
+/* One call for a rank's whole step of the vocabulary-parallel LM head over the peer exchange:
+ * qx_cuda_lm_head_shard_partials_q into this rank's slot of `gather` (slots are slot_stride floats
+ * apart, slot_stride a multiple of 4 and at least T * (2C + L)), qx_cuda_peer_push of that slot to
+ * peer_gather[r] (each peer's address of the SAME slot), qx_cuda_peer_wait, then
+ * qx_cuda_lm_head_shard_reduce over the world slots.  `gather` is the half of the symmetric buffer
+ * that belongs to this step's parity. */
+qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void* wq, const float* bias_local,
+                                         int32_t* ids, float* gather, int64_t slot_stride, void* const* peer_gather,
+                                         void* const* peer_flags, const void* flags, void* tickets, int32_t* status,
+                                         int world, int self, int step, int timeout_ms, void* workspace,
+                                         size_t workspace_bytes, int64_t T, int64_t V_local, int64_t K,
+                                         int64_t vocab_offset, int64_t max_tiles, const char* format, qx_dtype dtype,
+                                         int mode, int topk, double temperature, uint32_t seed, double top_p);
+
 /* ---- introspection --------------------------------------------------------------------------- */
 /* block_k / block_bytes of a format name; returns 0 and leaves the outputs alone if unknown
  * (the table of kernels/matmul/decode_linear/decode_linear.cpp:25-34). */

@@ -1102,4 +1102,34 @@ qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self
   return check_launch(op);
 }
 
+qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void* wq, const float* bias_local,
+                                         int32_t* ids, float* gather, int64_t slot_stride, void* const* peer_gather,
+                                         void* const* peer_flags, const void* flags, void* tickets, int32_t* status,
+                                         int world, int self, int step, int timeout_ms, void* workspace,
+                                         size_t workspace_bytes, int64_t T, int64_t V_local, int64_t K,
+                                         int64_t vocab_offset, int64_t max_tiles, const char* format, qx_dtype dtype,
+                                         int mode, int topk, double temperature, uint32_t seed, double top_p) {
+  static const char* op = "quantized_lm_head_sample.sharded";
+  if (!gather || !ids) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16 and self a rank of it");
+  const int kk = mode >= 2 ? topk : 1;
+  const int64_t C = qx_cuda_lm_head_shard_candidates(mode, kk, max_tiles);
+  const int64_t Ls = mode == 3 ? max_tiles : 0;
+  const int64_t per = T * (2 * C + Ls);
+  if (slot_stride < per || slot_stride % 4 != 0) return fail(QX_INVALID_SHAPE, op, "slot_stride must be a multiple of 4 floats and hold T * (2C + L)");
+  float* mine = gather + (size_t)self * slot_stride;
+  qx_status st = qx_cuda_lm_head_shard_partials_q(stream, h, wq, bias_local, mine, (int32_t*)(mine + T * C),
+                                                  Ls ? mine + 2 * T * C : nullptr, workspace, workspace_bytes, T, V_local,
+                                                  K, vocab_offset, max_tiles, format, dtype, mode, topk, temperature, seed);
+  if (st.code != QX_OK) return st;
+  if (world > 1) {
+    st = qx_cuda_peer_push(stream, mine, (size_t)slot_stride * 4, peer_gather, peer_flags, world, self, step, tickets);
+    if (st.code != QX_OK) return st;
+    st = qx_cuda_peer_wait(stream, flags, world, self, step, timeout_ms, status);
+    if (st.code != QX_OK) return st;
+  }
+  return qx_cuda_lm_head_shard_reduce(stream, gather, (const int32_t*)(gather + T * C), Ls ? gather + 2 * T * C : nullptr, ids,
+                                      world, T, max_tiles, world > 1 ? slot_stride : 0, mode, topk, temperature, seed, top_p);
+}
+
 }  // extern "C"

@@ -168,12 +168,12 @@ class VocabParallelLMHead:
         self._status = None
 
     # ---- peer exchange ----------------------------------------------------------------------
-    def _peer_state(self, per: int, device):
+    def _peer_state(self, per: int, device, shape_key=()):
         """Symmetric buffers for slots of `per` floats: two halves of world slots (padded to 16 bytes),
         a flag word per rank, the push kernel's ticket word and the wait kernel's status word.  None
         when the symmetric allocation is not available (every rank then takes the NCCL path: the
         decision is agreed over the group so that no rank waits for a peer that went the other way)."""
-        key = (per, device)
+        key = (per, device) + tuple(shape_key)
         if key in self._peer:
             return self._peer[key]
         st = None
@@ -217,7 +217,7 @@ class VocabParallelLMHead:
         T = h.size(0)
         C, L = candidate_layout(m, kk, self.max_tiles)
         per = T * (2 * C + L)
-        st = self._peer_state(per, h.device) if self.exchange in ("auto", "peer") else None
+        st = self._peer_state(per, h.device, (T, m, kk)) if self.exchange in ("auto", "peer") else None
         if st is not None:
             return self._sample_peer(st, h, m, kk, T, per, temperature, seed, top_p)
         if self.exchange == "peer":
@@ -236,25 +236,45 @@ class VocabParallelLMHead:
 
     def _sample_peer(self, st, h, m, kk, T, per, temperature, seed, top_p):
         """Stage 1 into this rank's slot, push of the slot to every peer, bounded wait for the peers'
-        flags, stage 2 - all on the current stream, no collective call."""
+        flags, stage 2 - one library call, all on the current stream, no collective call."""
         import ctypes
         self._step += 1
         step, stride, W = self._step, st["stride"], self.world
-        half = (step & 1) * W * stride
-        g = st["buf"][half:half + W * stride]
-        mine = g[self.rank * stride:self.rank * stride + per]
-        lm_head_shard_partials(h, self.wq, self.bias, self.begin, self.max_tiles, self.fmt, m, kk,
-                               temperature, seed, out=mine)
-        off = 4 * (half + self.rank * stride)
-        dst = (ctypes.c_void_p * W)(*[p + off for p in st["bptr"]])
-        flg = (ctypes.c_void_p * W)(*st["fptr"])
-        L = _lib.lib()
+        par = step & 1
+        if "calls" not in st:                      # per buffer half: local base, peers' addresses of this rank's slot
+            st["calls"] = []
+            for half in (0, 1):
+                base = half * W * stride
+                off = 4 * (base + self.rank * stride)
+                st["calls"].append((st["buf"].data_ptr() + 4 * base,
+                                    (ctypes.c_void_p * W)(*[p + off for p in st["bptr"]])))
+            st["flg"] = (ctypes.c_void_p * W)(*st["fptr"])
+            V_local = self.wq.shape[0]
+            K = self.wq.shape[1] * _LM_QUANT_BLOCK_K[self.fmt]
+            _check_lm_head(h, self.wq, self.bias, V_local, K, self.fmt, m, kk, float(temperature), 1.0)
+            _check(self.wq.is_contiguous(), "VocabParallelLMHead: wq_local must be contiguous")
+            st["shape"] = (V_local, K)
+            st["bias"] = None
+            if self.bias is not None and self.bias.numel() > 1:
+                _check(self.bias.numel() == V_local, "lm_head_sample_q: bias must be (V,)")
+                st["bias"] = self.bias.to(torch.float32).contiguous()
+            st["ws_bytes"] = _lib.lib().qx_cuda_lm_head_shard_workspace_bytes(T, V_local, K, m, max(kk, 1))
+        _check(h.is_cuda and h.dim() == 2 and h.dtype in _DT, "lm_head_sample_q: inputs must be CUDA and h must be floating point")
+        _same_device("lm_head_sample_q", h, self.wq)
+        V_local, K = st["shape"]
+        _check(h.size(1) == K, "lm_head_sample_q: h must be (T, K)")
+        base, dst = st["calls"][par]
         with torch.cuda.device(h.device):
-            _lib.check(L.qx_cuda_peer_push(_stream(), mine.data_ptr(), 4 * stride, dst, flg, W, self.rank, step,
-                                           st["tickets"].data_ptr()))
-            _lib.check(L.qx_cuda_peer_wait(_stream(), st["flags"].data_ptr(), W, self.rank, step, 5000,
-                                           self._status.data_ptr()))
-        return lm_head_reduce_gathered(g, W, T, self.max_tiles, m, kk, temperature, seed, top_p, stride=stride)
+            hc = h.contiguous()
+            ws = _workspace(h.device, st["ws_bytes"])
+            ids = torch.empty(T, dtype=torch.int32, device=h.device)
+            _lib.check(_lib.lib().qx_cuda_lm_head_sample_sharded(
+                _stream(), hc.data_ptr(), self.wq.data_ptr(), _ptr(st["bias"]), ids.data_ptr(), base, stride, dst,
+                st["flg"], st["flags"].data_ptr(), st["tickets"].data_ptr(), self._status.data_ptr(), W, self.rank,
+                step, 5000, ws.data_ptr(), st["ws_bytes"], T, V_local, K, self.begin, self.max_tiles,
+                self.fmt.encode(), _DT[h.dtype], m, max(kk, 1), float(temperature), int(seed) & 0xFFFFFFFF,
+                float(top_p)))
+        return ids
 
 
 # ----------------------------------------------------------------------------------------------
