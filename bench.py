@@ -754,7 +754,7 @@ def main():
             for mode, kw in (("argmax", {}), ("topk", {"k": 50, "temperature": TEMP}),
                              ("topp", {"k": TOPK, "temperature": TEMP, "top_p": TOP_P})):
                 fn = lambda i: heads[i % copies].sample(hT, mode, seed=SEED + i, **kw)
-                for i in range(3):
+                for i in range(max(3, copies)):
                     fn(i)
                 ms = timed(fn, 20) / 20
                 lm_sweep.append({"T": T, "mode": mode, "ms": round(ms, 5), "tokens_per_s": round(T / (ms * 1e-3), 1),

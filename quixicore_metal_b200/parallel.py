@@ -133,12 +133,23 @@ def lm_head_merge(parts, mode, k=0, temperature=1.0, seed=0, top_p=0.9, max_tile
                                    max_tiles, m, kk, temperature, seed, top_p)
 
 
+class _PeerExchange:
+    """Per process group: symmetric buffers by shape, the running step number, the status word."""
+
+    def __init__(self):
+        self.peer = {}
+        self.step = 0
+        self.status = None
+
+
 class VocabParallelLMHead:
     """One rank's shard of a packed LM head plus the merge over a process group.
 
     wq_local holds rows [begin, end) of the full (V, K/block_k, block_bytes) matrix, where
     (begin, end) = vocab_shard_bounds(V, world)[rank].  `sample` returns the same int32 (T,)
     ids on every rank."""
+
+    _shared = {}
 
     def __init__(self, wq_local, V: int, fmt: str, group=None, bias_local=None, exchange: str = "auto"):
         import torch.distributed as dist
@@ -163,9 +174,11 @@ class VocabParallelLMHead:
         # library's own kernels (symmetric allocation), "nccl" = all_gather_into_tensor.  "auto" takes
         # the peer form when the symmetric allocation can be made and falls back to NCCL otherwise.
         self.exchange = exchange if self.world > 1 else "none"
-        self._peer = {}
-        self._step = 0
-        self._status = None
+        # Exchange buffers, the step counter and the status word belong to the process group, not to
+        # one head: every head of the group uses them in the same order on every rank, so sharing keeps
+        # the step numbers of all ranks aligned and costs one symmetric allocation per shape.
+        self._x = VocabParallelLMHead._shared.setdefault(id(group) if group is not None else 0, _PeerExchange())
+        self._head_cache = {}
 
     # ---- peer exchange ----------------------------------------------------------------------
     def _peer_state(self, per: int, device, shape_key=()):
@@ -174,8 +187,8 @@ class VocabParallelLMHead:
         when the symmetric allocation is not available (every rank then takes the NCCL path: the
         decision is agreed over the group so that no rank waits for a peer that went the other way)."""
         key = (per, device) + tuple(shape_key)
-        if key in self._peer:
-            return self._peer[key]
+        if key in self._x.peer:
+            return self._x.peer[key]
         st = None
         ok = 1
         try:
@@ -195,21 +208,21 @@ class VocabParallelLMHead:
         self.dist.all_reduce(agreed, op=self.dist.ReduceOp.MIN, group=self.group)   # also orders the zero-fill before any push
         if int(agreed.item()) == 0:
             st = None
-        if self._status is None:
-            self._status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._peer[key] = st
+        if self._x.status is None:
+            self._x.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._x.peer[key] = st
         return st
 
     def exchange_used(self) -> str:
         """'peer' once a call went through the peer-store exchange, else 'nccl' (or 'none' on one GPU)."""
         if self.world == 1:
             return "none"
-        return "peer" if any(v is not None for v in self._peer.values()) else "nccl"
+        return "peer" if any(v is not None for v in self._x.peer.values()) else "nccl"
 
     def exchange_status(self) -> int:
         """0 while every bounded wait for the peers' flags has completed; 1 once one ran out (the ids
         of that call are invalid).  Synchronises the stream."""
-        return 0 if self._status is None else int(self._status.item())
+        return 0 if self._x.status is None else int(self._x.status.item())
 
     def sample(self, h, mode="argmax", k=0, temperature=1.0, seed=0, top_p=0.9):
         m = _mode_id(mode)
@@ -238,8 +251,8 @@ class VocabParallelLMHead:
         """Stage 1 into this rank's slot, push of the slot to every peer, bounded wait for the peers'
         flags, stage 2 - one library call, all on the current stream, no collective call."""
         import ctypes
-        self._step += 1
-        step, stride, W = self._step, st["stride"], self.world
+        self._x.step += 1
+        step, stride, W = self._x.step, st["stride"], self.world
         par = step & 1
         if "calls" not in st:                      # per buffer half: local base, peers' addresses of this rank's slot
             st["calls"] = []
@@ -249,29 +262,31 @@ class VocabParallelLMHead:
                 st["calls"].append((st["buf"].data_ptr() + 4 * base,
                                     (ctypes.c_void_p * W)(*[p + off for p in st["bptr"]])))
             st["flg"] = (ctypes.c_void_p * W)(*st["fptr"])
+        hk = (T, m, kk)
+        if hk not in self._head_cache:             # this head's checked shapes, fp32 bias and workspace size
             V_local = self.wq.shape[0]
             K = self.wq.shape[1] * _LM_QUANT_BLOCK_K[self.fmt]
             _check_lm_head(h, self.wq, self.bias, V_local, K, self.fmt, m, kk, float(temperature), 1.0)
             _check(self.wq.is_contiguous(), "VocabParallelLMHead: wq_local must be contiguous")
-            st["shape"] = (V_local, K)
-            st["bias"] = None
+            bias = None
             if self.bias is not None and self.bias.numel() > 1:
                 _check(self.bias.numel() == V_local, "lm_head_sample_q: bias must be (V,)")
-                st["bias"] = self.bias.to(torch.float32).contiguous()
-            st["ws_bytes"] = _lib.lib().qx_cuda_lm_head_shard_workspace_bytes(T, V_local, K, m, max(kk, 1))
+                bias = self.bias.to(torch.float32).contiguous()
+            self._head_cache[hk] = (V_local, K, bias,
+                                    _lib.lib().qx_cuda_lm_head_shard_workspace_bytes(T, V_local, K, m, max(kk, 1)))
         _check(h.is_cuda and h.dim() == 2 and h.dtype in _DT, "lm_head_sample_q: inputs must be CUDA and h must be floating point")
         _same_device("lm_head_sample_q", h, self.wq)
-        V_local, K = st["shape"]
-        _check(h.size(1) == K, "lm_head_sample_q: h must be (T, K)")
+        V_local, K, bias32, ws_bytes = self._head_cache[hk]
+        _check(h.size(1) == K and temperature > 0.0, "lm_head_sample_q: h must be (T, K), temperature positive")
         base, dst = st["calls"][par]
         with torch.cuda.device(h.device):
             hc = h.contiguous()
-            ws = _workspace(h.device, st["ws_bytes"])
+            ws = _workspace(h.device, ws_bytes)
             ids = torch.empty(T, dtype=torch.int32, device=h.device)
             _lib.check(_lib.lib().qx_cuda_lm_head_sample_sharded(
-                _stream(), hc.data_ptr(), self.wq.data_ptr(), _ptr(st["bias"]), ids.data_ptr(), base, stride, dst,
-                st["flg"], st["flags"].data_ptr(), st["tickets"].data_ptr(), self._status.data_ptr(), W, self.rank,
-                step, 5000, ws.data_ptr(), st["ws_bytes"], T, V_local, K, self.begin, self.max_tiles,
+                _stream(), hc.data_ptr(), self.wq.data_ptr(), _ptr(bias32), ids.data_ptr(), base, stride, dst,
+                st["flg"], st["flags"].data_ptr(), st["tickets"].data_ptr(), self._x.status.data_ptr(), W, self.rank,
+                step, 5000, ws.data_ptr(), ws_bytes, T, V_local, K, self.begin, self.max_tiles,
                 self.fmt.encode(), _DT[h.dtype], m, max(kk, 1), float(temperature), int(seed) & 0xFFFFFFFF,
                 float(top_p)))
         return ids
