@@ -1,9 +1,10 @@
-"""Multi-GPU forms of the path: one process per GPU, torch.distributed (NCCL over NVLink) only
-for the small exchange steps.
+"""Multi-GPU forms of the path: one process per GPU; the LM head's small exchange step runs on
+this library's own peer-store kernels over NVLink (symmetric allocation), torch.distributed (NCCL)
+is the fallback for it and carries the projection stack's all-reduces.
 
 Vocabulary-parallel `lm_head_sample`: the vocabulary is cut at multiples of 256 so that every
 256-row tile of the reference's top-p pool lives on one GPU; each rank runs stage 1 on its rows
-(ids stay global), one all-gather moves the per-rank candidates ((val,id) per row for argmax /
+(ids stay global), one exchange moves the per-rank candidates ((val,id) per row for argmax /
 categorical, k pairs for top-k, the tile pools and tile log-sum-exps for top-p), and every rank
 runs the same stage 2.  Max-with-lowest-id, top-k-of-top-k and sum-of-exp merges are associative,
 so the ids equal the single-GPU call on the same logits.  The reference has no multi-device code;
