@@ -624,7 +624,9 @@ def stack_sweep(device, world: int, rank: int, peak_gbs: float, layers: int = 80
                     "timing": "cuda-graph replay" if ms != ms_eager else "eager", "weight_bytes_per_gpu": int(wb),
                     "gbs_per_gpu": round(wb / (ms * 1e-3) / 1e9, 1),
                     "frac_of_measured_peak": round(wb / (ms * 1e-3) / 1e9 / peak_gbs, 4),
-                    "allreduces_per_step": 2 * layers if world > 1 else 0})
+                    "allreduces_per_step": 2 * layers if world > 1 else 0,
+                    "allreduce": {"peer": "peer stores + fused residual", "nccl": "nccl all_reduce", "none": "none"}[stack.exchange_used()],
+                    "exchange_timeouts": stack.exchange_status()})
     del stack, Ls
     torch.cuda.empty_cache()
     return out

@@ -469,6 +469,23 @@ qx_status qx_cuda_peer_push(void* stream, const void* src, size_t bytes, void* c
 qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self, int step, int timeout_ms,
                             int32_t* status);
 
+/* All-reduce of fp32 partial sums (row-parallel projections) over peer stores, with the residual add
+ * and the cast fused into the consumer.  Every rank owns a symmetric buffer of 2 * world * n floats
+ * (two halves by step parity, one slot of n floats per rank), a flag word per rank, one step counter
+ * (device int, zero-initialised, local) and a ticket word.  qx_cuda_peer_sum_push: the step is
+ * *counter + 1; src (n floats, n % 4 == 0) goes into slot [step & 1][self] of every rank's buffer
+ * (peer_bufs[r] = rank r's buffer base, this rank's included), then the step is published in
+ * ((int*)peer_flags[r])[self] on every rank and stored to *counter.  qx_cuda_peer_sum_finish: waits
+ * (bounded, timeout_ms; on expiry *status = 1 and the call carries on) until every flag carries
+ * *counter, then out[i] = T(sum over r = 0..world-1 of slot[r][i] + residual[i]) - the same order on
+ * every rank, so all ranks hold identical results.  The step number is device state, not an argument:
+ * the two launches can be captured in a CUDA graph and replayed. */
+qx_status qx_cuda_peer_sum_push(void* stream, const float* src, int64_t n, void* const* peer_bufs,
+                                void* const* peer_flags, int world, int self, void* counter, void* tickets);
+qx_status qx_cuda_peer_sum_finish(void* stream, const float* buf, const void* flags, const void* counter,
+                                  const void* residual, void* out, int64_t n, int world, qx_dtype dtype,
+                                  int timeout_ms, int32_t* status);
+
 /* One call for a rank's whole step of the vocabulary-parallel LM head over the peer exchange:
  * qx_cuda_lm_head_shard_partials_q into this rank's slot of `gather` (slots are slot_stride floats
  * apart, slot_stride a multiple of 4 and at least T * (2C + L)), qx_cuda_peer_push of that slot to

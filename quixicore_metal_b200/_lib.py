@@ -116,6 +116,10 @@ def lib() -> C.CDLL:
     L.qx_cuda_lm_head_sample_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i64, C.POINTER(vp), C.POINTER(vp), vp, vp, vp,
                                                  i32, i32, i32, i32, vp, sz, i64, i64, i64, i64, i64, cs, i32,
                                                  i32, i32, f64, u32, f64]
+    L.qx_cuda_peer_sum_push.restype = Status
+    L.qx_cuda_peer_sum_push.argtypes = [vp, vp, i64, C.POINTER(vp), C.POINTER(vp), i32, i32, vp, vp]
+    L.qx_cuda_peer_sum_finish.restype = Status
+    L.qx_cuda_peer_sum_finish.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp]
     L.qx_cuda_peer_wait.restype = Status
     L.qx_cuda_peer_wait.argtypes = [vp, vp, i32, i32, i32, i32, vp]
     L.qx_cuda_lm_head_masked_workspace_bytes.restype = sz

@@ -1132,4 +1132,33 @@ qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void
                                       world, T, max_tiles, world > 1 ? slot_stride : 0, mode, topk, temperature, seed, top_p);
 }
 
+qx_status qx_cuda_peer_sum_push(void* stream, const float* src, int64_t n, void* const* peer_bufs,
+                                void* const* peer_flags, int world, int self, void* counter, void* tickets) {
+  static const char* op = "peer_sum_push";
+  if (!src || !peer_bufs || !peer_flags || !counter || !tickets) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16 and self a rank of it");
+  if (n <= 0 || n % 4 != 0) return fail(QX_INVALID_SHAPE, op, "n must be a positive multiple of 4 floats");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  if (!launch_peer_sum_push((cudaStream_t)stream, src, (size_t)n, peer_bufs, peer_flags, world, self, (int*)counter, (unsigned*)tickets))
+    return fail(QX_INVALID_ARGUMENT, op, "source and buffers must be 16-byte aligned, flags non-null");
+  return check_launch(op);
+}
+
+qx_status qx_cuda_peer_sum_finish(void* stream, const float* buf, const void* flags, const void* counter,
+                                  const void* residual, void* out, int64_t n, int world, qx_dtype dtype,
+                                  int timeout_ms, int32_t* status) {
+  static const char* op = "peer_sum_finish";
+  if (!buf || !flags || !counter || !residual || !out || !status) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16");
+  if (n <= 0) return fail(QX_INVALID_SHAPE, op, "n must be positive");
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "residual / out must be fp32, fp16 or bf16");
+  if (timeout_ms < 1 || timeout_ms > 10000) return fail(QX_INVALID_ARGUMENT, op, "timeout_ms must be 1..10000");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  launch_peer_sum_finish((cudaStream_t)stream, buf, (const int*)flags, (const int*)counter, residual, out, (size_t)n, world,
+                         dtype, timeout_ms * 4000, status);
+  return check_launch(op);
+}
+
 }  // extern "C"

@@ -172,6 +172,11 @@ void launch_base_q_rows(cudaStream_t st, const BaseQDesc& d, const void* codes, 
 bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
                       int world, int self, int step, unsigned* tickets);
 void launch_peer_wait(cudaStream_t st, const int* flags, int world, int self, int step, int max_polls, int* status);
+// All-reduce of fp32 partials over peer stores with the residual add and the cast fused into the consumer.
+bool launch_peer_sum_push(cudaStream_t st, const float* src, size_t n, void* const* peer_bufs, void* const* peer_flags,
+                          int world, int self, int* counter, unsigned* tickets);
+void launch_peer_sum_finish(cudaStream_t st, const float* buf, const int* flags, const int* counter, const void* residual,
+                            void* out, size_t n, int world, qx_dtype dtype, int max_polls, int* status);
 
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);

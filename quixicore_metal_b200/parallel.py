@@ -311,12 +311,18 @@ class TPDecodeStack:
     Partial sums cross the ranks in fp32 (not in the 16-bit I/O type), so the only difference from
     the single-device result is the order of the K summation."""
 
-    def __init__(self, layers, fmt: str, head_dim: int = 128, group=None, tensor_parallel: bool = True):
+    def __init__(self, layers, fmt: str, head_dim: int = 128, group=None, tensor_parallel: bool = True,
+                 exchange: str = "auto"):
         import torch.distributed as dist
         self.dist, self.group = dist, group
         # tensor_parallel=False: `layers` are whole (unsharded) tensors and no collective runs, even
         # inside an initialised process group (the single-device result the sharded one is checked against)
         self.world = dist.get_world_size(group) if (tensor_parallel and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if (tensor_parallel and dist.is_initialized()) else 0
+        # "auto": row-parallel partials are summed over peer stores by this library's kernels when a
+        # symmetric allocation can be made, else by NCCL all-reduce; "nccl" forces the latter
+        self.exchange = exchange
+        self._sum = {}
         self.layers, self.fmt, self.head_dim = layers, fmt, head_dim
         bk = _LM_QUANT_BLOCK_K[fmt]
         l0 = layers[0]
@@ -330,6 +336,70 @@ class TPDecodeStack:
             self.dist.all_reduce(t, group=self.group)
         return t
 
+    # ---- sum of the row-parallel partials over peer stores, residual add and cast fused ----------
+    def _peer_sum_state(self, n: int, device):
+        """Symmetric buffer (two halves of world slots of n floats), flags, step counter, tickets and
+        status for partials of n floats; None when symmetric memory is unavailable (agreed over the
+        group, every rank then uses the NCCL all-reduce)."""
+        key = (n, device)
+        if key in self._sum:
+            return self._sum[key]
+        st, ok = None, 1
+        try:
+            import ctypes
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty(2 * self.world * n, dtype=torch.float32, device=device)
+            flags = symm.empty(64, dtype=torch.int32, device=device)
+            buf.zero_(); flags.zero_()
+            grp = self.group if self.group is not None else self.dist.group.WORLD
+            hb, hf = symm.rendezvous(buf, grp), symm.rendezvous(flags, grp)
+            W = self.world
+            st = {"buf": buf, "flags": flags, "keep": (hb, hf),
+                  "bptr": (ctypes.c_void_p * W)(*list(hb.buffer_ptrs)), "fptr": (ctypes.c_void_p * W)(*list(hf.buffer_ptrs)),
+                  "counter": torch.zeros(1, dtype=torch.int32, device=device),
+                  "tickets": torch.zeros(1, dtype=torch.int32, device=device),
+                  "status": torch.zeros(1, dtype=torch.int32, device=device)}
+        except Exception:
+            ok = 0
+        agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+        self.dist.all_reduce(agreed, op=self.dist.ReduceOp.MIN, group=self.group)
+        if int(agreed.item()) == 0:
+            st = None
+        self._sum[key] = st
+        return st
+
+    def _sum_add_residual(self, part, x):
+        """x + sum over the ranks of `part` (fp32 partial of this rank), in x's dtype."""
+        if self.world == 1:
+            return (part + x.float()).to(x.dtype)
+        n = part.numel()
+        # small partials (decode batches) are latency-bound: peer stores; large ones keep NCCL's pipelined rings
+        small = n <= 65536 or self.exchange == "peer"
+        st = self._peer_sum_state(n, part.device) if (self.exchange in ("auto", "peer") and n % 4 == 0 and small) else None
+        if st is None:
+            return (self._all_reduce(part) + x.float()).to(x.dtype)
+        from . import _lib
+        L = _lib.lib()
+        pc, xc = part.contiguous(), x.contiguous()
+        out = torch.empty_like(xc)
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(L.qx_cuda_peer_sum_push(stream, pc.data_ptr(), n, st["bptr"], st["fptr"], self.world, self.rank,
+                                           st["counter"].data_ptr(), st["tickets"].data_ptr()))
+        _lib.check(L.qx_cuda_peer_sum_finish(stream, st["buf"].data_ptr(), st["flags"].data_ptr(), st["counter"].data_ptr(),
+                                             xc.data_ptr(), out.data_ptr(), n, self.world, _DT[x.dtype], 5000,
+                                             st["status"].data_ptr()))
+        return out
+
+    def exchange_used(self) -> str:
+        if self.world == 1:
+            return "none"
+        return "peer" if any(v is not None for v in self._sum.values()) else "nccl"
+
+    def exchange_status(self) -> int:
+        """Number of shapes whose bounded wait for the peers ran out (their results are invalid)."""
+        return sum(int(v["status"].item()) for v in self._sum.values() if v is not None)
+
     def layer(self, x, L, trace=None):
         """One block.  `trace`, if given, is a dict that receives the residual stream after the
         O projection ("h"), for tests that compare each half of the block on its own inputs."""
@@ -340,13 +410,11 @@ class TPDecodeStack:
         n_kv = self.kv_local // hd
         v = qkv[:, self.q_local + self.kv_local:].reshape(-1, n_kv, 1, hd)
         attn = v.expand(-1, n_kv, self.q_local // self.kv_local, hd).reshape(-1, self.q_local).contiguous()
-        o = self._all_reduce(tk_torch.decode_linear_partial(attn, L["o"], self.fmt))
-        x = (o + x.float()).to(x.dtype)
+        x = self._sum_add_residual(tk_torch.decode_linear_partial(attn, L["o"], self.fmt), x)
         if trace is not None:
             trace["h"] = x
         mid = tk.decode_swiglu(x, L["gate"], L["up"], format=self.fmt)
-        d = self._all_reduce(tk_torch.decode_linear_partial(mid, L["down"], self.fmt))
-        return (d + x.float()).to(x.dtype)
+        return self._sum_add_residual(tk_torch.decode_linear_partial(mid, L["down"], self.fmt), x)
 
     def forward(self, x):
         for L in self.layers:

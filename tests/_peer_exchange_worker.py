@@ -37,6 +37,34 @@ def main():
         a = peer.sample(h, mode, seed=step, **kw)
         c = nccl.sample(h, mode, seed=step, **kw)
         bad += int((a != c).sum())
+    # tensor-parallel projection stack: partial sums over peer stores against NCCL all-reduce, eager and
+    # replayed from a CUDA graph (the step number of the exchange is device state)
+    hidden, q, kv, inter, fmt = 1024, 2048, 1024, 4096, "nvfp4"
+    rs = np.random.default_rng(11)
+    mk = lambda n, k: torch.from_numpy(O.synth_pack(fmt, (0.02 * rs.standard_normal((n, k))).astype(np.float32))).to(dev)
+    full = {"qkv": mk(q + 2 * kv, hidden), "o": mk(hidden, q), "gate": mk(inter, hidden), "up": mk(inter, hidden),
+            "down": mk(hidden, inter)}
+    mine = parallel.TPDecodeStack.shard_layer(full, rank, world, fmt, q, kv)
+    sp = parallel.TPDecodeStack([mine, mine], fmt, exchange="auto")
+    sn = parallel.TPDecodeStack([mine, mine], fmt, exchange="nccl")
+    stack_bad = 0
+    for M in (1, 5):
+        x = (torch.randn((M, hidden), generator=g) * 0.05).bfloat16().to(dev)
+        a, c = sp.forward(x).float(), sn.forward(x).float()
+        stack_bad += int(((a - c).abs() > c.abs() * 2.0 ** -6 + 1e-3 * c.abs().max()).sum())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            sp.forward(x)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y = sp.forward(x)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        stack_bad += int(((y.float() - c).abs() > c.abs() * 2.0 ** -6 + 1e-3 * c.abs().max()).sum())
+    bad += stack_bad + sp.exchange_status()
     used, status = peer.exchange_used(), peer.exchange_status()
     t = torch.tensor([bad, status, 1 if used == "peer" else 0], device=dev)
     dist.all_reduce(t)

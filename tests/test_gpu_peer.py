@@ -97,3 +97,48 @@ def test_two_ranks_peer_exchange_gives_the_nccl_ids():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "peer exchange ok" in out.stdout
+
+
+def test_sum_push_and_finish_on_one_gpu_as_three_ranks():
+    """Three 'ranks' whose buffers live on this GPU, run one after the other on one stream: after
+    all three have pushed step s, each finish returns residual + the sum of the three partials
+    (bit-identical on every rank), for consecutive steps (both buffer halves).  A finish whose peers
+    never pushed gives up after its limit and reports it."""
+    _l, L = _lib()
+    W, n = 3, 2048
+    bufs = [torch.zeros(2 * W * n, device="cuda") for _ in range(W)]
+    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(W)]
+    counters = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(W)]
+    tickets = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for step in range(1, 4):
+        parts = [torch.randn(n, device="cuda") for _ in range(W)]
+        res = torch.randn(n, device="cuda").bfloat16()
+        for r in range(W):
+            rc = L.qx_cuda_peer_sum_push(st, parts[r].data_ptr(), n, _ptrs(bufs), _ptrs(flags), W, r,
+                                         counters[r].data_ptr(), tickets.data_ptr())
+            assert rc.code == 0, rc.detail
+        outs = []
+        for r in range(W):
+            out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+            rc = L.qx_cuda_peer_sum_finish(st, bufs[r].data_ptr(), flags[r].data_ptr(), counters[r].data_ptr(),
+                                           res.data_ptr(), out.data_ptr(), n, W, _l.DTYPE_BF16, 1000, status.data_ptr())
+            assert rc.code == 0, rc.detail
+            outs.append(out)
+        torch.cuda.synchronize()
+        want = (((parts[0] + parts[1]) + parts[2]) + res.float()).bfloat16()
+        for r in range(W):
+            assert torch.equal(outs[r], want), (step, r)
+            assert int(counters[r]) == step and flags[r][:W].tolist() == [step] * W
+        assert int(status) == 0
+    # rank 0 pushes step 4 alone: its finish waits for ranks 1 and 2, which never come
+    rc = L.qx_cuda_peer_sum_push(st, parts[0].data_ptr(), n, _ptrs([bufs[0]] * W), _ptrs([flags[0]] + [torch.zeros(64, dtype=torch.int32, device="cuda")] * 2), W, 0,
+                                 counters[0].data_ptr(), tickets.data_ptr())
+    assert rc.code == 0
+    t0 = time.time()
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    L.qx_cuda_peer_sum_finish(st, bufs[0].data_ptr(), flags[0].data_ptr(), counters[0].data_ptr(), res.data_ptr(),
+                              out.data_ptr(), n, W, _l.DTYPE_BF16, 50, status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status) == 1 and time.time() - t0 < 5.0
