@@ -377,6 +377,7 @@ class TPDecodeStack:
         # small partials (decode batches) are latency-bound: peer stores; large ones keep NCCL's pipelined rings
         small = n <= 65536 or self.exchange == "peer"
         st = self._peer_sum_state(n, part.device) if (self.exchange in ("auto", "peer") and n % 4 == 0 and small) else None
+        self._last = "nccl" if st is None else "peer"
         if st is None:
             return (self._all_reduce(part) + x.float()).to(x.dtype)
         from . import _lib
@@ -392,9 +393,8 @@ class TPDecodeStack:
         return out
 
     def exchange_used(self) -> str:
-        if self.world == 1:
-            return "none"
-        return "peer" if any(v is not None for v in self._sum.values()) else "nccl"
+        """How the most recent partial sum crossed the ranks: 'peer', 'nccl', or 'none' on one GPU."""
+        return "none" if self.world == 1 else getattr(self, "_last", "nccl")
 
     def exchange_status(self) -> int:
         """Number of shapes whose bounded wait for the peers ran out (their results are invalid)."""
