@@ -7,6 +7,8 @@ import re
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the reference checkout, when it sits beside this repository (absent on a GPU machine: those checks skip)
+_REF_ROOT = os.environ.get("QX_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 @pytest.fixture(scope="module")
@@ -205,7 +207,7 @@ def test_header_layout_static_asserts(tmp_path):
         pytest.skip("no g++")
     src = tmp_path / "layout.cpp"
     src.write_text(_LAYOUT_CHECK)
-    ref_inc = "/root/reference/include"
+    ref_inc = os.path.join(_REF_ROOT, "include")
     cmd = [gxx, "-std=c++17", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(src)]
     if os.path.exists(os.path.join(ref_inc, "quixicore", "contract", "kernel_abi.hpp")):
         cmd += ["-DWITH_REFERENCE", "-I", ref_inc]
@@ -221,7 +223,7 @@ def test_header_layout_static_asserts(tmp_path):
 
 
 # ---- the Python binding against the reference module it replaces --------------------------------
-_REF_TK_TORCH = "/root/reference/bindings/pytorch_mps/tk_torch/__init__.py"
+_REF_TK_TORCH = os.path.join(_REF_ROOT, "bindings", "pytorch_mps", "tk_torch", "__init__.py")
 # (name, positional parameters with defaults) of bindings/pytorch_mps/tk_torch/__init__.py:932-958,
 # :1620-1637, :1738-1745, kept here so the check also runs where the reference checkout is absent
 _BQ_TAIL = ["bits", "group_size", "scale_dtype='bf16'", "symmetric=False", "layout='metal'"]
@@ -303,7 +305,7 @@ def test_install_routes_the_reference_router_here():
         q.install_as_tk_torch()
         import tk_torch
         assert tk_torch is q.tk_torch
-        ref_py = "/root/reference/bindings/python"
+        ref_py = os.path.join(_REF_ROOT, "bindings", "python")
         if os.path.exists(os.path.join(ref_py, "tk", "__init__.py")):
             sys.path.insert(0, ref_py)
             try:
