@@ -469,32 +469,58 @@ qx_status qx_cuda_peer_push(void* stream, const void* src, size_t bytes, void* c
 qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self, int step, int timeout_ms,
                             int32_t* status);
 
-/* All-reduce of fp32 partial sums (row-parallel projections) over peer stores, with the residual add
- * and the cast fused into the consumer.  Every rank owns a symmetric buffer of 2 * world * n floats
- * (two halves by step parity, one slot of n floats per rank), a flag word per rank, one step counter
- * (device int, zero-initialised, local) and a ticket word.  qx_cuda_peer_sum_push: the step is
- * *counter + 1; src (n floats, n % 4 == 0) goes into slot [step & 1][self] of every rank's buffer
- * (peer_bufs[r] = rank r's buffer base, this rank's included), then the step is published in
- * ((int*)peer_flags[r])[self] on every rank and stored to *counter.  qx_cuda_peer_sum_finish: waits
- * (bounded, timeout_ms; on expiry *status = 1 and the call carries on) until every flag carries
- * *counter, then out[i] = T(sum over r = 0..world-1 of slot[r][i] + residual[i]) - the same order on
- * every rank, so all ranks hold identical results.  The step number is device state, not an argument:
- * the two launches can be captured in a CUDA graph and replayed. */
-qx_status qx_cuda_peer_sum_push(void* stream, const float* src, int64_t n, void* const* peer_bufs,
-                                void* const* peer_flags, int world, int self, void* counter, void* tickets);
-qx_status qx_cuda_peer_sum_finish(void* stream, const float* buf, const void* flags, const void* counter,
-                                  const void* residual, void* out, int64_t n, int world, qx_dtype dtype,
-                                  int timeout_ms, int32_t* status);
+/* All-reduce of fp32 partial sums (row-parallel projections) over peer stores with the residual add and
+ * the cast fused, as ONE launch, flag-in-data (what the tensor-parallel projection stack uses for
+ * decode-sized partials).  Every rank owns a zero-initialised symmetric buffer of 2 * world * (n / 2)
+ * 16-byte words = 16 * world * n bytes (two halves by step parity, one slot per rank); a word is
+ * {x, step, y, step}: two floats, each beside the step number, so that the receiver polls the data itself
+ * and nothing else (no flag array, no fence) crosses NVLink.  The step is *counter + 1 (device int,
+ * zero-initialised, local; stored back by the last CTA: replayable from a CUDA graph).  A thread stores
+ * its elements of src (n floats, n even) into slot [step & 1][self] of every rank's buffer (peer_bufs[r] =
+ * rank r's buffer base, this rank's included), reads slot [step & 1][r] of its own buffer for r = 0 ..
+ * world - 1 in that order - bounded polls, about timeout_ms; on expiry *status = 1, the call carries on
+ * with invalid sums and later calls on that status word do not wait - and writes
+ * out[i] = T(sum over r + residual[i]): the same order on every rank, so all ranks hold identical
+ * results.  n must be the same on every rank.  Replaces (Python) `dist.all_reduce(partial); out = (partial +
+ * residual).to(dtype)` after the row-parallel projections of a decoder block.
+ * qx_cuda_peer_allreduce_local runs all `world` ranks, whose buffers all live on the current device, as
+ * one cooperative launch (arrays of `world` pointers per argument): ranks that wait for one another
+ * cannot be separate launches on one GPU. */
+qx_status qx_cuda_peer_allreduce(void* stream, const float* src, const void* residual, void* out, int64_t n,
+                                 void* const* peer_bufs, int world, int self, void* counter, void* tickets,
+                                 int32_t* status, qx_dtype dtype, int timeout_ms);
+qx_status qx_cuda_peer_allreduce_local(void* stream, const float* const* src, const void* const* residual,
+                                       void* const* out, int64_t n, void* const* peer_bufs, int world,
+                                       void* const* counter, void* const* tickets, int32_t* const* status,
+                                       qx_dtype dtype, int timeout_ms);
+
+/* All-gather of small slots as ONE launch, flag-in-data: the latency form of qx_cuda_peer_push +
+ * qx_cuda_peer_wait for slots of a few KB.  `gather` is LOCAL memory of world slots of slot_floats floats
+ * (slot_floats even) whose slot [self] is filled; peer_words[r] = base of rank r's zero-initialised
+ * symmetric word buffer of 2 * world * (slot_floats / 2) 16-byte words {x, step, y, step} (two halves by
+ * step parity, one slot per sending rank).  A thread sends its pair of floats to every peer's word buffer,
+ * then polls its own word buffer for the same pair of every peer (bounded, about timeout_ms; on expiry
+ * *status = 1, the call carries on and later calls on that status word do not wait) and writes it into
+ * slot [r] of `gather`.  `step` must grow by one per exchange on every rank.  Replaces (Python)
+ * `dist.all_gather_into_tensor`.  qx_cuda_peer_gather_local: all `world` ranks on the current device as one
+ * cooperative launch (gather / status: arrays of `world` pointers). */
+qx_status qx_cuda_peer_gather(void* stream, float* gather, int64_t slot_floats, void* const* peer_words, int world,
+                              int self, int step, int timeout_ms, int32_t* status);
+qx_status qx_cuda_peer_gather_local(void* stream, float* const* gather, int64_t slot_floats, void* const* peer_words,
+                                    int world, int step, int timeout_ms, int32_t* const* status);
 
 /* One call for a rank's whole step of the vocabulary-parallel LM head over the peer exchange:
  * qx_cuda_lm_head_shard_partials_q into this rank's slot of `gather` (slots are slot_stride floats
- * apart, slot_stride a multiple of 4 and at least T * (2C + L)), qx_cuda_peer_push of that slot to
- * peer_gather[r] (each peer's address of the SAME slot), qx_cuda_peer_wait, then
- * qx_cuda_lm_head_shard_reduce over the world slots.  `gather` is the half of the symmetric buffer
- * that belongs to this step's parity. */
+ * apart, slot_stride a multiple of 4 and at least T * (2C + L)), then the exchange, then
+ * qx_cuda_lm_head_shard_reduce over the world slots.  Exchange with peer_words == NULL:
+ * qx_cuda_peer_push of the slot to peer_gather[r] (each peer's address of the SAME slot) and
+ * qx_cuda_peer_wait; `gather` is then the half of the symmetric buffer that belongs to this step's
+ * parity.  With peer_words: qx_cuda_peer_gather (small slots; peer_gather / peer_flags / flags /
+ * tickets are not used). */
 qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void* wq, const float* bias_local,
                                          int32_t* ids, float* gather, int64_t slot_stride, void* const* peer_gather,
-                                         void* const* peer_flags, const void* flags, void* tickets, int32_t* status,
+                                         void* const* peer_flags, const void* flags, void* tickets,
+                                         void* const* peer_words, int32_t* status,
                                          int world, int self, int step, int timeout_ms, void* workspace,
                                          size_t workspace_bytes, int64_t T, int64_t V_local, int64_t K,
                                          int64_t vocab_offset, int64_t max_tiles, const char* format, qx_dtype dtype,

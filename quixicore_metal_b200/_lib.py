@@ -113,13 +113,19 @@ def lib() -> C.CDLL:
     L.qx_cuda_peer_push.restype = Status
     L.qx_cuda_peer_push.argtypes = [vp, vp, sz, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, vp]
     L.qx_cuda_lm_head_sample_sharded.restype = Status
-    L.qx_cuda_lm_head_sample_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i64, C.POINTER(vp), C.POINTER(vp), vp, vp, vp,
+    L.qx_cuda_lm_head_sample_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i64, C.POINTER(vp), C.POINTER(vp), vp, vp,
+                                                 C.POINTER(vp), vp,
                                                  i32, i32, i32, i32, vp, sz, i64, i64, i64, i64, i64, cs, i32,
                                                  i32, i32, f64, u32, f64]
-    L.qx_cuda_peer_sum_push.restype = Status
-    L.qx_cuda_peer_sum_push.argtypes = [vp, vp, i64, C.POINTER(vp), C.POINTER(vp), i32, i32, vp, vp]
-    L.qx_cuda_peer_sum_finish.restype = Status
-    L.qx_cuda_peer_sum_finish.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp]
+    L.qx_cuda_peer_gather.restype = Status
+    L.qx_cuda_peer_gather.argtypes = [vp, vp, i64, C.POINTER(vp), i32, i32, i32, i32, vp]
+    L.qx_cuda_peer_gather_local.restype = Status
+    L.qx_cuda_peer_gather_local.argtypes = [vp, C.POINTER(vp), i64, C.POINTER(vp), i32, i32, i32, C.POINTER(vp)]
+    L.qx_cuda_peer_allreduce.restype = Status
+    L.qx_cuda_peer_allreduce.argtypes = [vp, vp, vp, vp, i64, C.POINTER(vp), i32, i32, vp, vp, vp, i32, i32]
+    L.qx_cuda_peer_allreduce_local.restype = Status
+    L.qx_cuda_peer_allreduce_local.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), i64, C.POINTER(vp), i32,
+                                               C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), i32, i32]
     L.qx_cuda_peer_wait.restype = Status
     L.qx_cuda_peer_wait.argtypes = [vp, vp, i32, i32, i32, i32, vp]
     L.qx_cuda_lm_head_masked_workspace_bytes.restype = sz

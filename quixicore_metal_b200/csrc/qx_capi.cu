@@ -1102,9 +1102,40 @@ qx_status qx_cuda_peer_wait(void* stream, const void* flags, int world, int self
   return check_launch(op);
 }
 
+qx_status qx_cuda_peer_gather(void* stream, float* gather, int64_t slot_floats, void* const* peer_words, int world,
+                              int self, int step, int timeout_ms, int32_t* status) {
+  static const char* op = "peer_gather";
+  if (!gather || !peer_words || !status) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16, self in [0, world)");
+  if (slot_floats <= 0 || slot_floats % 2 != 0) return fail(QX_INVALID_SHAPE, op, "slot_floats must be a positive even number");
+  if (timeout_ms < 1 || timeout_ms > 10000) return fail(QX_INVALID_ARGUMENT, op, "timeout_ms must be 1..10000");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  int* sp = status;
+  if (!launch_peer_gather((cudaStream_t)stream, &gather, (size_t)slot_floats, peer_words, world, self, 1, step, &sp, timeout_ms * 1000))
+    return fail(QX_INVALID_ARGUMENT, op, "gather must be 8-byte aligned, every word buffer 16-byte aligned");
+  return check_launch(op);
+}
+
+qx_status qx_cuda_peer_gather_local(void* stream, float* const* gather, int64_t slot_floats, void* const* peer_words,
+                                    int world, int step, int timeout_ms, int32_t* const* status) {
+  static const char* op = "peer_gather_local";
+  if (!gather || !peer_words || !status) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16");
+  if (slot_floats <= 0 || slot_floats % 2 != 0) return fail(QX_INVALID_SHAPE, op, "slot_floats must be a positive even number");
+  if (timeout_ms < 1 || timeout_ms > 10000) return fail(QX_INVALID_ARGUMENT, op, "timeout_ms must be 1..10000");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  if (!launch_peer_gather((cudaStream_t)stream, gather, (size_t)slot_floats, peer_words, world, 0, world, step,
+                          (int* const*)status, timeout_ms * 1000))
+    return fail(QX_INVALID_ARGUMENT, op, "null / misaligned buffers, or the cooperative launch was refused");
+  return check_launch(op);
+}
+
 qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void* wq, const float* bias_local,
                                          int32_t* ids, float* gather, int64_t slot_stride, void* const* peer_gather,
-                                         void* const* peer_flags, const void* flags, void* tickets, int32_t* status,
+                                         void* const* peer_flags, const void* flags, void* tickets,
+                                         void* const* peer_words, int32_t* status,
                                          int world, int self, int step, int timeout_ms, void* workspace,
                                          size_t workspace_bytes, int64_t T, int64_t V_local, int64_t K,
                                          int64_t vocab_offset, int64_t max_tiles, const char* format, qx_dtype dtype,
@@ -1122,7 +1153,10 @@ qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void
                                                   Ls ? mine + 2 * T * C : nullptr, workspace, workspace_bytes, T, V_local,
                                                   K, vocab_offset, max_tiles, format, dtype, mode, topk, temperature, seed);
   if (st.code != QX_OK) return st;
-  if (world > 1) {
+  if (world > 1 && peer_words) {
+    st = qx_cuda_peer_gather(stream, gather, slot_stride, peer_words, world, self, step, timeout_ms, status);
+    if (st.code != QX_OK) return st;
+  } else if (world > 1) {
     st = qx_cuda_peer_push(stream, mine, (size_t)slot_stride * 4, peer_gather, peer_flags, world, self, step, tickets);
     if (st.code != QX_OK) return st;
     st = qx_cuda_peer_wait(stream, flags, world, self, step, timeout_ms, status);
@@ -1132,32 +1166,40 @@ qx_status qx_cuda_lm_head_sample_sharded(void* stream, const void* h, const void
                                       world, T, max_tiles, world > 1 ? slot_stride : 0, mode, topk, temperature, seed, top_p);
 }
 
-qx_status qx_cuda_peer_sum_push(void* stream, const float* src, int64_t n, void* const* peer_bufs,
-                                void* const* peer_flags, int world, int self, void* counter, void* tickets) {
-  static const char* op = "peer_sum_push";
-  if (!src || !peer_bufs || !peer_flags || !counter || !tickets) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
-  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16 and self a rank of it");
-  if (n <= 0 || n % 4 != 0) return fail(QX_INVALID_SHAPE, op, "n must be a positive multiple of 4 floats");
-  qx_status st;
-  if (!device_ready(op, &st)) return st;
-  if (!launch_peer_sum_push((cudaStream_t)stream, src, (size_t)n, peer_bufs, peer_flags, world, self, (int*)counter, (unsigned*)tickets))
-    return fail(QX_INVALID_ARGUMENT, op, "source and buffers must be 16-byte aligned, flags non-null");
-  return check_launch(op);
-}
-
-qx_status qx_cuda_peer_sum_finish(void* stream, const float* buf, const void* flags, const void* counter,
-                                  const void* residual, void* out, int64_t n, int world, qx_dtype dtype,
-                                  int timeout_ms, int32_t* status) {
-  static const char* op = "peer_sum_finish";
-  if (!buf || !flags || !counter || !residual || !out || !status) return fail(QX_INVALID_ARGUMENT, op, "null pointer");
-  if (world < 1 || world > 16) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16");
-  if (n <= 0) return fail(QX_INVALID_SHAPE, op, "n must be positive");
+qx_status qx_cuda_peer_allreduce(void* stream, const float* src, const void* residual, void* out, int64_t n,
+                                 void* const* peer_bufs, int world, int self, void* counter, void* tickets,
+                                 int32_t* status, qx_dtype dtype, int timeout_ms) {
+  static const char* op = "peer_allreduce";
+  if (!src || !residual || !out || !peer_bufs || !counter || !tickets || !status)
+    return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16 || self < 0 || self >= world) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16, self in [0, world)");
+  if (n <= 0 || n % 2 != 0) return fail(QX_INVALID_SHAPE, op, "n must be a positive even number");
   if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "residual / out must be fp32, fp16 or bf16");
   if (timeout_ms < 1 || timeout_ms > 10000) return fail(QX_INVALID_ARGUMENT, op, "timeout_ms must be 1..10000");
   qx_status st;
   if (!device_ready(op, &st)) return st;
-  launch_peer_sum_finish((cudaStream_t)stream, buf, (const int*)flags, (const int*)counter, residual, out, (size_t)n, world,
-                         dtype, timeout_ms * 4000, status);
+  int* c = (int*)counter; unsigned* t = (unsigned*)tickets; int* sp = status;
+  if (!launch_peer_allreduce((cudaStream_t)stream, &src, &residual, &out, (size_t)n, peer_bufs, world, self, 1,
+                             &c, &t, &sp, dtype, timeout_ms * 1000))
+    return fail(QX_INVALID_ARGUMENT, op, "src must be 8-byte aligned, every buffer 16-byte aligned");
+  return check_launch(op);
+}
+
+qx_status qx_cuda_peer_allreduce_local(void* stream, const float* const* src, const void* const* residual, void* const* out,
+                                       int64_t n, void* const* peer_bufs, int world, void* const* counter,
+                                       void* const* tickets, int32_t* const* status, qx_dtype dtype, int timeout_ms) {
+  static const char* op = "peer_allreduce_local";
+  if (!src || !residual || !out || !peer_bufs || !counter || !tickets || !status)
+    return fail(QX_INVALID_ARGUMENT, op, "null pointer");
+  if (world < 1 || world > 16) return fail(QX_INVALID_ARGUMENT, op, "world must be 1..16");
+  if (n <= 0 || n % 2 != 0) return fail(QX_INVALID_SHAPE, op, "n must be a positive even number");
+  if (!float_dtype(dtype)) return fail(QX_UNSUPPORTED_DTYPE, op, "residual / out must be fp32, fp16 or bf16");
+  if (timeout_ms < 1 || timeout_ms > 10000) return fail(QX_INVALID_ARGUMENT, op, "timeout_ms must be 1..10000");
+  qx_status st;
+  if (!device_ready(op, &st)) return st;
+  if (!launch_peer_allreduce((cudaStream_t)stream, src, residual, out, (size_t)n, peer_bufs, world, 0, world,
+                             (int* const*)counter, (unsigned* const*)tickets, (int* const*)status, dtype, timeout_ms * 1000))
+    return fail(QX_INVALID_ARGUMENT, op, "null / misaligned buffers, or the cooperative launch was refused");
   return check_launch(op);
 }
 

@@ -173,10 +173,12 @@ bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* cons
                       int world, int self, int step, unsigned* tickets);
 void launch_peer_wait(cudaStream_t st, const int* flags, int world, int self, int step, int max_polls, int* status);
 // All-reduce of fp32 partials over peer stores with the residual add and the cast fused into the consumer.
-bool launch_peer_sum_push(cudaStream_t st, const float* src, size_t n, void* const* peer_bufs, void* const* peer_flags,
-                          int world, int self, int* counter, unsigned* tickets);
-void launch_peer_sum_finish(cudaStream_t st, const float* buf, const int* flags, const int* counter, const void* residual,
-                            void* out, size_t n, int world, qx_dtype dtype, int max_polls, int* status);
+bool launch_peer_gather(cudaStream_t st, float* const* gather, size_t slot_floats, void* const* peer_words, int world,
+                        int self, int local_ranks, int step, int* const* status, int max_polls);
+bool launch_peer_allreduce(cudaStream_t st, const float* const* src, const void* const* residual, void* const* out,
+                           size_t n, void* const* peer_bufs, int world, int self, int local_ranks,
+                           int* const* counter, unsigned* const* tickets, int* const* status, qx_dtype dtype,
+                           int max_polls);
 
 void launch_quantize_per_token(cudaStream_t st, const void* x, void* codes, float* scale,
                                int64_t rows, int64_t D, qx_dtype dtype, int kind);

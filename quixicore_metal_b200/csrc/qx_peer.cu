@@ -66,102 +66,130 @@ peer_wait_kernel(const int* __restrict__ flags, int world, int self, int step, i
   if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) *status = 1;
 }
 
-// ---- all-reduce of fp32 partial sums with the residual add fused into the consumer ----------------------
-// Symmetric buffer per rank: two halves (step parity) of `world` slots of slot_floats floats.  The
-// step number lives in device memory (*counter, one word per rank, advanced by the push kernel), so
-// the same launches can be replayed from a CUDA graph: nothing step-dependent is a kernel argument.
-//   push:   s = *counter + 1; the rank's partial goes into slot [s & 1][self] of EVERY rank's buffer
-//           (its own included); the CTA with the last ticket publishes s in flag[self] on every rank
-//           and stores s to *counter.
-//   finish: s = *counter; every CTA waits (bounded) until all flags carry s, then
-//           out[i] = T(sum over ranks r = 0..world-1 of slot[s & 1][r][i] + residual[i]): the same
-//           order on every rank, so all ranks hold bit-identical results.
-__global__ void __launch_bounds__(256)
-peer_sum_push_kernel(const float4* __restrict__ src, PeerPtrs bufs, PeerPtrs flags, size_t n4, size_t slot_floats,
-                     int world, int self, int* __restrict__ counter, unsigned* __restrict__ tickets) {
-  const int s = *reinterpret_cast<volatile int*>(counter) + 1;
-  const size_t slot = ((size_t)(s & 1) * world + self) * slot_floats / 4;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-    const float4 v = src[i];
-    for (int r = 0; r < world; ++r) reinterpret_cast<float4*>(bufs.p[r])[slot + i] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned t = atomicAdd(tickets, 1u);
-    if (t == gridDim.x - 1) {
-      *tickets = 0u;
-      __threadfence_system();
-      for (int r = 0; r < world; ++r) {
-        volatile int* f = reinterpret_cast<volatile int*>(flags.p[r]) + self;
-        *f = s;
-      }
-      *reinterpret_cast<volatile int*>(counter) = s;
-      __threadfence_system();
-    }
-  }
+// ---- all-reduce of fp32 partial sums with the residual add and the cast fused, ONE launch, flag-in-data ----
+// Latency form for decode-sized partials (row-parallel projections): every 16-byte store carries two floats and, beside each, the step
+// number {x, s, y, s}; the receiver polls the data words themselves until both step fields match, so there
+// is no separate flag, no fence and no barrier between the store and its use - one NVLink crossing per
+// all-reduce.  8-byte halves are single-copy atomic, and each half carries its own step field.
+// Every rank owns a buffer of two halves (step parity) of `world` slots of n / 2 such 16-byte words; a
+// slot's stale content is from step s - 2, never s.  A thread stores its elements of the rank's partial into
+// slot [s & 1][self] of every rank (its own included), then reads slot [s & 1][r] of its own buffer for
+// r = 0 .. world - 1 in order (bounded polls; on expiry *status = 1, the thread stops waiting and the result
+// is not valid), adds the residual and casts.  A thread waits only for stores of the same element by the
+// other GPUs and has stored before it waits: no CTA depends on another CTA of its grid.  The last CTA of the
+// grid stores s to *counter (device-side step: the launch can be replayed from a CUDA graph).  blockIdx.y
+// selects the rank when several ranks whose buffers live on ONE GPU run as one cooperative launch
+// (separate launches that wait for one another on one GPU are not guaranteed to overlap).
+struct PeerSumRank {
+  const float2* src; const void* residual; void* out; int* counter; unsigned* tickets; int* status;
+};
+struct PeerSumRanks { PeerSumRank r[PEER_MAX]; };
+
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-peer_sum_finish_kernel(const float* __restrict__ buf, const int* __restrict__ flags, const int* __restrict__ counter,
-                       const T* __restrict__ residual, T* __restrict__ out, size_t n, size_t slot_floats, int world,
-                       int max_polls, int* __restrict__ status) {
-  __shared__ int timed_out;
-  const int s = *reinterpret_cast<const volatile int*>(counter);
-  if (threadIdx.x == 0) timed_out = 0;
-  __syncthreads();
-  if (threadIdx.x < world && *reinterpret_cast<volatile int*>(status) == 0) {
-    const volatile int* f = flags + threadIdx.x;
-    bool ok = false;
-    for (int i = 0; i < max_polls; ++i) {
-      if (*f - s >= 0) { ok = true; break; }
-      __nanosleep(100);
+peer_allreduce_kernel(const PeerSumRanks ranks, const PeerPtrs bufs, size_t n2, int world, int self0, int max_polls) {
+  const PeerSumRank me = ranks.r[blockIdx.y];
+  const int self = self0 + (int)blockIdx.y;
+  const int s = *reinterpret_cast<volatile int*>(me.counter) + 1;
+  const bool may_wait = *reinterpret_cast<volatile int*>(me.status) == 0;   // an earlier wait ran out: do not wait again
+  const size_t half = (size_t)(s & 1) * world * n2;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t j0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (size_t j = j0; j < n2; j += stride) {
+    const float2 v = me.src[j];
+    const uint4 w = make_uint4(__float_as_uint(v.x), (uint32_t)s, __float_as_uint(v.y), (uint32_t)s);
+    for (int r = 0; r < world; ++r) st_volatile_v4(reinterpret_cast<uint4*>(bufs.p[r]) + half + (size_t)self * n2 + j, w);
+  }
+  const uint4* in = reinterpret_cast<const uint4*>(bufs.p[self]) + half;
+  const T* res = reinterpret_cast<const T*>(me.residual);
+  T* out = reinterpret_cast<T*>(me.out);
+  bool dead = !may_wait;
+  for (size_t j = j0; j < n2; j += stride) {
+    float ax = 0.f, ay = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const uint4* p = in + (size_t)r * n2 + j;
+      uint4 w = ld_volatile_v4(p);
+      if (!dead) {
+        int polls = 0;
+        while (w.y != (uint32_t)s || w.w != (uint32_t)s) {
+          if (++polls > max_polls) { dead = true; break; }
+          w = ld_volatile_v4(p);
+        }
+      }
+      ax += __uint_as_float(w.x);
+      ay += __uint_as_float(w.z);
     }
-    if (!ok) timed_out = 1;
+    out[2 * j] = from_f32<T>(ax + to_f32<T>(res[2 * j]));
+    out[2 * j + 1] = from_f32<T>(ay + to_f32<T>(res[2 * j + 1]));
   }
-  __threadfence_system();
+  if (dead && may_wait) *me.status = 1;                    // nothing hangs; the sums are not valid
   __syncthreads();
-  if (timed_out && threadIdx.x == 0) *status = 1;      // the sums below are then not valid; nothing hangs
-  const float* half = buf + (size_t)(s & 1) * world * slot_floats;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    float acc = 0.f;
-    for (int r = 0; r < world; ++r) acc += half[(size_t)r * slot_floats + i];
-    out[i] = from_f32<T>(acc + to_f32<T>(residual[i]));
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(me.tickets, 1u);
+    if (t == gridDim.x - 1) {                              // every CTA of this rank has read *counter
+      *me.tickets = 0u;
+      *reinterpret_cast<volatile int*>(me.counter) = s;
+    }
   }
+}
+
+
+// ---- all-gather of small slots, ONE launch, flag-in-data ---------------------------------------------------
+// The latency form of push + wait for candidate slots of a few KB (argmax / top-k candidates, top-p pools of
+// a single row): same 16-byte words {x, step, y, step} as the all-reduce above.  A thread sends its pair of
+// floats of the local slot [self] of `gather` to the word buffer of every peer, then polls its own word
+// buffer for the same pair of every peer (bounded; on expiry *status = 1 and the thread stops waiting) and
+// writes it into slot [r] of `gather`, which the merge stage reads as plain floats.  Word buffer of a rank:
+// two halves (step parity) of `world` slots of n2 words.  blockIdx.y = rank when all ranks live on one GPU
+// and run as one cooperative launch.
+struct PeerGatherRank { float2* gather; int* status; };
+struct PeerGatherRanks { PeerGatherRank r[PEER_MAX]; };
+
+__global__ void __launch_bounds__(256)
+peer_gather_kernel(const PeerGatherRanks ranks, const PeerPtrs words, size_t n2, int world, int self0, int step,
+                   int max_polls) {
+  const PeerGatherRank me = ranks.r[blockIdx.y];
+  const int self = self0 + (int)blockIdx.y;
+  const bool may_wait = *reinterpret_cast<volatile int*>(me.status) == 0;
+  const size_t half = (size_t)(step & 1) * world * n2;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t j0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (size_t j = j0; j < n2; j += stride) {
+    const float2 v = me.gather[(size_t)self * n2 + j];
+    const uint4 w = make_uint4(__float_as_uint(v.x), (uint32_t)step, __float_as_uint(v.y), (uint32_t)step);
+    for (int r = 0; r < world; ++r)
+      if (r != self) st_volatile_v4(reinterpret_cast<uint4*>(words.p[r]) + half + (size_t)self * n2 + j, w);
+  }
+  const uint4* in = reinterpret_cast<const uint4*>(words.p[self]) + half;
+  bool dead = !may_wait;
+  for (size_t j = j0; j < n2; j += stride) {
+    for (int r = 0; r < world; ++r) {
+      if (r == self) continue;
+      const uint4* p = in + (size_t)r * n2 + j;
+      uint4 w = ld_volatile_v4(p);
+      if (!dead) {
+        int polls = 0;
+        while (w.y != (uint32_t)step || w.w != (uint32_t)step) {
+          if (++polls > max_polls) { dead = true; break; }
+          w = ld_volatile_v4(p);
+        }
+      }
+      me.gather[(size_t)r * n2 + j] = make_float2(__uint_as_float(w.x), __uint_as_float(w.z));
+    }
+  }
+  if (dead && may_wait) *me.status = 1;
 }
 
 }  // namespace
-
-bool launch_peer_sum_push(cudaStream_t st, const float* src, size_t n, void* const* peer_bufs, void* const* peer_flags,
-                          int world, int self, int* counter, unsigned* tickets) {
-  if (world < 1 || world > PEER_MAX || n % 4 != 0 || ((uintptr_t)src & 15) != 0) return false;
-  PeerPtrs b{}, f{};
-  for (int r = 0; r < world; ++r) {
-    b.p[r] = peer_bufs[r]; f.p[r] = peer_flags[r];
-    if (((uintptr_t)peer_bufs[r] & 15) != 0 || !peer_flags[r]) return false;
-  }
-  int blocks = (int)((n / 4 + 255) / 256);
-  if (blocks > sm_count()) blocks = sm_count();
-  if (blocks < 1) blocks = 1;
-  peer_sum_push_kernel<<<blocks, 256, 0, st>>>((const float4*)src, b, f, n / 4, n, world, self, counter, tickets);
-  note_launch();
-  return true;
-}
-
-void launch_peer_sum_finish(cudaStream_t st, const float* buf, const int* flags, const int* counter, const void* residual,
-                            void* out, size_t n, int world, qx_dtype dtype, int max_polls, int* status) {
-  int blocks = (int)((n + 255) / 256);
-  if (blocks > sm_count()) blocks = sm_count();
-  if (blocks < 1) blocks = 1;
-  if (dtype == QX_DTYPE_F32)
-    peer_sum_finish_kernel<float><<<blocks, 256, 0, st>>>(buf, flags, counter, (const float*)residual, (float*)out, n, n, world, max_polls, status);
-  else if (dtype == QX_DTYPE_F16)
-    peer_sum_finish_kernel<__half><<<blocks, 256, 0, st>>>(buf, flags, counter, (const __half*)residual, (__half*)out, n, n, world, max_polls, status);
-  else
-    peer_sum_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(buf, flags, counter, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n, n, world, max_polls, status);
-  note_launch();
-}
 
 bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
                       int world, int self, int step, unsigned* tickets) {
@@ -183,6 +211,83 @@ bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* cons
 void launch_peer_wait(cudaStream_t st, const int* flags, int world, int self, int step, int max_polls, int* status) {
   peer_wait_kernel<<<1, 32, 0, st>>>(flags, world, self, step, max_polls, status);
   note_launch();
+}
+
+}  // namespace qx
+
+namespace qx {
+
+// local_ranks == 1: this process is rank `self`.  local_ranks == world: all ranks live on this GPU and
+// run as one cooperative launch (rank = blockIdx.y); src / residual / out / counter / tickets / status
+// are then arrays of `world` pointers, else arrays of one.
+bool launch_peer_allreduce(cudaStream_t st, const float* const* src, const void* const* residual, void* const* out,
+                           size_t n, void* const* peer_bufs, int world, int self, int local_ranks,
+                           int* const* counter, unsigned* const* tickets, int* const* status, qx_dtype dtype,
+                           int max_polls) {
+  if (world < 1 || world > PEER_MAX || n % 2 != 0 || n == 0) return false;
+  if (local_ranks != 1 && local_ranks != world) return false;
+  PeerSumRanks ranks{};
+  PeerPtrs b{};
+  for (int r = 0; r < world; ++r) {
+    b.p[r] = peer_bufs[r];
+    if (!peer_bufs[r] || ((uintptr_t)peer_bufs[r] & 15) != 0) return false;
+  }
+  for (int r = 0; r < local_ranks; ++r) {
+    if (!src[r] || !residual[r] || !out[r] || !counter[r] || !tickets[r] || !status[r]) return false;
+    if (((uintptr_t)src[r] & 7) != 0) return false;
+    ranks.r[r] = PeerSumRank{(const float2*)src[r], residual[r], out[r], counter[r], tickets[r], status[r]};
+  }
+  size_t n2 = n / 2;
+  int chunks = (int)((n2 + 255) / 256);
+  if (chunks > sm_count()) chunks = sm_count();
+  if (local_ranks > 1 && chunks * local_ranks > sm_count()) chunks = sm_count() / local_ranks;
+  if (chunks < 1) chunks = 1;
+  int self0 = local_ranks > 1 ? 0 : self;
+  dim3 grid((unsigned)chunks, (unsigned)local_ranks);
+  void* args[] = {&ranks, &b, &n2, &world, &self0, &max_polls};
+  const void* fn = dtype == QX_DTYPE_F32 ? (const void*)peer_allreduce_kernel<float>
+                   : dtype == QX_DTYPE_F16 ? (const void*)peer_allreduce_kernel<__half>
+                                           : (const void*)peer_allreduce_kernel<__nv_bfloat16>;
+  cudaError_t e = local_ranks > 1 ? cudaLaunchCooperativeKernel(fn, grid, dim3(256), args, 0, st)
+                                  : cudaLaunchKernel(fn, grid, dim3(256), args, 0, st);
+  if (e != cudaSuccess) { cudaGetLastError(); return false; }
+  note_launch();
+  return true;
+}
+
+}  // namespace qx
+
+namespace qx {
+
+// local_ranks == 1: this process is rank `self`; local_ranks == world: all ranks on this GPU, one
+// cooperative launch, gather / status arrays of `world` pointers.
+bool launch_peer_gather(cudaStream_t st, float* const* gather, size_t slot_floats, void* const* peer_words, int world,
+                        int self, int local_ranks, int step, int* const* status, int max_polls) {
+  if (world < 1 || world > PEER_MAX || slot_floats % 2 != 0 || slot_floats == 0) return false;
+  if (local_ranks != 1 && local_ranks != world) return false;
+  PeerGatherRanks ranks{};
+  PeerPtrs w{};
+  for (int r = 0; r < world; ++r) {
+    w.p[r] = peer_words[r];
+    if (!peer_words[r] || ((uintptr_t)peer_words[r] & 15) != 0) return false;
+  }
+  for (int r = 0; r < local_ranks; ++r) {
+    if (!gather[r] || !status[r] || ((uintptr_t)gather[r] & 7) != 0) return false;
+    ranks.r[r] = PeerGatherRank{(float2*)gather[r], status[r]};
+  }
+  size_t n2 = slot_floats / 2;
+  int chunks = (int)((n2 + 255) / 256);
+  if (chunks > sm_count()) chunks = sm_count();
+  if (local_ranks > 1 && chunks * local_ranks > sm_count()) chunks = sm_count() / local_ranks;
+  if (chunks < 1) chunks = 1;
+  int self0 = local_ranks > 1 ? 0 : self;
+  dim3 grid((unsigned)chunks, (unsigned)local_ranks);
+  void* args[] = {&ranks, &w, &n2, &world, &self0, &step, &max_polls};
+  cudaError_t e = local_ranks > 1 ? cudaLaunchCooperativeKernel((const void*)peer_gather_kernel, grid, dim3(256), args, 0, st)
+                                  : cudaLaunchKernel((const void*)peer_gather_kernel, grid, dim3(256), args, 0, st);
+  if (e != cudaSuccess) { cudaGetLastError(); return false; }
+  note_launch();
+  return true;
 }
 
 }  // namespace qx

@@ -184,7 +184,8 @@ class VocabParallelLMHead:
     # ---- peer exchange ----------------------------------------------------------------------
     def _peer_state(self, per: int, device, shape_key=()):
         """Symmetric buffers for slots of `per` floats: two halves of world slots (padded to 16 bytes),
-        a flag word per rank, the push kernel's ticket word and the wait kernel's status word.  None
+        either as 16-byte words that carry their step number (small slots) or as plain floats with a
+        flag word per rank and the push kernel's ticket word (large slots).  None
         when the symmetric allocation is not available (every rank then takes the NCCL path: the
         decision is agreed over the group so that no rank waits for a peer that went the other way)."""
         key = (per, device) + tuple(shape_key)
@@ -196,13 +197,23 @@ class VocabParallelLMHead:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
             stride = (per + 3) // 4 * 4
-            buf = symm.empty(2 * self.world * stride, dtype=torch.float32, device=device)
-            flags = symm.empty(64, dtype=torch.int32, device=device)
-            buf.zero_(); flags.zero_()
             grp = self.group if self.group is not None else self.dist.group.WORLD
-            hb, hf = symm.rendezvous(buf, grp), symm.rendezvous(flags, grp)
-            st = {"stride": stride, "buf": buf, "flags": flags, "bptr": list(hb.buffer_ptrs), "fptr": list(hf.buffer_ptrs),
-                  "tickets": torch.zeros(1, dtype=torch.int32, device=device), "keep": (hb, hf)}
+            # slots of a few KB (argmax / top-k candidates, the pools of one row) go as 16-byte words that
+            # carry their own step number - one launch, one NVLink crossing; larger ones as plain
+            # stores followed by a flag (half the bytes)
+            if 8 * stride * (self.world - 1) <= (1 << 20):
+                words = symm.empty(4 * self.world * stride, dtype=torch.float32, device=device)
+                words.zero_()
+                hw = symm.rendezvous(words, grp)
+                st = {"stride": stride, "buf": torch.zeros(self.world * stride, dtype=torch.float32, device=device),
+                      "words": words, "wptr": list(hw.buffer_ptrs), "keep": hw}
+            else:
+                buf = symm.empty(2 * self.world * stride, dtype=torch.float32, device=device)
+                flags = symm.empty(64, dtype=torch.int32, device=device)
+                buf.zero_(); flags.zero_()
+                hb, hf = symm.rendezvous(buf, grp), symm.rendezvous(flags, grp)
+                st = {"stride": stride, "buf": buf, "flags": flags, "bptr": list(hb.buffer_ptrs), "fptr": list(hf.buffer_ptrs),
+                      "tickets": torch.zeros(1, dtype=torch.int32, device=device), "keep": (hb, hf)}
         except Exception:                                   # no symmetric memory on this system / build
             ok = 0
         agreed = torch.tensor([ok], dtype=torch.int32, device=device)
@@ -255,6 +266,9 @@ class VocabParallelLMHead:
         self._x.step += 1
         step, stride, W = self._x.step, st["stride"], self.world
         par = step & 1
+        if "calls" not in st and "words" in st:    # flag-in-data words: one local gather buffer, the peers' word buffers
+            st["calls"] = [(st["buf"].data_ptr(), None)] * 2
+            st["wrd"] = (ctypes.c_void_p * W)(*st["wptr"])
         if "calls" not in st:                      # per buffer half: local base, peers' addresses of this rank's slot
             st["calls"] = []
             for half in (0, 1):
@@ -286,7 +300,7 @@ class VocabParallelLMHead:
             ids = torch.empty(T, dtype=torch.int32, device=h.device)
             _lib.check(_lib.lib().qx_cuda_lm_head_sample_sharded(
                 _stream(), hc.data_ptr(), self.wq.data_ptr(), _ptr(bias32), ids.data_ptr(), base, stride, dst,
-                st["flg"], st["flags"].data_ptr(), st["tickets"].data_ptr(), self._x.status.data_ptr(), W, self.rank,
+                st.get("flg"), _ptr(st.get("flags")), _ptr(st.get("tickets")), st.get("wrd"), self._x.status.data_ptr(), W, self.rank,
                 step, 5000, ws.data_ptr(), ws_bytes, T, V_local, K, self.begin, self.max_tiles,
                 self.fmt.encode(), _DT[h.dtype], m, max(kk, 1), float(temperature), int(seed) & 0xFFFFFFFF,
                 float(top_p)))
@@ -338,9 +352,9 @@ class TPDecodeStack:
 
     # ---- sum of the row-parallel partials over peer stores, residual add and cast fused ----------
     def _peer_sum_state(self, n: int, device):
-        """Symmetric buffer (two halves of world slots of n floats), flags, step counter, tickets and
-        status for partials of n floats; None when symmetric memory is unavailable (agreed over the
-        group, every rank then uses the NCCL all-reduce)."""
+        """Symmetric buffer (two halves of world slots of n / 2 16-byte words {x, step, y, step}), step
+        counter, tickets and status for partials of n floats; None when symmetric memory is
+        unavailable (agreed over the group, every rank then uses the NCCL all-reduce)."""
         key = (n, device)
         if key in self._sum:
             return self._sum[key]
@@ -349,14 +363,12 @@ class TPDecodeStack:
             import ctypes
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
-            buf = symm.empty(2 * self.world * n, dtype=torch.float32, device=device)
-            flags = symm.empty(64, dtype=torch.int32, device=device)
-            buf.zero_(); flags.zero_()
+            buf = symm.empty(4 * self.world * n, dtype=torch.float32, device=device)
+            buf.zero_()
             grp = self.group if self.group is not None else self.dist.group.WORLD
-            hb, hf = symm.rendezvous(buf, grp), symm.rendezvous(flags, grp)
+            hb = symm.rendezvous(buf, grp)
             W = self.world
-            st = {"buf": buf, "flags": flags, "keep": (hb, hf),
-                  "bptr": (ctypes.c_void_p * W)(*list(hb.buffer_ptrs)), "fptr": (ctypes.c_void_p * W)(*list(hf.buffer_ptrs)),
+            st = {"buf": buf, "keep": hb, "bptr": (ctypes.c_void_p * W)(*list(hb.buffer_ptrs)),
                   "counter": torch.zeros(1, dtype=torch.int32, device=device),
                   "tickets": torch.zeros(1, dtype=torch.int32, device=device),
                   "status": torch.zeros(1, dtype=torch.int32, device=device)}
@@ -374,9 +386,10 @@ class TPDecodeStack:
         if self.world == 1:
             return (part + x.float()).to(x.dtype)
         n = part.numel()
-        # small partials (decode batches) are latency-bound: peer stores; large ones keep NCCL's pipelined rings
-        small = n <= 65536 or self.exchange == "peer"
-        st = self._peer_sum_state(n, part.device) if (self.exchange in ("auto", "peer") and n % 4 == 0 and small) else None
+        # decode-sized partials are latency-bound: one-shot peer stores while a rank sends at most 4 MB
+        # (8 bytes per float and peer); larger ones keep NCCL's bandwidth-optimal algorithms
+        small = 8 * n * (self.world - 1) <= (4 << 20) or self.exchange == "peer"
+        st = self._peer_sum_state(n, part.device) if (self.exchange in ("auto", "peer") and n % 2 == 0 and small) else None
         self._last = "nccl" if st is None else "peer"
         if st is None:
             return (self._all_reduce(part) + x.float()).to(x.dtype)
@@ -385,11 +398,9 @@ class TPDecodeStack:
         pc, xc = part.contiguous(), x.contiguous()
         out = torch.empty_like(xc)
         stream = torch.cuda.current_stream().cuda_stream
-        _lib.check(L.qx_cuda_peer_sum_push(stream, pc.data_ptr(), n, st["bptr"], st["fptr"], self.world, self.rank,
-                                           st["counter"].data_ptr(), st["tickets"].data_ptr()))
-        _lib.check(L.qx_cuda_peer_sum_finish(stream, st["buf"].data_ptr(), st["flags"].data_ptr(), st["counter"].data_ptr(),
-                                             xc.data_ptr(), out.data_ptr(), n, self.world, _DT[x.dtype], 5000,
-                                             st["status"].data_ptr()))
+        _lib.check(L.qx_cuda_peer_allreduce(stream, pc.data_ptr(), xc.data_ptr(), out.data_ptr(), n, st["bptr"],
+                                            self.world, self.rank, st["counter"].data_ptr(), st["tickets"].data_ptr(),
+                                            st["status"].data_ptr(), _DT[x.dtype], 5000))
         return out
 
     def exchange_used(self) -> str:

@@ -99,46 +99,97 @@ def test_two_ranks_peer_exchange_gives_the_nccl_ids():
     assert "peer exchange ok" in out.stdout
 
 
-def test_sum_push_and_finish_on_one_gpu_as_three_ranks():
-    """Three 'ranks' whose buffers live on this GPU, run one after the other on one stream: after
-    all three have pushed step s, each finish returns residual + the sum of the three partials
-    (bit-identical on every rank), for consecutive steps (both buffer halves).  A finish whose peers
-    never pushed gives up after its limit and reports it."""
+def test_single_launch_allreduce_with_three_ranks_on_one_gpu():
+    """All three ranks' buffers live on this GPU and run as ONE cooperative launch (ranks that wait for
+    one another cannot be separate launches on one GPU): every rank returns residual + the partials
+    summed in rank order, bit-identical, over consecutive steps (both buffer halves), for sizes of one
+    and of several CTAs per rank."""
     _l, L = _lib()
-    W, n = 3, 2048
-    bufs = [torch.zeros(2 * W * n, device="cuda") for _ in range(W)]
-    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(W)]
-    counters = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(W)]
+    W = 3
+    for n in (2048, 8192 * 5, 6):
+        bufs = [torch.zeros(4 * W * n, device="cuda") for _ in range(W)]
+        counters = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(W)]
+        tickets = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(W)]
+        status = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(W)]
+        st = torch.cuda.current_stream().cuda_stream
+        for step in range(1, 5):
+            parts = [torch.randn(n, device="cuda") for _ in range(W)]
+            res = [torch.randn(n, device="cuda").bfloat16() for _ in range(W)]
+            outs = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+            rc = L.qx_cuda_peer_allreduce_local(st, _ptrs(parts), _ptrs(res), _ptrs(outs), n, _ptrs(bufs), W,
+                                                _ptrs(counters), _ptrs(tickets), _ptrs(status), _l.DTYPE_BF16, 1000)
+            assert rc.code == 0, rc.detail
+            torch.cuda.synchronize()
+            total = (parts[0] + parts[1]) + parts[2]
+            for r in range(W):
+                assert torch.equal(outs[r], (total + res[r].float()).bfloat16()), (n, step, r)
+                assert int(counters[r]) == step and int(tickets[r]) == 0 and int(status[r]) == 0
+
+
+def test_single_launch_allreduce_gives_up_when_the_peers_never_come():
+    """Rank 0 of three runs alone: its wait for the words of ranks 1 and 2 (which nothing writes) ends
+    at its limit, the status word says so, the context stays usable and a later call does not wait."""
+    _l, L = _lib()
+    W, n = 3, 4096
+    buf = torch.zeros(4 * W * n, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
     tickets = torch.zeros(1, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    st = torch.cuda.current_stream().cuda_stream
-    for step in range(1, 4):
-        parts = [torch.randn(n, device="cuda") for _ in range(W)]
-        res = torch.randn(n, device="cuda").bfloat16()
-        for r in range(W):
-            rc = L.qx_cuda_peer_sum_push(st, parts[r].data_ptr(), n, _ptrs(bufs), _ptrs(flags), W, r,
-                                         counters[r].data_ptr(), tickets.data_ptr())
-            assert rc.code == 0, rc.detail
-        outs = []
-        for r in range(W):
-            out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
-            rc = L.qx_cuda_peer_sum_finish(st, bufs[r].data_ptr(), flags[r].data_ptr(), counters[r].data_ptr(),
-                                           res.data_ptr(), out.data_ptr(), n, W, _l.DTYPE_BF16, 1000, status.data_ptr())
-            assert rc.code == 0, rc.detail
-            outs.append(out)
-        torch.cuda.synchronize()
-        want = (((parts[0] + parts[1]) + parts[2]) + res.float()).bfloat16()
-        for r in range(W):
-            assert torch.equal(outs[r], want), (step, r)
-            assert int(counters[r]) == step and flags[r][:W].tolist() == [step] * W
-        assert int(status) == 0
-    # rank 0 pushes step 4 alone: its finish waits for ranks 1 and 2, which never come
-    rc = L.qx_cuda_peer_sum_push(st, parts[0].data_ptr(), n, _ptrs([bufs[0]] * W), _ptrs([flags[0]] + [torch.zeros(64, dtype=torch.int32, device="cuda")] * 2), W, 0,
-                                 counters[0].data_ptr(), tickets.data_ptr())
-    assert rc.code == 0
-    t0 = time.time()
+    part = torch.randn(n, device="cuda")
+    res = torch.randn(n, device="cuda").bfloat16()
     out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
-    L.qx_cuda_peer_sum_finish(st, bufs[0].data_ptr(), flags[0].data_ptr(), counters[0].data_ptr(), res.data_ptr(),
-                              out.data_ptr(), n, W, _l.DTYPE_BF16, 50, status.data_ptr())
+    st = torch.cuda.current_stream().cuda_stream
+    t0 = time.time()
+    rc = L.qx_cuda_peer_allreduce(st, part.data_ptr(), res.data_ptr(), out.data_ptr(), n, _ptrs([buf] * W), W, 0,
+                                  counter.data_ptr(), tickets.data_ptr(), status.data_ptr(), _l.DTYPE_BF16, 20)
+    assert rc.code == 0, rc.detail
+    torch.cuda.synchronize()
+    assert int(status) == 1 and int(counter) == 1 and time.time() - t0 < 5.0
+    t0 = time.time()
+    rc = L.qx_cuda_peer_allreduce(st, part.data_ptr(), res.data_ptr(), out.data_ptr(), n, _ptrs([buf] * W), W, 0,
+                                  counter.data_ptr(), tickets.data_ptr(), status.data_ptr(), _l.DTYPE_BF16, 5000)
+    torch.cuda.synchronize()
+    assert rc.code == 0 and int(counter) == 2 and time.time() - t0 < 1.0
+    assert torch.equal(torch.ones(4, device="cuda") * 2, torch.full((4,), 2.0, device="cuda"))   # the context still works
+
+
+def test_single_launch_gather_with_three_ranks_on_one_gpu():
+    """All-gather of small slots by words that carry their step number: three ranks on this GPU as ONE
+    cooperative launch; afterwards every rank's gather buffer holds every rank's slot bit for bit
+    (NaN payloads and int32 ids travelling as float bits included), over consecutive steps."""
+    _l, L = _lib()
+    W = 3
+    for n in (2, 200, 40000):
+        words = [torch.zeros(4 * W * n, device="cuda") for _ in range(W)]
+        status = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(W)]
+        st = torch.cuda.current_stream().cuda_stream
+        for step in range(1, 5):
+            slots = [torch.randint(-2 ** 31, 2 ** 31 - 1, (n,), dtype=torch.int32, device="cuda") for _ in range(W)]
+            gathers = [torch.zeros(W * n, dtype=torch.int32, device="cuda") for _ in range(W)]
+            for r in range(W):
+                gathers[r][r * n:(r + 1) * n] = slots[r]
+            rc = L.qx_cuda_peer_gather_local(st, _ptrs(gathers), n, _ptrs(words), W, step, 1000, _ptrs(status))
+            assert rc.code == 0, rc.detail
+            torch.cuda.synchronize()
+            want = torch.cat(slots)
+            for r in range(W):
+                assert torch.equal(gathers[r], want), (n, step, r)
+                assert int(status[r]) == 0
+
+
+def test_single_launch_gather_gives_up_when_the_peers_never_come():
+    _l, L = _lib()
+    W, n = 3, 512
+    words = torch.zeros(4 * W * n, device="cuda")
+    gather = torch.zeros(W * n, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    t0 = time.time()
+    rc = L.qx_cuda_peer_gather(st, gather.data_ptr(), n, _ptrs([words] * W), W, 0, 1, 20, status.data_ptr())
+    assert rc.code == 0, rc.detail
     torch.cuda.synchronize()
     assert int(status) == 1 and time.time() - t0 < 5.0
+    t0 = time.time()
+    rc = L.qx_cuda_peer_gather(st, gather.data_ptr(), n, _ptrs([words] * W), W, 0, 2, 5000, status.data_ptr())
+    torch.cuda.synchronize()
+    assert rc.code == 0 and time.time() - t0 < 1.0
