@@ -69,15 +69,22 @@ prep_activations_kernel(const T* __restrict__ x, __half* __restrict__ x16,
   float amax = 0.f;
   if constexpr (sizeof(T) == 2) {
     const uint4* xv = reinterpret_cast<const uint4*>(xr);          // 8 elements per load (K % 8 == 0)
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
-      const uint4 v = __ldg(xv + i);
+    const int nv = K / 8;
+    auto fold = [&](const uint4& v) {
       const T* e = reinterpret_cast<const T*>(&v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float a = fabsf(to_f32<T>(e[j]));
         if (a < 3.0e38f) amax = fmaxf(amax, a);                    // inf / nan do not choose the scale
       }
+    };
+    int i = threadIdx.x;
+    for (; i + 3 * (int)blockDim.x < nv; i += 4 * blockDim.x) {    // four loads in flight per thread
+      const uint4 v0 = __ldg(xv + i), v1 = __ldg(xv + i + blockDim.x), v2 = __ldg(xv + i + 2 * blockDim.x),
+                  v3 = __ldg(xv + i + 3 * blockDim.x);
+      fold(v0); fold(v1); fold(v2); fold(v3);
     }
+    for (; i < nv; i += blockDim.x) fold(__ldg(xv + i));
   } else {
     for (int c = threadIdx.x; c < K; c += blockDim.x) {
       const float a = fabsf(to_f32<T>(xr[c]));
@@ -106,6 +113,17 @@ prep_activations_kernel(const T* __restrict__ x, __half* __restrict__ x16,
       out[((size_t)(pos >> 6) * img_rows + ml) * 64 + ((((pos >> 3) & 7) ^ (ml & 7)) << 3) + (pos & 7)] =
           __float2half_rn(to_f32<T>(xr[c]) * down);
     }
+  } else if (sizeof(T) == 2) {
+    __half* out = x16 + (size_t)m * K;                             // slices are whole 32-column groups: 8 per load
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    for (int i = c0 / 8 + threadIdx.x; i < c1 / 8; i += blockDim.x) {
+      const uint4 v = __ldg(xv + i);
+      const T* e = reinterpret_cast<const T*>(&v);
+      const int c = 8 * i;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        out[(c & ~31) + perm_position(perm, (c & 31) + j)] = __float2half_rn(to_f32<T>(e[j]) * down);
+    }
   } else {
     __half* out = x16 + (size_t)m * K;
     for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
@@ -118,8 +136,8 @@ prep_activations_kernel(const T* __restrict__ x, __half* __restrict__ x16,
 
 void launch_prep_activations(cudaStream_t st, const void* x, qx_dtype dtype, __half* x16,
                              float* rowscale, int M, int K, int perm, int img_rows) {
-  int slices = (K + 2047) / 2048;
-  if (slices > 16) slices = 16;
+  int slices = (K + 1023) / 1024;
+  if (slices > 32) slices = 32;
   const int rows = img_rows > 0 ? (M + img_rows - 1) / img_rows * img_rows : M;
   dim3 grid(slices, rows);
   if (dtype == QX_DTYPE_F16)
@@ -155,10 +173,13 @@ struct StreamCfg {
   }
 };
 
-template <int FMT, int NT, bool DUAL, bool HALF, typename T>
+// XS: batch 1 with the activation row prepared by every CTA itself into shared memory (xsrc = the raw
+// 16-bit row, bf16 if x_bf16 else f16; x16 / rowscale unused) instead of by a preparation kernel: one launch less in front of a
+// projection whose own run takes 5 - 50 us.  Same arithmetic, same results.
+template <int FMT, int NT, bool DUAL, bool HALF, typename T, bool XS>
 __global__ void __launch_bounds__(StreamCfg<FMT, DUAL, HALF>::max_warps(NT) * 32, 1)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_constant__ CUtensorMap wmap1,
-                   const __half* __restrict__ x16, const float* __restrict__ rowscale,
+                   const __half* __restrict__ x16, const float* __restrict__ rowscale, const uint16_t* __restrict__ xsrc, int x_bf16,
                    const T* __restrict__ bias0, const T* __restrict__ bias1,
                    const T* __restrict__ residual, T* __restrict__ y, int M, int K, int N,
                    int activation, int use_bias, int use_residual, uint8_t* __restrict__ mx_blocks,
@@ -195,11 +216,20 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   auto range_begin = [&](int w) { return (int)(S * (unsigned)w / (unsigned)nwarps); };
   const int sb = range_begin(warp), se = range_begin(warp + 1);
 
-  const __half* xr[NT];
+  using XP = typename std::conditional<XS, SmemRow, const __half*>::type;
+  XP xr[NT];
+  // XS: [prepared row: K halves][row scale][32 floats of reduction scratch] behind the partial-sum slots
+  uint8_t* xs_base = smem_raw + (((size_t)nwarps * Cfg::warp_smem(NT) + 15) & ~(size_t)15);
+  const float* rs_ptr = rowscale;
+  if constexpr (XS) {
+    rs_ptr = reinterpret_cast<const float*>(xs_base + (size_t)K * 2);
+    xr[0] = SmemRow{g == 0 ? smem_u32(xs_base) : 0u};
+  } else {
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int m = nt * 8 + g;
-    xr[nt] = m < M ? x16 + (size_t)m * K : nullptr;
+    for (int nt = 0; nt < NT; ++nt) {
+      const int m = nt * 8 + g;
+      xr[nt] = m < M ? x16 + (size_t)m * K : nullptr;
+    }
   }
 
   // (tile, chunk) of the next step to fetch
@@ -215,6 +245,50 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   // Programmatic dependent launch: this grid may start while the activation-preparation kernel is
   // still running (the weight boxes above do not depend on it); everything below reads its output.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if constexpr (XS) {
+    // the preparation kernel's arithmetic for row 0, by this CTA: largest finite magnitude ->
+    // power-of-two scale -> f16(x * 2^-S) in the decoders' column order
+    static_assert(NT == 1, "in-kernel preparation: one row");
+    __half* xs = reinterpret_cast<__half*>(xs_base);
+    float* rs_s = reinterpret_cast<float*>(xs_base + (size_t)K * 2);
+    float* red = rs_s + 1;
+    const uint4* xv = reinterpret_cast<const uint4*>(xsrc);
+    auto widen = [&](uint16_t b) {
+      return x_bf16 ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
+    };
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+      const uint4 v = __ldg(xv + i);
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = fabsf(widen(e[j]));
+        if (a < 3.0e38f) amax = fmaxf(amax, a);
+      }
+    }
+    amax = warp_max(amax);
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    amax = 0.f;
+    for (int i = 0; i < nwarps; ++i) amax = fmaxf(amax, red[i]);
+    int S = 0;
+    if (amax > 0.f) {
+      S = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 14;
+      S = max(-110, min(110, S));
+    }
+    const float down = __uint_as_float((uint32_t)(127 - S) << 23);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+      const uint4 v = __ldg(xv + i);
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+      const int c0 = 8 * i;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        xs[(c0 & ~31) + perm_position(F::PERM, (c0 & 31) + j)] = __float2half_rn(widen(e[j]) * down);
+    }
+    if (threadIdx.x == 0) *rs_s = __uint_as_float((uint32_t)(127 + S) << 23);
+    __syncthreads();
+  }
 
   float acc[NSETS][NT][4];
   auto clear_acc = [&]() {
@@ -236,7 +310,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
         const int n = row0 + g + (e >> 1) * 8;
         const int m = nt * 8 + 2 * t + (e & 1);
         if (n < N && m < M) {
-          const float rs = rowscale[m] * GroupProc<FMT>::ACC_SCALE;
+          const float rs = rs_ptr[m] * GroupProc<FMT>::ACC_SCALE;
           float v = acc[0][nt][e] * rs;
           const size_t o = (size_t)m * N + n;
           if constexpr (DUAL) {
@@ -353,40 +427,22 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   }
 }
 
-template <int FMT, int NT, bool DUAL, bool HALF, typename T>
-static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
-  const int sms = sm_count();
-  const int ntiles = (int)((a.N + 15) / 16);
+template <int FMT, int NT, bool DUAL, bool HALF, typename T, bool XS>
+static bool launch_stream_x(cudaStream_t st, const GemvArgs& a, int nwarps, size_t smem, int blocks, const __half* x16,
+                            const float* rowscale, int* err) {
   using Cfg = StreamCfg<FMT, DUAL, HALF>;
-  const int nwarps = Cfg::max_warps(NT);
-  // one CTA per SM; a CTA takes a contiguous, balanced share of the m-tiles and its warps split the
-  // (tile, chunk) steps of that share evenly
-  const int units = (a.out_quant == OQ_MXFP8 && !a.out_f32 && a.N % 32 == 0) ? (ntiles + 1) / 2 : ntiles;
-  const int blocks = units < sms ? units : sms;
-  const long long nch = (a.K + Cfg::KC - 1) / Cfg::KC;
-  if ((long long)((ntiles + blocks - 1) / blocks + 2) * nch * (nwarps + 1) >= (1LL << 31)) return false;
-  const size_t smem = (size_t)nwarps * Cfg::warp_smem(NT);
   static bool attr_set[64] = {};                    // per instantiation and device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return false;
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, NT, DUAL, HALF, T>,
+    if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, NT, DUAL, HALF, T, XS>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
     attr_set[dev] = true;
   }
-  int* err = device_error_flag();
-  if (!err) return false;
-
-  // prepared activations and row scales live in the call's scratch
-  const size_t x16_bytes = ((size_t)a.M * a.K * 2 + 255) & ~(size_t)255;
-  if (!a.scratch || a.scratch_bytes < x16_bytes + (((size_t)a.M * 4 + 255) & ~(size_t)255)) return false;
-  __half* x16 = (__half*)a.scratch;
-  float* rowscale = (float*)((char*)a.scratch + x16_bytes);
-  launch_prep_activations(st, a.x, a.dtype, x16, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM);
   using WSG = typename Cfg::WS::G;
   const size_t row_bytes = (size_t)(a.K / StreamFmt<FMT>::BK) * StreamFmt<FMT>::BB;
   CUtensorMap map0, map1;
@@ -396,7 +452,8 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   if (!maps_ok) return false;
   // MXFP8 output rows are packed by the same kernel (needs whole 32-channel blocks)
   uint8_t* mx = (a.out_quant == OQ_MXFP8 && !a.out_f32 && a.N % 32 == 0) ? (uint8_t*)a.q_codes : nullptr;
-  // launched as a programmatic dependent of the preparation kernel (see griddepcontrol.wait)
+  // launched as a programmatic dependent of the kernel before it (see griddepcontrol.wait): the
+  // preparation kernel, or with XS whatever produced the activations
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
   cfg.blockDim = dim3((unsigned)(nwarps * 32));
@@ -407,15 +464,56 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, HALF, T>, map0, map1, (const __half*)x16,
-                         (const float*)rowscale, (const T*)a.bias0, (const T*)a.bias1,
-                         (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation,
-                         a.use_bias, a.use_residual, mx, err) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<FMT, NT, DUAL, HALF, T, XS>, map0, map1, x16, rowscale, (const uint16_t*)a.x,
+                         (int)(a.dtype == QX_DTYPE_BF16),
+                         (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual, (T*)a.y, (int)a.M, (int)a.K,
+                         (int)a.N, a.activation, a.use_bias, a.use_residual, mx, err) != cudaSuccess) {
     cudaGetLastError();
-    gemv_stream_kernel<FMT, NT, DUAL, HALF, T><<<blocks, nwarps * 32, smem, st>>>(
-        map0, map1, x16, rowscale, (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual,
+    gemv_stream_kernel<FMT, NT, DUAL, HALF, T, XS><<<blocks, nwarps * 32, smem, st>>>(
+        map0, map1, x16, rowscale, (const uint16_t*)a.x, (int)(a.dtype == QX_DTYPE_BF16), (const T*)a.bias0, (const T*)a.bias1, (const T*)a.residual,
         (T*)a.y, (int)a.M, (int)a.K, (int)a.N, a.activation, a.use_bias, a.use_residual, mx, err);
   }
+  return true;
+}
+
+template <int FMT, int NT, bool DUAL, bool HALF, typename T>
+static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
+  const int sms = sm_count();
+  const int ntiles = (int)((a.N + 15) / 16);
+  using Cfg = StreamCfg<FMT, DUAL, HALF>;
+  int nwarps = Cfg::max_warps(NT);
+  // one CTA per SM; a CTA takes a contiguous, balanced share of the m-tiles and its warps split the
+  // (tile, chunk) steps of that share evenly
+  const int units = (a.out_quant == OQ_MXFP8 && !a.out_f32 && a.N % 32 == 0) ? (ntiles + 1) / 2 : ntiles;
+  const int blocks = units < sms ? units : sms;
+  const long long nch = (a.K + Cfg::KC - 1) / Cfg::KC;
+  if ((long long)((ntiles + blocks - 1) / blocks + 2) * nch * (nwarps + 1) >= (1LL << 31)) return false;
+  int* err = device_error_flag();
+  if (!err) return false;
+
+  // Batch 1 with a row that fits beside the rings (giving up at most two of the warps): every CTA
+  // prepares the row itself, no preparation kernel.
+  if constexpr (NT == 1) {
+    if (a.M == 1 && ((uintptr_t)a.x & 15) == 0 && a.K % 8 == 0 && (a.dtype == QX_DTYPE_BF16 || a.dtype == QX_DTYPE_F16)) {
+      const size_t extra = (size_t)a.K * 2 + 4 + 32 * 4;
+      for (int w = nwarps; w >= nwarps - 2 && w >= 8; --w) {
+        const size_t smem = (((size_t)w * Cfg::warp_smem(NT) + 15) & ~(size_t)15) + extra;
+        if (smem <= 227 * 1024) {
+          if (!launch_stream_x<FMT, NT, DUAL, HALF, T, true>(st, a, w, smem, blocks, nullptr, nullptr, err)) return false;
+          note_launch(1);
+          return true;
+        }
+      }
+    }
+  }
+  // prepared activations and row scales live in the call's scratch
+  const size_t x16_bytes = ((size_t)a.M * a.K * 2 + 255) & ~(size_t)255;
+  if (!a.scratch || a.scratch_bytes < x16_bytes + (((size_t)a.M * 4 + 255) & ~(size_t)255)) return false;
+  __half* x16 = (__half*)a.scratch;
+  float* rowscale = (float*)((char*)a.scratch + x16_bytes);
+  const size_t smem = (size_t)nwarps * Cfg::warp_smem(NT);
+  launch_prep_activations(st, a.x, a.dtype, x16, rowscale, (int)a.M, (int)a.K, StreamFmt<FMT>::PERM);
+  if (!launch_stream_x<FMT, NT, DUAL, HALF, T, false>(st, a, nwarps, smem, blocks, x16, rowscale, err)) return false;
   note_launch(2);
   return true;
 }

@@ -396,6 +396,23 @@ __device__ __forceinline__ void unit32(const uint32_t (&s)[2 * NSETS], uint32_t 
 __device__ __forceinline__ uint4 ldg_or_zero(const __half* row, int off) {
   return row ? __ldg(reinterpret_cast<const uint4*>(row + off)) : make_uint4(0u, 0u, 0u, 0u);
 }
+__device__ __forceinline__ uint2 ldg2_or_zero(const __half* row, int off) {
+  return row ? __ldg(reinterpret_cast<const uint2*>(row + off)) : make_uint2(0u, 0u);
+}
+// A prepared activation row that lives in shared memory (batch 1, prepared by the consuming kernel
+// itself): shared-window address of its first element, 0 = no row.  The group processors take the row
+// pointers as a template type, so the same code reads the row from global memory or from here.
+struct SmemRow { uint32_t addr; };
+__device__ __forceinline__ uint4 ldg_or_zero(SmemRow row, int off) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (row.addr) asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(row.addr + 2u * (uint32_t)off));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg2_or_zero(SmemRow row, int off) {
+  uint2 v = make_uint2(0u, 0u);
+  if (row.addr) asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(row.addr + 2u * (uint32_t)off));
+  return v;
+}
 
 // ---- group processors: one GROUP of columns for this thread's rows ---------------------------------
 // s[r]: shared address of column 0 of the group in row slot r (r = 0,1: rows g, g+8 of the gate /
@@ -407,8 +424,8 @@ template <int FMT> struct GroupProc {
   static constexpr bool PIPED = true;       // has the unit-pipelined form for large batches
   static constexpr float ACC_SCALE = 1.f;   // run() accumulates dot products / ACC_SCALE
   template <int NT> struct BFrag { uint4 v[UNITS][NT]; };
-  template <int NT>
-  __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int t,
+  template <int NT, class XP>
+  __device__ __forceinline__ static void load_b(const XP (&xr)[NT], int col, int t,
                                                 BFrag<NT>& b) {
 #pragma unroll
     for (int u = 0; u < UNITS; ++u)
@@ -417,9 +434,9 @@ template <int FMT> struct GroupProc {
   }
   // PRE: the fragments were fetched one group ahead into `b` (small batches); otherwise they are
   // loaded unit by unit from xr / col (large batches, where a whole group would not fit registers).
-  template <int NSETS, int NT, bool PRE, int J>
+  template <int NSETS, int NT, bool PRE, int J, class XP>
   __device__ __forceinline__ static void one(const uint32_t (&s)[2 * NSETS], int t, const BFrag<NT>& b,
-                                             const __half* const (&xr)[NT], int col,
+                                             const XP (&xr)[NT], int col,
                                              float (&acc)[NSETS][NT][4]) {
     if constexpr (PRE) {
       unit32<FMT, J, NSETS, NT>(s, (uint32_t)(J * F::BB), t, b.v[J], acc);
@@ -430,9 +447,9 @@ template <int FMT> struct GroupProc {
       unit32<FMT, J, NSETS, NT>(s, (uint32_t)(J * F::BB), t, bb, acc);
     }
   }
-  template <int NSETS, int NT, bool PRE>
+  template <int NSETS, int NT, bool PRE, class XP>
   __device__ __forceinline__ static void run(const uint32_t (&s)[2 * NSETS], int t,
-                                             const BFrag<NT>& b, const __half* const (&xr)[NT],
+                                             const BFrag<NT>& b, const XP (&xr)[NT],
                                              int col, float (&acc)[NSETS][NT][4]) {
     one<NSETS, NT, PRE, 0>(s, t, b, xr, col, acc);
     if constexpr (UNITS > 1) one<NSETS, NT, PRE, 1>(s, t, b, xr, col, acc);
@@ -442,9 +459,9 @@ template <int FMT> struct GroupProc {
   // Large batches: the activation fragments of one unit (NT x 16 bytes) are fetched one unit ahead.
   // `carry` holds the fragments of this group's first unit on entry and those of the next group's
   // first unit on exit (when there is a next group).
-  template <int NSETS, int NT, int J>
+  template <int NSETS, int NT, int J, class XP>
   __device__ __forceinline__ static void piped(const uint32_t (&s)[2 * NSETS], int t,
-                                               const __half* const (&xr)[NT], int col, bool has_next,
+                                               const XP (&xr)[NT], int col, bool has_next,
                                                uint4 (&cur)[NT], float (&acc)[NSETS][NT][4]) {
     uint4 nxt[NT];
     if constexpr (J + 1 < UNITS) {
@@ -459,8 +476,8 @@ template <int FMT> struct GroupProc {
     for (int nt = 0; nt < NT; ++nt) cur[nt] = nxt[nt];
     if constexpr (J + 1 < UNITS) piped<NSETS, NT, J + 1>(s, t, xr, col, has_next, cur, acc);
   }
-  template <int NT>
-  __device__ __forceinline__ static void load_first(const __half* const (&xr)[NT], int col, int t,
+  template <int NT, class XP>
+  __device__ __forceinline__ static void load_first(const XP (&xr)[NT], int col, int t,
                                                     uint4 (&cur)[NT]) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) cur[nt] = ldg_or_zero(xr[nt], col + 8 * t);
@@ -500,8 +517,8 @@ template <> struct GroupProc<F_NVFP4> {
     a[3][0] = h2mul(cvt_e2m1x2<3>(x1), s2); a[3][1] = h2mul(cvt_e2m1x2<0>(x2), s2);
   }
   template <int NT> struct BFrag { uint4 v[2][NT]; };
-  template <int NT>
-  __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int t,
+  template <int NT, class XP>
+  __device__ __forceinline__ static void load_b(const XP (&xr)[NT], int col, int t,
                                                 BFrag<NT>& b) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -509,9 +526,9 @@ template <> struct GroupProc<F_NVFP4> {
       b.v[1][nt] = ldg_or_zero(xr[nt], col + 16 * t + 8);
     }
   }
-  template <int NSETS, int NT, bool PRE>
+  template <int NSETS, int NT, bool PRE, class XP>
   __device__ __forceinline__ static void run(const uint32_t (&s)[2 * NSETS], int t,
-                                             const BFrag<NT>& b, const __half* const (&xr)[NT],
+                                             const BFrag<NT>& b, const XP (&xr)[NT],
                                              int col, float (&acc)[NSETS][NT][4]) {
     uint32_t a[2 * NSETS][4][2];
 #pragma unroll
@@ -558,17 +575,15 @@ template <> struct GroupProc<F_Q6_K> {
     a0 = h2sub(__byte_perm(c, 0x64646464u, 0x4240), 0x64206420u);
     a1 = h2sub(__byte_perm(c, 0x64646464u, 0x4341), 0x64206420u);
   }
-  template <int NT> struct BFrag { const __half* xr[NT]; int col; };   // fetched inside run()
-  template <int NT>
-  __device__ __forceinline__ static void load_b(const __half* const (&xr)[NT], int col, int,
+  template <int NT> struct BFrag { int col; };   // the fragments are fetched inside run()
+  template <int NT, class XP>
+  __device__ __forceinline__ static void load_b(const XP (&xr)[NT], int col, int,
                                                 BFrag<NT>& b) {
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) b.xr[nt] = xr[nt];
     b.col = col;
   }
-  template <int ODD, int NSETS, int NT>
+  template <int ODD, int NSETS, int NT, class XP>
   __device__ __forceinline__ static void superblock(const uint32_t (&s)[2 * NSETS], uint32_t boff,
-                                                    int t, const __half* const (&xr)[NT], int col,
+                                                    int t, const XP (&xr)[NT], int col,
                                                     float (&acc)[NSETS][NT][4]) {
     float d[2 * NSETS];
 #pragma unroll
@@ -583,8 +598,7 @@ template <> struct GroupProc<F_Q6_K> {
         for (int g = 0; g < 4; ++g)
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
-            bq[g][nt] = xr[nt] ? __ldg(reinterpret_cast<const uint2*>(xr[nt] + col + 128 * c + 32 * g + 16 * l + 4 * t))
-                               : make_uint2(0u, 0u);
+            bq[g][nt] = ldg2_or_zero(xr[nt], col + 128 * c + 32 * g + 16 * l + 4 * t);
 #pragma unroll
         for (int r = 0; r < 2 * NSETS; ++r) {
           const uint32_t base = s[r] + boff;
@@ -626,9 +640,9 @@ template <> struct GroupProc<F_Q6_K> {
       }
     }
   }
-  template <int NSETS, int NT, bool PRE>
+  template <int NSETS, int NT, bool PRE, class XP>
   __device__ __forceinline__ static void run(const uint32_t (&s)[2 * NSETS], int t,
-                                             const BFrag<NT>&, const __half* const (&xr)[NT],
+                                             const BFrag<NT>&, const XP (&xr)[NT],
                                              int col, float (&acc)[NSETS][NT][4]) {
     superblock<0, NSETS, NT>(s, 0u, t, xr, col, acc);
     superblock<1, NSETS, NT>(s, 210u, t, xr, col + 256, acc);
