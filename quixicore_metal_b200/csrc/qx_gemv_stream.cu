@@ -247,47 +247,8 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if constexpr (XS) {
-    // the preparation kernel's arithmetic for row 0, by this CTA: largest finite magnitude ->
-    // power-of-two scale -> f16(x * 2^-S) in the decoders' column order
     static_assert(NT == 1, "in-kernel preparation: one row");
-    __half* xs = reinterpret_cast<__half*>(xs_base);
-    float* rs_s = reinterpret_cast<float*>(xs_base + (size_t)K * 2);
-    float* red = rs_s + 1;
-    const uint4* xv = reinterpret_cast<const uint4*>(xsrc);
-    auto widen = [&](uint16_t b) {
-      return x_bf16 ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
-    };
-    float amax = 0.f;
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
-      const uint4 v = __ldg(xv + i);
-      const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float a = fabsf(widen(e[j]));
-        if (a < 3.0e38f) amax = fmaxf(amax, a);
-      }
-    }
-    amax = warp_max(amax);
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
-    amax = 0.f;
-    for (int i = 0; i < nwarps; ++i) amax = fmaxf(amax, red[i]);
-    int S = 0;
-    if (amax > 0.f) {
-      S = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 14;
-      S = max(-110, min(110, S));
-    }
-    const float down = __uint_as_float((uint32_t)(127 - S) << 23);
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
-      const uint4 v = __ldg(xv + i);
-      const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
-      const int c0 = 8 * i;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        xs[(c0 & ~31) + perm_position(F::PERM, (c0 & 31) + j)] = __float2half_rn(widen(e[j]) * down);
-    }
-    if (threadIdx.x == 0) *rs_s = __uint_as_float((uint32_t)(127 + S) << 23);
-    __syncthreads();
+    cta_prepare_row<F::PERM>(xs_base, xsrc, x_bf16, K);
   }
 
   float acc[NSETS][NT][4];
@@ -495,7 +456,7 @@ static bool launch_stream_t(cudaStream_t st, const GemvArgs& a) {
   // prepares the row itself, no preparation kernel.
   if constexpr (NT == 1) {
     if (a.M == 1 && ((uintptr_t)a.x & 15) == 0 && a.K % 8 == 0 && (a.dtype == QX_DTYPE_BF16 || a.dtype == QX_DTYPE_F16)) {
-      const size_t extra = (size_t)a.K * 2 + 4 + 32 * 4;
+      const size_t extra = cta_prepared_row_bytes((size_t)a.K);
       for (int w = nwarps; w >= nwarps - 2 && w >= 8; --w) {
         const size_t smem = (((size_t)w * Cfg::warp_smem(NT) + 15) & ~(size_t)15) + extra;
         if (smem <= 227 * 1024) {

@@ -456,10 +456,13 @@ constexpr int LMH_TOK_CHUNK = 16;
 
 // WROWS = vocabulary rows per warp: 32 (8 warps, two m-tiles share every activation fragment) or
 // 16 (16 warps: more loads in flight; used from 9 hidden rows per pass).
-template <int FMT, int NT, int WROWS>
+// XS: a single hidden row, prepared by every CTA itself into shared memory (xsrc = the raw 16-bit row,
+// bf16 if x_bf16 else f16; x16 / rowscale unused) instead of by the preparation kernel.
+template <int FMT, int NT, int WROWS, bool XS>
 __global__ void __launch_bounds__(256 / WROWS * 32, 1)
 lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ x16,
-                  const float* __restrict__ rowscale, const float* __restrict__ bias,
+                  const float* __restrict__ rowscale, const uint16_t* __restrict__ xsrc, int x_bf16,
+                  const float* __restrict__ bias,
                   float* __restrict__ part_val, int32_t* __restrict__ part_id,
                   float* __restrict__ part_lse, int T_total, int tokens_per_group, int V, int K,
                   long long vocab_offset, long long tiles_stride, int mode, int topk, float invtemp,
@@ -495,6 +498,17 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
 #pragma unroll
   for (int p = 0; p < C::STAGES - 1; ++p)
     if (p < steps) ws.issue(p, step_row0(p), p % nch);
+  // Programmatic dependent launch: the weight boxes above do not depend on the kernel before this one
+  // (the preparation kernel, or with XS whatever produced the hidden row); everything below does.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  using XP = typename std::conditional<XS, SmemRow, const __half*>::type;
+  uint8_t* xs_base = reinterpret_cast<uint8_t*>(logit + LMH_TOK_CHUNK * LMH_LOGIT_PITCH);   // XS: behind the logit buffer
+  const float* rs_ptr = rowscale;
+  if constexpr (XS) {
+    static_assert(NT == 1, "in-kernel preparation: one row");
+    cta_prepare_row<F::PERM>(xs_base, xsrc, x_bf16, K);
+    rs_ptr = reinterpret_cast<const float*>(xs_base + (size_t)K * 2);
+  }
 
   float acc[NSETS][NT][4];
   for (int j = 0; j < my_tiles; ++j) {
@@ -503,11 +517,15 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
     const int t_base = (item % groups) * tokens_per_group;
     const int T_pass = min(tokens_per_group, T_total - t_base);
     const int row0 = tile * LMH_TILE + warp * WROWS;
-    const __half* xr[NT];
+    XP xr[NT];
+    if constexpr (XS) {
+      xr[0] = SmemRow{g == 0 ? smem_u32(xs_base) : 0u};
+    } else {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int m = nt * 8 + g;
-      xr[nt] = m < T_pass ? x16 + (size_t)(t_base + m) * K : nullptr;
+      for (int nt = 0; nt < NT; ++nt) {
+        const int m = nt * 8 + g;
+        xr[nt] = m < T_pass ? x16 + (size_t)(t_base + m) * K : nullptr;
+      }
     }
 #pragma unroll
     for (int a = 0; a < NSETS; ++a)
@@ -584,7 +602,7 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
             for (int e = 0; e < 4; ++e) {
               const int ml = h * 8 + 2 * t + (e & 1);
               const int m = nt * 8 + 2 * t + (e & 1);
-              const float rs = m < T_pass ? rowscale[t_base + m] * GP::ACC_SCALE : 0.f;
+              const float rs = m < T_pass ? rs_ptr[t_base + m] * GP::ACC_SCALE : 0.f;
               logit[ml * LMH_LOGIT_PITCH + warp * WROWS + set * 16 + g + (e >> 1) * 8] = acc[set][nt][e] * rs;
             }
         }
@@ -726,7 +744,7 @@ static bool lmh_stream_ok(const LmHeadArgs& a) {
          row_bytes % 16 == 0 && ((uintptr_t)a.wq & 15) == 0 && a.V >= 32;
 }
 
-template <int FMT, int NT>
+template <int FMT, int NT, bool XS>
 static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __half* x16,
                                  const float* rowscale, float* pv, int32_t* pi, float* pl,
                                  int64_t tiles_stride, int* err, const CUtensorMap& wmap) {
@@ -735,21 +753,39 @@ static void launch_lmh_stream_nt(cudaStream_t st, const LmHeadArgs& a, const __h
   constexpr int NW = 256 / WROWS;
   using WS = WarpStream<FMT, C::KC, WROWS, C::STAGES>;
   const size_t smem = (size_t)NW * WS::WARP_BYTES + (size_t)NW * C::STAGES * 8 +
-                      (size_t)LMH_TOK_CHUNK * LMH_LOGIT_PITCH * 4;
+                      (size_t)LMH_TOK_CHUNK * LMH_LOGIT_PITCH * 4 + (XS ? cta_prepared_row_bytes((size_t)a.K) : 0);
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT, WROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(lmh_stream_kernel<FMT, NT, WROWS, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr_set[dev] = true;
   }
   const int real_tiles = (int)((a.V + LMH_TILE - 1) / LMH_TILE);
   const int tpg = NT * 8;
   const long long items = (long long)real_tiles * ((a.T + tpg - 1) / tpg);
-  dim3 grid((unsigned)(items < sm_count() ? items : sm_count()));
-  lmh_stream_kernel<FMT, NT, WROWS><<<grid, NW * 32, smem, st>>>(
-      wmap, x16, rowscale, a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
-      (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed, a.mask, err);
+  const unsigned blocks = (unsigned)(items < sm_count() ? items : sm_count());
+  // a programmatic dependent of the kernel before it (see griddepcontrol.wait in the kernel)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(NW * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, lmh_stream_kernel<FMT, NT, WROWS, XS>, wmap, x16, rowscale, (const uint16_t*)a.h,
+                         (int)(a.dtype == QX_DTYPE_BF16), a.bias, pv, pi, pl, (int)a.T, tpg, (int)a.V, (int)a.K,
+                         (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed,
+                         a.mask, err) != cudaSuccess) {
+    cudaGetLastError();
+    lmh_stream_kernel<FMT, NT, WROWS, XS><<<blocks, NW * 32, smem, st>>>(
+        wmap, x16, rowscale, (const uint16_t*)a.h, (int)(a.dtype == QX_DTYPE_BF16), a.bias, pv, pi, pl, (int)a.T, tpg,
+        (int)a.V, (int)a.K, (long long)a.vocab_offset, (long long)tiles_stride, a.mode, a.topk, a.invtemp, a.seed,
+        a.mask, err);
+  }
   note_launch();
 }
 
@@ -891,6 +927,14 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   }
   __half* x16 = sc.act;
   float* rowscale = sc.rowscale;
+  // a single hidden row is prepared by the stage-1 CTAs themselves (one launch less per decoded token)
+  using WS1 = WarpStream<FMT, LmhCfg<FMT>::KC, 32, LmhCfg<FMT>::STAGES>;
+  if (a.T == 1 && ((uintptr_t)a.h & 15) == 0 && a.K % 8 == 0 &&
+      (size_t)8 * WS1::WARP_BYTES + (size_t)8 * LmhCfg<FMT>::STAGES * 8 + (size_t)LMH_TOK_CHUNK * LMH_LOGIT_PITCH * 4 +
+              cta_prepared_row_bytes((size_t)a.K) <= 227 * 1024) {
+    launch_lmh_stream_nt<FMT, 1, true>(st, a, nullptr, nullptr, pv, pi, pl, tiles_stride, err, wmap);
+    return true;
+  }
   launch_prep_activations(st, a.h, a.dtype, x16, rowscale, (int)a.T, (int)a.K, StreamFmt<FMT>::PERM);
   note_launch();
   // hidden rows per CTA: 64 when there are enough vocabulary tiles to fill the GPU; fewer rows
@@ -899,10 +943,10 @@ static bool launch_lmh_stream(cudaStream_t st, const LmHeadArgs& a, float* pv, i
   int tpg = 64;
   while (tpg > 8 && (long long)real_tiles * ((a.T + tpg - 1) / tpg) < sm_count() && a.T > tpg / 2) tpg >>= 1;
   while (tpg > 8 && a.T <= tpg / 2) tpg >>= 1;
-  if (tpg <= 8) launch_lmh_stream_nt<FMT, 1>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-  else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-  else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
-  else launch_lmh_stream_nt<FMT, 8>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  if (tpg <= 8) launch_lmh_stream_nt<FMT, 1, false>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  else if (tpg <= 16) launch_lmh_stream_nt<FMT, 2, false>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  else if (tpg <= 32) launch_lmh_stream_nt<FMT, 4, false>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
+  else launch_lmh_stream_nt<FMT, 8, false>(st, a, x16, rowscale, pv, pi, pl, tiles_stride, err, wmap);
   return true;
 }
 

@@ -414,6 +414,56 @@ __device__ __forceinline__ uint2 ldg2_or_zero(SmemRow row, int off) {
   return v;
 }
 
+// One activation row prepared by the whole CTA into shared memory, with the arithmetic of the
+// preparation kernel: largest finite magnitude -> power-of-two scale 2^-S that puts it in [2^14, 2^15)
+// -> xs[perm(c)] = f16(x[c] * 2^-S); *rs = 2^S.  xsrc: the raw 16-bit row (bf16 if x_bf16, else f16),
+// 16-byte aligned, K % 8 == 0.  Layout at xs_base: K halves, the scale, 32 floats of scratch.
+// Every thread of the CTA calls it (it contains CTA barriers).
+template <int PERM>
+__device__ __forceinline__ void cta_prepare_row(uint8_t* xs_base, const uint16_t* __restrict__ xsrc, int x_bf16, int K) {
+  __half* xs = reinterpret_cast<__half*>(xs_base);
+  float* rs_s = reinterpret_cast<float*>(xs_base + (size_t)K * 2);
+  float* red = rs_s + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const uint4* xv = reinterpret_cast<const uint4*>(xsrc);
+  auto widen = [&](uint16_t b) {
+    return x_bf16 ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
+  };
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    const uint4 v = __ldg(xv + i);
+    const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = fabsf(widen(e[j]));
+      if (a < 3.0e38f) amax = fmaxf(amax, a);          // inf / nan do not choose the scale
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int i = 0; i < nwarps; ++i) amax = fmaxf(amax, red[i]);
+  int S = 0;
+  if (amax > 0.f) {
+    S = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 14;
+    S = max(-110, min(110, S));
+  }
+  const float down = __uint_as_float((uint32_t)(127 - S) << 23);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    const uint4 v = __ldg(xv + i);
+    const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+    const int c0 = 8 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      xs[(c0 & ~31) + perm_position(PERM, (c0 & 31) + j)] = __float2half_rn(widen(e[j]) * down);
+  }
+  if (threadIdx.x == 0) *rs_s = __uint_as_float((uint32_t)(127 + S) << 23);
+  __syncthreads();
+}
+constexpr size_t cta_prepared_row_bytes(size_t K) { return K * 2 + 4 + 32 * 4; }
+
 // ---- group processors: one GROUP of columns for this thread's rows ---------------------------------
 // s[r]: shared address of column 0 of the group in row slot r (r = 0,1: rows g, g+8 of the gate /
 // only matrix; r = 2,3: the same rows of the up matrix).  The thread's prepared activations of the
