@@ -469,6 +469,7 @@ lmh_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __half* __rest
                   uint32_t seed, const LmhMask mask, int* __restrict__ err_flag) {
   using F = StreamFmt<FMT>;
   using C = LmhCfg<FMT>;
+  asm volatile("griddepcontrol.launch_dependents;");   // the merge stage may be scheduled; it waits for this grid's end
   constexpr int NW = 256 / WROWS;             // warps per CTA
   constexpr int NSETS = WROWS / 16;
   using WS = WarpStream<FMT, C::KC, WROWS, C::STAGES>;
@@ -975,6 +976,9 @@ lmh_reduce_kernel(const float* __restrict__ cand_val, const int32_t* __restrict_
                   int topk, float invtemp, uint32_t seed, float top_p, int32_t* __restrict__ ids,
                   int emit_set, float* __restrict__ out_val, int32_t* __restrict__ out_id) {
   __shared__ BlockScratch S;
+  // Programmatic dependent launch: this grid may be scheduled while the kernel before it (stage 1, or the
+  // exchange) still runs; nothing is read or written before that kernel has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int t = blockIdx.x;
   const int tid = threadIdx.x, nth = blockDim.x;
   // candidates of row t: shard s contributes ncand_s entries at (s*shard_stride + t*ncand_s + j)
@@ -1311,9 +1315,25 @@ void launch_lm_head_reduce(cudaStream_t st, const float* cand_val, const int32_t
     }
   }
   const long long stride_l = shard_stride > 0 ? shard_stride : (long long)T * (nlse > 0 ? nlse : 1);
-  lmh_reduce_kernel<<<(unsigned)T, LMH_RED_THREADS, smem, st>>>(
-      cand_val, cand_id, cand_lse, shards, (int)T, (long long)ncand, (long long)(nlse > 0 ? nlse : 1),
-      stride_c, stride_l, cache_elems, mode, topk, invtemp, seed, top_p, ids, emit_set, out_val, out_id);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)T);
+  cfg.blockDim = dim3(LMH_RED_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const long long ncand_a = (long long)ncand, nlse_a = (long long)(nlse > 0 ? nlse : 1);
+  if (cudaLaunchKernelEx(&cfg, lmh_reduce_kernel, cand_val, cand_id, cand_lse, shards, (int)T, ncand_a, nlse_a,
+                         (long long)stride_c, (long long)stride_l, cache_elems, mode, topk, invtemp, seed, top_p, ids,
+                         emit_set, out_val, out_id) != cudaSuccess) {
+    cudaGetLastError();
+    lmh_reduce_kernel<<<(unsigned)T, LMH_RED_THREADS, smem, st>>>(
+        cand_val, cand_id, cand_lse, shards, (int)T, ncand_a, nlse_a, stride_c, stride_l, cache_elems, mode, topk,
+        invtemp, seed, top_p, ids, emit_set, out_val, out_id);
+  }
   note_launch();
 }
 

@@ -134,6 +134,7 @@ tc_pipeline_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   constexpr int CW = BN / 4;                      // hidden rows per worker warp in its scale role
   constexpr int RST = C::RST;
   extern __shared__ uint8_t smem_dyn[];
+  asm volatile("griddepcontrol.launch_dependents;");   // a programmatic dependent may be scheduled; it waits for this grid's end
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
