@@ -191,6 +191,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
   constexpr int NACC = NSETS * NT * 4;
 
   extern __shared__ __align__(128) uint8_t smem_raw[];
+  asm volatile("griddepcontrol.launch_dependents;");   // a programmatic dependent may be scheduled; it waits for this grid's end
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
 

@@ -97,6 +97,11 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 peer_allreduce_kernel(const PeerSumRanks ranks, const PeerPtrs bufs, size_t n2, int world, int self0, int max_polls) {
+  // Programmatic dependent launch on both sides: this grid may be scheduled while the projection before it
+  // still runs (nothing is read or written before that kernel has completed), and the projection after it
+  // may be scheduled and fetch its first weights while this grid waits for the peers.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
   const PeerSumRank me = ranks.r[blockIdx.y];
   const int self = self0 + (int)blockIdx.y;
   const int s = *reinterpret_cast<volatile int*>(me.counter) + 1;
@@ -248,8 +253,22 @@ bool launch_peer_allreduce(cudaStream_t st, const float* const* src, const void*
   const void* fn = dtype == QX_DTYPE_F32 ? (const void*)peer_allreduce_kernel<float>
                    : dtype == QX_DTYPE_F16 ? (const void*)peer_allreduce_kernel<__half>
                                            : (const void*)peer_allreduce_kernel<__nv_bfloat16>;
-  cudaError_t e = local_ranks > 1 ? cudaLaunchCooperativeKernel(fn, grid, dim3(256), args, 0, st)
-                                  : cudaLaunchKernel(fn, grid, dim3(256), args, 0, st);
+  cudaError_t e;
+  if (local_ranks > 1) {
+    e = cudaLaunchCooperativeKernel(fn, grid, dim3(256), args, 0, st);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelExC(&cfg, fn, args);
+    if (e != cudaSuccess) { cudaGetLastError(); e = cudaLaunchKernel(fn, grid, dim3(256), args, 0, st); }
+  }
   if (e != cudaSuccess) { cudaGetLastError(); return false; }
   note_launch();
   return true;
