@@ -27,6 +27,8 @@ struct PeerPtrs { void* p[PEER_MAX]; };
 __global__ void __launch_bounds__(256)
 peer_push_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs flags, size_t n16, int world, int self,
                  int step, unsigned* __restrict__ tickets) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");     // launched as a programmatic dependent of the producer of src
+  asm volatile("griddepcontrol.launch_dependents;");
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
     const uint4 v = src[i];
     for (int r = 0; r < world; ++r)
@@ -51,6 +53,8 @@ peer_push_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs flags, si
 
 __global__ void __launch_bounds__(32)
 peer_wait_kernel(const int* __restrict__ flags, int world, int self, int step, int max_polls, int* __restrict__ status) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
   const int r = threadIdx.x;
   bool ok = true;
   if (*reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier wait already ran out: do not wait again
@@ -162,6 +166,8 @@ struct PeerGatherRanks { PeerGatherRank r[PEER_MAX]; };
 __global__ void __launch_bounds__(256)
 peer_gather_kernel(const PeerGatherRanks ranks, const PeerPtrs words, size_t n2, int world, int self0, int step,
                    int max_polls) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");     // launched as a programmatic dependent of the producer of the slot
+  asm volatile("griddepcontrol.launch_dependents;");
   const PeerGatherRank me = ranks.r[blockIdx.y];
   const int self = self0 + (int)blockIdx.y;
   const bool may_wait = *reinterpret_cast<volatile int*>(me.status) == 0;
@@ -196,6 +202,22 @@ peer_gather_kernel(const PeerGatherRanks ranks, const PeerPtrs words, size_t n2,
 
 }  // namespace
 
+// Launch as a programmatic dependent of the kernel before it on the stream (plain launch if refused).
+static cudaError_t launch_dependent(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+  if (e != cudaSuccess) { cudaGetLastError(); e = cudaLaunchKernel(fn, grid, block, args, 0, st); }
+  return e;
+}
+
 bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
                       int world, int self, int step, unsigned* tickets) {
   if (world < 1 || world > PEER_MAX || bytes % 16 != 0 || ((uintptr_t)src & 15) != 0) return false;
@@ -208,13 +230,20 @@ bool launch_peer_push(cudaStream_t st, const void* src, size_t bytes, void* cons
   int blocks = (int)((n16 + 255) / 256);
   if (blocks > 2 * sm_count()) blocks = 2 * sm_count();
   if (blocks < 1) blocks = 1;
-  peer_push_kernel<<<blocks, 256, 0, st>>>((const uint4*)src, d, f, n16, world, self, step, tickets);
+  const uint4* src16 = (const uint4*)src;
+  size_t n16v = n16;
+  void* args[] = {&src16, &d, &f, &n16v, &world, &self, &step, &tickets};
+  if (launch_dependent((const void*)peer_push_kernel, dim3((unsigned)blocks), dim3(256), args, st) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
   note_launch();
   return true;
 }
 
 void launch_peer_wait(cudaStream_t st, const int* flags, int world, int self, int step, int max_polls, int* status) {
-  peer_wait_kernel<<<1, 32, 0, st>>>(flags, world, self, step, max_polls, status);
+  void* args[] = {&flags, &world, &self, &step, &max_polls, &status};
+  if (launch_dependent((const void*)peer_wait_kernel, dim3(1), dim3(32), args, st) != cudaSuccess) cudaGetLastError();
   note_launch();
 }
 
@@ -257,17 +286,7 @@ bool launch_peer_allreduce(cudaStream_t st, const float* const* src, const void*
   if (local_ranks > 1) {
     e = cudaLaunchCooperativeKernel(fn, grid, dim3(256), args, 0, st);
   } else {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(256);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelExC(&cfg, fn, args);
-    if (e != cudaSuccess) { cudaGetLastError(); e = cudaLaunchKernel(fn, grid, dim3(256), args, 0, st); }
+    e = launch_dependent(fn, grid, dim3(256), args, st);
   }
   if (e != cudaSuccess) { cudaGetLastError(); return false; }
   note_launch();
@@ -303,7 +322,7 @@ bool launch_peer_gather(cudaStream_t st, float* const* gather, size_t slot_float
   dim3 grid((unsigned)chunks, (unsigned)local_ranks);
   void* args[] = {&ranks, &w, &n2, &world, &self0, &step, &max_polls};
   cudaError_t e = local_ranks > 1 ? cudaLaunchCooperativeKernel((const void*)peer_gather_kernel, grid, dim3(256), args, 0, st)
-                                  : cudaLaunchKernel((const void*)peer_gather_kernel, grid, dim3(256), args, 0, st);
+                                  : launch_dependent((const void*)peer_gather_kernel, grid, dim3(256), args, st);
   if (e != cudaSuccess) { cudaGetLastError(); return false; }
   note_launch();
   return true;
