@@ -385,7 +385,10 @@ def neighbour_sweep(device, peak_gbs: float):
 
 
 def _graph_ms(step, copies: int, reps: int = 5):
-    """Per-call time of `step` replayed from a CUDA graph that holds one call per weight copy."""
+    """Per-call time of `step` replayed from a CUDA graph that cycles over the weight copies; the graph
+    holds at least 16 calls (a serving graph holds hundreds of kernels), so that the launch of the graph
+    itself is not what is measured."""
+    calls = copies * max(1, -(-16 // copies))
     for i in range(3):
         step(i)
     torch.cuda.synchronize()
@@ -395,7 +398,7 @@ def _graph_ms(step, copies: int, reps: int = 5):
             step(i)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=st):
-            for i in range(copies):
+            for i in range(calls):
                 step(i)
     torch.cuda.synchronize()
     for _ in range(2):
@@ -406,7 +409,7 @@ def _graph_ms(step, copies: int, reps: int = 5):
     for _ in range(reps):
         g.replay()
     e1.record(); torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / (reps * copies)
+    return e0.elapsed_time(e1) / (reps * calls)
 
 
 def gemv_sweep(device, peak_gbs: float):
@@ -480,18 +483,19 @@ def gemv_sweep(device, peak_gbs: float):
             with torch.cuda.stream(side):
                 for i in range(copies):
                     step(i)
+                calls = copies * max(1, -(-16 // copies))     # at least 16 calls per graph, cycling over the copies
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
-                    for i in range(copies):
+                    for i in range(calls):
                         step(i)
             torch.cuda.current_stream().wait_stream(side)
             graph.replay(); torch.cuda.synchronize()
-            reps = max(2, 40 // copies)
+            reps = max(2, 80 // calls)
             e0.record()
             for _ in range(reps):
                 graph.replay()
             e1.record(); torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / (reps * copies)
+            ms = e0.elapsed_time(e1) / (reps * calls)
             del graph
         except Exception as exc:   # keep the eager number if capture is not possible
             print(f"graph capture skipped for {fmt} M={M}: {exc}", file=sys.stderr)
