@@ -1,6 +1,6 @@
-"""Multi-GPU forms of the path: one process per GPU; the LM head's small exchange step runs on
-this library's own peer-store kernels over NVLink (symmetric allocation), torch.distributed (NCCL)
-is the fallback for it and carries the projection stack's all-reduces.
+"""Multi-GPU forms of the path: one process per GPU; the LM head's exchange step and the projection
+stack's all-reduces of decode-sized partials run on this library's own peer-store kernels over NVLink
+(symmetric allocations); torch.distributed (NCCL) is the fallback and carries large all-reduces.
 
 Vocabulary-parallel `lm_head_sample`: the vocabulary is cut at multiples of 256 so that every
 256-row tile of the reference's top-p pool lives on one GPU; each rank runs stage 1 on its rows
@@ -260,8 +260,9 @@ class VocabParallelLMHead:
                                        top_p)
 
     def _sample_peer(self, st, h, m, kk, T, per, temperature, seed, top_p):
-        """Stage 1 into this rank's slot, push of the slot to every peer, bounded wait for the peers'
-        flags, stage 2 - one library call, all on the current stream, no collective call."""
+        """Stage 1 into this rank's slot, exchange of the slots (small slots: one launch whose 16-byte
+        words carry the step number; large ones: push of the slot to every peer, then a bounded wait
+        for the peers' flags), stage 2 - one library call, all on the current stream, no collective."""
         import ctypes
         self._x.step += 1
         step, stride, W = self._x.step, st["stride"], self.world
