@@ -182,6 +182,11 @@ struct BQStreamParams {
   int experts;
   int nst;              // ring depth per warp
   int* err;
+  // XS instantiation (one activation column): the raw 16-bit activations, prepared by every CTA itself
+  // into shared memory at byte offset xs_off of the dynamic window (x16 / rowscale unused)
+  const uint16_t* xsrc;
+  int x_bf16;
+  unsigned xs_off;
 };
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
@@ -269,15 +274,29 @@ struct BQCursor {
 // with c the 32-column chunks, P the tensor-core partial over the subnormal codes (= 2^-24 * sum
 // code * x), S[c,n] the sum of the 32 prepared activations, beta = bias (asymmetric) or
 // -2^(BITS-1) * scale (symmetric).
-template <int BITS, int NC>
+template <int BITS, int NC, bool XS>
 __global__ void __launch_bounds__(bq_warps(BITS) * 32, 1)
 base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                      const __grid_constant__ CUtensorMap map2, const BQStreamParams p) {
   using G = BQGeom<BITS>;
   extern __shared__ __align__(128) uint8_t bq_smem[];
+  // a programmatic dependent of the kernel before it: nothing of its output is touched before this point
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;");
   const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int K = p.K, nchunks = K / 32, nst = p.nst;
+  // prepared activations and row scales: global (preparation kernel), or with XS this CTA's own copy of
+  // the single column in shared memory (read through generic addresses)
+  const __half* x16 = p.x16;
+  const float* rowscale = p.rowscale;
+  if constexpr (XS) {
+    static_assert(NC == 1, "in-kernel preparation: one activation column");
+    cta_prepare_row<5>(bq_smem + p.xs_off, p.xsrc, p.x_bf16, K);
+    x16 = reinterpret_cast<const __half*>(bq_smem + p.xs_off);
+    rowscale = reinterpret_cast<const float*>(bq_smem + p.xs_off + (size_t)K * 2);
+  }
+  auto ldx = [](const uint4* q) { if constexpr (XS) return *q; else return __ldg(q); };
   const int spt1 = (K + BQ_KC - 1) / BQ_KC;
   const int mats = p.mode == 1 ? 2 : 1;
   const int spt = mats * spt1;
@@ -302,10 +321,10 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     const int c = i >> 3, n = i & 7;
     float s = 0.f;
     if (n < ncol && c < nchunks) {
-      const uint4* xp = reinterpret_cast<const uint4*>(p.x16 + (size_t)(col0 + n) * K + (size_t)c * 32);
+      const uint4* xp = reinterpret_cast<const uint4*>(x16 + (size_t)(col0 + n) * K + (size_t)c * 32);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint4 v = __ldg(xp + q);
+        const uint4 v = ldx(xp + q);
         const float2 a = f16x2_to_f32(v.x), b = f16x2_to_f32(v.y), c2 = f16x2_to_f32(v.z), d = f16x2_to_f32(v.w);
         s += ((a.x + a.y) + (b.x + b.y)) + ((c2.x + c2.y) + (d.x + d.y));
       }
@@ -447,7 +466,7 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     const uint32_t base = myring + slot * G::BOX_BYTES;
     const uint32_t rowA = base + g * G::PITCH + t * BITS, rowB = rowA + 8 * G::PITCH;
     // lanes whose column does not exist read column 0: their D columns are never written out
-    const __half* xr = p.x16 + (size_t)(col0 + (g < ncol ? g : 0)) * K + (size_t)stage * BQ_KC + 8 * t;
+    const __half* xr = x16 + (size_t)(col0 + (g < ncol ? g : 0)) * K + (size_t)stage * BQ_KC + 8 * t;
     const int nch = min(16, nchunks - stage * 16);
     auto chunk = [&](int c, const uint4& bv) {
       uint32_t pa[4], pb[4];
@@ -465,17 +484,17 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
     if (nch == 16) {                               // a whole stage: no branches, the activation loads 4 chunks ahead
       uint4 bq[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) bq[c] = __ldg(reinterpret_cast<const uint4*>(xr + c * 32));
+      for (int c = 0; c < 4; ++c) bq[c] = ldx(reinterpret_cast<const uint4*>(xr + c * 32));
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
         const uint4 bv = bq[c & 3];
-        if (c + 4 < 16) bq[c & 3] = __ldg(reinterpret_cast<const uint4*>(xr + (c + 4) * 32));
+        if (c + 4 < 16) bq[c & 3] = ldx(reinterpret_cast<const uint4*>(xr + (c + 4) * 32));
         chunk(c, bv);
       }
     } else {
 #pragma unroll
       for (int c = 0; c < 16; ++c)
-        if (c < nch) chunk(c, __ldg(reinterpret_cast<const uint4*>(xr + c * 32)));
+        if (c < nch) chunk(c, ldx(reinterpret_cast<const uint4*>(xr + c * 32)));
     }
     __syncwarp();
     if (issued < n_items) { issue(issued); ++issued; }
@@ -530,7 +549,7 @@ base_q_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_cons
       const float gsum = atomicExch(red + rs * 256 + idx, 0.f);
       const float usum = mats == 2 ? atomicExch(red + rs * 256 + 128 + idx, 0.f) : 0.f;
       if (n < ncol && trow0 + r < so.rows) {
-        const float sc = __ldg(p.rowscale + col0 + n);
+        const float sc = rowscale[col0 + n];
         const float v = mats == 2 ? silu(gsum * sc) * (usum * sc) : gsum * sc;
         bq_store(so.out, (long long)(trow0 + r) * p.orow + (long long)(col0 + n) * p.ocol, v, p.out_dtype);
       }
@@ -570,20 +589,34 @@ size_t base_q_scratch_bytes(int64_t K, int64_t M, qx_dtype dtype, bool x_is_km) 
   return n;
 }
 
-template <int BITS, int NC>
+template <int BITS, int NC, bool XS>
 static bool bq_launch_stream_nc(cudaStream_t st, const CUtensorMap* maps, const BQStreamParams& p, int gx, int gy,
                                 int warps, size_t smem) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(base_q_stream_kernel<BITS, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(base_q_stream_kernel<BITS, NC, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
     attr_set[dev] = true;
   }
-  base_q_stream_kernel<BITS, NC><<<dim3(gx, gy), warps * 32, smem, st>>>(maps[0], maps[1], maps[2], p);
+  // a programmatic dependent of the kernel before it (see griddepcontrol.wait in the kernel)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(gx, gy);
+  cfg.blockDim = dim3(warps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, base_q_stream_kernel<BITS, NC, XS>, maps[0], maps[1], maps[2], p) != cudaSuccess) {
+    cudaGetLastError();
+    base_q_stream_kernel<BITS, NC, XS><<<dim3(gx, gy), warps * 32, smem, st>>>(maps[0], maps[1], maps[2], p);
+  }
   note_launch();
   return true;
 }
@@ -591,9 +624,10 @@ static bool bq_launch_stream_nc(cudaStream_t st, const CUtensorMap* maps, const 
 template <int BITS>
 static bool bq_launch_stream(cudaStream_t st, const CUtensorMap* maps, const BQStreamParams& p, int gx, int gy,
                              int warps, size_t smem) {
-  if (p.M == 1) return bq_launch_stream_nc<BITS, 1>(st, maps, p, gx, gy, warps, smem);
-  if (p.M <= 4) return bq_launch_stream_nc<BITS, 4>(st, maps, p, gx, gy, warps, smem);
-  return bq_launch_stream_nc<BITS, 8>(st, maps, p, gx, gy, warps, smem);
+  if (p.M == 1 && p.xsrc) return bq_launch_stream_nc<BITS, 1, true>(st, maps, p, gx, gy, warps, smem);
+  if (p.M == 1) return bq_launch_stream_nc<BITS, 1, false>(st, maps, p, gx, gy, warps, smem);
+  if (p.M <= 4) return bq_launch_stream_nc<BITS, 4, false>(st, maps, p, gx, gy, warps, smem);
+  return bq_launch_stream_nc<BITS, 8, false>(st, maps, p, gx, gy, warps, smem);
 }
 
 // One launch over up to three weight matrices (mode 0) or a gate / up pair (mode 1).  x: (K, M) when
@@ -621,9 +655,18 @@ bool launch_base_q_matmul(cudaStream_t st, const BaseQDesc& d, const BaseQMat* m
     }
     __half* x16 = (__half*)ws;
     float* rowscale = (float*)(ws + bq_align256((size_t)M * K * 2));
-    launch_prep_activations(st, xr, dtype, x16, rowscale, (int)M, (int)K, 5);
-    note_launch();
     BQStreamParams p{};
+    // one activation column whose prepared copy fits behind the rings: every CTA prepares it itself
+    const size_t xs_off = (smem + 15) & ~(size_t)15;
+    if (M == 1 && !ex && xs_off + cta_prepared_row_bytes((size_t)K) <= 227 * 1024) {
+      p.xsrc = (const uint16_t*)xr;
+      p.x_bf16 = dtype == QX_DTYPE_BF16;
+      p.xs_off = (unsigned)xs_off;
+      smem = xs_off + cta_prepared_row_bytes((size_t)K);
+    } else {
+      launch_prep_activations(st, xr, dtype, x16, rowscale, (int)M, (int)K, 5);
+      note_launch();
+    }
     CUtensorMap maps[3];
     const int pitch = BQ_KC * d.bits / 8 + 16;
     int tiles = 0;
