@@ -314,7 +314,15 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap0, const __grid_const
     typename GP::template BFrag<NT> bcur, bnext;
     if (PRE && ngroups > 0) GP::template load_b<NT>(xr, col_base, t, bcur);
     constexpr int FULL = Cfg::KC / F::GROUP;
-    if (QX_STREAM_UNROLL >= NT && ngroups == FULL) {
+    if constexpr (NT > 2 && GP::PIPED) {
+      uint4 bcar[NT];                             // 32 rows: the fragments of the next unit, fetched one unit ahead
+      if (ngroups > 0) GP::template load_first<NT>(xr, col_base, t, bcar);
+      for (int gi = 0; gi < ngroups; ++gi) {
+        GP::template piped<NSETS, NT, 0>(s, t, xr, col_base + gi * F::GROUP, gi + 1 < ngroups, bcar, acc);
+#pragma unroll
+        for (int r = 0; r < 2 * NSETS; ++r) s[r] += GROUP_BYTES;
+      }
+    } else if (QX_STREAM_UNROLL >= NT && ngroups == FULL) {
       // a whole stage (every stage but the last of a ragged K): fully unrolled, so the shared-memory
       // offsets are immediates and the prefetched fragments need no register moves
 #pragma unroll
@@ -486,6 +494,8 @@ static bool launch_stream_f(cudaStream_t st, const GemvArgs& a) {
   constexpr bool H = FMT != F_Q6_K;                 // half-width stages where the format allows
   if (a.M <= 2 && !dual) return launch_stream_t<FMT, 1, false, false, T>(st, a);
   if (a.M <= 8) return dual ? launch_stream_t<FMT, 1, true, H, T>(st, a) : launch_stream_t<FMT, 1, false, H, T>(st, a);
+  // 17 - 32 rows of a single matrix in one pass (reached through the pass form below)
+  if (a.M > 16 && !dual) return launch_stream_t<FMT, 4, false, H, T>(st, a);
   // 9 - 16 rows, single matrix: full-width stages (the rings of fewer, wider stages keep more bytes in flight)
   return dual ? launch_stream_t<FMT, 2, true, H, T>(st, a) : launch_stream_t<FMT, 2, false, false, T>(st, a);
 }
@@ -536,6 +546,9 @@ bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a) {
 // a 70B-class block, any tensor-parallel shard) leaves most SMs idle there (N = 8192: 32 of 148),
 // while the streaming kernel spreads any N over all SMs.  Re-reading the weights once per pass is
 // cheaper than that as long as the passes are few (option "stream_passes": 0 never, 2 whenever possible).
+// rows per pass: 32 for a single matrix, 16 for a SwiGLU pair (twice the accumulators)
+static int stream_pass_rows(const GemvArgs& a) { return a.w1 ? 16 : 32; }
+
 bool stream_passes_ok(const GemvArgs& a) {
   const int mode = options().stream_passes;
   // q6_K has no tcgen05 pipeline form, so it takes passes up to 256 rows.
@@ -546,23 +559,25 @@ bool stream_passes_ok(const GemvArgs& a) {
   if (mode == 2 || a.format == F_Q6_K) return true;
   // passes win while the pipeline would leave most SMs without an item
   const long long items = (a.N + 255) / 256;          // work items of the tcgen05 pipeline
-  const int passes = (int)((a.M + 15) / 16);
+  const int per = stream_pass_rows(a);
+  const int passes = (int)((a.M + per - 1) / per);
   return (passes <= 2 && items <= 96) || items <= 48;
 }
 
 size_t stream_scratch_bytes(const GemvArgs& a) {
   int64_t rows = 0;
   if (stream_path_ok(a)) rows = a.M;
-  else if (stream_passes_ok(a)) rows = 16;
+  else if (stream_passes_ok(a)) rows = stream_pass_rows(a);
   if (rows == 0) return 0;
   return (((size_t)rows * a.K * 2 + 255) & ~(size_t)255) + (((size_t)rows * 4 + 255) & ~(size_t)255);
 }
 
 bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a) {
   const size_t out_size = a.out_f32 ? 4 : 2;
-  for (int64_t m0 = 0; m0 < a.M; m0 += 16) {
+  const int64_t per = stream_pass_rows(a);
+  for (int64_t m0 = 0; m0 < a.M; m0 += per) {
     GemvArgs b = a;
-    b.M = a.M - m0 < 16 ? a.M - m0 : 16;
+    b.M = a.M - m0 < per ? a.M - m0 : per;
     b.x = (const char*)a.x + (size_t)m0 * a.K * 2;
     b.y = (char*)a.y + (size_t)m0 * a.N * out_size;
     if (a.residual) b.residual = (const char*)a.residual + (size_t)m0 * a.N * 2;
