@@ -538,7 +538,7 @@ uint64_t qx_cuda_launch_count(void);
 int qx_cuda_device_error(void);
 /* Chooses between device paths that compute the same result (identical up to fp32 summation
  * order); meant for tests and A/B timing.  Names: "stream_passes" (0 never / 1 when faster / 2
- * whenever possible: 17 - 64 rows as 16-row passes of the streaming kernel instead of the tcgen05
+ * whenever possible: 17 - 64 rows as passes (32 rows; 16 for a SwiGLU pair) of the streaming kernel instead of the tcgen05
  * pipeline), "force_generic", "tc_pipeline", "lm_head_ksplit" (0 / 1).  Returns
  * 1 if the option exists and took the value.  Process-wide, not synchronised with running calls. */
 int qx_cuda_set_option(const char* name, int value);

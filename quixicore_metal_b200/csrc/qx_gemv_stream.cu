@@ -541,7 +541,7 @@ bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a) {
   return launch_stream_dt<__nv_bfloat16>(st, a);
 }
 
-// Batches of 17 - 64 rows as passes of 16 rows through the streaming kernel.  The tcgen05 pipeline
+// Batches of 17 - 64 rows as passes of 32 rows (16 for a SwiGLU pair) through the streaming kernel.  The tcgen05 pipeline
 // gives every CTA one item of 256 weight rows; a projection with few such items (O / down / QKV of
 // a 70B-class block, any tensor-parallel shard) leaves most SMs idle there (N = 8192: 32 of 148),
 // while the streaming kernel spreads any N over all SMs.  Re-reading the weights once per pass is

@@ -35,7 +35,7 @@ enum OutQuant : int { OQ_NONE = 0, OQ_FP8 = 1, OQ_INT8 = 2, OQ_MXFP8 = 3 };
 // Switches between device paths that compute the same result (identical up to fp32 summation
 // order).  Defaults are the measured-fastest choices; qx_cuda_set_option changes them.
 struct Options {
-  int stream_passes = 1;        // 17 - 64 rows as 16-row passes: 0 never, 1 when faster, 2 whenever possible
+  int stream_passes = 1;        // 17 - 64 rows as passes of the streaming kernel: 0 never, 1 when faster, 2 whenever possible
   bool force_generic = false;   // keep every call on the shape-generic kernels
   bool tc_pipeline = true;      // batch > 16 on the tcgen05 pipeline
   bool lm_head_ksplit = true;   // share the items of a partial round over K between CTAs
@@ -51,7 +51,7 @@ void launch_gemv_generic(cudaStream_t st, const GemvArgs& a);
 // Streaming tensor-core path (bf16 activations, batch <= 16, 16-byte aligned bases).
 bool stream_path_ok(const GemvArgs& a);
 bool launch_gemv_stream(cudaStream_t st, const GemvArgs& a);
-// The same kernel in passes of 16 rows for batches of 17 - 64 rows, when that beats the tcgen05 path.
+// The same kernel in passes of 32 / 16 rows for batches of 17 - 64 rows, when that beats the tcgen05 path.
 bool stream_passes_ok(const GemvArgs& a);
 bool launch_gemv_stream_passes(cudaStream_t st, const GemvArgs& a);
 // tcgen05 path (bf16 activations, batch > 16, K % 256 == 0, single weight matrix).
