@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .tk import _LM_HEAD_MODES, _LM_QUANT_BLOCK_K
-from .tk_torch import _DT, _check, _check_lm_head, _ptr, _same_device, _stream, _workspace
+from .tk_torch import _DT, _check, _check_lm_head, _guard, _ptr, _same_device, _stream, _workspace
 
 TILE_V = 256
 
@@ -74,7 +74,7 @@ def lm_head_shard_partials(h, wq_local, bias_local, vocab_offset: int, max_tiles
     T = h.size(0)
     C, L = candidate_layout(m, kk, max_tiles)
     lib = _lib.lib()
-    with torch.cuda.device(h.device):
+    with _guard(h.device):
         hc, wc = h.contiguous(), wq_local.contiguous()
         bc = None
         if bias_local is not None and bias_local.numel() > 1:
@@ -104,7 +104,7 @@ def lm_head_reduce_gathered(gathered, shards: int, T: int, max_tiles: int, mode,
     C, L = candidate_layout(m, kk, max_tiles)
     per = T * (2 * C + L)
     g = gathered.view(-1)
-    with torch.cuda.device(gathered.device):
+    with _guard(gathered.device):
         # the planar per-shard buffers are read in place: values, ids and lses start at fixed
         # offsets of shard 0 and every further shard lies `per` elements on
         base = g.data_ptr()
@@ -295,7 +295,7 @@ class VocabParallelLMHead:
         V_local, K, bias32, ws_bytes = self._head_cache[hk]
         _check(h.size(1) == K and temperature > 0.0, "lm_head_sample_q: h must be (T, K), temperature positive")
         base, dst = st["calls"][par]
-        with torch.cuda.device(h.device):
+        with _guard(h.device):
             hc = h.contiguous()
             ws = _workspace(h.device, ws_bytes)
             ids = torch.empty(T, dtype=torch.int32, device=h.device)
@@ -398,7 +398,7 @@ class TPDecodeStack:
         L = _lib.lib()
         pc, xc = part.contiguous(), x.contiguous()
         out = torch.empty_like(xc)
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = _stream()
         _lib.check(L.qx_cuda_peer_allreduce(stream, pc.data_ptr(), xc.data_ptr(), out.data_ptr(), n, st["bptr"],
                                             self.world, self.rank, st["counter"].data_ptr(), st["tickets"].data_ptr(),
                                             st["status"].data_ptr(), _DT[x.dtype], 5000))

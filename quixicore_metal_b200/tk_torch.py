@@ -9,6 +9,8 @@ stream.  There is no eager / CPU fallback: a missing library or a non-CUDA tenso
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from . import _lib
@@ -18,8 +20,23 @@ _BLOCK = {"q4_0": (32, 18), "q8_0": (32, 34), "q6_K": (256, 210), "mxfp8": (32, 
           "nvfp4": (16, 9), "mxfp4": (32, 17)}
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_NULL_GUARD = contextlib.nullcontext()
+
+
 def _stream() -> int:
+    """Handle of torch's current stream on the current device (without building a Stream object: the
+    call is on the path of every eager operator, where a few microseconds of host time are visible)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+def _guard(device):
+    """Context that makes `device` current; free when it already is."""
+    if torch.cuda.current_device() == device.index:
+        return _NULL_GUARD
+    return torch.cuda.device(device)
 
 
 def _ptr(t) -> int:
@@ -47,7 +64,8 @@ _WS = {}
 def _workspace(device, nbytes: int):
     """Scratch tensor for calls on the current stream of `device`, reused by later calls on the same
     stream (they are ordered, so sharing it is safe) and grown geometrically."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, _raw_stream(device.index) if _raw_stream is not None
+           else torch.cuda.current_stream(device).cuda_stream)
     ws = _WS.get(key)
     if ws is None or ws.numel() < nbytes:
         size = max(int(nbytes), 1 << 20, 0 if ws is None else 2 * ws.numel())
@@ -112,7 +130,7 @@ def decode_linear_epilogue(x, weight, bias, residual, format="", activation=0,
     _check(not use_residual or (residual.is_cuda and residual.dim() == 2 and residual.size(0) == B
                                 and residual.size(1) == N and residual.dtype == x.dtype),
            "decode_linear_epilogue: residual must be (B,N) with x dtype")
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc, wc = x.contiguous(), weight.contiguous()
         bc = bias.contiguous() if use_bias else None
         rc = residual.contiguous() if use_residual else None
@@ -132,7 +150,7 @@ def decode_linear_partial(x, weight, format):
     N = _check_weight(x, weight, fmt, "decode_linear_partial")
     _same_device("decode_linear_partial", x, weight)
     B, K = x.shape
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc, wc = x.contiguous(), weight.contiguous()
         out = torch.empty((B, N), dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().qx_cuda_decode_linear_partial(
@@ -157,7 +175,7 @@ def decode_swiglu(x, gate_weight, up_weight, gate_bias, up_bias, format="", use_
                             and up_bias.size(0) == N),
            "decode_swiglu: both biases must be (N,) with x dtype")
     B, K = x.shape
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc, gc, uc = x.contiguous(), gate_weight.contiguous(), up_weight.contiguous()
         gb = gate_bias.contiguous() if use_bias else None
         ub = up_bias.contiguous() if use_bias else None
@@ -174,7 +192,7 @@ def _quantize_per_token(x, kind: int, name: str):
            f"{name}: x must be a non-empty CUDA fp32/fp16/bf16 tensor")
     D = x.size(-1)
     rows = x.numel() // D
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc = x.contiguous()
         codes = torch.empty(x.shape, dtype=torch.uint8 if kind == 0 else torch.int8, device=x.device)
         scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
@@ -200,7 +218,7 @@ def quantize_mxfp8_rows(x):
     _check(x.is_cuda and x.dtype in _DT and x.dim() == 2 and x.size(1) % 32 == 0 and x.numel() > 0,
            "quantize_mxfp8_rows: x must be CUDA (rows, D) fp32/fp16/bf16 with D % 32 == 0")
     rows, D = x.shape
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc = x.contiguous()
         blocks = torch.empty((rows, D // 32, 33), dtype=torch.uint8, device=x.device)
         _lib.check(_lib.lib().qx_cuda_quantize_mxfp8_rows(
@@ -240,7 +258,7 @@ def lm_head_sample_q(h, Wq, bias, V, K, fmt, mode, topk, temperature, seed, top_
     use_bias = bias is not None and bias.numel() > 1
     if use_bias:
         _check(bias.numel() == V, "lm_head_sample_q: bias must be (V,)")
-    with torch.cuda.device(h.device):
+    with _guard(h.device):
         hc, wc = h.contiguous(), Wq.contiguous()
         bc = bias.to(torch.float32).contiguous() if use_bias else None
         out = torch.empty((T,), dtype=torch.int32, device=h.device)
@@ -271,7 +289,7 @@ def lm_head_sample(h, W, bias, mode, k, temperature, seed):
     if mode == 2:
         _check(1 <= k <= 64, "lm_head_sample: topk k must be in [1, 64]")
         _check(k <= V, "lm_head_sample: topk k must be <= vocab size V")
-    with torch.cuda.device(h.device):
+    with _guard(h.device):
         hc, wc = h.contiguous(), W.contiguous()
         bc = bias.to(torch.float32).contiguous() if use_bias else None
         out = torch.empty((T,), dtype=torch.int32, device=h.device)
@@ -289,7 +307,7 @@ def _sample_logits(logits, kind: int, name: str, k=0, p=1.0, temperature=1.0, se
            f"{name}: logits must be a non-empty CUDA fp32/fp16/bf16 tensor")
     V = logits.size(-1)
     rows = logits.numel() // V
-    with torch.cuda.device(logits.device):
+    with _guard(logits.device):
         lc = logits.contiguous()
         out = torch.empty(logits.shape[:-1], dtype=torch.int32, device=logits.device)
         _lib.check(_lib.lib().qx_cuda_sample_logits(
@@ -349,7 +367,7 @@ def lm_head_masked(h, W, bias, allow_mask, format="", topk=1, normalize_allowed=
     _check(not use_bias or (bias.dim() == 1 and bias.size(0) == V),
            "lm_head_masked: bias must be (V,) or scalar placeholder")
     _same_device("lm_head_masked", h, W, allow_mask, bias if use_bias else None)
-    with torch.cuda.device(h.device):
+    with _guard(h.device):
         hc, wc = h.contiguous(), W.contiguous()
         bc = bias.to(torch.float32).contiguous() if use_bias else None
         mc = allow_mask.to(torch.int32).contiguous()
@@ -377,7 +395,7 @@ def lm_head_candidates(h, W, bias, candidate_ids, offsets, format="", topk=1):
     _check(not use_bias or (bias.dim() == 1 and bias.size(0) == V),
            "lm_head_candidates: bias must be (V,) or scalar placeholder")
     _same_device("lm_head_candidates", h, W, candidate_ids, offsets, bias if use_bias else None)
-    with torch.cuda.device(h.device):
+    with _guard(h.device):
         hc, wc = h.contiguous(), W.contiguous()
         bc = bias.to(torch.float32).contiguous() if use_bias else None
         cc, oc = candidate_ids.to(torch.int32).contiguous(), offsets.to(torch.int32).contiguous()
@@ -415,7 +433,7 @@ def lm_head_beam_advance(h, Wq, bias, cum_log_probs, beam_width, fmt="q4_0"):
     _check(not use_bias or (bias.dim() == 1 and bias.size(0) == V),
            "lm_head_beam_advance: bias must be (V,) or a scalar placeholder")
     _same_device("lm_head_beam_advance", h, Wq, cum_log_probs, bias if use_bias else None)
-    with torch.cuda.device(h.device):
+    with _guard(h.device):
         hc, wc = h.contiguous(), Wq.contiguous()
         bc = bias.to(torch.float32).contiguous() if use_bias else None
         cc = cum_log_probs.to(torch.float32).contiguous()
@@ -444,7 +462,7 @@ def _qgemm(wq, x, format, name):
            f"{name}: wq (N,K/bk,bytes), x (K,M) with x rows == K")
     _same_device(name, wq, x)
     M = x.size(1)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         wc, xc = wq.contiguous(), x.contiguous()
         out = torch.empty((N, M), dtype=x.dtype, device=x.device)
         L = _lib.lib()
@@ -485,7 +503,7 @@ def quantized_embedding(table, ids, add, format, scale=1.0, use_add=False, outpu
     _check(not use_add or (add.dtype == dtype and tuple(add.shape) == shape),
            "quantized_embedding: add must match output shape and output_dtype")
     _same_device("quantized_embedding", table, ids, add if use_add else None)
-    with torch.cuda.device(table.device):
+    with _guard(table.device):
         tc, ic = table.contiguous(), ids.to(torch.int32).contiguous()
         ac = add.contiguous() if use_add else None
         out = torch.empty(shape, dtype=dtype, device=table.device)
@@ -509,7 +527,7 @@ def _rms_norm_add(x, residual, weight, eps, quant, static_scale=0.0, group=0, ue
            and weight.dtype == x.dtype, f"{name}: residual must match x, weight must be (D,) with x dtype")
     _same_device(name, x, residual, weight)
     rows = x.numel() // D
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc, rc, wc = x.contiguous(), residual.contiguous(), weight.contiguous()
         added = torch.empty_like(xc)
         y = torch.empty_like(xc) if quant == 0 else None
@@ -570,7 +588,7 @@ def _silu_mul_quant(x, gate, act, alpha, limit, quant, group=0, ue8m0=False, nam
     if quant == 4:
         _check(group > 0 and group % 4 == 0 and D % group == 0,
                f"{name}: group_size must be a multiple of 4 that divides D")
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc, gc = x.contiguous(), gate.contiguous()
         codes = torch.empty(x.shape, dtype=torch.int8 if quant == 3 else torch.uint8, device=x.device)
         sshape = tuple(x.shape[:-1]) + ((D // group,) if quant == 4 else ())
@@ -648,7 +666,7 @@ def base_qdequant(codes, scales, biases, bits, group_size, scale_dtype="bf16", s
     desc = _bq_desc(bits, group_size, scale_dtype, symmetric, layout)
     _check(str(output_dtype) in _BQ_OUT, "BaseQN: output_dtype must be float16, bfloat16, or float32")
     planes, keep, (rows,), K = _bq_planes("base_qdequant", codes, scales, biases, desc)
-    with torch.cuda.device(codes.device):
+    with _guard(codes.device):
         out = torch.empty((rows, K), dtype=_BQ_OUT[str(output_dtype)], device=codes.device)
         _lib.check(_lib.lib().qx_cuda_base_qdequant(_stream(), planes, desc, _ptr(out), rows, K, _DT[out.dtype]))
     return out
@@ -663,7 +681,7 @@ def base_qembedding(codes, scales, biases, ids, bits, group_size, scale_dtype="b
     _check(ids.is_cuda and ids.numel() > 0 and not ids.dtype.is_floating_point,
            "base_qembedding: ids must be a non-empty integer tensor")
     _same_device("base_qembedding", codes, ids)
-    with torch.cuda.device(codes.device):
+    with _guard(codes.device):
         ic = ids.to(torch.int32).contiguous()
         out = torch.empty(tuple(ids.shape) + (K,), dtype=_BQ_OUT[str(output_dtype)], device=codes.device)
         _lib.check(_lib.lib().qx_cuda_base_qembedding(_stream(), planes, desc, _ptr(ic), _ptr(out), rows, K,
@@ -679,7 +697,7 @@ def _bq_matmul(name, codes, scales, biases, x, desc, gemv_only):
     _check(x.size(1) > 0, "BaseQN matmul: M must be positive")
     _same_device(name, codes, x)
     M = x.size(1)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc = x.contiguous()
         out = torch.empty((rows, M), dtype=x.dtype, device=x.device)
         L = _lib.lib()
@@ -711,7 +729,7 @@ def base_qgemv_qkv(q_codes, q_scales, q_biases, k_codes, k_scales, k_biases, v_c
     _check(x.is_cuda and x.dim() == 2 and x.size(0) == K and x.size(1) == 1 and x.dtype in _DT,
            f"{name}: x must be (K, 1) float16, bfloat16, or float32")
     _same_device(name, q_codes, k_codes, v_codes, x)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc = x.contiguous()
         outs = [torch.empty((r, 1), dtype=x.dtype, device=x.device) for r in (qr, kr, vr)]
         L = _lib.lib()
@@ -732,7 +750,7 @@ def base_qgemv_swiglu(gate_codes, gate_scales, gate_biases, up_codes, up_scales,
     _check(x.is_cuda and x.dim() == 2 and x.size(0) == K and x.size(1) == 1 and x.dtype in _DT,
            f"{name}: x must be (K, 1) float16, bfloat16, or float32")
     _same_device(name, gate_codes, up_codes, x)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc = x.contiguous()
         out = torch.empty((rows, 1), dtype=x.dtype, device=x.device)
         L = _lib.lib()
@@ -753,7 +771,7 @@ def base_qlm_head_argmax(codes, scales, biases, x, bits, group_size, scale_dtype
     _check(x.is_cuda and x.size(0) == K and x.dtype in _DT, f"{name}: x must be (K, batch) with K matching the packed weights")
     _same_device(name, codes, x)
     batch = x.size(1)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         xc = x.contiguous()
         ids = torch.empty((batch,), dtype=torch.int32, device=x.device)
         L = _lib.lib()
@@ -774,7 +792,7 @@ def _bq_moe(name, codes, scales, biases, input, expert_of_tile, desc, swiglu):
     _check(not swiglu or expert_rows % 2 == 0, f"{name}: the gate/up row axis must be even")
     _same_device(name, codes, input, expert_of_tile)
     cols = expert_rows // 2 if swiglu else expert_rows
-    with torch.cuda.device(input.device):
+    with _guard(input.device):
         xc, ec = input.contiguous(), expert_of_tile.contiguous()
         out = torch.zeros((total, cols), dtype=input.dtype, device=input.device)
         L = _lib.lib()
