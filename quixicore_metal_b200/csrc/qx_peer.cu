@@ -1,19 +1,26 @@
-// Exchange of the per-shard LM-head candidates between GPUs by plain peer stores over NVLink,
-// in place of an all-gather: every rank copies its slot of the gather buffer into the same slot of
-// every peer's buffer (symmetric allocation), then publishes a step number in a flag word on every
-// peer; the merge stage of a rank starts once the flags of all peers carry the current step.
+// Exchanges between GPUs by plain peer stores over NVLink into symmetric allocations, in place of the
+// collectives of a decode step: the all-gather of the per-shard LM-head candidates and the all-reduce of
+// the row-parallel projections' fp32 partials.  No multicast / multimem is used.  Two forms:
 //
-//   push:  grid of copy CTAs; 16-byte loads from the local slot, one 16-byte store per peer.  Every
-//          CTA fences its stores system-wide and takes a ticket; the CTA that takes the last ticket
-//          fences again and writes the step number to flag[self] on every peer.
-//   wait:  one warp, lane r polls flag[r] (acquire, system scope) until it is at least the step
-//          number.  The wait is bounded: when it runs out the kernel writes 1 to *status and returns,
-//          so a missing peer costs the call its result but never hangs the GPU; later waits on the
-//          same status word return at once.
+//   flag-in-data (peer_gather_kernel, peer_allreduce_kernel; small messages): every 16-byte store carries
+//          two floats and, beside each, the step number; the receiver polls the data words themselves.
+//          One launch, one NVLink crossing, no fence and no separate flag.  Described at the kernels.
+//   push + wait (peer_push_kernel, peer_wait_kernel; large slots, where doubling the bytes costs more
+//          than a fence): every rank copies its slot of the gather buffer into the same slot of every
+//          peer's buffer, then publishes the step number in a flag word on every peer; the merge stage
+//          of a rank starts once the flags of all peers carry the current step.
+//          push:  grid of copy CTAs; 16-byte loads from the local slot, one 16-byte store per peer.  Every
+//                 CTA fences its stores system-wide and takes a ticket; the CTA that takes the last
+//                 ticket fences again and writes the step number to flag[self] on every peer.
+//          wait:  one warp, lane r polls flag[r] (acquire, system scope) until it is at least the step.
 //
-// Buffers alternate between two halves by step parity: a peer may already push step n + 1 while this
-// rank still merges step n, but never step n + 2 (its merge of n + 1 needs this rank's push of n + 1,
-// which is enqueued behind this rank's merge of n).  No multicast / multimem is used.
+// Every wait is bounded: when it runs out the kernel writes 1 to *status and carries on, so a missing peer
+// costs the call its result but never hangs the GPU; later waits on the same status word return at once.
+// Buffers alternate between two halves by step parity: a peer may already send step n + 1 while this
+// rank still consumes step n, but never step n + 2 (that needs this rank's data of step n + 1, which is
+// enqueued behind this rank's consumer of n).  All kernels are programmatic dependent launches: they may
+// be scheduled while the producer of their input still runs and touch nothing before
+// griddepcontrol.wait; each lets its own dependent be scheduled as soon as it has started.
 #include "qx_common.cuh"
 #include "qx_kernels.h"
 
