@@ -111,6 +111,42 @@ def test_lm_head_validation_status_codes(L):
     assert _code(st) == "insufficient_workspace"
 
 
+def test_peer_exchange_validation_status_codes(L):
+    """The peer-store entries refuse bad arguments with the contract's codes before a device is touched."""
+    from quixicore_metal_b200 import _lib
+    p, bf16 = 0x1000, _lib.DTYPE_BF16
+    two = (C.c_void_p * 2)(p, p)
+
+    def allreduce(n=8192, world=2, rank=0, dtype=bf16, timeout=100, src=p, bufs=two):
+        return L.qx_cuda_peer_allreduce(None, src, p, p, n, bufs, world, rank, p, p, p, dtype, timeout)
+    assert _code(allreduce(src=None)) == "invalid_argument"
+    assert _code(allreduce(bufs=None)) == "invalid_argument"
+    assert _code(allreduce(world=17)) == "invalid_argument"
+    assert _code(allreduce(rank=2)) == "invalid_argument"
+    assert _code(allreduce(n=0)) == "invalid_shape"
+    assert _code(allreduce(n=7)) == "invalid_shape"
+    assert _code(allreduce(dtype=99)) == "unsupported_dtype"
+    assert _code(allreduce(timeout=0)) == "invalid_argument"
+    assert _code(allreduce(timeout=20000)) == "invalid_argument"
+
+    def gather(slot=64, world=2, rank=0, step=1, timeout=100, buf=p, words=two):
+        return L.qx_cuda_peer_gather(None, buf, slot, words, world, rank, step, timeout, p)
+    assert _code(gather(buf=None)) == "invalid_argument"
+    assert _code(gather(words=None)) == "invalid_argument"
+    assert _code(gather(world=0)) == "invalid_argument"
+    assert _code(gather(rank=-1)) == "invalid_argument"
+    assert _code(gather(slot=0)) == "invalid_shape"
+    assert _code(gather(slot=3)) == "invalid_shape"
+    assert _code(gather(timeout=0)) == "invalid_argument"
+    # the sharded LM-head call checks its slot geometry first
+    st = L.qx_cuda_lm_head_sample_sharded(None, p, p, None, p, p, 6, None, None, None, None, None, p, 2, 0, 1, 100, p, 1 << 30,
+                                          2, 512, 64, 0, 2, b"q8_0", bf16, 0, 0, 1.0, 0, 0.9)
+    assert _code(st) == "invalid_shape" and b"slot_stride" in st.detail
+    st = L.qx_cuda_lm_head_sample_sharded(None, p, p, None, p, p, 64, None, None, None, None, None, p, 2, 5, 1, 100, p, 1 << 30,
+                                          2, 512, 64, 0, 2, b"q8_0", bf16, 0, 0, 1.0, 0, 0.9)
+    assert _code(st) == "invalid_argument"
+
+
 def test_generic_dispatch_validation(L):
     from quixicore_metal_b200 import capi
     st = L.qx_cuda_dispatch(None, None)
