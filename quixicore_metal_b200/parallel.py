@@ -57,6 +57,20 @@ def candidate_layout(mode, k: int, max_tiles: int):
     return C, (max_tiles if m == 3 else 0)
 
 
+def candidate_exchange_form(per: int, world: int) -> str:
+    """How slots of `per` floats cross the ranks of the peer exchange: "words" (one launch, 16-byte
+    words that carry the step number: twice the bytes, no fence and no flag) while a rank sends at
+    most 1 MB, else "push" (plain stores, then a flag word)."""
+    stride = (per + 3) // 4 * 4
+    return "words" if 8 * stride * (world - 1) <= (1 << 20) else "push"
+
+
+def partial_sum_over_peers(n: int, world: int) -> bool:
+    """Whether fp32 partials of n floats are summed by the one-launch peer-store all-reduce: while a
+    rank sends at most 4 MB (8 bytes per float and peer); larger ones keep NCCL's algorithms."""
+    return n % 2 == 0 and 8 * n * (world - 1) <= (4 << 20)
+
+
 def lm_head_shard_partials(h, wq_local, bias_local, vocab_offset: int, max_tiles: int, fmt: str,
                            mode, k=0, temperature=1.0, seed=0, out=None):
     """Stage 1 on this shard's rows.  Returns one fp32 tensor (T, 2C + L) holding, per row,
@@ -201,7 +215,7 @@ class VocabParallelLMHead:
             # slots of a few KB (argmax / top-k candidates, the pools of one row) go as 16-byte words that
             # carry their own step number - one launch, one NVLink crossing; larger ones as plain
             # stores followed by a flag (half the bytes)
-            if 8 * stride * (self.world - 1) <= (1 << 20):
+            if candidate_exchange_form(per, self.world) == "words":
                 words = symm.empty(4 * self.world * stride, dtype=torch.float32, device=device)
                 words.zero_()
                 hw = symm.rendezvous(words, grp)
@@ -389,8 +403,8 @@ class TPDecodeStack:
         n = part.numel()
         # decode-sized partials are latency-bound: one-shot peer stores while a rank sends at most 4 MB
         # (8 bytes per float and peer); larger ones keep NCCL's bandwidth-optimal algorithms
-        small = 8 * n * (self.world - 1) <= (4 << 20) or self.exchange == "peer"
-        st = self._peer_sum_state(n, part.device) if (self.exchange in ("auto", "peer") and n % 2 == 0 and small) else None
+        small = partial_sum_over_peers(n, self.world) or (self.exchange == "peer" and n % 2 == 0)
+        st = self._peer_sum_state(n, part.device) if (self.exchange in ("auto", "peer") and small) else None
         self._last = "nccl" if st is None else "peer"
         if st is None:
             return (self._all_reduce(part) + x.float()).to(x.dtype)

@@ -96,3 +96,22 @@ def test_two_gloo_ranks_exchange_and_merge(mode):
             p.join(120)
         assert all(p.exitcode == 0 for p in procs)
         assert dict(out) == {0: True, 1: True}
+
+
+def test_exchange_form_follows_the_bytes_a_rank_sends():
+    """Small candidate slots travel as words that carry their step number, large ones as plain stores
+    plus a flag; decode-sized partial sums use the peer all-reduce, large ones NCCL."""
+    V, kk = 128256, 32
+    for world in (2, 4, 8):
+        tiles = parallel.max_shard_tiles(V, world)
+        for T, mode, want in ((1, 0, "words"), (64, 0, "words"), (64, 2, "words"), (1, 3, "words"), (64, 3, "push")):
+            C, L = parallel.candidate_layout(mode, 50 if mode == 2 else kk, tiles)
+            assert parallel.candidate_exchange_form(T * (2 * C + L), world) == want, (world, T, mode)
+    # the boundary: exactly 1 MB sent per rank still goes as words
+    assert parallel.candidate_exchange_form((1 << 20) // 8, 2) == "words"
+    assert parallel.candidate_exchange_form((1 << 20) // 8 + 4, 2) == "push"
+    hidden = 8192
+    assert parallel.partial_sum_over_peers(hidden * 1, 8) and parallel.partial_sum_over_peers(hidden * 8, 8)
+    assert not parallel.partial_sum_over_peers(hidden * 32, 8)
+    assert parallel.partial_sum_over_peers(hidden * 32, 2) and not parallel.partial_sum_over_peers(hidden * 128, 2)
+    assert not parallel.partial_sum_over_peers(7, 2)          # pairs of floats per word
